@@ -1,0 +1,110 @@
+// Shared device / host helpers for the conef_b200 kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include "conef.h"
+
+void conef_set_error(const char* fmt, ...);
+
+#define CONEF_CHECK_LAUNCH(name)                                              \
+  do {                                                                        \
+    cudaError_t e__ = cudaGetLastError();                                     \
+    if (e__ != cudaSuccess) {                                                 \
+      conef_set_error("%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+      return 1;                                                               \
+    }                                                                         \
+  } while (0)
+
+#define CONEF_CUDA(call)                                                      \
+  do {                                                                        \
+    cudaError_t e__ = (call);                                                 \
+    if (e__ != cudaSuccess) {                                                 \
+      conef_set_error("%s failed: %s", #call, cudaGetErrorString(e__));       \
+      return 1;                                                               \
+    }                                                                         \
+  } while (0)
+
+// Error codes written into the device status word by kernels whose waits ran out.
+enum {
+  CONEF_STATUS_OK = 0,
+  CONEF_STATUS_FLAG_TIMEOUT = 1,      // a peer never published the expected epoch
+  CONEF_STATUS_MBAR_TIMEOUT = 2,      // an mbarrier phase never completed
+  CONEF_STATUS_BAD_ARG = 3,
+};
+
+// Reference hash on signed 32-bit ints, done in uint32 so nothing overflows in
+// C++: wrapping multiply, explicit arithmetic shift, non-negative remainder.
+__host__ __device__ __forceinline__ uint32_t conef_sar(uint32_t h, int s) {
+  return (uint32_t)(((int32_t)h) >> s);  // arithmetic shift on every supported compiler
+}
+__host__ __device__ __forceinline__ int conef_hash(int value, int range, int a, int b) {
+  uint32_t h = (uint32_t)a * (uint32_t)value + (uint32_t)b;
+  h ^= conef_sar(h, 16);
+  h *= 0x85ebca6bu;
+  h ^= conef_sar(h, 13);
+  h *= 0xc2b2ae35u;
+  h ^= conef_sar(h, 16);   // sign bit is cleared here (x ^ (x >>arith 16) has a zero top bit)
+  return (int)(h % (uint32_t)range);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum of `v`; every thread gets the result.  `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+__device__ __forceinline__ float unpack_sign(int e) { return e < 0 ? 1.f : -1.f; }
+__device__ __forceinline__ int unpack_bucket(int e) { return e & 0x7fffffff; }
+
+// System-scope acquire load / release store for flags other GPUs write.
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ld_relaxed_sys_f32(const float* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Wait until flags[0..world) have all reached `epoch` (wrap-safe compare), at
+// most `limit` polls per flag.  Returns false when a wait ran out; the caller
+// records the failure and carries on without touching peer data.
+__device__ __forceinline__ bool wait_flags_bounded(const uint32_t* flags, int world, uint32_t epoch,
+                                                   long long limit) {
+  for (int p = 0; p < world; ++p) {
+    long long n = 0;
+    while ((int32_t)(ld_acquire_sys(flags + p) - epoch) < 0) {
+      if (++n > limit) return false;
+      __nanosleep(64);
+    }
+  }
+  return true;
+}

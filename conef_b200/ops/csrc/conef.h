@@ -1,0 +1,176 @@
+// C ABI of the conef_b200 native library (sm_100a).
+//
+// Every entry point takes raw device pointers plus the CUDA stream to launch
+// on, returns 0 on success and a non-zero code on failure (the message is
+// available through conef_last_error()).  Nothing here allocates device
+// memory except the functions whose name says so (conef_ipc_*); callers own
+// all buffers.  The Python package binds these with ctypes.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// One compressed (n x m) matrix living inside a flat gradient bucket.
+// Offsets are in elements.  The sketch of the matrix is an (n x W) block in a
+// flat sketch arena; its column hash table (m packed int32 entries:
+// bucket | sign<<31) and its per-bucket column counts (W entries) live in flat
+// int32 arenas.
+typedef struct ConefMat {
+  long long g_off;    // matrix start inside the bucket
+  long long p_off;    // (n x r) block inside the flat P memory
+  long long q_off;    // (m x r) block inside the flat Q memory
+  long long sk_off;   // (n x W) block inside the sketch arena (-1: none)
+  int n, m, r, W;
+  int tab_off;        // offset into the hash-table arena (-1: none)
+  int cnt_off;        // offset into the counts arena (-1: none)
+  int q_rows;         // rows per CTA row-block in the Q = M^T P kernel
+  int q_atomic;       // 1 if several row-blocks accumulate into Q
+} ConefMat;
+
+// A contiguous run of elements of the bucket (one uncompressed tensor, or the
+// selected part of a random block) and where it sits in a staging buffer.
+typedef struct ConefSeg {
+  long long src_off;  // offset inside the bucket
+  long long dst_off;  // offset inside the staging buffer
+  long long len;
+} ConefSeg;
+
+// One tensor handled by the random-block kernels, viewed as (n x m).
+typedef struct ConefBlk {
+  long long g_off;    // tensor start inside the bucket
+  long long numel;
+  long long start;    // first selected flat index
+  long long block;    // number of selected elements (wraps around to index 0)
+  long long stage_off;// offset of the block inside the staging buffer
+  long long sk_off;   // sketch arena offset, or offset into the dense / quantised error arena
+  int n, m, W;
+  int tab_off, cnt_off;
+  int scale_off;      // first scale slot of this tensor in the 8-bit store's scale array
+} ConefBlk;
+
+enum { CONEF_EF_NONE = 0, CONEF_EF_DENSE = 1, CONEF_EF_SKETCH = 2, CONEF_EF_QUANT8 = 3 };
+
+const char* conef_last_error(void);
+int conef_version(void);
+
+// ---- count sketch (sketch.cu) ---------------------------------------------
+int conef_build_hash_table(int32_t* table, int32_t* counts, int D, int W,
+                           int a, int b, int sa, int sb, cudaStream_t stream);
+int conef_sketch_query(float* mat, const void* cs, int cs_is_half, const int32_t* table,
+                       int N, int D, int W, float alpha, cudaStream_t stream);
+int conef_sketch_update(const float* vec, void* cs, int cs_is_half, const int32_t* table,
+                        const int32_t* counts, int N, int D, int W, float beta,
+                        cudaStream_t stream);
+int conef_sketch3_query(float* mat, const float* cs0, const float* cs1, const float* cs2,
+                        const int32_t* t0, const int32_t* t1, const int32_t* t2,
+                        int N, int D, int W, float alpha, cudaStream_t stream);
+int conef_sketch3_update(const float* vec, float* cs0, float* cs1, float* cs2,
+                         const int32_t* t0, const int32_t* t1, const int32_t* t2,
+                         int N, int D, int W, float beta, cudaStream_t stream);
+
+// ---- grouped PowerSGD pipeline, SIMT (powersgd.cu) --------------------------
+// P_i = (G_i + error_i) Q_i for every matrix of a bucket; the corrected
+// matrix is written back into the bucket when ef_mode != NONE.
+int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
+                 const float* sketch, const int32_t* tables, const float* dense_err,
+                 const float* Q, float* P, float alpha, int ef_mode, int max_rank,
+                 cudaStream_t stream);
+// Batched Gram-Schmidt over the (rows x r) blocks of a flat buffer.  which=0
+// orthogonalises the P blocks (n x r), which=1 the Q blocks (m x r).  With
+// world > 1 the kernel first waits (bounded) until every peer has published
+// `epoch` in flags[peer] and sums the peers' buffers (peer_bufs[0..world)) into
+// `buf`; status[0] becomes non-zero when a wait gives up.
+int conef_orthogonalize(const ConefMat* mats, int nmats, int which, float* buf, float eps,
+                        const float* const* peer_bufs, const uint32_t* flags, int world,
+                        uint32_t epoch, int* status, long long spin_limit, cudaStream_t stream);
+int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket,
+                 const float* P, float* Q, int max_rank, cudaStream_t stream);
+// M_hat = P Q^T written into the bucket; residual (M - M_hat) goes to the
+// error store selected by ef_mode (dense buffer or count sketch with decay).
+int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta,
+                          float* bucket, const float* P, const float* Q, float q_scale,
+                          float* sketch, const int32_t* tables, const int32_t* counts,
+                          float* dense_err, float beta, int ef_mode, int max_rank,
+                          size_t smem_bytes, cudaStream_t stream);
+// Philox-keyed standard normal fill: element e of the buffer depends only on
+// (seed, e), so every rank generates the same Q without communication.
+int conef_fill_normal(float* buf, long long numel, uint64_t seed, cudaStream_t stream);
+
+// ---- tcgen05 / TMEM / TMA tiles (powersgd_tc.cu) ----------------------------
+int conef_tc_supported(void);
+int conef_psgd_p_tc(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
+                    const float* sketch, const int32_t* tables, const float* dense_err,
+                    const float* Q, float* P, float alpha, int ef_mode, int* status,
+                    cudaStream_t stream);
+int conef_psgd_q_tc(const ConefMat* mats, const int4* tiles, int ntiles, const float* bucket,
+                    const float* P, float* Q, int* status, cudaStream_t stream);
+
+// ---- segments, random blocks, quantised error (blocks.cu) -------------------
+int conef_gather_segments(const ConefSeg* segs, int nsegs, const float* bucket,
+                          const float* dense_err, float* staging, long long total,
+                          cudaStream_t stream);
+// bucket[seg] = scale * sum_peers staging_peer[seg]; with dense_err != NULL the
+// pre-reduction local value minus the result is stored as the new error.
+int conef_scatter_segments(const ConefSeg* segs, int nsegs, float* bucket,
+                           const float* const* peer_staging, int world, const float* local_staging,
+                           float scale, float* dense_err, long long total, cudaStream_t stream);
+int conef_randblock_gather(const ConefBlk* blks, const int2* tiles, int ntiles, int rows_per_cta,
+                           float* bucket, float* staging, float gather_scale,
+                           float* sketch, const int32_t* tables, const int32_t* counts,
+                           float* dense_err, int8_t* qcodes, float* qscales,
+                           float alpha, float beta, int ef_mode, size_t smem_bytes,
+                           cudaStream_t stream);
+int conef_randblock_scatter(const ConefBlk* blks, int nblks, float* bucket,
+                            const float* const* peer_staging, int world,
+                            const float* local_staging, float scale, long long total_block,
+                            cudaStream_t stream);
+int conef_quant8_query(float* x, const int8_t* codes, const float* scales, long long numel,
+                       float alpha, cudaStream_t stream);
+int conef_quant8_update(const float* v, int8_t* codes, float* scales, long long numel,
+                        float beta, cudaStream_t stream);
+
+// ---- in-kernel collectives over peer memory (symm.cu) -----------------------
+// Publish `epoch` into slot `rank` of every peer's flag array.
+int conef_signal_peers(uint32_t* const* peer_flags, int world, int rank, uint32_t epoch,
+                       cudaStream_t stream);
+// out[i] = scale * sum_p peer_bufs[p][i] after a bounded wait on flags.
+int conef_allreduce_oneshot(float* out, const float* const* peer_bufs, uint32_t* const* peer_flags,
+                            const uint32_t* my_flags, int world, int rank, uint32_t epoch,
+                            long long numel, float scale, int* status, long long spin_limit,
+                            cudaStream_t stream);
+int conef_wait_flags(const uint32_t* my_flags, int world, uint32_t epoch, int* status,
+                     long long spin_limit, cudaStream_t stream);
+int conef_ipc_get_handle(void* dev_ptr, void* handle_out_64B);
+int conef_ipc_open_handle(const void* handle_64B, void** dev_ptr_out);
+int conef_ipc_close_handle(void* dev_ptr);
+
+// ---- multi-tensor LAMB (lamb.cu) --------------------------------------------
+typedef struct ConefLambTensor {
+  float* p;          // parameter (fp32)
+  float* g;          // gradient on entry; overwritten with the LAMB update direction
+  float* m;          // first moment
+  float* v;          // second moment
+  long long numel;
+  float weight_decay;
+  int pad;
+} ConefLambTensor;
+// norms: scratch of 1 + 2*ntensors floats ([0] squared global gradient norm,
+// [1+2t] squared parameter norm, [2+2t] squared update norm of tensor t).
+int conef_lamb_step(const ConefLambTensor* tensors, int ntensors, const int2* chunks, int nchunks,
+                    int chunk_elems, float* norms, float lr, float beta1, float beta2, float eps,
+                    int step, int bias_correction, float grad_scale, float max_grad_norm,
+                    cudaStream_t stream);
+
+// ---- host implementations (cpu_ops.cu) --------------------------------------
+void conef_cpu_hash_table(int32_t* table, int32_t* counts, int D, int W, int a, int b, int sa, int sb);
+void conef_cpu_sketch_query(float* mat, const float* cs, const int32_t* table, int N, int D, int W, float alpha);
+void conef_cpu_sketch_update(const float* vec, float* cs, const int32_t* table, const int32_t* counts,
+                             int N, int D, int W, float beta);
+void conef_cpu_gram_schmidt(float* mat, int rows, int cols, float eps);
+
+#ifdef __cplusplus
+}
+#endif

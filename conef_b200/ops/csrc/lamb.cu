@@ -1,0 +1,97 @@
+// Multi-tensor LAMB: every parameter tensor of the model in three launches.
+// Stands in for apex.optimizers.FusedLAMB, which the reference's BERT driver
+// imports (examples/BertPretraining/run_pretraining_conef.py:42,449-450) and
+// which is not available without apex.
+//   launch 1: squared global gradient norm (for clipping)
+//   launch 2: moments, update direction u = m_hat / (sqrt(v_hat) + eps) + wd * p,
+//             written over the gradient; squared norms of p and u per tensor
+//   launch 3: p -= lr * trust * u with trust = |p| / |u| (1 when either is 0)
+#include "common.cuh"
+
+constexpr int L_THREADS = 512;
+
+__global__ void __launch_bounds__(L_THREADS)
+k_lamb_gnorm(const ConefLambTensor* __restrict__ tensors, const int2* __restrict__ chunks, int chunk_elems,
+             float* __restrict__ norms) {
+  __shared__ float scratch[33];
+  const int2 c = chunks[blockIdx.x];
+  const ConefLambTensor T = tensors[c.x];
+  const long long lo = (long long)c.y * chunk_elems;
+  const long long hi = min(lo + (long long)chunk_elems, T.numel);
+  float s = 0.f;
+  for (long long i = lo + threadIdx.x; i < hi; i += L_THREADS) { const float g = T.g[i]; s = fmaf(g, g, s); }
+  s = block_sum(s, scratch);
+  if (threadIdx.x == 0) atomicAdd(&norms[0], s);
+}
+
+__global__ void __launch_bounds__(L_THREADS)
+k_lamb_stage1(const ConefLambTensor* __restrict__ tensors, const int2* __restrict__ chunks, int chunk_elems,
+              float* __restrict__ norms, float beta1, float beta2, float eps, float bc1, float bc2,
+              float grad_scale, float max_grad_norm) {
+  __shared__ float scratch[33];
+  const int2 c = chunks[blockIdx.x];
+  const ConefLambTensor T = tensors[c.x];
+  const long long lo = (long long)c.y * chunk_elems;
+  const long long hi = min(lo + (long long)chunk_elems, T.numel);
+  // gradient un-scaling and global-norm clipping folded into one factor
+  float gmul = 1.f / grad_scale;
+  if (max_grad_norm > 0.f) {
+    const float gn = sqrtf(norms[0]) * gmul;
+    if (gn > max_grad_norm) gmul *= max_grad_norm / gn;
+  }
+  float pn = 0.f, un = 0.f;
+  for (long long i = lo + threadIdx.x; i < hi; i += L_THREADS) {
+    const float g = T.g[i] * gmul;
+    const float p = T.p[i];
+    const float m = beta1 * T.m[i] + (1.f - beta1) * g;
+    const float v = beta2 * T.v[i] + (1.f - beta2) * g * g;
+    T.m[i] = m;
+    T.v[i] = v;
+    const float u = (m / bc1) / (sqrtf(v / bc2) + eps) + T.weight_decay * p;
+    T.g[i] = u;
+    pn = fmaf(p, p, pn);
+    un = fmaf(u, u, un);
+  }
+  pn = block_sum(pn, scratch);
+  un = block_sum(un, scratch);
+  if (threadIdx.x == 0) {
+    atomicAdd(&norms[1 + 2 * c.x], pn);
+    atomicAdd(&norms[2 + 2 * c.x], un);
+  }
+}
+
+__global__ void __launch_bounds__(L_THREADS)
+k_lamb_stage2(const ConefLambTensor* __restrict__ tensors, const int2* __restrict__ chunks, int chunk_elems,
+              const float* __restrict__ norms, float lr) {
+  const int2 c = chunks[blockIdx.x];
+  const ConefLambTensor T = tensors[c.x];
+  const long long lo = (long long)c.y * chunk_elems;
+  const long long hi = min(lo + (long long)chunk_elems, T.numel);
+  const float pn = sqrtf(norms[1 + 2 * c.x]), un = sqrtf(norms[2 + 2 * c.x]);
+  const float trust = (pn > 0.f && un > 0.f) ? pn / un : 1.f;
+  const float step = lr * trust;
+  for (long long i = lo + threadIdx.x; i < hi; i += L_THREADS) T.p[i] -= step * T.g[i];
+}
+
+extern "C" int conef_lamb_step(const ConefLambTensor* tensors, int ntensors, const int2* chunks, int nchunks,
+                               int chunk_elems, float* norms, float lr, float beta1, float beta2, float eps,
+                               int step, int bias_correction, float grad_scale, float max_grad_norm,
+                               cudaStream_t stream) {
+  if (ntensors <= 0 || nchunks <= 0) return 0;
+  CONEF_CUDA(cudaMemsetAsync(norms, 0, sizeof(float) * (size_t)(1 + 2 * ntensors), stream));
+  if (max_grad_norm > 0.f) {
+    k_lamb_gnorm<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, norms);
+    CONEF_CHECK_LAUNCH("k_lamb_gnorm");
+  }
+  float bc1 = 1.f, bc2 = 1.f;
+  if (bias_correction) {
+    bc1 = 1.f - powf(beta1, (float)step);
+    bc2 = 1.f - powf(beta2, (float)step);
+  }
+  k_lamb_stage1<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, norms, beta1, beta2, eps, bc1, bc2,
+                                                 grad_scale, max_grad_norm);
+  CONEF_CHECK_LAUNCH("k_lamb_stage1");
+  k_lamb_stage2<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, norms, lr);
+  CONEF_CHECK_LAUNCH("k_lamb_stage2");
+  return 0;
+}

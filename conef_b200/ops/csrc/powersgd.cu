@@ -1,0 +1,394 @@
+// Grouped PowerSGD pipeline, SIMT edition: every kernel processes all the
+// compressed matrices of one DDP bucket in a single launch, driven by a
+// device-resident table of ConefMat descriptors and a tile table.
+//
+// Replaces, per matrix and per step, of the reference (communication/powerSGD_hook.py):
+//   :409  DenseCS.query        -> folded into k_psgd_p (error add before P = M Q)
+//   :497  torch.matmul(M, Q)   -> k_psgd_p
+//   :12-43 _orthogonalize      -> k_orthogonalize (all matrices of the bucket, one launch)
+//   :531  torch.matmul(M^T, P) -> k_psgd_q
+//   :550  torch.matmul(P, Q^T), :558/:563 residual, CountSketch.py:27-67 update
+//                              -> k_psgd_decompress (one pass, residual kept in registers)
+#include "common.cuh"
+
+constexpr int P_WARPS = 8;       // rows per CTA in k_psgd_p (one warp per row)
+constexpr int Q_THREADS = 256;   // columns per CTA in k_psgd_q
+constexpr int D_THREADS = 256;
+
+// ---------------------------------------------------------------------------
+// P = (G + err) Q, one warp per matrix row.
+template <int RP>
+__global__ void __launch_bounds__(P_WARPS * 32)
+k_psgd_p(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, float* __restrict__ bucket,
+         const float* __restrict__ sketch, const int32_t* __restrict__ tables,
+         const float* __restrict__ dense_err, const float* __restrict__ Q, float* __restrict__ P,
+         float alpha, int ef_mode) {
+  const int2 t = tiles[blockIdx.x];
+  const ConefMat M = mats[t.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = t.y * P_WARPS + warp;
+  if (row >= M.n) return;
+  const int m = M.m, r = M.r;
+  float* g = bucket + M.g_off + (size_t)row * m;
+  const float* q = Q + M.q_off;
+  float acc[RP];
+#pragma unroll
+  for (int c = 0; c < RP; ++c) acc[c] = 0.f;
+
+  if (ef_mode == CONEF_EF_SKETCH) {
+    const float* srow = sketch + M.sk_off + (size_t)row * M.W;
+    const int32_t* tab = tables + M.tab_off;
+#pragma unroll 4
+    for (int j = lane; j < m; j += 32) {
+      const int e = tab[j];
+      const float v = g[j] + alpha * unpack_sign(e) * srow[unpack_bucket(e)];
+      g[j] = v;
+#pragma unroll
+      for (int c = 0; c < RP; ++c)
+        if (c < r) acc[c] = fmaf(v, q[(size_t)j * r + c], acc[c]);
+    }
+  } else if (ef_mode == CONEF_EF_DENSE) {
+    const float* erow = dense_err + M.g_off + (size_t)row * m;
+#pragma unroll 4
+    for (int j = lane; j < m; j += 32) {
+      const float v = g[j] + erow[j];
+      g[j] = v;
+#pragma unroll
+      for (int c = 0; c < RP; ++c)
+        if (c < r) acc[c] = fmaf(v, q[(size_t)j * r + c], acc[c]);
+    }
+  } else {
+#pragma unroll 4
+    for (int j = lane; j < m; j += 32) {
+      const float v = g[j];
+#pragma unroll
+      for (int c = 0; c < RP; ++c)
+        if (c < r) acc[c] = fmaf(v, q[(size_t)j * r + c], acc[c]);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < RP; ++c) acc[c] = warp_sum(acc[c]);
+  if (lane == 0) {
+    float* p = P + M.p_off + (size_t)row * r;
+#pragma unroll
+    for (int c = 0; c < RP; ++c)
+      if (c < r) p[c] = acc[c];
+  }
+}
+
+template <int RP>
+static int launch_p(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket, const float* sketch,
+                    const int32_t* tables, const float* dense_err, const float* Q, float* P, float alpha,
+                    int ef_mode, cudaStream_t stream) {
+  k_psgd_p<RP><<<ntiles, P_WARPS * 32, 0, stream>>>(mats, tiles, bucket, sketch, tables, dense_err, Q, P, alpha, ef_mode);
+  CONEF_CHECK_LAUNCH("k_psgd_p");
+  return 0;
+}
+
+#define DISPATCH_RANK(max_rank, fn, ...)                                   \
+  do {                                                                     \
+    if ((max_rank) <= 1) return fn<1>(__VA_ARGS__);                        \
+    if ((max_rank) <= 2) return fn<2>(__VA_ARGS__);                        \
+    if ((max_rank) <= 4) return fn<4>(__VA_ARGS__);                        \
+    if ((max_rank) <= 8) return fn<8>(__VA_ARGS__);                        \
+    if ((max_rank) <= 16) return fn<16>(__VA_ARGS__);                      \
+    if ((max_rank) <= 32) return fn<32>(__VA_ARGS__);                      \
+    conef_set_error("rank %d > 32 is not supported by the native kernels", (max_rank)); \
+    return 2;                                                              \
+  } while (0)
+
+extern "C" int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
+                            const float* sketch, const int32_t* tables, const float* dense_err,
+                            const float* Q, float* P, float alpha, int ef_mode, int max_rank,
+                            cudaStream_t stream) {
+  if (ntiles <= 0) return 0;
+  DISPATCH_RANK(max_rank, launch_p, mats, tiles, ntiles, bucket, sketch, tables, dense_err, Q, P, alpha, ef_mode, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Batched Gram-Schmidt: one CTA per matrix, all matrices of the bucket in one
+// launch.  Per column: one reduction pass (norm and the dot products with all
+// later columns at once) and one update pass.  With world > 1 the CTA first
+// sums the peers' copies of its block (fused all-reduce over peer memory).
+constexpr int O_THREADS = 512;
+constexpr int O_MAXR = 32;
+
+__global__ void __launch_bounds__(O_THREADS)
+k_orthogonalize(const ConefMat* __restrict__ mats, int which, float* __restrict__ buf, float eps,
+                const float* const* __restrict__ peer_bufs, const uint32_t* __restrict__ flags, int world,
+                uint32_t epoch, int* __restrict__ status, long long spin_limit) {
+  __shared__ float red[O_MAXR][17];   // per-warp partials: [column][warp]
+  __shared__ float dots[O_MAXR];
+  __shared__ int ok;
+  const ConefMat M = mats[blockIdx.x];
+  const int rows = which == 0 ? M.n : M.m;
+  const int r = M.r;
+  const size_t off = which == 0 ? M.p_off : M.q_off;
+  float* a = buf + off;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t total = (size_t)rows * r;
+
+  if (world > 1) {
+    if (tid == 0) {
+      ok = wait_flags_bounded(flags, world, epoch, spin_limit) ? 1 : 0;
+      if (!ok) atomicExch(status, CONEF_STATUS_FLAG_TIMEOUT);
+    }
+    __syncthreads();
+    if (!ok) return;  // leave the local values untouched; the host raises
+    for (size_t i = tid; i < total; i += O_THREADS) {
+      float s = 0.f;
+      for (int p = 0; p < world; ++p) s += ld_relaxed_sys_f32(peer_bufs[p] + off + i);
+      a[i] = s;
+    }
+    __syncthreads();
+  }
+
+  for (int c = 0; c < r; ++c) {
+    // pass 1: dots[d] = <col c, col d> for d >= c
+    float part[O_MAXR];
+#pragma unroll
+    for (int d = 0; d < O_MAXR; ++d) part[d] = 0.f;
+    for (int i = tid; i < rows; i += O_THREADS) {
+      const float* rowp = a + (size_t)i * r;
+      const float vc = rowp[c];
+#pragma unroll
+      for (int d = 0; d < O_MAXR; ++d)
+        if (d >= c && d < r) part[d] = fmaf(vc, rowp[d], part[d]);
+    }
+#pragma unroll
+    for (int d = 0; d < O_MAXR; ++d) {
+      if (d >= c && d < r) {
+        const float s = warp_sum(part[d]);
+        if (lane == 0) red[d][warp] = s;
+      }
+    }
+    __syncthreads();
+    if (tid < r && tid >= c) {
+      float s = 0.f;
+      for (int w = 0; w < O_THREADS / 32; ++w) s += red[tid][w];
+      dots[tid] = s;
+    }
+    __syncthreads();
+    // pass 2: col c /= (norm + eps); col d -= <q_c, col d> q_c
+    const float norm = sqrtf(dots[c]);
+    const float inv = 1.f / (norm + eps);
+    for (int i = tid; i < rows; i += O_THREADS) {
+      float* rowp = a + (size_t)i * r;
+      const float qc = rowp[c] * inv;
+      rowp[c] = qc;
+      for (int d = c + 1; d < r; ++d) rowp[d] -= (dots[d] * inv) * qc;
+    }
+    __syncthreads();
+  }
+}
+
+extern "C" int conef_orthogonalize(const ConefMat* mats, int nmats, int which, float* buf, float eps,
+                                   const float* const* peer_bufs, const uint32_t* flags, int world,
+                                   uint32_t epoch, int* status, long long spin_limit,
+                                   cudaStream_t stream) {
+  if (nmats <= 0) return 0;
+  k_orthogonalize<<<nmats, O_THREADS, 0, stream>>>(mats, which, buf, eps, peer_bufs, flags, world, epoch,
+                                                  status, spin_limit);
+  CONEF_CHECK_LAUNCH("k_orthogonalize");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Q = M^T P.  Tile = (matrix, row block, column block); a thread owns one
+// column and walks the rows of the block, P rows are broadcast from shared
+// memory.  Several row blocks of one matrix combine with fp32 atomics.
+template <int RP>
+__global__ void __launch_bounds__(Q_THREADS)
+k_psgd_q(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, const float* __restrict__ bucket,
+         const float* __restrict__ P, float* __restrict__ Q) {
+  extern __shared__ float ps[];  // q_rows * RP
+  const int2 t = tiles[blockIdx.x];
+  const ConefMat M = mats[t.x];
+  const int m = M.m, r = M.r;
+  const int ncb = (m + Q_THREADS - 1) / Q_THREADS;
+  const int rb = t.y / ncb, cb = t.y - rb * ncb;
+  const int row0 = rb * M.q_rows;
+  const int rows = min(M.q_rows, M.n - row0);
+  const float* p = P + M.p_off + (size_t)row0 * r;
+  for (int i = threadIdx.x; i < rows * RP; i += Q_THREADS) {
+    const int ii = i / RP, c = i - ii * RP;
+    ps[i] = c < r ? p[(size_t)ii * r + c] : 0.f;
+  }
+  __syncthreads();
+  const int j = cb * Q_THREADS + threadIdx.x;
+  if (j >= m) return;
+  const float* g = bucket + M.g_off + (size_t)row0 * m + j;
+  float acc[RP];
+#pragma unroll
+  for (int c = 0; c < RP; ++c) acc[c] = 0.f;
+#pragma unroll 4
+  for (int ii = 0; ii < rows; ++ii) {
+    const float v = g[(size_t)ii * m];
+#pragma unroll
+    for (int c = 0; c < RP; ++c) acc[c] = fmaf(v, ps[ii * RP + c], acc[c]);
+  }
+  float* q = Q + M.q_off + (size_t)j * r;
+  if (M.q_atomic) {
+#pragma unroll
+    for (int c = 0; c < RP; ++c)
+      if (c < r) atomicAdd(q + c, acc[c]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < RP; ++c)
+      if (c < r) q[c] = acc[c];
+  }
+}
+
+template <int RP>
+static int launch_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket, const float* P,
+                    float* Q, size_t smem, cudaStream_t stream) {
+  CONEF_CUDA(cudaFuncSetAttribute(k_psgd_q<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+  k_psgd_q<RP><<<ntiles, Q_THREADS, smem, stream>>>(mats, tiles, bucket, P, Q);
+  CONEF_CHECK_LAUNCH("k_psgd_q");
+  return 0;
+}
+
+// Rows per row block never exceed CONEF_Q_MAX_ROWS (the host builds q_rows).
+#define CONEF_Q_MAX_ROWS 1024
+
+extern "C" int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket,
+                            const float* P, float* Q, int max_rank, cudaStream_t stream) {
+  if (ntiles <= 0) return 0;
+  int rp = max_rank <= 1 ? 1 : max_rank <= 2 ? 2 : max_rank <= 4 ? 4 : max_rank <= 8 ? 8 : max_rank <= 16 ? 16 : 32;
+  size_t smem = (size_t)CONEF_Q_MAX_ROWS * rp * sizeof(float);
+  DISPATCH_RANK(max_rank, launch_q, mats, tiles, ntiles, bucket, P, Q, smem, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Decompress + error feedback.  Tile = (matrix, block of rows_per_cta rows).
+// A thread owns a column: it loads Q[j, :] (scaled by q_scale = 1/world) and
+// the column's hash entry once, then for each row of the block computes
+// M_hat = <P[row, :], Q[j, :]>, writes it to the bucket and routes the residual
+// to the error store: a dense buffer, or the row's count sketch accumulated
+// with shared-memory atomics and flushed by one global store per sketch cell.
+template <int RP>
+__global__ void __launch_bounds__(D_THREADS)
+k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int rows_per_cta,
+                  float* __restrict__ bucket, const float* __restrict__ P, const float* __restrict__ Q,
+                  float q_scale, float* __restrict__ sketch, const int32_t* __restrict__ tables,
+                  const int32_t* __restrict__ counts, float* __restrict__ dense_err, float beta,
+                  int ef_mode) {
+  extern __shared__ float sm[];
+  const int2 t = tiles[blockIdx.x];
+  const ConefMat M = mats[t.x];
+  const int m = M.m, r = M.r, W = M.W;
+  const int row0 = t.y * rows_per_cta;
+  const int rows = min(rows_per_cta, M.n - row0);
+  float* ps = sm;                              // rows_per_cta * RP
+  float* acc = sm + (size_t)rows_per_cta * RP; // rows_per_cta * W (sketch mode)
+  const float* p = P + M.p_off + (size_t)row0 * r;
+  for (int i = threadIdx.x; i < rows * RP; i += D_THREADS) {
+    const int ii = i / RP, c = i - ii * RP;
+    ps[i] = c < r ? p[(size_t)ii * r + c] : 0.f;
+  }
+  if (ef_mode == CONEF_EF_SKETCH)
+    for (int i = threadIdx.x; i < rows * W; i += D_THREADS) acc[i] = 0.f;
+  __syncthreads();
+
+  const int32_t* tab = ef_mode == CONEF_EF_SKETCH ? tables + M.tab_off : nullptr;
+  float* g0 = bucket + M.g_off + (size_t)row0 * m;
+  for (int j = threadIdx.x; j < m; j += D_THREADS) {
+    float qv[RP];
+    const float* q = Q + M.q_off + (size_t)j * r;
+#pragma unroll
+    for (int c = 0; c < RP; ++c) qv[c] = c < r ? q[c] * q_scale : 0.f;
+    int h = 0;
+    float s = 0.f;
+    if (ef_mode == CONEF_EF_SKETCH) {
+      const int e = tab[j];
+      h = unpack_bucket(e);
+      s = unpack_sign(e);
+    }
+    for (int ii = 0; ii < rows; ++ii) {
+      float mh = 0.f;
+#pragma unroll
+      for (int c = 0; c < RP; ++c) mh = fmaf(ps[ii * RP + c], qv[c], mh);
+      float* gp = g0 + (size_t)ii * m + j;
+      const float resid = *gp - mh;
+      *gp = mh;
+      if (ef_mode == CONEF_EF_SKETCH) atomicAdd(&acc[ii * W + h], s * resid);
+      else if (ef_mode == CONEF_EF_DENSE) dense_err[M.g_off + (size_t)(row0 + ii) * m + j] = resid;
+    }
+  }
+  if (ef_mode == CONEF_EF_SKETCH) {
+    __syncthreads();
+    const float omb = 1.f - beta;
+    const int32_t* cnt = counts + M.cnt_off;
+    float* srow = sketch + M.sk_off + (size_t)row0 * W;
+    for (int i = threadIdx.x; i < rows * W; i += D_THREADS) {
+      const int h2 = i % W;
+      srow[i] = srow[i] * (1.f - omb * (float)cnt[h2]) + acc[i];
+    }
+  }
+}
+
+template <int RP>
+static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta, float* bucket,
+                    const float* P, const float* Q, float q_scale, float* sketch, const int32_t* tables,
+                    const int32_t* counts, float* dense_err, float beta, int ef_mode, size_t smem,
+                    cudaStream_t stream) {
+  smem += (size_t)rows_per_cta * RP * sizeof(float);
+  if (smem > 220 * 1024) { conef_set_error("decompress: %zu bytes of shared memory needed", smem); return 2; }
+  CONEF_CUDA(cudaFuncSetAttribute(k_psgd_decompress<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  k_psgd_decompress<RP><<<ntiles, D_THREADS, smem, stream>>>(mats, tiles, rows_per_cta, bucket, P, Q, q_scale,
+                                                           sketch, tables, counts, dense_err, beta, ef_mode);
+  CONEF_CHECK_LAUNCH("k_psgd_decompress");
+  return 0;
+}
+
+extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta,
+                                     float* bucket, const float* P, const float* Q, float q_scale,
+                                     float* sketch, const int32_t* tables, const int32_t* counts,
+                                     float* dense_err, float beta, int ef_mode, int max_rank,
+                                     size_t smem_bytes, cudaStream_t stream) {
+  if (ntiles <= 0) return 0;
+  DISPATCH_RANK(max_rank, launch_d, mats, tiles, ntiles, rows_per_cta, bucket, P, Q, q_scale, sketch, tables,
+                counts, dense_err, beta, ef_mode, smem_bytes, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Counter-based standard normal fill (Philox-4x32-10 + Box-Muller): the value
+// of element e depends only on (seed, e).
+__device__ __forceinline__ void philox_round(uint32_t& c0, uint32_t& c1, uint32_t& c2, uint32_t& c3,
+                                             uint32_t k0, uint32_t k1) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
+  const uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
+  const uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
+  const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+  c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+}
+
+__global__ void k_fill_normal(float* __restrict__ buf, long long numel, uint64_t seed) {
+  const long long quad = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long base = quad * 4;
+  if (base >= numel) return;
+  uint32_t c0 = (uint32_t)quad, c1 = (uint32_t)(quad >> 32), c2 = 0u, c3 = 0u;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    philox_round(c0, c1, c2, c3, k0, k1);
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  const float two_pi = 6.283185307179586f;
+  const float u0 = ((float)c0 + 1.f) * 2.3283064365386963e-10f;  // (0, 1]
+  const float u1 = (float)c1 * 2.3283064365386963e-10f;
+  const float u2 = ((float)c2 + 1.f) * 2.3283064365386963e-10f;
+  const float u3 = (float)c3 * 2.3283064365386963e-10f;
+  const float r0 = sqrtf(-2.f * logf(u0)), r1 = sqrtf(-2.f * logf(u2));
+  float out[4] = {r0 * cosf(two_pi * u1), r0 * sinf(two_pi * u1), r1 * cosf(two_pi * u3), r1 * sinf(two_pi * u3)};
+  for (int i = 0; i < 4; ++i)
+    if (base + i < numel) buf[base + i] = out[i];
+}
+
+extern "C" int conef_fill_normal(float* buf, long long numel, uint64_t seed, cudaStream_t stream) {
+  if (numel <= 0) return 0;
+  const long long quads = (numel + 3) / 4;
+  k_fill_normal<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(buf, numel, seed);
+  CONEF_CHECK_LAUNCH("k_fill_normal");
+  return 0;
+}

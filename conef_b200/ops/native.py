@@ -1,0 +1,157 @@
+"""ctypes binding of the in-tree native library (``_conef_native.so``).
+
+The library is built by :mod:`conef_b200.ops.build` (``__graft_entry__.build``)
+and lives next to this file.  On a machine with a CUDA device the library is
+mandatory: :func:`lib` raises instead of silently falling back to PyTorch ops.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+from typing import Optional
+
+import numpy as np
+import torch
+
+_SO = Path(__file__).resolve().parent / "_conef_native.so"
+_lib: Optional[C.CDLL] = None
+
+c_ll = C.c_longlong
+vp = C.c_void_p
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+# numpy dtypes mirroring the C structs of csrc/conef.h ---------------------
+MAT_DTYPE = np.dtype(
+    [("g_off", "<i8"), ("p_off", "<i8"), ("q_off", "<i8"), ("sk_off", "<i8"),
+     ("n", "<i4"), ("m", "<i4"), ("r", "<i4"), ("W", "<i4"),
+     ("tab_off", "<i4"), ("cnt_off", "<i4"), ("q_rows", "<i4"), ("q_atomic", "<i4")], align=True)
+SEG_DTYPE = np.dtype([("src_off", "<i8"), ("dst_off", "<i8"), ("len", "<i8")], align=True)
+BLK_DTYPE = np.dtype(
+    [("g_off", "<i8"), ("numel", "<i8"), ("start", "<i8"), ("block", "<i8"),
+     ("stage_off", "<i8"), ("sk_off", "<i8"),
+     ("n", "<i4"), ("m", "<i4"), ("W", "<i4"), ("tab_off", "<i4"), ("cnt_off", "<i4"),
+     ("scale_off", "<i4")], align=True)
+LAMB_DTYPE = np.dtype(
+    [("p", "<u8"), ("g", "<u8"), ("m", "<u8"), ("v", "<u8"), ("numel", "<i8"),
+     ("weight_decay", "<f4"), ("pad", "<i4")], align=True)
+assert MAT_DTYPE.itemsize == 64 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.itemsize == 72
+assert LAMB_DTYPE.itemsize == 48
+
+EF_NONE, EF_DENSE, EF_SKETCH, EF_QUANT8 = 0, 1, 2, 3
+
+_SIGNATURES = {
+    "conef_version": ([], C.c_int),
+    "conef_build_hash_table": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp], C.c_int),
+    "conef_sketch_query": ([vp, vp, C.c_int, vp, C.c_int, C.c_int, C.c_int, C.c_float, vp], C.c_int),
+    "conef_sketch_update": ([vp, vp, C.c_int, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, vp], C.c_int),
+    "conef_sketch3_query": ([vp] * 7 + [C.c_int, C.c_int, C.c_int, C.c_float, vp], C.c_int),
+    "conef_sketch3_update": ([vp] * 7 + [C.c_int, C.c_int, C.c_int, C.c_float, vp], C.c_int),
+    "conef_psgd_p": ([vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, C.c_float, C.c_int, C.c_int, vp], C.c_int),
+    "conef_orthogonalize": ([vp, C.c_int, C.c_int, vp, C.c_float, vp, vp, C.c_int, C.c_uint32, vp, c_ll, vp], C.c_int),
+    "conef_psgd_q": ([vp, vp, C.c_int, vp, vp, vp, C.c_int, vp], C.c_int),
+    "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
+                               C.c_int, C.c_int, C.c_size_t, vp], C.c_int),
+    "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),
+    "conef_tc_supported": ([], C.c_int),
+    "conef_gather_segments": ([vp, C.c_int, vp, vp, vp, c_ll, vp], C.c_int),
+    "conef_scatter_segments": ([vp, C.c_int, vp, vp, C.c_int, vp, C.c_float, vp, c_ll, vp], C.c_int),
+    "conef_randblock_gather": ([vp, vp, C.c_int, C.c_int, vp, vp, C.c_float, vp, vp, vp, vp, vp, vp,
+                                C.c_float, C.c_float, C.c_int, C.c_size_t, vp], C.c_int),
+    "conef_randblock_scatter": ([vp, C.c_int, vp, vp, C.c_int, vp, C.c_float, c_ll, vp], C.c_int),
+    "conef_quant8_query": ([vp, vp, vp, c_ll, C.c_float, vp], C.c_int),
+    "conef_quant8_update": ([vp, vp, vp, c_ll, C.c_float, vp], C.c_int),
+    "conef_signal_peers": ([vp, C.c_int, C.c_int, C.c_uint32, vp], C.c_int),
+    "conef_allreduce_oneshot": ([vp, vp, vp, vp, C.c_int, C.c_int, C.c_uint32, c_ll, C.c_float, vp, c_ll, vp], C.c_int),
+    "conef_wait_flags": ([vp, C.c_int, C.c_uint32, vp, c_ll, vp], C.c_int),
+    "conef_ipc_get_handle": ([vp, vp], C.c_int),
+    "conef_ipc_open_handle": ([vp, C.POINTER(vp)], C.c_int),
+    "conef_ipc_close_handle": ([vp], C.c_int),
+    "conef_lamb_step": ([vp, C.c_int, vp, C.c_int, C.c_int, vp, C.c_float, C.c_float, C.c_float, C.c_float,
+                         C.c_int, C.c_int, C.c_float, C.c_float, vp], C.c_int),
+    "conef_cpu_hash_table": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int], None),
+    "conef_cpu_sketch_query": ([vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float], None),
+    "conef_cpu_sketch_update": ([vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float], None),
+    "conef_cpu_gram_schmidt": ([vp, C.c_int, C.c_int, C.c_float], None),
+}
+_OPTIONAL = {
+    "conef_psgd_p_tc": ([vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, C.c_float, C.c_int, vp, vp], C.c_int),
+    "conef_psgd_q_tc": ([vp, vp, C.c_int, vp, vp, vp, vp, vp], C.c_int),
+}
+
+
+def so_path() -> Path:
+    return _SO
+
+
+def available() -> bool:
+    """True when the shared object exists and loads."""
+    try:
+        return lib() is not None
+    except NativeError:
+        return False
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _SO.exists():
+        raise NativeError(
+            f"native library {_SO} is missing; run `python -m conef_b200.ops.build` "
+            "(or __graft_entry__.build()) first")
+    try:
+        handle = C.CDLL(str(_SO))
+    except OSError as exc:  # pragma: no cover - depends on the machine
+        raise NativeError(f"cannot load {_SO}: {exc}") from exc
+    handle.conef_last_error.restype = C.c_char_p
+    for name, (argtypes, restype) in _SIGNATURES.items():
+        fn = getattr(handle, name)
+        fn.argtypes = argtypes
+        fn.restype = restype
+    for name, (argtypes, restype) in _OPTIONAL.items():
+        if hasattr(handle, name):
+            fn = getattr(handle, name)
+            fn.argtypes = argtypes
+            fn.restype = restype
+    _lib = handle
+    return handle
+
+
+def check(rc: int, what: str = "") -> None:
+    if rc != 0:
+        msg = lib().conef_last_error()
+        raise NativeError(f"{what} failed (rc={rc}): {msg.decode() if msg else ''}")
+
+
+def use_native(t: torch.Tensor) -> bool:
+    """Decide the execution path for tensor ``t``.
+
+    CUDA tensors run on the native kernels unless ``CONEF_BACKEND=torch`` asks
+    for the PyTorch-ops path (the baseline arm of the benchmarks).  A CUDA
+    tensor with no loadable library is an error, never a silent fallback.
+    """
+    if not t.is_cuda:
+        return False
+    if os.environ.get("CONEF_BACKEND", "native") == "torch":
+        return False
+    lib()  # raises if missing
+    return True
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def upload_struct_array(arr: np.ndarray, device) -> torch.Tensor:
+    """Copy a numpy structured array to the device as raw bytes."""
+    raw = torch.from_numpy(arr.view(np.uint8).reshape(-1).copy())
+    return raw.to(device)

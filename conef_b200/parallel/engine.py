@@ -1,0 +1,667 @@
+"""Native (sm_100a) execution of the hooks: per-bucket engines.
+
+An engine is built the first time a bucket is compressed and is reused while
+the bucket keeps its layout.  It owns the device-resident descriptor tables
+(one ``ConefMat`` / ``ConefSeg`` / ``ConefBlk`` record per tensor, plus tile
+tables), the hash-table arena, the symmetric buffers, and it rebinds the
+state's persistent tensors (error buffers, sketches, P/Q memory) so that the
+state keeps the reference's checkpoint layout while the kernels see flat
+arenas.
+
+Per step and bucket the PowerSGD engine enqueues, on a dedicated communication
+stream that waits for the gradients and that the returned future publishes:
+
+    gather(uncompressed) -> P = (G+e)Q -> [signal] -> allreduce(P)+Gram-Schmidt
+    -> scatter(uncompressed, reduced in-kernel) -> Q = M^T P -> allreduce(Q)/ws
+    -> M_hat = P Q^T + error update
+
+with no host synchronisation and no ``.wait()`` on the host (the reference
+blocks the host once per bucket, communication/powerSGD_hook.py:552-553).
+"""
+from __future__ import annotations
+
+import logging
+import math
+import os
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..compressors import DenseCS, Quant8Error, tables_for
+from ..compressors.count_sketch import HalfDenseCS
+from ..ops import native
+from ..ops import reference as ref
+from . import plan as planlib
+from .symm import DEFAULT_SPIN_LIMIT, SymmBuffer, SymmUnavailable, comm_backend_choice
+
+logger = logging.getLogger(__name__)
+
+_COMM_STREAMS: Dict[int, "torch.cuda.Stream"] = {}
+_SYMM_DISABLED = False
+
+P_ROWS = 8          # rows per CTA of the SIMT P kernel (csrc/powersgd.cu: P_WARPS)
+Q_COLS = 256        # columns per CTA of the Q kernel
+Q_MAX_ROWS = 1024
+QGROUP = ref.QUANT_GROUP
+SMEM_BUDGET = 200 * 1024
+TARGET_CTAS = 2 * 148
+
+
+def comm_stream_for(device: torch.device) -> "torch.cuda.Stream":
+    """One high-priority side stream per device, shared by all hooks."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    s = _COMM_STREAMS.get(idx)
+    if s is None:
+        s = torch.cuda.Stream(device=device, priority=-1)
+        _COMM_STREAMS[idx] = s
+    return s
+
+
+def _use_tc() -> bool:
+    """tcgen05 tiles for P / Q unless ``CONEF_TC=0``."""
+    if os.environ.get("CONEF_TC", "1") == "0":
+        return False
+    lib = native.lib()
+    return bool(lib.conef_tc_supported()) and hasattr(lib, "conef_psgd_p_tc")
+
+
+def _done_on_current_stream(buf: torch.Tensor) -> torch.futures.Future:
+    fut = torch.futures.Future(devices=[buf.device])
+    fut.set_result(buf)
+    return fut
+
+
+def _try_symm(regions, group, device) -> Optional[SymmBuffer]:
+    global _SYMM_DISABLED
+    choice = comm_backend_choice()
+    if group.size() == 1 or choice == "nccl" or _SYMM_DISABLED:
+        return None
+    try:
+        sb = SymmBuffer(regions, group, device, backend=choice)
+        logger.info("symmetric buffer (%s backend): %d bytes per rank", sb.backend, sb.total_bytes)
+        return sb
+    except SymmUnavailable as exc:
+        if choice != "auto":
+            raise
+        logger.warning("peer-memory collectives unavailable, using NCCL: %s", exc)
+        _SYMM_DISABLED = True
+        return None
+
+
+class _EngineBase:
+    def __init__(self, device):
+        self.device = device
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.step = 0
+        self.symm: Optional[SymmBuffer] = None
+        self.lib = native.lib()
+
+    def check_status(self) -> None:
+        code = int(self.status[0].item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(
+                f"device-side wait gave up (status {code}): a peer rank did not signal in time; "
+                "the gradients of the affected step are not valid")
+
+    def _nccl_sum(self, t: torch.Tensor, group, average=False) -> None:
+        if group.size() == 1 or t.numel() == 0:
+            return
+        if average:
+            dist.all_reduce(t, op=dist.ReduceOp.AVG, group=group)
+        else:
+            dist.all_reduce(t, group=group)
+
+
+# ==========================================================================
+# PowerSGD family
+# ==========================================================================
+class PowerSGDEngine(_EngineBase):
+    def __init__(self, state, buf: torch.Tensor, grads, group, variant: str):
+        super().__init__(buf.device)
+        self.variant = variant
+        self.group = group
+        self.world = group.size()
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.buf_ptr = buf.data_ptr()
+        self.buf_numel = buf.numel()
+        dev = self.device
+        if variant == "batched":
+            self.plan, self.side = planlib.build_batched_plan(buf.numel(), state.matrix_approximation_rank, dev, buf.dtype)
+            self.work = torch.zeros(self.side * self.side, device=dev, dtype=torch.float32)
+        else:
+            self.plan = planlib.build_powersgd_plan(buf, grads, state.matrix_approximation_rank,
+                                                    state.min_compression_rate)
+            self.work = None
+        plan = self.plan
+        self.max_rank = max(plan.max_rank, 1)
+        if self.max_rank > 32:
+            raise native.NativeError("matrix_approximation_rank > 32 is not supported by the native kernels")
+
+        # ---- error-feedback mode ------------------------------------------
+        ef = getattr(state, "use_error_feedback", False) and variant != "unbiased"
+        ec = ef and getattr(state, "use_error_compression", False)
+        if variant == "batched":
+            ec = False
+        kind = getattr(state, "error_compressor", "count_sketch")
+        if not ef:
+            self.ef_mode, self.external = native.EF_NONE, False
+        elif not ec:
+            self.ef_mode, self.external = native.EF_DENSE, False
+        elif kind == "count_sketch" and variant == "powersgd":
+            self.ef_mode, self.external = native.EF_SKETCH, False
+        else:
+            self.ef_mode, self.external = native.EF_NONE, True
+
+        # ---- descriptor tables ----------------------------------------------
+        mats = np.zeros(len(plan.mats), dtype=native.MAT_DTYPE)
+        total_cb = sum((e.m + Q_COLS - 1) // Q_COLS for e in plan.mats) or 1
+        want_rb = max(1, math.ceil(TARGET_CTAS / total_cb))
+        q_tiles, p_tiles = [], []
+        sk_off = tab_off = cnt_off = 0
+        table_chunks, count_chunks = [], []
+        table_index: Dict[tuple, tuple] = {}
+        self.widths = []
+        seeds = ref.derive_hash_seeds(getattr(state, "hash_seed", 0), 1)[0]
+        for k, e in enumerate(plan.mats):
+            nrb = max(1, min(want_rb, math.ceil(e.n / 64)))
+            q_rows = min(Q_MAX_ROWS, ((math.ceil(e.n / nrb) + 7) // 8) * 8)
+            nrb = math.ceil(e.n / q_rows)
+            ncb = (e.m + Q_COLS - 1) // Q_COLS
+            W = ref.sketch_width(e.m, state.sketch_size) if self.ef_mode == native.EF_SKETCH else 0
+            self.widths.append(W)
+            rec = mats[k]
+            rec["g_off"], rec["p_off"], rec["q_off"] = e.g_off, e.p_off, e.q_off
+            rec["n"], rec["m"], rec["r"], rec["W"] = e.n, e.m, e.r, W
+            rec["q_rows"], rec["q_atomic"] = q_rows, int(nrb > 1)
+            rec["sk_off"], rec["tab_off"], rec["cnt_off"] = -1, -1, -1
+            if self.ef_mode == native.EF_SKETCH:
+                rec["sk_off"] = sk_off
+                sk_off += e.n * W
+                key = (e.m, W)
+                if key not in table_index:
+                    _, _, packed, counts = tables_for(dev, e.m, W, seeds[0], seeds[1])
+                    table_index[key] = (tab_off, cnt_off)
+                    table_chunks.append(packed)
+                    count_chunks.append(counts)
+                    tab_off += e.m
+                    cnt_off += W
+                rec["tab_off"], rec["cnt_off"] = table_index[key]
+            p_tiles += [(k, rb) for rb in range(math.ceil(e.n / P_ROWS))]
+            q_tiles += [(k, t) for t in range(nrb * ncb)]
+        self.q_atomic = bool(mats["q_atomic"].any()) if len(mats) else False
+        self.mats_host = mats
+        self.mats_dev = native.upload_struct_array(mats, dev) if len(mats) else None
+        self.p_tiles = self._tiles(p_tiles)
+        self.q_tiles = self._tiles(q_tiles)
+        self.n_p_tiles, self.n_q_tiles = len(p_tiles), len(q_tiles)
+        # decompress: as many rows per CTA as the sketch rows allow in shared memory
+        maxW = max(self.widths, default=0)
+        self.d_rows = 8 if maxW == 0 else int(max(1, min(8, SMEM_BUDGET // (maxW * 4))))
+        if maxW * 4 > SMEM_BUDGET:
+            raise native.NativeError(f"sketch width {maxW} does not fit in shared memory")
+        self.d_smem = self.d_rows * maxW * 4
+        d_tiles = [(k, rb) for k, e in enumerate(plan.mats) for rb in range(math.ceil(e.n / self.d_rows))]
+        self.d_tiles = self._tiles(d_tiles)
+        self.n_d_tiles = len(d_tiles)
+        self.tables = torch.cat(table_chunks) if table_chunks else None
+        self.counts = torch.cat(count_chunks) if count_chunks else None
+
+        segs = np.zeros(len(plan.segs), dtype=native.SEG_DTYPE)
+        for k, s in enumerate(plan.segs):
+            segs[k] = (s.g_off, s.dst_off, s.numel)
+        self.segs_dev = native.upload_struct_array(segs, dev) if len(segs) else None
+
+        # ---- persistent state tensors ----------------------------------------
+        self.sketch_arena = None
+        if self.ef_mode == native.EF_SKETCH:
+            self.sketch_arena = torch.zeros(max(sk_off, 1), device=dev, dtype=torch.float32)
+        # ---- communication buffers ---------------------------------------------
+        self.staging = torch.empty(max(plan.total_unc, 1), device=dev, dtype=torch.float32)
+        self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_p, 4), max(plan.total_q, 4)], group, dev) \
+            if self.world > 1 else None
+        self.use_tc = _use_tc()
+        self._bound = None
+
+    def _tiles(self, tiles) -> Optional[torch.Tensor]:
+        if not tiles:
+            return None
+        return torch.from_numpy(np.asarray(tiles, dtype=np.int32).reshape(-1, 2)).to(self.device)
+
+    # -- binding of state tensors ---------------------------------------------
+    def bind_state(self, state, bidx: int) -> None:
+        plan, dev = self.plan, self.device
+        n_err = self.side * self.side if self.variant == "batched" else self.buf_numel
+        if self.ef_mode == native.EF_DENSE:
+            cur = state.error_dict.get(bidx)
+            if not (torch.is_tensor(cur) and cur.numel() == n_err and cur.device == dev
+                    and cur.dtype == torch.float32 and cur.is_contiguous()):
+                if torch.is_tensor(cur) and cur.numel() == n_err:
+                    state.error_dict[bidx] = cur.to(dev, torch.float32).contiguous()
+                else:
+                    logger.info("A zero tensor of length %d that represents local error is created.", n_err)
+                    state.error_dict[bidx] = torch.zeros(n_err, device=dev, dtype=torch.float32)
+        elif self.ef_mode == native.EF_SKETCH:
+            comps = state.error_dict.get(bidx)
+            if not isinstance(comps, dict):
+                comps = {}
+                state.error_dict[bidx] = comps
+            for cnt, (e, rec) in enumerate(zip(plan.mats, self.mats_host)):
+                W = int(rec["W"])
+                view = self.sketch_arena[int(rec["sk_off"]) : int(rec["sk_off"]) + e.n * W]
+                old = comps.get(cnt)
+                if isinstance(old, DenseCS) and not isinstance(old, HalfDenseCS) \
+                        and (old.N, old.D, old.range) == (e.n, e.m, W):
+                    if old.cs.data_ptr() != view.data_ptr():
+                        view.copy_(old.cs.reshape(-1).to(dev))
+                        old.cs = view.view(e.n, W)
+                else:
+                    comps[cnt] = DenseCS(e.n, e.m, state.sketch_size, device=dev,
+                                         seed=getattr(state, "hash_seed", 0), storage=view)
+        elif self.external:
+            from .hooks import _make_matrix_compressor
+            comps = state.error_dict.get(bidx)
+            if not isinstance(comps, dict):
+                comps = {}
+                state.error_dict[bidx] = comps
+            for cnt, e in enumerate(plan.mats):
+                if cnt not in comps:
+                    comps[cnt] = _make_matrix_compressor(state, e.n, e.m, dev, self.variant == "c2cs")
+
+    def _pq_memory(self, state, bidx):
+        """Flat P/Q tensors of the state; returns (pmem, qmem, fresh)."""
+        plan, dev = self.plan, self.device
+        warm = getattr(state, "warm_start", False) and self.variant != "unbiased"
+        p, q = state.p_memory_dict.get(bidx), state.q_memory_dict.get(bidx)
+        ok = (torch.is_tensor(p) and torch.is_tensor(q) and p.numel() == plan.total_p
+              and q.numel() == plan.total_q and p.device == dev and q.device == dev)
+        fresh = (not warm) or not ok
+        if not ok:
+            if warm:
+                logger.info("Allocating contiguous memory of length %d for Ps, and of length %d for Qs.",
+                            plan.total_p, plan.total_q)
+            # 16-byte aligned flat buffers (the reduce kernels use vector loads)
+            state.p_memory_dict[bidx] = torch.empty(max(plan.total_p, 1), device=dev, dtype=torch.float32)[: plan.total_p]
+            state.q_memory_dict[bidx] = torch.empty(max(plan.total_q, 1), device=dev, dtype=torch.float32)[: plan.total_q]
+        return state.p_memory_dict[bidx], state.q_memory_dict[bidx], fresh
+
+    # -- one step ------------------------------------------------------------------
+    def run(self, state, bucket, buf: torch.Tensor) -> None:
+        """Enqueue the whole compression pipeline for one bucket on the current stream."""
+        lib, plan, dev = self.lib, self.plan, self.device
+        bidx = bucket.index()
+        ws = self.world
+        st = native.stream_ptr(dev)
+        nmats = len(plan.mats)
+        edict = getattr(state, "error_dict", None)
+        if edict is not None and (self._bound is None or edict.get(bidx) is not self._bound):
+            self.bind_state(state, bidx)
+            self._bound = edict.get(bidx, False)
+        state.total_numel_before_compression += plan.numel_before
+        state.total_numel_after_compression += plan.numel_after
+
+        if self.variant == "batched":
+            work = self.work
+            work[: self.buf_numel].copy_(buf)
+            work[self.buf_numel :].zero_()
+        else:
+            work = buf
+        wp = work.data_ptr()
+
+        alpha, beta = (1.0 - getattr(state, "beta", 0.0), getattr(state, "beta", 0.0))
+        if self.external:
+            from .hooks import _ef_coeffs
+            alpha, beta = _ef_coeffs(state)
+        dense_err = state.error_dict[bidx] if self.ef_mode == native.EF_DENSE else None
+        sketch = self.sketch_arena
+
+        # external error compressors: query before, clone, update after
+        copy = None
+        if self.external:
+            comps = state.error_dict[bidx]
+            for cnt, e in enumerate(plan.mats):
+                comps[cnt].query(work[e.g_off : e.g_off + e.numel], alpha)
+            copy = work.clone()
+
+        pmem, qmem, fresh = self._pq_memory(state, bidx)
+        eps = float(getattr(state, "orthogonalization_epsilon", 0) or 0)
+        symm = self.symm
+        slot = self.step & 1
+        if nmats:
+            if fresh:
+                seed = int(state.rng.randint(1_000_000_000))
+                native.check(lib.conef_fill_normal(qmem.data_ptr(), qmem.numel(), seed, st), "fill_normal")
+            if self.variant != "unbiased":
+                native.check(lib.conef_orthogonalize(self.mats_dev.data_ptr(), nmats, 1, qmem.data_ptr(), eps,
+                                                     0, 0, 1, 0, self.status.data_ptr(), 0, st), "orth_q")
+
+        # 1. uncompressed tensors -> staging ; P = (G + e) Q
+        stage = symm.local(slot, 0) if symm else self.staging
+        p_target = symm.local(slot, 1) if symm else pmem
+        if plan.total_unc:
+            native.check(lib.conef_gather_segments(self.segs_dev.data_ptr(), len(plan.segs), wp,
+                                                   native.ptr(dense_err), stage.data_ptr(), plan.total_unc, st),
+                         "gather_segments")
+        if nmats:
+            self._launch_p(wp, sketch, dense_err, qmem, p_target, alpha, st)
+
+        # 2. all-reduce of staging and P ; Gram-Schmidt of P
+        orth_p = self.variant != "unbiased"
+        if symm:
+            self.epoch += 1
+            native.check(lib.conef_signal_peers(symm.peer_flags_dev(), ws, self.rank, self.epoch, st), "signal")
+            if nmats and orth_p:
+                native.check(lib.conef_orthogonalize(
+                    self.mats_dev.data_ptr(), nmats, 0, pmem.data_ptr(), eps, symm.peer_ptrs_dev(slot, 1),
+                    symm.flags_ptr(), ws, self.epoch, self.status.data_ptr(), DEFAULT_SPIN_LIMIT, st), "orth_p")
+            elif nmats:
+                native.check(lib.conef_allreduce_oneshot(
+                    pmem.data_ptr(), symm.peer_ptrs_dev(slot, 1), 0, symm.flags_ptr(), ws, self.rank, self.epoch,
+                    plan.total_p, 1.0 / ws, self.status.data_ptr(), DEFAULT_SPIN_LIMIT, st), "allreduce_p")
+            else:
+                native.check(lib.conef_wait_flags(symm.flags_ptr(), ws, self.epoch, self.status.data_ptr(),
+                                                  DEFAULT_SPIN_LIMIT, st), "wait_flags")
+            if plan.total_unc:
+                native.check(lib.conef_scatter_segments(
+                    self.segs_dev.data_ptr(), len(plan.segs), wp, symm.peer_ptrs_dev(slot, 0), ws, 0, 1.0 / ws,
+                    native.ptr(dense_err), plan.total_unc, st), "scatter_segments")
+        else:
+            if ws > 1:
+                if plan.total_unc:
+                    self._nccl_sum(stage[: plan.total_unc], self.group)
+                if nmats:
+                    self._nccl_sum(pmem, self.group, average=not orth_p)
+            if plan.total_unc:
+                native.check(lib.conef_scatter_segments(
+                    self.segs_dev.data_ptr(), len(plan.segs), wp, 0, 1, stage.data_ptr(), 1.0 / ws,
+                    native.ptr(dense_err), plan.total_unc, st), "scatter_segments")
+            if nmats and orth_p:
+                native.check(lib.conef_orthogonalize(self.mats_dev.data_ptr(), nmats, 0, pmem.data_ptr(), eps,
+                                                     0, 0, 1, 0, self.status.data_ptr(), 0, st), "orth_p")
+
+        if nmats:
+            # 3. Q = M^T P (skipped by the unbiased compressor: Q stays the random projection)
+            if self.variant != "unbiased":
+                q_target = symm.local(slot, 2) if symm else qmem
+                if self.q_atomic or self.use_tc:
+                    q_target[: plan.total_q].zero_()
+                self._launch_q(wp, pmem, q_target, st)
+                if symm:
+                    self.epoch += 1
+                    native.check(lib.conef_allreduce_oneshot(
+                        qmem.data_ptr(), symm.peer_ptrs_dev(slot, 2), symm.peer_flags_dev(), symm.flags_ptr(), ws,
+                        self.rank, self.epoch, plan.total_q, 1.0 / ws, self.status.data_ptr(),
+                        DEFAULT_SPIN_LIMIT, st), "allreduce_q")
+                elif ws > 1:
+                    self._nccl_sum(qmem, self.group, average=True)
+            # 4. M_hat = P Q^T, residual -> error store
+            native.check(lib.conef_psgd_decompress(
+                self.mats_dev.data_ptr(), self.d_tiles.data_ptr(), self.n_d_tiles, self.d_rows, wp,
+                pmem.data_ptr(), qmem.data_ptr(), 1.0, native.ptr(sketch), native.ptr(self.tables),
+                native.ptr(self.counts), native.ptr(dense_err), beta, self.ef_mode, self.max_rank,
+                self.d_smem, st), "decompress")
+
+        if self.external:
+            copy.sub_(work)
+            comps = state.error_dict[bidx]
+            for cnt, e in enumerate(plan.mats):
+                comps[cnt].update(copy[e.g_off : e.g_off + e.numel], beta)
+        if self.variant == "batched":
+            buf.copy_(work[: self.buf_numel])
+        if not getattr(state, "warm_start", False) or self.variant == "unbiased":
+            state.p_memory_dict.pop(bidx, None)
+            state.q_memory_dict.pop(bidx, None)
+        self.step += 1
+
+    def _launch_p(self, wp, sketch, dense_err, qmem, p_target, alpha, st):
+        lib = self.lib
+        if self.use_tc:
+            rc = lib.conef_psgd_p_tc(self.mats_dev.data_ptr(), self.p_tiles.data_ptr(), self.n_p_tiles, wp,
+                                     native.ptr(sketch), native.ptr(self.tables), native.ptr(dense_err),
+                                     qmem.data_ptr(), p_target.data_ptr(), alpha, self.ef_mode,
+                                     self.status.data_ptr(), st)
+            native.check(rc, "psgd_p_tc")
+            return
+        native.check(lib.conef_psgd_p(self.mats_dev.data_ptr(), self.p_tiles.data_ptr(), self.n_p_tiles, wp,
+                                      native.ptr(sketch), native.ptr(self.tables), native.ptr(dense_err),
+                                      qmem.data_ptr(), p_target.data_ptr(), alpha, self.ef_mode, self.max_rank, st),
+                     "psgd_p")
+
+    def _launch_q(self, wp, pmem, q_target, st):
+        lib = self.lib
+        native.check(lib.conef_psgd_q(self.mats_dev.data_ptr(), self.q_tiles.data_ptr(), self.n_q_tiles, wp,
+                                      pmem.data_ptr(), q_target.data_ptr(), self.max_rank, st), "psgd_q")
+
+
+def _get_engine(state, bucket, buf, group, factory):
+    bidx = bucket.index()
+    eng = state._engines.get(bidx)
+    if eng is None or eng.buf_ptr != buf.data_ptr() or eng.buf_numel != buf.numel():
+        eng = factory()
+        state._engines[bidx] = eng
+    return eng
+
+
+def run_powersgd_native(state, bucket, group, variant: str) -> torch.futures.Future:
+    buf = bucket.buffer()
+    dev = buf.device
+    stream = comm_stream_for(dev)
+    stream.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(stream):
+        eng = _get_engine(state, bucket, buf, group,
+                          lambda: PowerSGDEngine(state, buf, bucket.gradients(), group, variant))
+        eng.run(state, bucket, buf)
+        fut = _done_on_current_stream(buf)
+    state.maybe_increase_iter(bucket)
+    return fut
+
+
+# ==========================================================================
+# random block
+# ==========================================================================
+class RandBlockEngine(_EngineBase):
+    def __init__(self, state, buf, grads, group, unbiased: bool):
+        super().__init__(buf.device)
+        dev = self.device
+        self.group, self.world = group, group.size()
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.buf_ptr, self.buf_numel = buf.data_ptr(), buf.numel()
+        self.unbiased = unbiased
+        self.plan = planlib.build_block_plan(buf, grads, state.compression_ratio)
+        plan = self.plan
+        ef = (not unbiased) and state.use_error_feedback
+        ec = ef and state.use_error_compression
+        kind = getattr(state, "error_compressor", "count_sketch")
+        if not ef:
+            self.ef_mode = native.EF_NONE
+        elif not ec:
+            self.ef_mode = native.EF_DENSE
+        elif kind == "count_sketch":
+            self.ef_mode = native.EF_SKETCH
+        elif kind == "quant8":
+            self.ef_mode = native.EF_QUANT8
+        else:
+            raise native.NativeError(f"random block + {kind}: not fused")  # caller falls back
+
+        blks = np.zeros(len(plan.blocks), dtype=native.BLK_DTYPE)
+        seeds = ref.derive_hash_seeds(getattr(state, "hash_seed", 0), 1)[0]
+        arena = tab_off = cnt_off = scale_off = 0
+        table_index, table_chunks, count_chunks = {}, [], []
+        widths = []
+        for k, b in enumerate(plan.blocks):
+            rec = blks[k]
+            rec["g_off"], rec["numel"], rec["block"], rec["stage_off"] = b.g_off, b.numel, b.block, b.stage_off
+            rec["n"], rec["m"] = b.n, b.m
+            rec["tab_off"], rec["cnt_off"] = -1, -1
+            rec["sk_off"] = arena
+            if self.ef_mode == native.EF_SKETCH:
+                W = ref.sketch_width(b.m, state.sketch_size)
+                widths.append(W)
+                rec["W"] = W
+                key = (b.m, W)
+                if key not in table_index:
+                    _, _, packed, counts = tables_for(dev, b.m, W, seeds[0], seeds[1])
+                    table_index[key] = (tab_off, cnt_off)
+                    table_chunks.append(packed)
+                    count_chunks.append(counts)
+                    tab_off += b.m
+                    cnt_off += W
+                rec["tab_off"], rec["cnt_off"] = table_index[key]
+                arena += b.n * W
+            else:
+                arena += b.numel
+                rec["scale_off"] = scale_off
+                scale_off += (b.numel + QGROUP - 1) // QGROUP
+        self.blks_host = blks
+        self.arena_elems, self.n_scales = arena, scale_off
+        self.tables = torch.cat(table_chunks) if table_chunks else None
+        self.counts = torch.cat(count_chunks) if count_chunks else None
+        if self.ef_mode == native.EF_SKETCH:
+            maxW = max(widths, default=1)
+            if maxW * 4 > SMEM_BUDGET:
+                raise native.NativeError(f"sketch width {maxW} does not fit in shared memory")
+            self.rows = int(max(1, min(8, SMEM_BUDGET // (maxW * 4))))
+            self.smem = self.rows * maxW * 4
+            tiles = [(k, rb) for k, b in enumerate(plan.blocks) for rb in range(math.ceil(b.n / self.rows))]
+        else:
+            self.rows, self.smem = 0, 0
+            tiles = [(k, g) for k, b in enumerate(plan.blocks) for g in range((b.numel + QGROUP - 1) // QGROUP)]
+        self.n_tiles = len(tiles)
+        self.tiles = torch.from_numpy(np.asarray(tiles, dtype=np.int32).reshape(-1, 2)).to(dev) if tiles else None
+        segs = np.zeros(len(plan.segs), dtype=native.SEG_DTYPE)
+        for k, s in enumerate(plan.segs):
+            segs[k] = (s.g_off, s.dst_off, s.numel)
+        self.segs_dev = native.upload_struct_array(segs, dev) if len(segs) else None
+        self.blks_dev = torch.empty(max(blks.nbytes, 1), dtype=torch.uint8, device=dev)
+        self.staging_unc = torch.empty(max(plan.total_unc, 1), device=dev, dtype=torch.float32)
+        self.staging_blk = torch.empty(max(plan.total_block, 1), device=dev, dtype=torch.float32)
+        self.err_arena = self.codes = self.scales = None
+        self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_block, 4)], group, dev) \
+            if self.world > 1 else None
+
+    def bind_state(self, state, bidx):
+        if self.ef_mode == native.EF_NONE:
+            return
+        plan, dev = self.plan, self.device
+        errs = state.error_dict.get(bidx)
+        errs = errs if isinstance(errs, list) else []
+        new = []
+        if self.ef_mode == native.EF_QUANT8:
+            if self.codes is None:
+                self.codes = torch.zeros(max(self.arena_elems, 1), dtype=torch.int8, device=dev)
+                self.scales = torch.zeros(max(self.n_scales, 1), dtype=torch.float32, device=dev)
+            for k, (b, rec) in enumerate(zip(plan.blocks, self.blks_host)):
+                c0, s0 = int(rec["sk_off"]), int(rec["scale_off"])
+                ng = (b.numel + QGROUP - 1) // QGROUP
+                cv, sv = self.codes[c0 : c0 + b.numel], self.scales[s0 : s0 + ng]
+                old = errs[k] if k < len(errs) else None
+                if isinstance(old, Quant8Error) and old.codes.numel() == b.numel:
+                    if old.codes.data_ptr() != cv.data_ptr():
+                        cv.copy_(old.codes.to(dev)); sv.copy_(old.scales.to(dev))
+                        old.codes, old.scales = cv, sv
+                    new.append(old)
+                else:
+                    new.append(Quant8Error(b.n, b.m, device=dev, codes=cv, scales=sv))
+        else:
+            if self.err_arena is None:
+                self.err_arena = torch.zeros(max(self.arena_elems, 1), dtype=torch.float32, device=dev)
+            for k, (b, rec) in enumerate(zip(plan.blocks, self.blks_host)):
+                o = int(rec["sk_off"])
+                old = errs[k] if k < len(errs) else None
+                if self.ef_mode == native.EF_DENSE:
+                    view = self.err_arena[o : o + b.numel].view(b.n, b.m)
+                    if torch.is_tensor(old) and old.numel() == b.numel and old.data_ptr() != view.data_ptr():
+                        view.copy_(old.to(dev).view(b.n, b.m))
+                    new.append(view)
+                else:
+                    W = int(rec["W"])
+                    view = self.err_arena[o : o + b.n * W]
+                    if isinstance(old, DenseCS) and (old.N, old.D, old.range) == (b.n, b.m, W):
+                        if old.cs.data_ptr() != view.data_ptr():
+                            view.copy_(old.cs.reshape(-1).to(dev))
+                            old.cs = view.view(b.n, W)
+                        new.append(old)
+                    else:
+                        new.append(DenseCS(b.n, b.m, state.sketch_size, device=dev,
+                                           seed=getattr(state, "hash_seed", 0), storage=view))
+        state.error_dict[bidx] = new
+
+    def run(self, state, bucket, buf):
+        lib, plan, dev = self.lib, self.plan, self.device
+        bidx, ws = bucket.index(), self.world
+        st = native.stream_ptr(dev)
+        if self.step == 0 or self.ef_mode != native.EF_NONE and not isinstance(state.error_dict.get(bidx), list):
+            self.bind_state(state, bidx)
+        nb = len(plan.blocks)
+        # shared-RNG block offsets: one draw per compressed tensor, in bucket order
+        blks = self.blks_host
+        for k, b in enumerate(plan.blocks):
+            blks["start"][k] = int(state.rng.choice(b.numel))
+        if nb:
+            host = torch.from_numpy(blks.view(np.uint8).reshape(-1).copy()).pin_memory()
+            self.blks_dev[: host.numel()].copy_(host, non_blocking=True)
+        symm, slot = self.symm, self.step & 1
+        stage_unc = symm.local(slot, 0) if symm else self.staging_unc
+        stage_blk = symm.local(slot, 1) if symm else self.staging_blk
+        state.compressed_tensor_memory[bidx] = stage_blk[: plan.total_block]
+        bp = buf.data_ptr()
+        beta = getattr(state, "beta", 0.0)
+        if plan.total_unc:
+            native.check(lib.conef_gather_segments(self.segs_dev.data_ptr(), len(plan.segs), bp, 0,
+                                                   stage_unc.data_ptr(), plan.total_unc, st), "gather_segments")
+        if nb:
+            # gather scale 0 = unbiased estimator: the kernel divides the selected values by
+            # the per-tensor selection probability block/numel
+            native.check(lib.conef_randblock_gather(
+                self.blks_dev.data_ptr(), self.tiles.data_ptr(), self.n_tiles, self.rows, bp, stage_blk.data_ptr(),
+                0.0 if self.unbiased else 1.0, native.ptr(self.err_arena) if self.ef_mode == native.EF_SKETCH else 0,
+                native.ptr(self.tables), native.ptr(self.counts),
+                native.ptr(self.err_arena) if self.ef_mode == native.EF_DENSE else 0,
+                native.ptr(self.codes), native.ptr(self.scales), 1.0 - beta, beta, self.ef_mode, self.smem, st),
+                "randblock_gather")
+        if symm:
+            self.epoch += 1
+            native.check(lib.conef_signal_peers(symm.peer_flags_dev(), ws, self.rank, self.epoch, st), "signal")
+            native.check(lib.conef_wait_flags(symm.flags_ptr(), ws, self.epoch, self.status.data_ptr(),
+                                              DEFAULT_SPIN_LIMIT, st), "wait_flags")
+            peers_unc, peers_blk, loc_unc, loc_blk = symm.peer_ptrs_dev(slot, 0), symm.peer_ptrs_dev(slot, 1), 0, 0
+        else:
+            if ws > 1:
+                if plan.total_unc:
+                    self._nccl_sum(stage_unc[: plan.total_unc], self.group)
+                if nb:
+                    self._nccl_sum(stage_blk[: plan.total_block], self.group)
+            peers_unc = peers_blk = 0
+            loc_unc, loc_blk = stage_unc.data_ptr(), stage_blk.data_ptr()
+        if plan.total_unc:
+            native.check(lib.conef_scatter_segments(self.segs_dev.data_ptr(), len(plan.segs), bp, peers_unc, ws,
+                                                    loc_unc, 1.0 / ws, 0, plan.total_unc, st), "scatter_segments")
+        if nb:
+            native.check(lib.conef_randblock_scatter(self.blks_dev.data_ptr(), nb, bp, peers_blk, ws, loc_blk,
+                                                     1.0 / ws, plan.total_block, st), "randblock_scatter")
+        self.step += 1
+
+
+def run_randblock_native(state, bucket, group, unbiased: bool) -> torch.futures.Future:
+    from .hooks import _randblock_torch
+
+    buf = bucket.buffer()
+    dev = buf.device
+    stream = comm_stream_for(dev)
+    stream.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(stream):
+        try:
+            eng = _get_engine(state, bucket, buf, group,
+                              lambda: RandBlockEngine(state, buf, bucket.gradients(), group, unbiased))
+        except native.NativeError as exc:
+            if "not fused" not in str(exc):
+                raise
+            # compressors without a fused kernel: PyTorch ops + the stand-alone native kernels
+            return _randblock_torch(state, bucket, group, unbiased=unbiased)
+        eng.run(state, bucket, buf)
+        fut = _done_on_current_stream(buf)
+    state.maybe_increase_iter(bucket)
+    return fut
