@@ -12,6 +12,7 @@ The reference's import names are kept as thin aliases under
 """
 from .parallel import *  # noqa: F401,F403
 from .parallel import __all__ as _parallel_all
+from .trainer import DataParallelTrainer
 
 __version__ = "0.1.0"
-__all__ = list(_parallel_all)
+__all__ = list(_parallel_all) + ["DataParallelTrainer"]

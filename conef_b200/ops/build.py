@@ -76,7 +76,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
             if res.returncode != 0:
                 raise RuntimeError(f"nvcc failed on {src.name}")
             objs.append(str(obj))
-    link = [nvcc, "-shared", "-o", str(OUT), *objs, "-lcuda", "-lcudart"]
+    link = [nvcc, "-shared", "-o", str(OUT), *objs, "-lcudart"]
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)

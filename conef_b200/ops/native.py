@@ -15,7 +15,7 @@ import numpy as np
 import torch
 
 _SO = Path(__file__).resolve().parent / "_conef_native.so"
-_lib: Optional[C.CDLL] = None
+_lib = None
 
 c_ll = C.c_longlong
 vp = C.c_void_p
@@ -84,6 +84,43 @@ _OPTIONAL = {
 }
 
 
+# How many kernels one call of an entry point enqueues (memsets not counted);
+# everything not listed launches exactly one.  Host-only entry points launch none.
+_KERNELS_PER_CALL = {
+    "conef_lamb_step": 3, "conef_version": 0, "conef_tc_supported": 0, "conef_last_error": 0,
+    "conef_ipc_get_handle": 0, "conef_ipc_open_handle": 0, "conef_ipc_close_handle": 0,
+    "conef_cpu_hash_table": 0, "conef_cpu_sketch_query": 0, "conef_cpu_sketch_update": 0,
+    "conef_cpu_gram_schmidt": 0,
+}
+launch_count = 0  # kernels enqueued through this binding since import (see reset_launch_count)
+
+
+def reset_launch_count() -> int:
+    global launch_count
+    old, launch_count = launch_count, 0
+    return old
+
+
+class _CountingLib:
+    """Attribute proxy over the CDLL that counts kernel launches per call."""
+
+    def __init__(self, handle):
+        object.__setattr__(self, "_handle", handle)
+
+    def __getattr__(self, name):
+        fn = getattr(self._handle, name)
+        k = _KERNELS_PER_CALL.get(name, 1)
+        if k == 0:
+            wrapped = fn
+        else:
+            def wrapped(*args, _fn=fn, _k=k):
+                global launch_count
+                launch_count += _k
+                return _fn(*args)
+        object.__setattr__(self, name, wrapped)
+        return wrapped
+
+
 def so_path() -> Path:
     return _SO
 
@@ -96,7 +133,7 @@ def available() -> bool:
         return False
 
 
-def lib() -> C.CDLL:
+def lib():
     global _lib
     if _lib is not None:
         return _lib
@@ -118,8 +155,8 @@ def lib() -> C.CDLL:
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = restype
-    _lib = handle
-    return handle
+    _lib = _CountingLib(handle)
+    return _lib
 
 
 def check(rc: int, what: str = "") -> None:

@@ -42,6 +42,10 @@ from .states import (PowerSGDState, RandomBlockState, UnbiasedRandomBlockState, 
 
 logger = logging.getLogger(__name__)
 
+# Baseline switch: block the host after every bucket on the PyTorch-ops path, as the
+# reference does (communication/powerSGD_hook.py:552-553).  Off in the product path.
+SYNC_EVERY_BUCKET = False
+
 
 # --------------------------------------------------------------------------
 # helpers
@@ -54,6 +58,8 @@ def _done(tensor: torch.Tensor) -> torch.futures.Future[torch.Tensor]:
     """Future already holding ``tensor``; for CUDA tensors it carries an event on
     the current stream, so consumers order themselves after the queued work."""
     if tensor.is_cuda:
+        if SYNC_EVERY_BUCKET:
+            torch.cuda.synchronize(tensor.device)
         fut = torch.futures.Future(devices=[tensor.device])
     else:
         fut = torch.futures.Future()
