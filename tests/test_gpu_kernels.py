@@ -1,0 +1,153 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 reference (needs a B200)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import conef_b200 as cb
+from conef_b200.compressors import DenseCS, DenseCSHash3, HalfDenseCS, Quant8Error
+from conef_b200.ops import native
+from conef_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _st():
+    return native.stream_ptr(torch.device(DEV))
+
+
+def test_native_library_is_loaded():
+    assert native.lib().conef_version() >= 100
+
+
+@pytest.mark.parametrize("D,W", [(5760, 576), (650, 65), (33, 1), (1024, 409)])
+def test_hash_table_kernel(D, W):
+    tab = torch.zeros(D, dtype=torch.int32, device=DEV)
+    cnt = torch.zeros(W, dtype=torch.int32, device=DEV)
+    native.check(native.lib().conef_build_hash_table(tab.data_ptr(), cnt.data_ptr(), D, W, ref.DEFAULT_A,
+                                                     ref.DEFAULT_B, 2, 3, _st()))
+    want = ref.packed_hash_table(D, W, ref.DEFAULT_A, ref.DEFAULT_B)
+    assert np.array_equal(tab.cpu().numpy(), want)
+    idx, _ = ref.hash_table(D, W)
+    assert np.array_equal(cnt.cpu().numpy(), np.bincount(idx.numpy(), minlength=W))
+
+
+@pytest.mark.parametrize("cls", [DenseCS, HalfDenseCS, DenseCSHash3])
+@pytest.mark.parametrize("N,D,size", [(7, 333, 0.1), (64, 576, 0.1), (3, 50, 0.01), (130, 1030, 0.5)])
+def test_sketch_kernels_match_reference(cls, N, D, size):
+    torch.manual_seed(0)
+    g, c = cls(N, D, size, device=DEV), cls(N, D, size, device="cpu")
+    tol = dict(rtol=2e-3, atol=2e-3) if cls is HalfDenseCS else dict(rtol=1e-4, atol=1e-4)
+    for step in range(3):
+        v = torch.randn(N, D)
+        g.update(v.to(DEV), 0.9)
+        c.update(v.clone(), 0.9)
+        m = torch.randn(N, D)
+        mg = m.to(DEV)
+        g.query(mg, 0.1)
+        c.query(m, 0.1)
+        torch.testing.assert_close(mg.cpu(), m, **tol)
+    rows_g = g._rows() if cls is DenseCSHash3 else (g.cs,)
+    rows_c = c._rows() if cls is DenseCSHash3 else (c.cs,)
+    for a, b in zip(rows_g, rows_c):
+        torch.testing.assert_close(a.float().cpu(), b.float(), **tol)
+
+
+def test_quant8_kernels_match_reference():
+    torch.manual_seed(1)
+    g, c = Quant8Error(5, 1000, device=DEV), Quant8Error(5, 1000, device="cpu")
+    for _ in range(3):
+        v = torch.randn(5, 1000)
+        g.update(v.to(DEV), 0.5)
+        c.update(v.clone(), 0.5)
+    # codes may differ by one step where a value sits on a rounding boundary
+    assert (g.codes.cpu().int() - c.codes.int()).abs().max() <= 1
+    torch.testing.assert_close(g.scales.cpu(), c.scales, rtol=1e-5, atol=1e-7)
+    x = torch.randn(5, 1000)
+    xg = x.to(DEV)
+    g.query(xg, 0.7)
+    c.query(x, 0.7)
+    torch.testing.assert_close(xg.cpu(), x, rtol=0, atol=float(c.scales.max()) * 0.8)
+
+
+def test_fill_normal_is_deterministic_and_normal():
+    a = torch.empty(1_000_003, device=DEV)
+    b = torch.empty(1_000_003, device=DEV)
+    lib = native.lib()
+    native.check(lib.conef_fill_normal(a.data_ptr(), a.numel(), 12345, _st()))
+    native.check(lib.conef_fill_normal(b.data_ptr(), b.numel(), 12345, _st()))
+    assert torch.equal(a, b)
+    native.check(lib.conef_fill_normal(b.data_ptr(), b.numel(), 12346, _st()))
+    assert not torch.equal(a, b)
+    assert abs(float(a.mean())) < 5e-3 and abs(float(a.std()) - 1) < 5e-3
+    assert torch.isfinite(a).all()
+
+
+def test_lamb_kernel_matches_reference():
+    from conef_b200.optim import FusedLAMB
+
+    torch.manual_seed(2)
+    shapes = [(300, 70), (70,), (1, 5), (200000,)]
+    pg = [torch.nn.Parameter(torch.randn(s, device=DEV)) for s in shapes]
+    pc = [torch.nn.Parameter(p.detach().cpu().clone()) for p in pg]
+    og = FusedLAMB([{"params": pg[:2], "weight_decay": 0.01}, {"params": pg[2:], "weight_decay": 0.0}], lr=1e-2)
+    oc = FusedLAMB([{"params": pc[:2], "weight_decay": 0.01}, {"params": pc[2:], "weight_decay": 0.0}], lr=1e-2)
+    for _ in range(3):
+        for a, b in zip(pg, pc):
+            g = torch.randn(a.shape) * 3
+            a.grad, b.grad = g.to(DEV), g.clone()
+        og.step()
+        oc.step()
+    for a, b in zip(pg, pc):
+        torch.testing.assert_close(a.detach().cpu(), b.detach(), rtol=2e-4, atol=2e-5)
+
+
+def test_bounded_wait_gives_up_and_process_survives():
+    """A wait on a flag nobody sets returns an error status instead of hanging."""
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    native.check(native.lib().conef_wait_flags(flags.data_ptr(), 2, 5, status.data_ptr(), 2000, _st()))
+    torch.cuda.synchronize()
+    assert int(status[0]) == 1
+    # the context is still usable
+    assert float(torch.ones(4, device=DEV).sum()) == 4.0
+
+
+def test_oneshot_allreduce_math_with_preset_flags():
+    """Two 'ranks' emulated as two buffers on one GPU with the flags already published."""
+    n = 10_007
+    a, b = torch.randn(n, device=DEV), torch.randn(n, device=DEV)
+    out = torch.empty(n, device=DEV)
+    ptrs = torch.tensor([a.data_ptr(), b.data_ptr()], dtype=torch.int64, device=DEV)
+    flags = torch.full((8,), 3, dtype=torch.int32, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    native.check(native.lib().conef_allreduce_oneshot(out.data_ptr(), ptrs.data_ptr(), 0, flags.data_ptr(), 2, 0, 3,
+                                                      n, 0.5, status.data_ptr(), 1000, _st()))
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    torch.testing.assert_close(out, (a + b) * 0.5)
+
+
+def test_orthogonalize_kernel():
+    torch.manual_seed(3)
+    shapes = [(1000, 4), (37, 3), (5000, 8), (9, 1)]
+    mats = np.zeros(len(shapes), dtype=native.MAT_DTYPE)
+    off = 0
+    for k, (n, r) in enumerate(shapes):
+        mats[k]["n"], mats[k]["m"], mats[k]["r"], mats[k]["p_off"] = n, 1, r, off
+        off += n * r
+    flat = torch.randn(off)
+    dev = flat.to(DEV)
+    md = native.upload_struct_array(mats, torch.device(DEV))
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    native.check(native.lib().conef_orthogonalize(md.data_ptr(), len(shapes), 0, dev.data_ptr(), 0.0, 0, 0, 1, 0,
+                                                  status.data_ptr(), 0, _st()))
+    got = dev.cpu()
+    off = 0
+    for n, r in shapes:
+        want = flat[off : off + n * r].view(n, r).clone()
+        ref.gram_schmidt_ref(want)
+        torch.testing.assert_close(got[off : off + n * r].view(n, r), want, rtol=1e-3, atol=1e-4)
+        off += n * r
