@@ -151,6 +151,10 @@ def main():
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
 
+    # keep stdout to the one JSON line: NCCL prints its version banner there at VERSION level
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
+
     import torch
     import torch.distributed as dist
 

@@ -99,14 +99,24 @@ int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, i
 // (seed, e), so every rank generates the same Q without communication.
 int conef_fill_normal(float* buf, long long numel, uint64_t seed, cudaStream_t stream);
 
+// In-place error add for the matrices whose P product runs on the tensor-core path:
+// G <- G + alpha * unsketch(S)  (sketch mode)  or  G <- G + dense_err  (dense mode).
+int conef_ef_apply(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
+                   const float* sketch, const int32_t* tables, const float* dense_err, float alpha,
+                   int ef_mode, cudaStream_t stream);
+
 // ---- tcgen05 / TMEM / TMA tiles (powersgd_tc.cu) ----------------------------
 int conef_tc_supported(void);
-int conef_psgd_p_tc(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
-                    const float* sketch, const int32_t* tables, const float* dense_err,
-                    const float* Q, float* P, float alpha, int ef_mode, int* status,
-                    cudaStream_t stream);
-int conef_psgd_q_tc(const ConefMat* mats, const int4* tiles, int ntiles, const float* bucket,
-                    const float* P, float* Q, int* status, cudaStream_t stream);
+// Host side: two 128-byte tensor maps per matrix into maps_out (256 bytes per matrix);
+// ok[i] = 0 when matrix i cannot be addressed by TMA (base not 16-byte aligned or row
+// pitch not a multiple of 16 bytes).
+int conef_tc_encode_maps(const ConefMat* host_mats, int nmats, const float* bucket_dev,
+                         void* maps_out_256B_each, unsigned char* ok);
+// mode 0: P = M Q (small operand Q, output P).  mode 1: Q = M^T P (small operand P, output Q).
+// tiles: int4 records {matrix | atomic << 30, first output row, first K index, K extent}.
+int conef_psgd_tc(int mode, const ConefMat* mats, const void* maps, const void* tiles, int ntiles,
+                  const float* small_base, float* out_base, int max_rank, int* status,
+                  cudaStream_t stream);
 
 // ---- segments, random blocks, quantised error (blocks.cu) -------------------
 int conef_gather_segments(const ConefSeg* segs, int nsegs, const float* bucket,

@@ -35,35 +35,41 @@ k_psgd_p(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, floa
 #pragma unroll
   for (int c = 0; c < RP; ++c) acc[c] = 0.f;
 
-  if (ef_mode == CONEF_EF_SKETCH) {
-    const float* srow = sketch + M.sk_off + (size_t)row * M.W;
-    const int32_t* tab = tables + M.tab_off;
-#pragma unroll 4
-    for (int j = lane; j < m; j += 32) {
-      const int e = tab[j];
-      const float v = g[j] + alpha * unpack_sign(e) * srow[unpack_bucket(e)];
-      g[j] = v;
+  // Loads are issued PB at a time before any store: the corrected matrix is written
+  // back into the same buffer, and a store between two loads would serialise them.
+  constexpr int PB = 8;
+  const float* srow = ef_mode == CONEF_EF_SKETCH ? sketch + M.sk_off + (size_t)row * M.W : nullptr;
+  const int32_t* tab = ef_mode == CONEF_EF_SKETCH ? tables + M.tab_off : nullptr;
+  const float* erow = ef_mode == CONEF_EF_DENSE ? dense_err + M.g_off + (size_t)row * m : nullptr;
+  for (int j0 = lane; j0 < m; j0 += 32 * PB) {
+    float v[PB];
 #pragma unroll
-      for (int c = 0; c < RP; ++c)
-        if (c < r) acc[c] = fmaf(v, q[(size_t)j * r + c], acc[c]);
+    for (int u = 0; u < PB; ++u) {
+      const int j = j0 + 32 * u;
+      v[u] = j < m ? g[j] : 0.f;
     }
-  } else if (ef_mode == CONEF_EF_DENSE) {
-    const float* erow = dense_err + M.g_off + (size_t)row * m;
-#pragma unroll 4
-    for (int j = lane; j < m; j += 32) {
-      const float v = g[j] + erow[j];
-      g[j] = v;
+    if (ef_mode == CONEF_EF_SKETCH) {
+      int e[PB];
 #pragma unroll
-      for (int c = 0; c < RP; ++c)
-        if (c < r) acc[c] = fmaf(v, q[(size_t)j * r + c], acc[c]);
+      for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; e[u] = j < m ? __ldg(tab + j) : 0; }
+#pragma unroll
+      for (int u = 0; u < PB; ++u) {
+        const int j = j0 + 32 * u;
+        if (j < m) v[u] += alpha * unpack_sign(e[u]) * srow[unpack_bucket(e[u])];
+      }
+    } else if (ef_mode == CONEF_EF_DENSE) {
+#pragma unroll
+      for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; if (j < m) v[u] += __ldcs(erow + j); }
     }
-  } else {
-#pragma unroll 4
-    for (int j = lane; j < m; j += 32) {
-      const float v = g[j];
 #pragma unroll
-      for (int c = 0; c < RP; ++c)
-        if (c < r) acc[c] = fmaf(v, q[(size_t)j * r + c], acc[c]);
+    for (int u = 0; u < PB; ++u) {
+      const int j = j0 + 32 * u;
+      if (j < m) {
+        if (ef_mode != CONEF_EF_NONE) g[j] = v[u];
+#pragma unroll
+        for (int c = 0; c < RP; ++c)
+          if (c < r) acc[c] = fmaf(v[u], __ldg(q + (size_t)j * r + c), acc[c]);
+      }
     }
   }
 #pragma unroll
@@ -103,6 +109,55 @@ extern "C" int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles,
                             cudaStream_t stream) {
   if (ntiles <= 0) return 0;
   DISPATCH_RANK(max_rank, launch_p, mats, tiles, ntiles, bucket, sketch, tables, dense_err, Q, P, alpha, ef_mode, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Error add alone (one warp per row), for matrices whose P product is done by the
+// tensor-core kernel: that kernel reads M through TMA and cannot patch it on the fly.
+__global__ void __launch_bounds__(P_WARPS * 32)
+k_ef_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, float* __restrict__ bucket,
+           const float* __restrict__ sketch, const int32_t* __restrict__ tables,
+           const float* __restrict__ dense_err, float alpha, int ef_mode) {
+  const int2 t = tiles[blockIdx.x];
+  const ConefMat M = mats[t.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = t.y * P_WARPS + warp;
+  if (row >= M.n) return;
+  const int m = M.m;
+  float* g = bucket + M.g_off + (size_t)row * m;
+  constexpr int PB = 8;
+  const float* srow = ef_mode == CONEF_EF_SKETCH ? sketch + M.sk_off + (size_t)row * M.W : nullptr;
+  const int32_t* tab = ef_mode == CONEF_EF_SKETCH ? tables + M.tab_off : nullptr;
+  const float* erow = ef_mode == CONEF_EF_DENSE ? dense_err + M.g_off + (size_t)row * m : nullptr;
+  for (int j0 = lane; j0 < m; j0 += 32 * PB) {
+    float v[PB];
+#pragma unroll
+    for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; v[u] = j < m ? g[j] : 0.f; }
+    if (ef_mode == CONEF_EF_SKETCH) {
+      int e[PB];
+#pragma unroll
+      for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; e[u] = j < m ? __ldg(tab + j) : 0; }
+#pragma unroll
+      for (int u = 0; u < PB; ++u) {
+        const int j = j0 + 32 * u;
+        if (j < m) v[u] += alpha * unpack_sign(e[u]) * srow[unpack_bucket(e[u])];
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; if (j < m) v[u] += __ldcs(erow + j); }
+    }
+#pragma unroll
+    for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; if (j < m) g[j] = v[u]; }
+  }
+}
+
+extern "C" int conef_ef_apply(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
+                              const float* sketch, const int32_t* tables, const float* dense_err, float alpha,
+                              int ef_mode, cudaStream_t stream) {
+  if (ntiles <= 0 || ef_mode == CONEF_EF_NONE) return 0;
+  k_ef_apply<<<ntiles, P_WARPS * 32, 0, stream>>>(mats, tiles, bucket, sketch, tables, dense_err, alpha, ef_mode);
+  CONEF_CHECK_LAUNCH("k_ef_apply");
+  return 0;
 }
 
 // ---------------------------------------------------------------------------
@@ -260,15 +315,17 @@ extern "C" int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles,
 }
 
 // ---------------------------------------------------------------------------
-// Decompress + error feedback.  Tile = (matrix, block of rows_per_cta rows).
-// A thread owns a column: it loads Q[j, :] (scaled by q_scale = 1/world) and
-// the column's hash entry once, then for each row of the block computes
-// M_hat = <P[row, :], Q[j, :]>, writes it to the bucket and routes the residual
-// to the error store: a dense buffer, or the row's count sketch accumulated
-// with shared-memory atomics and flushed by one global store per sketch cell.
-template <int RP>
+// Decompress + error feedback.  Tile = (matrix, block of RB rows).
+// A thread owns a column: it loads Q[j, :] (scaled by q_scale) and the column's
+// hash entry once, then for the RB rows of the block loads M (all RB loads in
+// flight before the first store: M_hat overwrites M in the same buffer),
+// computes M_hat = <P[row, :], Q[j, :]>, writes it to the bucket and routes the
+// residual to the error store: a dense buffer, or the row's count sketch
+// accumulated with shared-memory atomics and flushed by one plain global store
+// per sketch cell (a sketch row belongs to exactly one CTA).
+template <int RP, int RB>
 __global__ void __launch_bounds__(D_THREADS)
-k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int rows_per_cta,
+k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles,
                   float* __restrict__ bucket, const float* __restrict__ P, const float* __restrict__ Q,
                   float q_scale, float* __restrict__ sketch, const int32_t* __restrict__ tables,
                   const int32_t* __restrict__ counts, float* __restrict__ dense_err, float beta,
@@ -277,14 +334,14 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
   const int2 t = tiles[blockIdx.x];
   const ConefMat M = mats[t.x];
   const int m = M.m, r = M.r, W = M.W;
-  const int row0 = t.y * rows_per_cta;
-  const int rows = min(rows_per_cta, M.n - row0);
-  float* ps = sm;                              // rows_per_cta * RP
-  float* acc = sm + (size_t)rows_per_cta * RP; // rows_per_cta * W (sketch mode)
+  const int row0 = t.y * RB;
+  const int rows = min(RB, M.n - row0);
+  float* ps = sm;                    // RB * RP
+  float* acc = sm + RB * RP;         // RB * W (sketch mode)
   const float* p = P + M.p_off + (size_t)row0 * r;
-  for (int i = threadIdx.x; i < rows * RP; i += D_THREADS) {
+  for (int i = threadIdx.x; i < RB * RP; i += D_THREADS) {
     const int ii = i / RP, c = i - ii * RP;
-    ps[i] = c < r ? p[(size_t)ii * r + c] : 0.f;
+    ps[i] = (c < r && ii < rows) ? p[(size_t)ii * r + c] : 0.f;
   }
   if (ef_mode == CONEF_EF_SKETCH)
     for (int i = threadIdx.x; i < rows * W; i += D_THREADS) acc[i] = 0.f;
@@ -292,27 +349,33 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
 
   const int32_t* tab = ef_mode == CONEF_EF_SKETCH ? tables + M.tab_off : nullptr;
   float* g0 = bucket + M.g_off + (size_t)row0 * m;
+  float* e0 = ef_mode == CONEF_EF_DENSE ? dense_err + M.g_off + (size_t)row0 * m : nullptr;
   for (int j = threadIdx.x; j < m; j += D_THREADS) {
     float qv[RP];
     const float* q = Q + M.q_off + (size_t)j * r;
 #pragma unroll
-    for (int c = 0; c < RP; ++c) qv[c] = c < r ? q[c] * q_scale : 0.f;
+    for (int c = 0; c < RP; ++c) qv[c] = c < r ? __ldg(q + c) * q_scale : 0.f;
     int h = 0;
     float s = 0.f;
     if (ef_mode == CONEF_EF_SKETCH) {
-      const int e = tab[j];
+      const int e = __ldg(tab + j);
       h = unpack_bucket(e);
       s = unpack_sign(e);
     }
-    for (int ii = 0; ii < rows; ++ii) {
-      float mh = 0.f;
+    float v[RB];
 #pragma unroll
-      for (int c = 0; c < RP; ++c) mh = fmaf(ps[ii * RP + c], qv[c], mh);
-      float* gp = g0 + (size_t)ii * m + j;
-      const float resid = *gp - mh;
-      *gp = mh;
-      if (ef_mode == CONEF_EF_SKETCH) atomicAdd(&acc[ii * W + h], s * resid);
-      else if (ef_mode == CONEF_EF_DENSE) dense_err[M.g_off + (size_t)(row0 + ii) * m + j] = resid;
+    for (int ii = 0; ii < RB; ++ii) v[ii] = ii < rows ? __ldcs(g0 + (size_t)ii * m + j) : 0.f;
+#pragma unroll
+    for (int ii = 0; ii < RB; ++ii) {
+      if (ii < rows) {
+        float mh = 0.f;
+#pragma unroll
+        for (int c = 0; c < RP; ++c) mh = fmaf(ps[ii * RP + c], qv[c], mh);
+        g0[(size_t)ii * m + j] = mh;
+        const float resid = v[ii] - mh;
+        if (ef_mode == CONEF_EF_SKETCH) atomicAdd(&acc[ii * W + h], s * resid);
+        else if (ef_mode == CONEF_EF_DENSE) __stcs(e0 + (size_t)ii * m + j, resid);
+      }
     }
   }
   if (ef_mode == CONEF_EF_SKETCH) {
@@ -322,9 +385,27 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
     float* srow = sketch + M.sk_off + (size_t)row0 * W;
     for (int i = threadIdx.x; i < rows * W; i += D_THREADS) {
       const int h2 = i % W;
-      srow[i] = srow[i] * (1.f - omb * (float)cnt[h2]) + acc[i];
+      srow[i] = srow[i] * (1.f - omb * (float)__ldg(cnt + h2)) + acc[i];
     }
   }
+}
+
+template <int RP, int RB>
+static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket, const float* P,
+                       const float* Q, float q_scale, float* sketch, const int32_t* tables,
+                       const int32_t* counts, float* dense_err, float beta, int ef_mode, size_t smem,
+                       cudaStream_t stream) {
+  smem += (size_t)RB * RP * sizeof(float);
+  if (smem > 220 * 1024) { conef_set_error("decompress: %zu bytes of shared memory needed", smem); return 2; }
+  static size_t configured = 0;
+  if (smem > 48 * 1024 && smem > configured) {
+    CONEF_CUDA(cudaFuncSetAttribute(k_psgd_decompress<RP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = smem;
+  }
+  k_psgd_decompress<RP, RB><<<ntiles, D_THREADS, smem, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables,
+                                                                counts, dense_err, beta, ef_mode);
+  CONEF_CHECK_LAUNCH("k_psgd_decompress");
+  return 0;
 }
 
 template <int RP>
@@ -332,13 +413,18 @@ static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int row
                     const float* P, const float* Q, float q_scale, float* sketch, const int32_t* tables,
                     const int32_t* counts, float* dense_err, float beta, int ef_mode, size_t smem,
                     cudaStream_t stream) {
-  smem += (size_t)rows_per_cta * RP * sizeof(float);
-  if (smem > 220 * 1024) { conef_set_error("decompress: %zu bytes of shared memory needed", smem); return 2; }
-  CONEF_CUDA(cudaFuncSetAttribute(k_psgd_decompress<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  k_psgd_decompress<RP><<<ntiles, D_THREADS, smem, stream>>>(mats, tiles, rows_per_cta, bucket, P, Q, q_scale,
-                                                           sketch, tables, counts, dense_err, beta, ef_mode);
-  CONEF_CHECK_LAUNCH("k_psgd_decompress");
-  return 0;
+#define CONEF_D_CASE(RB)                                                                              \
+  case RB: return launch_d_rb<RP, RB>(mats, tiles, ntiles, bucket, P, Q, q_scale, sketch, tables, counts, \
+                                      dense_err, beta, ef_mode, smem, stream)
+  switch (rows_per_cta) {
+    CONEF_D_CASE(8);
+    CONEF_D_CASE(4);
+    CONEF_D_CASE(2);
+    CONEF_D_CASE(1);
+  }
+#undef CONEF_D_CASE
+  conef_set_error("decompress: rows_per_cta must be 1, 2, 4 or 8 (got %d)", rows_per_cta);
+  return 2;
 }
 
 extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta,

@@ -58,6 +58,9 @@ _SIGNATURES = {
                                C.c_int, C.c_int, C.c_size_t, vp], C.c_int),
     "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),
     "conef_tc_supported": ([], C.c_int),
+    "conef_ef_apply": ([vp, vp, C.c_int, vp, vp, vp, vp, C.c_float, C.c_int, vp], C.c_int),
+    "conef_tc_encode_maps": ([vp, C.c_int, vp, vp, vp], C.c_int),
+    "conef_psgd_tc": ([C.c_int, vp, vp, vp, C.c_int, vp, vp, C.c_int, vp, vp], C.c_int),
     "conef_gather_segments": ([vp, C.c_int, vp, vp, vp, c_ll, vp], C.c_int),
     "conef_scatter_segments": ([vp, C.c_int, vp, vp, C.c_int, vp, C.c_float, vp, c_ll, vp], C.c_int),
     "conef_randblock_gather": ([vp, vp, C.c_int, C.c_int, vp, vp, C.c_float, vp, vp, vp, vp, vp, vp,
@@ -78,16 +81,13 @@ _SIGNATURES = {
     "conef_cpu_sketch_update": ([vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float], None),
     "conef_cpu_gram_schmidt": ([vp, C.c_int, C.c_int, C.c_float], None),
 }
-_OPTIONAL = {
-    "conef_psgd_p_tc": ([vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, C.c_float, C.c_int, vp, vp], C.c_int),
-    "conef_psgd_q_tc": ([vp, vp, C.c_int, vp, vp, vp, vp, vp], C.c_int),
-}
+_OPTIONAL = {}
 
 
 # How many kernels one call of an entry point enqueues (memsets not counted);
 # everything not listed launches exactly one.  Host-only entry points launch none.
 _KERNELS_PER_CALL = {
-    "conef_lamb_step": 3, "conef_version": 0, "conef_tc_supported": 0, "conef_last_error": 0,
+    "conef_lamb_step": 3, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
     "conef_ipc_get_handle": 0, "conef_ipc_open_handle": 0, "conef_ipc_close_handle": 0,
     "conef_cpu_hash_table": 0, "conef_cpu_sketch_query": 0, "conef_cpu_sketch_update": 0,
     "conef_cpu_gram_schmidt": 0,

@@ -63,8 +63,7 @@ def _use_tc() -> bool:
     """tcgen05 tiles for P / Q unless ``CONEF_TC=0``."""
     if os.environ.get("CONEF_TC", "1") == "0":
         return False
-    lib = native.lib()
-    return bool(lib.conef_tc_supported()) and hasattr(lib, "conef_psgd_p_tc")
+    return bool(native.lib().conef_tc_supported())
 
 
 def _done_on_current_stream(buf: torch.Tensor) -> torch.futures.Future:
@@ -198,11 +197,17 @@ class PowerSGDEngine(_EngineBase):
         self.p_tiles = self._tiles(p_tiles)
         self.q_tiles = self._tiles(q_tiles)
         self.n_p_tiles, self.n_q_tiles = len(p_tiles), len(q_tiles)
-        # decompress: as many rows per CTA as the sketch rows allow in shared memory
+        # decompress: rows per CTA in {8, 4, 2, 1}: the most that fit in shared memory while
+        # still giving every SM a few CTAs
         maxW = max(self.widths, default=0)
-        self.d_rows = 8 if maxW == 0 else int(max(1, min(8, SMEM_BUDGET // (maxW * 4))))
         if maxW * 4 > SMEM_BUDGET:
             raise native.NativeError(f"sketch width {maxW} does not fit in shared memory")
+        total_rows = sum(e.n for e in plan.mats)
+        self.d_rows = 1
+        for cand in (8, 4, 2):
+            if cand * maxW * 4 <= SMEM_BUDGET // 2 and total_rows // cand >= 3 * 148:
+                self.d_rows = cand
+                break
         self.d_smem = self.d_rows * maxW * 4
         d_tiles = [(k, rb) for k, e in enumerate(plan.mats) for rb in range(math.ceil(e.n / self.d_rows))]
         self.d_tiles = self._tiles(d_tiles)
@@ -223,8 +228,67 @@ class PowerSGDEngine(_EngineBase):
         self.staging = torch.empty(max(plan.total_unc, 1), device=dev, dtype=torch.float32)
         self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_p, 4), max(plan.total_q, 4)], group, dev) \
             if self.world > 1 else None
-        self.use_tc = _use_tc()
         self._bound = None
+        self._build_tc_tables(buf if variant != "batched" else self.work)
+
+    # -- tensor-core path tables -----------------------------------------------
+    def _build_tc_tables(self, work: torch.Tensor) -> None:
+        """Tensor maps and split-K tile lists for the matrices TMA can address; the
+        others stay on the SIMT kernels."""
+        plan, dev = self.plan, self.device
+        self.use_tc = False
+        nm = len(plan.mats)
+        if not nm or not _use_tc():
+            return
+        maps = np.zeros(nm * 256, dtype=np.uint8)   # two 128-byte tensor maps per matrix
+        ok = np.zeros(nm, dtype=np.uint8)
+        host = np.ascontiguousarray(self.mats_host)
+        native.check(self.lib.conef_tc_encode_maps(host.ctypes.data, nm, work.data_ptr(), maps.ctypes.data,
+                                                   ok.ctypes.data), "tc_encode_maps")
+        if not ok.any():
+            return
+        self.tc_ok = ok.astype(bool)
+
+        def split_tiles(mode):
+            # mode 0 (P): output rows = n, K = m.  mode 1 (Q): output rows = m, K = n.
+            blocks = sum(math.ceil((e.m if mode else e.n) / 128) for e, good in zip(plan.mats, self.tc_ok) if good)
+            want = max(1, math.ceil(TARGET_CTAS / max(blocks, 1)))
+            tiles, any_atomic = [], False
+            for k, (e, good) in enumerate(zip(plan.mats, self.tc_ok)):
+                if not good:
+                    continue
+                mn, K = (e.m, e.n) if mode else (e.n, e.m)
+                splits = max(1, min(want, math.ceil(K / 256)))
+                klen = math.ceil(math.ceil(K / splits) / 32) * 32
+                splits = math.ceil(K / klen)
+                flag = (1 << 30) if splits > 1 else 0
+                any_atomic |= splits > 1
+                for mb in range(math.ceil(mn / 128)):
+                    for sp in range(splits):
+                        tiles.append((k | flag, mb * 128, sp * klen, klen))
+            t = torch.from_numpy(np.asarray(tiles, dtype=np.int32).reshape(-1, 4)).to(dev)
+            return t, len(tiles), any_atomic
+
+        self.tc_p_tiles, self.n_tc_p, self.tc_p_atomic = split_tiles(0)
+        self.tc_q_tiles, self.n_tc_q, self.tc_q_atomic = split_tiles(1)
+        self.tc_maps = torch.from_numpy(maps).to(dev)
+        assert self.tc_maps.data_ptr() % 128 == 0
+        good = [k for k in range(nm) if self.tc_ok[k]]
+        bad = [k for k in range(nm) if not self.tc_ok[k]]
+        self.ef_tiles = self._tiles([(k, rb) for k in good for rb in range(math.ceil(plan.mats[k].n / P_ROWS))])
+        self.n_ef_tiles = sum(math.ceil(plan.mats[k].n / P_ROWS) for k in good)
+        # SIMT tile lists shrink to the matrices TMA cannot address
+        p_tiles = [(k, rb) for k in bad for rb in range(math.ceil(plan.mats[k].n / P_ROWS))]
+        q_tiles = []
+        for k in bad:
+            rec = self.mats_host[k]
+            nrb = math.ceil(int(rec["n"]) / int(rec["q_rows"]))
+            ncb = (int(rec["m"]) + Q_COLS - 1) // Q_COLS
+            q_tiles += [(k, t) for t in range(nrb * ncb)]
+        self.p_tiles, self.n_p_tiles = self._tiles(p_tiles), len(p_tiles)
+        self.q_tiles, self.n_q_tiles = self._tiles(q_tiles), len(q_tiles)
+        self.q_atomic = any(bool(self.mats_host[k]["q_atomic"]) for k in bad)
+        self.use_tc = True
 
     def _tiles(self, tiles) -> Optional[torch.Tensor]:
         if not tiles:
@@ -386,7 +450,7 @@ class PowerSGDEngine(_EngineBase):
             # 3. Q = M^T P (skipped by the unbiased compressor: Q stays the random projection)
             if self.variant != "unbiased":
                 q_target = symm.local(slot, 2) if symm else qmem
-                if self.q_atomic or self.use_tc:
+                if self.q_atomic or (self.use_tc and self.tc_q_atomic):
                     q_target[: plan.total_q].zero_()
                 self._launch_q(wp, pmem, q_target, st)
                 if symm:
@@ -419,21 +483,31 @@ class PowerSGDEngine(_EngineBase):
     def _launch_p(self, wp, sketch, dense_err, qmem, p_target, alpha, st):
         lib = self.lib
         if self.use_tc:
-            rc = lib.conef_psgd_p_tc(self.mats_dev.data_ptr(), self.p_tiles.data_ptr(), self.n_p_tiles, wp,
-                                     native.ptr(sketch), native.ptr(self.tables), native.ptr(dense_err),
-                                     qmem.data_ptr(), p_target.data_ptr(), alpha, self.ef_mode,
-                                     self.status.data_ptr(), st)
-            native.check(rc, "psgd_p_tc")
-            return
-        native.check(lib.conef_psgd_p(self.mats_dev.data_ptr(), self.p_tiles.data_ptr(), self.n_p_tiles, wp,
-                                      native.ptr(sketch), native.ptr(self.tables), native.ptr(dense_err),
-                                      qmem.data_ptr(), p_target.data_ptr(), alpha, self.ef_mode, self.max_rank, st),
-                     "psgd_p")
+            # error add as a pre-pass (TMA cannot patch the tile), then tcgen05 tiles
+            if self.ef_mode != native.EF_NONE:
+                native.check(lib.conef_ef_apply(self.mats_dev.data_ptr(), native.ptr(self.ef_tiles),
+                                                self.n_ef_tiles, wp, native.ptr(sketch), native.ptr(self.tables),
+                                                native.ptr(dense_err), alpha, self.ef_mode, st), "ef_apply")
+            if self.tc_p_atomic:
+                p_target[: self.plan.total_p].zero_()
+            native.check(lib.conef_psgd_tc(0, self.mats_dev.data_ptr(), self.tc_maps.data_ptr(),
+                                           self.tc_p_tiles.data_ptr(), self.n_tc_p, qmem.data_ptr(),
+                                           p_target.data_ptr(), self.max_rank, self.status.data_ptr(), st), "psgd_tc(P)")
+        if self.n_p_tiles:
+            native.check(lib.conef_psgd_p(self.mats_dev.data_ptr(), self.p_tiles.data_ptr(), self.n_p_tiles, wp,
+                                          native.ptr(sketch), native.ptr(self.tables), native.ptr(dense_err),
+                                          qmem.data_ptr(), p_target.data_ptr(), alpha, self.ef_mode, self.max_rank,
+                                          st), "psgd_p")
 
     def _launch_q(self, wp, pmem, q_target, st):
         lib = self.lib
-        native.check(lib.conef_psgd_q(self.mats_dev.data_ptr(), self.q_tiles.data_ptr(), self.n_q_tiles, wp,
-                                      pmem.data_ptr(), q_target.data_ptr(), self.max_rank, st), "psgd_q")
+        if self.use_tc:
+            native.check(lib.conef_psgd_tc(1, self.mats_dev.data_ptr(), self.tc_maps.data_ptr(),
+                                           self.tc_q_tiles.data_ptr(), self.n_tc_q, pmem.data_ptr(),
+                                           q_target.data_ptr(), self.max_rank, self.status.data_ptr(), st), "psgd_tc(Q)")
+        if self.n_q_tiles:
+            native.check(lib.conef_psgd_q(self.mats_dev.data_ptr(), self.q_tiles.data_ptr(), self.n_q_tiles, wp,
+                                          pmem.data_ptr(), q_target.data_ptr(), self.max_rank, st), "psgd_q")
 
 
 def _get_engine(state, bucket, buf, group, factory):

@@ -76,8 +76,9 @@ def grad_offsets(buffer: torch.Tensor, grads: Sequence[torch.Tensor]) -> List[in
             offs.append(running)
             continue
         off = (g.data_ptr() - base) // esz
-        if off < 0 or off + g.numel() > buffer.numel() or not g.is_contiguous():
-            # not a view of the buffer (should not happen with DDP): assume packed order
+        dense = g.is_contiguous() or (g.dim() == 4 and g.is_contiguous(memory_format=torch.channels_last))
+        if off < 0 or off + g.numel() > buffer.numel() or not dense:
+            # not a dense view of the buffer (should not happen with DDP): assume packed order
             off = running
         offs.append(off)
         running = off + g.numel()
@@ -87,6 +88,10 @@ def grad_offsets(buffer: torch.Tensor, grads: Sequence[torch.Tensor]) -> List[in
 def build_powersgd_plan(buffer: torch.Tensor, grads: Sequence[torch.Tensor], rank: int,
                         min_compression_rate: float) -> BucketPlan:
     """Partition as in communication/powerSGD_hook.py:394-418 of the reference."""
+    # A gradient is viewed as (shape[0], numel / shape[0]) over its chunk of the bucket *as it
+    # lies in memory*.  For channels-last convolution weights the chunk is ordered
+    # (out, kh, kw, in): still one row per output channel, with the columns permuted - which
+    # changes neither the low-rank structure nor the statistics of the sketch.
     plan = BucketPlan(signature=bucket_signature(buffer, grads), total=buffer.numel())
     offs = grad_offsets(buffer, grads)
     for i, (g, off) in enumerate(zip(grads, offs)):

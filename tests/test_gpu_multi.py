@@ -1,0 +1,185 @@
+"""Two-GPU tests: in-kernel collectives over peer memory vs NCCL vs the closed form (needs >= 2 B200)."""
+import argparse
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+
+import conef_b200 as cb
+from conef_b200.ops import native
+from conef_b200.ops import reference as ref
+from conef_b200.parallel import plan as planlib
+
+from helpers import FakeBucket, run_ranks
+
+pytestmark = pytest.mark.gpu
+SHAPES = [(256, 1024), (64,), (130, 64, 3, 3), (130,), (640, 40, 3, 3), (10, 257), (10,), (33, 2052)]
+
+
+def _need_two_gpus():
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+
+
+def _rel(a, b):
+    return float((a - b).norm() / b.norm().clamp_min(1e-12))
+
+
+def _oneshot_worker(rank, world, comm):
+    os.environ["CONEF_COMM"] = comm
+    from conef_b200.parallel.symm import DEFAULT_SPIN_LIMIT, SymmBuffer
+
+    dev = torch.device("cuda", rank)
+    sb = SymmBuffer([1000, 5000], dist.group.WORLD, dev, backend=comm)
+    lib = native.lib()
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    out = torch.empty(5000, device=dev)
+    for epoch in range(1, 5):
+        slot = epoch & 1
+        src = torch.full((5000,), float(rank + 1) * epoch, device=dev) + torch.arange(5000, device=dev)
+        sb.local(slot, 1).copy_(src)
+        native.check(lib.conef_allreduce_oneshot(out.data_ptr(), sb.peer_ptrs_dev(slot, 1), sb.peer_flags_dev(),
+                                                 sb.flags_ptr(), world, rank, epoch, 5000, 1.0 / world,
+                                                 status.data_ptr(), DEFAULT_SPIN_LIMIT,
+                                                 native.stream_ptr(dev)))
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0
+        want = torch.arange(5000, device=dev) + epoch * sum(range(1, world + 1)) / world
+        torch.testing.assert_close(out, want.float())
+    print(f"rank {rank}: one-shot all-reduce ok ({sb.backend} backend)")
+
+
+@pytest.mark.parametrize("comm", ["auto", "ipc"])
+def test_oneshot_allreduce_over_peer_memory(comm):
+    _need_two_gpus()
+    run_ranks(_oneshot_worker, world=2, args=(comm,), backend="nccl")
+
+
+def _powersgd_worker(rank, world, comm, tc, kw):
+    os.environ["CONEF_COMM"] = comm
+    os.environ["CONEF_TC"] = tc
+    dev = torch.device("cuda", rank)
+    s = cb.PowerSGDState(None, start_powerSGD_iter=2, **kw)
+    s.iter = 2
+    fb = FakeBucket(SHAPES)
+    r = kw["matrix_approximation_rank"]
+    plan = planlib.build_powersgd_plan(fb.buffer(), fb.gradients(), r, 2)
+    g = torch.Generator().manual_seed(0)
+    s.p_memory_dict[0] = torch.zeros(plan.total_p).to(dev)
+    q0 = torch.randn(plan.total_q, generator=g)
+    s.q_memory_dict[0] = q0.clone().to(dev)
+    b = FakeBucket(SHAPES, device=dev, seed=100 + rank)
+    local = b.buffer().clone()
+    allb = [torch.zeros_like(local) for _ in range(world)]
+    dist.all_gather(allb, local)
+    out = cb.powerSGD_hook(s, b).wait()
+    torch.cuda.synchronize()
+    s.check_status()
+    eng = s._engines[0]
+    assert (eng.symm is not None) == (comm != "nccl"), "unexpected communication path"
+    # every rank ends the step with the same gradients, bit for bit
+    outs = [torch.zeros_like(out) for _ in range(world)]
+    dist.all_gather(outs, out.contiguous())
+    assert torch.equal(outs[0], outs[1])
+    # closed form from all ranks' inputs (first step: no error yet)
+    mean = (sum(allb) / world).cpu()
+    tol = 1e-2 if tc == "1" else 2e-3
+    for seg in plan.segs:
+        torch.testing.assert_close(out[seg.g_off : seg.g_off + seg.numel].cpu(), mean[seg.g_off : seg.g_off + seg.numel])
+    for e in plan.mats:
+        q = q0[e.q_off : e.q_off + e.m * e.r].view(e.m, e.r).clone()
+        ref.gram_schmidt_ref(q)
+        mats = [a[e.g_off : e.g_off + e.numel].view(e.n, e.m).cpu() for a in allb]
+        p = sum(m @ q for m in mats)
+        ref.gram_schmidt_ref(p)
+        q2 = sum(m.t() @ p for m in mats) / world
+        got = out[e.g_off : e.g_off + e.numel].view(e.n, e.m).cpu()
+        assert _rel(got, p @ q2.t()) < tol, (e, _rel(got, p @ q2.t()))
+    # two more steps with error feedback keep the ranks in lock step
+    for i in range(2):
+        b.refill(200 + 10 * i + rank)
+        out = cb.powerSGD_hook(s, b).wait()
+    torch.cuda.synchronize()
+    s.check_status()
+    outs = [torch.zeros_like(out) for _ in range(world)]
+    dist.all_gather(outs, out.contiguous())
+    assert torch.equal(outs[0], outs[1]) and torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("comm,tc", [("auto", "0"), ("auto", "1"), ("nccl", "0")])
+def test_powersgd_two_gpus(comm, tc):
+    _need_two_gpus()
+    kw = dict(matrix_approximation_rank=4, use_error_feedback=True, use_error_compression=True, sketch_size=0.1)
+    run_ranks(_powersgd_worker, world=2, args=(comm, tc, kw), backend="nccl")
+
+
+def _randblock_worker(rank, world, comm, kw):
+    os.environ["CONEF_COMM"] = comm
+    dev = torch.device("cuda", rank)
+    s = cb.RandomBlockState(None, start_compression_iter=2, compression_ratio=0.2, **kw)
+    s.iter = 2
+    b = FakeBucket(SHAPES, device=dev, seed=300 + rank)
+    local = b.buffer().clone()
+    allb = [torch.zeros_like(local) for _ in range(world)]
+    dist.all_gather(allb, local)
+    out = cb.RandomBlock_hook(s, b).wait()
+    torch.cuda.synchronize()
+    s.check_status()
+    mean = sum(allb) / world
+    bp = planlib.build_block_plan(local, FakeBucket(SHAPES).gradients(), 0.2)
+    rng = np.random.RandomState(42)
+    for blk in bp.blocks:
+        mask = ref.block_mask(blk.numel, 0.2, int(rng.choice(blk.numel)), device=dev)
+        t = out[blk.g_off : blk.g_off + blk.numel]
+        torch.testing.assert_close(t[mask], mean[blk.g_off : blk.g_off + blk.numel][mask])
+        assert float(t[~mask].abs().sum()) == 0.0
+    for seg in bp.segs:
+        torch.testing.assert_close(out[seg.g_off : seg.g_off + seg.numel], mean[seg.g_off : seg.g_off + seg.numel])
+    for i in range(3):
+        b.refill(400 + 10 * i + rank)
+        out = cb.RandomBlock_hook(s, b).wait()
+    torch.cuda.synchronize()
+    s.check_status()
+    outs = [torch.zeros_like(out) for _ in range(world)]
+    dist.all_gather(outs, out.contiguous())
+    assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("comm", ["auto", "nccl"])
+def test_randomblock_two_gpus(comm):
+    _need_two_gpus()
+    run_ranks(_randblock_worker, world=2, args=(comm, dict(use_error_feedback=True)), backend="nccl")
+
+
+def _ddp_worker(rank, world, name):
+    import torch.nn.functional as F
+
+    from conef_b200 import DataParallelTrainer, models
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    ns = argparse.Namespace(grad_reducer=name, start_compression_iter=2, compression_ratio=0.1, beta=0.9,
+                            sketch_size=0.1, matrix_approximation_rank=4, min_compression_rate=2,
+                            orthogonalization_epsilon=0, error_compressor=None)
+    tr = DataParallelTrainer(models.WideResNet(16, 4, 0.0, 10), lambda p: torch.optim.SGD(p, lr=0.05, momentum=0.9),
+                             F.cross_entropy, reducer=ns, device=dev, autocast_dtype=torch.bfloat16,
+                             channels_last=True, bucket_cap_mb=2)
+    g = torch.Generator().manual_seed(10 + rank)
+    x = torch.randn(32, 3, 32, 32, generator=g).to(dev)
+    y = torch.randint(0, 10, (32,), generator=g).to(dev)
+    losses = [float(tr.step(x, y)) for _ in range(8)]
+    torch.cuda.synchronize()
+    tr.check()
+    flat = torch.cat([p.detach().reshape(-1) for p in tr.model.module.parameters()])
+    both = [torch.zeros_like(flat) for _ in range(world)]
+    dist.all_gather(both, flat)
+    assert torch.equal(both[0], both[1]), "parameters diverged across ranks"
+    assert np.isfinite(losses).all() and losses[-1] < losses[0]
+
+
+@pytest.mark.parametrize("name", ["conef_powersgd", "ef_randomblock", "unbiased_mtrx"])
+def test_ddp_two_gpus_ranks_agree(name):
+    _need_two_gpus()
+    run_ranks(_ddp_worker, world=2, args=(name,), backend="nccl")
