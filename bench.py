@@ -151,9 +151,11 @@ def main():
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
         return 0
 
-    # keep stdout to the one JSON line: NCCL prints its version banner there at VERSION level
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # Keep stdout to the one JSON line: libraries (NCCL's version banner, for one) write there,
+    # so file descriptor 1 points at stderr while the benchmark runs and the line goes to the real stdout.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
 
     import torch
     import torch.distributed as dist
@@ -308,7 +310,7 @@ def main():
         }
         if state is not None and hasattr(state, "compression_stats"):
             out["compression_rate"] = state.compression_stats()[0]
-        print(json.dumps(out))
+        os.write(real_stdout, (json.dumps(out) + "\n").encode())
     dist.barrier()
     dist.destroy_process_group()
     return 0
