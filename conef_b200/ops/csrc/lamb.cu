@@ -95,3 +95,52 @@ extern "C" int conef_lamb_step(const ConefLambTensor* tensors, int ntensors, con
   CONEF_CHECK_LAUNCH("k_lamb_stage2");
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant (declared in conef_noalloc.h): the norm scratch lives in
+// static device memory instead of a caller-provided buffer.
+#include "conef_noalloc.h"
+
+static __device__ __align__(256) float g_lamb_scratch[1 + 2 * CONEF_NOALLOC_MAX_TENSORS];
+
+// In host code the array's name is only a handle; kernels need its device address,
+// looked up once per device with that device current.
+static float* g_lamb_scratch_addr[64] = {nullptr};
+
+extern "C" int conef_lamb_step_noalloc(const ConefLambTensor* tensors, int ntensors, const int2* chunks,
+                                       int nchunks, int chunk_elems, float lr, float beta1, float beta2,
+                                       float eps, int step, int bias_correction, float grad_scale,
+                                       float max_grad_norm, cudaStream_t stream) {
+  if (ntensors <= 0 || nchunks <= 0) return 0;
+  if (ntensors > CONEF_NOALLOC_MAX_TENSORS) {
+    conef_set_error("conef_lamb_step_noalloc: %d tensors exceed the built-in scratch of %d tensors; "
+                    "use conef_lamb_step with a caller-provided buffer", ntensors, CONEF_NOALLOC_MAX_TENSORS);
+    return 2;
+  }
+  int dev = -1;
+  CONEF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) { conef_set_error("conef_lamb_step_noalloc: unsupported device index %d", dev); return 2; }
+  if (g_lamb_scratch_addr[dev] == nullptr) {
+    float* addr = nullptr;
+    CONEF_CUDA(cudaGetSymbolAddress((void**)&addr, g_lamb_scratch));
+    g_lamb_scratch_addr[dev] = addr;
+  }
+  float* norms = g_lamb_scratch_addr[dev];
+  // the accumulators of this call start at zero; the rest of the array keeps old values
+  CONEF_CUDA(cudaMemsetAsync(norms, 0, sizeof(float) * (size_t)(1 + 2 * ntensors), stream));
+  if (max_grad_norm > 0.f) {
+    k_lamb_gnorm<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, norms);
+    CONEF_CHECK_LAUNCH("k_lamb_gnorm");
+  }
+  float bc1 = 1.f, bc2 = 1.f;
+  if (bias_correction) {
+    bc1 = 1.f - powf(beta1, (float)step);
+    bc2 = 1.f - powf(beta2, (float)step);
+  }
+  k_lamb_stage1<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, norms, beta1, beta2, eps, bc1, bc2,
+                                                 grad_scale, max_grad_norm);
+  CONEF_CHECK_LAUNCH("k_lamb_stage1");
+  k_lamb_stage2<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, norms, lr);
+  CONEF_CHECK_LAUNCH("k_lamb_stage2");
+  return 0;
+}
