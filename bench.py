@@ -186,7 +186,7 @@ def main():
         ns.grad_reducer = "allreduce"
     if not use_cuda:
         ac_dtype = None
-        tkw = {}
+        tkw = {k: v for k, v in tkw.items() if k != "channels_last"}
     trainer = DataParallelTrainer(model, opt_factory, loss_fn, reducer=ns, device=device,
                                   autocast_dtype=ac_dtype, **tkw)
     if args.impl == "restated" and trainer.state is not None:
