@@ -1,0 +1,194 @@
+"""Micro-benchmark of the compression kernels in isolation, with roofline fractions.
+
+    python -m conef_b200.utils.kernel_bench --case wrn --iters 20
+    python -m conef_b200.utils.kernel_bench --case bert --only decompress --iters 3     # small, for ncu
+
+Builds one synthetic gradient "bucket" larger than the 126 MB L2 (so that DRAM figures
+mean something), runs every kernel of the PowerSGD + ConEF pipeline and of the
+random-block pipeline on it, times each with CUDA events on the launching stream (warm-up,
+synchronise on both sides) and reports achieved bytes/s against the measured HBM copy
+bandwidth (``MEASURED_PEAKS.json`` next to the repository root when present, else the
+6.65 TB/s fallback).  Algorithmic bytes are the minimum traffic of each kernel: every
+matrix element read (and written, where the kernel rewrites it) once.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from pathlib import Path
+
+import numpy as np
+import torch
+
+import conef_b200 as cb
+from conef_b200.ops import native
+from conef_b200.parallel.engine import PowerSGDEngine, RandBlockEngine
+
+CASES = {
+    # (shapes, rank): matrices as in the named model, repeated until the bucket exceeds L2
+    "wrn": ([(640, 640, 3, 3)] * 10 + [(640,)] * 10 + [(320, 320, 3, 3)] * 6 + [(100, 640), (100,)], 4),
+    "bert": ([(1024, 1024)] * 24 + [(4096, 1024)] * 8 + [(1024, 4096)] * 8 + [(1024,)] * 16 + [(4096,)] * 8, 8),
+    "small": ([(256, 1024), (64,), (640, 360)], 4),
+}
+
+
+class _Bucket:
+    def __init__(self, shapes, device):
+        total = sum(int(np.prod(s)) for s in shapes)
+        self.buf = torch.randn(total, device=device)
+        self.shapes = shapes
+
+    def buffer(self):
+        return self.buf
+
+    def index(self):
+        return 0
+
+    def is_last(self):
+        return True
+
+    def gradients(self):
+        out, off = [], 0
+        for s in self.shapes:
+            n = int(np.prod(s))
+            out.append(self.buf[off : off + n].view(s))
+            off += n
+        return out
+
+
+def _peak_gbs() -> tuple:
+    for cand in (Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json",):
+        if cand.exists():
+            return float(json.loads(cand.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def _time(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for s, e in ev:
+        s.record()
+        fn()
+        e.record()
+    torch.cuda.synchronize()
+    ts = sorted(s.elapsed_time(e) for s, e in ev)
+    return ts[len(ts) // 2] * 1e-3          # median, seconds
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="wrn", choices=sorted(CASES))
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--only", default=None, help="run only kernels whose name contains this")
+    ap.add_argument("--sketch-size", type=float, default=0.1)
+    args = ap.parse_args()
+
+    import torch.distributed as dist
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29655")
+    if not dist.is_initialized():
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shapes, rank = CASES[args.case]
+    bucket = _Bucket(shapes, dev)
+    buf = bucket.buffer()
+    peak, peak_kind = _peak_gbs()
+    group = dist.group.WORLD
+    st = native.stream_ptr(dev)
+    lib = native.lib()
+    rows = []
+
+    def record(name, seconds, nbytes, note=""):
+        gbs = nbytes / seconds / 1e9
+        rows.append((name, seconds * 1e6, nbytes / 1e6, gbs, gbs / peak, note))
+
+    def want(name):
+        return args.only is None or args.only in name
+
+    # ---------------- PowerSGD + ConEF sketch pipeline ----------------
+    for tc in ("1", "0"):
+        os.environ["CONEF_TC"] = tc
+        state = cb.PowerSGDState(None, matrix_approximation_rank=rank, start_powerSGD_iter=2,
+                                 use_error_compression=True, sketch_size=args.sketch_size)
+        eng = PowerSGDEngine(state, buf, bucket.gradients(), group, "powersgd")
+        eng.bind_state(state, 0)
+        plan = eng.plan
+        mat_bytes = 4 * sum(e.numel for e in plan.mats)
+        sk_bytes = 4 * eng.sketch_arena.numel()
+        pmem = torch.randn(plan.total_p, device=dev)
+        qmem = torch.randn(plan.total_q, device=dev)
+        eng.sketch_arena.normal_()
+        tag = "tc" if eng.use_tc else "simt"
+        if tc == "1" and not eng.use_tc:
+            continue
+        if want(f"p_{tag}"):
+            t = _time(lambda: eng._launch_p(buf.data_ptr(), eng.sketch_arena, None, qmem, pmem, 0.1, st), args.iters)
+            extra = " (error add pre-pass + tcgen05 tiles)" if eng.use_tc else " (error add fused)"
+            record(f"p_{tag}: P=(G+e)Q", t, 2 * mat_bytes + sk_bytes, "read G + sketch, write G" + extra)
+        if want(f"q_{tag}"):
+            def run_q():
+                if eng.q_atomic or (eng.use_tc and eng.tc_q_atomic):
+                    qmem.zero_()
+                eng._launch_q(buf.data_ptr(), pmem, qmem, st)
+            t = _time(run_q, args.iters)
+            record(f"q_{tag}: Q=M^T P", t, mat_bytes, "read M")
+        if tc == "1":
+            continue
+        if want("orth"):
+            t = _time(lambda: native.check(lib.conef_orthogonalize(eng.mats_dev.data_ptr(), len(plan.mats), 0,
+                                                                   pmem.data_ptr(), 0.0, 0, 0, 1, 0,
+                                                                   eng.status.data_ptr(), 0, st)), args.iters)
+            record("orthogonalize(P)", t, 8 * plan.total_p, "latency bound: 2r passes over P")
+        if want("decompress"):
+            t = _time(lambda: native.check(lib.conef_psgd_decompress(
+                eng.mats_dev.data_ptr(), eng.d_tiles.data_ptr(), eng.n_d_tiles, eng.d_rows, buf.data_ptr(),
+                pmem.data_ptr(), qmem.data_ptr(), 1.0, eng.sketch_arena.data_ptr(), eng.tables.data_ptr(),
+                eng.counts.data_ptr(), 0, 0.9, native.EF_SKETCH, eng.max_rank, eng.d_smem, st)), args.iters)
+            record("decompress+sketch update", t, 2 * mat_bytes + 2 * sk_bytes, "read M, write M_hat, r/w sketch")
+        if want("segments"):
+            t = _time(lambda: native.check(lib.conef_gather_segments(
+                eng.segs_dev.data_ptr(), len(plan.segs), buf.data_ptr(), 0, eng.staging.data_ptr(), plan.total_unc,
+                st)), args.iters)
+            record("gather_segments", t, 8 * plan.total_unc, "latency bound (small)")
+        # whole hook, one bucket
+        if want("hook"):
+            state.iter = 2
+            t = _time(lambda: cb.powerSGD_hook(state, bucket).wait(), args.iters)
+            record("powerSGD_hook (whole bucket, ws=1)", t, 6 * mat_bytes,
+                   "ideal: P pass r+w, Q pass r, decompress r+w (+sketch)")
+
+    # ---------------- random block pipeline ----------------
+    for kind, kw in (("ef", dict()), ("sketch", dict(use_error_compression=True, sketch_size=args.sketch_size)),
+                     ("quant8", dict(use_error_compression=True, error_compressor="quant8", beta=0.0))):
+        if not want(f"randblock_{kind}"):
+            continue
+        state = cb.RandomBlockState(None, start_compression_iter=2, compression_ratio=0.1, **kw)
+        state.iter = 2
+        nbytes = 4 * sum(int(np.prod(s)) for s in shapes if len(s) > 1)
+        t = _time(lambda: cb.RandomBlock_hook(state, bucket).wait(), args.iters)
+        per = {"ef": 4.0, "sketch": 2.2, "quant8": 2.5}[kind]      # passes over the tensors (r/w gradient + error store)
+        record(f"RandomBlock_hook {kind} (whole bucket, ws=1)", t, per * nbytes, "gather+error update, scatter")
+
+    # ---------------- LAMB ----------------
+    if want("lamb"):
+        from conef_b200.optim import FusedLAMB
+        ps = [torch.nn.Parameter(torch.randn(s, device=dev)) for s in shapes]
+        for p in ps:
+            p.grad = torch.randn_like(p)
+        opt = FusedLAMB(ps, lr=1e-3)
+        n = sum(p.numel() for p in ps)
+        t = _time(opt.step, args.iters)
+        record("FusedLAMB.step", t, 4 * n * (1 + 7 + 3), "gnorm r, stage1 r4 w3, stage2 r2 w1")
+
+    print(f"case={args.case} bucket={buf.numel() * 4 / 1e6:.1f} MB rank={rank} peak={peak:.0f} GB/s ({peak_kind})")
+    print(f"{'kernel':44s} {'us':>9s} {'MB':>9s} {'GB/s':>8s} {'of ' + peak_kind:>12s}  note")
+    for name, us, mb, gbs, frac, note in rows:
+        print(f"{name:44s} {us:9.1f} {mb:9.1f} {gbs:8.0f} {frac:12.2f}  {note}")
+
+
+if __name__ == "__main__":
+    main()
