@@ -27,7 +27,9 @@ typedef struct ConefMat {
   int tab_off;        // offset into the hash-table arena (-1: none)
   int cnt_off;        // offset into the counts arena (-1: none)
   int q_rows;         // rows per CTA row-block in the Q = M^T P kernel
-  int q_atomic;       // 1 if several row-blocks accumulate into Q
+  int q_atomic;       // 1 if several CTAs (or several records) accumulate into the same Q block
+  int src;            // 0: the matrix lives in the gradient bucket, 1: in the auxiliary buffer
+  int pad;
 } ConefMat;
 
 // A contiguous run of elements of the bucket (one uncompressed tensor, or the
@@ -72,11 +74,11 @@ int conef_sketch3_update(const float* vec, float* cs0, float* cs1, float* cs2,
                          int N, int D, int W, float beta, cudaStream_t stream);
 
 // ---- grouped PowerSGD pipeline, SIMT (powersgd.cu) --------------------------
-// P_i = (G_i + error_i) Q_i for every matrix of a bucket; the corrected
-// matrix is written back into the bucket when ef_mode != NONE.
-int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
-                 const float* sketch, const int32_t* tables, const float* dense_err,
-                 const float* Q, float* P, float alpha, int ef_mode, int max_rank,
+// P_i (+)= A_i Q_i for every record: A_i is a matrix of the bucket (src 0) or of the
+// auxiliary buffer (src 1: a sketch (n x W) or a dense error matrix).  With atomic_out
+// the results are added to P (several records feed the same block), which the caller zeroed.
+int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket,
+                 const float* aux, const float* Q, float* P, int atomic_out, int max_rank,
                  cudaStream_t stream);
 // Batched Gram-Schmidt over the (rows x r) blocks of a flat buffer.  which=0
 // orthogonalises the P blocks (n x r), which=1 the Q blocks (m x r).  With
@@ -87,23 +89,24 @@ int conef_orthogonalize(const ConefMat* mats, int nmats, int which, float* buf, 
                         const float* const* peer_bufs, const uint32_t* flags, int world,
                         uint32_t epoch, int* status, long long spin_limit, cudaStream_t stream);
 int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket,
-                 const float* P, float* Q, int max_rank, cudaStream_t stream);
-// M_hat = P Q^T written into the bucket; residual (M - M_hat) goes to the
-// error store selected by ef_mode (dense buffer or count sketch with decay).
+                 const float* aux, const float* P, float* Q, int max_rank, cudaStream_t stream);
+// M_hat = P Q^T written into the bucket.  M = G + remembered error is formed on the fly
+// (alpha * unsketch(S) or the dense buffer); the residual M - M_hat goes to the error
+// store selected by ef_mode (dense buffer, or count sketch with decay beta).
+// smem_bytes = 2 * rows_per_cta * max W * 4 in sketch mode, else 0.
 int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta,
                           float* bucket, const float* P, const float* Q, float q_scale,
                           float* sketch, const int32_t* tables, const int32_t* counts,
-                          float* dense_err, float beta, int ef_mode, int max_rank,
+                          float* dense_err, float alpha, float beta, int ef_mode, int max_rank,
                           size_t smem_bytes, cudaStream_t stream);
+// Sparse sign matrix H of the sketch applied to the small factors (see csrc/sketch.cu):
+// unproject = 0: Z_i += scale * H_i^T Q_i ; unproject = 1: Q_i += scale * H_i Y_i.
+// Record nmats + i describes the sketch of matrix i; its q_off is where Z_i / Y_i live.
+int conef_sketch_project(const ConefMat* mats, int nmats, int max_cols, const int32_t* tables,
+                         float* qz, float scale, int unproject, cudaStream_t stream);
 // Philox-keyed standard normal fill: element e of the buffer depends only on
 // (seed, e), so every rank generates the same Q without communication.
 int conef_fill_normal(float* buf, long long numel, uint64_t seed, cudaStream_t stream);
-
-// In-place error add for the matrices whose P product runs on the tensor-core path:
-// G <- G + alpha * unsketch(S)  (sketch mode)  or  G <- G + dense_err  (dense mode).
-int conef_ef_apply(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
-                   const float* sketch, const int32_t* tables, const float* dense_err, float alpha,
-                   int ef_mode, cudaStream_t stream);
 
 // ---- tcgen05 / TMEM / TMA tiles (powersgd_tc.cu) ----------------------------
 int conef_tc_supported(void);
@@ -111,7 +114,7 @@ int conef_tc_supported(void);
 // ok[i] = 0 when matrix i cannot be addressed by TMA (base not 16-byte aligned or row
 // pitch not a multiple of 16 bytes).
 int conef_tc_encode_maps(const ConefMat* host_mats, int nmats, const float* bucket_dev,
-                         void* maps_out_256B_each, unsigned char* ok);
+                         const float* aux_dev, void* maps_out_256B_each, unsigned char* ok);
 // mode 0: P = M Q (small operand Q, output P).  mode 1: Q = M^T P (small operand P, output Q).
 // tiles: int4 records {matrix | atomic << 30, first output row, first K index, K extent}.
 int conef_psgd_tc(int mode, const ConefMat* mats, const void* maps, const void* tiles, int ntiles,

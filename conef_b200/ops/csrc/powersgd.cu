@@ -2,8 +2,16 @@
 // compressed matrices of one DDP bucket in a single launch, driven by a
 // device-resident table of ConefMat descriptors and a tile table.
 //
+// The error-corrected matrix M = G + e is never written: the products are linear, so
+//   P = M Q   = G Q   + e Q        and      Q' = M^T P = G^T P + e^T P
+// and the error term is one more "matrix" of the same launch.  For the count sketch,
+// e = alpha * S H^T with the (n x W) sketch S and the sparse sign matrix H, hence
+// e Q = S (alpha H^T Q) and e^T P = alpha H (S^T P): tall-skinny products over S, which is
+// sketch_size times the size of G (csrc/sketch.cu has the two small H kernels).  For dense
+// error feedback e is the error buffer itself.  The decompress kernel adds e on the fly.
+//
 // Replaces, per matrix and per step, of the reference (communication/powerSGD_hook.py):
-//   :409  DenseCS.query        -> folded into k_psgd_p (error add before P = M Q)
+//   :409  DenseCS.query        -> never materialised (see above)
 //   :497  torch.matmul(M, Q)   -> k_psgd_p
 //   :12-43 _orthogonalize      -> k_orthogonalize (all matrices of the bucket, one launch)
 //   :531  torch.matmul(M^T, P) -> k_psgd_q
@@ -16,31 +24,25 @@ constexpr int Q_THREADS = 256;   // columns per CTA in k_psgd_q
 constexpr int D_THREADS = 256;
 
 // ---------------------------------------------------------------------------
-// P = (G + err) Q, one warp per matrix row.
+// P (+)= A Q for every record of the table, one warp per matrix row.  A record reads its
+// matrix from the gradient bucket (src = 0) or from the auxiliary buffer (src = 1: sketch
+// arena or dense error buffer).
 template <int RP>
 __global__ void __launch_bounds__(P_WARPS * 32)
-k_psgd_p(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, float* __restrict__ bucket,
-         const float* __restrict__ sketch, const int32_t* __restrict__ tables,
-         const float* __restrict__ dense_err, const float* __restrict__ Q, float* __restrict__ P,
-         float alpha, int ef_mode) {
+k_psgd_p(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, const float* __restrict__ bucket,
+         const float* __restrict__ aux, const float* __restrict__ Q, float* __restrict__ P, int atomic_out) {
   const int2 t = tiles[blockIdx.x];
   const ConefMat M = mats[t.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = t.y * P_WARPS + warp;
   if (row >= M.n) return;
   const int m = M.m, r = M.r;
-  float* g = bucket + M.g_off + (size_t)row * m;
+  const float* g = (M.src ? aux : bucket) + M.g_off + (size_t)row * m;
   const float* q = Q + M.q_off;
   float acc[RP];
 #pragma unroll
   for (int c = 0; c < RP; ++c) acc[c] = 0.f;
-
-  // Loads are issued PB at a time before any store: the corrected matrix is written
-  // back into the same buffer, and a store between two loads would serialise them.
-  constexpr int PB = 8;
-  const float* srow = ef_mode == CONEF_EF_SKETCH ? sketch + M.sk_off + (size_t)row * M.W : nullptr;
-  const int32_t* tab = ef_mode == CONEF_EF_SKETCH ? tables + M.tab_off : nullptr;
-  const float* erow = ef_mode == CONEF_EF_DENSE ? dense_err + M.g_off + (size_t)row * m : nullptr;
+  constexpr int PB = 8;      // independent loads in flight per lane
   for (int j0 = lane; j0 < m; j0 += 32 * PB) {
     float v[PB];
 #pragma unroll
@@ -48,24 +50,10 @@ k_psgd_p(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, floa
       const int j = j0 + 32 * u;
       v[u] = j < m ? g[j] : 0.f;
     }
-    if (ef_mode == CONEF_EF_SKETCH) {
-      int e[PB];
-#pragma unroll
-      for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; e[u] = j < m ? __ldg(tab + j) : 0; }
-#pragma unroll
-      for (int u = 0; u < PB; ++u) {
-        const int j = j0 + 32 * u;
-        if (j < m) v[u] += alpha * unpack_sign(e[u]) * srow[unpack_bucket(e[u])];
-      }
-    } else if (ef_mode == CONEF_EF_DENSE) {
-#pragma unroll
-      for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; if (j < m) v[u] += __ldcs(erow + j); }
-    }
 #pragma unroll
     for (int u = 0; u < PB; ++u) {
       const int j = j0 + 32 * u;
       if (j < m) {
-        if (ef_mode != CONEF_EF_NONE) g[j] = v[u];
 #pragma unroll
         for (int c = 0; c < RP; ++c)
           if (c < r) acc[c] = fmaf(v[u], __ldg(q + (size_t)j * r + c), acc[c]);
@@ -77,16 +65,19 @@ k_psgd_p(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, floa
   if (lane == 0) {
     float* p = P + M.p_off + (size_t)row * r;
 #pragma unroll
-    for (int c = 0; c < RP; ++c)
-      if (c < r) p[c] = acc[c];
+    for (int c = 0; c < RP; ++c) {
+      if (c < r) {
+        if (atomic_out) atomicAdd(p + c, acc[c]);
+        else p[c] = acc[c];
+      }
+    }
   }
 }
 
 template <int RP>
-static int launch_p(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket, const float* sketch,
-                    const int32_t* tables, const float* dense_err, const float* Q, float* P, float alpha,
-                    int ef_mode, cudaStream_t stream) {
-  k_psgd_p<RP><<<ntiles, P_WARPS * 32, 0, stream>>>(mats, tiles, bucket, sketch, tables, dense_err, Q, P, alpha, ef_mode);
+static int launch_p(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket, const float* aux,
+                    const float* Q, float* P, int atomic_out, cudaStream_t stream) {
+  k_psgd_p<RP><<<ntiles, P_WARPS * 32, 0, stream>>>(mats, tiles, bucket, aux, Q, P, atomic_out);
   CONEF_CHECK_LAUNCH("k_psgd_p");
   return 0;
 }
@@ -103,61 +94,11 @@ static int launch_p(const ConefMat* mats, const int2* tiles, int ntiles, float* 
     return 2;                                                              \
   } while (0)
 
-extern "C" int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
-                            const float* sketch, const int32_t* tables, const float* dense_err,
-                            const float* Q, float* P, float alpha, int ef_mode, int max_rank,
+extern "C" int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket,
+                            const float* aux, const float* Q, float* P, int atomic_out, int max_rank,
                             cudaStream_t stream) {
   if (ntiles <= 0) return 0;
-  DISPATCH_RANK(max_rank, launch_p, mats, tiles, ntiles, bucket, sketch, tables, dense_err, Q, P, alpha, ef_mode, stream);
-}
-
-// ---------------------------------------------------------------------------
-// Error add alone (one warp per row), for matrices whose P product is done by the
-// tensor-core kernel: that kernel reads M through TMA and cannot patch it on the fly.
-__global__ void __launch_bounds__(P_WARPS * 32)
-k_ef_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, float* __restrict__ bucket,
-           const float* __restrict__ sketch, const int32_t* __restrict__ tables,
-           const float* __restrict__ dense_err, float alpha, int ef_mode) {
-  const int2 t = tiles[blockIdx.x];
-  const ConefMat M = mats[t.x];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = t.y * P_WARPS + warp;
-  if (row >= M.n) return;
-  const int m = M.m;
-  float* g = bucket + M.g_off + (size_t)row * m;
-  constexpr int PB = 8;
-  const float* srow = ef_mode == CONEF_EF_SKETCH ? sketch + M.sk_off + (size_t)row * M.W : nullptr;
-  const int32_t* tab = ef_mode == CONEF_EF_SKETCH ? tables + M.tab_off : nullptr;
-  const float* erow = ef_mode == CONEF_EF_DENSE ? dense_err + M.g_off + (size_t)row * m : nullptr;
-  for (int j0 = lane; j0 < m; j0 += 32 * PB) {
-    float v[PB];
-#pragma unroll
-    for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; v[u] = j < m ? g[j] : 0.f; }
-    if (ef_mode == CONEF_EF_SKETCH) {
-      int e[PB];
-#pragma unroll
-      for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; e[u] = j < m ? __ldg(tab + j) : 0; }
-#pragma unroll
-      for (int u = 0; u < PB; ++u) {
-        const int j = j0 + 32 * u;
-        if (j < m) v[u] += alpha * unpack_sign(e[u]) * srow[unpack_bucket(e[u])];
-      }
-    } else {
-#pragma unroll
-      for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; if (j < m) v[u] += __ldcs(erow + j); }
-    }
-#pragma unroll
-    for (int u = 0; u < PB; ++u) { const int j = j0 + 32 * u; if (j < m) g[j] = v[u]; }
-  }
-}
-
-extern "C" int conef_ef_apply(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket,
-                              const float* sketch, const int32_t* tables, const float* dense_err, float alpha,
-                              int ef_mode, cudaStream_t stream) {
-  if (ntiles <= 0 || ef_mode == CONEF_EF_NONE) return 0;
-  k_ef_apply<<<ntiles, P_WARPS * 32, 0, stream>>>(mats, tiles, bucket, sketch, tables, dense_err, alpha, ef_mode);
-  CONEF_CHECK_LAUNCH("k_ef_apply");
-  return 0;
+  DISPATCH_RANK(max_rank, launch_p, mats, tiles, ntiles, bucket, aux, Q, P, atomic_out, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -255,7 +196,7 @@ extern "C" int conef_orthogonalize(const ConefMat* mats, int nmats, int which, f
 template <int RP>
 __global__ void __launch_bounds__(Q_THREADS)
 k_psgd_q(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, const float* __restrict__ bucket,
-         const float* __restrict__ P, float* __restrict__ Q) {
+         const float* __restrict__ aux, const float* __restrict__ P, float* __restrict__ Q) {
   extern __shared__ float ps[];  // q_rows * RP
   const int2 t = tiles[blockIdx.x];
   const ConefMat M = mats[t.x];
@@ -272,7 +213,7 @@ k_psgd_q(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, cons
   __syncthreads();
   const int j = cb * Q_THREADS + threadIdx.x;
   if (j >= m) return;
-  const float* g = bucket + M.g_off + (size_t)row0 * m + j;
+  const float* g = (M.src ? aux : bucket) + M.g_off + (size_t)row0 * m + j;
   float acc[RP];
 #pragma unroll
   for (int c = 0; c < RP; ++c) acc[c] = 0.f;
@@ -295,10 +236,14 @@ k_psgd_q(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, cons
 }
 
 template <int RP>
-static int launch_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket, const float* P,
-                    float* Q, size_t smem, cudaStream_t stream) {
-  CONEF_CUDA(cudaFuncSetAttribute(k_psgd_q<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-  k_psgd_q<RP><<<ntiles, Q_THREADS, smem, stream>>>(mats, tiles, bucket, P, Q);
+static int launch_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket, const float* aux,
+                    const float* P, float* Q, size_t smem, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    CONEF_CUDA(cudaFuncSetAttribute(k_psgd_q<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    configured = true;
+  }
+  k_psgd_q<RP><<<ntiles, Q_THREADS, smem, stream>>>(mats, tiles, bucket, aux, P, Q);
   CONEF_CHECK_LAUNCH("k_psgd_q");
   return 0;
 }
@@ -307,28 +252,29 @@ static int launch_q(const ConefMat* mats, const int2* tiles, int ntiles, const f
 #define CONEF_Q_MAX_ROWS 1024
 
 extern "C" int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket,
-                            const float* P, float* Q, int max_rank, cudaStream_t stream) {
+                            const float* aux, const float* P, float* Q, int max_rank, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
   int rp = max_rank <= 1 ? 1 : max_rank <= 2 ? 2 : max_rank <= 4 ? 4 : max_rank <= 8 ? 8 : max_rank <= 16 ? 16 : 32;
   size_t smem = (size_t)CONEF_Q_MAX_ROWS * rp * sizeof(float);
-  DISPATCH_RANK(max_rank, launch_q, mats, tiles, ntiles, bucket, P, Q, smem, stream);
+  DISPATCH_RANK(max_rank, launch_q, mats, tiles, ntiles, bucket, aux, P, Q, smem, stream);
 }
 
 // ---------------------------------------------------------------------------
 // Decompress + error feedback.  Tile = (matrix, block of RB rows).
-// A thread owns a column: it loads Q[j, :] (scaled by q_scale) and the column's
-// hash entry once, then for the RB rows of the block loads M (all RB loads in
-// flight before the first store: M_hat overwrites M in the same buffer),
-// computes M_hat = <P[row, :], Q[j, :]>, writes it to the bucket and routes the
-// residual to the error store: a dense buffer, or the row's count sketch
-// accumulated with shared-memory atomics and flushed by one plain global store
-// per sketch cell (a sketch row belongs to exactly one CTA).
+// A thread owns a column: it loads Q[j, :] (scaled by q_scale) and the column's hash
+// entry once, then for the RB rows of the block loads G (all RB loads in flight before
+// the first store: M_hat overwrites G in the same buffer), adds the remembered error on
+// the fly (M = G + alpha * s_j * S_old[row, h_j] from the sketch rows held in shared
+// memory, or G + E for the dense store), computes M_hat = <P[row, :], Q[j, :]>, writes it
+// to the bucket and routes the residual M - M_hat to the error store: the dense buffer, or
+// the row's count sketch accumulated with shared-memory atomics and flushed by one plain
+// global store per sketch cell (a sketch row belongs to exactly one CTA).
 template <int RP, int RB>
 __global__ void __launch_bounds__(D_THREADS)
 k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles,
                   float* __restrict__ bucket, const float* __restrict__ P, const float* __restrict__ Q,
                   float q_scale, float* __restrict__ sketch, const int32_t* __restrict__ tables,
-                  const int32_t* __restrict__ counts, float* __restrict__ dense_err, float beta,
+                  const int32_t* __restrict__ counts, float* __restrict__ dense_err, float alpha, float beta,
                   int ef_mode) {
   extern __shared__ float sm[];
   const int2 t = tiles[blockIdx.x];
@@ -336,15 +282,17 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
   const int m = M.m, r = M.r, W = M.W;
   const int row0 = t.y * RB;
   const int rows = min(RB, M.n - row0);
-  float* ps = sm;                    // RB * RP
-  float* acc = sm + RB * RP;         // RB * W (sketch mode)
+  float* ps = sm;                          // RB * RP
+  float* acc = sm + RB * RP;               // RB * W   new contributions   (sketch mode)
+  float* old = acc + (size_t)RB * W;       // RB * W   sketch rows as they were (sketch mode)
   const float* p = P + M.p_off + (size_t)row0 * r;
   for (int i = threadIdx.x; i < RB * RP; i += D_THREADS) {
     const int ii = i / RP, c = i - ii * RP;
     ps[i] = (c < r && ii < rows) ? p[(size_t)ii * r + c] : 0.f;
   }
+  float* srow = ef_mode == CONEF_EF_SKETCH ? sketch + M.sk_off + (size_t)row0 * W : nullptr;
   if (ef_mode == CONEF_EF_SKETCH)
-    for (int i = threadIdx.x; i < rows * W; i += D_THREADS) acc[i] = 0.f;
+    for (int i = threadIdx.x; i < rows * W; i += D_THREADS) { acc[i] = 0.f; old[i] = srow[i]; }
   __syncthreads();
 
   const int32_t* tab = ef_mode == CONEF_EF_SKETCH ? tables + M.tab_off : nullptr;
@@ -365,6 +313,10 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
     float v[RB];
 #pragma unroll
     for (int ii = 0; ii < RB; ++ii) v[ii] = ii < rows ? __ldcs(g0 + (size_t)ii * m + j) : 0.f;
+    if (ef_mode == CONEF_EF_DENSE) {
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii) if (ii < rows) v[ii] += __ldcs(e0 + (size_t)ii * m + j);
+    }
 #pragma unroll
     for (int ii = 0; ii < RB; ++ii) {
       if (ii < rows) {
@@ -372,9 +324,12 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
 #pragma unroll
         for (int c = 0; c < RP; ++c) mh = fmaf(ps[ii * RP + c], qv[c], mh);
         g0[(size_t)ii * m + j] = mh;
-        const float resid = v[ii] - mh;
-        if (ef_mode == CONEF_EF_SKETCH) atomicAdd(&acc[ii * W + h], s * resid);
-        else if (ef_mode == CONEF_EF_DENSE) __stcs(e0 + (size_t)ii * m + j, resid);
+        if (ef_mode == CONEF_EF_SKETCH) {
+          const float resid = v[ii] + alpha * s * old[ii * W + h] - mh;
+          atomicAdd(&acc[ii * W + h], s * resid);
+        } else if (ef_mode == CONEF_EF_DENSE) {
+          __stcs(e0 + (size_t)ii * m + j, v[ii] - mh);
+        }
       }
     }
   }
@@ -382,10 +337,9 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
     __syncthreads();
     const float omb = 1.f - beta;
     const int32_t* cnt = counts + M.cnt_off;
-    float* srow = sketch + M.sk_off + (size_t)row0 * W;
     for (int i = threadIdx.x; i < rows * W; i += D_THREADS) {
       const int h2 = i % W;
-      srow[i] = srow[i] * (1.f - omb * (float)__ldg(cnt + h2)) + acc[i];
+      srow[i] = old[i] * (1.f - omb * (float)__ldg(cnt + h2)) + acc[i];
     }
   }
 }
@@ -393,8 +347,8 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
 template <int RP, int RB>
 static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket, const float* P,
                        const float* Q, float q_scale, float* sketch, const int32_t* tables,
-                       const int32_t* counts, float* dense_err, float beta, int ef_mode, size_t smem,
-                       cudaStream_t stream) {
+                       const int32_t* counts, float* dense_err, float alpha, float beta, int ef_mode,
+                       size_t smem, cudaStream_t stream) {
   smem += (size_t)RB * RP * sizeof(float);
   if (smem > 220 * 1024) { conef_set_error("decompress: %zu bytes of shared memory needed", smem); return 2; }
   static size_t configured = 0;
@@ -403,7 +357,7 @@ static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, floa
     configured = smem;
   }
   k_psgd_decompress<RP, RB><<<ntiles, D_THREADS, smem, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables,
-                                                                counts, dense_err, beta, ef_mode);
+                                                                counts, dense_err, alpha, beta, ef_mode);
   CONEF_CHECK_LAUNCH("k_psgd_decompress");
   return 0;
 }
@@ -411,11 +365,11 @@ static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, floa
 template <int RP>
 static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta, float* bucket,
                     const float* P, const float* Q, float q_scale, float* sketch, const int32_t* tables,
-                    const int32_t* counts, float* dense_err, float beta, int ef_mode, size_t smem,
+                    const int32_t* counts, float* dense_err, float alpha, float beta, int ef_mode, size_t smem,
                     cudaStream_t stream) {
 #define CONEF_D_CASE(RB)                                                                              \
   case RB: return launch_d_rb<RP, RB>(mats, tiles, ntiles, bucket, P, Q, q_scale, sketch, tables, counts, \
-                                      dense_err, beta, ef_mode, smem, stream)
+                                      dense_err, alpha, beta, ef_mode, smem, stream)
   switch (rows_per_cta) {
     CONEF_D_CASE(8);
     CONEF_D_CASE(4);
@@ -430,11 +384,11 @@ static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int row
 extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta,
                                      float* bucket, const float* P, const float* Q, float q_scale,
                                      float* sketch, const int32_t* tables, const int32_t* counts,
-                                     float* dense_err, float beta, int ef_mode, int max_rank,
+                                     float* dense_err, float alpha, float beta, int ef_mode, int max_rank,
                                      size_t smem_bytes, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
   DISPATCH_RANK(max_rank, launch_d, mats, tiles, ntiles, rows_per_cta, bucket, P, Q, q_scale, sketch, tables,
-                counts, dense_err, beta, ef_mode, smem_bytes, stream);
+                counts, dense_err, alpha, beta, ef_mode, smem_bytes, stream);
 }
 
 // ---------------------------------------------------------------------------

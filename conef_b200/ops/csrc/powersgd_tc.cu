@@ -347,16 +347,16 @@ extern "C" int conef_tc_supported(void) { return get_encode_fn() != nullptr ? 1 
 // and its row pitch is a multiple of 16 bytes; ok[i] = 0 marks the others, which the
 // caller routes to the SIMT kernels.
 extern "C" int conef_tc_encode_maps(const ConefMat* host_mats, int nmats, const float* bucket_dev,
-                                    void* maps_out_256B_each, unsigned char* ok) {
+                                    const float* aux_dev, void* maps_out_256B_each, unsigned char* ok) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) { conef_set_error("cuTensorMapEncodeTiled is not available"); return 1; }
   CUtensorMap* out = (CUtensorMap*)maps_out_256B_each;
   for (int i = 0; i < nmats; ++i) {
     const ConefMat& M = host_mats[i];
-    const uintptr_t base = (uintptr_t)(bucket_dev + M.g_off);
+    const uintptr_t base = (uintptr_t)((M.src ? aux_dev : bucket_dev) + M.g_off);
     ok[i] = 0;
     memset(&out[2 * i], 0, 2 * sizeof(CUtensorMap));
-    if ((base & 15) != 0 || (M.m % 4) != 0 || M.m < 4) continue;
+    if ((base & 15) != 0 || (M.m % 4) != 0 || M.m < 4 || (M.src && aux_dev == nullptr)) continue;
     cuuint64_t dims[2] = {(cuuint64_t)M.m, (cuuint64_t)M.n};
     cuuint64_t strides[1] = {(cuuint64_t)M.m * sizeof(float)};
     cuuint32_t box[2] = {32, 32};

@@ -218,3 +218,55 @@ extern "C" int conef_sketch3_update(const float* vec, float* cs0, float* cs1, fl
   CONEF_CHECK_LAUNCH("k_sketch3_update");
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// The sparse sign matrix H (m x W, one entry per row: H[j, h_j] = s_j) applied to the
+// small PowerSGD factors, grouped over the matrices of a bucket.  With the sketch S,
+//   unsketch(S) Q   = S (H^T Q)      -> k_sketch_project   : Z[h, :] += scale * s_j * Q[j, :]
+//   unsketch(S)^T P = H (S^T P)      -> k_sketch_unproject : Q[j, :] += scale * s_j * Y[h_j, :]
+// Z and Y are (W x r) blocks stored behind the Q blocks of the same flat buffer: record
+// nmats + i of the table describes the sketch of matrix i and its q_off points there.
+__global__ void k_sketch_project(const ConefMat* __restrict__ mats, int nmats, const int32_t* __restrict__ tables,
+                                 float* __restrict__ qz, float scale) {
+  const ConefMat M = mats[blockIdx.y];
+  const ConefMat E = mats[nmats + blockIdx.y];
+  const int r = M.r;
+  const int32_t* tab = tables + M.tab_off;
+  const float* q = qz + M.q_off;
+  float* z = qz + E.q_off;
+  for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < M.m; j += gridDim.x * blockDim.x) {
+    const int e = tab[j];
+    const float s = unpack_sign(e) * scale;
+    float* zr = z + (size_t)unpack_bucket(e) * r;
+    for (int c = 0; c < r; ++c) atomicAdd(zr + c, s * q[(size_t)j * r + c]);
+  }
+}
+
+__global__ void k_sketch_unproject(const ConefMat* __restrict__ mats, int nmats, const int32_t* __restrict__ tables,
+                                   float* __restrict__ qy, float scale) {
+  const ConefMat M = mats[blockIdx.y];
+  const ConefMat E = mats[nmats + blockIdx.y];
+  const int r = M.r;
+  const int32_t* tab = tables + M.tab_off;
+  float* q = qy + M.q_off;
+  const float* y = qy + E.q_off;
+  for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < M.m; j += gridDim.x * blockDim.x) {
+    const int e = tab[j];
+    const float s = unpack_sign(e) * scale;
+    const float* yr = y + (size_t)unpack_bucket(e) * r;
+    for (int c = 0; c < r; ++c) q[(size_t)j * r + c] += s * yr[c];
+  }
+}
+
+extern "C" int conef_sketch_project(const ConefMat* mats, int nmats, int max_cols, const int32_t* tables,
+                                    float* qz, float scale, int unproject, cudaStream_t stream) {
+  if (nmats <= 0) return 0;
+  int bx = (max_cols + 255) / 256;
+  if (bx < 1) bx = 1;
+  if (bx > 32) bx = 32;
+  dim3 grid(bx, nmats);
+  if (unproject) k_sketch_unproject<<<grid, 256, 0, stream>>>(mats, nmats, tables, qz, scale);
+  else k_sketch_project<<<grid, 256, 0, stream>>>(mats, nmats, tables, qz, scale);
+  CONEF_CHECK_LAUNCH("k_sketch_project");
+  return 0;
+}

@@ -119,7 +119,9 @@ class _EngineBase:
 # PowerSGD family
 # ==========================================================================
 class PowerSGDEngine(_EngineBase):
-    def __init__(self, state, buf: torch.Tensor, grads, group, variant: str):
+    """One bucket of the PowerSGD family (layer-wise, batched, transposed-sketch, unbiased)."""
+
+    def __init__(self, state, buf: torch.Tensor, grads, group, variant: str, bidx: int = 0):
         super().__init__(buf.device)
         self.variant = variant
         self.group = group
@@ -154,32 +156,29 @@ class PowerSGDEngine(_EngineBase):
             self.ef_mode, self.external = native.EF_SKETCH, False
         else:
             self.ef_mode, self.external = native.EF_NONE, True
+        # The remembered error enters the two products as extra records of the same launches
+        # (P = G Q + e Q, Q' = G^T P + e^T P); the corrected matrix is never written.
+        self.fused_err = self.ef_mode in (native.EF_SKETCH, native.EF_DENSE)
 
-        # ---- descriptor tables ----------------------------------------------
-        mats = np.zeros(len(plan.mats), dtype=native.MAT_DTYPE)
-        total_cb = sum((e.m + Q_COLS - 1) // Q_COLS for e in plan.mats) or 1
-        want_rb = max(1, math.ceil(TARGET_CTAS / total_cb))
-        q_tiles, p_tiles = [], []
-        sk_off = tab_off = cnt_off = 0
+        # ---- descriptor records -----------------------------------------------
+        nm = len(plan.mats)
+        self.nm = nm
+        nrec = nm * (2 if self.fused_err else 1)
+        mats = np.zeros(nrec, dtype=native.MAT_DTYPE)
+        sk_off = tab_off = cnt_off = z_off = 0
         table_chunks, count_chunks = [], []
         table_index: Dict[tuple, tuple] = {}
         self.widths = []
         seeds = ref.derive_hash_seeds(getattr(state, "hash_seed", 0), 1)[0]
         for k, e in enumerate(plan.mats):
-            nrb = max(1, min(want_rb, math.ceil(e.n / 64)))
-            q_rows = min(Q_MAX_ROWS, ((math.ceil(e.n / nrb) + 7) // 8) * 8)
-            nrb = math.ceil(e.n / q_rows)
-            ncb = (e.m + Q_COLS - 1) // Q_COLS
             W = ref.sketch_width(e.m, state.sketch_size) if self.ef_mode == native.EF_SKETCH else 0
             self.widths.append(W)
             rec = mats[k]
             rec["g_off"], rec["p_off"], rec["q_off"] = e.g_off, e.p_off, e.q_off
             rec["n"], rec["m"], rec["r"], rec["W"] = e.n, e.m, e.r, W
-            rec["q_rows"], rec["q_atomic"] = q_rows, int(nrb > 1)
             rec["sk_off"], rec["tab_off"], rec["cnt_off"] = -1, -1, -1
             if self.ef_mode == native.EF_SKETCH:
                 rec["sk_off"] = sk_off
-                sk_off += e.n * W
                 key = (e.m, W)
                 if key not in table_index:
                     _, _, packed, counts = tables_for(dev, e.m, W, seeds[0], seeds[1])
@@ -189,106 +188,132 @@ class PowerSGDEngine(_EngineBase):
                     tab_off += e.m
                     cnt_off += W
                 rec["tab_off"], rec["cnt_off"] = table_index[key]
-            p_tiles += [(k, rb) for rb in range(math.ceil(e.n / P_ROWS))]
-            q_tiles += [(k, t) for t in range(nrb * ncb)]
-        self.q_atomic = bool(mats["q_atomic"].any()) if len(mats) else False
+                # record nm + k: the (n x W) sketch as a matrix; Z / Y (W x r) live behind the Q blocks
+                err = mats[nm + k]
+                err["src"], err["g_off"], err["n"], err["m"], err["r"] = 1, sk_off, e.n, W, e.r
+                err["p_off"], err["q_off"] = e.p_off, plan.total_q + z_off
+                err["sk_off"], err["tab_off"], err["cnt_off"] = -1, -1, -1
+                sk_off += e.n * W
+                z_off += W * e.r
+            elif self.ef_mode == native.EF_DENSE:
+                err = mats[nm + k]
+                err["src"], err["g_off"], err["n"], err["m"], err["r"] = 1, e.g_off, e.n, e.m, e.r
+                err["p_off"], err["q_off"] = e.p_off, e.q_off
+                err["sk_off"], err["tab_off"], err["cnt_off"] = -1, -1, -1
+        self.total_z = z_off
+        self.max_cols = max((e.m for e in plan.mats), default=0)
+        # row blocks of the SIMT Q kernel
+        total_cb = sum((int(r["m"]) + Q_COLS - 1) // Q_COLS for r in mats) or 1
+        want_rb = max(1, math.ceil(TARGET_CTAS / total_cb))
+        for rec in mats:
+            n = int(rec["n"])
+            nrb = max(1, min(want_rb, math.ceil(n / 64)))
+            q_rows = min(Q_MAX_ROWS, ((math.ceil(n / nrb) + 7) // 8) * 8)
+            rec["q_rows"] = q_rows
+            shared_out = self.ef_mode == native.EF_DENSE      # gradient and error record feed one Q block
+            rec["q_atomic"] = int(math.ceil(n / q_rows) > 1 or shared_out)
         self.mats_host = mats
-        self.mats_dev = native.upload_struct_array(mats, dev) if len(mats) else None
-        self.p_tiles = self._tiles(p_tiles)
-        self.q_tiles = self._tiles(q_tiles)
-        self.n_p_tiles, self.n_q_tiles = len(p_tiles), len(q_tiles)
-        # decompress: rows per CTA in {8, 4, 2, 1}: the most that fit in shared memory while
-        # still giving every SM a few CTAs
+        self.mats_dev = native.upload_struct_array(mats, dev) if nrec else None
+        self.tables = torch.cat(table_chunks) if table_chunks else None
+        self.counts = torch.cat(count_chunks) if count_chunks else None
+
+        # decompress: rows per CTA in {8, 4, 2, 1}: the most that fit in shared memory (two
+        # copies of the sketch rows) while still giving every SM a few CTAs
         maxW = max(self.widths, default=0)
-        if maxW * 4 > SMEM_BUDGET:
+        if maxW * 8 > SMEM_BUDGET:
             raise native.NativeError(f"sketch width {maxW} does not fit in shared memory")
         total_rows = sum(e.n for e in plan.mats)
         self.d_rows = 1
         for cand in (8, 4, 2):
-            if cand * maxW * 4 <= SMEM_BUDGET // 2 and total_rows // cand >= 3 * 148:
+            if cand * maxW * 8 <= SMEM_BUDGET // 2 and total_rows // cand >= 3 * 148:
                 self.d_rows = cand
                 break
-        self.d_smem = self.d_rows * maxW * 4
+        self.d_smem = 2 * self.d_rows * maxW * 4
         d_tiles = [(k, rb) for k, e in enumerate(plan.mats) for rb in range(math.ceil(e.n / self.d_rows))]
         self.d_tiles = self._tiles(d_tiles)
         self.n_d_tiles = len(d_tiles)
-        self.tables = torch.cat(table_chunks) if table_chunks else None
-        self.counts = torch.cat(count_chunks) if count_chunks else None
 
         segs = np.zeros(len(plan.segs), dtype=native.SEG_DTYPE)
         for k, s in enumerate(plan.segs):
             segs[k] = (s.g_off, s.dst_off, s.numel)
         self.segs_dev = native.upload_struct_array(segs, dev) if len(segs) else None
 
-        # ---- persistent state tensors ----------------------------------------
+        # ---- buffers ---------------------------------------------------------------
         self.sketch_arena = None
         if self.ef_mode == native.EF_SKETCH:
             self.sketch_arena = torch.zeros(max(sk_off, 1), device=dev, dtype=torch.float32)
-        # ---- communication buffers ---------------------------------------------
+        # Q blocks followed by the Z / Y blocks of the sketch records
+        self.qz = torch.zeros(max(plan.total_q + self.total_z, 1), device=dev, dtype=torch.float32)
         self.staging = torch.empty(max(plan.total_unc, 1), device=dev, dtype=torch.float32)
-        self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_p, 4), max(plan.total_q, 4)], group, dev) \
-            if self.world > 1 else None
+        self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_p, 4), max(plan.total_q + self.total_z, 4)],
+                              group, dev) if self.world > 1 else None
         self._bound = None
-        self._build_tc_tables(buf if variant != "batched" else self.work)
-
-    # -- tensor-core path tables -----------------------------------------------
-    def _build_tc_tables(self, work: torch.Tensor) -> None:
-        """Tensor maps and split-K tile lists for the matrices TMA can address; the
-        others stay on the SIMT kernels."""
-        plan, dev = self.plan, self.device
+        self.aux_ptr = -1
         self.use_tc = False
-        nm = len(plan.mats)
-        if not nm or not _use_tc():
-            return
-        maps = np.zeros(nm * 256, dtype=np.uint8)   # two 128-byte tensor maps per matrix
-        ok = np.zeros(nm, dtype=np.uint8)
-        host = np.ascontiguousarray(self.mats_host)
-        native.check(self.lib.conef_tc_encode_maps(host.ctypes.data, nm, work.data_ptr(), maps.ctypes.data,
-                                                   ok.ctypes.data), "tc_encode_maps")
-        if not ok.any():
-            return
+        self.bind_state(state, bidx)
+        self._bound = getattr(state, "error_dict", {}).get(bidx, False) if hasattr(state, "error_dict") else None
+
+    # -- auxiliary (error) buffer and tile tables ----------------------------------------
+    def _aux(self, state, bidx) -> Optional[torch.Tensor]:
+        if self.ef_mode == native.EF_SKETCH:
+            return self.sketch_arena
+        if self.ef_mode == native.EF_DENSE:
+            return state.error_dict[bidx]
+        return None
+
+    def _build_tiles(self, work: torch.Tensor, aux: Optional[torch.Tensor]) -> None:
+        """SIMT tile lists, and - for the records TMA can address - tensor maps plus split-K
+        tile lists of the tensor-core kernel."""
+        dev, recs = self.device, self.mats_host
+        nrec = len(recs)
+        self.aux_ptr = native.ptr(aux)
+        self.use_tc = False
+        ok = np.zeros(nrec, dtype=np.uint8)
+        if nrec and _use_tc():
+            maps = np.zeros(nrec * 256, dtype=np.uint8)   # two 128-byte tensor maps per record
+            host = np.ascontiguousarray(recs)
+            native.check(self.lib.conef_tc_encode_maps(host.ctypes.data, nrec, work.data_ptr(), self.aux_ptr,
+                                                       maps.ctypes.data, ok.ctypes.data), "tc_encode_maps")
+            if ok.any():
+                self.tc_maps = torch.from_numpy(maps).to(dev)
+                assert self.tc_maps.data_ptr() % 128 == 0
+                self.use_tc = True
         self.tc_ok = ok.astype(bool)
+        good = [k for k in range(nrec) if self.tc_ok[k]]
+        bad = [k for k in range(nrec) if not self.tc_ok[k]]
 
         def split_tiles(mode):
             # mode 0 (P): output rows = n, K = m.  mode 1 (Q): output rows = m, K = n.
-            blocks = sum(math.ceil((e.m if mode else e.n) / 128) for e, good in zip(plan.mats, self.tc_ok) if good)
+            blocks = sum(math.ceil(int(recs[k]["m"] if mode else recs[k]["n"]) / 128) for k in good)
             want = max(1, math.ceil(TARGET_CTAS / max(blocks, 1)))
-            tiles, any_atomic = [], False
-            for k, (e, good) in enumerate(zip(plan.mats, self.tc_ok)):
-                if not good:
-                    continue
-                mn, K = (e.m, e.n) if mode else (e.n, e.m)
+            tiles = []
+            for k in good:
+                n, m = int(recs[k]["n"]), int(recs[k]["m"])
+                mn, K = (m, n) if mode else (n, m)
                 splits = max(1, min(want, math.ceil(K / 256)))
                 klen = math.ceil(math.ceil(K / splits) / 32) * 32
                 splits = math.ceil(K / klen)
-                flag = (1 << 30) if splits > 1 else 0
-                any_atomic |= splits > 1
+                shared = self.fused_err if mode == 0 else self.ef_mode == native.EF_DENSE
+                flag = (1 << 30) if (splits > 1 or shared) else 0
                 for mb in range(math.ceil(mn / 128)):
                     for sp in range(splits):
                         tiles.append((k | flag, mb * 128, sp * klen, klen))
-            t = torch.from_numpy(np.asarray(tiles, dtype=np.int32).reshape(-1, 4)).to(dev)
-            return t, len(tiles), any_atomic
+            t = torch.from_numpy(np.asarray(tiles, dtype=np.int32).reshape(-1, 4)).to(dev) if tiles else None
+            return t, len(tiles)
 
-        self.tc_p_tiles, self.n_tc_p, self.tc_p_atomic = split_tiles(0)
-        self.tc_q_tiles, self.n_tc_q, self.tc_q_atomic = split_tiles(1)
-        self.tc_maps = torch.from_numpy(maps).to(dev)
-        assert self.tc_maps.data_ptr() % 128 == 0
-        good = [k for k in range(nm) if self.tc_ok[k]]
-        bad = [k for k in range(nm) if not self.tc_ok[k]]
-        self.ef_tiles = self._tiles([(k, rb) for k in good for rb in range(math.ceil(plan.mats[k].n / P_ROWS))])
-        self.n_ef_tiles = sum(math.ceil(plan.mats[k].n / P_ROWS) for k in good)
-        # SIMT tile lists shrink to the matrices TMA cannot address
-        p_tiles = [(k, rb) for k in bad for rb in range(math.ceil(plan.mats[k].n / P_ROWS))]
+        self.tc_p_tiles, self.n_tc_p = split_tiles(0)
+        self.tc_q_tiles, self.n_tc_q = split_tiles(1)
+        p_tiles = [(k, rb) for k in bad for rb in range(math.ceil(int(recs[k]["n"]) / P_ROWS))]
         q_tiles = []
         for k in bad:
-            rec = self.mats_host[k]
-            nrb = math.ceil(int(rec["n"]) / int(rec["q_rows"]))
-            ncb = (int(rec["m"]) + Q_COLS - 1) // Q_COLS
+            nrb = math.ceil(int(recs[k]["n"]) / int(recs[k]["q_rows"]))
+            ncb = (int(recs[k]["m"]) + Q_COLS - 1) // Q_COLS
             q_tiles += [(k, t) for t in range(nrb * ncb)]
         self.p_tiles, self.n_p_tiles = self._tiles(p_tiles), len(p_tiles)
         self.q_tiles, self.n_q_tiles = self._tiles(q_tiles), len(q_tiles)
-        self.q_atomic = any(bool(self.mats_host[k]["q_atomic"]) for k in bad)
-        self.use_tc = True
+        # outputs that are accumulated must start from zero
+        self.p_zero = self.fused_err or self.use_tc
+        self.q_zero = self.fused_err or self.use_tc or bool(recs["q_atomic"].any()) if nrec else False
 
     def _tiles(self, tiles) -> Optional[torch.Tensor]:
         if not tiles:
@@ -334,23 +359,31 @@ class PowerSGDEngine(_EngineBase):
             for cnt, e in enumerate(plan.mats):
                 if cnt not in comps:
                     comps[cnt] = _make_matrix_compressor(state, e.n, e.m, dev, self.variant == "c2cs")
+        # tile tables and tensor maps depend on where the error buffer lives
+        aux = self._aux(state, bidx) if hasattr(state, "error_dict") else None
+        if native.ptr(aux) != self.aux_ptr:
+            work = self.work if self.variant == "batched" else None
+            self._build_tiles(work if work is not None else _PtrOnly(self.buf_ptr), aux)
 
     def _pq_memory(self, state, bidx):
-        """Flat P/Q tensors of the state; returns (pmem, qmem, fresh)."""
+        """Flat P/Q tensors of the state; Q is a view of the engine's combined Q|Z buffer.
+        Returns (pmem, qmem, fresh)."""
         plan, dev = self.plan, self.device
         warm = getattr(state, "warm_start", False) and self.variant != "unbiased"
         p, q = state.p_memory_dict.get(bidx), state.q_memory_dict.get(bidx)
         ok = (torch.is_tensor(p) and torch.is_tensor(q) and p.numel() == plan.total_p
-              and q.numel() == plan.total_q and p.device == dev and q.device == dev)
+              and q.numel() == plan.total_q and p.device == dev)
         fresh = (not warm) or not ok
+        qview = self.qz[: plan.total_q]
+        if ok and q.data_ptr() != qview.data_ptr():
+            qview.copy_(q.to(dev))                    # restored from a checkpoint or set by the user
         if not ok:
             if warm:
                 logger.info("Allocating contiguous memory of length %d for Ps, and of length %d for Qs.",
                             plan.total_p, plan.total_q)
-            # 16-byte aligned flat buffers (the reduce kernels use vector loads)
             state.p_memory_dict[bidx] = torch.empty(max(plan.total_p, 1), device=dev, dtype=torch.float32)[: plan.total_p]
-            state.q_memory_dict[bidx] = torch.empty(max(plan.total_q, 1), device=dev, dtype=torch.float32)[: plan.total_q]
-        return state.p_memory_dict[bidx], state.q_memory_dict[bidx], fresh
+        state.q_memory_dict[bidx] = qview
+        return state.p_memory_dict[bidx], qview, fresh
 
     # -- one step ------------------------------------------------------------------
     def run(self, state, bucket, buf: torch.Tensor) -> None:
@@ -359,9 +392,9 @@ class PowerSGDEngine(_EngineBase):
         bidx = bucket.index()
         ws = self.world
         st = native.stream_ptr(dev)
-        nmats = len(plan.mats)
+        nm = self.nm
         edict = getattr(state, "error_dict", None)
-        if edict is not None and (self._bound is None or edict.get(bidx) is not self._bound):
+        if edict is not None and edict.get(bidx, False) is not self._bound:
             self.bind_state(state, bidx)
             self._bound = edict.get(bidx, False)
         state.total_numel_before_compression += plan.numel_before
@@ -381,6 +414,7 @@ class PowerSGDEngine(_EngineBase):
             alpha, beta = _ef_coeffs(state)
         dense_err = state.error_dict[bidx] if self.ef_mode == native.EF_DENSE else None
         sketch = self.sketch_arena
+        aux = self.aux_ptr if self.fused_err else 0
 
         # external error compressors: query before, clone, update after
         copy = None
@@ -394,34 +428,42 @@ class PowerSGDEngine(_EngineBase):
         eps = float(getattr(state, "orthogonalization_epsilon", 0) or 0)
         symm = self.symm
         slot = self.step & 1
-        if nmats:
+        if nm:
             if fresh:
                 seed = int(state.rng.randint(1_000_000_000))
                 native.check(lib.conef_fill_normal(qmem.data_ptr(), qmem.numel(), seed, st), "fill_normal")
             if self.variant != "unbiased":
-                native.check(lib.conef_orthogonalize(self.mats_dev.data_ptr(), nmats, 1, qmem.data_ptr(), eps,
+                native.check(lib.conef_orthogonalize(self.mats_dev.data_ptr(), nm, 1, qmem.data_ptr(), eps,
                                                      0, 0, 1, 0, self.status.data_ptr(), 0, st), "orth_q")
+            if self.ef_mode == native.EF_SKETCH:
+                # Z = alpha * H^T Q, so that the sketch records contribute alpha * unsketch(S) Q to P
+                self.qz[plan.total_q :].zero_()
+                native.check(lib.conef_sketch_project(self.mats_dev.data_ptr(), nm, self.max_cols,
+                                                      self.tables.data_ptr(), self.qz.data_ptr(), alpha, 0, st),
+                             "sketch_project")
 
-        # 1. uncompressed tensors -> staging ; P = (G + e) Q
+        # 1. uncompressed tensors -> staging ; P = G Q + e Q
         stage = symm.local(slot, 0) if symm else self.staging
         p_target = symm.local(slot, 1) if symm else pmem
         if plan.total_unc:
             native.check(lib.conef_gather_segments(self.segs_dev.data_ptr(), len(plan.segs), wp,
                                                    native.ptr(dense_err), stage.data_ptr(), plan.total_unc, st),
                          "gather_segments")
-        if nmats:
-            self._launch_p(wp, sketch, dense_err, qmem, p_target, alpha, st)
+        if nm:
+            if self.p_zero:
+                p_target[: plan.total_p].zero_()
+            self._launch_p(wp, aux, self.qz, p_target, st)
 
         # 2. all-reduce of staging and P ; Gram-Schmidt of P
         orth_p = self.variant != "unbiased"
         if symm:
             self.epoch += 1
             native.check(lib.conef_signal_peers(symm.peer_flags_dev(), ws, self.rank, self.epoch, st), "signal")
-            if nmats and orth_p:
+            if nm and orth_p:
                 native.check(lib.conef_orthogonalize(
-                    self.mats_dev.data_ptr(), nmats, 0, pmem.data_ptr(), eps, symm.peer_ptrs_dev(slot, 1),
+                    self.mats_dev.data_ptr(), nm, 0, pmem.data_ptr(), eps, symm.peer_ptrs_dev(slot, 1),
                     symm.flags_ptr(), ws, self.epoch, self.status.data_ptr(), DEFAULT_SPIN_LIMIT, st), "orth_p")
-            elif nmats:
+            elif nm:
                 native.check(lib.conef_allreduce_oneshot(
                     pmem.data_ptr(), symm.peer_ptrs_dev(slot, 1), 0, symm.flags_ptr(), ws, self.rank, self.epoch,
                     plan.total_p, 1.0 / ws, self.status.data_ptr(), DEFAULT_SPIN_LIMIT, st), "allreduce_p")
@@ -436,23 +478,28 @@ class PowerSGDEngine(_EngineBase):
             if ws > 1:
                 if plan.total_unc:
                     self._nccl_sum(stage[: plan.total_unc], self.group)
-                if nmats:
+                if nm:
                     self._nccl_sum(pmem, self.group, average=not orth_p)
             if plan.total_unc:
                 native.check(lib.conef_scatter_segments(
                     self.segs_dev.data_ptr(), len(plan.segs), wp, 0, 1, stage.data_ptr(), 1.0 / ws,
                     native.ptr(dense_err), plan.total_unc, st), "scatter_segments")
-            if nmats and orth_p:
-                native.check(lib.conef_orthogonalize(self.mats_dev.data_ptr(), nmats, 0, pmem.data_ptr(), eps,
+            if nm and orth_p:
+                native.check(lib.conef_orthogonalize(self.mats_dev.data_ptr(), nm, 0, pmem.data_ptr(), eps,
                                                      0, 0, 1, 0, self.status.data_ptr(), 0, st), "orth_p")
 
-        if nmats:
-            # 3. Q = M^T P (skipped by the unbiased compressor: Q stays the random projection)
+        if nm:
+            # 3. Q = G^T P + e^T P (skipped by the unbiased compressor: Q stays the random projection)
             if self.variant != "unbiased":
-                q_target = symm.local(slot, 2) if symm else qmem
-                if self.q_atomic or (self.use_tc and self.tc_q_atomic):
-                    q_target[: plan.total_q].zero_()
-                self._launch_q(wp, pmem, q_target, st)
+                q_target = symm.local(slot, 2) if symm else self.qz
+                if self.q_zero:
+                    q_target.zero_()
+                self._launch_q(wp, aux, pmem, q_target, st)
+                if self.ef_mode == native.EF_SKETCH:
+                    # Q += alpha * H Y with Y = S^T P computed by the sketch records
+                    native.check(lib.conef_sketch_project(self.mats_dev.data_ptr(), nm, self.max_cols,
+                                                          self.tables.data_ptr(), q_target.data_ptr(), alpha, 1, st),
+                                 "sketch_unproject")
                 if symm:
                     self.epoch += 1
                     native.check(lib.conef_allreduce_oneshot(
@@ -461,11 +508,11 @@ class PowerSGDEngine(_EngineBase):
                         DEFAULT_SPIN_LIMIT, st), "allreduce_q")
                 elif ws > 1:
                     self._nccl_sum(qmem, self.group, average=True)
-            # 4. M_hat = P Q^T, residual -> error store
+            # 4. M_hat = P Q^T ; residual of (G + e) -> error store
             native.check(lib.conef_psgd_decompress(
                 self.mats_dev.data_ptr(), self.d_tiles.data_ptr(), self.n_d_tiles, self.d_rows, wp,
                 pmem.data_ptr(), qmem.data_ptr(), 1.0, native.ptr(sketch), native.ptr(self.tables),
-                native.ptr(self.counts), native.ptr(dense_err), beta, self.ef_mode, self.max_rank,
+                native.ptr(self.counts), native.ptr(dense_err), alpha, beta, self.ef_mode, self.max_rank,
                 self.d_smem, st), "decompress")
 
         if self.external:
@@ -480,34 +527,37 @@ class PowerSGDEngine(_EngineBase):
             state.q_memory_dict.pop(bidx, None)
         self.step += 1
 
-    def _launch_p(self, wp, sketch, dense_err, qmem, p_target, alpha, st):
+    def _launch_p(self, wp, aux, small: torch.Tensor, p_target: torch.Tensor, st) -> None:
+        """P (+)= A Q over every record: tcgen05 tiles where TMA can address the matrix, SIMT elsewhere."""
         lib = self.lib
-        if self.use_tc:
-            # error add as a pre-pass (TMA cannot patch the tile), then tcgen05 tiles
-            if self.ef_mode != native.EF_NONE:
-                native.check(lib.conef_ef_apply(self.mats_dev.data_ptr(), native.ptr(self.ef_tiles),
-                                                self.n_ef_tiles, wp, native.ptr(sketch), native.ptr(self.tables),
-                                                native.ptr(dense_err), alpha, self.ef_mode, st), "ef_apply")
-            if self.tc_p_atomic:
-                p_target[: self.plan.total_p].zero_()
+        if self.use_tc and self.n_tc_p:
             native.check(lib.conef_psgd_tc(0, self.mats_dev.data_ptr(), self.tc_maps.data_ptr(),
-                                           self.tc_p_tiles.data_ptr(), self.n_tc_p, qmem.data_ptr(),
+                                           self.tc_p_tiles.data_ptr(), self.n_tc_p, small.data_ptr(),
                                            p_target.data_ptr(), self.max_rank, self.status.data_ptr(), st), "psgd_tc(P)")
         if self.n_p_tiles:
-            native.check(lib.conef_psgd_p(self.mats_dev.data_ptr(), self.p_tiles.data_ptr(), self.n_p_tiles, wp,
-                                          native.ptr(sketch), native.ptr(self.tables), native.ptr(dense_err),
-                                          qmem.data_ptr(), p_target.data_ptr(), alpha, self.ef_mode, self.max_rank,
-                                          st), "psgd_p")
+            native.check(lib.conef_psgd_p(self.mats_dev.data_ptr(), self.p_tiles.data_ptr(), self.n_p_tiles, wp, aux,
+                                          small.data_ptr(), p_target.data_ptr(), int(self.p_zero), self.max_rank, st),
+                         "psgd_p")
 
-    def _launch_q(self, wp, pmem, q_target, st):
+    def _launch_q(self, wp, aux, pmem: torch.Tensor, q_target: torch.Tensor, st) -> None:
         lib = self.lib
-        if self.use_tc:
+        if self.use_tc and self.n_tc_q:
             native.check(lib.conef_psgd_tc(1, self.mats_dev.data_ptr(), self.tc_maps.data_ptr(),
                                            self.tc_q_tiles.data_ptr(), self.n_tc_q, pmem.data_ptr(),
                                            q_target.data_ptr(), self.max_rank, self.status.data_ptr(), st), "psgd_tc(Q)")
         if self.n_q_tiles:
-            native.check(lib.conef_psgd_q(self.mats_dev.data_ptr(), self.q_tiles.data_ptr(), self.n_q_tiles, wp,
+            native.check(lib.conef_psgd_q(self.mats_dev.data_ptr(), self.q_tiles.data_ptr(), self.n_q_tiles, wp, aux,
                                           pmem.data_ptr(), q_target.data_ptr(), self.max_rank, st), "psgd_q")
+
+
+class _PtrOnly:
+    """Carries a raw device address where only ``data_ptr()`` is needed."""
+
+    def __init__(self, ptr: int):
+        self._ptr = ptr
+
+    def data_ptr(self) -> int:
+        return self._ptr
 
 
 def _get_engine(state, bucket, buf, group, factory):
@@ -526,7 +576,7 @@ def run_powersgd_native(state, bucket, group, variant: str) -> torch.futures.Fut
     stream.wait_stream(torch.cuda.current_stream(dev))
     with torch.cuda.stream(stream):
         eng = _get_engine(state, bucket, buf, group,
-                          lambda: PowerSGDEngine(state, buf, bucket.gradients(), group, variant))
+                          lambda: PowerSGDEngine(state, buf, bucket.gradients(), group, variant, bucket.index()))
         eng.run(state, bucket, buf)
         fut = _done_on_current_stream(buf)
     state.maybe_increase_iter(bucket)

@@ -115,27 +115,34 @@ def main():
         state = cb.PowerSGDState(None, matrix_approximation_rank=rank, start_powerSGD_iter=2,
                                  use_error_compression=True, sketch_size=args.sketch_size)
         eng = PowerSGDEngine(state, buf, bucket.gradients(), group, "powersgd")
-        eng.bind_state(state, 0)
         plan = eng.plan
         mat_bytes = 4 * sum(e.numel for e in plan.mats)
         sk_bytes = 4 * eng.sketch_arena.numel()
         pmem = torch.randn(plan.total_p, device=dev)
-        qmem = torch.randn(plan.total_q, device=dev)
+        qz = eng.qz
+        qz.normal_()
+        qmem = qz[: plan.total_q]
         eng.sketch_arena.normal_()
         tag = "tc" if eng.use_tc else "simt"
         if tc == "1" and not eng.use_tc:
             continue
         if want(f"p_{tag}"):
-            t = _time(lambda: eng._launch_p(buf.data_ptr(), eng.sketch_arena, None, qmem, pmem, 0.1, st), args.iters)
-            extra = " (error add pre-pass + tcgen05 tiles)" if eng.use_tc else " (error add fused)"
-            record(f"p_{tag}: P=(G+e)Q", t, 2 * mat_bytes + sk_bytes, "read G + sketch, write G" + extra)
+            def run_p():
+                qz[plan.total_q :].zero_()
+                native.check(lib.conef_sketch_project(eng.mats_dev.data_ptr(), eng.nm, eng.max_cols,
+                                                      eng.tables.data_ptr(), qz.data_ptr(), 0.1, 0, st))
+                pmem.zero_()
+                eng._launch_p(buf.data_ptr(), eng.aux_ptr, qz, pmem, st)
+            t = _time(run_p, args.iters)
+            record(f"p_{tag}: P=GQ+S(aH^TQ)", t, mat_bytes + sk_bytes, "read G and the sketch once, nothing written back")
         if want(f"q_{tag}"):
             def run_q():
-                if eng.q_atomic or (eng.use_tc and eng.tc_q_atomic):
-                    qmem.zero_()
-                eng._launch_q(buf.data_ptr(), pmem, qmem, st)
+                qz.zero_()
+                eng._launch_q(buf.data_ptr(), eng.aux_ptr, pmem, qz, st)
+                native.check(lib.conef_sketch_project(eng.mats_dev.data_ptr(), eng.nm, eng.max_cols,
+                                                      eng.tables.data_ptr(), qz.data_ptr(), 0.1, 1, st))
             t = _time(run_q, args.iters)
-            record(f"q_{tag}: Q=M^T P", t, mat_bytes, "read M")
+            record(f"q_{tag}: Q=G^TP+aH(S^TP)", t, mat_bytes + sk_bytes, "read G and the sketch once")
         if tc == "1":
             continue
         if want("orth"):
@@ -147,7 +154,7 @@ def main():
             t = _time(lambda: native.check(lib.conef_psgd_decompress(
                 eng.mats_dev.data_ptr(), eng.d_tiles.data_ptr(), eng.n_d_tiles, eng.d_rows, buf.data_ptr(),
                 pmem.data_ptr(), qmem.data_ptr(), 1.0, eng.sketch_arena.data_ptr(), eng.tables.data_ptr(),
-                eng.counts.data_ptr(), 0, 0.9, native.EF_SKETCH, eng.max_rank, eng.d_smem, st)), args.iters)
+                eng.counts.data_ptr(), 0, 0.1, 0.9, native.EF_SKETCH, eng.max_rank, eng.d_smem, st)), args.iters)
             record("decompress+sketch update", t, 2 * mat_bytes + 2 * sk_bytes, "read M, write M_hat, r/w sketch")
         if want("segments"):
             t = _time(lambda: native.check(lib.conef_gather_segments(
@@ -158,8 +165,8 @@ def main():
         if want("hook"):
             state.iter = 2
             t = _time(lambda: cb.powerSGD_hook(state, bucket).wait(), args.iters)
-            record("powerSGD_hook (whole bucket, ws=1)", t, 6 * mat_bytes,
-                   "ideal: P pass r+w, Q pass r, decompress r+w (+sketch)")
+            record("powerSGD_hook (whole bucket, ws=1)", t, 4 * mat_bytes + 4 * sk_bytes,
+                   "ideal: G read by P, Q and decompress, written once; sketch read 3x, written once")
 
     # ---------------- random block pipeline ----------------
     for kind, kw in (("ef", dict()), ("sketch", dict(use_error_compression=True, sketch_size=args.sketch_size)),

@@ -42,8 +42,8 @@ def test_tc_p_and_q_tiles_match_matmul(single_rank_group, monkeypatch, rank):
     st = native.stream_ptr(buf.device)
     g = torch.Generator().manual_seed(0)
     qmem = torch.randn(plan.total_q, generator=g).to(DEV)
-    pmem = torch.full((plan.total_p,), float("nan"), device=DEV)
-    eng._launch_p(buf.data_ptr(), None, None, qmem, pmem, 0.0, st)
+    pmem = torch.zeros(plan.total_p, device=DEV)       # split-K tiles accumulate
+    eng._launch_p(buf.data_ptr(), 0, qmem, pmem, st)
     torch.cuda.synchronize()
     assert int(eng.status[0]) == 0, "an mbarrier wait gave up"
     errs = []
@@ -59,7 +59,7 @@ def test_tc_p_and_q_tiles_match_matmul(single_rank_group, monkeypatch, rank):
     errs = []
     # Q = M^T P
     qout = torch.zeros(plan.total_q, device=DEV)
-    eng._launch_q(buf.data_ptr(), pmem, qout, st)
+    eng._launch_q(buf.data_ptr(), 0, pmem, qout, st)
     torch.cuda.synchronize()
     assert int(eng.status[0]) == 0
     for e in plan.mats:
