@@ -108,3 +108,10 @@ __device__ __forceinline__ bool wait_flags_bounded(const uint32_t* flags, int wo
   }
   return true;
 }
+
+// Offset (in floats) of element (k, n) of a small operand inside its packed copy: per K step
+// of 8 rows, NP/8 groups of 8 columns, each two 8x4 core matrices (k%8 < 4, k%8 >= 4) of
+// 32 floats: K-major, no swizzle, exactly what tcgen05.mma reads for a K=8 tf32 step.
+__host__ __device__ __forceinline__ long long conef_packed_offset(long long k, int n, int np) {
+  return (k >> 3) * (np * 8) + (n >> 3) * 64 + ((k & 7) >> 2) * 32 + (n & 7) * 4 + (k & 3);
+}

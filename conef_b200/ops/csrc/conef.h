@@ -30,6 +30,8 @@ typedef struct ConefMat {
   int q_atomic;       // 1 if several CTAs (or several records) accumulate into the same Q block
   int src;            // 0: the matrix lives in the gradient bucket, 1: in the auxiliary buffer
   int pad;
+  long long qpk_off;  // packed copy of the (m x r) block for the tensor-core kernel (floats), see conef_pack_small
+  long long ppk_off;  // packed copy of the (n x r) block
 } ConefMat;
 
 // A contiguous run of elements of the bucket (one uncompressed tensor, or the
@@ -88,6 +90,12 @@ int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles, const floa
 int conef_orthogonalize(const ConefMat* mats, int nmats, int which, float* buf, float eps,
                         const float* const* peer_bufs, const uint32_t* flags, int world,
                         uint32_t epoch, int* status, long long spin_limit, cudaStream_t stream);
+// Same, and additionally writes the result in the packed tensor-core layout (see
+// conef_pack_small) into `packed` with NP = packed_np columns.
+int conef_orthogonalize_packed(const ConefMat* mats, int nmats, int which, float* buf, float eps,
+                               const float* const* peer_bufs, const uint32_t* flags, int world,
+                               uint32_t epoch, int* status, long long spin_limit, float* packed,
+                               int packed_np, cudaStream_t stream);
 int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket,
                  const float* aux, const float* P, float* Q, int max_rank, cudaStream_t stream);
 // M_hat = P Q^T written into the bucket.  M = G + remembered error is formed on the fly
@@ -117,9 +125,16 @@ int conef_tc_encode_maps(const ConefMat* host_mats, int nmats, const float* buck
                          const float* aux_dev, void* maps_out_256B_each, unsigned char* ok);
 // mode 0: P = M Q (small operand Q, output P).  mode 1: Q = M^T P (small operand P, output Q).
 // tiles: int4 records {matrix | atomic << 30, first output row, first K index, K extent}.
+// small_packed: the small operands in the tensor-core operand layout (conef_pack_small).
 int conef_psgd_tc(int mode, const ConefMat* mats, const void* maps, const void* tiles, int ntiles,
-                  const float* small_base, float* out_base, int max_rank, int* status,
+                  const float* small_packed, float* out_base, int max_rank, int* status,
                   cudaStream_t stream);
+// Copy the (rows x r) blocks of `src` (which = 0: P blocks, 1: Q blocks) into the layout the
+// tensor-core kernel reads with one bulk copy per stage: K-major 8x4 core matrices, r padded
+// with zeros to NP = 16 (max_rank <= 16) or 32 columns, rows padded to a multiple of 32.
+// Pad cells are never written: `dst` must be zero-initialised once.
+int conef_pack_small(const ConefMat* mats, int nrec, int which, const float* src, float* dst,
+                     int max_rank, cudaStream_t stream);
 
 // ---- segments, random blocks, quantised error (blocks.cu) -------------------
 int conef_gather_segments(const ConefSeg* segs, int nsegs, const float* bucket,

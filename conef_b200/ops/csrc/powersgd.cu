@@ -112,7 +112,8 @@ constexpr int O_MAXR = 32;
 __global__ void __launch_bounds__(O_THREADS)
 k_orthogonalize(const ConefMat* __restrict__ mats, int which, float* __restrict__ buf, float eps,
                 const float* const* __restrict__ peer_bufs, const uint32_t* __restrict__ flags, int world,
-                uint32_t epoch, int* __restrict__ status, long long spin_limit) {
+                uint32_t epoch, int* __restrict__ status, long long spin_limit, float* __restrict__ packed,
+                int packed_np) {
   __shared__ float red[O_MAXR][17];   // per-warp partials: [column][warp]
   __shared__ float dots[O_MAXR];
   __shared__ int ok;
@@ -176,6 +177,14 @@ k_orthogonalize(const ConefMat* __restrict__ mats, int which, float* __restrict_
     }
     __syncthreads();
   }
+  if (packed != nullptr) {
+    float* pk = packed + (which == 0 ? M.ppk_off : M.qpk_off);
+    for (size_t i = tid; i < total; i += O_THREADS) {
+      const long long row = i / r;
+      const int c = (int)(i - row * r);
+      pk[conef_packed_offset(row, c, packed_np)] = a[i];
+    }
+  }
 }
 
 extern "C" int conef_orthogonalize(const ConefMat* mats, int nmats, int which, float* buf, float eps,
@@ -184,8 +193,44 @@ extern "C" int conef_orthogonalize(const ConefMat* mats, int nmats, int which, f
                                    cudaStream_t stream) {
   if (nmats <= 0) return 0;
   k_orthogonalize<<<nmats, O_THREADS, 0, stream>>>(mats, which, buf, eps, peer_bufs, flags, world, epoch,
-                                                  status, spin_limit);
+                                                  status, spin_limit, nullptr, 0);
   CONEF_CHECK_LAUNCH("k_orthogonalize");
+  return 0;
+}
+
+extern "C" int conef_orthogonalize_packed(const ConefMat* mats, int nmats, int which, float* buf, float eps,
+                                          const float* const* peer_bufs, const uint32_t* flags, int world,
+                                          uint32_t epoch, int* status, long long spin_limit, float* packed,
+                                          int packed_np, cudaStream_t stream) {
+  if (nmats <= 0) return 0;
+  k_orthogonalize<<<nmats, O_THREADS, 0, stream>>>(mats, which, buf, eps, peer_bufs, flags, world, epoch,
+                                                  status, spin_limit, packed, packed_np);
+  CONEF_CHECK_LAUNCH("k_orthogonalize");
+  return 0;
+}
+
+// Packed copies of the small operands for the tensor-core kernel (layout: conef_packed_offset).
+__global__ void k_pack_small(const ConefMat* __restrict__ mats, int which, const float* __restrict__ src,
+                             float* __restrict__ dst, int np) {
+  const ConefMat M = mats[blockIdx.y];
+  const int rows = which == 0 ? M.n : M.m;
+  const int r = M.r;
+  const float* a = src + (which == 0 ? M.p_off : M.q_off);
+  float* pk = dst + (which == 0 ? M.ppk_off : M.qpk_off);
+  const size_t total = (size_t)rows * r;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const long long row = i / r;
+    const int c = (int)(i - row * r);
+    pk[conef_packed_offset(row, c, np)] = a[i];
+  }
+}
+
+extern "C" int conef_pack_small(const ConefMat* mats, int nrec, int which, const float* src, float* dst,
+                                int max_rank, cudaStream_t stream) {
+  if (nrec <= 0) return 0;
+  dim3 grid(16, nrec);
+  k_pack_small<<<grid, 256, 0, stream>>>(mats, which, src, dst, max_rank <= 16 ? 16 : 32);
+  CONEF_CHECK_LAUNCH("k_pack_small");
   return 0;
 }
 

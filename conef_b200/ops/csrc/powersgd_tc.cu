@@ -7,10 +7,11 @@
 //
 // One CTA computes a 128 x NP accumulator tile (NP = r padded to 16 or 32) in
 // tensor memory:
-//   warp 4, one lane : TMA producer - four 32x32 fp32 boxes of M per stage
-//                      (cp.async.bulk.tensor.2d, 128-byte swizzle), local memory only
-//   warps 0-3        : stage the matching 32 x r slice of the small operand into
-//                      shared memory (transposed to K-major, no swizzle, zero padded), later the epilogue
+//   warp 4, one lane : TMA producer - per stage four 32x32 fp32 boxes of M
+//                      (cp.async.bulk.tensor.2d, 128-byte swizzle) and one bulk copy of the
+//                      matching 32 x NP slice of the small operand, which the host side keeps
+//                      pre-packed in the K-major core-matrix layout; local memory only
+//   warps 0-3        : epilogue
 //   warp 5, one lane : tcgen05.mma.kind::tf32 (4 x K=8 per stage), tcgen05.commit frees the stage
 //   epilogue         : tcgen05.ld 32 lanes x NP columns per warp -> r floats per output row,
 //                      plain store or fp32 atomics when K is split across CTAs
@@ -62,6 +63,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort_flag = 1;
   return false;
+}
+
+// plain (untiled) bulk copy global -> shared, 16-byte aligned on both sides, size a multiple of 16
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
@@ -120,7 +127,7 @@ constexpr int tc_smem_bytes() {
 template <int NP, int Q_MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ maps,
-            const TcTile* __restrict__ tiles, const float* __restrict__ small_base, float* __restrict__ out_base,
+            const TcTile* __restrict__ tiles, const float* __restrict__ small_packed, float* __restrict__ out_base,
             int* __restrict__ status
 #ifdef CONEF_TC_DEBUG
             , float* __restrict__ dbg
@@ -146,7 +153,8 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
   const int k_total = Q_MODE ? M.n : M.m;
   const int k_end = min(k_total, T.k0 + T.klen);
   const int iters = (k_end - T.k0 + TC_BK - 1) / TC_BK;
-  const float* small = small_base + (Q_MODE ? M.p_off : M.q_off);   // (k_total x r), row-major
+  // small operand, packed: per K step of 8 rows NP * 8 floats (see conef_packed_offset)
+  const float* small = small_packed + (Q_MODE ? M.ppk_off : M.qpk_off);
   float* out = out_base + (Q_MODE ? M.q_off : M.p_off);              // (mn_total x r), row-major
   const CUtensorMap* tmap = maps + 2 * mat + Q_MODE;   // [2*mat] K-major view, [2*mat+1] MN-major view
 
@@ -155,7 +163,7 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < TC_STAGES; ++s) {
-      mbar_init(smem_u32(full + s), 1 + 4);   // TMA thread + one arrival per staging warp
+      mbar_init(smem_u32(full + s), 1);       // the producer's arrive.expect_tx
       mbar_init(smem_u32(empty + s), 1);      // tcgen05.commit
     }
     mbar_init(smem_u32(accum), 1);
@@ -179,9 +187,10 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
         const int s = it % TC_STAGES;
         if (!mbar_wait(smem_u32(empty + s), ((it / TC_STAGES) & 1) ^ 1, abort_flag)) break;
         const uint32_t bar = smem_u32(full + s);
-        mbar_arrive_expect_tx(bar, A_STAGE_BYTES);
+        mbar_arrive_expect_tx(bar, A_STAGE_BYTES + BStage<NP>::BYTES);
         const uint32_t dst = smem_u32(a_st + s * A_STAGE_BYTES);
         const int k = T.k0 + it * TC_BK;
+        bulk_load(smem_u32(b_st + s * BStage<NP>::BYTES), small + (size_t)k * NP, BStage<NP>::BYTES, bar);
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
           // the tensor map is (columns, rows) of M with a 32 x 32 box; x is a multiple of 32 elements
@@ -219,27 +228,8 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
       if (ok) umma_commit(smem_u32(accum));   // accumulator complete
     }
   } else {
-    // ---------------- small-operand staging (warps 0-3), then epilogue ----------------
-    const int t = threadIdx.x;                 // 0..127
+    // ---------------- epilogue (warps 0-3) ----------------
     bool ok = true;
-    for (int it = 0; it < iters && ok; ++it) {
-      const int s = it % TC_STAGES;
-      ok = mbar_wait(smem_u32(empty + s), ((it / TC_STAGES) & 1) ^ 1, abort_flag);
-      if (!ok) break;
-      uint8_t* bdst = b_st + s * BStage<NP>::BYTES;
-      // K-major, no swizzle: 8 x 4 core matrices of 128 B.  Per K step of 8 (ks), element (n, k) lives at
-      //   ks * (NP/8)*256 + (n/8)*256 + ((k%8)/4)*128 + (n%8)*16 + (k%4)*4
-      for (int idx = t; idx < TC_BK * NP; idx += 128) {
-        const int kk = idx / NP, n = idx - kk * NP;
-        const int k = T.k0 + it * TC_BK + kk;
-        const float v = (k < k_end && n < r) ? __ldg(small + (size_t)k * r + n) : 0.f;
-        const int off = (kk >> 3) * ((NP / 8) * 256) + (n >> 3) * 256 + ((kk & 7) >> 2) * 128 + (n & 7) * 16 + (kk & 3) * 4;
-        *reinterpret_cast<float*>(bdst + off) = v;
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMA
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(full + s));
-    }
     if (ok) ok = mbar_wait(smem_u32(accum), 0, abort_flag);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -375,7 +365,7 @@ extern "C" int conef_tc_encode_maps(const ConefMat* host_mats, int nmats, const 
 // mode 0: P = M Q (small operand Q, output P); mode 1: Q = M^T P (small operand P, output Q).
 extern "C" int conef_psgd_tc(int mode, const ConefMat* mats, const void* maps, const void* tiles, int ntiles,
                              const float* small_base, float* out_base, int max_rank, int* status,
-                             cudaStream_t stream) {
+                             cudaStream_t stream) {   // small_base: packed small operands
   if (ntiles <= 0) return 0;
   if (max_rank > 32) { conef_set_error("tcgen05 path supports rank <= 32"); return 2; }
   if (max_rank <= 16) {

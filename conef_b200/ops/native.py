@@ -30,7 +30,7 @@ MAT_DTYPE = np.dtype(
     [("g_off", "<i8"), ("p_off", "<i8"), ("q_off", "<i8"), ("sk_off", "<i8"),
      ("n", "<i4"), ("m", "<i4"), ("r", "<i4"), ("W", "<i4"),
      ("tab_off", "<i4"), ("cnt_off", "<i4"), ("q_rows", "<i4"), ("q_atomic", "<i4"),
-     ("src", "<i4"), ("pad", "<i4")], align=True)
+     ("src", "<i4"), ("pad", "<i4"), ("qpk_off", "<i8"), ("ppk_off", "<i8")], align=True)
 SEG_DTYPE = np.dtype([("src_off", "<i8"), ("dst_off", "<i8"), ("len", "<i8")], align=True)
 BLK_DTYPE = np.dtype(
     [("g_off", "<i8"), ("numel", "<i8"), ("start", "<i8"), ("block", "<i8"),
@@ -40,7 +40,7 @@ BLK_DTYPE = np.dtype(
 LAMB_DTYPE = np.dtype(
     [("p", "<u8"), ("g", "<u8"), ("m", "<u8"), ("v", "<u8"), ("numel", "<i8"),
      ("weight_decay", "<f4"), ("pad", "<i4")], align=True)
-assert MAT_DTYPE.itemsize == 72 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.itemsize == 72
+assert MAT_DTYPE.itemsize == 88 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.itemsize == 72
 assert LAMB_DTYPE.itemsize == 48
 
 EF_NONE, EF_DENSE, EF_SKETCH, EF_QUANT8 = 0, 1, 2, 3
@@ -56,6 +56,9 @@ _SIGNATURES = {
     "conef_sketch_project": ([vp, C.c_int, C.c_int, vp, vp, C.c_float, C.c_int, vp], C.c_int),
     "conef_orthogonalize": ([vp, C.c_int, C.c_int, vp, C.c_float, vp, vp, C.c_int, C.c_uint32, vp, c_ll, vp], C.c_int),
     "conef_psgd_q": ([vp, vp, C.c_int, vp, vp, vp, vp, C.c_int, vp], C.c_int),
+    "conef_orthogonalize_packed": ([vp, C.c_int, C.c_int, vp, C.c_float, vp, vp, C.c_int, C.c_uint32, vp, c_ll, vp,
+                                    C.c_int, vp], C.c_int),
+    "conef_pack_small": ([vp, C.c_int, C.c_int, vp, vp, C.c_int, vp], C.c_int),
     "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
                                C.c_float, C.c_int, C.c_int, C.c_size_t, vp], C.c_int),
     "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),

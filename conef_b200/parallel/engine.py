@@ -202,6 +202,25 @@ class PowerSGDEngine(_EngineBase):
                 err["sk_off"], err["tab_off"], err["cnt_off"] = -1, -1, -1
         self.total_z = z_off
         self.max_cols = max((e.m for e in plan.mats), default=0)
+        # packed copies of the small operands for the tensor-core kernel: rows padded to a
+        # multiple of 32, columns to NP; an error record that shares a block shares its copy
+        self.np_cols = 16 if self.max_rank <= 16 else 32
+        qpk = ppk = 0
+        pad32 = lambda x: (x + 31) // 32 * 32
+        for k in range(nm):
+            mats[k]["qpk_off"], mats[k]["ppk_off"] = qpk, ppk
+            qpk += pad32(int(mats[k]["m"])) * self.np_cols
+            ppk += pad32(int(mats[k]["n"])) * self.np_cols
+        if self.fused_err:
+            for k in range(nm):
+                err = mats[nm + k]
+                err["ppk_off"] = mats[k]["ppk_off"]
+                if self.ef_mode == native.EF_DENSE:
+                    err["qpk_off"] = mats[k]["qpk_off"]
+                else:
+                    err["qpk_off"] = qpk
+                    qpk += pad32(int(err["m"])) * self.np_cols
+        self.qpk_total, self.ppk_total = qpk, ppk
         # row blocks of the SIMT Q kernel
         total_cb = sum((int(r["m"]) + Q_COLS - 1) // Q_COLS for r in mats) or 1
         want_rb = max(1, math.ceil(TARGET_CTAS / total_cb))
@@ -245,6 +264,7 @@ class PowerSGDEngine(_EngineBase):
         # Q blocks followed by the Z / Y blocks of the sketch records
         self.qz = torch.zeros(max(plan.total_q + self.total_z, 1), device=dev, dtype=torch.float32)
         self.staging = torch.empty(max(plan.total_unc, 1), device=dev, dtype=torch.float32)
+        self.qpk = self.ppk = None       # allocated (zeroed: pad cells stay zero) when the tensor-core path is on
         self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_p, 4), max(plan.total_q + self.total_z, 4)],
                               group, dev) if self.world > 1 else None
         self._bound = None
@@ -278,6 +298,9 @@ class PowerSGDEngine(_EngineBase):
                 self.tc_maps = torch.from_numpy(maps).to(dev)
                 assert self.tc_maps.data_ptr() % 128 == 0
                 self.use_tc = True
+                if self.qpk is None:
+                    self.qpk = torch.zeros(max(self.qpk_total, 1), device=dev, dtype=torch.float32)
+                    self.ppk = torch.zeros(max(self.ppk_total, 1), device=dev, dtype=torch.float32)
         self.tc_ok = ok.astype(bool)
         good = [k for k in range(nrec) if self.tc_ok[k]]
         bad = [k for k in range(nrec) if not self.tc_ok[k]]
@@ -460,9 +483,10 @@ class PowerSGDEngine(_EngineBase):
             self.epoch += 1
             native.check(lib.conef_signal_peers(symm.peer_flags_dev(), ws, self.rank, self.epoch, st), "signal")
             if nm and orth_p:
-                native.check(lib.conef_orthogonalize(
+                native.check(lib.conef_orthogonalize_packed(
                     self.mats_dev.data_ptr(), nm, 0, pmem.data_ptr(), eps, symm.peer_ptrs_dev(slot, 1),
-                    symm.flags_ptr(), ws, self.epoch, self.status.data_ptr(), DEFAULT_SPIN_LIMIT, st), "orth_p")
+                    symm.flags_ptr(), ws, self.epoch, self.status.data_ptr(), DEFAULT_SPIN_LIMIT,
+                    native.ptr(self.ppk) if self.use_tc else 0, self.np_cols, st), "orth_p")
             elif nm:
                 native.check(lib.conef_allreduce_oneshot(
                     pmem.data_ptr(), symm.peer_ptrs_dev(slot, 1), 0, symm.flags_ptr(), ws, self.rank, self.epoch,
@@ -485,8 +509,9 @@ class PowerSGDEngine(_EngineBase):
                     self.segs_dev.data_ptr(), len(plan.segs), wp, 0, 1, stage.data_ptr(), 1.0 / ws,
                     native.ptr(dense_err), plan.total_unc, st), "scatter_segments")
             if nm and orth_p:
-                native.check(lib.conef_orthogonalize(self.mats_dev.data_ptr(), nm, 0, pmem.data_ptr(), eps,
-                                                     0, 0, 1, 0, self.status.data_ptr(), 0, st), "orth_p")
+                native.check(lib.conef_orthogonalize_packed(
+                    self.mats_dev.data_ptr(), nm, 0, pmem.data_ptr(), eps, 0, 0, 1, 0, self.status.data_ptr(), 0,
+                    native.ptr(self.ppk) if self.use_tc else 0, self.np_cols, st), "orth_p")
 
         if nm:
             # 3. Q = G^T P + e^T P (skipped by the unbiased compressor: Q stays the random projection)
@@ -494,7 +519,7 @@ class PowerSGDEngine(_EngineBase):
                 q_target = symm.local(slot, 2) if symm else self.qz
                 if self.q_zero:
                     q_target.zero_()
-                self._launch_q(wp, aux, pmem, q_target, st)
+                self._launch_q(wp, aux, pmem, q_target, st, packed=True)
                 if self.ef_mode == native.EF_SKETCH:
                     # Q += alpha * H Y with Y = S^T P computed by the sketch records
                     native.check(lib.conef_sketch_project(self.mats_dev.data_ptr(), nm, self.max_cols,
@@ -528,22 +553,30 @@ class PowerSGDEngine(_EngineBase):
         self.step += 1
 
     def _launch_p(self, wp, aux, small: torch.Tensor, p_target: torch.Tensor, st) -> None:
-        """P (+)= A Q over every record: tcgen05 tiles where TMA can address the matrix, SIMT elsewhere."""
+        """P (+)= A Q over every record: tcgen05 tiles where TMA can address the matrix, SIMT elsewhere.
+        ``small`` is the flat Q|Z buffer; the tensor-core kernel reads its packed copy."""
         lib = self.lib
         if self.use_tc and self.n_tc_p:
+            native.check(lib.conef_pack_small(self.mats_dev.data_ptr(), len(self.mats_host), 1, small.data_ptr(),
+                                              self.qpk.data_ptr(), self.max_rank, st), "pack_small(Q)")
             native.check(lib.conef_psgd_tc(0, self.mats_dev.data_ptr(), self.tc_maps.data_ptr(),
-                                           self.tc_p_tiles.data_ptr(), self.n_tc_p, small.data_ptr(),
+                                           self.tc_p_tiles.data_ptr(), self.n_tc_p, self.qpk.data_ptr(),
                                            p_target.data_ptr(), self.max_rank, self.status.data_ptr(), st), "psgd_tc(P)")
         if self.n_p_tiles:
             native.check(lib.conef_psgd_p(self.mats_dev.data_ptr(), self.p_tiles.data_ptr(), self.n_p_tiles, wp, aux,
                                           small.data_ptr(), p_target.data_ptr(), int(self.p_zero), self.max_rank, st),
                          "psgd_p")
 
-    def _launch_q(self, wp, aux, pmem: torch.Tensor, q_target: torch.Tensor, st) -> None:
+    def _launch_q(self, wp, aux, pmem: torch.Tensor, q_target: torch.Tensor, st, packed: bool = False) -> None:
+        """Q (+)= A^T P over every record.  ``packed`` says the packed copy of P is already up to date
+        (the Gram-Schmidt kernel writes it)."""
         lib = self.lib
         if self.use_tc and self.n_tc_q:
+            if not packed:
+                native.check(lib.conef_pack_small(self.mats_dev.data_ptr(), self.nm, 0, pmem.data_ptr(),
+                                                  self.ppk.data_ptr(), self.max_rank, st), "pack_small(P)")
             native.check(lib.conef_psgd_tc(1, self.mats_dev.data_ptr(), self.tc_maps.data_ptr(),
-                                           self.tc_q_tiles.data_ptr(), self.n_tc_q, pmem.data_ptr(),
+                                           self.tc_q_tiles.data_ptr(), self.n_tc_q, self.ppk.data_ptr(),
                                            q_target.data_ptr(), self.max_rank, self.status.data_ptr(), st), "psgd_tc(Q)")
         if self.n_q_tiles:
             native.check(lib.conef_psgd_q(self.mats_dev.data_ptr(), self.q_tiles.data_ptr(), self.n_q_tiles, wp, aux,
