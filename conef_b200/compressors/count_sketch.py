@@ -92,7 +92,7 @@ class DenseCS:
     def query(self, grad_plus_error: torch.Tensor, alpha: float) -> None:
         mat = self._check(grad_plus_error)
         idx, sign, packed, _ = self._tables()
-        if native.use_native(mat) and mat.dtype == torch.float32:
+        if native.use_native(mat) and mat.dtype == torch.float32 and self.cs.is_contiguous():
             native.check(native.lib().conef_sketch_query(
                 mat.data_ptr(), self.cs.data_ptr(), int(self.cs.dtype == torch.float16), packed.data_ptr(),
                 self.N, self.D, self.range, float(alpha), native.stream_ptr(mat.device)), "sketch_query")
@@ -102,12 +102,12 @@ class DenseCS:
     def update(self, vec: torch.Tensor, beta: float) -> None:
         mat = self._check(vec)
         idx, sign, packed, counts = self._tables()
-        if native.use_native(mat) and mat.dtype == torch.float32:
+        if native.use_native(mat) and mat.dtype == torch.float32 and self.cs.is_contiguous():
             native.check(native.lib().conef_sketch_update(
                 mat.data_ptr(), self.cs.data_ptr(), int(self.cs.dtype == torch.float16), packed.data_ptr(),
                 counts.data_ptr(), self.N, self.D, self.range, float(beta),
                 native.stream_ptr(mat.device)), "sketch_update")
-        elif self.cs.dtype == torch.float32:
+        elif self.cs.dtype == torch.float32 and self.cs.is_contiguous():
             ref.sketch_update_ref(mat.float(), self.cs, idx, sign, beta)
         else:
             tmp = self.cs.float()
@@ -140,7 +140,7 @@ class DenseCS:
         self.sketch_size = float(d.get("sketch_size", self.range / max(self.D, 1)))
         cs = torch.from_numpy(np.asarray(d["cs"])).to(self.storage_dtype)
         if keep is not None and keep.numel() == cs.numel():
-            keep.copy_(cs.view_as(keep))  # keep arena-backed storage in place
+            keep.copy_(cs.reshape(keep.shape))  # keep arena-backed storage in place
             self.cs = keep
         else:
             self.cs = cs.to(default_device())

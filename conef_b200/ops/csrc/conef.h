@@ -29,7 +29,7 @@ typedef struct ConefMat {
   int q_rows;         // rows per CTA row-block in the Q = M^T P kernel
   int q_atomic;       // 1 if several CTAs (or several records) accumulate into the same Q block
   int src;            // 0: the matrix lives in the gradient bucket, 1: in the auxiliary buffer
-  int pad;
+  int Wp;             // row pitch of the sketch block in floats (W rounded up so that TMA can address it)
   long long qpk_off;  // packed copy of the (m x r) block for the tensor-core kernel (floats), see conef_pack_small
   long long ppk_off;  // packed copy of the (n x r) block
 } ConefMat;

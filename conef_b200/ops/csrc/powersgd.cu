@@ -324,7 +324,7 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
   extern __shared__ float sm[];
   const int2 t = tiles[blockIdx.x];
   const ConefMat M = mats[t.x];
-  const int m = M.m, r = M.r, W = M.W;
+  const int m = M.m, r = M.r, W = M.W, Wp = M.Wp;
   const int row0 = t.y * RB;
   const int rows = min(RB, M.n - row0);
   float* ps = sm;                          // RB * RP
@@ -335,15 +335,35 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
     const int ii = i / RP, c = i - ii * RP;
     ps[i] = (c < r && ii < rows) ? p[(size_t)ii * r + c] : 0.f;
   }
-  float* srow = ef_mode == CONEF_EF_SKETCH ? sketch + M.sk_off + (size_t)row0 * W : nullptr;
+  float* srow = ef_mode == CONEF_EF_SKETCH ? sketch + M.sk_off + (size_t)row0 * Wp : nullptr;
   if (ef_mode == CONEF_EF_SKETCH)
-    for (int i = threadIdx.x; i < rows * W; i += D_THREADS) { acc[i] = 0.f; old[i] = srow[i]; }
+    for (int i = threadIdx.x; i < rows * W; i += D_THREADS) {
+      const int ii = i / W, h2 = i - ii * W;
+      acc[i] = 0.f;
+      old[i] = srow[(size_t)ii * Wp + h2];
+    }
   __syncthreads();
 
   const int32_t* tab = ef_mode == CONEF_EF_SKETCH ? tables + M.tab_off : nullptr;
   float* g0 = bucket + M.g_off + (size_t)row0 * m;
   float* e0 = ef_mode == CONEF_EF_DENSE ? dense_err + M.g_off + (size_t)row0 * m : nullptr;
-  for (int j = threadIdx.x; j < m; j += D_THREADS) {
+  // Software pipeline: the RB loads of the next column are issued before the current column
+  // is processed, so that loads stay in flight across the stores of M_hat.
+  float v[RB], vn[RB];
+  int j = threadIdx.x;
+#pragma unroll
+  for (int ii = 0; ii < RB; ++ii) {
+    v[ii] = (ii < rows && j < m) ? __ldcs(g0 + (size_t)ii * m + j) : 0.f;
+    if (ef_mode == CONEF_EF_DENSE && ii < rows && j < m) v[ii] += __ldcs(e0 + (size_t)ii * m + j);
+  }
+  for (; j < m; j += D_THREADS) {
+    const int jn = j + D_THREADS;
+#pragma unroll
+    for (int ii = 0; ii < RB; ++ii) vn[ii] = (ii < rows && jn < m) ? __ldcs(g0 + (size_t)ii * m + jn) : 0.f;
+    if (ef_mode == CONEF_EF_DENSE) {
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii) if (ii < rows && jn < m) vn[ii] += __ldcs(e0 + (size_t)ii * m + jn);
+    }
     float qv[RP];
     const float* q = Q + M.q_off + (size_t)j * r;
 #pragma unroll
@@ -354,13 +374,6 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
       const int e = __ldg(tab + j);
       h = unpack_bucket(e);
       s = unpack_sign(e);
-    }
-    float v[RB];
-#pragma unroll
-    for (int ii = 0; ii < RB; ++ii) v[ii] = ii < rows ? __ldcs(g0 + (size_t)ii * m + j) : 0.f;
-    if (ef_mode == CONEF_EF_DENSE) {
-#pragma unroll
-      for (int ii = 0; ii < RB; ++ii) if (ii < rows) v[ii] += __ldcs(e0 + (size_t)ii * m + j);
     }
 #pragma unroll
     for (int ii = 0; ii < RB; ++ii) {
@@ -377,14 +390,16 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
         }
       }
     }
+#pragma unroll
+    for (int ii = 0; ii < RB; ++ii) v[ii] = vn[ii];
   }
   if (ef_mode == CONEF_EF_SKETCH) {
     __syncthreads();
     const float omb = 1.f - beta;
     const int32_t* cnt = counts + M.cnt_off;
     for (int i = threadIdx.x; i < rows * W; i += D_THREADS) {
-      const int h2 = i % W;
-      srow[i] = old[i] * (1.f - omb * (float)__ldg(cnt + h2)) + acc[i];
+      const int ii = i / W, h2 = i - ii * W;
+      srow[(size_t)ii * Wp + h2] = old[i] * (1.f - omb * (float)__ldg(cnt + h2)) + acc[i];
     }
   }
 }

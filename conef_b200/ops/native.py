@@ -30,7 +30,7 @@ MAT_DTYPE = np.dtype(
     [("g_off", "<i8"), ("p_off", "<i8"), ("q_off", "<i8"), ("sk_off", "<i8"),
      ("n", "<i4"), ("m", "<i4"), ("r", "<i4"), ("W", "<i4"),
      ("tab_off", "<i4"), ("cnt_off", "<i4"), ("q_rows", "<i4"), ("q_atomic", "<i4"),
-     ("src", "<i4"), ("pad", "<i4"), ("qpk_off", "<i8"), ("ppk_off", "<i8")], align=True)
+     ("src", "<i4"), ("Wp", "<i4"), ("qpk_off", "<i8"), ("ppk_off", "<i8")], align=True)
 SEG_DTYPE = np.dtype([("src_off", "<i8"), ("dst_off", "<i8"), ("len", "<i8")], align=True)
 BLK_DTYPE = np.dtype(
     [("g_off", "<i8"), ("numel", "<i8"), ("start", "<i8"), ("block", "<i8"),

@@ -178,7 +178,8 @@ class PowerSGDEngine(_EngineBase):
             rec["n"], rec["m"], rec["r"], rec["W"] = e.n, e.m, e.r, W
             rec["sk_off"], rec["tab_off"], rec["cnt_off"] = -1, -1, -1
             if self.ef_mode == native.EF_SKETCH:
-                rec["sk_off"] = sk_off
+                Wp = (W + 3) // 4 * 4       # row pitch: 16-byte multiple so that TMA can address the sketch
+                rec["sk_off"], rec["Wp"] = sk_off, Wp
                 key = (e.m, W)
                 if key not in table_index:
                     _, _, packed, counts = tables_for(dev, e.m, W, seeds[0], seeds[1])
@@ -190,11 +191,12 @@ class PowerSGDEngine(_EngineBase):
                 rec["tab_off"], rec["cnt_off"] = table_index[key]
                 # record nm + k: the (n x W) sketch as a matrix; Z / Y (W x r) live behind the Q blocks
                 err = mats[nm + k]
-                err["src"], err["g_off"], err["n"], err["m"], err["r"] = 1, sk_off, e.n, W, e.r
+                # (its pad columns stay zero and meet zero rows of Z / produce unused rows of Y)
+                err["src"], err["g_off"], err["n"], err["m"], err["r"] = 1, sk_off, e.n, Wp, e.r
                 err["p_off"], err["q_off"] = e.p_off, plan.total_q + z_off
                 err["sk_off"], err["tab_off"], err["cnt_off"] = -1, -1, -1
-                sk_off += e.n * W
-                z_off += W * e.r
+                sk_off += e.n * Wp
+                z_off += Wp * e.r
             elif self.ef_mode == native.EF_DENSE:
                 err = mats[nm + k]
                 err["src"], err["g_off"], err["n"], err["m"], err["r"] = 1, e.g_off, e.n, e.m, e.r
@@ -305,15 +307,22 @@ class PowerSGDEngine(_EngineBase):
         good = [k for k in range(nrec) if self.tc_ok[k]]
         bad = [k for k in range(nrec) if not self.tc_ok[k]]
 
+        waves = float(os.environ.get("CONEF_TC_WAVES", 3))
+        min_k = int(os.environ.get("CONEF_TC_MIN_K", 384))
+        max_k = int(os.environ.get("CONEF_TC_MAX_K", 1024))
+
         def split_tiles(mode):
             # mode 0 (P): output rows = n, K = m.  mode 1 (Q): output rows = m, K = n.
-            blocks = sum(math.ceil(int(recs[k]["m"] if mode else recs[k]["n"]) / 128) for k in good)
-            want = max(1, math.ceil(TARGET_CTAS / max(blocks, 1)))
+            # Every tile gets about the same K extent, chosen so that the launch has a few
+            # waves of CTAs (two CTAs fit on an SM) without making tiles too short.
+            dims = [((int(recs[k]["m"]), int(recs[k]["n"])) if mode else (int(recs[k]["n"]), int(recs[k]["m"])))
+                    for k in good]
+            work = sum(math.ceil(mn / 128) * K for mn, K in dims)
+            klen_t = work / max(1.0, waves * TARGET_CTAS)
+            klen_t = int(min(max_k, max(min_k, math.ceil(klen_t / 32) * 32)))
             tiles = []
-            for k in good:
-                n, m = int(recs[k]["n"]), int(recs[k]["m"])
-                mn, K = (m, n) if mode else (n, m)
-                splits = max(1, min(want, math.ceil(K / 256)))
+            for k, (mn, K) in zip(good, dims):
+                splits = max(1, round(K / klen_t))
                 klen = math.ceil(math.ceil(K / splits) / 32) * 32
                 splits = math.ceil(K / klen)
                 shared = self.fused_err if mode == 0 else self.ef_mode == native.EF_DENSE
@@ -362,17 +371,19 @@ class PowerSGDEngine(_EngineBase):
                 comps = {}
                 state.error_dict[bidx] = comps
             for cnt, (e, rec) in enumerate(zip(plan.mats, self.mats_host)):
-                W = int(rec["W"])
-                view = self.sketch_arena[int(rec["sk_off"]) : int(rec["sk_off"]) + e.n * W]
+                W, Wp = int(rec["W"]), int(rec["Wp"])
+                # (n, W) view with row pitch Wp into the arena
+                view = self.sketch_arena[int(rec["sk_off"]) : int(rec["sk_off"]) + e.n * Wp].view(e.n, Wp)[:, :W]
                 old = comps.get(cnt)
                 if isinstance(old, DenseCS) and not isinstance(old, HalfDenseCS) \
                         and (old.N, old.D, old.range) == (e.n, e.m, W):
                     if old.cs.data_ptr() != view.data_ptr():
-                        view.copy_(old.cs.reshape(-1).to(dev))
-                        old.cs = view.view(e.n, W)
+                        view.copy_(old.cs.to(dev))
+                        old.cs = view
                 else:
-                    comps[cnt] = DenseCS(e.n, e.m, state.sketch_size, device=dev,
-                                         seed=getattr(state, "hash_seed", 0), storage=view)
+                    comp = DenseCS(e.n, e.m, state.sketch_size, device="cpu", seed=getattr(state, "hash_seed", 0))
+                    comp.cs = view
+                    comps[cnt] = comp
         elif self.external:
             from .hooks import _make_matrix_compressor
             comps = state.error_dict.get(bidx)
