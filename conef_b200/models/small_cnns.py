@@ -1,0 +1,48 @@
+"""VGG-11/13/16/19 with batch norm and LeNet for 32x32 inputs.
+
+Counterparts of the reference's ``examples/ImageClassification/models/vgg.py:14-43`` and
+``lenet.py:5-23`` (whose ``forward`` has a typo that makes it unusable; this one runs).
+"""
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+VGG_LAYOUTS = {
+    "VGG11": [64, "M", 128, "M", 256, 256, "M", 512, 512, "M", 512, 512, "M"],
+    "VGG13": [64, 64, "M", 128, 128, "M", 256, 256, "M", 512, 512, "M", 512, 512, "M"],
+    "VGG16": [64, 64, "M", 128, 128, "M", 256, 256, 256, "M", 512, 512, 512, "M", 512, 512, 512, "M"],
+    "VGG19": [64, 64, "M", 128, 128, "M", 256, 256, 256, 256, "M", 512, 512, 512, 512, "M", 512, 512, 512, 512, "M"],
+}
+
+
+class VGG(nn.Module):
+    def __init__(self, name="VGG16", num_classes=10):
+        super().__init__()
+        layers, cin = [], 3
+        for item in VGG_LAYOUTS[name]:
+            if item == "M":
+                layers.append(nn.MaxPool2d(2, 2))
+            else:
+                layers += [nn.Conv2d(cin, item, 3, padding=1), nn.BatchNorm2d(item), nn.ReLU(inplace=True)]
+                cin = item
+        self.features = nn.Sequential(*layers)
+        self.classifier = nn.Linear(512, num_classes)
+
+    def forward(self, x):
+        return self.classifier(torch.flatten(self.features(x), 1))
+
+
+class LeNet(nn.Module):
+    def __init__(self, num_classes=10):
+        super().__init__()
+        self.conv1 = nn.Conv2d(3, 6, 5)
+        self.conv2 = nn.Conv2d(6, 16, 5)
+        self.fc1 = nn.Linear(16 * 5 * 5, 120)
+        self.fc2 = nn.Linear(120, 84)
+        self.fc3 = nn.Linear(84, num_classes)
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.conv1(x)), 2)
+        x = F.max_pool2d(F.relu(self.conv2(x)), 2)
+        x = torch.flatten(x, 1)
+        return self.fc3(F.relu(self.fc2(F.relu(self.fc1(x)))))

@@ -150,7 +150,8 @@ def _powersgd_torch(state, bucket, group, *, transposed_sketch=False) -> torch.f
     if conef:
         comps = state.error_dict.setdefault(bidx, {})
         for cnt, (e, mat) in enumerate(zip(plan.mats, mats)):
-            if cnt not in comps:
+            want = (e.m, e.n) if transposed_sketch else (e.n, e.m)
+            if cnt not in comps or (comps[cnt].N, comps[cnt].D) != want:
                 comps[cnt] = _make_matrix_compressor(state, e.n, e.m, device, transposed_sketch)
             comps[cnt].query(mat, alpha)
             copies.append(mat.clone())
@@ -215,7 +216,7 @@ def powerSGD_hook(state: PowerSGDState, bucket: dist.GradBucket) -> torch.future
     """Layer-wise PowerSGD with optional (compressed) error feedback."""
     group = _group(state)
     buf = bucket.buffer()
-    if state.iter < state.start_powerSGD_iter:
+    if state.in_warmup(state.start_powerSGD_iter, bucket):
         state.maybe_increase_iter(bucket)
         return allreduce_fut(group, buf)
     if _native_ok(state, buf):
@@ -235,7 +236,7 @@ def C2CS_hook_v2(state: PowerSGDState, bucket: dist.GradBucket) -> torch.futures
     ``(n, m)`` matrix's memory (communication/powerSGD_hook.py:918-920)."""
     group = _group(state)
     buf = bucket.buffer()
-    if state.iter < state.start_powerSGD_iter:
+    if state.in_warmup(state.start_powerSGD_iter, bucket):
         state.maybe_increase_iter(bucket)
         return allreduce_fut(group, buf)
     if _native_ok(state, buf):
@@ -248,7 +249,7 @@ def batched_powerSGD_hook(state: PowerSGDState, bucket: dist.GradBucket) -> torc
     """The whole bucket as one zero-padded square matrix; dense error feedback only."""
     group = _group(state)
     buf = bucket.buffer()
-    if state.iter < state.start_powerSGD_iter:
+    if state.in_warmup(state.start_powerSGD_iter, bucket):
         state.maybe_increase_iter(bucket)
         return allreduce_fut(group, buf)
     if _native_ok(state, buf):
@@ -317,7 +318,7 @@ def UnbiasedMtrx_hook(state: unbiasedMtrxState, bucket: dist.GradBucket) -> torc
     (communication/unbiasedMtrx_hook.py:279-285); that collective is dropped."""
     group = _group(state)
     buf = bucket.buffer()
-    if state.iter < state.start_powerSGD_iter:
+    if state.in_warmup(state.start_powerSGD_iter, bucket):
         state.maybe_increase_iter(bucket)
         return allreduce_fut(group, buf)
     if _native_ok(state, buf):
@@ -440,7 +441,7 @@ def RandomBlock_hook(state: RandomBlockState, bucket: dist.GradBucket) -> torch.
     """Send one random contiguous block per tensor; the rest goes to error feedback."""
     group = _group(state)
     buf = bucket.buffer()
-    if state.iter < state.start_compression_iter:
+    if state.in_warmup(state.start_compression_iter, bucket):
         state.maybe_increase_iter(bucket)
         return allreduce_fut(group, buf)
     if _native_ok(state, buf):
@@ -454,7 +455,7 @@ def UnbiasedRandomBlock_hook(state: UnbiasedRandomBlockState, bucket: dist.GradB
     selection probability so the estimate is unbiased."""
     group = _group(state)
     buf = bucket.buffer()
-    if state.iter < state.start_compression_iter:
+    if state.in_warmup(state.start_compression_iter, bucket):
         state.maybe_increase_iter(bucket)
         return allreduce_fut(group, buf)
     if _native_ok(state, buf):

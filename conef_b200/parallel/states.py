@@ -32,7 +32,7 @@ from ..compressors.other import ERROR_COMPRESSORS
 logger = logging.getLogger(__name__)
 
 # slots that never go into a checkpoint / pickle
-_RUNTIME_SLOTS = ("process_group", "_engines", "_timers", "_status_checked")
+_RUNTIME_SLOTS = ("process_group", "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen")
 
 
 def _to_cpu(obj):
@@ -79,11 +79,35 @@ class _StateBase:
         self._engines = {}
         self._timers = None
         self._status_checked = 0
+        self._process_iters = 0      # reduced iterations seen by this process (not persisted)
+        self._sig_seen = set()       # buckets whose layout was checked in this process
+        self.bucket_signatures = {}  # persisted: bucket index -> (numel, parameter shapes)
+
+    def in_warmup(self, start_iter: int, bucket=None) -> bool:
+        """Plain all-reduce while ``iter < start_iter`` - and, after a resume, for as long as a
+        bucket does not have the layout its saved state was built for: DDP rebuilds its buckets
+        after the first iteration of a process, so per-bucket state restored from a checkpoint
+        only lines up with the rebuilt layout."""
+        if self.iter < start_iter:
+            return True
+        if bucket is None:
+            return False
+        bidx = bucket.index()
+        if bidx in self._sig_seen:
+            return False
+        sig = (bucket.buffer().numel(), tuple(tuple(g.shape) for g in bucket.gradients()))
+        known = self.bucket_signatures.get(bidx)
+        if known is not None and known != sig and self._process_iters < 1:
+            return True              # pre-rebuild layout of a resumed run: leave the saved state alone
+        self.bucket_signatures[bidx] = sig
+        self._sig_seen.add(bidx)
+        return False
 
     # iteration counter: advances once per step, on the last bucket
     def maybe_increase_iter(self, bucket) -> None:
         if bucket.is_last():
             self.iter += 1
+            self._process_iters += 1
         start = getattr(self, "start_powerSGD_iter", None)
         if start is None:
             start = getattr(self, "start_compression_iter")
@@ -130,6 +154,8 @@ class _StateBase:
                 setattr(self, n, v)
         # device tables are rebuilt against the restored tensors on the next call
         self._engines = {}
+        self._sig_seen = set()
+        self._process_iters = 0
 
     # -- metrics -----------------------------------------------------------
     def ef_buffer_bytes(self) -> int:
@@ -165,7 +191,8 @@ class PowerSGDState(_StateBase):
         "iter", "total_numel_before_compression", "total_numel_after_compression",
         "compression_stats_logging_frequency", "next_stats_report",
         # additions
-        "error_compressor", "error_rank", "hash_seed", "_engines", "_timers", "_status_checked",
+        "error_compressor", "error_rank", "hash_seed", "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen",
+        "bucket_signatures",
     ]
 
     def __init__(self, process_group, matrix_approximation_rank=1, start_powerSGD_iter=1_000,
@@ -254,7 +281,8 @@ class RandomBlockState(_StateBase):
         "process_group", "compression_ratio", "start_compression_iter", "n_blocks",
         "use_error_compression", "beta", "sketch_size", "use_error_feedback", "rng", "error_dict",
         "iter", "compression_stats_logging_frequency", "next_stats_report", "compressed_tensor_memory",
-        "error_compressor", "hash_seed", "_engines", "_timers", "_status_checked",
+        "error_compressor", "hash_seed", "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen",
+        "bucket_signatures",
     ]
 
     def __init__(self, process_group, compression_ratio=0.1, start_compression_iter=1_000,
@@ -301,7 +329,8 @@ class UnbiasedRandomBlockState(_StateBase):
     __slots__ = [
         "process_group", "compression_ratio", "start_compression_iter", "rng", "iter",
         "compression_stats_logging_frequency", "next_stats_report", "compressed_tensor_memory",
-        "_engines", "_timers", "_status_checked",
+        "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen",
+        "bucket_signatures",
     ]
 
     def __init__(self, process_group, compression_ratio=0.1, start_compression_iter=1_000, random_seed=42,
@@ -327,7 +356,8 @@ class unbiasedMtrxState(_StateBase):
         "orthogonalization_epsilon", "rng", "p_memory_dict", "q_memory_dict", "iter",
         "total_numel_before_compression", "total_numel_after_compression",
         "compression_stats_logging_frequency", "next_stats_report",
-        "_engines", "_timers", "_status_checked",
+        "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen",
+        "bucket_signatures",
     ]
 
     def __init__(self, process_group, matrix_approximation_rank=1, start_powerSGD_iter=1_000,

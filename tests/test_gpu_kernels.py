@@ -151,3 +151,21 @@ def test_orthogonalize_kernel():
         ref.gram_schmidt_ref(want)
         torch.testing.assert_close(got[off : off + n * r].view(n, r), want, rtol=1e-3, atol=1e-4)
         off += n * r
+
+
+def test_runtime_compiled_kernel_loader():
+    """A CUDA source string compiled at run time for the device's architecture and launched on torch's stream."""
+    from conef_b200.ops.jit import JitKernel
+
+    src = r'''
+    extern "C" __global__ void axpy(float* y, const float* x, float a, int n) {
+      int i = blockIdx.x * blockDim.x + threadIdx.x;
+      if (i < n) y[i] += a * x[i];
+    }'''
+    k = JitKernel(src, "axpy")
+    assert JitKernel.compute_arch().startswith("sm_")
+    x, y = torch.randn(1000, device=DEV), torch.randn(1000, device=DEV)
+    want = y + 2.5 * x
+    k(grid=(4, 1, 1), block=(256, 1, 1), args=[y, x, 2.5, 1000])
+    torch.cuda.synchronize()
+    torch.testing.assert_close(y, want)
