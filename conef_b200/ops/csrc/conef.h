@@ -34,6 +34,13 @@ typedef struct ConefMat {
   long long ppk_off;  // packed copy of the (n x r) block
 } ConefMat;
 
+// One small-factor correction (see conef_lowrank_correct): offsets in floats into the four
+// base pointers given at launch.
+typedef struct ConefCorr {
+  long long t_off, x_off, l_off, r_off;
+  int rows_t, rows_l, c1, c2;
+} ConefCorr;
+
 // A contiguous run of elements of the bucket (one uncompressed tensor, or the
 // selected part of a random block) and where it sits in a staging buffer.
 typedef struct ConefSeg {
@@ -112,6 +119,10 @@ int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, i
 // Record nmats + i describes the sketch of matrix i; its q_off is where Z_i / Y_i live.
 int conef_sketch_project(const ConefMat* mats, int nmats, int max_cols, const int32_t* tables,
                          float* qz, float scale, int unproject, cudaStream_t stream);
+// Per matrix: T (rows_t x c1) += coef * X (rows_t x c2) * (L (rows_l x c2)^T Rm (rows_l x c1)).
+// Used by the low-rank error store, whose factors enter PowerSGD's products as small corrections.
+int conef_lowrank_correct(const ConefCorr* table, int nmats, float* T, const float* X, const float* L,
+                          const float* Rm, float coef, cudaStream_t stream);
 // Philox-keyed standard normal fill: element e of the buffer depends only on
 // (seed, e), so every rank generates the same Q without communication.
 int conef_fill_normal(float* buf, long long numel, uint64_t seed, cudaStream_t stream);

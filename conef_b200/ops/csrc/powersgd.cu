@@ -353,13 +353,14 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
   int j = threadIdx.x;
 #pragma unroll
   for (int ii = 0; ii < RB; ++ii) {
-    v[ii] = (ii < rows && j < m) ? __ldcs(g0 + (size_t)ii * m + j) : 0.f;
+    v[ii] = (ef_mode != CONEF_EF_NONE && ii < rows && j < m) ? __ldcs(g0 + (size_t)ii * m + j) : 0.f;
     if (ef_mode == CONEF_EF_DENSE && ii < rows && j < m) v[ii] += __ldcs(e0 + (size_t)ii * m + j);
   }
   for (; j < m; j += D_THREADS) {
     const int jn = j + D_THREADS;
 #pragma unroll
-    for (int ii = 0; ii < RB; ++ii) vn[ii] = (ii < rows && jn < m) ? __ldcs(g0 + (size_t)ii * m + jn) : 0.f;
+    for (int ii = 0; ii < RB; ++ii)
+      vn[ii] = (ef_mode != CONEF_EF_NONE && ii < rows && jn < m) ? __ldcs(g0 + (size_t)ii * m + jn) : 0.f;
     if (ef_mode == CONEF_EF_DENSE) {
 #pragma unroll
       for (int ii = 0; ii < RB; ++ii) if (ii < rows && jn < m) vn[ii] += __ldcs(e0 + (size_t)ii * m + jn);
@@ -490,5 +491,60 @@ extern "C" int conef_fill_normal(float* buf, long long numel, uint64_t seed, cud
   const long long quads = (numel + 3) / 4;
   k_fill_normal<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(buf, numel, seed);
   CONEF_CHECK_LAUNCH("k_fill_normal");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Small-factor corrections of the low-rank error store: per matrix
+//   T (rows_t x c1) += coef * X (rows_t x c2) * ( L (rows_l x c2)^T  Rm (rows_l x c1) )
+// One CTA per matrix: the (c2 x c1) product is reduced over rows_l in shared memory, then
+// applied to every row of T.  All operands are tall-skinny factors (c1, c2 <= 32).
+constexpr int C_THREADS = 256;
+
+__global__ void __launch_bounds__(C_THREADS)
+k_lowrank_correct(const ConefCorr* __restrict__ table, float* __restrict__ Tb, const float* __restrict__ Xb,
+                  const float* __restrict__ Lb, const float* __restrict__ Rb, float coef) {
+  __shared__ float C[32 * 32];
+  const ConefCorr K = table[blockIdx.x];
+  const int c1 = K.c1, c2 = K.c2, pairs = c1 * c2;
+  const float* L = Lb + K.l_off;
+  const float* Rm = Rb + K.r_off;
+  for (int i = threadIdx.x; i < pairs; i += C_THREADS) C[i] = 0.f;
+  __syncthreads();
+  if (pairs <= C_THREADS) {
+    const int groups = C_THREADS / pairs;
+    const int g = threadIdx.x / pairs, pr = threadIdx.x - g * pairs;
+    if (g < groups) {
+      const int a = pr / c1, b = pr - a * c1;
+      float acc = 0.f;
+      for (int i = g; i < K.rows_l; i += groups) acc = fmaf(L[(size_t)i * c2 + a], Rm[(size_t)i * c1 + b], acc);
+      atomicAdd(&C[pr], acc);
+    }
+  } else {
+    for (int pr = threadIdx.x; pr < pairs; pr += C_THREADS) {
+      const int a = pr / c1, b = pr - a * c1;
+      float acc = 0.f;
+      for (int i = 0; i < K.rows_l; ++i) acc = fmaf(L[(size_t)i * c2 + a], Rm[(size_t)i * c1 + b], acc);
+      C[pr] = acc;
+    }
+  }
+  __syncthreads();
+  float* T = Tb + K.t_off;
+  const float* X = Xb + K.x_off;
+  const size_t total = (size_t)K.rows_t * c1;
+  for (size_t e = threadIdx.x; e < total; e += C_THREADS) {
+    const size_t i = e / c1;
+    const int b = (int)(e - i * c1);
+    float acc = 0.f;
+    for (int a = 0; a < c2; ++a) acc = fmaf(X[i * c2 + a], C[a * c1 + b], acc);
+    T[e] += coef * acc;
+  }
+}
+
+extern "C" int conef_lowrank_correct(const ConefCorr* table, int nmats, float* T, const float* X, const float* L,
+                                     const float* Rm, float coef, cudaStream_t stream) {
+  if (nmats <= 0) return 0;
+  k_lowrank_correct<<<nmats, C_THREADS, 0, stream>>>(table, T, X, L, Rm, coef);
+  CONEF_CHECK_LAUNCH("k_lowrank_correct");
   return 0;
 }

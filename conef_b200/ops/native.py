@@ -40,6 +40,9 @@ BLK_DTYPE = np.dtype(
 LAMB_DTYPE = np.dtype(
     [("p", "<u8"), ("g", "<u8"), ("m", "<u8"), ("v", "<u8"), ("numel", "<i8"),
      ("weight_decay", "<f4"), ("pad", "<i4")], align=True)
+CORR_DTYPE = np.dtype([("t_off", "<i8"), ("x_off", "<i8"), ("l_off", "<i8"), ("r_off", "<i8"),
+                       ("rows_t", "<i4"), ("rows_l", "<i4"), ("c1", "<i4"), ("c2", "<i4")], align=True)
+assert CORR_DTYPE.itemsize == 48
 assert MAT_DTYPE.itemsize == 88 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.itemsize == 72
 assert LAMB_DTYPE.itemsize == 48
 
@@ -62,6 +65,7 @@ _SIGNATURES = {
     "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
                                C.c_float, C.c_int, C.c_int, C.c_size_t, vp], C.c_int),
     "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),
+    "conef_lowrank_correct": ([vp, C.c_int, vp, vp, vp, vp, C.c_float, vp], C.c_int),
     "conef_tc_supported": ([], C.c_int),
     "conef_tc_encode_maps": ([vp, C.c_int, vp, vp, vp, vp], C.c_int),
     "conef_psgd_tc": ([C.c_int, vp, vp, vp, C.c_int, vp, vp, C.c_int, vp, vp], C.c_int),

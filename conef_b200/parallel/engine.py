@@ -154,8 +154,15 @@ class PowerSGDEngine(_EngineBase):
             self.ef_mode, self.external = native.EF_DENSE, False
         elif kind == "count_sketch" and variant == "powersgd":
             self.ef_mode, self.external = native.EF_SKETCH, False
+        elif kind == "lowrank" and variant == "powersgd" and os.environ.get("CONEF_LOWRANK_NATIVE", "1") == "1":
+            self.ef_mode, self.external = native.EF_NONE, False       # factors handled by run()'s low-rank branch
         else:
             self.ef_mode, self.external = native.EF_NONE, True
+        # Low-rank error store e = U V^T: its factors enter the products as small corrections
+        # (P += a U (V^T Q), Q' += a V (U^T P)) and are refreshed by one power-iteration step
+        # U' = orth(T V), V' = T^T U' on T = G + (a+b) U V^T - P Q^T, computed without forming T:
+        # the extra records multiply G by V and G^T by U'.
+        self.lowrank = ef and ec and kind == "lowrank" and not self.external and variant == "powersgd"
         # The remembered error enters the two products as extra records of the same launches
         # (P = G Q + e Q, Q' = G^T P + e^T P); the corrected matrix is never written.
         self.fused_err = self.ef_mode in (native.EF_SKETCH, native.EF_DENSE)
@@ -163,9 +170,10 @@ class PowerSGDEngine(_EngineBase):
         # ---- descriptor records -----------------------------------------------
         nm = len(plan.mats)
         self.nm = nm
-        nrec = nm * (2 if self.fused_err else 1)
+        nrec = nm * (2 if (self.fused_err or self.lowrank) else 1)
         mats = np.zeros(nrec, dtype=native.MAT_DTYPE)
-        sk_off = tab_off = cnt_off = z_off = 0
+        sk_off = tab_off = cnt_off = z_off = u_off = 0
+        err_rank = int(getattr(state, "error_rank", None) or state.matrix_approximation_rank) if self.lowrank else 0
         table_chunks, count_chunks = [], []
         table_index: Dict[tuple, tuple] = {}
         self.widths = []
@@ -202,7 +210,19 @@ class PowerSGDEngine(_EngineBase):
                 err["src"], err["g_off"], err["n"], err["m"], err["r"] = 1, e.g_off, e.n, e.m, e.r
                 err["p_off"], err["q_off"] = e.p_off, e.q_off
                 err["sk_off"], err["tab_off"], err["cnt_off"] = -1, -1, -1
-        self.total_z = z_off
+            elif self.lowrank:
+                # record nm + k: the same gradient matrix against the error factors: V (m x k) sits
+                # behind the Q blocks, G V / U' (n x k) behind the P blocks
+                kk = min(err_rank, e.n, e.m)
+                err = mats[nm + k]
+                err["src"], err["g_off"], err["n"], err["m"], err["r"] = 0, e.g_off, e.n, e.m, kk
+                err["p_off"], err["q_off"] = plan.total_p + u_off, plan.total_q + z_off
+                err["sk_off"], err["tab_off"], err["cnt_off"] = -1, -1, -1
+                u_off += e.n * kk
+                z_off += e.m * kk
+        self.total_z, self.total_u = z_off, u_off
+        if self.lowrank:
+            self.max_rank = max(self.max_rank, err_rank)
         self.max_cols = max((e.m for e in plan.mats), default=0)
         # packed copies of the small operands for the tensor-core kernel: rows padded to a
         # multiple of 32, columns to NP; an error record that shares a block shares its copy
@@ -213,6 +233,11 @@ class PowerSGDEngine(_EngineBase):
             mats[k]["qpk_off"], mats[k]["ppk_off"] = qpk, ppk
             qpk += pad32(int(mats[k]["m"])) * self.np_cols
             ppk += pad32(int(mats[k]["n"])) * self.np_cols
+        if self.lowrank:
+            for k in range(nm, nrec):
+                mats[k]["qpk_off"], mats[k]["ppk_off"] = qpk, ppk
+                qpk += pad32(int(mats[k]["m"])) * self.np_cols
+                ppk += pad32(int(mats[k]["n"])) * self.np_cols
         if self.fused_err:
             for k in range(nm):
                 err = mats[nm + k]
@@ -267,8 +292,15 @@ class PowerSGDEngine(_EngineBase):
         self.qz = torch.zeros(max(plan.total_q + self.total_z, 1), device=dev, dtype=torch.float32)
         self.staging = torch.empty(max(plan.total_unc, 1), device=dev, dtype=torch.float32)
         self.qpk = self.ppk = None       # allocated (zeroed: pad cells stay zero) when the tensor-core path is on
-        self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_p, 4), max(plan.total_q + self.total_z, 4)],
-                              group, dev) if self.world > 1 else None
+        # P blocks followed by the U blocks of the low-rank records
+        self.pu = torch.zeros(max(plan.total_p + self.total_u, 1), device=dev, dtype=torch.float32)
+        self.u_old = self.qz2 = None
+        if self.lowrank:
+            self.u_old = torch.zeros(max(self.total_u, 1), device=dev, dtype=torch.float32)
+            self.qz2 = torch.zeros_like(self.qz)
+            self._build_corrections()
+        self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_p + self.total_u, 4),
+                               max(plan.total_q + self.total_z, 4)], group, dev) if self.world > 1 else None
         self._bound = None
         self.aux_ptr = -1
         self.use_tc = False
@@ -334,18 +366,56 @@ class PowerSGDEngine(_EngineBase):
             return t, len(tiles)
 
         self.tc_p_tiles, self.n_tc_p = split_tiles(0)
-        self.tc_q_tiles, self.n_tc_q = split_tiles(1)
         p_tiles = [(k, rb) for k in bad for rb in range(math.ceil(int(recs[k]["n"]) / P_ROWS))]
-        q_tiles = []
-        for k in bad:
-            nrb = math.ceil(int(recs[k]["n"]) / int(recs[k]["q_rows"]))
-            ncb = (int(recs[k]["m"]) + Q_COLS - 1) // Q_COLS
-            q_tiles += [(k, t) for t in range(nrb * ncb)]
         self.p_tiles, self.n_p_tiles = self._tiles(p_tiles), len(p_tiles)
-        self.q_tiles, self.n_q_tiles = self._tiles(q_tiles), len(q_tiles)
+        # Q tiles for all records, and separately for the gradient records and the extra records
+        # (the low-rank store runs them as two passes)
+        all_good, all_bad = good, bad
+        self.qsets = {}
+        for name, keep in (("all", lambda k: True), ("grad", lambda k: k < self.nm), ("err", lambda k: k >= self.nm)):
+            good = [k for k in all_good if keep(k)]
+            tc_t, n_tc = split_tiles(1)
+            q_tiles = []
+            for k in (k for k in all_bad if keep(k)):
+                nrb = math.ceil(int(recs[k]["n"]) / int(recs[k]["q_rows"]))
+                ncb = (int(recs[k]["m"]) + Q_COLS - 1) // Q_COLS
+                q_tiles += [(k, t) for t in range(nrb * ncb)]
+            self.qsets[name] = (tc_t, n_tc, self._tiles(q_tiles), len(q_tiles))
+        good = all_good
         # outputs that are accumulated must start from zero
         self.p_zero = self.fused_err or self.use_tc
         self.q_zero = self.fused_err or self.use_tc or bool(recs["q_atomic"].any()) if nrec else False
+
+    def _build_corrections(self) -> None:
+        """Per-matrix offset tables of the six small-factor corrections of the low-rank store.
+        Buffers: ``pu`` = [P | U'], ``u_old`` = U, ``qz`` = [Q | V], ``qz2`` = [. | V']."""
+        nm, recs, plan = self.nm, self.mats_host, self.plan
+
+        def table(rows):
+            arr = np.zeros(nm, dtype=native.CORR_DTYPE)
+            for k in range(nm):
+                arr[k] = rows(recs[k], recs[nm + k])
+            return native.upload_struct_array(arr, self.device)
+        uo = lambda e: int(e["p_off"]) - plan.total_p          # offset inside u_old
+        n_, m_, r_, k_ = (lambda g: int(g["n"])), (lambda g: int(g["m"])), (lambda g: int(g["r"])), (lambda e: int(e["r"]))
+        self.corr = {
+            # P += a U (V^T Q)            T = P (pu / symm)   X = U (u_old)   L = V (qz)    Rm = Q (qz)
+            "p": table(lambda g, e: (int(g["p_off"]), uo(e), int(e["q_off"]), int(g["q_off"]), n_(g), m_(g), r_(g), k_(e))),
+            # Q' += a V (U^T P)           T = Q' (q_target)   X = V (qz)      L = U (u_old) Rm = P (pu)
+            "q": table(lambda g, e: (int(g["q_off"]), int(e["q_off"]), uo(e), int(g["p_off"]), m_(g), n_(g), r_(g), k_(e))),
+            # A1 += (a+b) U (V^T V)       T = A1 (pu)         X = U (u_old)   L = V (qz)    Rm = V (qz)
+            "u1": table(lambda g, e: (int(e["p_off"]), uo(e), int(e["q_off"]), int(e["q_off"]), n_(g), m_(g), k_(e), k_(e))),
+            # A1 -= P (Q^T V)             T = A1 (pu)         X = P (pu)      L = Q (qz)    Rm = V (qz)
+            "u2": table(lambda g, e: (int(e["p_off"]), int(g["p_off"]), int(g["q_off"]), int(e["q_off"]), n_(g), m_(g), k_(e), r_(g))),
+            # A2 += (a+b) V (U^T U')      T = A2 (qz2)        X = V (qz)      L = U (u_old) Rm = U' (pu)
+            "v1": table(lambda g, e: (int(e["q_off"]), int(e["q_off"]), uo(e), int(e["p_off"]), m_(g), n_(g), k_(e), k_(e))),
+            # A2 -= Q (P^T U')            T = A2 (qz2)        X = Q (qz)      L = P (pu)    Rm = U' (pu)
+            "v2": table(lambda g, e: (int(e["q_off"]), int(g["q_off"]), int(g["p_off"]), int(e["p_off"]), m_(g), n_(g), k_(e), r_(g))),
+        }
+
+    def _correct(self, name, T, X, L, Rm, coef, st) -> None:
+        native.check(self.lib.conef_lowrank_correct(self.corr[name].data_ptr(), self.nm, T.data_ptr(), X.data_ptr(),
+                                                    L.data_ptr(), Rm.data_ptr(), float(coef), st), f"lowrank_correct({name})")
 
     def _tiles(self, tiles) -> Optional[torch.Tensor]:
         if not tiles:
@@ -384,6 +454,27 @@ class PowerSGDEngine(_EngineBase):
                     comp = DenseCS(e.n, e.m, state.sketch_size, device="cpu", seed=getattr(state, "hash_seed", 0))
                     comp.cs = view
                     comps[cnt] = comp
+        elif self.lowrank:
+            from ..compressors import LowRankError
+            comps = state.error_dict.get(bidx)
+            if not isinstance(comps, dict):
+                comps = {}
+                state.error_dict[bidx] = comps
+            nm = self.nm
+            for cnt, e in enumerate(plan.mats):
+                rec = self.mats_host[nm + cnt]
+                kk = int(rec["r"])
+                u0 = int(rec["p_off"]) - plan.total_p
+                uview = self.u_old[u0 : u0 + e.n * kk].view(e.n, kk)
+                vview = self.qz[int(rec["q_off"]) : int(rec["q_off"]) + e.m * kk].view(e.m, kk)
+                old = comps.get(cnt)
+                if not (isinstance(old, LowRankError) and (old.N, old.D, old.rank) == (e.n, e.m, kk)):
+                    old = LowRankError(e.n, e.m, kk, device="cpu", seed=getattr(state, "hash_seed", 0))
+                    comps[cnt] = old
+                if old.U.data_ptr() != uview.data_ptr():
+                    uview.copy_(old.U.to(dev))
+                    vview.copy_(old.V.to(dev))
+                    old.U, old.V = uview, vview
         elif self.external:
             from .hooks import _make_matrix_compressor
             comps = state.error_dict.get(bidx)
@@ -408,16 +499,16 @@ class PowerSGDEngine(_EngineBase):
         ok = (torch.is_tensor(p) and torch.is_tensor(q) and p.numel() == plan.total_p
               and q.numel() == plan.total_q and p.device == dev)
         fresh = (not warm) or not ok
-        qview = self.qz[: plan.total_q]
+        qview, pview = self.qz[: plan.total_q], self.pu[: plan.total_p]
         if ok and q.data_ptr() != qview.data_ptr():
             qview.copy_(q.to(dev))                    # restored from a checkpoint or set by the user
-        if not ok:
-            if warm:
-                logger.info("Allocating contiguous memory of length %d for Ps, and of length %d for Qs.",
-                            plan.total_p, plan.total_q)
-            state.p_memory_dict[bidx] = torch.empty(max(plan.total_p, 1), device=dev, dtype=torch.float32)[: plan.total_p]
-        state.q_memory_dict[bidx] = qview
-        return state.p_memory_dict[bidx], qview, fresh
+        if ok and p.data_ptr() != pview.data_ptr():
+            pview.copy_(p.to(dev))
+        if not ok and warm:
+            logger.info("Allocating contiguous memory of length %d for Ps, and of length %d for Qs.",
+                        plan.total_p, plan.total_q)
+        state.p_memory_dict[bidx], state.q_memory_dict[bidx] = pview, qview
+        return pview, qview, fresh
 
     # -- one step ------------------------------------------------------------------
     def run(self, state, bucket, buf: torch.Tensor) -> None:
@@ -443,7 +534,7 @@ class PowerSGDEngine(_EngineBase):
         wp = work.data_ptr()
 
         alpha, beta = (1.0 - getattr(state, "beta", 0.0), getattr(state, "beta", 0.0))
-        if self.external:
+        if self.external or self.lowrank:
             from .hooks import _ef_coeffs
             alpha, beta = _ef_coeffs(state)
         dense_err = state.error_dict[bidx] if self.ef_mode == native.EF_DENSE else None
@@ -485,8 +576,10 @@ class PowerSGDEngine(_EngineBase):
                          "gather_segments")
         if nm:
             if self.p_zero:
-                p_target[: plan.total_p].zero_()
+                p_target[: plan.total_p + self.total_u].zero_()
             self._launch_p(wp, aux, self.qz, p_target, st)
+            if self.lowrank:
+                self._correct("p", p_target, self.u_old, self.qz, self.qz, alpha, st)     # P += a U (V^T Q)
 
         # 2. all-reduce of staging and P ; Gram-Schmidt of P
         orth_p = self.variant != "unbiased"
@@ -525,12 +618,21 @@ class PowerSGDEngine(_EngineBase):
                     native.ptr(self.ppk) if self.use_tc else 0, self.np_cols, st), "orth_p")
 
         if nm:
+            if self.lowrank and symm:
+                # G V arrived behind the P blocks of the symmetric slot; it is local data
+                self.pu[plan.total_p :].copy_(p_target[plan.total_p : plan.total_p + self.total_u])
             # 3. Q = G^T P + e^T P (skipped by the unbiased compressor: Q stays the random projection)
             if self.variant != "unbiased":
                 q_target = symm.local(slot, 2) if symm else self.qz
-                if self.q_zero:
-                    q_target.zero_()
-                self._launch_q(wp, aux, pmem, q_target, st, packed=True)
+                if self.lowrank:
+                    if self.q_zero:
+                        q_target[: plan.total_q].zero_()         # the V blocks behind Q stay as they are
+                    self._launch_q(wp, aux, self.pu, q_target, st, packed=True, subset="grad")
+                    self._correct("q", q_target, self.qz, self.u_old, self.pu, alpha, st)   # Q' += a V (U^T P)
+                else:
+                    if self.q_zero:
+                        q_target.zero_()
+                    self._launch_q(wp, aux, pmem, q_target, st, packed=True)
                 if self.ef_mode == native.EF_SKETCH:
                     # Q += alpha * H Y with Y = S^T P computed by the sketch records
                     native.check(lib.conef_sketch_project(self.mats_dev.data_ptr(), nm, self.max_cols,
@@ -544,6 +646,8 @@ class PowerSGDEngine(_EngineBase):
                         DEFAULT_SPIN_LIMIT, st), "allreduce_q")
                 elif ws > 1:
                     self._nccl_sum(qmem, self.group, average=True)
+            if self.lowrank:
+                self._refresh_lowrank(wp, alpha, beta, st)
             # 4. M_hat = P Q^T ; residual of (G + e) -> error store
             native.check(lib.conef_psgd_decompress(
                 self.mats_dev.data_ptr(), self.d_tiles.data_ptr(), self.n_d_tiles, self.d_rows, wp,
@@ -578,20 +682,40 @@ class PowerSGDEngine(_EngineBase):
                                           small.data_ptr(), p_target.data_ptr(), int(self.p_zero), self.max_rank, st),
                          "psgd_p")
 
-    def _launch_q(self, wp, aux, pmem: torch.Tensor, q_target: torch.Tensor, st, packed: bool = False) -> None:
-        """Q (+)= A^T P over every record.  ``packed`` says the packed copy of P is already up to date
-        (the Gram-Schmidt kernel writes it)."""
+    def _launch_q(self, wp, aux, pmem: torch.Tensor, q_target: torch.Tensor, st, packed: bool = False,
+                  subset: str = "all") -> None:
+        """Q (+)= A^T P over the records of ``subset``.  ``packed`` says the packed copy of the small
+        operand is already up to date (the Gram-Schmidt kernel writes it)."""
         lib = self.lib
-        if self.use_tc and self.n_tc_q:
+        tc_tiles, n_tc, q_tiles, n_q = self.qsets[subset]
+        if self.use_tc and n_tc:
             if not packed:
                 native.check(lib.conef_pack_small(self.mats_dev.data_ptr(), self.nm, 0, pmem.data_ptr(),
                                                   self.ppk.data_ptr(), self.max_rank, st), "pack_small(P)")
             native.check(lib.conef_psgd_tc(1, self.mats_dev.data_ptr(), self.tc_maps.data_ptr(),
-                                           self.tc_q_tiles.data_ptr(), self.n_tc_q, self.ppk.data_ptr(),
+                                           tc_tiles.data_ptr(), n_tc, self.ppk.data_ptr(),
                                            q_target.data_ptr(), self.max_rank, self.status.data_ptr(), st), "psgd_tc(Q)")
-        if self.n_q_tiles:
-            native.check(lib.conef_psgd_q(self.mats_dev.data_ptr(), self.q_tiles.data_ptr(), self.n_q_tiles, wp, aux,
+        if n_q:
+            native.check(lib.conef_psgd_q(self.mats_dev.data_ptr(), q_tiles.data_ptr(), n_q, wp, aux,
                                           pmem.data_ptr(), q_target.data_ptr(), self.max_rank, st), "psgd_q")
+
+    def _refresh_lowrank(self, wp, alpha, beta, st) -> None:
+        """One power-iteration step of the error factors on T = G + (a+b) U V^T - P Q^T:
+        U' = orth(T V) with G V already behind the P blocks, then V' = T^T U'."""
+        lib, plan, nm = self.lib, self.plan, self.nm
+        rec_bytes = native.MAT_DTYPE.itemsize
+        err_recs = self.mats_dev.data_ptr() + nm * rec_bytes
+        self._correct("u1", self.pu, self.u_old, self.qz, self.qz, alpha + beta, st)    # += (a+b) U (V^T V)
+        self._correct("u2", self.pu, self.pu, self.qz, self.qz, -1.0, st)               # -= P (Q^T V)
+        native.check(lib.conef_orthogonalize_packed(
+            err_recs, nm, 0, self.pu.data_ptr(), 1e-12, 0, 0, 1, 0, self.status.data_ptr(), 0,
+            native.ptr(self.ppk) if self.use_tc else 0, self.np_cols, st), "orth_u")
+        self.qz2.zero_()
+        self._launch_q(wp, 0, self.pu, self.qz2, st, packed=True, subset="err")          # G^T U'
+        self._correct("v1", self.qz2, self.qz, self.u_old, self.pu, alpha + beta, st)   # += (a+b) V (U^T U')
+        self._correct("v2", self.qz2, self.qz, self.pu, self.pu, -1.0, st)              # -= Q (P^T U')
+        self.u_old.copy_(self.pu[plan.total_p : plan.total_p + self.total_u])
+        self.qz[plan.total_q :].copy_(self.qz2[plan.total_q :])
 
 
 class _PtrOnly:

@@ -220,3 +220,48 @@ def test_smoke_entry_point(single_rank_group):
     import __graft_entry__ as entry
 
     entry.smoke()
+
+
+@pytest.mark.parametrize("tc", ["0", "1"])
+def test_hpowersgd_lowrank_error_native_vs_cpu(single_rank_group, monkeypatch, tc):
+    """Low-rank error store: factors enter the products as small corrections on the GPU;
+    the CPU path forms the residual explicitly.  Same results, same stored factors."""
+    shapes = [(256, 1024), (64,), (130, 64, 3, 3), (640, 40, 3, 3), (10, 257), (33, 2052)]
+
+    def mk(device):
+        s = cb.hPowerSGDState(None, start_powerSGD_iter=2, matrix_approximation_rank=4, use_error_compression=True,
+                              error_compressor="lowrank", error_rank=3)
+        s.iter = 2
+        fb = FakeBucket(shapes)
+        plan = planlib.build_powersgd_plan(fb.buffer(), fb.gradients(), 4, 2)
+        g = torch.Generator().manual_seed(0)
+        s.p_memory_dict[0] = torch.zeros(plan.total_p).to(device)
+        s.q_memory_dict[0] = torch.randn(plan.total_q, generator=g).to(device)
+        return s
+
+    def run(device, backend):
+        monkeypatch.setenv("CONEF_BACKEND", backend)
+        monkeypatch.setenv("CONEF_TC", tc)
+        s = mk(device)
+        b = FakeBucket(shapes, device=device, seed=1)
+        outs = []
+        for i in range(4):
+            b.refill(30 + i)
+            outs.append(cb.hpowerSGD_hook(s, b).wait().detach().cpu().clone())
+        if device != "cpu":
+            torch.cuda.synchronize()
+            s.check_status()
+            assert s._engines[0].lowrank
+        return outs, s
+    gpu, sg = run(DEV, "native")
+    cpu, sc = run("cpu", "torch")
+    rel = lambda a, b: float((a - b).norm() / b.norm().clamp_min(1e-12))
+    tol = 2e-2 if tc == "1" else 2e-3
+    for a, c in zip(gpu, cpu):
+        assert rel(a, c) < tol, rel(a, c)
+    for k, comp in sc.error_dict[0].items():
+        g = sg.error_dict[0][k]
+        assert (g.N, g.D, g.rank) == (comp.N, comp.D, comp.rank)
+        # the factors are defined up to the sign of each column: compare the products
+        assert rel(g.U.cpu() @ g.V.cpu().t(), comp.U @ comp.V.t()) < 10 * tol
+    assert sg.ef_buffer_bytes() == sc.ef_buffer_bytes()
