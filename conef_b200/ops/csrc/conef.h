@@ -37,8 +37,12 @@ typedef struct ConefMat {
 // One small-factor correction (see conef_lowrank_correct): offsets in floats into the four
 // base pointers given at launch.
 typedef struct ConefCorr {
-  long long t_off, x_off, l_off, r_off;
-  int rows_t, rows_l, c1, c2;
+  long long t_off;          // T (rows_t x c1)
+  long long x_off[2];       // X_t (rows_t x c2[t])
+  long long l_off[2];       // L_t (rows_l x c2[t])
+  long long r_off[2];       // Rm_t (rows_l x c1)
+  int rows_t, rows_l, c1, nterms;
+  int c2[2];
 } ConefCorr;
 
 // A contiguous run of elements of the bucket (one uncompressed tensor, or the
@@ -89,20 +93,18 @@ int conef_sketch3_update(const float* vec, float* cs0, float* cs1, float* cs2,
 int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket,
                  const float* aux, const float* Q, float* P, int atomic_out, int max_rank,
                  cudaStream_t stream);
-// Batched Gram-Schmidt over the (rows x r) blocks of a flat buffer.  which=0
-// orthogonalises the P blocks (n x r), which=1 the Q blocks (m x r).  With
-// world > 1 the kernel first waits (bounded) until every peer has published
-// `epoch` in flags[peer] and sums the peers' buffers (peer_bufs[0..world)) into
-// `buf`; status[0] becomes non-zero when a wait gives up.
-int conef_orthogonalize(const ConefMat* mats, int nmats, int which, float* buf, float eps,
-                        const float* const* peer_bufs, const uint32_t* flags, int world,
-                        uint32_t epoch, int* status, long long spin_limit, cudaStream_t stream);
-// Same, and additionally writes the result in the packed tensor-core layout (see
-// conef_pack_small) into `packed` with NP = packed_np columns.
-int conef_orthogonalize_packed(const ConefMat* mats, int nmats, int which, float* buf, float eps,
-                               const float* const* peer_bufs, const uint32_t* flags, int world,
-                               uint32_t epoch, int* status, long long spin_limit, float* packed,
-                               int packed_np, cudaStream_t stream);
+// Orthonormalise the (rows x r) blocks of a flat buffer: which = 0 the P blocks (n x r),
+// which = 1 the Q blocks (m x r).  Row-parallel Gram-Schmidt through the Gram matrix, applied
+// twice (csrc/orth.cu).  tiles: int2 {record, chunk of 512 rows}.  With world > 1 each chunk
+// first waits (bounded) until every peer has published `epoch` in flags[peer] and sums the
+// peers' buffers (peer_bufs[0..world)) into `buf`; status[0] becomes non-zero when a wait gives up.
+// packed (nullable): also write the result in the tensor-core operand layout with packed_np columns.
+// gram: scratch of 2 * nrecords * 1024 floats.
+int conef_orthogonalize_packed(const ConefMat* mats, const int2* tiles, int ntiles, int nrecords,
+                               int which, float* buf, float eps, const float* const* peer_bufs,
+                               const uint32_t* flags, int world, uint32_t epoch, int* status,
+                               long long spin_limit, float* packed, int packed_np, float* gram,
+                               cudaStream_t stream);
 int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket,
                  const float* aux, const float* P, float* Q, int max_rank, cudaStream_t stream);
 // M_hat = P Q^T written into the bucket.  M = G + remembered error is formed on the fly
@@ -119,10 +121,14 @@ int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, i
 // Record nmats + i describes the sketch of matrix i; its q_off is where Z_i / Y_i live.
 int conef_sketch_project(const ConefMat* mats, int nmats, int max_cols, const int32_t* tables,
                          float* qz, float scale, int unproject, cudaStream_t stream);
-// Per matrix: T (rows_t x c1) += coef * X (rows_t x c2) * (L (rows_l x c2)^T Rm (rows_l x c1)).
+// Per matrix: T (rows_t x c1) += sum over up to two terms of coef_t * X_t (rows_t x c2_t) * (L_t^T Rm_t).
 // Used by the low-rank error store, whose factors enter PowerSGD's products as small corrections.
-int conef_lowrank_correct(const ConefCorr* table, int nmats, float* T, const float* X, const float* L,
-                          const float* Rm, float coef, cudaStream_t stream);
+// reduce_tiles chunk rows_l, apply_tiles chunk rows_t (int2 {matrix, chunk of 512 rows});
+// cbuf: scratch of nmats * 2 * 1024 floats.
+int conef_lowrank_correct(const ConefCorr* table, int nmats, const int2* reduce_tiles, int n_reduce,
+                          const int2* apply_tiles, int n_apply, float* T, const float* X0, const float* L0,
+                          const float* R0, float coef0, const float* X1, const float* L1, const float* R1,
+                          float coef1, float* cbuf, cudaStream_t stream);
 // Philox-keyed standard normal fill: element e of the buffer depends only on
 // (seed, e), so every rank generates the same Q without communication.
 int conef_fill_normal(float* buf, long long numel, uint64_t seed, cudaStream_t stream);

@@ -13,7 +13,7 @@
 // Replaces, per matrix and per step, of the reference (communication/powerSGD_hook.py):
 //   :409  DenseCS.query        -> never materialised (see above)
 //   :497  torch.matmul(M, Q)   -> k_psgd_p
-//   :12-43 _orthogonalize      -> k_orthogonalize (all matrices of the bucket, one launch)
+//   :12-43 _orthogonalize      -> k_gram + k_qr_apply (csrc/orth.cu; all matrices of the bucket per launch)
 //   :531  torch.matmul(M^T, P) -> k_psgd_q
 //   :550  torch.matmul(P, Q^T), :558/:563 residual, CountSketch.py:27-67 update
 //                              -> k_psgd_decompress (one pass, residual kept in registers)
@@ -102,113 +102,6 @@ extern "C" int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles,
 }
 
 // ---------------------------------------------------------------------------
-// Batched Gram-Schmidt: one CTA per matrix, all matrices of the bucket in one
-// launch.  Per column: one reduction pass (norm and the dot products with all
-// later columns at once) and one update pass.  With world > 1 the CTA first
-// sums the peers' copies of its block (fused all-reduce over peer memory).
-constexpr int O_THREADS = 512;
-constexpr int O_MAXR = 32;
-
-__global__ void __launch_bounds__(O_THREADS)
-k_orthogonalize(const ConefMat* __restrict__ mats, int which, float* __restrict__ buf, float eps,
-                const float* const* __restrict__ peer_bufs, const uint32_t* __restrict__ flags, int world,
-                uint32_t epoch, int* __restrict__ status, long long spin_limit, float* __restrict__ packed,
-                int packed_np) {
-  __shared__ float red[O_MAXR][17];   // per-warp partials: [column][warp]
-  __shared__ float dots[O_MAXR];
-  __shared__ int ok;
-  const ConefMat M = mats[blockIdx.x];
-  const int rows = which == 0 ? M.n : M.m;
-  const int r = M.r;
-  const size_t off = which == 0 ? M.p_off : M.q_off;
-  float* a = buf + off;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const size_t total = (size_t)rows * r;
-
-  if (world > 1) {
-    if (tid == 0) {
-      ok = wait_flags_bounded(flags, world, epoch, spin_limit) ? 1 : 0;
-      if (!ok) atomicExch(status, CONEF_STATUS_FLAG_TIMEOUT);
-    }
-    __syncthreads();
-    if (!ok) return;  // leave the local values untouched; the host raises
-    for (size_t i = tid; i < total; i += O_THREADS) {
-      float s = 0.f;
-      for (int p = 0; p < world; ++p) s += ld_relaxed_sys_f32(peer_bufs[p] + off + i);
-      a[i] = s;
-    }
-    __syncthreads();
-  }
-
-  for (int c = 0; c < r; ++c) {
-    // pass 1: dots[d] = <col c, col d> for d >= c
-    float part[O_MAXR];
-#pragma unroll
-    for (int d = 0; d < O_MAXR; ++d) part[d] = 0.f;
-    for (int i = tid; i < rows; i += O_THREADS) {
-      const float* rowp = a + (size_t)i * r;
-      const float vc = rowp[c];
-#pragma unroll
-      for (int d = 0; d < O_MAXR; ++d)
-        if (d >= c && d < r) part[d] = fmaf(vc, rowp[d], part[d]);
-    }
-#pragma unroll
-    for (int d = 0; d < O_MAXR; ++d) {
-      if (d >= c && d < r) {
-        const float s = warp_sum(part[d]);
-        if (lane == 0) red[d][warp] = s;
-      }
-    }
-    __syncthreads();
-    if (tid < r && tid >= c) {
-      float s = 0.f;
-      for (int w = 0; w < O_THREADS / 32; ++w) s += red[tid][w];
-      dots[tid] = s;
-    }
-    __syncthreads();
-    // pass 2: col c /= (norm + eps); col d -= <q_c, col d> q_c
-    const float norm = sqrtf(dots[c]);
-    const float inv = 1.f / (norm + eps);
-    for (int i = tid; i < rows; i += O_THREADS) {
-      float* rowp = a + (size_t)i * r;
-      const float qc = rowp[c] * inv;
-      rowp[c] = qc;
-      for (int d = c + 1; d < r; ++d) rowp[d] -= (dots[d] * inv) * qc;
-    }
-    __syncthreads();
-  }
-  if (packed != nullptr) {
-    float* pk = packed + (which == 0 ? M.ppk_off : M.qpk_off);
-    for (size_t i = tid; i < total; i += O_THREADS) {
-      const long long row = i / r;
-      const int c = (int)(i - row * r);
-      pk[conef_packed_offset(row, c, packed_np)] = a[i];
-    }
-  }
-}
-
-extern "C" int conef_orthogonalize(const ConefMat* mats, int nmats, int which, float* buf, float eps,
-                                   const float* const* peer_bufs, const uint32_t* flags, int world,
-                                   uint32_t epoch, int* status, long long spin_limit,
-                                   cudaStream_t stream) {
-  if (nmats <= 0) return 0;
-  k_orthogonalize<<<nmats, O_THREADS, 0, stream>>>(mats, which, buf, eps, peer_bufs, flags, world, epoch,
-                                                  status, spin_limit, nullptr, 0);
-  CONEF_CHECK_LAUNCH("k_orthogonalize");
-  return 0;
-}
-
-extern "C" int conef_orthogonalize_packed(const ConefMat* mats, int nmats, int which, float* buf, float eps,
-                                          const float* const* peer_bufs, const uint32_t* flags, int world,
-                                          uint32_t epoch, int* status, long long spin_limit, float* packed,
-                                          int packed_np, cudaStream_t stream) {
-  if (nmats <= 0) return 0;
-  k_orthogonalize<<<nmats, O_THREADS, 0, stream>>>(mats, which, buf, eps, peer_bufs, flags, world, epoch,
-                                                  status, spin_limit, packed, packed_np);
-  CONEF_CHECK_LAUNCH("k_orthogonalize");
-  return 0;
-}
-
 // Packed copies of the small operands for the tensor-core kernel (layout: conef_packed_offset).
 __global__ void k_pack_small(const ConefMat* __restrict__ mats, int which, const float* __restrict__ src,
                              float* __restrict__ dst, int np) {
@@ -491,60 +384,5 @@ extern "C" int conef_fill_normal(float* buf, long long numel, uint64_t seed, cud
   const long long quads = (numel + 3) / 4;
   k_fill_normal<<<(unsigned)((quads + 255) / 256), 256, 0, stream>>>(buf, numel, seed);
   CONEF_CHECK_LAUNCH("k_fill_normal");
-  return 0;
-}
-
-// ---------------------------------------------------------------------------
-// Small-factor corrections of the low-rank error store: per matrix
-//   T (rows_t x c1) += coef * X (rows_t x c2) * ( L (rows_l x c2)^T  Rm (rows_l x c1) )
-// One CTA per matrix: the (c2 x c1) product is reduced over rows_l in shared memory, then
-// applied to every row of T.  All operands are tall-skinny factors (c1, c2 <= 32).
-constexpr int C_THREADS = 256;
-
-__global__ void __launch_bounds__(C_THREADS)
-k_lowrank_correct(const ConefCorr* __restrict__ table, float* __restrict__ Tb, const float* __restrict__ Xb,
-                  const float* __restrict__ Lb, const float* __restrict__ Rb, float coef) {
-  __shared__ float C[32 * 32];
-  const ConefCorr K = table[blockIdx.x];
-  const int c1 = K.c1, c2 = K.c2, pairs = c1 * c2;
-  const float* L = Lb + K.l_off;
-  const float* Rm = Rb + K.r_off;
-  for (int i = threadIdx.x; i < pairs; i += C_THREADS) C[i] = 0.f;
-  __syncthreads();
-  if (pairs <= C_THREADS) {
-    const int groups = C_THREADS / pairs;
-    const int g = threadIdx.x / pairs, pr = threadIdx.x - g * pairs;
-    if (g < groups) {
-      const int a = pr / c1, b = pr - a * c1;
-      float acc = 0.f;
-      for (int i = g; i < K.rows_l; i += groups) acc = fmaf(L[(size_t)i * c2 + a], Rm[(size_t)i * c1 + b], acc);
-      atomicAdd(&C[pr], acc);
-    }
-  } else {
-    for (int pr = threadIdx.x; pr < pairs; pr += C_THREADS) {
-      const int a = pr / c1, b = pr - a * c1;
-      float acc = 0.f;
-      for (int i = 0; i < K.rows_l; ++i) acc = fmaf(L[(size_t)i * c2 + a], Rm[(size_t)i * c1 + b], acc);
-      C[pr] = acc;
-    }
-  }
-  __syncthreads();
-  float* T = Tb + K.t_off;
-  const float* X = Xb + K.x_off;
-  const size_t total = (size_t)K.rows_t * c1;
-  for (size_t e = threadIdx.x; e < total; e += C_THREADS) {
-    const size_t i = e / c1;
-    const int b = (int)(e - i * c1);
-    float acc = 0.f;
-    for (int a = 0; a < c2; ++a) acc = fmaf(X[i * c2 + a], C[a * c1 + b], acc);
-    T[e] += coef * acc;
-  }
-}
-
-extern "C" int conef_lowrank_correct(const ConefCorr* table, int nmats, float* T, const float* X, const float* L,
-                                     const float* Rm, float coef, cudaStream_t stream) {
-  if (nmats <= 0) return 0;
-  k_lowrank_correct<<<nmats, C_THREADS, 0, stream>>>(table, T, X, L, Rm, coef);
-  CONEF_CHECK_LAUNCH("k_lowrank_correct");
   return 0;
 }

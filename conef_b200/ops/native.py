@@ -40,9 +40,10 @@ BLK_DTYPE = np.dtype(
 LAMB_DTYPE = np.dtype(
     [("p", "<u8"), ("g", "<u8"), ("m", "<u8"), ("v", "<u8"), ("numel", "<i8"),
      ("weight_decay", "<f4"), ("pad", "<i4")], align=True)
-CORR_DTYPE = np.dtype([("t_off", "<i8"), ("x_off", "<i8"), ("l_off", "<i8"), ("r_off", "<i8"),
-                       ("rows_t", "<i4"), ("rows_l", "<i4"), ("c1", "<i4"), ("c2", "<i4")], align=True)
-assert CORR_DTYPE.itemsize == 48
+CORR_DTYPE = np.dtype([("t_off", "<i8"), ("x_off", "<i8", (2,)), ("l_off", "<i8", (2,)), ("r_off", "<i8", (2,)),
+                       ("rows_t", "<i4"), ("rows_l", "<i4"), ("c1", "<i4"), ("nterms", "<i4"),
+                       ("c2", "<i4", (2,))], align=True)
+assert CORR_DTYPE.itemsize == 80
 assert MAT_DTYPE.itemsize == 88 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.itemsize == 72
 assert LAMB_DTYPE.itemsize == 48
 
@@ -57,15 +58,15 @@ _SIGNATURES = {
     "conef_sketch3_update": ([vp] * 7 + [C.c_int, C.c_int, C.c_int, C.c_float, vp], C.c_int),
     "conef_psgd_p": ([vp, vp, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, vp], C.c_int),
     "conef_sketch_project": ([vp, C.c_int, C.c_int, vp, vp, C.c_float, C.c_int, vp], C.c_int),
-    "conef_orthogonalize": ([vp, C.c_int, C.c_int, vp, C.c_float, vp, vp, C.c_int, C.c_uint32, vp, c_ll, vp], C.c_int),
     "conef_psgd_q": ([vp, vp, C.c_int, vp, vp, vp, vp, C.c_int, vp], C.c_int),
-    "conef_orthogonalize_packed": ([vp, C.c_int, C.c_int, vp, C.c_float, vp, vp, C.c_int, C.c_uint32, vp, c_ll, vp,
-                                    C.c_int, vp], C.c_int),
+    "conef_orthogonalize_packed": ([vp, vp, C.c_int, C.c_int, C.c_int, vp, C.c_float, vp, vp, C.c_int, C.c_uint32,
+                                    vp, c_ll, vp, C.c_int, vp, vp], C.c_int),
     "conef_pack_small": ([vp, C.c_int, C.c_int, vp, vp, C.c_int, vp], C.c_int),
     "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
                                C.c_float, C.c_int, C.c_int, C.c_size_t, vp], C.c_int),
     "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),
-    "conef_lowrank_correct": ([vp, C.c_int, vp, vp, vp, vp, C.c_float, vp], C.c_int),
+    "conef_lowrank_correct": ([vp, C.c_int, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_float, vp, vp, vp,
+                               C.c_float, vp, vp], C.c_int),
     "conef_tc_supported": ([], C.c_int),
     "conef_tc_encode_maps": ([vp, C.c_int, vp, vp, vp, vp], C.c_int),
     "conef_psgd_tc": ([C.c_int, vp, vp, vp, C.c_int, vp, vp, C.c_int, vp, vp], C.c_int),
@@ -95,7 +96,7 @@ _OPTIONAL = {}
 # How many kernels one call of an entry point enqueues (memsets not counted);
 # everything not listed launches exactly one.  Host-only entry points launch none.
 _KERNELS_PER_CALL = {
-    "conef_lamb_step": 3, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
+    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_lowrank_correct": 2, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
     "conef_ipc_get_handle": 0, "conef_ipc_open_handle": 0, "conef_ipc_close_handle": 0,
     "conef_cpu_hash_table": 0, "conef_cpu_sketch_query": 0, "conef_cpu_sketch_update": 0,
     "conef_cpu_gram_schmidt": 0,

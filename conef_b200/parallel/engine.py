@@ -262,6 +262,14 @@ class PowerSGDEngine(_EngineBase):
         self.mats_dev = native.upload_struct_array(mats, dev) if nrec else None
         self.tables = torch.cat(table_chunks) if table_chunks else None
         self.counts = torch.cat(count_chunks) if count_chunks else None
+        # 512-row chunks for the row-parallel Gram-Schmidt and correction kernels
+        OC = 512
+        chunk = lambda ks, field: [(k, c) for k in ks for c in range(math.ceil(int(mats[k][field]) / OC))]
+        tl = lambda lst: (self._tiles(lst), len(lst))
+        self.orth_tiles = {(0, "grad"): tl(chunk(range(nm), "n")), (1, "grad"): tl(chunk(range(nm), "m")),
+                           (0, "err"): tl(chunk(range(nm, nrec), "n") if self.lowrank else [])}
+        self.chunks_n, self.chunks_m = tl(chunk(range(nm), "n")), tl(chunk(range(nm), "m"))
+        self.gram = torch.zeros(max(nrec, 1) * 2 * 1024, device=dev, dtype=torch.float32)
 
         # decompress: rows per CTA in {8, 4, 2, 1}: the most that fit in shared memory (two
         # copies of the sketch rows) while still giving every SM a few CTAs
@@ -387,35 +395,63 @@ class PowerSGDEngine(_EngineBase):
         self.q_zero = self.fused_err or self.use_tc or bool(recs["q_atomic"].any()) if nrec else False
 
     def _build_corrections(self) -> None:
-        """Per-matrix offset tables of the six small-factor corrections of the low-rank store.
+        """Per-matrix offset tables of the four small-factor corrections of the low-rank store.
         Buffers: ``pu`` = [P | U'], ``u_old`` = U, ``qz`` = [Q | V], ``qz2`` = [. | V']."""
         nm, recs, plan = self.nm, self.mats_host, self.plan
 
         def table(rows):
             arr = np.zeros(nm, dtype=native.CORR_DTYPE)
             for k in range(nm):
-                arr[k] = rows(recs[k], recs[nm + k])
+                t_off, rows_t, rows_l, c1, terms = rows(recs[k], recs[nm + k])
+                rec = arr[k]
+                rec["t_off"], rec["rows_t"], rec["rows_l"], rec["c1"], rec["nterms"] = t_off, rows_t, rows_l, c1, len(terms)
+                for i, (x, l, r, c2) in enumerate(terms):
+                    rec["x_off"][i], rec["l_off"][i], rec["r_off"][i], rec["c2"][i] = x, l, r, c2
             return native.upload_struct_array(arr, self.device)
-        uo = lambda e: int(e["p_off"]) - plan.total_p          # offset inside u_old
-        n_, m_, r_, k_ = (lambda g: int(g["n"])), (lambda g: int(g["m"])), (lambda g: int(g["r"])), (lambda e: int(e["r"]))
+        I = lambda v: int(v)
+        uo = lambda e: I(e["p_off"]) - plan.total_p          # offset inside u_old
         self.corr = {
-            # P += a U (V^T Q)            T = P (pu / symm)   X = U (u_old)   L = V (qz)    Rm = Q (qz)
-            "p": table(lambda g, e: (int(g["p_off"]), uo(e), int(e["q_off"]), int(g["q_off"]), n_(g), m_(g), r_(g), k_(e))),
-            # Q' += a V (U^T P)           T = Q' (q_target)   X = V (qz)      L = U (u_old) Rm = P (pu)
-            "q": table(lambda g, e: (int(g["q_off"]), int(e["q_off"]), uo(e), int(g["p_off"]), m_(g), n_(g), r_(g), k_(e))),
-            # A1 += (a+b) U (V^T V)       T = A1 (pu)         X = U (u_old)   L = V (qz)    Rm = V (qz)
-            "u1": table(lambda g, e: (int(e["p_off"]), uo(e), int(e["q_off"]), int(e["q_off"]), n_(g), m_(g), k_(e), k_(e))),
-            # A1 -= P (Q^T V)             T = A1 (pu)         X = P (pu)      L = Q (qz)    Rm = V (qz)
-            "u2": table(lambda g, e: (int(e["p_off"]), int(g["p_off"]), int(g["q_off"]), int(e["q_off"]), n_(g), m_(g), k_(e), r_(g))),
-            # A2 += (a+b) V (U^T U')      T = A2 (qz2)        X = V (qz)      L = U (u_old) Rm = U' (pu)
-            "v1": table(lambda g, e: (int(e["q_off"]), int(e["q_off"]), uo(e), int(e["p_off"]), m_(g), n_(g), k_(e), k_(e))),
-            # A2 -= Q (P^T U')            T = A2 (qz2)        X = Q (qz)      L = P (pu)    Rm = U' (pu)
-            "v2": table(lambda g, e: (int(e["q_off"]), int(g["q_off"]), int(g["p_off"]), int(e["p_off"]), m_(g), n_(g), k_(e), r_(g))),
+            # P += a U (V^T Q):   T = P,  X = U (u_old), L = V (qz), Rm = Q (qz)
+            "p": table(lambda g, e: (I(g["p_off"]), I(g["n"]), I(g["m"]), I(g["r"]),
+                                     [(uo(e), I(e["q_off"]), I(g["q_off"]), I(e["r"]))])),
+            # Q' += a V (U^T P):  T = Q', X = V (qz), L = U (u_old), Rm = P (pu)
+            "q": table(lambda g, e: (I(g["q_off"]), I(g["m"]), I(g["n"]), I(g["r"]),
+                                     [(I(e["q_off"]), uo(e), I(g["p_off"]), I(e["r"]))])),
+            # G V += (a+b) U (V^T V) - P (Q^T V):  T = pu tail; term 0: X = U (u_old), L = V, Rm = V (qz);
+            #                                      term 1: X = P (pu), L = Q (qz), Rm = V (qz)
+            "u": table(lambda g, e: (I(e["p_off"]), I(g["n"]), I(g["m"]), I(e["r"]),
+                                     [(uo(e), I(e["q_off"]), I(e["q_off"]), I(e["r"])),
+                                      (I(g["p_off"]), I(g["q_off"]), I(e["q_off"]), I(g["r"]))])),
+            # G^T U' += (a+b) V (U^T U') - Q (P^T U'):  T = qz2 tail; term 0: X = V (qz), L = U (u_old), Rm = U' (pu);
+            #                                           term 1: X = Q (qz), L = P (pu), Rm = U' (pu)
+            "v": table(lambda g, e: (I(e["q_off"]), I(g["m"]), I(g["n"]), I(e["r"]),
+                                     [(I(e["q_off"]), uo(e), I(e["p_off"]), I(e["r"])),
+                                      (I(g["q_off"]), I(g["p_off"]), I(e["p_off"]), I(g["r"]))])),
         }
+        self.cbuf = torch.zeros(max(nm, 1) * 2 * 1024, device=self.device, dtype=torch.float32)
 
-    def _correct(self, name, T, X, L, Rm, coef, st) -> None:
-        native.check(self.lib.conef_lowrank_correct(self.corr[name].data_ptr(), self.nm, T.data_ptr(), X.data_ptr(),
-                                                    L.data_ptr(), Rm.data_ptr(), float(coef), st), f"lowrank_correct({name})")
+    def _correct(self, name, T, terms, st) -> None:
+        """``terms``: one or two ``(X, L, Rm, coef)``; reductions run over rows of L, updates over rows of T."""
+        over_n = name in ("q", "v")       # these reduce over the n rows and update m rows
+        red = self.chunks_n if over_n else self.chunks_m
+        app = self.chunks_m if over_n else self.chunks_n
+        (x0, l0, r0, c0) = terms[0]
+        (x1, l1, r1, c1) = terms[1] if len(terms) > 1 else (x0, l0, r0, 0.0)
+        native.check(self.lib.conef_lowrank_correct(
+            self.corr[name].data_ptr(), self.nm, red[0].data_ptr(), red[1], app[0].data_ptr(), app[1], T.data_ptr(),
+            x0.data_ptr(), l0.data_ptr(), r0.data_ptr(), float(c0), x1.data_ptr(), l1.data_ptr(), r1.data_ptr(),
+            float(c1), self.cbuf.data_ptr(), st), f"lowrank_correct({name})")
+
+    def _orth(self, which: int, subset: str, buf: torch.Tensor, eps: float, st, peers=0, flags=0, world=1, epoch=0,
+              packed: bool = False) -> None:
+        tiles, n = self.orth_tiles[(which, subset)]
+        if not n:
+            return
+        native.check(self.lib.conef_orthogonalize_packed(
+            self.mats_dev.data_ptr(), tiles.data_ptr(), n, len(self.mats_host), which, buf.data_ptr(), float(eps),
+            peers, flags, world, epoch, self.status.data_ptr(), DEFAULT_SPIN_LIMIT if world > 1 else 0,
+            native.ptr(self.ppk if which == 0 else self.qpk) if (packed and self.use_tc) else 0, self.np_cols,
+            self.gram.data_ptr(), st), "orthogonalize")
 
     def _tiles(self, tiles) -> Optional[torch.Tensor]:
         if not tiles:
@@ -558,8 +594,7 @@ class PowerSGDEngine(_EngineBase):
                 seed = int(state.rng.randint(1_000_000_000))
                 native.check(lib.conef_fill_normal(qmem.data_ptr(), qmem.numel(), seed, st), "fill_normal")
             if self.variant != "unbiased":
-                native.check(lib.conef_orthogonalize(self.mats_dev.data_ptr(), nm, 1, qmem.data_ptr(), eps,
-                                                     0, 0, 1, 0, self.status.data_ptr(), 0, st), "orth_q")
+                self._orth(1, "grad", self.qz, eps, st)
             if self.ef_mode == native.EF_SKETCH:
                 # Z = alpha * H^T Q, so that the sketch records contribute alpha * unsketch(S) Q to P
                 self.qz[plan.total_q :].zero_()
@@ -579,7 +614,7 @@ class PowerSGDEngine(_EngineBase):
                 p_target[: plan.total_p + self.total_u].zero_()
             self._launch_p(wp, aux, self.qz, p_target, st)
             if self.lowrank:
-                self._correct("p", p_target, self.u_old, self.qz, self.qz, alpha, st)     # P += a U (V^T Q)
+                self._correct("p", p_target, [(self.u_old, self.qz, self.qz, alpha)], st)     # P += a U (V^T Q)
 
         # 2. all-reduce of staging and P ; Gram-Schmidt of P
         orth_p = self.variant != "unbiased"
@@ -587,10 +622,8 @@ class PowerSGDEngine(_EngineBase):
             self.epoch += 1
             native.check(lib.conef_signal_peers(symm.peer_flags_dev(), ws, self.rank, self.epoch, st), "signal")
             if nm and orth_p:
-                native.check(lib.conef_orthogonalize_packed(
-                    self.mats_dev.data_ptr(), nm, 0, pmem.data_ptr(), eps, symm.peer_ptrs_dev(slot, 1),
-                    symm.flags_ptr(), ws, self.epoch, self.status.data_ptr(), DEFAULT_SPIN_LIMIT,
-                    native.ptr(self.ppk) if self.use_tc else 0, self.np_cols, st), "orth_p")
+                self._orth(0, "grad", self.pu, eps, st, symm.peer_ptrs_dev(slot, 1), symm.flags_ptr(), ws, self.epoch,
+                           packed=True)
             elif nm:
                 native.check(lib.conef_allreduce_oneshot(
                     pmem.data_ptr(), symm.peer_ptrs_dev(slot, 1), 0, symm.flags_ptr(), ws, self.rank, self.epoch,
@@ -613,9 +646,7 @@ class PowerSGDEngine(_EngineBase):
                     self.segs_dev.data_ptr(), len(plan.segs), wp, 0, 1, stage.data_ptr(), 1.0 / ws,
                     native.ptr(dense_err), plan.total_unc, st), "scatter_segments")
             if nm and orth_p:
-                native.check(lib.conef_orthogonalize_packed(
-                    self.mats_dev.data_ptr(), nm, 0, pmem.data_ptr(), eps, 0, 0, 1, 0, self.status.data_ptr(), 0,
-                    native.ptr(self.ppk) if self.use_tc else 0, self.np_cols, st), "orth_p")
+                self._orth(0, "grad", self.pu, eps, st, packed=True)
 
         if nm:
             if self.lowrank and symm:
@@ -628,7 +659,7 @@ class PowerSGDEngine(_EngineBase):
                     if self.q_zero:
                         q_target[: plan.total_q].zero_()         # the V blocks behind Q stay as they are
                     self._launch_q(wp, aux, self.pu, q_target, st, packed=True, subset="grad")
-                    self._correct("q", q_target, self.qz, self.u_old, self.pu, alpha, st)   # Q' += a V (U^T P)
+                    self._correct("q", q_target, [(self.qz, self.u_old, self.pu, alpha)], st)   # Q' += a V (U^T P)
                 else:
                     if self.q_zero:
                         q_target.zero_()
@@ -702,18 +733,14 @@ class PowerSGDEngine(_EngineBase):
     def _refresh_lowrank(self, wp, alpha, beta, st) -> None:
         """One power-iteration step of the error factors on T = G + (a+b) U V^T - P Q^T:
         U' = orth(T V) with G V already behind the P blocks, then V' = T^T U'."""
-        lib, plan, nm = self.lib, self.plan, self.nm
-        rec_bytes = native.MAT_DTYPE.itemsize
-        err_recs = self.mats_dev.data_ptr() + nm * rec_bytes
-        self._correct("u1", self.pu, self.u_old, self.qz, self.qz, alpha + beta, st)    # += (a+b) U (V^T V)
-        self._correct("u2", self.pu, self.pu, self.qz, self.qz, -1.0, st)               # -= P (Q^T V)
-        native.check(lib.conef_orthogonalize_packed(
-            err_recs, nm, 0, self.pu.data_ptr(), 1e-12, 0, 0, 1, 0, self.status.data_ptr(), 0,
-            native.ptr(self.ppk) if self.use_tc else 0, self.np_cols, st), "orth_u")
+        plan = self.plan
+        # G V += (a+b) U (V^T V) - P (Q^T V)
+        self._correct("u", self.pu, [(self.u_old, self.qz, self.qz, alpha + beta), (self.pu, self.qz, self.qz, -1.0)], st)
+        self._orth(0, "err", self.pu, 1e-12, st, packed=True)
         self.qz2.zero_()
         self._launch_q(wp, 0, self.pu, self.qz2, st, packed=True, subset="err")          # G^T U'
-        self._correct("v1", self.qz2, self.qz, self.u_old, self.pu, alpha + beta, st)   # += (a+b) V (U^T U')
-        self._correct("v2", self.qz2, self.qz, self.pu, self.pu, -1.0, st)              # -= Q (P^T U')
+        # G^T U' += (a+b) V (U^T U') - Q (P^T U')
+        self._correct("v", self.qz2, [(self.qz, self.u_old, self.pu, alpha + beta), (self.qz, self.pu, self.pu, -1.0)], st)
         self.u_old.copy_(self.pu[plan.total_p : plan.total_p + self.total_u])
         self.qz[plan.total_q :].copy_(self.qz2[plan.total_q :])
 

@@ -146,10 +146,11 @@ def main():
         if tc == "1":
             continue
         if want("orth"):
-            t = _time(lambda: native.check(lib.conef_orthogonalize(eng.mats_dev.data_ptr(), len(plan.mats), 0,
-                                                                   pmem.data_ptr(), 0.0, 0, 0, 1, 0,
-                                                                   eng.status.data_ptr(), 0, st)), args.iters)
-            record("orthogonalize(P)", t, 8 * plan.total_p, "latency bound: 2r passes over P")
+            def run_orth():
+                eng.pu.normal_()
+                eng._orth(0, "grad", eng.pu, 0.0, st)
+            t = _time(run_orth, args.iters)
+            record("orthogonalize(P)", t, 24 * plan.total_p, "3 row-parallel passes over P (read + write)")
         if want("decompress"):
             t = _time(lambda: native.check(lib.conef_psgd_decompress(
                 eng.mats_dev.data_ptr(), eng.d_tiles.data_ptr(), eng.n_d_tiles, eng.d_rows, buf.data_ptr(),

@@ -131,25 +131,32 @@ def test_oneshot_allreduce_math_with_preset_flags():
 
 
 def test_orthogonalize_kernel():
+    """Row-parallel Gram-Schmidt (Gram matrix, applied twice) against the column-by-column oracle."""
     torch.manual_seed(3)
-    shapes = [(1000, 4), (37, 3), (5000, 8), (9, 1)]
+    shapes = [(1000, 4), (37, 3), (5000, 8), (9, 1), (30528, 8), (700, 20)]
     mats = np.zeros(len(shapes), dtype=native.MAT_DTYPE)
-    off = 0
+    off, tiles = 0, []
     for k, (n, r) in enumerate(shapes):
         mats[k]["n"], mats[k]["m"], mats[k]["r"], mats[k]["p_off"] = n, 1, r, off
         off += n * r
+        tiles += [(k, c) for c in range((n + 511) // 512)]
     flat = torch.randn(off)
     dev = flat.to(DEV)
     md = native.upload_struct_array(mats, torch.device(DEV))
+    td = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    gram = torch.zeros(2 * len(shapes) * 1024, device=DEV)
     status = torch.zeros(4, dtype=torch.int32, device=DEV)
-    native.check(native.lib().conef_orthogonalize(md.data_ptr(), len(shapes), 0, dev.data_ptr(), 0.0, 0, 0, 1, 0,
-                                                  status.data_ptr(), 0, _st()))
+    native.check(native.lib().conef_orthogonalize_packed(md.data_ptr(), td.data_ptr(), len(tiles), len(shapes), 0,
+                                                         dev.data_ptr(), 0.0, 0, 0, 1, 0, status.data_ptr(), 0, 0, 16,
+                                                         gram.data_ptr(), _st()))
     got = dev.cpu()
     off = 0
     for n, r in shapes:
         want = flat[off : off + n * r].view(n, r).clone()
         ref.gram_schmidt_ref(want)
-        torch.testing.assert_close(got[off : off + n * r].view(n, r), want, rtol=1e-3, atol=1e-4)
+        g = got[off : off + n * r].view(n, r)
+        torch.testing.assert_close(g, want, rtol=1e-3, atol=1e-4)
+        torch.testing.assert_close(g.t() @ g, torch.eye(r), rtol=0, atol=1e-4)
         off += n * r
 
 
