@@ -99,7 +99,8 @@ int conef_psgd_p(const ConefMat* mats, const int2* tiles, int ntiles, const floa
 // first waits (bounded) until every peer has published `epoch` in flags[peer] and sums the
 // peers' buffers (peer_bufs[0..world)) into `buf`; status[0] becomes non-zero when a wait gives up.
 // packed (nullable): also write the result in the tensor-core operand layout with packed_np columns.
-// gram: scratch of 2 * nrecords * 1024 floats.
+// gram: scratch of 2 * ntiles * 1024 floats.  The result depends only on the input bits (fixed
+// summation order), so ranks that start from the same reduced P end with the same factors.
 int conef_orthogonalize_packed(const ConefMat* mats, const int2* tiles, int ntiles, int nrecords,
                                int which, float* buf, float eps, const float* const* peer_bufs,
                                const uint32_t* flags, int world, uint32_t epoch, int* status,

@@ -24,10 +24,11 @@ constexpr int OC_THREADS = 256;
 constexpr int OC_MAXR = 32;
 constexpr int GRAM_STRIDE = OC_MAXR * OC_MAXR;
 
-// partial[c2 x c1] += L[rows x c2]^T Rm[rows x c1] over `rows` rows, accumulated into shared `Csm`
-// (zeroed by the caller), all threads of the CTA participate.
+// Csm[c2 x c1] = L[rows x c2]^T Rm[rows x c1] over `rows` rows; all threads of the CTA take part.
+// The summation order is fixed (no atomics): every rank must obtain bit-identical factors from
+// bit-identical inputs, otherwise the replicas drift apart.  `scratch` holds OC_THREADS floats.
 __device__ __forceinline__ void pair_reduce(const float* __restrict__ L, const float* __restrict__ Rm, int rows,
-                                            int c2, int c1, float* Csm) {
+                                            int c2, int c1, float* Csm, float* scratch) {
   const int pairs = c1 * c2;
   if (pairs <= OC_THREADS) {
     const int groups = OC_THREADS / pairs;
@@ -36,16 +37,23 @@ __device__ __forceinline__ void pair_reduce(const float* __restrict__ L, const f
       const int a = pr / c1, b = pr - a * c1;
       float acc = 0.f;
       for (int i = g; i < rows; i += groups) acc = fmaf(L[(size_t)i * c2 + a], Rm[(size_t)i * c1 + b], acc);
-      atomicAdd(&Csm[pr], acc);
+      scratch[g * pairs + pr] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x < pairs) {
+      float acc = 0.f;
+      for (int gg = 0; gg < groups; ++gg) acc += scratch[gg * pairs + threadIdx.x];
+      Csm[threadIdx.x] = acc;
     }
   } else {
     for (int pr = threadIdx.x; pr < pairs; pr += OC_THREADS) {
       const int a = pr / c1, b = pr - a * c1;
       float acc = 0.f;
       for (int i = 0; i < rows; ++i) acc = fmaf(L[(size_t)i * c2 + a], Rm[(size_t)i * c1 + b], acc);
-      Csm[pr] += acc;
+      Csm[pr] = acc;
     }
   }
+  __syncthreads();
 }
 
 __global__ void __launch_bounds__(OC_THREADS)
@@ -53,6 +61,7 @@ k_gram(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int wh
        float* __restrict__ gram, const float* const* __restrict__ peer_bufs, const uint32_t* __restrict__ flags,
        int world, uint32_t epoch, int* __restrict__ status, long long spin_limit) {
   __shared__ float Csm[GRAM_STRIDE];
+  __shared__ float scratch[OC_THREADS];
   __shared__ int ok;
   const int2 t = tiles[blockIdx.x];
   const ConefMat M = mats[t.x];
@@ -73,12 +82,10 @@ k_gram(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int wh
       a[i] = s;
     }
   }
-  for (int i = threadIdx.x; i < r * r; i += OC_THREADS) Csm[i] = 0.f;
   __syncthreads();
-  pair_reduce(a, a, rows, r, r, Csm);
-  __syncthreads();
-  float* g = gram + (size_t)t.x * GRAM_STRIDE;
-  for (int i = threadIdx.x; i < r * r; i += OC_THREADS) atomicAdd(g + i, Csm[i]);
+  pair_reduce(a, a, rows, r, r, Csm, scratch);
+  float* g = gram + (size_t)blockIdx.x * GRAM_STRIDE;      // one partial per tile, summed in order by k_qr_apply
+  for (int i = threadIdx.x; i < r * r; i += OC_THREADS) g[i] = Csm[i];
 }
 
 __global__ void __launch_bounds__(OC_THREADS)
@@ -89,18 +96,21 @@ k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
   __shared__ float R[OC_MAXR][OC_MAXR + 1];
   __shared__ float Ri[OC_MAXR][OC_MAXR + 1];
   __shared__ float Csm[GRAM_STRIDE];
+  __shared__ float scratch[OC_THREADS];
   const int2 t = tiles[blockIdx.x];
   const ConefMat M = mats[t.x];
   const int rows_total = which == 0 ? M.n : M.m, r = M.r;
   const size_t off = (which == 0 ? M.p_off : M.q_off) + (size_t)t.y * OC_ROWS * r;
   const int rows = min(OC_ROWS, rows_total - t.y * OC_ROWS);
   float* a = buf + off;
-  const float* g = gram_in + (size_t)t.x * GRAM_STRIDE;
+  // the tiles of one matrix are consecutive: sum their Gram partials in tile order
+  const int first = blockIdx.x - t.y, count = (rows_total + OC_ROWS - 1) / OC_ROWS;
   for (int i = threadIdx.x; i < r * r; i += OC_THREADS) {
-    G[i / r][i % r] = g[i];
+    float acc = 0.f;
+    for (int c = 0; c < count; ++c) acc += gram_in[(size_t)(first + c) * GRAM_STRIDE + i];
+    G[i / r][i % r] = acc;
     R[i / r][i % r] = 0.f;
     Ri[i / r][i % r] = 0.f;
-    Csm[i] = 0.f;
   }
   __syncthreads();
   if (threadIdx.x < 32) {
@@ -152,23 +162,21 @@ k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
   }
   if (gram_out != nullptr) {
     __syncthreads();
-    pair_reduce(a, a, rows, r, r, Csm);
-    __syncthreads();
-    float* go = gram_out + (size_t)t.x * GRAM_STRIDE;
-    for (int i = threadIdx.x; i < r * r; i += OC_THREADS) atomicAdd(go + i, Csm[i]);
+    pair_reduce(a, a, rows, r, r, Csm, scratch);
+    float* go = gram_out + (size_t)blockIdx.x * GRAM_STRIDE;
+    for (int i = threadIdx.x; i < r * r; i += OC_THREADS) go[i] = Csm[i];
   }
 }
 
-// gram: scratch of 2 * nrecords * 1024 floats (nrecords = size of the mats table).
+// gram: scratch of 2 * ntiles * 1024 floats (one Gram partial per tile and round).
 extern "C" int conef_orthogonalize_packed(const ConefMat* mats, const int2* tiles, int ntiles, int nrecords,
                                           int which, float* buf, float eps, const float* const* peer_bufs,
                                           const uint32_t* flags, int world, uint32_t epoch, int* status,
                                           long long spin_limit, float* packed, int packed_np, float* gram,
                                           cudaStream_t stream) {
   if (ntiles <= 0) return 0;
-  const size_t gbytes = sizeof(float) * (size_t)nrecords * GRAM_STRIDE;
-  float* gram2 = gram + (size_t)nrecords * GRAM_STRIDE;
-  CONEF_CUDA(cudaMemsetAsync(gram, 0, 2 * gbytes, stream));
+  (void)nrecords;
+  float* gram2 = gram + (size_t)ntiles * GRAM_STRIDE;
   k_gram<<<ntiles, OC_THREADS, 0, stream>>>(mats, tiles, which, buf, gram, peer_bufs, flags, world, epoch, status,
                                            spin_limit);
   CONEF_CHECK_LAUNCH("k_gram");
@@ -186,6 +194,7 @@ k_corr_reduce(const ConefCorr* __restrict__ table, const int2* __restrict__ tile
               const float* __restrict__ R0b, const float* __restrict__ L1b, const float* __restrict__ R1b,
               float* __restrict__ cbuf) {
   __shared__ float Csm[GRAM_STRIDE];
+  __shared__ float scratch[OC_THREADS];
   const int2 t = tiles[blockIdx.x];
   const ConefCorr K = table[t.x];
   const int row0 = t.y * OC_ROWS;
@@ -195,10 +204,7 @@ k_corr_reduce(const ConefCorr* __restrict__ table, const int2* __restrict__ tile
     const float* L = (term ? L1b : L0b) + K.l_off[term] + (size_t)row0 * c2;
     const float* Rm = (term ? R1b : R0b) + K.r_off[term] + (size_t)row0 * c1;
     __syncthreads();
-    for (int i = threadIdx.x; i < c1 * c2; i += OC_THREADS) Csm[i] = 0.f;
-    __syncthreads();
-    pair_reduce(L, Rm, rows, c2, c1, Csm);
-    __syncthreads();
+    pair_reduce(L, Rm, rows, c2, c1, Csm, scratch);
     float* c = cbuf + ((size_t)t.x * 2 + term) * GRAM_STRIDE;
     for (int i = threadIdx.x; i < c1 * c2; i += OC_THREADS) atomicAdd(c + i, Csm[i]);
   }

@@ -269,7 +269,8 @@ class PowerSGDEngine(_EngineBase):
         self.orth_tiles = {(0, "grad"): tl(chunk(range(nm), "n")), (1, "grad"): tl(chunk(range(nm), "m")),
                            (0, "err"): tl(chunk(range(nm, nrec), "n") if self.lowrank else [])}
         self.chunks_n, self.chunks_m = tl(chunk(range(nm), "n")), tl(chunk(range(nm), "m"))
-        self.gram = torch.zeros(max(nrec, 1) * 2 * 1024, device=dev, dtype=torch.float32)
+        max_tiles = max((n for _, n in self.orth_tiles.values()), default=1)
+        self.gram = torch.zeros(max(max_tiles, 1) * 2 * 1024, device=dev, dtype=torch.float32)
 
         # decompress: rows per CTA in {8, 4, 2, 1}: the most that fit in shared memory (two
         # copies of the sketch rows) while still giving every SM a few CTAs

@@ -144,7 +144,7 @@ def test_orthogonalize_kernel():
     dev = flat.to(DEV)
     md = native.upload_struct_array(mats, torch.device(DEV))
     td = torch.tensor(tiles, dtype=torch.int32, device=DEV)
-    gram = torch.zeros(2 * len(shapes) * 1024, device=DEV)
+    gram = torch.zeros(2 * len(tiles) * 1024, device=DEV)
     status = torch.zeros(4, dtype=torch.int32, device=DEV)
     native.check(native.lib().conef_orthogonalize_packed(md.data_ptr(), td.data_ptr(), len(tiles), len(shapes), 0,
                                                          dev.data_ptr(), 0.0, 0, 0, 1, 0, status.data_ptr(), 0, 0, 16,
