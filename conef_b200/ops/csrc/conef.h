@@ -189,6 +189,23 @@ int conef_allreduce_oneshot(float* out, const float* const* peer_bufs, uint32_t*
                             cudaStream_t stream);
 int conef_wait_flags(const uint32_t* my_flags, int world, uint32_t epoch, int* status,
                      long long spin_limit, cudaStream_t stream);
+// Variants with `epoch_base` (nullable device word added to `epoch` on the device): a captured
+// launch replayed from a CUDA graph gets a fresh epoch each time without new kernel arguments.
+int conef_signal_peers_ex(uint32_t* const* peer_flags, int world, int rank, uint32_t epoch,
+                          const uint32_t* epoch_base, cudaStream_t stream);
+int conef_allreduce_oneshot_ex(float* out, const float* const* peer_bufs, uint32_t* const* peer_flags,
+                               const uint32_t* my_flags, int world, int rank, uint32_t epoch,
+                               long long numel, float scale, int* status, long long spin_limit,
+                               const uint32_t* epoch_base, cudaStream_t stream);
+int conef_wait_flags_ex(const uint32_t* my_flags, int world, uint32_t epoch, int* status,
+                        long long spin_limit, const uint32_t* epoch_base, cudaStream_t stream);
+int conef_orthogonalize_packed_ex(const ConefMat* mats, const int2* tiles, int ntiles, int nrecords,
+                                  int which, float* buf, float eps, const float* const* peer_bufs,
+                                  const uint32_t* flags, int world, uint32_t epoch, int* status,
+                                  long long spin_limit, float* packed, int packed_np, float* gram,
+                                  const uint32_t* epoch_base, cudaStream_t stream);
+// *word = value (add = 0) or *word += value (add = 1), in stream order.
+int conef_epoch_word(uint32_t* word, uint32_t value, int add, cudaStream_t stream);
 int conef_ipc_get_handle(void* dev_ptr, void* handle_out_64B);
 int conef_ipc_open_handle(const void* handle_64B, void** dev_ptr_out);
 int conef_ipc_close_handle(void* dev_ptr);

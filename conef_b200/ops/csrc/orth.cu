@@ -59,7 +59,8 @@ __device__ __forceinline__ void pair_reduce(const float* __restrict__ L, const f
 __global__ void __launch_bounds__(OC_THREADS)
 k_gram(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int which, float* __restrict__ buf,
        float* __restrict__ gram, const float* const* __restrict__ peer_bufs, const uint32_t* __restrict__ flags,
-       int world, uint32_t epoch, int* __restrict__ status, long long spin_limit) {
+       int world, uint32_t epoch, int* __restrict__ status, long long spin_limit,
+       const uint32_t* __restrict__ epoch_base) {
   __shared__ float Csm[GRAM_STRIDE];
   __shared__ float scratch[OC_THREADS];
   __shared__ int ok;
@@ -71,6 +72,7 @@ k_gram(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int wh
   float* a = buf + off;
   if (world > 1) {
     if (threadIdx.x == 0) {
+      if (epoch_base != nullptr) epoch += *epoch_base;
       ok = wait_flags_bounded(flags, world, epoch, spin_limit) ? 1 : 0;
       if (!ok) atomicExch(status, CONEF_STATUS_FLAG_TIMEOUT);
     }
@@ -169,22 +171,31 @@ k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
 }
 
 // gram: scratch of 2 * ntiles * 1024 floats (one Gram partial per tile and round).
-extern "C" int conef_orthogonalize_packed(const ConefMat* mats, const int2* tiles, int ntiles, int nrecords,
-                                          int which, float* buf, float eps, const float* const* peer_bufs,
-                                          const uint32_t* flags, int world, uint32_t epoch, int* status,
-                                          long long spin_limit, float* packed, int packed_np, float* gram,
-                                          cudaStream_t stream) {
+extern "C" int conef_orthogonalize_packed_ex(const ConefMat* mats, const int2* tiles, int ntiles, int nrecords,
+                                             int which, float* buf, float eps, const float* const* peer_bufs,
+                                             const uint32_t* flags, int world, uint32_t epoch, int* status,
+                                             long long spin_limit, float* packed, int packed_np, float* gram,
+                                             const uint32_t* epoch_base, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
   (void)nrecords;
   float* gram2 = gram + (size_t)ntiles * GRAM_STRIDE;
   k_gram<<<ntiles, OC_THREADS, 0, stream>>>(mats, tiles, which, buf, gram, peer_bufs, flags, world, epoch, status,
-                                           spin_limit);
+                                           spin_limit, epoch_base);
   CONEF_CHECK_LAUNCH("k_gram");
   k_qr_apply<<<ntiles, OC_THREADS, 0, stream>>>(mats, tiles, which, buf, gram, gram2, eps, nullptr, 0);
   CONEF_CHECK_LAUNCH("k_qr_apply");
   k_qr_apply<<<ntiles, OC_THREADS, 0, stream>>>(mats, tiles, which, buf, gram2, nullptr, 0.f, packed, packed_np);
   CONEF_CHECK_LAUNCH("k_qr_apply");
   return 0;
+}
+
+extern "C" int conef_orthogonalize_packed(const ConefMat* mats, const int2* tiles, int ntiles, int nrecords,
+                                          int which, float* buf, float eps, const float* const* peer_bufs,
+                                          const uint32_t* flags, int world, uint32_t epoch, int* status,
+                                          long long spin_limit, float* packed, int packed_np, float* gram,
+                                          cudaStream_t stream) {
+  return conef_orthogonalize_packed_ex(mats, tiles, ntiles, nrecords, which, buf, eps, peer_bufs, flags, world,
+                                       epoch, status, spin_limit, packed, packed_np, gram, nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -16,7 +16,11 @@
 #include <string.h>
 #include "common.cuh"
 
-__global__ void k_signal_peers(uint32_t* const* __restrict__ peer_flags, int world, int rank, uint32_t epoch) {
+// epoch_base (nullable): a device word added to `epoch`, so that a captured launch can be
+// replayed with an epoch that advances on the device.
+__global__ void k_signal_peers(uint32_t* const* __restrict__ peer_flags, int world, int rank, uint32_t epoch,
+                               const uint32_t* __restrict__ epoch_base) {
+  if (epoch_base != nullptr) epoch += *epoch_base;
   // Everything the preceding kernels of this stream wrote must be visible to
   // the peers before the flag: fence at system scope, then release-store.
   __threadfence_system();
@@ -24,25 +28,37 @@ __global__ void k_signal_peers(uint32_t* const* __restrict__ peer_flags, int wor
   if (p < world) st_release_sys(peer_flags[p] + rank, epoch);
 }
 
-extern "C" int conef_signal_peers(uint32_t* const* peer_flags, int world, int rank, uint32_t epoch,
-                                  cudaStream_t stream) {
+extern "C" int conef_signal_peers_ex(uint32_t* const* peer_flags, int world, int rank, uint32_t epoch,
+                                     const uint32_t* epoch_base, cudaStream_t stream) {
   if (world <= 1) return 0;
-  k_signal_peers<<<1, 32, 0, stream>>>(peer_flags, world, rank, epoch);
+  k_signal_peers<<<1, 32, 0, stream>>>(peer_flags, world, rank, epoch, epoch_base);
   CONEF_CHECK_LAUNCH("k_signal_peers");
   return 0;
 }
 
+extern "C" int conef_signal_peers(uint32_t* const* peer_flags, int world, int rank, uint32_t epoch,
+                                  cudaStream_t stream) {
+  return conef_signal_peers_ex(peer_flags, world, rank, epoch, nullptr, stream);
+}
+
 __global__ void k_wait_flags(const uint32_t* __restrict__ my_flags, int world, uint32_t epoch,
-                             int* __restrict__ status, long long spin_limit) {
+                             int* __restrict__ status, long long spin_limit,
+                             const uint32_t* __restrict__ epoch_base) {
+  if (epoch_base != nullptr) epoch += *epoch_base;
   if (threadIdx.x == 0 && !wait_flags_bounded(my_flags, world, epoch, spin_limit))
     atomicExch(status, CONEF_STATUS_FLAG_TIMEOUT);
 }
 
-extern "C" int conef_wait_flags(const uint32_t* my_flags, int world, uint32_t epoch, int* status,
-                                long long spin_limit, cudaStream_t stream) {
-  k_wait_flags<<<1, 32, 0, stream>>>(my_flags, world, epoch, status, spin_limit);
+extern "C" int conef_wait_flags_ex(const uint32_t* my_flags, int world, uint32_t epoch, int* status,
+                                   long long spin_limit, const uint32_t* epoch_base, cudaStream_t stream) {
+  k_wait_flags<<<1, 32, 0, stream>>>(my_flags, world, epoch, status, spin_limit, epoch_base);
   CONEF_CHECK_LAUNCH("k_wait_flags");
   return 0;
+}
+
+extern "C" int conef_wait_flags(const uint32_t* my_flags, int world, uint32_t epoch, int* status,
+                                long long spin_limit, cudaStream_t stream) {
+  return conef_wait_flags_ex(my_flags, world, epoch, status, spin_limit, nullptr, stream);
 }
 
 // signal + wait + reduce in one kernel.  Block 0 publishes the epoch; every
@@ -51,8 +67,9 @@ __global__ void __launch_bounds__(256)
 k_allreduce_oneshot(float* __restrict__ out, const float* const* __restrict__ peer_bufs,
                     uint32_t* const* __restrict__ peer_flags, const uint32_t* __restrict__ my_flags,
                     int world, int rank, uint32_t epoch, long long numel, float scale,
-                    int* __restrict__ status, long long spin_limit) {
+                    int* __restrict__ status, long long spin_limit, const uint32_t* __restrict__ epoch_base) {
   __shared__ int ok;
+  if (epoch_base != nullptr) epoch += *epoch_base;
   if (blockIdx.x == 0 && threadIdx.x < world && peer_flags != nullptr) {
     __threadfence_system();
     st_release_sys(peer_flags[threadIdx.x] + rank, epoch);
@@ -84,18 +101,37 @@ k_allreduce_oneshot(float* __restrict__ out, const float* const* __restrict__ pe
   }
 }
 
-extern "C" int conef_allreduce_oneshot(float* out, const float* const* peer_bufs,
-                                       uint32_t* const* peer_flags, const uint32_t* my_flags, int world,
-                                       int rank, uint32_t epoch, long long numel, float scale,
-                                       int* status, long long spin_limit, cudaStream_t stream) {
+extern "C" int conef_allreduce_oneshot_ex(float* out, const float* const* peer_bufs,
+                                          uint32_t* const* peer_flags, const uint32_t* my_flags, int world,
+                                          int rank, uint32_t epoch, long long numel, float scale, int* status,
+                                          long long spin_limit, const uint32_t* epoch_base, cudaStream_t stream) {
   if (numel <= 0) return 0;
   if (((uintptr_t)out & 15) != 0) { conef_set_error("allreduce_oneshot: output must be 16-byte aligned"); return 2; }
   long long blocks = (numel / 4 + 255) / 256;
   if (blocks < 1) blocks = 1;
   if (blocks > 296) blocks = 296;  // all blocks must be able to wait at once: 2 per SM
   k_allreduce_oneshot<<<(unsigned)blocks, 256, 0, stream>>>(out, peer_bufs, peer_flags, my_flags, world, rank,
-                                                          epoch, numel, scale, status, spin_limit);
+                                                          epoch, numel, scale, status, spin_limit, epoch_base);
   CONEF_CHECK_LAUNCH("k_allreduce_oneshot");
+  return 0;
+}
+
+extern "C" int conef_allreduce_oneshot(float* out, const float* const* peer_bufs,
+                                       uint32_t* const* peer_flags, const uint32_t* my_flags, int world,
+                                       int rank, uint32_t epoch, long long numel, float scale,
+                                       int* status, long long spin_limit, cudaStream_t stream) {
+  return conef_allreduce_oneshot_ex(out, peer_bufs, peer_flags, my_flags, world, rank, epoch, numel, scale,
+                                    status, spin_limit, nullptr, stream);
+}
+
+// The device-side epoch word of captured launches: set it, or advance it by `delta`.
+__global__ void k_epoch_word(uint32_t* word, uint32_t value, int add) {
+  if (threadIdx.x == 0) *word = add ? *word + value : value;
+}
+
+extern "C" int conef_epoch_word(uint32_t* word, uint32_t value, int add, cudaStream_t stream) {
+  k_epoch_word<<<1, 32, 0, stream>>>(word, value, add);
+  CONEF_CHECK_LAUNCH("k_epoch_word");
   return 0;
 }
 

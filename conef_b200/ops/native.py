@@ -48,6 +48,54 @@ assert MAT_DTYPE.itemsize == 88 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.items
 assert LAMB_DTYPE.itemsize == 48
 
 EF_NONE, EF_DENSE, EF_SKETCH, EF_QUANT8 = 0, 1, 2, 3
+PHASE_P, PHASE_Q, PHASE_D, PHASE_ALL = 1, 2, 4, 7
+
+
+class TileList(C.Structure):
+    """Mirror of ``ConefTileList`` (csrc/executor.h)."""
+    _fields_ = [("tiles", C.c_void_p), ("n", C.c_int), ("pad", C.c_int)]
+
+
+class QSet(C.Structure):
+    _fields_ = [("tc", TileList), ("simt", TileList)]
+
+
+class PsgdPlan(C.Structure):
+    """Mirror of ``ConefPsgdPlan`` (csrc/executor.h): field order and types must match."""
+    _fields_ = [
+        ("mats", C.c_void_p),
+        ("nrec", C.c_int), ("nm", C.c_int), ("max_rank", C.c_int), ("np_cols", C.c_int), ("max_cols", C.c_int),
+        ("unbiased", C.c_int), ("ef_mode", C.c_int), ("lowrank", C.c_int),
+        ("use_tc", C.c_int), ("p_zero", C.c_int), ("q_zero", C.c_int),
+        ("tables", C.c_void_p), ("counts", C.c_void_p), ("sketch", C.c_void_p), ("dense_err", C.c_void_p),
+        ("aux", C.c_void_p),
+        ("qz", C.c_void_p), ("total_q", C.c_longlong), ("total_z", C.c_longlong),
+        ("pu", C.c_void_p), ("total_p", C.c_longlong), ("total_u", C.c_longlong),
+        ("u_old", C.c_void_p), ("qz2", C.c_void_p), ("qpk", C.c_void_p), ("ppk", C.c_void_p),
+        ("segs", C.c_void_p), ("nsegs", C.c_int), ("pad0", C.c_int), ("total_unc", C.c_longlong),
+        ("staging", C.c_void_p), ("tc_maps", C.c_void_p),
+        ("tc_p", TileList), ("simt_p", TileList),
+        ("qset_all", QSet), ("qset_grad", QSet), ("qset_err", QSet),
+        ("d_tiles", TileList), ("d_rows", C.c_int), ("pad1", C.c_int), ("d_smem", C.c_size_t),
+        ("orth_q", TileList), ("orth_p", TileList), ("orth_u", TileList),
+        ("chunks_n", TileList), ("chunks_m", TileList),
+        ("gram", C.c_void_p), ("cbuf", C.c_void_p),
+        ("corr_p", C.c_void_p), ("corr_q", C.c_void_p), ("corr_u", C.c_void_p), ("corr_v", C.c_void_p),
+        ("status", C.c_void_p),
+        ("world", C.c_int), ("rank", C.c_int), ("has_symm", C.c_int), ("pad2", C.c_int),
+        ("peer_flags", C.c_void_p), ("my_flags", C.c_void_p),
+        ("peer_stage", C.c_void_p * 2), ("peer_p", C.c_void_p * 2), ("peer_q", C.c_void_p * 2),
+        ("local_stage", C.c_void_p * 2), ("local_p", C.c_void_p * 2), ("local_q", C.c_void_p * 2),
+        ("spin_limit", C.c_longlong),
+        ("work", C.c_void_p), ("slot", C.c_int), ("fresh", C.c_int), ("seed", C.c_ulonglong),
+        ("epoch", C.c_uint), ("alpha", C.c_float), ("beta", C.c_float), ("eps", C.c_float),
+        ("launched", C.c_int),
+        ("use_graph", C.c_int), ("epoch_word", C.c_void_p), ("epoch_shadow", C.c_uint),
+        ("graph_runs", C.c_int * 2), ("graph_exec", C.c_void_p * 2), ("graph_launched", C.c_int * 2),
+        ("graph_ncoll", C.c_int * 2), ("key_work", C.c_void_p),
+        ("key_alpha", C.c_float), ("key_beta", C.c_float), ("key_eps", C.c_float),
+        ("graph_replays", C.c_int),
+    ]
 
 _SIGNATURES = {
     "conef_version": ([], C.c_int),
@@ -83,6 +131,11 @@ _SIGNATURES = {
     "conef_ipc_get_handle": ([vp, vp], C.c_int),
     "conef_ipc_open_handle": ([vp, C.POINTER(vp)], C.c_int),
     "conef_ipc_close_handle": ([vp], C.c_int),
+    "conef_psgd_run": ([C.POINTER(PsgdPlan), C.c_int, vp], C.c_int),
+    "conef_psgd_plan_size": ([], C.c_int),
+    "conef_psgd_step": ([C.POINTER(PsgdPlan), vp], C.c_int),
+    "conef_psgd_plan_release": ([C.POINTER(PsgdPlan)], C.c_int),
+    "conef_epoch_word": ([vp, C.c_uint32, C.c_int, vp], C.c_int),
     "conef_lamb_step": ([vp, C.c_int, vp, C.c_int, C.c_int, vp, C.c_float, C.c_float, C.c_float, C.c_float,
                          C.c_int, C.c_int, C.c_float, C.c_float, vp], C.c_int),
     "conef_cpu_hash_table": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int], None),
@@ -96,7 +149,7 @@ _OPTIONAL = {}
 # How many kernels one call of an entry point enqueues (memsets not counted);
 # everything not listed launches exactly one.  Host-only entry points launch none.
 _KERNELS_PER_CALL = {
-    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_lowrank_correct": 2, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
+    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_lowrank_correct": 2, "conef_psgd_run": 0, "conef_psgd_plan_size": 0, "conef_psgd_step": 0, "conef_psgd_plan_release": 0, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
     "conef_ipc_get_handle": 0, "conef_ipc_open_handle": 0, "conef_ipc_close_handle": 0,
     "conef_cpu_hash_table": 0, "conef_cpu_sketch_query": 0, "conef_cpu_sketch_update": 0,
     "conef_cpu_gram_schmidt": 0,
@@ -164,6 +217,9 @@ def lib():
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = restype
+    if handle.conef_psgd_plan_size() != C.sizeof(PsgdPlan):
+        raise NativeError(f"PsgdPlan mirrors {C.sizeof(PsgdPlan)} bytes, the library expects "
+                          f"{handle.conef_psgd_plan_size()}: rebuild with `python -m conef_b200.ops.build`")
     _lib = _CountingLib(handle)
     return _lib
 

@@ -313,6 +313,9 @@ class PowerSGDEngine(_EngineBase):
         self._bound = None
         self.aux_ptr = -1
         self.use_tc = False
+        self.exec_plan = None
+        self.epoch_word = None
+        self.tc_maps = None
         self.bind_state(state, bidx)
         self._bound = getattr(state, "error_dict", {}).get(bidx, False) if hasattr(state, "error_dict") else None
 
@@ -526,6 +529,102 @@ class PowerSGDEngine(_EngineBase):
         if native.ptr(aux) != self.aux_ptr:
             work = self.work if self.variant == "batched" else None
             self._build_tiles(work if work is not None else _PtrOnly(self.buf_ptr), aux)
+        self._build_exec(state, bidx)
+
+    def _build_exec(self, state, bidx: int) -> None:
+        """Fill the plan of the native executor (csrc/executor.h): every pointer and size the
+        pipeline needs, so that one host call per step enqueues all of it."""
+        self._release_exec()
+        if self.external or os.environ.get("CONEF_EXECUTOR", "native") != "native":
+            return
+        P, plan = native.PsgdPlan(), self.plan
+        ptr = native.ptr
+
+        def tl(t, n):
+            return native.TileList(ptr(t) if n else None, int(n), 0)
+
+        def qset(name):
+            tc_t, n_tc, q_t, n_q = self.qsets[name]
+            return native.QSet(tl(tc_t, n_tc), tl(q_t, n_q))
+        nrec = len(self.mats_host)
+        P.mats, P.nrec, P.nm = ptr(self.mats_dev), nrec, self.nm
+        P.max_rank, P.np_cols, P.max_cols = self.max_rank, self.np_cols, self.max_cols
+        P.unbiased, P.ef_mode, P.lowrank = int(self.variant == "unbiased"), self.ef_mode, int(self.lowrank)
+        P.use_tc, P.p_zero, P.q_zero = int(self.use_tc), int(bool(self.p_zero)), int(bool(self.q_zero))
+        P.tables, P.counts, P.sketch = ptr(self.tables), ptr(self.counts), ptr(self.sketch_arena)
+        P.dense_err = ptr(state.error_dict[bidx]) if self.ef_mode == native.EF_DENSE else None
+        P.aux = self.aux_ptr if (self.fused_err and self.aux_ptr > 0) else None
+        P.qz, P.total_q, P.total_z = ptr(self.qz), plan.total_q, self.total_z
+        P.pu, P.total_p, P.total_u = ptr(self.pu), plan.total_p, self.total_u
+        P.u_old, P.qz2, P.qpk, P.ppk = ptr(self.u_old), ptr(self.qz2), ptr(self.qpk), ptr(self.ppk)
+        P.segs, P.nsegs, P.total_unc = ptr(self.segs_dev), len(plan.segs), plan.total_unc
+        P.staging = ptr(self.staging)
+        P.tc_maps = ptr(self.tc_maps) if self.use_tc else None
+        P.tc_p, P.simt_p = tl(self.tc_p_tiles, self.n_tc_p), tl(self.p_tiles, self.n_p_tiles)
+        P.qset_all, P.qset_grad, P.qset_err = qset("all"), qset("grad"), qset("err")
+        P.d_tiles, P.d_rows, P.d_smem = tl(self.d_tiles, self.n_d_tiles), self.d_rows, self.d_smem
+        P.orth_q, P.orth_p = tl(*self.orth_tiles[(1, "grad")]), tl(*self.orth_tiles[(0, "grad")])
+        P.orth_u = tl(*self.orth_tiles[(0, "err")])
+        P.chunks_n, P.chunks_m = tl(*self.chunks_n), tl(*self.chunks_m)
+        P.gram = ptr(self.gram)
+        if self.lowrank:
+            P.cbuf = ptr(self.cbuf)
+            P.corr_p, P.corr_q = ptr(self.corr["p"]), ptr(self.corr["q"])
+            P.corr_u, P.corr_v = ptr(self.corr["u"]), ptr(self.corr["v"])
+        P.status = ptr(self.status)
+        P.world, P.rank, P.has_symm = self.world, self.rank, int(self.symm is not None)
+        symm = self.symm
+        if symm is not None:
+            P.peer_flags, P.my_flags = symm.peer_flags_dev(), symm.flags_ptr()
+            for slot in (0, 1):
+                P.peer_stage[slot], P.peer_p[slot], P.peer_q[slot] = (symm.peer_ptrs_dev(slot, r) for r in range(3))
+                P.local_stage[slot], P.local_p[slot], P.local_q[slot] = (ptr(symm.local(slot, r)) for r in range(3))
+        P.spin_limit = DEFAULT_SPIN_LIMIT
+        # steps that draw no new random Q are captured into a CUDA graph per buffer slot and replayed
+        P.use_graph = int(os.environ.get("CONEF_GRAPH", "1") == "1")
+        if self.epoch_word is None:
+            self.epoch_word = torch.zeros(4, dtype=torch.int32, device=self.device)
+        P.epoch_word = ptr(self.epoch_word)
+        P.epoch_shadow = 0
+        self.exec_plan = P
+
+    def _release_exec(self) -> None:
+        plan = getattr(self, "exec_plan", None)
+        self.exec_plan = None
+        if plan is not None:
+            try:
+                self.lib.conef_psgd_plan_release(plan)
+            except Exception:       # interpreter shutdown
+                pass
+
+    def __del__(self):
+        self._release_exec()
+
+    def _run_native(self, state, work, alpha: float, beta: float, fresh: bool, eps: float, st) -> None:
+        """One step through the native executor: one host call (three when the reductions
+        go through NCCL because no peer memory could be set up)."""
+        P, lib, plan = self.exec_plan, self.lib, self.plan
+        P.work, P.slot, P.epoch = work.data_ptr(), self.step & 1, self.epoch & 0xFFFFFFFF
+        P.fresh = int(fresh and self.nm > 0)
+        P.seed = int(state.rng.randint(1_000_000_000)) if P.fresh else 0
+        P.alpha, P.beta, P.eps = alpha, beta, eps
+        if self.world == 1 or self.symm is not None:
+            native.check(lib.conef_psgd_step(P, st), "psgd_step")
+            native.launch_count += P.launched
+        else:
+            native.check(lib.conef_psgd_run(P, native.PHASE_P, st), "psgd_run(P)")
+            native.launch_count += P.launched
+            if plan.total_unc:
+                self._nccl_sum(self.staging[: plan.total_unc], self.group)
+            if self.nm:
+                self._nccl_sum(self.pu[: plan.total_p], self.group, average=self.variant == "unbiased")
+            native.check(lib.conef_psgd_run(P, native.PHASE_Q, st), "psgd_run(Q)")
+            native.launch_count += P.launched
+            if self.nm and self.variant != "unbiased":
+                self._nccl_sum(self.qz[: plan.total_q], self.group, average=True)
+            native.check(lib.conef_psgd_run(P, native.PHASE_D, st), "psgd_run(D)")
+            native.launch_count += P.launched
+        self.epoch = int(P.epoch)
 
     def _pq_memory(self, state, bidx):
         """Flat P/Q tensors of the state; Q is a view of the engine's combined Q|Z buffer.
@@ -588,6 +687,15 @@ class PowerSGDEngine(_EngineBase):
 
         pmem, qmem, fresh = self._pq_memory(state, bidx)
         eps = float(getattr(state, "orthogonalization_epsilon", 0) or 0)
+        if self.exec_plan is not None:
+            self._run_native(state, work, alpha, beta, fresh, eps, st)
+            if self.variant == "batched":
+                buf.copy_(work[: self.buf_numel])
+            if not getattr(state, "warm_start", False) or self.variant == "unbiased":
+                state.p_memory_dict.pop(bidx, None)
+                state.q_memory_dict.pop(bidx, None)
+            self.step += 1
+            return
         symm = self.symm
         slot = self.step & 1
         if nm:
