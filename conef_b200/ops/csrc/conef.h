@@ -154,6 +154,15 @@ int conef_psgd_tc(int mode, const ConefMat* mats, const void* maps, const void* 
 int conef_pack_small(const ConefMat* mats, int nrec, int which, const float* src, float* dst,
                      int max_rank, cudaStream_t stream);
 
+// ---- grouped magnitude top-k (topk.cu) -----------------------------------------
+// For each of the first nmats records: keep the max(1, int(0.5 * ratio * n * m)) largest-magnitude
+// entries of the (n x m) matrix at err + g_off and zero the rest (entries tying with the k-th
+// magnitude are all kept).  tiles: int2 {matrix, chunk of conef_topk_chunk() elements}.
+// scratch: nmats * (2048 + 2) 32-bit words, zeroed once by the caller.
+int conef_topk_keep(const ConefMat* mats, int nmats, const int2* tiles, int ntiles, float* err,
+                    float ratio, uint32_t* scratch, cudaStream_t stream);
+int conef_topk_chunk(void);
+
 // ---- segments, random blocks, quantised error (blocks.cu) -------------------
 int conef_gather_segments(const ConefSeg* segs, int nsegs, const float* bucket,
                           const float* dense_err, float* staging, long long total,

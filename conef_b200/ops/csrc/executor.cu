@@ -101,6 +101,7 @@ static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint3
   float* stage = symm ? plan->local_stage[slot] : plan->staging;
   float* p_target = symm ? plan->local_p[slot] : pmem;
   float* dense_err = plan->ef_mode == CONEF_EF_DENSE ? plan->dense_err : nullptr;
+  float* seg_err = plan->topk ? nullptr : dense_err;      // error of the uncompressed tensors
   const bool orth_p = !plan->unbiased;
   const float inv_ws = 1.0f / (float)ws;
 
@@ -116,7 +117,7 @@ static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint3
       }
     }
     if (plan->total_unc)
-      RUN(conef_gather_segments(plan->segs, plan->nsegs, plan->work, dense_err, stage, plan->total_unc, s));
+      RUN(conef_gather_segments(plan->segs, plan->nsegs, plan->work, seg_err, stage, plan->total_unc, s));
     if (nm) {
       if (plan->p_zero) OK(zero_floats(p_target, tp + tu, s));
       OK(launch_p(plan, aux, p_target, s));
@@ -140,12 +141,12 @@ static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint3
         RUN(conef_wait_flags_ex(plan->my_flags, ws, ep, plan->status, plan->spin_limit, eb, s));
       if (plan->total_unc)
         RUN(conef_scatter_segments(plan->segs, plan->nsegs, plan->work, plan->peer_stage[slot], ws, nullptr,
-                                   inv_ws, dense_err, plan->total_unc, s));
+                                   inv_ws, seg_err, plan->total_unc, s));
     } else {
       // world > 1 without peer memory: the caller all-reduced staging and P between the phases
       if (plan->total_unc)
         RUN(conef_scatter_segments(plan->segs, plan->nsegs, plan->work, nullptr, 1, stage, inv_ws,
-                                   dense_err, plan->total_unc, s));
+                                   seg_err, plan->total_unc, s));
       if (nm && orth_p)
         OK(orth(plan, 0, plan->orth_p, plan->pu, plan->eps, nullptr, nullptr, 1, 0, true, s));
     }
@@ -192,6 +193,11 @@ static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint3
                               plan->work, pmem, qmem, 1.0f, plan->sketch, plan->tables, plan->counts,
                               dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank,
                               plan->d_smem, s));
+    if (plan->topk) {
+      RUN(conef_topk_keep(plan->mats, nm, (const int2*)plan->topk_tiles.tiles, plan->topk_tiles.n,
+                          plan->dense_err, plan->topk_ratio, plan->topk_scratch, s));
+      plan->launched += 6;
+    }
   }
   return 0;
 }

@@ -85,6 +85,12 @@ typedef struct ConefPsgdPlan {
   float* key_work;               // what the graphs were captured with
   float key_alpha, key_beta, key_eps;
   int graph_replays;             // out: number of graph launches so far
+  // ---- top-k error store (dense error buffer pruned after every step) ---------------------------
+  int topk;                      // 1: dense_err holds the matrices' errors only (no error for the
+                                 //    uncompressed tensors) and is pruned to its largest entries
+  float topk_ratio;
+  ConefTileList topk_tiles;
+  uint32_t* topk_scratch;
 } ConefPsgdPlan;
 
 enum { CONEF_PHASE_P = 1, CONEF_PHASE_Q = 2, CONEF_PHASE_D = 4, CONEF_PHASE_ALL = 7 };

@@ -156,8 +156,16 @@ class PowerSGDEngine(_EngineBase):
             self.ef_mode, self.external = native.EF_SKETCH, False
         elif kind == "lowrank" and variant == "powersgd" and os.environ.get("CONEF_LOWRANK_NATIVE", "1") == "1":
             self.ef_mode, self.external = native.EF_NONE, False       # factors handled by run()'s low-rank branch
+        elif kind == "topk" and variant == "powersgd" and self._coeffs(state) == (1.0, 0.0) \
+                and os.environ.get("CONEF_TOPK_NATIVE", "1") == "1":
+            # top-k store: a dense error buffer (the reference stores it dense as well,
+            # communication/hPowerSGD_hook.py:90-97) that enters the products like dense error
+            # feedback and is pruned to its largest entries by one grouped radix select per step
+            self.ef_mode, self.external = native.EF_DENSE, False
         else:
             self.ef_mode, self.external = native.EF_NONE, True
+        self.topk = ef and ec and kind == "topk" and self.ef_mode == native.EF_DENSE
+        self.topk_ratio = float(getattr(state, "topk_ratio", 0.4))
         # Low-rank error store e = U V^T: its factors enter the products as small corrections
         # (P += a U (V^T Q), Q' += a V (U^T P)) and are refreshed by one power-iteration step
         # U' = orth(T V), V' = T^T U' on T = G + (a+b) U V^T - P Q^T, computed without forming T:
@@ -294,6 +302,14 @@ class PowerSGDEngine(_EngineBase):
         self.segs_dev = native.upload_struct_array(segs, dev) if len(segs) else None
 
         # ---- buffers ---------------------------------------------------------------
+        self.topk_arena = self.topk_scratch = self.topk_tiles = None
+        self.n_topk_tiles = 0
+        if self.topk:
+            self.topk_arena = torch.zeros(max(buf.numel(), 1), device=dev, dtype=torch.float32)
+            ch = self.lib.conef_topk_chunk()
+            tk = [(k, c) for k, e in enumerate(plan.mats) for c in range(math.ceil(e.n * e.m / ch))]
+            self.topk_tiles, self.n_topk_tiles = self._tiles(tk), len(tk)
+            self.topk_scratch = torch.zeros(max(nm, 1) * (2048 + 2), device=dev, dtype=torch.int32)
         self.sketch_arena = None
         if self.ef_mode == native.EF_SKETCH:
             self.sketch_arena = torch.zeros(max(sk_off, 1), device=dev, dtype=torch.float32)
@@ -319,12 +335,23 @@ class PowerSGDEngine(_EngineBase):
         self.bind_state(state, bidx)
         self._bound = getattr(state, "error_dict", {}).get(bidx, False) if hasattr(state, "error_dict") else None
 
+    @staticmethod
+    def _coeffs(state):
+        from .hooks import _ef_coeffs
+        return _ef_coeffs(state)
+
+    def _dense_err(self, state, bidx) -> Optional[torch.Tensor]:
+        """The dense error buffer laid out like the bucket (None unless dense or top-k feedback)."""
+        if self.ef_mode != native.EF_DENSE:
+            return None
+        return self.topk_arena if self.topk else state.error_dict[bidx]
+
     # -- auxiliary (error) buffer and tile tables ----------------------------------------
     def _aux(self, state, bidx) -> Optional[torch.Tensor]:
         if self.ef_mode == native.EF_SKETCH:
             return self.sketch_arena
         if self.ef_mode == native.EF_DENSE:
-            return state.error_dict[bidx]
+            return self._dense_err(state, bidx)
         return None
 
     def _build_tiles(self, work: torch.Tensor, aux: Optional[torch.Tensor]) -> None:
@@ -466,7 +493,22 @@ class PowerSGDEngine(_EngineBase):
     def bind_state(self, state, bidx: int) -> None:
         plan, dev = self.plan, self.device
         n_err = self.side * self.side if self.variant == "batched" else self.buf_numel
-        if self.ef_mode == native.EF_DENSE:
+        if self.topk:
+            from ..compressors import TopKError
+            comps = state.error_dict.get(bidx)
+            if not isinstance(comps, dict):
+                comps = {}
+                state.error_dict[bidx] = comps
+            for cnt, e in enumerate(plan.mats):
+                view = self.topk_arena[e.g_off : e.g_off + e.n * e.m].view(e.n, e.m)
+                old = comps.get(cnt)
+                if not (isinstance(old, TopKError) and (old.N, old.D) == (e.n, e.m)):
+                    old = TopKError(e.n, e.m, self.topk_ratio, device="cpu")
+                    comps[cnt] = old
+                if old.err.data_ptr() != view.data_ptr():
+                    view.copy_(old.err.to(dev))
+                    old.err = view
+        elif self.ef_mode == native.EF_DENSE:
             cur = state.error_dict.get(bidx)
             if not (torch.is_tensor(cur) and cur.numel() == n_err and cur.device == dev
                     and cur.dtype == torch.float32 and cur.is_contiguous()):
@@ -552,7 +594,11 @@ class PowerSGDEngine(_EngineBase):
         P.unbiased, P.ef_mode, P.lowrank = int(self.variant == "unbiased"), self.ef_mode, int(self.lowrank)
         P.use_tc, P.p_zero, P.q_zero = int(self.use_tc), int(bool(self.p_zero)), int(bool(self.q_zero))
         P.tables, P.counts, P.sketch = ptr(self.tables), ptr(self.counts), ptr(self.sketch_arena)
-        P.dense_err = ptr(state.error_dict[bidx]) if self.ef_mode == native.EF_DENSE else None
+        P.dense_err = ptr(self._dense_err(state, bidx))
+        P.topk, P.topk_ratio = int(self.topk), self.topk_ratio
+        if self.topk:
+            P.topk_tiles = tl(self.topk_tiles, self.n_topk_tiles)
+            P.topk_scratch = ptr(self.topk_scratch)
         P.aux = self.aux_ptr if (self.fused_err and self.aux_ptr > 0) else None
         P.qz, P.total_q, P.total_z = ptr(self.qz), plan.total_q, self.total_z
         P.pu, P.total_p, P.total_u = ptr(self.pu), plan.total_p, self.total_u
@@ -673,7 +719,8 @@ class PowerSGDEngine(_EngineBase):
         if self.external or self.lowrank:
             from .hooks import _ef_coeffs
             alpha, beta = _ef_coeffs(state)
-        dense_err = state.error_dict[bidx] if self.ef_mode == native.EF_DENSE else None
+        dense_err = self._dense_err(state, bidx)
+        seg_err = None if self.topk else dense_err        # the uncompressed tensors carry no top-k error
         sketch = self.sketch_arena
         aux = self.aux_ptr if self.fused_err else 0
 
@@ -716,7 +763,7 @@ class PowerSGDEngine(_EngineBase):
         p_target = symm.local(slot, 1) if symm else pmem
         if plan.total_unc:
             native.check(lib.conef_gather_segments(self.segs_dev.data_ptr(), len(plan.segs), wp,
-                                                   native.ptr(dense_err), stage.data_ptr(), plan.total_unc, st),
+                                                   native.ptr(seg_err), stage.data_ptr(), plan.total_unc, st),
                          "gather_segments")
         if nm:
             if self.p_zero:
@@ -743,7 +790,7 @@ class PowerSGDEngine(_EngineBase):
             if plan.total_unc:
                 native.check(lib.conef_scatter_segments(
                     self.segs_dev.data_ptr(), len(plan.segs), wp, symm.peer_ptrs_dev(slot, 0), ws, 0, 1.0 / ws,
-                    native.ptr(dense_err), plan.total_unc, st), "scatter_segments")
+                    native.ptr(seg_err), plan.total_unc, st), "scatter_segments")
         else:
             if ws > 1:
                 if plan.total_unc:
@@ -753,7 +800,7 @@ class PowerSGDEngine(_EngineBase):
             if plan.total_unc:
                 native.check(lib.conef_scatter_segments(
                     self.segs_dev.data_ptr(), len(plan.segs), wp, 0, 1, stage.data_ptr(), 1.0 / ws,
-                    native.ptr(dense_err), plan.total_unc, st), "scatter_segments")
+                    native.ptr(seg_err), plan.total_unc, st), "scatter_segments")
             if nm and orth_p:
                 self._orth(0, "grad", self.pu, eps, st, packed=True)
 
@@ -794,6 +841,10 @@ class PowerSGDEngine(_EngineBase):
                 pmem.data_ptr(), qmem.data_ptr(), 1.0, native.ptr(sketch), native.ptr(self.tables),
                 native.ptr(self.counts), native.ptr(dense_err), alpha, beta, self.ef_mode, self.max_rank,
                 self.d_smem, st), "decompress")
+            if self.topk:
+                native.check(lib.conef_topk_keep(self.mats_dev.data_ptr(), nm, self.topk_tiles.data_ptr(),
+                                                 self.n_topk_tiles, dense_err.data_ptr(), self.topk_ratio,
+                                                 self.topk_scratch.data_ptr(), st), "topk_keep")
 
         if self.external:
             copy.sub_(work)

