@@ -47,6 +47,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "restated", "allreduce"])
     ap.add_argument("--config", default="wrn", choices=["wrn", "resnet20", "lstm", "transformer", "bert"])
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch (default: the config's)")
+    ap.add_argument("--error-compressor", default=None,
+                    help="replace the configuration's error store (e.g. topk, the reference's own hPowerSGD "
+                         "store, for --config transformer); the headline configurations leave it unset")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--small", action="store_true", help="shrunken model, for smoke tests only (not a valid number)")
     return ap.parse_args()
@@ -184,6 +187,9 @@ def main():
     model, opt_factory, loss_fn, make_batch, per_gpu, ns, ac_dtype, desc, tkw = build_workload(args, device, world)
     if args.impl == "allreduce":
         ns.grad_reducer = "allreduce"
+    if args.error_compressor:
+        ns.error_compressor = args.error_compressor
+        desc["reducer"] += f" [error store replaced by {args.error_compressor}]"
     if not use_cuda:
         ac_dtype = None
         tkw = {k: v for k, v in tkw.items() if k != "channels_last"}

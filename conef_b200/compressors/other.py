@@ -72,13 +72,35 @@ class TopKError(DenseError):
 
     def update(self, v, beta):
         self.err.mul_(beta).add_(v.view(self.N, self.D))
-        ref.topk_keep_(self.err, self.topk_ratio)
+        if native.use_native(self.err) and self.err.dtype == torch.float32 and self.err.is_contiguous():
+            self._native_keep()
+        else:
+            ref.topk_keep_(self.err, self.topk_ratio)
+
+    def _native_keep(self):
+        """Radix select on the device (csrc/topk.cu) instead of a sort."""
+        lib = native.lib()
+        tabs = getattr(self, "_tk", None)
+        if tabs is None or tabs[0].device != self.err.device:
+            rec = np.zeros(1, dtype=native.MAT_DTYPE)
+            rec[0]["n"], rec[0]["m"] = self.N, self.D
+            ch = lib.conef_topk_chunk()
+            nt = (self.N * self.D + ch - 1) // ch
+            tiles = np.zeros((nt, 2), dtype=np.int32)
+            tiles[:, 1] = np.arange(nt)
+            dev = self.err.device
+            tabs = (native.upload_struct_array(rec, dev), torch.from_numpy(tiles).to(dev),
+                    torch.zeros(2050, dtype=torch.int32, device=dev), nt)
+            self._tk = tabs
+        native.check(lib.conef_topk_keep(tabs[0].data_ptr(), 1, tabs[1].data_ptr(), tabs[3], self.err.data_ptr(),
+                                         self.topk_ratio, tabs[2].data_ptr(), native.stream_ptr(self.err.device)),
+                     "topk_keep")
 
     def nbytes(self):
         return max(1, int(0.5 * self.topk_ratio * self.N * self.D)) * 8
 
     def __getstate__(self):
-        d = super().__getstate__()
+        d = super().__getstate__()          # the device tables (_tk) are rebuilt on demand
         d["topk_ratio"] = self.topk_ratio
         return d
 
