@@ -117,6 +117,19 @@ int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, i
                           float* sketch, const int32_t* tables, const int32_t* counts,
                           float* dense_err, float alpha, float beta, int ef_mode, int max_rank,
                           size_t smem_bytes, cudaStream_t stream);
+// The same for the count-sketch store, without atomics: tiles are int2 {matrix, block of
+// 4 * conef_dc_groups(m) rows}.  ell: the hash tables regrouped by sketch cell (one blob per (m, W)
+// table: [G x (base, steps)] [32 G cell ids] [interleaved column lists, -1 padded], G = ceil(W / 32);
+// see ops/reference.py:ell_hash_table); ell_hdr[cnt_off] = offset of the table's blob in `ell`.
+// Shared memory: 16 * max_cols bytes with max_cols = max over the launch's matrices of
+// m * conef_dc_groups(m); at most 220 KB.  Launching matrices of similar m together keeps the
+// occupancy of the narrow ones.
+int conef_psgd_decompress_csr(const ConefMat* mats, const int2* tiles, int ntiles, int max_cols,
+                              float* bucket, const float* P, const float* Q, float q_scale,
+                              float* sketch, const int32_t* counts, const int32_t* ell,
+                              const int32_t* ell_hdr, float alpha, float beta, int max_rank,
+                              cudaStream_t stream);
+int conef_dc_groups(int m);
 // Sparse sign matrix H of the sketch applied to the small factors (see csrc/sketch.cu):
 // unproject = 0: Z_i += scale * H_i^T Q_i ; unproject = 1: Q_i += scale * H_i Y_i.
 // Record nmats + i describes the sketch of matrix i; its q_off is where Z_i / Y_i live.

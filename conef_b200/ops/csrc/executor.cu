@@ -189,6 +189,17 @@ static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint3
       OK(copy_floats(plan->u_old, plan->pu + tp, tu, s));
       OK(copy_floats(plan->qz + tq, plan->qz2 + tq, tz, s));
     }
+    bool csr = false;
+    if (plan->ef_mode == CONEF_EF_SKETCH)
+      for (int c = 0; c < 4; ++c) {
+        const ConefTileList& tl = plan->dc_tiles[c];
+        if (tl.n <= 0) continue;
+        csr = true;
+        RUN(conef_psgd_decompress_csr(plan->mats, (const int2*)tl.tiles, tl.n, tl.pad, plan->work, pmem, qmem,
+                                      1.0f, plan->sketch, plan->counts, plan->ell, plan->ell_hdr,
+                                      plan->alpha, plan->beta, plan->max_rank, s));
+      }
+    if (!csr)
     RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_rows,
                               plan->work, pmem, qmem, 1.0f, plan->sketch, plan->tables, plan->counts,
                               dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank,

@@ -91,6 +91,11 @@ typedef struct ConefPsgdPlan {
   float topk_ratio;
   ConefTileList topk_tiles;
   uint32_t* topk_scratch;
+  // ---- count-sketch decompress without atomics (used when dc_tiles.n > 0) --------------------------
+  const int32_t* ell;            // hash tables regrouped by sketch cell
+  const int32_t* ell_hdr;        // per table (indexed like `counts`): offset of its blob in `ell`
+  ConefTileList dc_tiles[4];     // int2 {matrix, row block}; one launch per shared-memory class;
+                                 // `pad` of each list carries the class's max m * groups(m)
 } ConefPsgdPlan;
 
 enum { CONEF_PHASE_P = 1, CONEF_PHASE_Q = 2, CONEF_PHASE_D = 4, CONEF_PHASE_ALL = 7 };

@@ -182,7 +182,8 @@ class PowerSGDEngine(_EngineBase):
         mats = np.zeros(nrec, dtype=native.MAT_DTYPE)
         sk_off = tab_off = cnt_off = z_off = u_off = 0
         err_rank = int(getattr(state, "error_rank", None) or state.matrix_approximation_rank) if self.lowrank else 0
-        table_chunks, count_chunks = [], []
+        table_chunks, count_chunks, ell_chunks, ell_offsets = [], [], [], {}
+        ell_len = 0
         table_index: Dict[tuple, tuple] = {}
         self.widths = []
         seeds = ref.derive_hash_seeds(getattr(state, "hash_seed", 0), 1)[0]
@@ -202,6 +203,10 @@ class PowerSGDEngine(_EngineBase):
                     table_index[key] = (tab_off, cnt_off)
                     table_chunks.append(packed)
                     count_chunks.append(counts)
+                    blob = ref.ell_hash_table(packed.cpu().numpy(), W)     # for the decompress kernel
+                    ell_offsets[cnt_off] = ell_len
+                    ell_chunks.append(torch.from_numpy(blob))
+                    ell_len += len(blob)
                     tab_off += e.m
                     cnt_off += W
                 rec["tab_off"], rec["cnt_off"] = table_index[key]
@@ -270,6 +275,13 @@ class PowerSGDEngine(_EngineBase):
         self.mats_dev = native.upload_struct_array(mats, dev) if nrec else None
         self.tables = torch.cat(table_chunks) if table_chunks else None
         self.counts = torch.cat(count_chunks) if count_chunks else None
+        self.ell = self.ell_hdr = None
+        if ell_chunks:
+            self.ell = torch.cat(ell_chunks).to(dev)
+            hdr = np.zeros(max(cnt_off, 1), dtype=np.int32)
+            for at, off in ell_offsets.items():
+                hdr[at] = off
+            self.ell_hdr = torch.from_numpy(hdr).to(dev)
         # 512-row chunks for the row-parallel Gram-Schmidt and correction kernels
         OC = 512
         chunk = lambda ks, field: [(k, c) for k in ks for c in range(math.ceil(int(mats[k][field]) / OC))]
@@ -295,6 +307,26 @@ class PowerSGDEngine(_EngineBase):
         d_tiles = [(k, rb) for k, e in enumerate(plan.mats) for rb in range(math.ceil(e.n / self.d_rows))]
         self.d_tiles = self._tiles(d_tiles)
         self.n_d_tiles = len(d_tiles)
+        # count-sketch store: the kernel without atomics keeps 16 bytes per column in shared memory
+        # (row blocks of 4 * groups(m) rows; one launch per shared-memory class so that narrow
+        # matrices are not charged the shared memory of the widest one).  Off by default: on B200 it
+        # does not beat the kernel with shared-memory atomics yet (its two phases do not overlap at
+        # the occupancy its shared memory and registers allow); CONEF_DECOMPRESS_CSR=1 selects it.
+        self.dc_classes, self.n_dc_tiles = [], 0
+        if self.ef_mode == native.EF_SKETCH and self.max_cols * 16 + 2048 <= 200 * 1024 \
+                and os.environ.get("CONEF_DECOMPRESS_CSR", "0") == "1":
+            groups = {k: self.lib.conef_dc_groups(e.m) for k, e in enumerate(plan.mats)}
+            classes: Dict[int, list] = {}
+            for k, e in enumerate(plan.mats):
+                need = e.m * groups[k] * 16
+                cls = 0 if need <= 16 << 10 else 1 if need <= 32 << 10 else 2 if need <= 64 << 10 else 3
+                blocks = math.ceil(e.n / (4 * groups[k]))
+                classes.setdefault(cls, []).extend((k, rb) for rb in range(blocks))
+            for cls in sorted(classes):
+                lst = classes[cls]
+                width = max(plan.mats[k].m * groups[k] for k, _ in lst)
+                self.dc_classes.append((self._tiles(lst), len(lst), width))
+                self.n_dc_tiles += len(lst)
 
         segs = np.zeros(len(plan.segs), dtype=native.SEG_DTYPE)
         for k, s in enumerate(plan.segs):
@@ -609,6 +641,9 @@ class PowerSGDEngine(_EngineBase):
         P.tc_p, P.simt_p = tl(self.tc_p_tiles, self.n_tc_p), tl(self.p_tiles, self.n_p_tiles)
         P.qset_all, P.qset_grad, P.qset_err = qset("all"), qset("grad"), qset("err")
         P.d_tiles, P.d_rows, P.d_smem = tl(self.d_tiles, self.n_d_tiles), self.d_rows, self.d_smem
+        for i, (tiles, n, width) in enumerate(self.dc_classes):
+            P.dc_tiles[i] = native.TileList(ptr(tiles), n, width)
+        P.ell, P.ell_hdr = ptr(self.ell), ptr(self.ell_hdr)
         P.orth_q, P.orth_p = tl(*self.orth_tiles[(1, "grad")]), tl(*self.orth_tiles[(0, "grad")])
         P.orth_u = tl(*self.orth_tiles[(0, "err")])
         P.chunks_n, P.chunks_m = tl(*self.chunks_n), tl(*self.chunks_m)
@@ -836,11 +871,14 @@ class PowerSGDEngine(_EngineBase):
             if self.lowrank:
                 self._refresh_lowrank(wp, alpha, beta, st)
             # 4. M_hat = P Q^T ; residual of (G + e) -> error store
-            native.check(lib.conef_psgd_decompress(
-                self.mats_dev.data_ptr(), self.d_tiles.data_ptr(), self.n_d_tiles, self.d_rows, wp,
-                pmem.data_ptr(), qmem.data_ptr(), 1.0, native.ptr(sketch), native.ptr(self.tables),
-                native.ptr(self.counts), native.ptr(dense_err), alpha, beta, self.ef_mode, self.max_rank,
-                self.d_smem, st), "decompress")
+            if self.n_dc_tiles:
+                self.launch_decompress_csr(wp, pmem, qmem, alpha, beta, st)
+            else:
+                native.check(lib.conef_psgd_decompress(
+                    self.mats_dev.data_ptr(), self.d_tiles.data_ptr(), self.n_d_tiles, self.d_rows, wp,
+                    pmem.data_ptr(), qmem.data_ptr(), 1.0, native.ptr(sketch), native.ptr(self.tables),
+                    native.ptr(self.counts), native.ptr(dense_err), alpha, beta, self.ef_mode, self.max_rank,
+                    self.d_smem, st), "decompress")
             if self.topk:
                 native.check(lib.conef_topk_keep(self.mats_dev.data_ptr(), nm, self.topk_tiles.data_ptr(),
                                                  self.n_topk_tiles, dense_err.data_ptr(), self.topk_ratio,
@@ -857,6 +895,14 @@ class PowerSGDEngine(_EngineBase):
             state.p_memory_dict.pop(bidx, None)
             state.q_memory_dict.pop(bidx, None)
         self.step += 1
+
+    def launch_decompress_csr(self, wp, pmem, qmem, alpha, beta, st) -> None:
+        """M_hat into the bucket and the residual into the count sketch, one launch per class."""
+        for tiles, n, width in self.dc_classes:
+            native.check(self.lib.conef_psgd_decompress_csr(
+                self.mats_dev.data_ptr(), tiles.data_ptr(), n, width, wp, pmem.data_ptr(), qmem.data_ptr(), 1.0,
+                self.sketch_arena.data_ptr(), self.counts.data_ptr(), self.ell.data_ptr(),
+                self.ell_hdr.data_ptr(), alpha, beta, self.max_rank, st), "decompress_csr")
 
     def _launch_p(self, wp, aux, small: torch.Tensor, p_target: torch.Tensor, st) -> None:
         """P (+)= A Q over every record: tcgen05 tiles where TMA can address the matrix, SIMT elsewhere.

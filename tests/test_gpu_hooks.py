@@ -346,3 +346,27 @@ def test_hpowersgd_topk_error_native_vs_cpu(single_rank_group, monkeypatch, exec
         assert int((mine != 0).sum()) == int((comp.err != 0).sum())
         torch.testing.assert_close(mine, comp.err, **TOL)
     assert sg.ef_buffer_bytes() == sc.ef_buffer_bytes()
+
+
+@pytest.mark.parametrize("kw", [
+    dict(matrix_approximation_rank=2, sketch_size=0.1),
+    dict(matrix_approximation_rank=8, sketch_size=0.3, beta=0.5),
+], ids=["r2", "r8"])
+def test_decompress_without_atomics_matches_atomic_kernel(single_rank_group, monkeypatch, kw):
+    """Two kernels for the count-sketch store: per-cell sums over a CSR of the hash table (default)
+    and shared-memory atomics; same outputs and same sketches over several steps."""
+    monkeypatch.setenv("CONEF_TC", "0")
+    kw = dict(use_error_feedback=True, use_error_compression=True, **kw)
+
+    def run(flag):
+        monkeypatch.setenv("CONEF_DECOMPRESS_CSR", flag)
+        state = _powersgd_states(DEV, **kw)
+        outs = _steps(cb.powerSGD_hook, state, DEV, monkeypatch, "native", steps=4)
+        eng = state._engines[0]
+        assert bool(eng.n_dc_tiles) == (flag == "1")
+        return outs, eng.sketch_arena.cpu().clone()
+    a, sa = run("1")
+    b, sb = run("0")
+    for x, y in zip(a, b):
+        torch.testing.assert_close(x, y, **TOL)
+    torch.testing.assert_close(sa, sb, **TOL)
