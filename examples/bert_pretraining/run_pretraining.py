@@ -24,7 +24,7 @@ from torch.utils.data import DataLoader
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
 import conef_b200 as cb  # noqa: E402
 from conef_b200 import models  # noqa: E402
-from conef_b200.data import SyntheticBertShard  # noqa: E402
+from conef_b200.data import ShardPrefetcher, SyntheticBertShard, shard_files  # noqa: E402
 from conef_b200.optim import FusedLAMB, LinearWarmUpScheduler  # noqa: E402
 from conef_b200.utils import (GracefulStop, JsonLogger, latest_checkpoint, load_checkpoint,  # noqa: E402
                               save_checkpoint)
@@ -47,6 +47,8 @@ def parse():
     p.add_argument("--resume_from_checkpoint", action="store_true")
     p.add_argument("--checkpoint_activations", action="store_true")
     p.add_argument("--bf16", action="store_true", default=True)
+    p.add_argument("--input_dir", default=None,
+                   help="directory of .npz shards written by create_pretraining_data.py; synthetic shards when omitted")
     p.add_argument("--shard_size", type=int, default=2048, help="synthetic instances per shard")
     p.add_argument("--seed", type=int, default=42)
     p.add_argument("--grad_reducer", default="conef_powersgd", choices=cb.REDUCERS)
@@ -115,11 +117,24 @@ def main():
     done, t_start, seqs = 0, time.time(), 0
     amp = torch.autocast("cuda", dtype=torch.bfloat16) if (cuda and args.bf16) else torch.autocast("cpu", enabled=False)
     ddp.train()
+    def epoch_shards(epoch):
+        """This rank's shards of an epoch; files are read one shard ahead in the background."""
+        if args.input_dir:
+            pre = ShardPrefetcher(shard_files(args.input_dir, rank, world, epoch, args.seed),
+                                  args.max_predictions_per_seq)
+            yield from pre
+            pre.close()
+        else:
+            yield SyntheticBertShard(args.shard_size, args.max_seq_length, 30522, args.max_predictions_per_seq,
+                                     seed=args.seed + 1000 * epoch + rank)
+
+    def batches(epoch):
+        for shard in epoch_shards(epoch):
+            yield from DataLoader(shard, micro, shuffle=True, num_workers=0 if args.input_dir else 2,
+                                  pin_memory=cuda, drop_last=len(shard) >= micro)
+
     while done < steps_this_run and global_step < args.max_steps and not stop.requested:
-        shard = SyntheticBertShard(args.shard_size, args.max_seq_length, 30522, args.max_predictions_per_seq,
-                                   seed=args.seed + 1000 * epoch + rank)          # this rank's shard of the epoch
-        loader = DataLoader(shard, micro, shuffle=True, num_workers=2, pin_memory=cuda, drop_last=True)
-        for it, batch in enumerate(loader):
+        for it, batch in enumerate(batches(epoch)):
             ids, seg, mask, labels, nsp = (t.to(device, non_blocking=True) for t in batch)
             sync = (it + 1) % args.gradient_accumulation_steps == 0
             ctx = ddp.no_sync() if not sync else torch.autocast("cpu", enabled=False)

@@ -10,7 +10,7 @@ import conef_b200 as cb
 from conef_b200 import data, optim, utils
 from conef_b200.ops import reference as ref
 
-from helpers import FakeBucket
+from helpers import FakeBucket, free_port
 
 SHAPES = [(32, 3, 3, 3), (32,), (48, 32, 3, 3), (10, 48), (10,)]
 
@@ -142,3 +142,92 @@ def test_trainer_checkpoint_resume_over_gloo(single_rank_group, tmp_path):
     tr2.load_state_dict(sd)
     assert tr2.state.iter == 4 and tr2.state.ef_buffer_bytes() == tr.state.ef_buffer_bytes()
     assert torch.isfinite(tr2.step(x, y))
+
+
+def _toy_corpus(tmp_path):
+    words = ["the", "cat", "dog", "sat", "ran", "on", "mat", "fast", "slow", "blue", "red", "house", "tree", "##s", "##ing"]
+    vocab = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]"] + words
+    vf = tmp_path / "vocab.txt"
+    vf.write_text("\n".join(vocab) + "\n")
+    import random
+    rng = random.Random(0)
+    lines = []
+    for d in range(12):
+        for s in range(rng.randint(3, 7)):
+            lines.append(" ".join(rng.choice(words[:13]) for _ in range(rng.randint(4, 12))))
+        lines.append("")
+    cf = tmp_path / "corpus.txt"
+    cf.write_text("\n".join(lines))
+    return vf, cf
+
+
+def test_pretraining_instances_shards_and_prefetch(tmp_path):
+    """Documents -> sentence-pair / masked-LM instances -> .npz shards -> dataset, following the
+    recipe of the reference's create_pretraining_data.py."""
+    from conef_b200 import data as D
+    vf, cf = _toy_corpus(tmp_path)
+    tok = D.BertTokenizer(str(vf))
+    docs = D.read_documents([str(cf)], tok)
+    assert len(docs) == 12 and all(len(d) >= 3 for d in docs)
+    inst = D.create_training_instances(docs, list(tok.vocab.keys()), max_seq_length=32, dupe_factor=3,
+                                       max_predictions_per_seq=5, seed=1)
+    assert len(inst) >= 12 * 3
+    n_random = 0
+    for it in inst:
+        assert it.tokens[0] == "[CLS]" and it.tokens[-1] == "[SEP]" and it.tokens.count("[SEP]") == 2
+        assert len(it.tokens) <= 32 and len(it.tokens) == len(it.segment_ids)
+        first_sep = it.tokens.index("[SEP]")
+        assert set(it.segment_ids[: first_sep + 1]) == {0} and set(it.segment_ids[first_sep + 1 :]) == {1}
+        assert 1 <= len(it.masked_lm_positions) <= 5 and len(it.masked_lm_positions) == len(it.masked_lm_labels)
+        assert all(it.tokens[p] not in ("[CLS]", "[SEP]") or it.tokens[p] == "[MASK]" for p in it.masked_lm_positions)
+        assert 0 not in it.masked_lm_positions
+        n_random += it.is_random_next
+    assert 0.2 < n_random / len(inst) < 0.8
+    # shards
+    half = len(inst) // 2
+    for k, part in enumerate((inst[:half], inst[half:])):
+        D.write_shard(str(tmp_path / f"part_{k}.npz"), D.instances_to_arrays(part, tok, 32, 5))
+    files = D.shard_files(str(tmp_path), rank=0, world=2, epoch=0) + D.shard_files(str(tmp_path), rank=1, world=2, epoch=0)
+    assert sorted(files) == sorted(str(tmp_path / f"part_{k}.npz") for k in range(2))
+    assert len(D.shard_files(str(tmp_path), rank=3, world=4)) == 1            # fewer files than ranks: wrap
+    total = 0
+    pre = D.ShardPrefetcher(sorted(files), 5)
+    for shard in pre:
+        assert isinstance(shard, D.PretrainingShard)
+        ids, seg, mask, labels, nsp = shard[0]
+        assert ids.shape == (32,) and seg.shape == (32,) and mask.shape == (32,) and labels.shape == (32,)
+        assert int(mask.sum()) >= 5 and nsp in (0, 1)
+        assert 1 <= int((labels >= 0).sum()) <= 5 and bool((labels[mask == 0] == -1).all())
+        assert int(ids[0]) == tok.vocab["[CLS]"]
+        total += len(shard)
+    pre.close()
+    assert total == len(inst)
+    # the first instance survives the round trip
+    first = D.PretrainingShard(str(tmp_path / "part_0.npz"))[0]
+    want_ids = tok.convert_tokens_to_ids(inst[0].tokens)
+    assert first[0][: len(want_ids)].tolist() == want_ids
+    for p, lab in zip(inst[0].masked_lm_positions, tok.convert_tokens_to_ids(inst[0].masked_lm_labels)):
+        assert int(first[3][p]) == lab
+
+
+def test_bert_driver_trains_from_shard_files(tmp_path):
+    """create_pretraining_data.py -> run_pretraining.py --input_dir, end to end on CPU."""
+    import subprocess, sys, json
+    vf, cf = _toy_corpus(tmp_path)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), RANK="0", WORLD_SIZE="1",
+               CUDA_VISIBLE_DEVICES="")
+    shards = tmp_path / "shards"
+    subprocess.run([sys.executable, os.path.join(root, "examples/bert_pretraining/create_pretraining_data.py"),
+                    "--input_file", str(cf), "--vocab_file", str(vf), "--output_prefix", str(shards / "part"),
+                    "--shards", "2", "--max_seq_length", "32", "--max_predictions_per_seq", "5", "--dupe_factor", "2"],
+                   check=True, env=env, timeout=300)
+    assert len(list(shards.glob("*.npz"))) == 2
+    out = tmp_path / "run"
+    subprocess.run([sys.executable, os.path.join(root, "examples/bert_pretraining/run_pretraining.py"),
+                    "--bert_model", "tiny", "--input_dir", str(shards), "--output_dir", str(out),
+                    "--max_seq_length", "32", "--max_predictions_per_seq", "5", "--train_batch_size", "4",
+                    "--max_steps", "6", "--grad_reducer", "conef_powersgd", "--matrix_approximation_rank", "2"],
+                   check=True, env=env, timeout=600)
+    lines = [json.loads(l) for l in (out / "log.jsonl").read_text().splitlines()]
+    assert any(l.get("step") == "summary" for l in lines)
