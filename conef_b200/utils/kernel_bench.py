@@ -174,6 +174,8 @@ def main():
             record("powerSGD_hook (whole bucket, ws=1)", t, 4 * mat_bytes + 4 * sk_bytes,
                    "ideal: G read by P, Q and decompress, written once; sketch read 3x, written once")
 
+    os.environ["CONEF_TC"] = "1"
+
     # ---------------- random block pipeline ----------------
     for kind, kw in (("ef", dict()), ("sketch", dict(use_error_compression=True, sketch_size=args.sketch_size)),
                      ("quant8", dict(use_error_compression=True, error_compressor="quant8", beta=0.0))):
@@ -185,6 +187,23 @@ def main():
         t = _time(lambda: cb.RandomBlock_hook(state, bucket).wait(), args.iters)
         per = {"ef": 4.0, "sketch": 2.2, "quant8": 2.5}[kind]      # passes over the tensors (r/w gradient + error store)
         record(f"RandomBlock_hook {kind} (whole bucket, ws=1)", t, per * nbytes, "gather+error update, scatter")
+
+    # ---------------- hPowerSGD top-k error store ----------------
+    if want("topk"):
+        state = cb.hPowerSGDState(None, matrix_approximation_rank=rank, start_powerSGD_iter=2,
+                                  use_error_compression=True, topk_ratio=0.4)
+        eng = PowerSGDEngine(state, buf, bucket.gradients(), group, "powersgd")
+        eng.topk_arena.normal_()
+        mat_bytes = 4 * sum(e.numel for e in eng.plan.mats)
+        t = _time(lambda: native.check(lib.conef_topk_keep(
+            eng.mats_dev.data_ptr(), eng.nm, eng.topk_tiles.data_ptr(), eng.n_topk_tiles, eng.topk_arena.data_ptr(),
+            0.4, eng.topk_scratch.data_ptr(), st)), args.iters)
+        record("topk_keep (radix select, all matrices)", t, 4.8 * mat_bytes,
+               "3 histogram reads + prune (read, ~80 % written back)")
+        state.iter = 2
+        t = _time(lambda: cb.hpowerSGD_hook(state, bucket).wait(), args.iters)
+        record("hpowerSGD_hook top-k (whole bucket, ws=1)", t, (3 * 2 + 2 + 4.8) * mat_bytes,
+               "G and E read by P, Q, decompress; M_hat and E written; top-k")
 
     # ---------------- LAMB ----------------
     if want("lamb"):
