@@ -19,14 +19,38 @@
 //                              -> k_psgd_decompress (one pass, residual kept in registers)
 #include "common.cuh"
 
-constexpr int P_WARPS = 8;       // rows per CTA in k_psgd_p (one warp per row)
+constexpr int P_WARPS = 8;       // warps per CTA in k_psgd_p
+constexpr int P_WROWS = 4;       // matrix rows per warp: a Q row is loaded once for the four of them
 constexpr int Q_THREADS = 256;   // columns per CTA in k_psgd_q
 constexpr int D_THREADS = 256;
 
+// Q[j, 0..r) scaled into registers.  With r a multiple of 4 and a 16-byte aligned block the row
+// comes in as 16-byte loads: scalar loads of a stride-r pattern cost r wavefronts of mostly unused
+// bytes per warp, which made the Q rows, not the gradient, the dominant load traffic.
+template <int RP>
+__device__ __forceinline__ void load_q_row(const float* __restrict__ q, int r, float q_scale, bool vec,
+                                           float (&qv)[RP]) {
+  if (RP >= 4 && vec) {
+#pragma unroll
+    for (int c = 0; c < RP; c += 4) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (c < r) x = __ldg(reinterpret_cast<const float4*>(q + c));
+      qv[c] = x.x * q_scale;
+      if (c + 1 < RP) qv[c + 1] = x.y * q_scale;
+      if (c + 2 < RP) qv[c + 2] = x.z * q_scale;
+      if (c + 3 < RP) qv[c + 3] = x.w * q_scale;
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < RP; ++c) qv[c] = c < r ? __ldg(q + c) * q_scale : 0.f;
+  }
+}
+
 // ---------------------------------------------------------------------------
-// P (+)= A Q for every record of the table, one warp per matrix row.  A record reads its
-// matrix from the gradient bucket (src = 0) or from the auxiliary buffer (src = 1: sketch
-// arena or dense error buffer).
+// P (+)= A Q for every record of the table.  A warp owns P_WROWS matrix rows and walks the columns:
+// the lanes read 32 consecutive entries of each row, the Q row of a column is loaded once (16-byte
+// loads) for the rows of the warp.  A record reads its matrix from the gradient bucket (src = 0) or
+// from the auxiliary buffer (src = 1: sketch arena or dense error buffer).
 template <int RP>
 __global__ void __launch_bounds__(P_WARPS * 32)
 k_psgd_p(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, const float* __restrict__ bucket,
@@ -34,41 +58,56 @@ k_psgd_p(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, cons
   const int2 t = tiles[blockIdx.x];
   const ConefMat M = mats[t.x];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = t.y * P_WARPS + warp;
-  if (row >= M.n) return;
+  const int row0 = (t.y * P_WARPS + warp) * P_WROWS;
+  if (row0 >= M.n) return;
+  const int rows = min(P_WROWS, M.n - row0);
   const int m = M.m, r = M.r;
-  const float* g = (M.src ? aux : bucket) + M.g_off + (size_t)row * m;
+  const float* g = (M.src ? aux : bucket) + M.g_off + (size_t)row0 * m;
   const float* q = Q + M.q_off;
-  float acc[RP];
+  const bool qvec = (r & 3) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+  float acc[P_WROWS][RP];
 #pragma unroll
-  for (int c = 0; c < RP; ++c) acc[c] = 0.f;
-  constexpr int PB = 8;      // independent loads in flight per lane
+  for (int rr = 0; rr < P_WROWS; ++rr)
+#pragma unroll
+    for (int c = 0; c < RP; ++c) acc[rr][c] = 0.f;
+  constexpr int PB = 4;      // column groups in flight per lane (times P_WROWS rows)
   for (int j0 = lane; j0 < m; j0 += 32 * PB) {
-    float v[PB];
+    float v[PB][P_WROWS];
 #pragma unroll
     for (int u = 0; u < PB; ++u) {
       const int j = j0 + 32 * u;
-      v[u] = j < m ? g[j] : 0.f;
+#pragma unroll
+      for (int rr = 0; rr < P_WROWS; ++rr) v[u][rr] = (j < m && rr < rows) ? g[(size_t)rr * m + j] : 0.f;
     }
 #pragma unroll
     for (int u = 0; u < PB; ++u) {
       const int j = j0 + 32 * u;
       if (j < m) {
+        float qv[RP];
+        load_q_row<RP>(q + (size_t)j * r, r, 1.f, qvec, qv);
 #pragma unroll
-        for (int c = 0; c < RP; ++c)
-          if (c < r) acc[c] = fmaf(v[u], __ldg(q + (size_t)j * r + c), acc[c]);
+        for (int rr = 0; rr < P_WROWS; ++rr)
+#pragma unroll
+          for (int c = 0; c < RP; ++c) acc[rr][c] = fmaf(v[u][rr], qv[c], acc[rr][c]);
       }
     }
   }
 #pragma unroll
-  for (int c = 0; c < RP; ++c) acc[c] = warp_sum(acc[c]);
-  if (lane == 0) {
-    float* p = P + M.p_off + (size_t)row * r;
+  for (int rr = 0; rr < P_WROWS; ++rr)
 #pragma unroll
-    for (int c = 0; c < RP; ++c) {
-      if (c < r) {
-        if (atomic_out) atomicAdd(p + c, acc[c]);
-        else p[c] = acc[c];
+    for (int c = 0; c < RP; ++c) acc[rr][c] = warp_sum(acc[rr][c]);
+  if (lane == 0) {
+#pragma unroll
+    for (int rr = 0; rr < P_WROWS; ++rr) {
+      if (rr < rows) {
+        float* p = P + M.p_off + (size_t)(row0 + rr) * r;
+#pragma unroll
+        for (int c = 0; c < RP; ++c) {
+          if (c < r) {
+            if (atomic_out) atomicAdd(p + c, acc[rr][c]);
+            else p[c] = acc[rr][c];
+          }
+        }
       }
     }
   }
@@ -195,28 +234,6 @@ extern "C" int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles,
   int rp = max_rank <= 1 ? 1 : max_rank <= 2 ? 2 : max_rank <= 4 ? 4 : max_rank <= 8 ? 8 : max_rank <= 16 ? 16 : 32;
   size_t smem = (size_t)CONEF_Q_MAX_ROWS * rp * sizeof(float);
   DISPATCH_RANK(max_rank, launch_q, mats, tiles, ntiles, bucket, aux, P, Q, smem, stream);
-}
-
-// Q[j, 0..r) scaled into registers.  With r a multiple of 4 and a 16-byte aligned block the row
-// comes in as 16-byte loads: scalar loads of a stride-r pattern cost r wavefronts of mostly unused
-// bytes per warp, which made the Q rows, not the gradient, the dominant load traffic.
-template <int RP>
-__device__ __forceinline__ void load_q_row(const float* __restrict__ q, int r, float q_scale, bool vec,
-                                           float (&qv)[RP]) {
-  if (RP >= 4 && vec) {
-#pragma unroll
-    for (int c = 0; c < RP; c += 4) {
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (c < r) x = __ldg(reinterpret_cast<const float4*>(q + c));
-      qv[c] = x.x * q_scale;
-      if (c + 1 < RP) qv[c + 1] = x.y * q_scale;
-      if (c + 2 < RP) qv[c + 2] = x.z * q_scale;
-      if (c + 3 < RP) qv[c + 3] = x.w * q_scale;
-    }
-  } else {
-#pragma unroll
-    for (int c = 0; c < RP; ++c) qv[c] = c < r ? __ldg(q + c) * q_scale : 0.f;
-  }
 }
 
 // ---------------------------------------------------------------------------

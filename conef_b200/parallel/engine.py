@@ -41,7 +41,7 @@ logger = logging.getLogger(__name__)
 _COMM_STREAMS: Dict[int, "torch.cuda.Stream"] = {}
 _SYMM_DISABLED = False
 
-P_ROWS = 8          # rows per CTA of the SIMT P kernel (csrc/powersgd.cu: P_WARPS)
+P_ROWS = 32         # rows per CTA of the SIMT P kernel (csrc/powersgd.cu: P_WARPS * P_WROWS)
 Q_COLS = 256        # columns per CTA of the Q kernel
 Q_MAX_ROWS = 1024
 QGROUP = ref.QUANT_GROUP
