@@ -50,6 +50,7 @@ def parse_args():
     ap.add_argument("--error-compressor", default=None,
                     help="replace the configuration's error store (e.g. topk, the reference's own hPowerSGD "
                          "store, for --config transformer); the headline configurations leave it unset")
+    ap.add_argument("--bucket-cap-mb", type=float, default=None, help="DDP bucket size (default: the trainer's)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--small", action="store_true", help="shrunken model, for smoke tests only (not a valid number)")
     return ap.parse_args()
@@ -193,6 +194,8 @@ def main():
     if not use_cuda:
         ac_dtype = None
         tkw = {k: v for k, v in tkw.items() if k != "channels_last"}
+    if args.bucket_cap_mb:
+        tkw["bucket_cap_mb"] = args.bucket_cap_mb
     trainer = DataParallelTrainer(model, opt_factory, loss_fn, reducer=ns, device=device,
                                   autocast_dtype=ac_dtype, **tkw)
     if args.impl == "restated" and trainer.state is not None:
@@ -309,7 +312,7 @@ def main():
                        "rank": ns.matrix_approximation_rank, "sketch_size": ns.sketch_size, "beta": ns.beta,
                        "l2": "256 MB buffer written between timed steps (outside the per-step event pair)",
                        "timing": "CUDA events per step on the launching stream, mean over steps, max over ranks",
-                       "comm": os.environ.get("CONEF_COMM", "auto"), "tc": os.environ.get("CONEF_TC", "1")},
+                       "comm": os.environ.get("CONEF_COMM", "auto"), "bucket_cap_mb": tkw.get("bucket_cap_mb", 25.0), "tc": os.environ.get("CONEF_TC", "1")},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
             "wall_s_timed_region": wall,
             "ef_buffer_mb": (state.ef_buffer_bytes() / 1e6) if state is not None else 0.0,
