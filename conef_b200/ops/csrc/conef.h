@@ -111,7 +111,7 @@ int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles, const floa
 // M_hat = P Q^T written into the bucket.  M = G + remembered error is formed on the fly
 // (alpha * unsketch(S) or the dense buffer); the residual M - M_hat goes to the error
 // store selected by ef_mode (dense buffer, or count sketch with decay beta).
-// smem_bytes = 2 * rows_per_cta * max W * 4 in sketch mode, else 0.
+// smem_bytes = rows_per_cta * max W * 4 in sketch mode, else 0.
 int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta,
                           float* bucket, const float* P, const float* Q, float q_scale,
                           float* sketch, const int32_t* tables, const int32_t* counts,

@@ -292,18 +292,18 @@ class PowerSGDEngine(_EngineBase):
         max_tiles = max((n for _, n in self.orth_tiles.values()), default=1)
         self.gram = torch.zeros(max(max_tiles, 1) * 2 * 1024, device=dev, dtype=torch.float32)
 
-        # decompress: rows per CTA in {8, 4, 2, 1}: the most that fit in shared memory (two
-        # copies of the sketch rows) while still giving every SM a few CTAs
+        # decompress: rows per CTA in {8, 4, 2, 1}: the most that fit in shared memory (one
+        # accumulator row of the sketch width per matrix row) while still giving every SM a few CTAs
         maxW = max(self.widths, default=0)
-        if maxW * 8 > SMEM_BUDGET:
+        if maxW * 4 > SMEM_BUDGET:
             raise native.NativeError(f"sketch width {maxW} does not fit in shared memory")
         total_rows = sum(e.n for e in plan.mats)
         self.d_rows = 1
         for cand in (8, 4, 2):
-            if cand * maxW * 8 <= SMEM_BUDGET // 2 and total_rows // cand >= 3 * 148:
+            if cand * maxW * 4 <= SMEM_BUDGET // 4 and total_rows // cand >= 3 * 148:
                 self.d_rows = cand
                 break
-        self.d_smem = 2 * self.d_rows * maxW * 4
+        self.d_smem = self.d_rows * maxW * 4
         d_tiles = [(k, rb) for k, e in enumerate(plan.mats) for rb in range(math.ceil(e.n / self.d_rows))]
         self.d_tiles = self._tiles(d_tiles)
         self.n_d_tiles = len(d_tiles)
