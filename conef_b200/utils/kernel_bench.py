@@ -187,6 +187,20 @@ def main():
         t = _time(lambda: cb.RandomBlock_hook(state, bucket).wait(), args.iters)
         per = {"ef": 4.0, "sketch": 2.2, "quant8": 2.5}[kind]      # passes over the tensors (r/w gradient + error store)
         record(f"RandomBlock_hook {kind} (whole bucket, ws=1)", t, per * nbytes, "gather+error update, scatter")
+        # the two kernels alone (the hook also draws the block offsets on the host and uploads them)
+        eng = state._engines[0]
+        beta = getattr(state, "beta", 0.0)
+        sk = native.ptr(eng.err_arena) if eng.ef_mode == native.EF_SKETCH else 0
+        de = native.ptr(eng.err_arena) if eng.ef_mode == native.EF_DENSE else 0
+        t = _time(lambda: native.check(lib.conef_randblock_gather(
+            eng.blks_dev.data_ptr(), eng.tiles.data_ptr(), eng.n_tiles, eng.rows, buf.data_ptr(),
+            eng.staging_blk.data_ptr(), 1.0, sk, native.ptr(eng.tables), native.ptr(eng.counts), de,
+            native.ptr(eng.codes), native.ptr(eng.scales), 1.0 - beta, beta, eng.ef_mode, eng.smem, st)), args.iters)
+        record(f"  randblock_gather kernel {kind}", t, (per - 0.2) * nbytes, "read G (+ error), write G / block, update error")
+        t = _time(lambda: native.check(lib.conef_randblock_scatter(
+            eng.blks_dev.data_ptr(), len(eng.plan.blocks), buf.data_ptr(), 0, 1, eng.staging_blk.data_ptr(), 1.0,
+            eng.plan.total_block, st)), args.iters)
+        record(f"  randblock_scatter kernel {kind}", t, 0.2 * nbytes, "read block, write block")
 
     # ---------------- hPowerSGD top-k error store ----------------
     if want("topk"):
