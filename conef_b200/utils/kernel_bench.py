@@ -64,12 +64,17 @@ def _peak_gbs() -> tuple:
     return 6650.0, "fallback"
 
 
-def _time(fn, iters, warmup=3):
+def _time(fn, iters, warmup=3, prep=None):
+    """Median device time of ``fn``; ``prep`` (untimed) restores the inputs before every call."""
     for _ in range(warmup):
+        if prep is not None:
+            prep()
         fn()
     torch.cuda.synchronize()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
     for s, e in ev:
+        if prep is not None:
+            prep()
         s.record()
         fn()
         e.record()
@@ -184,7 +189,9 @@ def main():
         state = cb.RandomBlockState(None, start_compression_iter=2, compression_ratio=0.1, **kw)
         state.iter = 2
         nbytes = 4 * sum(int(np.prod(s)) for s in shapes if len(s) > 1)
-        t = _time(lambda: cb.RandomBlock_hook(state, bucket).wait(), args.iters)
+        fresh = buf.clone()
+        refill = lambda: buf.copy_(fresh)       # the hook zeroes what it does not send
+        t = _time(lambda: cb.RandomBlock_hook(state, bucket).wait(), args.iters, prep=refill)
         per = {"ef": 4.0, "sketch": 2.2, "quant8": 2.5}[kind]      # passes over the tensors (r/w gradient + error store)
         record(f"RandomBlock_hook {kind} (whole bucket, ws=1)", t, per * nbytes, "gather+error update, scatter")
         # the two kernels alone (the hook also draws the block offsets on the host and uploads them)
@@ -195,7 +202,8 @@ def main():
         t = _time(lambda: native.check(lib.conef_randblock_gather(
             eng.blks_dev.data_ptr(), eng.tiles.data_ptr(), eng.n_tiles, eng.rows, buf.data_ptr(),
             eng.staging_blk.data_ptr(), 1.0, sk, native.ptr(eng.tables), native.ptr(eng.counts), de,
-            native.ptr(eng.codes), native.ptr(eng.scales), 1.0 - beta, beta, eng.ef_mode, eng.smem, st)), args.iters)
+            native.ptr(eng.codes), native.ptr(eng.scales), 1.0 - beta, beta, eng.ef_mode, eng.smem, st)), args.iters,
+            prep=refill)
         record(f"  randblock_gather kernel {kind}", t, (per - 0.2) * nbytes, "read G (+ error), write G / block, update error")
         t = _time(lambda: native.check(lib.conef_randblock_scatter(
             eng.blks_dev.data_ptr(), len(eng.plan.blocks), buf.data_ptr(), 0, 1, eng.staging_blk.data_ptr(), 1.0,
