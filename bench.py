@@ -35,7 +35,7 @@ if REPO not in sys.path:
     sys.path.insert(0, REPO)
 
 REFERENCE_UNAVAILABLE = (
-    "pip: '/root/reference' is not installable (neither setup.py nor pyproject.toml); its hooks also need "
+    "pip: the reference tree is not installable (neither setup.py nor pyproject.toml); its hooks also need "
     "torch-1.9 GradBucket methods, CuPy, pynvrtc and apex, none of which exist in this image")
 
 
