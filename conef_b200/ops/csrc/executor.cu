@@ -200,10 +200,10 @@ static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint3
                                       plan->alpha, plan->beta, plan->max_rank, s));
       }
     if (!csr)
-    RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_rows,
-                              plan->work, pmem, qmem, 1.0f, plan->sketch, plan->tables, plan->counts,
-                              dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank,
-                              plan->d_smem, s));
+      RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_rows,
+                                plan->work, pmem, qmem, 1.0f, plan->sketch, plan->tables, plan->counts,
+                                dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank,
+                                plan->d_smem, s));
     if (plan->topk) {
       RUN(conef_topk_keep(plan->mats, nm, (const int2*)plan->topk_tiles.tiles, plan->topk_tiles.n,
                           plan->dense_err, plan->topk_ratio, plan->topk_scratch, s));
