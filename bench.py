@@ -319,6 +319,8 @@ def main():
         }
         if state is not None and hasattr(state, "compression_stats"):
             out["compression_rate"] = state.compression_stats()[0]
+        if state is not None:
+            out["wire_mb_per_step_per_rank"] = state.wire_bytes_per_step() / 1e6
         os.write(real_stdout, (json.dumps(out) + "\n").encode())
     dist.barrier()
     dist.destroy_process_group()

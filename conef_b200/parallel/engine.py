@@ -689,7 +689,14 @@ class PowerSGDEngine(_EngineBase):
         P.fresh = int(fresh and self.nm > 0)
         P.seed = int(state.rng.randint(1_000_000_000)) if P.fresh else 0
         P.alpha, P.beta, P.eps = alpha, beta, eps
-        if self.world == 1 or self.symm is not None:
+        timers = getattr(state, "_timers", None)
+        if timers is not None and (self.world == 1 or self.symm is not None):
+            for name, phase in (("psgd/P=GQ", native.PHASE_P), ("psgd/reduce+orth+Q=GtP", native.PHASE_Q),
+                                ("psgd/reduce+decompress", native.PHASE_D)):
+                with timers.phase(name, self.device):
+                    native.check(lib.conef_psgd_run(P, phase, st), "psgd_run")
+                native.launch_count += P.launched
+        elif self.world == 1 or self.symm is not None:
             native.check(lib.conef_psgd_step(P, st), "psgd_step")
             native.launch_count += P.launched
         else:
@@ -741,6 +748,7 @@ class PowerSGDEngine(_EngineBase):
             self._bound = edict.get(bidx, False)
         state.total_numel_before_compression += plan.numel_before
         state.total_numel_after_compression += plan.numel_after
+        state.account_wire(plan.numel_after, plan.numel_before, bucket)
 
         if self.variant == "batched":
             work = self.work
@@ -1061,6 +1069,11 @@ class RandBlockEngine(_EngineBase):
             segs[k] = (s.g_off, s.dst_off, s.numel)
         self.segs_dev = native.upload_struct_array(segs, dev) if len(segs) else None
         self.blks_dev = torch.empty(max(blks.nbytes, 1), dtype=torch.uint8, device=dev)
+        # two pinned staging copies of the block table (the block offsets change every step); an
+        # event per copy says when its upload has been consumed
+        self._pin = [torch.empty(max(blks.nbytes, 1), dtype=torch.uint8).pin_memory() for _ in range(2)] \
+            if dev.type == "cuda" else None
+        self._pin_evt = [None, None]
         self.staging_unc = torch.empty(max(plan.total_unc, 1), device=dev, dtype=torch.float32)
         self.staging_blk = torch.empty(max(plan.total_block, 1), device=dev, dtype=torch.float32)
         self.err_arena = self.codes = self.scales = None
@@ -1126,12 +1139,20 @@ class RandBlockEngine(_EngineBase):
         for k, b in enumerate(plan.blocks):
             blks["start"][k] = int(state.rng.choice(b.numel))
         if nb:
-            host = torch.from_numpy(blks.view(np.uint8).reshape(-1).copy()).pin_memory()
-            self.blks_dev[: host.numel()].copy_(host, non_blocking=True)
+            k = self.step & 1
+            if self._pin_evt[k] is not None:
+                self._pin_evt[k].synchronize()          # the upload of two steps ago (long done)
+            raw = blks.view(np.uint8).reshape(-1)
+            self._pin[k].numpy()[: raw.size] = raw
+            self.blks_dev[: raw.size].copy_(self._pin[k][: raw.size], non_blocking=True)
+            if self._pin_evt[k] is None:
+                self._pin_evt[k] = torch.cuda.Event()
+            self._pin_evt[k].record()
         symm, slot = self.symm, self.step & 1
         stage_unc = symm.local(slot, 0) if symm else self.staging_unc
         stage_blk = symm.local(slot, 1) if symm else self.staging_blk
         state.compressed_tensor_memory[bidx] = stage_blk[: plan.total_block]
+        state.account_wire(plan.total_unc + plan.total_block, buf.numel(), bucket)
         bp = buf.data_ptr()
         beta = getattr(state, "beta", 0.0)
         if plan.total_unc:

@@ -131,6 +131,7 @@ def _powersgd_torch(state, bucket, group, *, transposed_sketch=False) -> torch.f
     plan = planlib.build_powersgd_plan(buf, grads, state.matrix_approximation_rank, state.min_compression_rate)
     state.total_numel_before_compression += plan.numel_before
     state.total_numel_after_compression += plan.numel_after
+    state.account_wire(plan.numel_after, plan.numel_before, bucket)
 
     dense_ef = state.use_error_feedback and not state.use_error_compression
     conef = state.use_error_feedback and state.use_error_compression
@@ -268,6 +269,7 @@ def _batched_torch(state, bucket, group):
     rank = min(side, state.matrix_approximation_rank)
     state.total_numel_before_compression += total
     state.total_numel_after_compression += side * state.matrix_approximation_rank * 2
+    state.account_wire(side * state.matrix_approximation_rank * 2, total, bucket)
     _report_compression_stats(bucket, state)
 
     padded = torch.zeros(side * side, device=device, dtype=dtype)
@@ -330,6 +332,7 @@ def UnbiasedMtrx_hook(state: unbiasedMtrxState, bucket: dist.GradBucket) -> torc
                                        state.min_compression_rate)
     state.total_numel_before_compression += plan.numel_before
     state.total_numel_after_compression += plan.numel_after
+    state.account_wire(plan.numel_after, plan.numel_before, bucket)
     mats = [buf[e.g_off : e.g_off + e.numel].view(e.n, e.m) for e in plan.mats]
     unc = (torch.cat([buf[s.g_off : s.g_off + s.numel] for s in plan.segs])
            if plan.segs else torch.empty(0, device=device, dtype=dtype))
@@ -400,6 +403,7 @@ def _randblock_torch(state, bucket, group, *, unbiased: bool) -> torch.futures.F
             state.compressed_tensor_memory[bidx].numel() != plan.total_block:
         state.compressed_tensor_memory[bidx] = torch.empty(plan.total_block, dtype=torch.float32, device=device)
     staging = state.compressed_tensor_memory[bidx]
+    state.account_wire(plan.total_unc + plan.total_block, buf.numel(), bucket)
 
     starts = _draw_starts(state, plan)
     for cnt, (b, t, start) in enumerate(zip(plan.blocks, tens, starts)):

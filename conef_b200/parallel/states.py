@@ -32,7 +32,7 @@ from ..compressors.other import ERROR_COMPRESSORS
 logger = logging.getLogger(__name__)
 
 # slots that never go into a checkpoint / pickle
-_RUNTIME_SLOTS = ("process_group", "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen")
+_RUNTIME_SLOTS = ("process_group", "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen")
 
 
 def _to_cpu(obj):
@@ -77,7 +77,8 @@ class _StateBase:
 
     def _init_runtime(self):
         self._engines = {}
-        self._timers = None
+        self._timers = None              # utils.tracing.PhaseTimer when phase timing is on
+        self._wire = [0, 0, 0]           # fp32 elements sent, elements before compression, compressed steps
         self._status_checked = 0
         self._process_iters = 0      # reduced iterations seen by this process (not persisted)
         self._sig_seen = set()       # buckets whose layout was checked in this process
@@ -158,6 +159,33 @@ class _StateBase:
         self._process_iters = 0
 
     # -- metrics -----------------------------------------------------------
+    def account_wire(self, numel_sent: int, numel_before: int, bucket) -> None:
+        """Called by every compressed hook invocation: what this bucket puts on the wire."""
+        self._wire[0] += int(numel_sent)
+        self._wire[1] += int(numel_before)
+        if bucket.is_last():
+            self._wire[2] += 1
+
+    def wire_bytes_per_step(self) -> float:
+        """Bytes (fp32 payloads) this rank contributes to the collectives of one compressed step,
+        averaged over the compressed steps of this process; 0 before the first one."""
+        return 4.0 * self._wire[0] / self._wire[2] if self._wire[2] else 0.0
+
+    def wire_compression_rate(self) -> float:
+        """Gradient elements per element sent, over the compressed steps of this process."""
+        return self._wire[1] / self._wire[0] if self._wire[0] else 0.0
+
+    def enable_phase_timing(self, enabled: bool = True) -> None:
+        """Time the phases of every compressed hook call with CUDA events on the hook's stream
+        (P pass, reduction + Gram-Schmidt + Q pass, reduction + decompress).  While it is on, the
+        native executor issues the phases as separate calls instead of replaying its graph."""
+        from ..utils.tracing import PhaseTimer
+        self._timers = PhaseTimer() if enabled else None
+
+    def phase_summary(self) -> Dict[str, Dict[str, float]]:
+        """``{phase: {"ms", "calls", "ms_per_call"}}`` since phase timing was switched on."""
+        return self._timers.summary() if self._timers is not None else {}
+
     def ef_buffer_bytes(self) -> int:
         """Bytes of persistent error-feedback state (the ConEF headline metric)."""
         def size(o):
@@ -191,7 +219,7 @@ class PowerSGDState(_StateBase):
         "iter", "total_numel_before_compression", "total_numel_after_compression",
         "compression_stats_logging_frequency", "next_stats_report",
         # additions
-        "error_compressor", "error_rank", "hash_seed", "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen",
+        "error_compressor", "error_rank", "hash_seed", "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen",
         "bucket_signatures",
     ]
 
@@ -281,7 +309,7 @@ class RandomBlockState(_StateBase):
         "process_group", "compression_ratio", "start_compression_iter", "n_blocks",
         "use_error_compression", "beta", "sketch_size", "use_error_feedback", "rng", "error_dict",
         "iter", "compression_stats_logging_frequency", "next_stats_report", "compressed_tensor_memory",
-        "error_compressor", "hash_seed", "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen",
+        "error_compressor", "hash_seed", "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen",
         "bucket_signatures",
     ]
 
@@ -329,7 +357,7 @@ class UnbiasedRandomBlockState(_StateBase):
     __slots__ = [
         "process_group", "compression_ratio", "start_compression_iter", "rng", "iter",
         "compression_stats_logging_frequency", "next_stats_report", "compressed_tensor_memory",
-        "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen",
+        "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen",
         "bucket_signatures",
     ]
 
@@ -356,7 +384,7 @@ class unbiasedMtrxState(_StateBase):
         "orthogonalization_epsilon", "rng", "p_memory_dict", "q_memory_dict", "iter",
         "total_numel_before_compression", "total_numel_after_compression",
         "compression_stats_logging_frequency", "next_stats_report",
-        "_engines", "_timers", "_status_checked", "_process_iters", "_sig_seen",
+        "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen",
         "bucket_signatures",
     ]
 

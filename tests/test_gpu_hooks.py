@@ -370,3 +370,24 @@ def test_decompress_without_atomics_matches_atomic_kernel(single_rank_group, mon
     for x, y in zip(a, b):
         torch.testing.assert_close(x, y, **TOL)
     torch.testing.assert_close(sa, sb, **TOL)
+
+
+def test_phase_timing_and_wire_bytes_on_gpu(single_rank_group, monkeypatch):
+    """With phase timing on, the executor issues its three phases separately and brackets them with
+    CUDA events; results stay those of the untimed path."""
+    kw = dict(matrix_approximation_rank=4, use_error_feedback=True, warm_start=True, use_error_compression=True,
+              sketch_size=0.1)
+    monkeypatch.setenv("CONEF_TC", "0")
+    plain = _steps(cb.powerSGD_hook, _powersgd_states(DEV, **kw), DEV, monkeypatch, "native", steps=4)
+    state = _powersgd_states(DEV, **kw)
+    state.enable_phase_timing()
+    timed = _steps(cb.powerSGD_hook, state, DEV, monkeypatch, "native", steps=4)
+    for a, b in zip(plain, timed):
+        torch.testing.assert_close(a, b, **TOL)
+    summary = state.phase_summary()
+    assert set(summary) == {"psgd/P=GQ", "psgd/reduce+orth+Q=GtP", "psgd/reduce+decompress"}
+    assert all(v["calls"] == 4 and v["ms"] > 0 for v in summary.values())
+    plan = planlib.build_powersgd_plan(FakeBucket(SHAPES).buffer(), FakeBucket(SHAPES).gradients(), 4, 2)
+    assert state.wire_bytes_per_step() == 4.0 * plan.numel_after
+    state.enable_phase_timing(False)
+    assert state.phase_summary() == {}

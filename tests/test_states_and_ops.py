@@ -278,3 +278,31 @@ def test_randomblock_resume_is_bit_exact(single_rank_group):
     b2 = FakeBucket(SHAPES)
     b2.refill(9)
     assert torch.equal(want, cb.RandomBlock_hook(r, b2).wait())
+
+
+def test_wire_bytes_per_step_matches_the_plan(single_rank_group):
+    """What a compressed step puts on the wire: P + Q + uncompressed tensors for PowerSGD,
+    blocks + uncompressed tensors for RandomBlock."""
+    import conef_b200 as cb
+    from conef_b200.parallel import plan as planlib
+    shapes = [(64, 48), (48,), (32, 16, 3, 3), (5,)]
+    b = FakeBucket(shapes)
+    s = cb.PowerSGDState(None, matrix_approximation_rank=2, start_powerSGD_iter=2)
+    s.iter = 2
+    assert s.wire_bytes_per_step() == 0.0
+    for _ in range(3):
+        cb.powerSGD_hook(s, b).wait()
+    plan = planlib.build_powersgd_plan(b.buffer(), b.gradients(), 2, 2)
+    assert s.wire_bytes_per_step() == 4.0 * plan.numel_after
+    assert s.wire_bytes_per_step() == 4.0 * (plan.total_p + plan.total_q + plan.total_unc)
+    assert abs(s.wire_compression_rate() - s.compression_stats()[0]) < 1e-9
+    r = cb.RandomBlockState(None, compression_ratio=0.1, start_compression_iter=2)
+    r.iter = 2
+    for _ in range(2):
+        cb.RandomBlock_hook(r, b).wait()
+    sent = sum(max(1, int(0.1 * n)) for n in (64 * 48, 32 * 16 * 9)) + 48 + 5
+    assert r.wire_bytes_per_step() == 4.0 * sent
+    # the counters are run-time only: a restored state starts counting again
+    s2 = cb.PowerSGDState(None, matrix_approximation_rank=2, start_powerSGD_iter=2)
+    s2.load_state_dict(s.state_dict(), device="cpu")
+    assert s2.wire_bytes_per_step() == 0.0
