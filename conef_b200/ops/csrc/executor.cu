@@ -282,5 +282,56 @@ extern "C" int conef_psgd_step(ConefPsgdPlan* plan, cudaStream_t s) {
   return 0;
 }
 
+// ---------------------------------------------------------------------------
+// Random-block family: the order of operations of RandBlockEngine.run in parallel/engine.py.
+#define RUNB(call)                     \
+  do {                                 \
+    int rc_ = (call);                  \
+    if (rc_ != 0) return rc_;          \
+    ++plan->launched;                  \
+  } while (0)
+
+extern "C" int conef_randblock_run(ConefRandblockPlan* plan, int phases, cudaStream_t s) {
+  plan->launched = 0;
+  const int ws = plan->world, slot = plan->slot & 1;
+  const bool symm = plan->has_symm && ws > 1;
+  float* stage_unc = symm ? plan->local_unc[slot] : plan->staging_unc;
+  float* stage_blk = symm ? plan->local_blk[slot] : plan->staging_blk;
+  const float inv_ws = 1.0f / (float)ws;
+  if (phases & 1) {
+    if (plan->total_unc)
+      RUNB(conef_gather_segments(plan->segs, plan->nsegs, plan->work, nullptr, stage_unc, plan->total_unc, s));
+    if (plan->nblks)
+      // gather scale 0 = unbiased estimator: the kernel divides by the selection probability
+      RUNB(conef_randblock_gather(plan->blks, (const int2*)plan->tiles.tiles, plan->tiles.n, plan->rows_per_cta,
+                                  plan->work, stage_blk, plan->unbiased ? 0.0f : 1.0f,
+                                  plan->ef_mode == CONEF_EF_SKETCH ? plan->sketch : nullptr, plan->tables,
+                                  plan->counts, plan->ef_mode == CONEF_EF_DENSE ? plan->dense_err : nullptr,
+                                  plan->qcodes, plan->qscales, plan->alpha, plan->beta, plan->ef_mode, plan->smem, s));
+  }
+  if (phases & 2) {
+    const float* const* peers_unc = nullptr;
+    const float* const* peers_blk = nullptr;
+    const float *loc_unc = stage_unc, *loc_blk = stage_blk;
+    if (symm) {
+      plan->epoch += 1;
+      RUNB(conef_signal_peers(plan->peer_flags, ws, plan->rank, plan->epoch, s));
+      RUNB(conef_wait_flags(plan->my_flags, ws, plan->epoch, plan->status, plan->spin_limit, s));
+      peers_unc = plan->peer_unc[slot];
+      peers_blk = plan->peer_blk[slot];
+      loc_unc = loc_blk = nullptr;
+    }
+    if (plan->total_unc)
+      RUNB(conef_scatter_segments(plan->segs, plan->nsegs, plan->work, peers_unc, ws, loc_unc, inv_ws, nullptr,
+                                  plan->total_unc, s));
+    if (plan->nblks)
+      RUNB(conef_randblock_scatter(plan->blks, plan->nblks, plan->work, peers_blk, ws, loc_blk, inv_ws,
+                                   plan->total_block, s));
+  }
+  return 0;
+}
+
+extern "C" int conef_randblock_plan_size(void) { return (int)sizeof(ConefRandblockPlan); }
+
 // Size of the plan structure, so that a binding can verify its mirror of the layout.
 extern "C" int conef_psgd_plan_size(void) { return (int)sizeof(ConefPsgdPlan); }

@@ -98,6 +98,35 @@ typedef struct ConefPsgdPlan {
                                  // `pad` of each list carries the class's max m * groups(m)
 } ConefPsgdPlan;
 
+// ---- random-block family ---------------------------------------------------------------------------
+typedef struct ConefRandblockPlan {
+  // static
+  const ConefBlk* blks;  int nblks, rows_per_cta;      // the block table is re-uploaded every step (new offsets)
+  ConefTileList tiles;
+  const ConefSeg* segs;  int nsegs, ef_mode;
+  long long total_unc, total_block;
+  float* staging_unc;  float* staging_blk;              // local staging (no peer memory)
+  float* sketch;  const int32_t* tables;  const int32_t* counts;
+  float* dense_err;  int8_t* qcodes;  float* qscales;
+  size_t smem;
+  int* status;
+  int world, rank, has_symm, unbiased;
+  uint32_t* const* peer_flags;  const uint32_t* my_flags;
+  const float* const* peer_unc[2];  const float* const* peer_blk[2];
+  float* local_unc[2];  float* local_blk[2];
+  long long spin_limit;
+  // per step
+  float* work;  int slot, pad0;
+  unsigned int epoch;  float alpha, beta;
+  int launched;
+} ConefRandblockPlan;
+
+// Gather (block -> staging, error update), reduction over peer memory (bounded wait), scatter.
+// phases: 1 = gather, 2 = scatter; without peer memory and world > 1 the caller all-reduces the two
+// staging buffers between the phases.
+int conef_randblock_run(ConefRandblockPlan* plan, int phases, cudaStream_t stream);
+int conef_randblock_plan_size(void);
+
 enum { CONEF_PHASE_P = 1, CONEF_PHASE_Q = 2, CONEF_PHASE_D = 4, CONEF_PHASE_ALL = 7 };
 
 // phases: P = up to and including P = G Q (+ error terms);  Q = reduction of P (peer memory only),

@@ -38,11 +38,22 @@ k_topk_hist(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, c
   const int len = (int)min((long long)TK_CHUNK, numel - lo);
   const float* x = err + M.g_off + lo;
   const uint32_t prefix = PASS == 0 ? 0u : st[t.x].prefix;
-  for (int i = threadIdx.x; i < len; i += TK_THREADS) {
-    const uint32_t b = mag_bits(__ldg(x + i));
+  auto count = [&](float v) {
+    const uint32_t b = mag_bits(v);
     if (PASS == 0) atomicAdd(&h[b >> 20], 1u);
     else if (PASS == 1) { if ((b >> 20) == prefix) atomicAdd(&h[(b >> 10) & 1023u], 1u); }
     else { if ((b >> 10) == prefix) atomicAdd(&h[b & 1023u], 1u); }
+  };
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {        // 16-byte loads where the chunk starts aligned
+    const int len4 = len >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    for (int i = threadIdx.x; i < len4; i += TK_THREADS) {
+      const float4 v = __ldg(x4 + i);
+      count(v.x); count(v.y); count(v.z); count(v.w);
+    }
+    for (int i = (len4 << 2) + threadIdx.x; i < len; i += TK_THREADS) count(__ldg(x + i));
+  } else {
+    for (int i = threadIdx.x; i < len; i += TK_THREADS) count(__ldg(x + i));
   }
   __syncthreads();
   uint32_t* g = hist + (size_t)t.x * TK_BINS;
@@ -115,9 +126,27 @@ k_topk_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, 
   const int len = (int)min((long long)TK_CHUNK, numel - lo);
   float* x = err + M.g_off + lo;
   const uint32_t thr = st[t.x].prefix;      // the 31 magnitude bits of the k-th largest entry
-  for (int i = threadIdx.x; i < len; i += TK_THREADS) {
-    const float v = x[i];
-    if (mag_bits(v) < thr) x[i] = 0.f;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    const int len4 = len >> 2;
+    float4* x4 = reinterpret_cast<float4*>(x);
+    for (int i = threadIdx.x; i < len4; i += TK_THREADS) {
+      float4 v = x4[i];
+      const bool cx = mag_bits(v.x) < thr, cy = mag_bits(v.y) < thr, cz = mag_bits(v.z) < thr, cw = mag_bits(v.w) < thr;
+      if (cx | cy | cz | cw) {
+        if (cx) v.x = 0.f;
+        if (cy) v.y = 0.f;
+        if (cz) v.z = 0.f;
+        if (cw) v.w = 0.f;
+        x4[i] = v;
+      }
+    }
+    for (int i = (len4 << 2) + threadIdx.x; i < len; i += TK_THREADS)
+      if (mag_bits(x[i]) < thr) x[i] = 0.f;
+  } else {
+    for (int i = threadIdx.x; i < len; i += TK_THREADS) {
+      const float v = x[i];
+      if (mag_bits(v) < thr) x[i] = 0.f;
+    }
   }
 }
 

@@ -99,6 +99,28 @@ class PsgdPlan(C.Structure):
         ("ell", C.c_void_p), ("ell_hdr", C.c_void_p), ("dc_tiles", TileList * 4),
     ]
 
+class RandblockPlan(C.Structure):
+    """Mirror of ``ConefRandblockPlan`` (csrc/executor.h): field order and types must match."""
+    _fields_ = [
+        ("blks", C.c_void_p), ("nblks", C.c_int), ("rows_per_cta", C.c_int),
+        ("tiles", TileList),
+        ("segs", C.c_void_p), ("nsegs", C.c_int), ("ef_mode", C.c_int),
+        ("total_unc", C.c_longlong), ("total_block", C.c_longlong),
+        ("staging_unc", C.c_void_p), ("staging_blk", C.c_void_p),
+        ("sketch", C.c_void_p), ("tables", C.c_void_p), ("counts", C.c_void_p),
+        ("dense_err", C.c_void_p), ("qcodes", C.c_void_p), ("qscales", C.c_void_p),
+        ("smem", C.c_size_t), ("status", C.c_void_p),
+        ("world", C.c_int), ("rank", C.c_int), ("has_symm", C.c_int), ("unbiased", C.c_int),
+        ("peer_flags", C.c_void_p), ("my_flags", C.c_void_p),
+        ("peer_unc", C.c_void_p * 2), ("peer_blk", C.c_void_p * 2),
+        ("local_unc", C.c_void_p * 2), ("local_blk", C.c_void_p * 2),
+        ("spin_limit", C.c_longlong),
+        ("work", C.c_void_p), ("slot", C.c_int), ("pad0", C.c_int),
+        ("epoch", C.c_uint), ("alpha", C.c_float), ("beta", C.c_float),
+        ("launched", C.c_int),
+    ]
+
+
 _SIGNATURES = {
     "conef_version": ([], C.c_int),
     "conef_build_hash_table": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp], C.c_int),
@@ -140,6 +162,8 @@ _SIGNATURES = {
     "conef_topk_keep": ([vp, C.c_int, vp, C.c_int, vp, C.c_float, vp, vp], C.c_int),
     "conef_topk_chunk": ([], C.c_int),
     "conef_psgd_plan_size": ([], C.c_int),
+    "conef_randblock_run": ([C.POINTER(RandblockPlan), C.c_int, vp], C.c_int),
+    "conef_randblock_plan_size": ([], C.c_int),
     "conef_psgd_step": ([C.POINTER(PsgdPlan), vp], C.c_int),
     "conef_psgd_plan_release": ([C.POINTER(PsgdPlan)], C.c_int),
     "conef_epoch_word": ([vp, C.c_uint32, C.c_int, vp], C.c_int),
@@ -156,7 +180,7 @@ _OPTIONAL = {}
 # How many kernels one call of an entry point enqueues (memsets not counted);
 # everything not listed launches exactly one.  Host-only entry points launch none.
 _KERNELS_PER_CALL = {
-    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_lowrank_correct": 2, "conef_topk_keep": 7, "conef_topk_chunk": 0, "conef_dc_groups": 0, "conef_psgd_run": 0, "conef_psgd_plan_size": 0, "conef_psgd_step": 0, "conef_psgd_plan_release": 0, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
+    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_lowrank_correct": 2, "conef_topk_keep": 7, "conef_topk_chunk": 0, "conef_dc_groups": 0, "conef_psgd_run": 0, "conef_psgd_plan_size": 0, "conef_randblock_run": 0, "conef_randblock_plan_size": 0, "conef_psgd_step": 0, "conef_psgd_plan_release": 0, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
     "conef_ipc_get_handle": 0, "conef_ipc_open_handle": 0, "conef_ipc_close_handle": 0,
     "conef_cpu_hash_table": 0, "conef_cpu_sketch_query": 0, "conef_cpu_sketch_update": 0,
     "conef_cpu_gram_schmidt": 0,
@@ -224,6 +248,9 @@ def lib():
             fn = getattr(handle, name)
             fn.argtypes = argtypes
             fn.restype = restype
+    if handle.conef_randblock_plan_size() != C.sizeof(RandblockPlan):
+        raise NativeError(f"RandblockPlan mirrors {C.sizeof(RandblockPlan)} bytes, the library expects "
+                          f"{handle.conef_randblock_plan_size()}: rebuild with `python -m conef_b200.ops.build`")
     if handle.conef_psgd_plan_size() != C.sizeof(PsgdPlan):
         raise NativeError(f"PsgdPlan mirrors {C.sizeof(PsgdPlan)} bytes, the library expects "
                           f"{handle.conef_psgd_plan_size()}: rebuild with `python -m conef_b200.ops.build`")

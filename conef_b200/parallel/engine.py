@@ -1079,6 +1079,7 @@ class RandBlockEngine(_EngineBase):
         self.err_arena = self.codes = self.scales = None
         self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_block, 4)], group, dev) \
             if self.world > 1 else None
+        self.exec_plan, self._exec_key = None, None
 
     def bind_state(self, state, bidx):
         if self.ef_mode == native.EF_NONE:
@@ -1127,6 +1128,53 @@ class RandBlockEngine(_EngineBase):
                                            seed=getattr(state, "hash_seed", 0), storage=view))
         state.error_dict[bidx] = new
 
+    def _build_exec(self) -> None:
+        """Plan of the native executor (csrc/executor.h:ConefRandblockPlan)."""
+        P, plan, ptr = native.RandblockPlan(), self.plan, native.ptr
+        P.blks, P.nblks, P.rows_per_cta = ptr(self.blks_dev), len(plan.blocks), self.rows
+        P.tiles = native.TileList(ptr(self.tiles) if self.n_tiles else None, self.n_tiles, 0)
+        P.segs, P.nsegs, P.ef_mode = ptr(self.segs_dev), len(plan.segs), self.ef_mode
+        P.total_unc, P.total_block = plan.total_unc, plan.total_block
+        P.staging_unc, P.staging_blk = ptr(self.staging_unc), ptr(self.staging_blk)
+        P.sketch = ptr(self.err_arena) if self.ef_mode == native.EF_SKETCH else None
+        P.dense_err = ptr(self.err_arena) if self.ef_mode == native.EF_DENSE else None
+        P.tables, P.counts = ptr(self.tables), ptr(self.counts)
+        P.qcodes, P.qscales = ptr(self.codes), ptr(self.scales)
+        P.smem, P.status = self.smem, ptr(self.status)
+        P.world, P.rank, P.has_symm, P.unbiased = self.world, self.rank, int(self.symm is not None), int(self.unbiased)
+        symm = self.symm
+        if symm is not None:
+            P.peer_flags, P.my_flags = symm.peer_flags_dev(), symm.flags_ptr()
+            for slot in (0, 1):
+                P.peer_unc[slot], P.peer_blk[slot] = symm.peer_ptrs_dev(slot, 0), symm.peer_ptrs_dev(slot, 1)
+                P.local_unc[slot], P.local_blk[slot] = ptr(symm.local(slot, 0)), ptr(symm.local(slot, 1))
+        P.spin_limit = DEFAULT_SPIN_LIMIT
+        self.exec_plan = P
+        self._exec_key = (ptr(self.err_arena), ptr(self.codes))
+
+    def _run_native(self, state, buf, stage_unc, stage_blk, st) -> None:
+        """One step through the native executor: one host call (two with NCCL in between when no
+        peer memory could be set up)."""
+        if self.exec_plan is None or self._exec_key != (native.ptr(self.err_arena), native.ptr(self.codes)):
+            self._build_exec()
+        P, lib, plan = self.exec_plan, self.lib, self.plan
+        beta = getattr(state, "beta", 0.0)
+        P.work, P.slot, P.epoch = buf.data_ptr(), self.step & 1, self.epoch & 0xFFFFFFFF
+        P.alpha, P.beta = 1.0 - beta, beta
+        if self.world == 1 or self.symm is not None:
+            native.check(lib.conef_randblock_run(P, 3, st), "randblock_run")
+            native.launch_count += P.launched
+        else:
+            native.check(lib.conef_randblock_run(P, 1, st), "randblock_run(gather)")
+            native.launch_count += P.launched
+            if plan.total_unc:
+                self._nccl_sum(stage_unc[: plan.total_unc], self.group)
+            if len(plan.blocks):
+                self._nccl_sum(stage_blk[: plan.total_block], self.group)
+            native.check(lib.conef_randblock_run(P, 2, st), "randblock_run(scatter)")
+            native.launch_count += P.launched
+        self.epoch = int(P.epoch)
+
     def run(self, state, bucket, buf):
         lib, plan, dev = self.lib, self.plan, self.device
         bidx, ws = bucket.index(), self.world
@@ -1153,6 +1201,10 @@ class RandBlockEngine(_EngineBase):
         stage_blk = symm.local(slot, 1) if symm else self.staging_blk
         state.compressed_tensor_memory[bidx] = stage_blk[: plan.total_block]
         state.account_wire(plan.total_unc + plan.total_block, buf.numel(), bucket)
+        if os.environ.get("CONEF_EXECUTOR", "native") == "native":
+            self._run_native(state, buf, stage_unc, stage_blk, st)
+            self.step += 1
+            return
         bp = buf.data_ptr()
         beta = getattr(state, "beta", 0.0)
         if plan.total_unc:

@@ -187,3 +187,47 @@ def _ddp_worker(rank, world, name):
 def test_ddp_two_gpus_ranks_agree(name):
     _need_two_gpus()
     run_ranks(_ddp_worker, world=2, args=(name,), backend="nccl")
+
+
+def _graph_replay_worker(rank, world, graph):
+    """Ten steps over peer memory: with graphs the epochs of the in-kernel collectives come from a
+    device word; the ranks must stay bit-identical and match the run with direct launches."""
+    os.environ["CONEF_COMM"] = "auto"
+    os.environ["CONEF_TC"] = "0"
+    os.environ["CONEF_GRAPH"] = graph
+    dev = torch.device("cuda", rank)
+    kw = dict(matrix_approximation_rank=4, use_error_feedback=True, warm_start=True, use_error_compression=True,
+              sketch_size=0.1)
+    s = cb.PowerSGDState(None, start_powerSGD_iter=2, **kw)
+    s.iter = 2
+    fb = FakeBucket(SHAPES)
+    plan = planlib.build_powersgd_plan(fb.buffer(), fb.gradients(), 4, 2)
+    g = torch.Generator().manual_seed(0)
+    s.p_memory_dict[0] = torch.zeros(plan.total_p).to(dev)
+    s.q_memory_dict[0] = torch.randn(plan.total_q, generator=g).to(dev)
+    b = FakeBucket(SHAPES, device=dev, seed=100 + rank)
+    outs = []
+    for i in range(10):
+        b.refill(300 + 10 * i + rank)
+        outs.append(cb.powerSGD_hook(s, b).wait().clone())
+    torch.cuda.synchronize()
+    s.check_status()
+    eng = s._engines[0]
+    assert eng.symm is not None
+    assert eng.exec_plan.graph_replays == (6 if graph == "1" else 0)
+    last = outs[-1]
+    both = [torch.zeros_like(last) for _ in range(world)]
+    dist.all_gather(both, last.contiguous())
+    assert torch.equal(both[0], both[1]) and torch.isfinite(last).all()
+    return torch.stack(outs).cpu()
+
+
+def _graph_vs_direct_worker(rank, world):
+    a = _graph_replay_worker(rank, world, "1")
+    b = _graph_replay_worker(rank, world, "0")
+    torch.testing.assert_close(a, b, rtol=2e-3, atol=2e-4)
+
+
+def test_graph_replay_over_peer_memory_two_gpus():
+    _need_two_gpus()
+    run_ranks(_graph_vs_direct_worker, world=2, args=(), backend="nccl")
