@@ -250,7 +250,7 @@ extern "C" int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles,
 // A random shared-memory access per element costs about as much as streaming the element itself
 // (measured: 42 us to stream a 147 MB matrix, +45 us per gather or atomic), hence no gather.
 template <int RP, int RB>
-__global__ void __launch_bounds__(D_THREADS)
+__global__ void __launch_bounds__(D_THREADS, RP <= 8 ? 4 : 1)      // 64 registers: four CTAs per SM
 k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles,
                   float* __restrict__ bucket, const float* __restrict__ P, const float* __restrict__ Q,
                   float q_scale, float* __restrict__ sketch, const int32_t* __restrict__ tables,

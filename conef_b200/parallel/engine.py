@@ -303,6 +303,8 @@ class PowerSGDEngine(_EngineBase):
             if cand * maxW * 4 <= SMEM_BUDGET // 4 and total_rows // cand >= 3 * 148:
                 self.d_rows = cand
                 break
+        if os.environ.get("CONEF_D_ROWS"):
+            self.d_rows = int(os.environ["CONEF_D_ROWS"])
         self.d_smem = self.d_rows * maxW * 4
         d_tiles = [(k, rb) for k, e in enumerate(plan.mats) for rb in range(math.ceil(e.n / self.d_rows))]
         self.d_tiles = self._tiles(d_tiles)
