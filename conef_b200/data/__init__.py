@@ -1,5 +1,6 @@
 """Data utilities: synthetic datasets of the benchmark shapes, corpus batching, MLM masking, WordPiece."""
 from .corpus import Corpus, Dictionary, batchify, get_batch
+from . import glue
 from .masking import mask_tokens
 from .pretraining import (PretrainingShard, ShardPrefetcher, create_training_instances, instances_to_arrays,
                           load_shard, read_documents, shard_files, write_shard)

@@ -231,3 +231,52 @@ def test_bert_driver_trains_from_shard_files(tmp_path):
                    check=True, env=env, timeout=600)
     lines = [json.loads(l) for l in (out / "log.jsonl").read_text().splitlines()]
     assert any(l.get("step") == "summary" for l in lines)
+
+
+def test_glue_processors_and_features(tmp_path):
+    from conef_b200.data import glue
+    vf, _ = _toy_corpus(tmp_path)
+    tok = data.BertTokenizer(str(vf))
+    d = tmp_path / "mrpc"
+    d.mkdir()
+    (d / "train.tsv").write_text("Quality\t#1 ID\t#2 ID\t#1 String\t#2 String\n"
+                                 "1\t11\t12\tthe cat sat\tthe dog ran fast\n0\t13\t14\tblue house\tred tree\n")
+    (d / "dev.tsv").write_text("Quality\t#1 ID\t#2 ID\t#1 String\t#2 String\n1\t1\t2\tcat\tdog\n")
+    proc = glue.PROCESSORS["mrpc"]()
+    train = proc.get_train_examples(str(d))
+    assert [(e.text_a, e.text_b, e.label) for e in train] == [("the cat sat", "the dog ran fast", "1"),
+                                                              ("blue house", "red tree", "0")]
+    assert len(proc.get_dev_examples(str(d))) == 1 and proc.get_labels() == ["0", "1"]
+    feats = glue.convert_examples_to_features(train, proc.get_labels(), 12, tok)
+    f = feats[0]
+    assert len(f.input_ids) == len(f.input_mask) == len(f.segment_ids) == 12 and f.label_id == 1
+    assert f.input_ids[0] == tok.vocab["[CLS]"] and sum(f.input_mask) == 3 + 3 + 4
+    assert f.segment_ids[:5] == [0] * 5 and f.segment_ids[5:10] == [1] * 5 and f.segment_ids[10:] == [0, 0]
+    # truncation keeps the pair within the budget; single sentences get one separator
+    short = glue.convert_examples_to_features(train, proc.get_labels(), 8, tok)[0]
+    assert sum(short.input_mask) == 8 and short.input_ids.count(tok.vocab["[SEP]"]) == 2
+    c = tmp_path / "cola"
+    c.mkdir()
+    (c / "train.tsv").write_text("gj04\t1\t\tthe cat sat on the mat\n")
+    ex = glue.DataProcessor("CoLA").get_train_examples(str(c))[0]
+    assert (ex.text_a, ex.text_b, ex.label) == ("the cat sat on the mat", None, "1")
+    one = glue.convert_examples_to_features([ex], ["0", "1"], 16, tok)[0]
+    assert one.input_ids.count(tok.vocab["[SEP]"]) == 1 and set(one.segment_ids) == {0}
+    with pytest.raises(KeyError):
+        glue.DataProcessor("nope")
+
+
+def test_extract_features_script(tmp_path):
+    import json, subprocess, sys
+    vf, _ = _toy_corpus(tmp_path)
+    (tmp_path / "in.txt").write_text("the cat sat ||| the dog ran\n\nblue house\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    subprocess.run([sys.executable, os.path.join(root, "examples/bert_pretraining/extract_features.py"),
+                    "--input_file", str(tmp_path / "in.txt"), "--output_file", str(tmp_path / "out.jsonl"),
+                    "--vocab_file", str(vf), "--bert_model", "tiny", "--layers=-1,-2", "--max_seq_length", "16",
+                    "--no_cuda"], check=True, timeout=300, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    lines = [json.loads(l) for l in (tmp_path / "out.jsonl").read_text().splitlines()]
+    assert [l["linex_index"] for l in lines] == [0, 1]
+    first = lines[0]["features"]
+    assert [f["token"] for f in first] == ["[CLS]", "the", "cat", "sat", "[SEP]", "the", "dog", "ran", "[SEP]"]
+    assert [l["index"] for l in first[0]["layers"]] == [-1, -2] and len(first[0]["layers"][0]["values"]) == 128
