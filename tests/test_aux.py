@@ -280,3 +280,33 @@ def test_extract_features_script(tmp_path):
     first = lines[0]["features"]
     assert [f["token"] for f in first] == ["[CLS]", "the", "cat", "sat", "[SEP]", "the", "dog", "ran", "[SEP]"]
     assert [l["index"] for l in first[0]["layers"]] == [-1, -2] and len(first[0]["layers"][0]["values"]) == 128
+
+
+def test_question_answering_span_selection(tmp_path):
+    import importlib.util, json, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    path = os.path.join(root, "examples/bert_pretraining/inference.py")
+    spec = importlib.util.spec_from_file_location("qa_inference", path)
+    qa = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(qa)
+    vf, _ = _toy_corpus(tmp_path)
+    tok = data.BertTokenizer(str(vf))
+    ids, mask, seg, tokens, t2w, words = qa.build_features("the cat", "the dog sat on the mat fast", tok, 16, 4)
+    assert tokens == ["[CLS]", "the", "cat", "[SEP]", "the", "dog", "sat", "on", "the", "mat", "fast", "[SEP]"]
+    assert len(ids) == len(mask) == len(seg) == 16 and sum(mask) == 12
+    assert t2w == [-1, -1, -1, -1, 0, 1, 2, 3, 4, 5, 6, -1]
+    start = [0.0] * 12
+    end = [0.0] * 12
+    start[6], end[9] = 5.0, 4.0          # "sat on the mat"
+    start[1] = 9.0                       # inside the question: never an answer
+    best = qa.best_spans(start, end, t2w, words, n_best_size=3, max_answer_length=10)
+    assert best[0]["text"] == "sat on the mat" and best[0]["start_logit"] == 5.0
+    assert qa.best_spans(start, end, t2w, words, n_best_size=3, max_answer_length=2)[0]["text"] != "sat on the mat"
+    start[0], end[0] = 20.0, 20.0        # strong [CLS]: the empty answer wins when allowed
+    assert qa.best_spans(start, end, t2w, words, 3, 10, with_negative=True)[0]["text"] == ""
+    out = subprocess.run([sys.executable, path, "--vocab_file", str(vf), "--bert_model", "tiny", "--no_cuda",
+                          "--question", "the cat", "--context", "the dog sat on the mat", "--max_seq_length", "16",
+                          "--n_best_size", "3"], check=True, capture_output=True, text=True, timeout=300,
+                         env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    res = json.loads(out.stdout.strip().splitlines()[-1])
+    assert res["question"] == "the cat" and isinstance(res["answers"][0]["text"], str)
