@@ -45,6 +45,9 @@ def parse():
     p.add_argument("--steps_this_run", type=int, default=-1)
     p.add_argument("--num_steps_per_checkpoint", type=int, default=100)
     p.add_argument("--resume_from_checkpoint", action="store_true")
+    p.add_argument("--init_checkpoint", default=None,
+                   help="checkpoint file or directory (its latest checkpoint) whose model weights start a new run, "
+                        "e.g. phase 2 from the end of phase 1; optimizer, schedule and reducer state start fresh")
     p.add_argument("--checkpoint_activations", action="store_true")
     p.add_argument("--bf16", action="store_true", default=True)
     p.add_argument("--input_dir", default=None,
@@ -104,11 +107,18 @@ def main():
     state = cb.get_comm_hooks(args, ddp, args.local_rank)
     crit = models.BertPretrainingCriterion(cfg.vocab_size)
     global_step, epoch = 0, 0
+    resumed = False
     if args.resume_from_checkpoint:
         ck = latest_checkpoint(args.output_dir)
         if ck:
             info = load_checkpoint(ck, model=ddp, optimizer=opt, reducer_state=state, device=device, rank=rank)
             global_step, epoch = info["step"], info["extra"].get("epoch", 0)
+            resumed = True
+    if args.init_checkpoint and not resumed:
+        ck = latest_checkpoint(args.init_checkpoint) if os.path.isdir(args.init_checkpoint) else args.init_checkpoint
+        if not ck or not os.path.exists(ck):
+            raise FileNotFoundError(f"--init_checkpoint {args.init_checkpoint}: no checkpoint found")
+        load_checkpoint(ck, model=ddp, device=device, rank=rank)          # weights only
     if rank == 0:
         os.makedirs(args.output_dir, exist_ok=True)
     stop, log = GracefulStop(), JsonLogger(os.path.join(args.output_dir, "log.jsonl") if rank == 0 else None)

@@ -310,3 +310,28 @@ def test_question_answering_span_selection(tmp_path):
                          env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
     res = json.loads(out.stdout.strip().splitlines()[-1])
     assert res["question"] == "the cat" and isinstance(res["answers"][0]["text"], str)
+
+
+def test_bert_driver_phase_two_starts_from_phase_one_weights(tmp_path):
+    """--init_checkpoint: a new run (fresh optimizer and reducer state) from the weights of another."""
+    import json, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "examples/bert_pretraining/run_pretraining.py")
+
+    def run(out, *extra):
+        env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), RANK="0", WORLD_SIZE="1",
+                   CUDA_VISIBLE_DEVICES="")
+        subprocess.run([sys.executable, script, "--bert_model", "tiny", "--output_dir", str(out),
+                        "--train_batch_size", "4", "--max_steps", "4", "--shard_size", "32",
+                        "--grad_reducer", "ef_powersgd", "--matrix_approximation_rank", "2", *extra],
+                       check=True, env=env, timeout=600)
+    run(tmp_path / "p1", "--max_seq_length", "32", "--max_predictions_per_seq", "5")
+    run(tmp_path / "p2", "--max_seq_length", "64", "--max_predictions_per_seq", "10",
+        "--init_checkpoint", str(tmp_path / "p1"), "--resume_from_checkpoint")
+    a = torch.load(utils.latest_checkpoint(str(tmp_path / "p1")), map_location="cpu", weights_only=False)
+    b = torch.load(utils.latest_checkpoint(str(tmp_path / "p2")), map_location="cpu", weights_only=False)
+    assert a["step"] == 4 and b["step"] == 4          # phase 2 counted its own steps
+    moved = sum(float((a["model"][k].float() - b["model"][k].float()).abs().sum()) for k in a["model"])
+    assert moved > 0
+    with pytest.raises(subprocess.CalledProcessError):
+        run(tmp_path / "p3", "--init_checkpoint", str(tmp_path / "nothing_here"))
