@@ -21,7 +21,7 @@ from torch.utils.data.distributed import DistributedSampler
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
 import conef_b200 as cb  # noqa: E402
 from conef_b200 import models  # noqa: E402
-from conef_b200.data import SyntheticTranslationPairs, collate_translation  # noqa: E402
+from conef_b200.data import ParallelText, SyntheticTranslationPairs, collate_translation  # noqa: E402
 from conef_b200.utils import GracefulStop, JsonLogger  # noqa: E402
 
 PAD = models.seq2seq.PAD_IDX
@@ -31,6 +31,13 @@ def parse():
     p = argparse.ArgumentParser()
     p.add_argument("--epochs", type=int, default=1)
     p.add_argument("--pairs", type=int, default=2000, help="synthetic sentence pairs per epoch")
+    p.add_argument("--train_src", default=None, help="source-language text, one sentence per line (with --train_tgt: "
+                                                    "train on these files instead of synthetic pairs)")
+    p.add_argument("--train_tgt", default=None)
+    p.add_argument("--valid_src", default=None)
+    p.add_argument("--valid_tgt", default=None)
+    p.add_argument("--min_freq", type=int, default=1)
+    p.add_argument("--max_len", type=int, default=100)
     p.add_argument("--batch_size", type=int, default=32, help="sentence pairs per process")
     p.add_argument("--vocab", type=int, default=32000)
     p.add_argument("--num_encoder_layers", type=int, default=3)
@@ -76,16 +83,23 @@ def main():
         torch.cuda.set_device(device)
     dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world)
     torch.manual_seed(args.seed)
+    if args.train_src and args.train_tgt:
+        train = ParallelText(args.train_src, args.train_tgt, min_freq=args.min_freq, max_len=args.max_len)
+        valid = ParallelText(args.valid_src, args.valid_tgt, train.src_vocab, train.tgt_vocab, max_len=args.max_len) \
+            if (args.valid_src and args.valid_tgt) else train
+        src_vocab, tgt_vocab = len(train.src_vocab), len(train.tgt_vocab)
+    else:
+        train = SyntheticTranslationPairs(args.pairs, args.vocab, args.vocab, seed=1)
+        valid = SyntheticTranslationPairs(max(64, args.pairs // 10), args.vocab, args.vocab, seed=2)
+        src_vocab = tgt_vocab = args.vocab
     net = models.Seq2SeqTransformer(args.num_encoder_layers, args.num_decoder_layers, args.emb_size, args.nhead,
-                                    args.vocab, args.vocab, args.ffn_hid_dim, args.dropout)
+                                    src_vocab, tgt_vocab, args.ffn_hid_dim, args.dropout)
     for p in net.parameters():
         if p.dim() > 1:
             torch.nn.init.xavier_uniform_(p)
     trainer = cb.DataParallelTrainer(
         net, lambda p: torch.optim.Adam(p, lr=args.lr, betas=(0.9, 0.98), eps=1e-9), loss_fn, reducer=args,
         device=device, autocast_dtype=torch.bfloat16 if (args.bf16 and cuda) else None, forward_fn=forward)
-    train = SyntheticTranslationPairs(args.pairs, args.vocab, args.vocab, seed=1)
-    valid = SyntheticTranslationPairs(max(64, args.pairs // 10), args.vocab, args.vocab, seed=2)
     sampler = DistributedSampler(train, world, rank, shuffle=True, seed=args.seed)
     loader = DataLoader(train, args.batch_size, sampler=sampler, collate_fn=collate_translation, drop_last=True)
     vloader = DataLoader(valid, args.batch_size, collate_fn=collate_translation)

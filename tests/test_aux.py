@@ -335,3 +335,33 @@ def test_bert_driver_phase_two_starts_from_phase_one_weights(tmp_path):
     assert moved > 0
     with pytest.raises(subprocess.CalledProcessError):
         run(tmp_path / "p3", "--init_checkpoint", str(tmp_path / "nothing_here"))
+
+
+def test_parallel_text_and_translation_driver(tmp_path):
+    import subprocess, sys
+    src = ["ein mann geht .", "eine frau liest ein buch .", "der hund rennt schnell !", "", "ein kind spielt ."] * 8
+    tgt = ["a man walks .", "a woman reads a book .", "the dog runs fast !", "", "a child plays ."] * 8
+    (tmp_path / "train.de").write_text("\n".join(src) + "\n")
+    (tmp_path / "train.en").write_text("\n".join(tgt) + "\n")
+    ds = data.ParallelText(str(tmp_path / "train.de"), str(tmp_path / "train.en"))
+    assert len(ds) == 32                                           # empty lines dropped on both sides
+    assert list(ds.src_vocab)[:4] == ["<unk>", "<pad>", "<bos>", "<eos>"] and ds.src_vocab["."] == 4
+    s0, t0 = ds[0]
+    assert ds.decode(t0) == "a man walks ." and ds.decode(s0, "src") == "ein mann geht ."
+    batch_src, batch_tgt = data.collate_translation([ds[0], ds[1]])
+    assert batch_src.shape == (8, 2) and int(batch_src[0, 0]) == 2 and int(batch_src[5, 0]) == 3
+    assert int(batch_src[7, 0]) == 1                               # padded behind EOS
+    other = data.ParallelText(str(tmp_path / "train.de"), str(tmp_path / "train.en"), ds.src_vocab, {"<unk>": 0})
+    assert set(other[0][1].tolist()) == {0}                        # unknown words map to <unk>
+    (tmp_path / "short.en").write_text("one line\n")
+    with pytest.raises(ValueError):
+        data.ParallelText(str(tmp_path / "train.de"), str(tmp_path / "short.en"))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), RANK="0", WORLD_SIZE="1",
+               CUDA_VISIBLE_DEVICES="")
+    subprocess.run([sys.executable, os.path.join(root, "examples/machine_translation/main.py"),
+                    "--train_src", str(tmp_path / "train.de"), "--train_tgt", str(tmp_path / "train.en"),
+                    "--batch_size", "8", "--emb_size", "32", "--nhead", "2", "--ffn_hid_dim", "64",
+                    "--num_encoder_layers", "1", "--num_decoder_layers", "1", "--start_compression_iter", "2",
+                    "--matrix_approximation_rank", "2", "--grad_reducer", "ef_powersgd"],
+                   check=True, env=env, timeout=600)
