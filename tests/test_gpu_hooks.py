@@ -397,3 +397,37 @@ def test_phase_timing_and_wire_bytes_on_gpu(single_rank_group, monkeypatch):
     assert state.wire_bytes_per_step() == 4.0 * plan.numel_after
     state.enable_phase_timing(False)
     assert state.phase_summary() == {}
+
+
+@pytest.mark.parametrize("hook,mk", [
+    ("powerSGD_hook", lambda: _powersgd_states(DEV, matrix_approximation_rank=4, use_error_feedback=True,
+                                               use_error_compression=True, sketch_size=0.1)),
+    ("powerSGD_hook", lambda: _powersgd_states(DEV, matrix_approximation_rank=2, use_error_feedback=True)),
+    ("RandomBlock_hook", lambda: _rb_state(use_error_compression=True, sketch_size=0.1)),
+    ("RandomBlock_hook", lambda: _rb_state(use_error_compression=True, error_compressor="quant8", beta=0.0)),
+], ids=["psgd-sketch", "psgd-dense", "rb-sketch", "rb-quant8"])
+@pytest.mark.parametrize("tc,guard", [("0", 4096), ("1", 4096), ("1", 4099)], ids=["simt", "tc", "tc-unaligned"])
+def test_hooks_leave_the_memory_around_the_bucket_alone(single_rank_group, monkeypatch, hook, mk, tc, guard):
+    """Canaries before and behind the bucket (a slice of a larger allocation; with guard 4099 it does
+    not start on a 16-byte boundary, so TMA cannot address it) survive several steps of every fused path."""
+    monkeypatch.setenv("CONEF_TC", tc)
+    monkeypatch.setenv("CONEF_BACKEND", "native")
+    b = FakeBucket(SHAPES, device=DEV, seed=5)
+    n = b.buffer().numel()
+    big = torch.full((n + 2 * guard,), 1234.5, device=DEV)
+    big[guard : guard + n].copy_(b.buffer())
+    b._buf = big[guard : guard + n]
+    state = mk()
+    for i in range(4):
+        out = getattr(cb, hook)(state, b).wait()
+        assert out.data_ptr() == b.buffer().data_ptr()
+    torch.cuda.synchronize()
+    state.check_status()
+    assert bool((big[:guard] == 1234.5).all()) and bool((big[guard + n :] == 1234.5).all())
+    assert bool(torch.isfinite(big[guard : guard + n]).all())
+
+
+def _rb_state(**kw):
+    s = cb.RandomBlockState(None, compression_ratio=0.1, start_compression_iter=2, **kw)
+    s.iter = 2
+    return s
