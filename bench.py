@@ -17,8 +17,10 @@ of every step copied from pinned host memory and the loss of every step copied
 back to the host.  ``--impl restated`` runs the same model with the hooks
 executed as PyTorch ops + NCCL all-reduce in the reference's op order (with
 its one device synchronisation per bucket); ``--impl allreduce`` is plain
-uncompressed DDP.  ``--impl reference`` reports why the unmodified reference
-cannot run here.
+uncompressed DDP.  ``--impl reference`` runs the unmodified reference (a
+byte-identical copy under ``baseline/_ref``: its model, registry, hook, sketch
+kernels, NCCL + cuBLAS) through the adapters of ``baseline/compat`` with the same
+timing protocol; the product package is not imported on that path.
 """
 from __future__ import annotations
 
@@ -34,9 +36,33 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 if REPO not in sys.path:
     sys.path.insert(0, REPO)
 
-REFERENCE_UNAVAILABLE = (
-    "pip: the reference tree is not installable (neither setup.py nor pyproject.toml); its hooks also need "
-    "torch-1.9 GradBucket methods, CuPy, pynvrtc and apex, none of which exist in this image")
+
+
+def run_reference(args) -> int:
+    """``--impl reference``: the unmodified reference (``baseline/_ref``) through ``baseline/reference_arm.py``.
+
+    The product package must not be importable on this path: the repository root also holds a
+    ``communication`` alias package that would shadow the reference's directory of that name."""
+    import importlib.util
+
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    sys.path[:] = [p for p in sys.path if os.path.abspath(p or os.getcwd()) != REPO]
+    try:
+        spec = importlib.util.spec_from_file_location("reference_arm", os.path.join(REPO, "baseline", "reference_arm.py"))
+        arm = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(arm)
+        rc = arm.run(args, ClockSampler, real_stdout)
+        assert "conef_b200" not in sys.modules, "the reference arm must not load the product package"
+        return rc
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        traceback.print_exc()
+        if int(os.environ.get("RANK", "0")) == 0:
+            line = {"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}"[:300]}
+            os.write(real_stdout, (json.dumps(line) + "\n").encode())
+        return 0
 
 
 def parse_args():
@@ -152,8 +178,7 @@ def build_workload(args, device, world):
 def main():
     args = parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
+        return run_reference(args)
 
     # Keep stdout to the one JSON line: libraries (NCCL's version banner, for one) write there,
     # so file descriptor 1 points at stderr while the benchmark runs and the line goes to the real stdout.

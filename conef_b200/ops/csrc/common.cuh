@@ -109,6 +109,34 @@ __device__ __forceinline__ bool wait_flags_bounded(const uint32_t* flags, int wo
   return true;
 }
 
+// Philox-4x32-10 keyed by `seed` at counter `ctr`, turned into four standard normal values by
+// Box-Muller: a pure function of (seed, ctr), so every rank draws the same numbers.
+__device__ __forceinline__ void conef_philox_round(uint32_t& c0, uint32_t& c1, uint32_t& c2, uint32_t& c3,
+                                                   uint32_t k0, uint32_t k1) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
+  const uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
+  const uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
+  const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+  c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+}
+__device__ __forceinline__ void conef_philox_normal4(uint64_t seed, uint64_t ctr, float (&out)[4]) {
+  uint32_t c0 = (uint32_t)ctr, c1 = (uint32_t)(ctr >> 32), c2 = 0u, c3 = 0u;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    conef_philox_round(c0, c1, c2, c3, k0, k1);
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  const float two_pi = 6.283185307179586f;
+  const float u0 = ((float)c0 + 1.f) * 2.3283064365386963e-10f;  // (0, 1]
+  const float u1 = (float)c1 * 2.3283064365386963e-10f;
+  const float u2 = ((float)c2 + 1.f) * 2.3283064365386963e-10f;
+  const float u3 = (float)c3 * 2.3283064365386963e-10f;
+  const float r0 = sqrtf(-2.f * logf(u0)), r1 = sqrtf(-2.f * logf(u2));
+  out[0] = r0 * cosf(two_pi * u1); out[1] = r0 * sinf(two_pi * u1);
+  out[2] = r1 * cosf(two_pi * u3); out[3] = r1 * sinf(two_pi * u3);
+}
+
 // Offset (in floats) of element (k, n) of a small operand inside its packed copy: per K step
 // of 8 rows, NP/8 groups of 8 columns, each two 8x4 core matrices (k%8 < 4, k%8 >= 4) of
 // 32 floats: K-major, no swizzle, exactly what tcgen05.mma reads for a K=8 tf32 step.

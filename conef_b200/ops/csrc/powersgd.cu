@@ -556,35 +556,14 @@ extern "C" int conef_psgd_decompress_csr(const ConefMat* mats, const int2* tiles
 }
 
 // ---------------------------------------------------------------------------
-// Counter-based standard normal fill (Philox-4x32-10 + Box-Muller): the value
+// Counter-based standard normal fill (Philox-4x32-10 + Box-Muller, common.cuh): the value
 // of element e depends only on (seed, e).
-__device__ __forceinline__ void philox_round(uint32_t& c0, uint32_t& c1, uint32_t& c2, uint32_t& c3,
-                                             uint32_t k0, uint32_t k1) {
-  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
-  const uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
-  const uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
-  const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
-  c0 = n0; c1 = n1; c2 = n2; c3 = n3;
-}
-
 __global__ void k_fill_normal(float* __restrict__ buf, long long numel, uint64_t seed) {
   const long long quad = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long base = quad * 4;
   if (base >= numel) return;
-  uint32_t c0 = (uint32_t)quad, c1 = (uint32_t)(quad >> 32), c2 = 0u, c3 = 0u;
-  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
-#pragma unroll
-  for (int i = 0; i < 10; ++i) {
-    philox_round(c0, c1, c2, c3, k0, k1);
-    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
-  }
-  const float two_pi = 6.283185307179586f;
-  const float u0 = ((float)c0 + 1.f) * 2.3283064365386963e-10f;  // (0, 1]
-  const float u1 = (float)c1 * 2.3283064365386963e-10f;
-  const float u2 = ((float)c2 + 1.f) * 2.3283064365386963e-10f;
-  const float u3 = (float)c3 * 2.3283064365386963e-10f;
-  const float r0 = sqrtf(-2.f * logf(u0)), r1 = sqrtf(-2.f * logf(u2));
-  float out[4] = {r0 * cosf(two_pi * u1), r0 * sinf(two_pi * u1), r1 * cosf(two_pi * u3), r1 * sinf(two_pi * u3)};
+  float out[4];
+  conef_philox_normal4(seed, (uint64_t)quad, out);
   for (int i = 0; i < 4; ++i)
     if (base + i < numel) buf[base + i] = out[i];
 }

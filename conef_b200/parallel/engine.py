@@ -89,10 +89,24 @@ def _try_symm(regions, group, device) -> Optional[SymmBuffer]:
         return None
 
 
+_STATUS_WORDS: Dict[int, torch.Tensor] = {}
+
+
+def _status_words(device: torch.device) -> torch.Tensor:
+    """One status word block per device, shared by every engine of the process: a wait that gave
+    up anywhere is seen by whichever hook call looks next."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _STATUS_WORDS.get(idx)
+    if t is None:
+        t = torch.zeros(4, dtype=torch.int32, device=device)
+        _STATUS_WORDS[idx] = t
+    return t
+
+
 class _EngineBase:
     def __init__(self, device):
         self.device = device
-        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.status = _status_words(device)
         self.epoch = 0
         self.step = 0
         self.symm: Optional[SymmBuffer] = None
@@ -985,11 +999,14 @@ def run_powersgd_native(state, bucket, group, variant: str) -> torch.futures.Fut
     dev = buf.device
     stream = comm_stream_for(dev)
     stream.wait_stream(torch.cuda.current_stream(dev))
+    state.poll_status()
     with torch.cuda.stream(stream):
         eng = _get_engine(state, bucket, buf, group,
                           lambda: PowerSGDEngine(state, buf, bucket.gradients(), group, variant, bucket.index()))
         eng.run(state, bucket, buf)
         fut = _done_on_current_stream(buf)
+    if bucket.is_last() and eng.world > 1:
+        state.post_status(eng.status, stream)
     state.maybe_increase_iter(bucket)
     return fut
 
@@ -1252,6 +1269,7 @@ def run_randblock_native(state, bucket, group, unbiased: bool) -> torch.futures.
     dev = buf.device
     stream = comm_stream_for(dev)
     stream.wait_stream(torch.cuda.current_stream(dev))
+    state.poll_status()
     with torch.cuda.stream(stream):
         try:
             eng = _get_engine(state, bucket, buf, group,
@@ -1263,5 +1281,7 @@ def run_randblock_native(state, bucket, group, unbiased: bool) -> torch.futures.
             return _randblock_torch(state, bucket, group, unbiased=unbiased)
         eng.run(state, bucket, buf)
         fut = _done_on_current_stream(buf)
+    if bucket.is_last() and eng.world > 1:
+        state.post_status(eng.status, stream)
     state.maybe_increase_iter(bucket)
     return fut

@@ -32,7 +32,7 @@ from ..compressors.other import ERROR_COMPRESSORS
 logger = logging.getLogger(__name__)
 
 # slots that never go into a checkpoint / pickle
-_RUNTIME_SLOTS = ("process_group", "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen")
+_RUNTIME_SLOTS = ("process_group", "_engines", "_timers", "_wire", "_status_probe", "_process_iters", "_sig_seen")
 
 
 def _to_cpu(obj):
@@ -79,7 +79,7 @@ class _StateBase:
         self._engines = {}
         self._timers = None              # utils.tracing.PhaseTimer when phase timing is on
         self._wire = [0, 0, 0]           # fp32 elements sent, elements before compression, compressed steps
-        self._status_checked = 0
+        self._status_probe = None        # (pinned host copy of the device status word, its event)
         self._process_iters = 0      # reduced iterations seen by this process (not persisted)
         self._sig_seen = set()       # buckets whose layout was checked in this process
         self.bucket_signatures = {}  # persisted: bucket index -> (numel, parameter shapes)
@@ -201,9 +201,41 @@ class _StateBase:
         return size(getattr(self, "error_dict", {}))
 
     def check_status(self) -> None:
-        """Raise if a device-side bounded wait gave up (peer never signalled)."""
+        """Raise if a device-side bounded wait gave up (peer never signalled).  Synchronises."""
+        self._status_probe = None
         for eng in self._engines.values():
             eng.check_status()
+
+    # The hook path checks for itself, without a host synchronisation: the last bucket of a step
+    # enqueues a copy of the device status word into pinned memory behind its kernels, and every
+    # later hook call looks at that copy once its event has completed.
+    def post_status(self, status_dev, stream) -> None:
+        probe = self._status_probe
+        if probe is None:
+            host = torch.zeros(status_dev.numel(), dtype=status_dev.dtype).pin_memory()
+            probe = self._status_probe = [host, None, status_dev]
+        elif probe[1] is not None:
+            if not probe[1].query():
+                return                   # the previous copy has not landed yet: keep waiting for it
+            self.poll_status()
+        with torch.cuda.stream(stream):
+            probe[0].copy_(status_dev, non_blocking=True)
+            probe[1] = torch.cuda.Event()
+            probe[1].record(stream)
+        probe[2] = status_dev
+
+    def poll_status(self) -> None:
+        """Raise if the status word copied at the end of an earlier step shows a wait that gave up."""
+        probe = self._status_probe
+        if probe is None or probe[1] is None or not probe[1].query():
+            return
+        probe[1] = None
+        code = int(probe[0][0])
+        if code != 0:
+            probe[2].zero_()
+            raise RuntimeError(
+                f"device-side wait gave up (status {code}) in an earlier step: a peer rank did not signal in "
+                "time; the gradients of that step are not valid")
 
 
 def _check_error_compressor(kind):
@@ -219,7 +251,7 @@ class PowerSGDState(_StateBase):
         "iter", "total_numel_before_compression", "total_numel_after_compression",
         "compression_stats_logging_frequency", "next_stats_report",
         # additions
-        "error_compressor", "error_rank", "hash_seed", "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen",
+        "error_compressor", "error_rank", "hash_seed", "_engines", "_timers", "_wire", "_status_probe", "_process_iters", "_sig_seen",
         "bucket_signatures",
     ]
 
@@ -309,7 +341,7 @@ class RandomBlockState(_StateBase):
         "process_group", "compression_ratio", "start_compression_iter", "n_blocks",
         "use_error_compression", "beta", "sketch_size", "use_error_feedback", "rng", "error_dict",
         "iter", "compression_stats_logging_frequency", "next_stats_report", "compressed_tensor_memory",
-        "error_compressor", "hash_seed", "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen",
+        "error_compressor", "hash_seed", "_engines", "_timers", "_wire", "_status_probe", "_process_iters", "_sig_seen",
         "bucket_signatures",
     ]
 
@@ -357,7 +389,7 @@ class UnbiasedRandomBlockState(_StateBase):
     __slots__ = [
         "process_group", "compression_ratio", "start_compression_iter", "rng", "iter",
         "compression_stats_logging_frequency", "next_stats_report", "compressed_tensor_memory",
-        "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen",
+        "_engines", "_timers", "_wire", "_status_probe", "_process_iters", "_sig_seen",
         "bucket_signatures",
     ]
 
@@ -384,7 +416,7 @@ class unbiasedMtrxState(_StateBase):
         "orthogonalization_epsilon", "rng", "p_memory_dict", "q_memory_dict", "iter",
         "total_numel_before_compression", "total_numel_after_compression",
         "compression_stats_logging_frequency", "next_stats_report",
-        "_engines", "_timers", "_wire", "_status_checked", "_process_iters", "_sig_seen",
+        "_engines", "_timers", "_wire", "_status_probe", "_process_iters", "_sig_seen",
         "bucket_signatures",
     ]
 
