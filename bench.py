@@ -248,38 +248,44 @@ def main():
     sync()
     trainer.check()
 
+    def timed_steps(n):
+        """Mean device time per step over n steps (CUDA events per step on the launching stream,
+        L2 flushed before each, barrier + synchronise on both sides), max over ranks; wall seconds."""
+        dist.barrier()
+        sync()
+        if use_cuda:
+            starts = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+            ends = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
+        t0 = time.perf_counter()
+        per = []
+        for i in range(n):
+            if use_cuda:
+                flush.fill_(float(i))          # evict L2 between timed steps (outside the event pair)
+                starts[i].record()
+                trainer.step(*dev_batches[i % nbuf])
+                ends[i].record()
+            else:
+                t = time.perf_counter()
+                trainer.step(*dev_batches[i % nbuf])
+                per.append((time.perf_counter() - t) * 1e3)
+        sync()
+        dist.barrier()
+        wall_s = time.perf_counter() - t0
+        if use_cuda:
+            per = [s.elapsed_time(e) for s, e in zip(starts, ends)]
+        t_ms = torch.tensor([sum(per) / len(per)], device=device, dtype=torch.float64)
+        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
+        return float(t_ms.item()), wall_s
+
     sampler = ClockSampler(local_rank) if use_cuda and rank == 0 else None
     dist.barrier()
     sync()
     native.reset_launch_count()
     if sampler:
         sampler.start()
-    if use_cuda:
-        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-        ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
-    t0 = time.perf_counter()
-    per_step_ms = []
-    for i in range(args.steps):
-        if use_cuda:
-            flush.fill_(float(i))          # evict L2 between timed steps (outside the event pair)
-            starts[i].record()
-            trainer.step(*dev_batches[i % nbuf])
-            ends[i].record()
-        else:
-            t = time.perf_counter()
-            trainer.step(*dev_batches[i % nbuf])
-            per_step_ms.append((time.perf_counter() - t) * 1e3)
-    sync()
-    dist.barrier()
-    wall = time.perf_counter() - t0
+    ms, wall = timed_steps(args.steps)
     launches = native.reset_launch_count()
-    if use_cuda:
-        per_step_ms = [s.elapsed_time(e) for s, e in zip(starts, ends)]
     trainer.check()
-    ms = sum(per_step_ms) / len(per_step_ms)
-    t_ms = torch.tensor([ms], device=device, dtype=torch.float64)
-    dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    ms = float(t_ms.item())
     value = per_gpu * world / (ms / 1e3)
 
     # ---- end-to-end arm: pinned host inputs every step, loss read back every step ----
@@ -324,8 +330,33 @@ def main():
         trainer.check()
 
     clocks = sampler.stop() if sampler else None
+
+    # ---- what ran, and what it left exposed (untimed extras, after the measured regions) ----
+    state = trainer.state
+    engines = list(getattr(state, "_engines", {}).values()) if state is not None else []
+    backends = sorted({(e.symm.backend if e.symm is not None else ("nccl" if e.world > 1 else "local"))
+                       for e in engines}) or (["library all-reduce (no native engine ran)"] if world > 1 else ["none"])
+    graph_replays = sum(int(getattr(e.exec_plan, "graph_replays", 0) or 0) for e in engines
+                        if getattr(e, "exec_plan", None) is not None)
+    fused = [bool(getattr(e, "fused", False)) for e in engines]
+    phase_ms = exposed_ms = bypass_ms = None
+    if state is not None and use_cuda and args.impl == "ours":
+        state.enable_phase_timing()
+        for i in range(3):
+            trainer.step(*dev_batches[i % nbuf])
+        summary = state.phase_summary()
+        state.enable_phase_timing(False)
+        phase_ms = {k: round(v["ms"] / 3, 4) for k, v in summary.items()}     # per step, all buckets
+    if state is not None and args.impl in ("ours", "restated"):
+        from conef_b200.parallel import hooks as _hooks
+        _hooks.BYPASS = True            # hooks return their bucket untouched: a step without compression or comm
+        for i in range(2):
+            trainer.step(*dev_batches[i % nbuf])
+        bypass_ms, _ = timed_steps(args.steps)
+        _hooks.BYPASS = False
+        exposed_ms = ms - bypass_ms
+
     if rank == 0:
-        state = trainer.state
         out = {
             "metric": f"{desc['unit']} training throughput, {desc['model']}, {desc['reducer']}",
             "value": value, "unit": desc["unit"], "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -341,6 +372,13 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
             "wall_s_timed_region": wall,
             "ef_buffer_mb": (state.ef_buffer_bytes() / 1e6) if state is not None else 0.0,
+            # the data plane that actually ran (not the request): symm / ipc = own kernels over peer
+            # memory, local = one rank, nccl = library all-reduce
+            "comm_backend_used": backends, "graph_replays": graph_replays,
+            "buckets": len(engines), "buckets_on_fused_pipeline": sum(fused),
+            # step time minus the time of the same step with the hooks returning at once (same process)
+            "exposed_comm_ms": exposed_ms, "ms_per_step_hooks_bypassed": bypass_ms,
+            "phase_ms": phase_ms,
         }
         if state is not None and hasattr(state, "compression_stats"):
             out["compression_rate"] = state.compression_stats()[0]

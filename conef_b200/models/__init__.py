@@ -1,7 +1,9 @@
 """Model zoo of the example workloads (framework-layer PyTorch code)."""
 from . import seq2seq
-from .bert import (BertConfig, BertForMaskedLM, BertForPreTraining, BertForQuestionAnswering,
-                   BertForSequenceClassification, BertModel, BertPretrainingCriterion)
+from .bert import (BertConfig, BertForMaskedLM, BertForMultipleChoice, BertForNextSentencePrediction,
+                   BertForPreTraining, BertForQuestionAnswering, BertForSequenceClassification,
+                   BertForTokenClassification, BertModel, BertPreTrainedModel, BertPretrainingCriterion,
+                   load_tf_weights_in_bert, tf_variable_names)
 from .language import PositionalEncoding, RNNModel, TransformerModel, repackage_hidden
 from .seq2seq import Seq2SeqTransformer, create_mask
 from .densenet import DenseNet, DenseNet121, DenseNet161, DenseNet169, DenseNet201, densenet_cifar

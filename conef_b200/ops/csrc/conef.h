@@ -68,6 +68,38 @@ typedef struct ConefBlk {
 
 enum { CONEF_EF_NONE = 0, CONEF_EF_DENSE = 1, CONEF_EF_SKETCH = 2, CONEF_EF_QUANT8 = 3 };
 
+// Work that rides along with an orthogonalisation (conef_orthogonalize_fused), so that a bucket's
+// pipeline needs no separate launches for it.  All members may be zero / NULL.
+typedef struct ConefOrthExtra {
+  // Two regions cleared by the Gram kernel's CTAs (with world > 1: after the flag wait, i.e. once
+  // every peer is known to have finished reading them).
+  float* zero0;  long long zero0_n;
+  float* zero1;  long long zero1_n;
+  // Uncompressed tensors, handled by spare CTAs of the Gram kernel.
+  // seg_mode 1: staging[e] = bucket[...] (+ dense error, which then keeps the local value)
+  // seg_mode 2: bucket[...] = seg_scale * sum over peers of peer_staging[p][e] (after the flag wait)
+  int seg_mode, nsegs;
+  const ConefSeg* segs;
+  long long seg_total;
+  float* bucket;
+  float* dense_err;
+  float* staging;
+  const float* const* peer_staging;
+  float seg_scale;
+  // which == 1 only: the last pass adds alpha * s_j * Q[j, :] to cell h_j of the sketch record's
+  // small operand Z = alpha H^T Q, directly in the packed layout the tensor-core kernel reads
+  // (record nm + i describes the sketch of matrix i; `packed` must be given; the Z part of the
+  // packed buffer must be one of the zeroed regions).
+  float alpha;
+  int nm;
+  const int32_t* tables;
+  // With `bar` (two device words, zero once) and `max_rank` (largest r among the records) the whole
+  // orthogonalisation runs as one launch whose CTAs meet at two barriers, when the device can hold
+  // all of them at once; otherwise, and when either is zero, as three launches.
+  uint32_t* bar;
+  int max_rank;
+} ConefOrthExtra;
+
 const char* conef_last_error(void);
 int conef_version(void);
 
@@ -135,6 +167,14 @@ int conef_dc_groups(int m);
 // Record nmats + i describes the sketch of matrix i; its q_off is where Z_i / Y_i live.
 int conef_sketch_project(const ConefMat* mats, int nmats, int max_cols, const int32_t* tables,
                          float* qz, float scale, int unproject, cudaStream_t stream);
+// All-reduce of the Q blocks over peer memory fused with the sketch term's un-projection:
+// out Q_i[j, :] = scale * sum_p ( Q_p,i[j, :] + alpha s_j Y_p,i[h_j, :] ), every peer buffer laid out
+// [Q blocks | Y blocks] like `out`'s own buffer.  Waits (bounded) until my_flags[0..world) reached
+// `epoch` (+ *epoch_base); world == 1: no wait, peer_bufs[0] is local.  tables == NULL: plain sum.
+int conef_reduce_q(const ConefMat* mats, int nmats, int max_cols, const int32_t* tables, float* out,
+                   const float* const* peer_bufs, const uint32_t* my_flags, int world, uint32_t epoch,
+                   float alpha, float scale, int* status, long long spin_limit, const uint32_t* epoch_base,
+                   cudaStream_t stream);
 // Per matrix: T (rows_t x c1) += sum over up to two terms of coef_t * X_t (rows_t x c2_t) * (L_t^T Rm_t).
 // Used by the low-rank error store, whose factors enter PowerSGD's products as small corrections.
 // reduce_tiles chunk rows_l, apply_tiles chunk rows_t (int2 {matrix, chunk of 512 rows});
@@ -160,6 +200,13 @@ int conef_tc_encode_maps(const ConefMat* host_mats, int nmats, const float* buck
 int conef_psgd_tc(int mode, const ConefMat* mats, const void* maps, const void* tiles, int ntiles,
                   const float* small_packed, float* out_base, int max_rank, int* status,
                   cudaStream_t stream);
+// The same, and the CTA that finishes last publishes `epoch` (+ *epoch_base when given) in slot
+// `rank` of every peer's flag array (done: a device counter, zero between launches).  With
+// done == NULL or world == 1 nothing is published.
+int conef_psgd_tc_signal(int mode, const ConefMat* mats, const void* maps, const void* tiles, int ntiles,
+                         const float* small_packed, float* out_base, int max_rank, int* status,
+                         uint32_t* done, uint32_t* const* peer_flags, int world, int rank, uint32_t epoch,
+                         const uint32_t* epoch_base, cudaStream_t stream);
 // Copy the (rows x r) blocks of `src` (which = 0: P blocks, 1: Q blocks) into the layout the
 // tensor-core kernel reads with one bulk copy per stage: K-major 8x4 core matrices, r padded
 // with zeros to NP = 16 (max_rank <= 16) or 32 columns, rows padded to a multiple of 32.
@@ -226,6 +273,15 @@ int conef_orthogonalize_packed_ex(const ConefMat* mats, const int2* tiles, int n
                                   const uint32_t* flags, int world, uint32_t epoch, int* status,
                                   long long spin_limit, float* packed, int packed_np, float* gram,
                                   const uint32_t* epoch_base, cudaStream_t stream);
+// The same with the ride-along work of ConefOrthExtra.  With peer_bufs given and world == 1 the
+// input is read from peer_bufs[0] (no flags) and the result written to buf.
+int conef_orthogonalize_fused(const ConefMat* mats, const int2* tiles, int ntiles, int which, float* buf,
+                              float eps, const float* const* peer_bufs, const uint32_t* flags, int world,
+                              uint32_t epoch, int* status, long long spin_limit, float* packed,
+                              int packed_np, float* gram, const uint32_t* epoch_base,
+                              const ConefOrthExtra* extra, cudaStream_t stream);
+// Kernels enqueued by the calling thread's most recent conef_orthogonalize_* call.
+int conef_orth_last_launches(void);
 // *word = value (add = 0) or *word += value (add = 1), in stream order.
 int conef_epoch_word(uint32_t* word, uint32_t value, int add, cudaStream_t stream);
 int conef_ipc_get_handle(void* dev_ptr, void* handle_out_64B);

@@ -1,7 +1,6 @@
-// Native per-bucket executor of the PowerSGD family (see executor.h).  The order of operations is
-// the one of PowerSGDEngine.run in parallel/engine.py, which stays as the readable description and
-// as the path for externally supplied error compressors.
+// Native per-bucket executor of the PowerSGD family (see executor.h).
 #include "executor.h"
+#include <string.h>
 
 #define RUN(call)                      \
   do {                                 \
@@ -85,11 +84,106 @@ int correct(ConefPsgdPlan* plan, const ConefCorr* table, bool over_n, float* T, 
     if (rc_ != 0) return rc_;          \
   } while (0)
 
+// The fused pipeline: ten launches per bucket and step (plus the SIMT kernels of matrices that TMA
+// cannot address, and the top-k pruning).
+//   P:  k_gram(Q) [+ clears the sketch records' packed operand, + gathers the uncompressed tensors]
+//       k_qr_apply, k_qr_apply [final pass: writes Q packed, adds alpha H^T Q into the packed Z]
+//       k_tc_skinny<P>  [last CTA publishes epoch 1 to the peers]
+//   Q:  k_gram(P) [waits for epoch 1, sums the peers' P, clears the other slot's P and Q regions,
+//                  spare CTAs sum the peers' staged tensors back into the bucket]
+//       k_qr_apply, k_qr_apply [final pass writes P packed]
+//       k_tc_skinny<Q>  [last CTA publishes epoch 2]
+//   D:  k_reduce_q [waits for epoch 2, sums the peers' Q and un-projects the sketch term]
+//       k_psgd_decompress
+// The products accumulate with atomics into slot buffers that the Gram kernel of the following step
+// clears, after its flag wait has shown that every peer is done reading them, so nothing is memset.
+static int run_fused(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint32_t* eb, int* ncoll) {
+  const uint32_t ebase = eb ? 0u : plan->epoch;
+  const int nm = plan->nm, ws = plan->world, slot = plan->slot & 1;
+  const bool peers = ws > 1;
+  const bool sketch = plan->ef_mode == CONEF_EF_SKETCH;
+  const bool fused_err = sketch || plan->ef_mode == CONEF_EF_DENSE;
+  const float* aux = fused_err ? plan->aux : nullptr;
+  const long long tq = plan->total_q, tz = plan->total_z, tp = plan->total_p, tu = plan->total_u;
+  float* dense_err = plan->ef_mode == CONEF_EF_DENSE ? plan->dense_err : nullptr;
+  float* seg_err = plan->topk ? nullptr : dense_err;
+  float* p_target = plan->local_p[slot];
+  float* q_target = plan->local_q[slot];
+  const float inv_ws = 1.0f / (float)ws;
+  const long long spin = peers ? plan->spin_limit : 0;
+  uint32_t* const* pflags = peers ? plan->peer_flags : nullptr;
+
+  if (phases & CONEF_PHASE_P) {
+    if (plan->fresh) RUN(conef_fill_normal(plan->qz, tq, plan->seed, s));
+    ConefOrthExtra X;
+    memset(&X, 0, sizeof(X));
+    X.bar = plan->one_launch_orth ? plan->done_word + 1 : nullptr;
+    X.max_rank = plan->max_rank;
+    if (sketch) { X.zero0 = plan->zpk; X.zero0_n = plan->zpk_n; X.tables = plan->tables; X.nm = nm; X.alpha = plan->alpha; }
+    if (plan->total_unc) {
+      X.seg_mode = 1; X.nsegs = plan->nsegs; X.segs = plan->segs; X.seg_total = plan->total_unc;
+      X.bucket = plan->work; X.dense_err = seg_err; X.staging = plan->local_stage[slot];
+    }
+    RUN(conef_orthogonalize_fused(plan->mats, (const int2*)plan->orth_q.tiles, plan->orth_q.n, 1, plan->qz,
+                                  plan->eps, nullptr, nullptr, 1, 0, plan->status, 0, plan->qpk, plan->np_cols,
+                                  plan->gram, nullptr, &X, s));
+    plan->launched += conef_orth_last_launches() - 1;
+    if (plan->simt_p.n)
+      RUN(conef_psgd_p(plan->mats, (const int2*)plan->simt_p.tiles, plan->simt_p.n, plan->work, aux, plan->qz,
+                       p_target, 1, plan->max_rank, s));
+    const uint32_t ep = ebase + (uint32_t)(++*ncoll);
+    RUN(conef_psgd_tc_signal(0, plan->mats, plan->tc_maps, plan->tc_p.tiles, plan->tc_p.n, plan->qpk, p_target,
+                             plan->max_rank, plan->status, plan->done_word, pflags, ws, plan->rank, ep, eb, s));
+  }
+
+  if (phases & CONEF_PHASE_Q) {
+    // the epoch the P pass published: in this call, or in the previous one when the phases run one by one
+    const uint32_t ep1 = ebase + (uint32_t)*ncoll;
+    ConefOrthExtra X;
+    memset(&X, 0, sizeof(X));
+    X.bar = plan->one_launch_orth ? plan->done_word + 1 : nullptr;
+    X.max_rank = plan->max_rank;
+    X.zero0 = plan->local_p[slot ^ 1]; X.zero0_n = tp + tu;
+    X.zero1 = plan->local_q[slot ^ 1]; X.zero1_n = tq + tz;
+    if (plan->total_unc) {
+      X.seg_mode = 2; X.nsegs = plan->nsegs; X.segs = plan->segs; X.seg_total = plan->total_unc;
+      X.bucket = plan->work; X.dense_err = seg_err; X.peer_staging = plan->peer_stage[slot]; X.seg_scale = inv_ws;
+    }
+    RUN(conef_orthogonalize_fused(plan->mats, (const int2*)plan->orth_p.tiles, plan->orth_p.n, 0, plan->pu,
+                                  plan->eps, plan->peer_p[slot], plan->my_flags, ws, ep1, plan->status, spin,
+                                  plan->ppk, plan->np_cols, plan->gram, eb, &X, s));
+    plan->launched += conef_orth_last_launches() - 1;
+    if (plan->qset_all.simt.n)
+      RUN(conef_psgd_q(plan->mats, (const int2*)plan->qset_all.simt.tiles, plan->qset_all.simt.n, plan->work, aux,
+                       plan->pu, q_target, plan->max_rank, s));
+    const uint32_t ep2 = ebase + (uint32_t)(++*ncoll);
+    RUN(conef_psgd_tc_signal(1, plan->mats, plan->tc_maps, plan->qset_all.tc.tiles, plan->qset_all.tc.n, plan->ppk,
+                             q_target, plan->max_rank, plan->status, plan->done_word, pflags, ws, plan->rank, ep2,
+                             eb, s));
+  }
+
+  if (phases & CONEF_PHASE_D) {
+    const uint32_t ep2 = ebase + (uint32_t)*ncoll;      // the epoch the Q pass published
+    RUN(conef_reduce_q(plan->mats, nm, plan->max_cols, sketch ? plan->tables : nullptr, plan->qz,
+                       plan->peer_q[slot], plan->my_flags, ws, ep2, plan->alpha, inv_ws, plan->status, spin, eb, s));
+    RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_rows,
+                              plan->work, plan->pu, plan->qz, 1.0f, plan->sketch, plan->tables, plan->counts,
+                              dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank, plan->d_smem, s));
+    if (plan->topk) {
+      RUN(conef_topk_keep(plan->mats, nm, (const int2*)plan->topk_tiles.tiles, plan->topk_tiles.n,
+                          plan->dense_err, plan->topk_ratio, plan->topk_scratch, s));
+      plan->launched += 6;
+    }
+  }
+  return 0;
+}
+
 // eb: null for direct launches (epochs passed by value, continuing from plan->epoch); the device
 // epoch word while capturing (epochs relative to it).  *ncoll: collectives enqueued.
 static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint32_t* eb, int* ncoll) {
   plan->launched = 0;
   *ncoll = 0;
+  if (plan->fused) return run_fused(plan, phases, s, eb, ncoll);
   const uint32_t ebase = eb ? 0u : plan->epoch;
   const int nm = plan->nm, ws = plan->world, slot = plan->slot & 1;
   const bool symm = plan->has_symm && ws > 1;

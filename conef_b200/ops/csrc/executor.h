@@ -96,6 +96,14 @@ typedef struct ConefPsgdPlan {
   const int32_t* ell_hdr;        // per table (indexed like `counts`): offset of its blob in `ell`
   ConefTileList dc_tiles[4];     // int2 {matrix, row block}; one launch per shared-memory class;
                                  // `pad` of each list carries the class's max m * groups(m)
+  // ---- fused pipeline (ten launches per bucket and step) -------------------------------------------
+  int fused;                     // 1: run_fused (see executor.cu); needs tensor-core tiles in both products,
+                                 //    no low-rank store, not the unbiased variant, and slot buffers
+  int has_slots;                 // local_* / peer_* are set (symmetric memory, or plain local buffers with
+                                 //    one-entry pointer tables when world == 1); they start zeroed
+  uint32_t* done_word;           // device counter of the tile kernel's finished CTAs (zero between launches)
+  float* zpk;  long long zpk_n;  // packed small operands of the sketch records inside qpk
+  int one_launch_orth, pad3;     // 1: orthogonalisations as one launch with two CTA barriers (done_word[1..2])
 } ConefPsgdPlan;
 
 // ---- random-block family ---------------------------------------------------------------------------

@@ -12,17 +12,29 @@
 //                 column Gram-Schmidt produces in exact arithmetic (the QR factorisation with a
 //                 positive diagonal is unique).  The pass also accumulates the Gram matrix of its
 //                 output, and a second k_qr_apply re-orthogonalises with it ("twice is enough"),
-//                 which restores orthogonality to rounding level for conditioned inputs.
-//                 A numerically dependent column comes out as zero instead of normalised noise.
+//                 which restores orthogonality to rounding level.  The Gram matrix squares the
+//                 condition number, so a pivot that comes out below ORTH_SHIFT times its column's
+//                 squared norm cannot be told from rounding noise in fp32; such a pivot is raised to
+//                 that floor (a shifted Cholesky factor).  The column then leaves the first pass
+//                 short and almost orthogonal, and the second pass, whose Gram matrix is well
+//                 conditioned, finishes it: columns with a relative residual down to 1e-6 come out
+//                 orthonormal to 1e-6, where the column-by-column loop in fp32 loses orthogonality.
+//                 Only a column that is exactly zero has no direction to keep; the last pass fills
+//                 it with fixed pseudo-random values of unit expected norm (the same on every rank),
+//                 so that under warm start a rank of the factorisation is never lost for good.
 // The same two-pass structure serves the corrections of the low-rank error store:
 //   k_corr_reduce : C_t = L_t^T Rm_t   (up to two terms per matrix)
 //   k_corr_apply  : T += sum_t coef_t X_t C_t
+#include <string.h>
 #include "common.cuh"
 
 constexpr int OC_ROWS = 512;     // rows per CTA
 constexpr int OC_THREADS = 256;
 constexpr int OC_MAXR = 32;
 constexpr int GRAM_STRIDE = OC_MAXR * OC_MAXR;
+constexpr float ORTH_SHIFT = 1e-5f;          // pivot floor of the first pass, relative to the column's squared norm
+constexpr float ORTH_SHIFT_FINAL = 1e-7f;    // and of the last pass, whose input is nearly orthonormal
+constexpr unsigned long long ORTH_REFILL_SEED = 0x5EEDC01DF00DULL;
 
 // Csm[c2 x c1] = L[rows x c2]^T Rm[rows x c1] over `rows` rows; all threads of the CTA take part.
 // The summation order is fixed (no atomics): every rank must obtain bit-identical factors from
@@ -56,20 +68,26 @@ __device__ __forceinline__ void pair_reduce(const float* __restrict__ L, const f
   __syncthreads();
 }
 
+// Segment index whose dst_off is the largest one <= pos.
+__device__ __forceinline__ int orth_find_seg(const ConefSeg* segs, int n, long long pos) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (segs[mid].dst_off <= pos) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// CTAs [0, ntiles): one (matrix, 512-row chunk) each.  CTAs [ntiles, gridDim.x): the uncompressed
+// tensors of the bucket (X.seg_mode).  All CTAs share the clearing of X.zero0 / X.zero1.
 __global__ void __launch_bounds__(OC_THREADS)
-k_gram(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int which, float* __restrict__ buf,
-       float* __restrict__ gram, const float* const* __restrict__ peer_bufs, const uint32_t* __restrict__ flags,
-       int world, uint32_t epoch, int* __restrict__ status, long long spin_limit,
-       const uint32_t* __restrict__ epoch_base) {
+k_gram(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int ntiles, int which,
+       float* __restrict__ buf, float* __restrict__ gram, const float* const* __restrict__ peer_bufs,
+       const uint32_t* __restrict__ flags, int world, uint32_t epoch, int* __restrict__ status, long long spin_limit,
+       const uint32_t* __restrict__ epoch_base, const ConefOrthExtra X) {
   __shared__ float Csm[GRAM_STRIDE];
   __shared__ float scratch[OC_THREADS];
   __shared__ int ok;
-  const int2 t = tiles[blockIdx.x];
-  const ConefMat M = mats[t.x];
-  const int rows_total = which == 0 ? M.n : M.m, r = M.r;
-  const size_t off = (which == 0 ? M.p_off : M.q_off) + (size_t)t.y * OC_ROWS * r;
-  const int rows = min(OC_ROWS, rows_total - t.y * OC_ROWS);
-  float* a = buf + off;
   if (world > 1) {
     if (threadIdx.x == 0) {
       if (epoch_base != nullptr) epoch += *epoch_base;
@@ -78,6 +96,39 @@ k_gram(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int wh
     }
     __syncthreads();
     if (!ok) return;      // leave local values untouched; the host raises
+  }
+  {
+    const long long stride = (long long)gridDim.x * OC_THREADS;
+    const long long first = (long long)blockIdx.x * OC_THREADS + threadIdx.x;
+    for (long long i = first; i < X.zero0_n; i += stride) X.zero0[i] = 0.f;
+    for (long long i = first; i < X.zero1_n; i += stride) X.zero1[i] = 0.f;
+  }
+  if ((int)blockIdx.x >= ntiles) {
+    const long long stride = (long long)(gridDim.x - ntiles) * OC_THREADS;
+    for (long long e = (long long)(blockIdx.x - ntiles) * OC_THREADS + threadIdx.x; e < X.seg_total; e += stride) {
+      const int s = orth_find_seg(X.segs, X.nsegs, e);
+      const long long src = X.segs[s].src_off + (e - X.segs[s].dst_off);
+      if (X.seg_mode == 1) {
+        float v = X.bucket[src];
+        if (X.dense_err) { v += X.dense_err[src]; X.dense_err[src] = v; }   // the error slot keeps the local value
+        X.staging[e] = v;
+      } else {
+        float v = 0.f;
+        for (int p = 0; p < world; ++p) v += ld_relaxed_sys_f32(X.peer_staging[p] + e);
+        v *= X.seg_scale;
+        X.bucket[src] = v;
+        if (X.dense_err) X.dense_err[src] -= v;     // local value (stored by the gather) minus the average
+      }
+    }
+    return;
+  }
+  const int2 t = tiles[blockIdx.x];
+  const ConefMat M = mats[t.x];
+  const int rows_total = which == 0 ? M.n : M.m, r = M.r;
+  const size_t off = (which == 0 ? M.p_off : M.q_off) + (size_t)t.y * OC_ROWS * r;
+  const int rows = min(OC_ROWS, rows_total - t.y * OC_ROWS);
+  float* a = buf + off;
+  if (peer_bufs != nullptr) {
     for (int i = threadIdx.x; i < rows * r; i += OC_THREADS) {
       float s = 0.f;
       for (int p = 0; p < world; ++p) s += ld_relaxed_sys_f32(peer_bufs[p] + off + i);
@@ -92,8 +143,9 @@ k_gram(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int wh
 
 __global__ void __launch_bounds__(OC_THREADS)
 k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int which, float* __restrict__ buf,
-           const float* __restrict__ gram_in, float* __restrict__ gram_out, float eps, float* __restrict__ packed,
-           int packed_np) {
+           const float* __restrict__ gram_in, float* __restrict__ gram_out, float eps, float shift,
+           float* __restrict__ packed, int packed_np, const int32_t* __restrict__ proj_tables, int proj_nm,
+           float proj_alpha) {
   __shared__ float G[OC_MAXR][OC_MAXR + 1];
   __shared__ float R[OC_MAXR][OC_MAXR + 1];
   __shared__ float Ri[OC_MAXR][OC_MAXR + 1];
@@ -121,7 +173,9 @@ k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
     for (int j = 0; j < r; ++j) {
       float d = G[j][j];
       for (int k = 0; k < j; ++k) d -= R[k][j] * R[k][j];
-      const bool dead = !(d > 1e-10f * G[j][j]) || !(G[j][j] > 0.f);   // dependent (or empty) column
+      const bool dead = !(G[j][j] > 0.f);                 // an all-zero (or non-finite) column
+      const float floor_d = shift * G[j][j];
+      if (!(d > floor_d)) d = floor_d;                    // numerically dependent: shifted pivot
       const float rjj = dead ? 0.f : sqrtf(d);
       if (lane == j) R[j][j] = rjj;
       if (lane > j && lane < r) {
@@ -145,11 +199,25 @@ k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
   __syncthreads();
   float* pk = packed ? packed + (which == 0 ? M.ppk_off : M.qpk_off) : nullptr;
   const long long grow0 = (long long)t.y * OC_ROWS;
+  // last pass only: zero columns are refilled (see the header); value of (matrix, row, column)
+  const bool refill = gram_out == nullptr;
+  const float refill_scale = rsqrtf((float)rows_total);
+  // projection onto the sketch cells (last pass of Q): Z[h_j, :] += alpha s_j Q[j, :], packed layout
+  const bool project = proj_tables != nullptr && refill && which == 1 && pk != nullptr && M.tab_off >= 0;
+  const int32_t* tab = project ? proj_tables + M.tab_off : nullptr;
+  float* zpk = project ? packed + mats[proj_nm + t.x].qpk_off : nullptr;
   for (int i = threadIdx.x; i < rows; i += OC_THREADS) {
     float av[OC_MAXR];
     float* rowp = a + (size_t)i * r;
 #pragma unroll
     for (int k = 0; k < OC_MAXR; ++k) av[k] = k < r ? rowp[k] : 0.f;
+    float psc = 0.f;
+    long long ph = 0;
+    if (project) {
+      const int e = tab[grow0 + i];
+      psc = unpack_sign(e) * proj_alpha;
+      ph = unpack_bucket(e);
+    }
 #pragma unroll
     for (int c = 0; c < OC_MAXR; ++c) {
       if (c < r) {
@@ -159,6 +227,25 @@ k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
           if (k <= c) v = fmaf(av[k], Ri[k][c], v);
         rowp[c] = v;
         if (pk) pk[conef_packed_offset(grow0 + i, c, packed_np)] = v;
+        if (project) atomicAdd(zpk + conef_packed_offset(ph, c, packed_np), psc * v);
+      }
+    }
+  }
+  if (refill) {       // columns that were exactly zero (rare; not unrolled)
+#pragma unroll 1
+    for (int c = 0; c < r; ++c) {
+      if (R[c][c] > 0.f) continue;
+      for (int i = threadIdx.x; i < rows; i += OC_THREADS) {
+        float z[4];
+        conef_philox_normal4(ORTH_REFILL_SEED + (unsigned long long)t.x * 64ull + (unsigned long long)which * 32ull + c,
+                             (uint64_t)(grow0 + i), z);
+        const float v = z[0] * refill_scale;
+        a[(size_t)i * r + c] = v;
+        if (pk) pk[conef_packed_offset(grow0 + i, c, packed_np)] = v;
+        if (project) {
+          const int e = tab[grow0 + i];
+          atomicAdd(zpk + conef_packed_offset(unpack_bucket(e), c, packed_np), unpack_sign(e) * proj_alpha * v);
+        }
       }
     }
   }
@@ -170,23 +257,338 @@ k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
   }
 }
 
+// ---------------------------------------------------------------------------
+// The whole orthogonalisation in ONE launch: Gram partial -> barrier -> factor, apply, Gram partial of
+// the result -> barrier -> factor, apply, write.  The rows of a chunk stay in shared memory between
+// the rounds, so they are read from global memory once and written once, and the two launch
+// boundaries of the three-kernel form become two barriers among the CTAs of the launch.  Those
+// barriers need every tile CTA resident at once: the host checks the grid against the device's
+// capacity for this kernel and otherwise uses the three-kernel form.  Every wait is bounded.
+//
+// Sense-reversing barrier over two device words {arrivals, generation}; usable launch after launch
+// without a reset.  Returns false when the wait ran out.
+__device__ __forceinline__ bool cta_group_barrier(uint32_t* bar, unsigned expected, long long limit) {
+  __shared__ int bar_ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    bar_ok = 1;
+    const uint32_t gen = ld_acquire_sys(bar + 1);
+    __threadfence();                                   // this CTA's partials, then the arrival
+    if (atomicAdd(bar, 1u) == expected - 1) {
+      atomicExch(bar, 0u);
+      __threadfence();
+      atomicAdd(bar + 1, 1u);                          // releases the others
+    } else {
+      long long n = 0;
+      while (ld_acquire_sys(bar + 1) == gen) {
+        if (++n > limit) { bar_ok = 0; break; }
+        __nanosleep(32);
+      }
+    }
+    __threadfence();
+  }
+  __syncthreads();
+  return bar_ok != 0;
+}
+
+constexpr long long ORTH_BARRIER_LIMIT = 2LL * 1000 * 1000;
+
+// Shifted Cholesky factor of G (r x r, row stride RP + 1) and the inverse of its upper-triangular
+// factor, by the first warp; see the file header.  R and Ri must be zero on entry.
+template <int RP>
+__device__ __forceinline__ void chol_inverse(const float (*G)[RP + 1], float (*R)[RP + 1], float (*Ri)[RP + 1], int r,
+                                             float shift, float eps) {
+  const int lane = threadIdx.x;
+  for (int j = 0; j < r; ++j) {
+    float d = G[j][j];
+    for (int k = 0; k < j; ++k) d -= R[k][j] * R[k][j];
+    const bool dead = !(G[j][j] > 0.f);
+    const float floor_d = shift * G[j][j];
+    if (!(d > floor_d)) d = floor_d;
+    const float rjj = dead ? 0.f : sqrtf(d);
+    if (lane == j) R[j][j] = rjj;
+    if (lane > j && lane < r) {
+      float v = G[j][lane];
+      for (int k = 0; k < j; ++k) v -= R[k][j] * R[k][lane];
+      R[j][lane] = dead ? 0.f : v / rjj;
+    }
+    __syncwarp();
+  }
+  if (lane < r && R[lane][lane] > 0.f) {
+    const int c = lane;
+    for (int i = c; i >= 0; --i) {
+      if (!(R[i][i] > 0.f)) { Ri[i][c] = 0.f; continue; }
+      float v = (i == c) ? 1.f : 0.f;
+      for (int k = i + 1; k <= c; ++k) v -= R[i][k] * Ri[k][c];
+      Ri[i][c] = v / (R[i][i] + eps);
+    }
+  }
+}
+
+template <int RP>
+__global__ void __launch_bounds__(OC_THREADS, RP <= 16 ? 2 : 1)
+k_orth_one(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, int ntiles, int which,
+           float* __restrict__ buf, float* __restrict__ gram, const float* const* __restrict__ peer_bufs,
+           const uint32_t* __restrict__ flags, int world, uint32_t epoch, int* __restrict__ status, long long spin_limit,
+           const uint32_t* __restrict__ epoch_base, float eps, float* __restrict__ packed, int packed_np,
+           uint32_t* __restrict__ bar, const ConefOrthExtra X) {
+  extern __shared__ float xs[];                    // OC_ROWS x (RP + 1): the chunk's rows
+  constexpr int S = RP + 1;
+  __shared__ float G[RP][RP + 1], R[RP][RP + 1], Ri[RP][RP + 1];
+  __shared__ float part[OC_THREADS / 32][RP * RP < 32 ? 32 : RP * RP > 256 ? 256 : RP * RP];
+  __shared__ int ok;
+  bool peers_ok = true;
+  if (world > 1) {
+    if (threadIdx.x == 0) {
+      if (epoch_base != nullptr) epoch += *epoch_base;
+      ok = wait_flags_bounded(flags, world, epoch, spin_limit) ? 1 : 0;
+      if (!ok) atomicExch(status, CONEF_STATUS_FLAG_TIMEOUT);
+    }
+    __syncthreads();
+    peers_ok = ok != 0;     // on a timeout the CTA still takes part in the barriers, on zeros
+  }
+  if (peers_ok) {
+    const long long stride = (long long)gridDim.x * OC_THREADS;
+    const long long first = (long long)blockIdx.x * OC_THREADS + threadIdx.x;
+    for (long long i = first; i < X.zero0_n; i += stride) X.zero0[i] = 0.f;
+    for (long long i = first; i < X.zero1_n; i += stride) X.zero1[i] = 0.f;
+  }
+  if ((int)blockIdx.x >= ntiles) {                 // spare CTAs: the uncompressed tensors; no barriers
+    if (!peers_ok) return;
+    const long long stride = (long long)(gridDim.x - ntiles) * OC_THREADS;
+    for (long long e = (long long)(blockIdx.x - ntiles) * OC_THREADS + threadIdx.x; e < X.seg_total; e += stride) {
+      const int s = orth_find_seg(X.segs, X.nsegs, e);
+      const long long src = X.segs[s].src_off + (e - X.segs[s].dst_off);
+      if (X.seg_mode == 1) {
+        float v = X.bucket[src];
+        if (X.dense_err) { v += X.dense_err[src]; X.dense_err[src] = v; }
+        X.staging[e] = v;
+      } else {
+        float v = 0.f;
+        for (int p = 0; p < world; ++p) v += ld_relaxed_sys_f32(X.peer_staging[p] + e);
+        v *= X.seg_scale;
+        X.bucket[src] = v;
+        if (X.dense_err) X.dense_err[src] -= v;
+      }
+    }
+    return;
+  }
+  const int2 t = tiles[blockIdx.x];
+  const ConefMat M = mats[t.x];
+  const int rows_total = which == 0 ? M.n : M.m, r = M.r;
+  const size_t off = (which == 0 ? M.p_off : M.q_off) + (size_t)t.y * OC_ROWS * r;
+  const int rows = min(OC_ROWS, rows_total - t.y * OC_ROWS);
+  float* a = buf + off;
+  // ---- load the chunk (summing the peers' copies) ----
+  for (int i = threadIdx.x; i < rows * r; i += OC_THREADS) {
+    float v = 0.f;
+    if (peer_bufs != nullptr) {
+      if (peers_ok) for (int p = 0; p < world; ++p) v += ld_relaxed_sys_f32(peer_bufs[p] + off + i);
+    } else {
+      v = a[i];
+    }
+    const int row = i / r;
+    xs[row * S + (i - row * r)] = v;
+  }
+  const int first = blockIdx.x - t.y, count = (rows_total + OC_ROWS - 1) / OC_ROWS;
+  const int pairs = r * r;
+  float* pk = packed ? packed + (which == 0 ? M.ppk_off : M.qpk_off) : nullptr;
+  const long long grow0 = (long long)t.y * OC_ROWS;
+  const bool project = X.tables != nullptr && which == 1 && pk != nullptr && M.tab_off >= 0;
+  const int32_t* tab = project ? X.tables + M.tab_off : nullptr;
+  float* zpk = project ? packed + mats[X.nm + t.x].qpk_off : nullptr;
+  const float refill_scale = rsqrtf((float)rows_total);
+
+#pragma unroll 1
+  for (int round = 0; round < 2; ++round) {
+    __syncthreads();
+    // ---- Gram partial of the chunk, fixed summation order: warps over row slices, then warps 0..7 in order ----
+    {
+      float* g = gram + ((size_t)round * ntiles + blockIdx.x) * GRAM_STRIDE;
+      if (pairs <= 256) {
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int per = (rows + (OC_THREADS / 32) - 1) / (OC_THREADS / 32);
+        const int i0 = warp * per, i1 = min(rows, i0 + per);
+        for (int pr = lane; pr < pairs; pr += 32) {
+          const int ca = pr / r, cb = pr - ca * r;
+          float acc = 0.f;
+          for (int i = i0; i < i1; ++i) acc = fmaf(xs[i * S + ca], xs[i * S + cb], acc);
+          part[warp][pr] = acc;
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < pairs) {
+          float acc = 0.f;
+#pragma unroll
+          for (int w = 0; w < OC_THREADS / 32; ++w) acc += part[w][threadIdx.x];
+          g[threadIdx.x] = acc;
+        }
+      } else {
+        for (int pr = threadIdx.x; pr < pairs; pr += OC_THREADS) {
+          const int ca = pr / r, cb = pr - ca * r;
+          float acc = 0.f;
+          for (int i = 0; i < rows; ++i) acc = fmaf(xs[i * S + ca], xs[i * S + cb], acc);
+          g[pr] = acc;
+        }
+      }
+    }
+    if (!cta_group_barrier(bar, (unsigned)ntiles, ORTH_BARRIER_LIMIT) && threadIdx.x == 0)
+      atomicExch(status, CONEF_STATUS_FLAG_TIMEOUT);
+    // ---- the matrix's Gram matrix: partials in tile order; factor; inverse ----
+    for (int i = threadIdx.x; i < RP * (RP + 1); i += OC_THREADS) { (&R[0][0])[i] = 0.f; (&Ri[0][0])[i] = 0.f; }
+    for (int pr = threadIdx.x; pr < pairs; pr += OC_THREADS) {
+      const float* g = gram + ((size_t)round * ntiles + first) * GRAM_STRIDE + pr;
+      float acc = 0.f;
+      int c = 0;
+      for (; c + 4 <= count; c += 4) {
+        const float g0 = __ldcg(g + (size_t)c * GRAM_STRIDE), g1 = __ldcg(g + (size_t)(c + 1) * GRAM_STRIDE);
+        const float g2 = __ldcg(g + (size_t)(c + 2) * GRAM_STRIDE), g3 = __ldcg(g + (size_t)(c + 3) * GRAM_STRIDE);
+        acc += g0; acc += g1; acc += g2; acc += g3;
+      }
+      for (; c < count; ++c) acc += __ldcg(g + (size_t)c * GRAM_STRIDE);
+      G[pr / r][pr % r] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) chol_inverse<RP>(G, R, Ri, r, round == 0 ? ORTH_SHIFT : ORTH_SHIFT_FINAL, round == 0 ? eps : 0.f);
+    __syncthreads();
+    // ---- apply: every thread its rows ----
+    for (int i = threadIdx.x; i < rows; i += OC_THREADS) {
+      float av[RP];
+#pragma unroll
+      for (int k = 0; k < RP; ++k) av[k] = xs[i * S + k];
+      float psc = 0.f;
+      long long ph = 0;
+      if (round == 1 && project) {
+        const int e = tab[grow0 + i];
+        psc = unpack_sign(e) * X.alpha;
+        ph = unpack_bucket(e);
+      }
+#pragma unroll
+      for (int c = 0; c < RP; ++c) {
+        if (c < r) {
+          float v = 0.f;
+#pragma unroll
+          for (int k = 0; k <= c; ++k) v = fmaf(av[k], Ri[k][c], v);
+          if (round == 0) {
+            xs[i * S + c] = v;
+          } else {
+            a[(size_t)i * r + c] = v;
+            if (pk) pk[conef_packed_offset(grow0 + i, c, packed_np)] = v;
+            if (project) atomicAdd(zpk + conef_packed_offset(ph, c, packed_np), psc * v);
+          }
+        }
+      }
+    }
+  }
+  // ---- columns that were exactly zero: fixed pseudo-random values instead (rare; not unrolled) ----
+#pragma unroll 1
+  for (int c = 0; c < r; ++c) {
+    if (R[c][c] > 0.f) continue;
+    for (int i = threadIdx.x; i < rows; i += OC_THREADS) {
+      float z[4];
+      conef_philox_normal4(ORTH_REFILL_SEED + (unsigned long long)t.x * 64ull + (unsigned long long)which * 32ull + c,
+                           (uint64_t)(grow0 + i), z);
+      const float v = z[0] * refill_scale;
+      a[(size_t)i * r + c] = v;
+      if (pk) pk[conef_packed_offset(grow0 + i, c, packed_np)] = v;
+      if (project) {
+        const int e = tab[grow0 + i];
+        atomicAdd(zpk + conef_packed_offset(unpack_bucket(e), c, packed_np), unpack_sign(e) * X.alpha * v);
+      }
+    }
+  }
+}
+
+template <int RP>
+static int launch_orth_one(const ConefMat* mats, const int2* tiles, int ntiles, int seg_ctas, int which, float* buf,
+                           float eps, const float* const* peer_bufs, const uint32_t* flags, int world, uint32_t epoch,
+                           int* status, long long spin_limit, float* packed, int packed_np, float* gram,
+                           const uint32_t* epoch_base, uint32_t* bar, const ConefOrthExtra& X, cudaStream_t stream,
+                           bool* launched) {
+  *launched = false;
+  constexpr size_t smem = (size_t)OC_ROWS * (RP + 1) * sizeof(float);
+  static int capacity[64] = {};          // tile CTAs that can be resident at once, per device
+  int dev = 0;
+  CONEF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return 0;
+  if (capacity[dev] == 0) {
+    if (smem > 48 * 1024)
+      CONEF_CUDA(cudaFuncSetAttribute(k_orth_one<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int per_sm = 0, sms = 0;
+    CONEF_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_orth_one<RP>, OC_THREADS, smem));
+    CONEF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    capacity[dev] = per_sm * sms > 0 ? per_sm * sms : -1;
+  }
+  if (ntiles + seg_ctas > capacity[dev]) return 0;      // the caller uses the three-kernel form
+  k_orth_one<RP><<<ntiles + seg_ctas, OC_THREADS, smem, stream>>>(mats, tiles, ntiles, which, buf, gram, peer_bufs,
+                                                                 flags, world, epoch, status, spin_limit, epoch_base,
+                                                                 eps, packed, packed_np, bar, X);
+  CONEF_CHECK_LAUNCH("k_orth_one");
+  *launched = true;
+  return 0;
+}
+
+static thread_local int g_orth_launches = 0;
+// Kernels enqueued by this thread's most recent conef_orthogonalize_* call (1 or 3).
+extern "C" int conef_orth_last_launches(void) { return g_orth_launches; }
+
 // gram: scratch of 2 * ntiles * 1024 floats (one Gram partial per tile and round).
+extern "C" int conef_orthogonalize_fused(const ConefMat* mats, const int2* tiles, int ntiles, int which, float* buf,
+                                         float eps, const float* const* peer_bufs, const uint32_t* flags, int world,
+                                         uint32_t epoch, int* status, long long spin_limit, float* packed,
+                                         int packed_np, float* gram, const uint32_t* epoch_base,
+                                         const ConefOrthExtra* extra, cudaStream_t stream) {
+  ConefOrthExtra X;
+  if (extra) X = *extra; else memset(&X, 0, sizeof(X));
+  if (X.seg_total <= 0 || X.nsegs <= 0) { X.seg_mode = 0; X.seg_total = 0; }
+  int seg_ctas = 0;
+  if (X.seg_mode) {
+    seg_ctas = (int)((X.seg_total + 4 * OC_THREADS - 1) / (4 * OC_THREADS));
+    if (seg_ctas > 64) seg_ctas = 64;
+  }
+  if (ntiles <= 0 && seg_ctas == 0 && X.zero0_n <= 0 && X.zero1_n <= 0) return 0;
+  if (ntiles < 0) ntiles = 0;
+  if (ntiles > 0 && X.bar != nullptr && X.max_rank > 0 && X.max_rank <= OC_MAXR) {
+    // one launch when all tile CTAs can be resident together
+    bool launched = false;
+    int rc;
+#define CONEF_ORTH_ONE(RP)                                                                                     \
+    rc = launch_orth_one<RP>(mats, tiles, ntiles, seg_ctas, which, buf, eps, peer_bufs, flags, world, epoch, \
+                             status, spin_limit, packed, packed_np, gram, epoch_base, X.bar, X, stream, &launched)
+    if (X.max_rank <= 4) CONEF_ORTH_ONE(4);
+    else if (X.max_rank <= 8) CONEF_ORTH_ONE(8);
+    else if (X.max_rank <= 16) CONEF_ORTH_ONE(16);
+    else CONEF_ORTH_ONE(32);
+#undef CONEF_ORTH_ONE
+    if (rc != 0) return rc;
+    if (launched) { g_orth_launches = 1; return 0; }
+  }
+  g_orth_launches = ntiles > 0 ? 3 : 1;
+  int grid = ntiles + seg_ctas;
+  if (grid == 0) grid = 1;      // only regions to clear (after the flag wait)
+  float* gram2 = gram + (size_t)ntiles * GRAM_STRIDE;
+  k_gram<<<grid, OC_THREADS, 0, stream>>>(mats, tiles, ntiles, which, buf, gram,
+                                         peer_bufs, flags, world, epoch, status, spin_limit, epoch_base, X);
+  CONEF_CHECK_LAUNCH("k_gram");
+  if (ntiles <= 0) return 0;
+  k_qr_apply<<<ntiles, OC_THREADS, 0, stream>>>(mats, tiles, which, buf, gram, gram2, eps, ORTH_SHIFT, nullptr, 0,
+                                               nullptr, 0, 0.f);
+  CONEF_CHECK_LAUNCH("k_qr_apply");
+  k_qr_apply<<<ntiles, OC_THREADS, 0, stream>>>(mats, tiles, which, buf, gram2, nullptr, 0.f, ORTH_SHIFT_FINAL, packed,
+                                               packed_np, X.tables, X.nm, X.alpha);
+  CONEF_CHECK_LAUNCH("k_qr_apply");
+  return 0;
+}
+
 extern "C" int conef_orthogonalize_packed_ex(const ConefMat* mats, const int2* tiles, int ntiles, int nrecords,
                                              int which, float* buf, float eps, const float* const* peer_bufs,
                                              const uint32_t* flags, int world, uint32_t epoch, int* status,
                                              long long spin_limit, float* packed, int packed_np, float* gram,
                                              const uint32_t* epoch_base, cudaStream_t stream) {
-  if (ntiles <= 0) return 0;
   (void)nrecords;
-  float* gram2 = gram + (size_t)ntiles * GRAM_STRIDE;
-  k_gram<<<ntiles, OC_THREADS, 0, stream>>>(mats, tiles, which, buf, gram, peer_bufs, flags, world, epoch, status,
-                                           spin_limit, epoch_base);
-  CONEF_CHECK_LAUNCH("k_gram");
-  k_qr_apply<<<ntiles, OC_THREADS, 0, stream>>>(mats, tiles, which, buf, gram, gram2, eps, nullptr, 0);
-  CONEF_CHECK_LAUNCH("k_qr_apply");
-  k_qr_apply<<<ntiles, OC_THREADS, 0, stream>>>(mats, tiles, which, buf, gram2, nullptr, 0.f, packed, packed_np);
-  CONEF_CHECK_LAUNCH("k_qr_apply");
-  return 0;
+  if (ntiles <= 0) return 0;
+  return conef_orthogonalize_fused(mats, tiles, ntiles, which, buf, eps, world > 1 ? peer_bufs : nullptr, flags,
+                                   world, epoch, status, spin_limit, packed, packed_np, gram, epoch_base, nullptr,
+                                   stream);
 }
 
 extern "C" int conef_orthogonalize_packed(const ConefMat* mats, const int2* tiles, int ntiles, int nrecords,

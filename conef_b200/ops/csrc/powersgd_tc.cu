@@ -15,8 +15,14 @@
 //   warp 5, one lane : tcgen05.mma.kind::tf32 (4 x K=8 per stage), tcgen05.commit frees the stage
 //   epilogue         : tcgen05.ld 32 lanes x NP columns per warp -> r floats per output row,
 //                      plain store or fp32 atomics when K is split across CTAs
+//   tail             : the CTA that finishes last (a device counter) publishes the bucket's epoch
+//                      in every peer's flag array (release at system scope), so the all-reduce
+//                      that consumes the product starts from this kernel, not from a launch of
+//                      its own.  Peer memory is only written here (one flag word per peer),
+//                      never read, and never the source of a bulk or tensor copy.
 // Every mbarrier wait is bounded; when one gives up the CTA records
-// CONEF_STATUS_MBAR_TIMEOUT, lets its copies land, frees its tensor memory and returns.
+// CONEF_STATUS_MBAR_TIMEOUT, waits (bounded) for the copies it has in flight, frees its tensor
+// memory and returns.
 //
 // Replaces torch.matmul(tensor, q, out=p) and torch.matmul(tensor.t(), p, out=q) of the
 // reference (communication/powerSGD_hook.py:497-498,531-532), which are cuBLAS calls.
@@ -109,6 +115,14 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+struct TcSignal {           // all zero: nothing is published
+  uint32_t* done;           // counter of finished CTAs; zero between launches (the last CTA resets it)
+  uint32_t* const* peer_flags;
+  const uint32_t* epoch_base;   // nullable device word added to `epoch` (replayed launches)
+  uint32_t epoch;
+  int world, rank;
+};
+
 struct TcTile {      // one CTA's work
   int mat_flags;     // matrix index | (atomic accumulate << 30)
   int mn0;           // first output row of the 128-row tile (row of M in P mode, column of M in Q mode)
@@ -120,7 +134,7 @@ template <int NP> struct BStage { static constexpr int BYTES = NP * TC_BK * 4; }
 
 template <int NP>
 constexpr int tc_smem_bytes() {
-  return 1024 /* alignment slack */ + TC_STAGES * (A_STAGE_BYTES + BStage<NP>::BYTES) + 256;
+  return 1024 /* alignment slack */ + TC_STAGES * (A_STAGE_BYTES + BStage<NP>::BYTES) + 256;   // barriers, tmem slot, two flags
 }
 
 // Q_MODE = 0: out = P, A K-major, small operand = Q (m x r).   Q_MODE = 1: out = Q, A MN-major, small operand = P.
@@ -128,11 +142,7 @@ template <int NP, int Q_MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ maps,
             const TcTile* __restrict__ tiles, const float* __restrict__ small_packed, float* __restrict__ out_base,
-            int* __restrict__ status
-#ifdef CONEF_TC_DEBUG
-            , float* __restrict__ dbg
-#endif
-            ) {
+            int* __restrict__ status, const TcSignal sig) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* a_st = smem;
@@ -143,6 +153,7 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
   uint64_t* accum = bars + 2 * TC_STAGES;  // [1]
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * TC_STAGES + 1);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  volatile int* issued = abort_flag + 1;      // stages the producer has put in flight
 
   const TcTile T = tiles[blockIdx.x];
   const int mat = T.mat_flags & 0x3FFFFFFF;
@@ -162,6 +173,7 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    *issued = 0;
     for (int s = 0; s < TC_STAGES; ++s) {
       mbar_init(smem_u32(full + s), 1);       // the producer's arrive.expect_tx
       mbar_init(smem_u32(empty + s), 1);      // tcgen05.commit
@@ -197,6 +209,7 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
           if (Q_MODE) tma_load_2d(dst + a * BOX_BYTES, tmap, T.mn0 + 32 * a, k, bar);
           else        tma_load_2d(dst + a * BOX_BYTES, tmap, k, T.mn0 + 32 * a, bar);
         }
+        *issued = it + 1;
       }
     }
   } else if (warp == 5) {
@@ -254,15 +267,6 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
         }
       }
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#ifdef CONEF_TC_DEBUG
-      if (blockIdx.x == 0) {
-        for (int c = 0; c < NP; ++c) dbg[(warp * 32 + lane) * NP + c] = __uint_as_float(v[c]);
-        float* da = dbg + 128 * NP;
-        for (int i = threadIdx.x; i < A_STAGE_BYTES / 4; i += 128) da[i] = ((float*)a_st)[i];
-        float* dbb = da + A_STAGE_BYTES / 4;
-        for (int i = threadIdx.x; i < BStage<NP>::BYTES / 4; i += 128) dbb[i] = ((float*)b_st)[i];
-      }
-#endif
       const int row = T.mn0 + warp * 32 + lane;
       if (row < mn_total) {
         float* o = out + (size_t)row * r;
@@ -281,12 +285,31 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (*abort_flag) {
-    if (threadIdx.x == 0) atomicExch(status, CONEF_STATUS_MBAR_TIMEOUT);
-    __nanosleep(200000);   // give copies that are still in flight time to land in this CTA's shared memory
+    if (threadIdx.x == 0) {
+      atomicExch(status, CONEF_STATUS_MBAR_TIMEOUT);
+      // Copies still in flight must land before this CTA's shared memory passes to the next one:
+      // wait (bounded) for the `full` phase of every stage issued and not yet seen complete.
+      const int n_issued = *issued;
+      for (int it = max(0, n_issued - TC_STAGES); it < n_issued; ++it) {
+        const uint32_t bar = smem_u32(full + it % TC_STAGES), parity = (it / TC_STAGES) & 1;
+        for (long long spin = 0; spin < MBAR_SPIN_LIMIT && !mbar_try_wait(bar, parity); ++spin) {}
+      }
+    }
     __syncthreads();
   }
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 32;" ::"r"(tmem_base) : "memory");
+  }
+  // ---------------- publish: the last CTA tells the peers that this GPU's product is complete ----------------
+  if (sig.done != nullptr && threadIdx.x == 0) {
+    __threadfence();                                   // this CTA's results, then the counter
+    const unsigned prev = atomicAdd(sig.done, 1u);
+    if (prev == gridDim.x - 1) {
+      atomicExch(sig.done, 0u);                        // ready for the next launch
+      __threadfence_system();                          // everything counted above, then the flags
+      const uint32_t epoch = sig.epoch + (sig.epoch_base != nullptr ? *sig.epoch_base : 0u);
+      for (int p = 0; p < sig.world; ++p) st_release_sys(sig.peer_flags[p] + sig.rank, epoch);
+    }
   }
 }
 
@@ -310,19 +333,17 @@ EncodeTiledFn get_encode_fn() {
 
 template <int NP, int Q_MODE>
 int launch_tc(const ConefMat* mats, const void* maps, const void* tiles, int ntiles, const float* small_base,
-              float* out_base, int* status, cudaStream_t stream) {
+              float* out_base, int* status, const TcSignal& sig, cudaStream_t stream) {
   constexpr int smem = tc_smem_bytes<NP>();
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};      // the attribute is per device
+  int dev = 0;
+  CONEF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     CONEF_CUDA(cudaFuncSetAttribute(k_tc_skinny<NP, Q_MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   k_tc_skinny<NP, Q_MODE><<<ntiles, TC_THREADS, smem, stream>>>(mats, (const CUtensorMap*)maps, (const TcTile*)tiles,
-                                                               small_base, out_base, status
-#ifdef CONEF_TC_DEBUG
-                                                               , nullptr
-#endif
-                                                               );
+                                                               small_base, out_base, status, sig);
   CONEF_CHECK_LAUNCH("k_tc_skinny");
   return 0;
 }
@@ -363,15 +384,32 @@ extern "C" int conef_tc_encode_maps(const ConefMat* host_mats, int nmats, const 
 }
 
 // mode 0: P = M Q (small operand Q, output P); mode 1: Q = M^T P (small operand P, output Q).
-extern "C" int conef_psgd_tc(int mode, const ConefMat* mats, const void* maps, const void* tiles, int ntiles,
-                             const float* small_base, float* out_base, int max_rank, int* status,
-                             cudaStream_t stream) {   // small_base: packed small operands
+// With done != NULL the CTA that finishes last stores epoch (+ *epoch_base) into
+// peer_flags[p][rank] for every p < world.
+extern "C" int conef_psgd_tc_signal(int mode, const ConefMat* mats, const void* maps, const void* tiles, int ntiles,
+                                    const float* small_base, float* out_base, int max_rank, int* status,
+                                    uint32_t* done, uint32_t* const* peer_flags, int world, int rank,
+                                    uint32_t epoch, const uint32_t* epoch_base,
+                                    cudaStream_t stream) {   // small_base: packed small operands
   if (ntiles <= 0) return 0;
   if (max_rank > 32) { conef_set_error("tcgen05 path supports rank <= 32"); return 2; }
-  if (max_rank <= 16) {
-    return mode == 0 ? launch_tc<16, 0>(mats, maps, tiles, ntiles, small_base, out_base, status, stream)
-                     : launch_tc<16, 1>(mats, maps, tiles, ntiles, small_base, out_base, status, stream);
+  TcSignal sig;
+  memset(&sig, 0, sizeof(sig));
+  if (done != nullptr && peer_flags != nullptr && world > 1) {
+    sig.done = done; sig.peer_flags = peer_flags; sig.epoch_base = epoch_base;
+    sig.epoch = epoch; sig.world = world; sig.rank = rank;
   }
-  return mode == 0 ? launch_tc<32, 0>(mats, maps, tiles, ntiles, small_base, out_base, status, stream)
-                   : launch_tc<32, 1>(mats, maps, tiles, ntiles, small_base, out_base, status, stream);
+  if (max_rank <= 16) {
+    return mode == 0 ? launch_tc<16, 0>(mats, maps, tiles, ntiles, small_base, out_base, status, sig, stream)
+                     : launch_tc<16, 1>(mats, maps, tiles, ntiles, small_base, out_base, status, sig, stream);
+  }
+  return mode == 0 ? launch_tc<32, 0>(mats, maps, tiles, ntiles, small_base, out_base, status, sig, stream)
+                   : launch_tc<32, 1>(mats, maps, tiles, ntiles, small_base, out_base, status, sig, stream);
+}
+
+extern "C" int conef_psgd_tc(int mode, const ConefMat* mats, const void* maps, const void* tiles, int ntiles,
+                             const float* small_base, float* out_base, int max_rank, int* status,
+                             cudaStream_t stream) {
+  return conef_psgd_tc_signal(mode, mats, maps, tiles, ntiles, small_base, out_base, max_rank, status, nullptr,
+                              nullptr, 1, 0, 0, nullptr, stream);
 }

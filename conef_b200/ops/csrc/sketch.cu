@@ -258,6 +258,86 @@ __global__ void k_sketch_unproject(const ConefMat* __restrict__ mats, int nmats,
   }
 }
 
+// All-reduce of Q fused with the un-projection of the sketch term:
+//   Q[j, :] = scale * sum over peers p of ( Q_p[j, :] + alpha s_j Y_p[h_j, :] )
+// where every peer buffer holds [Q blocks | Y blocks] as its Q = M^T P pass left them
+// (Y_p = S_p^T P, record nmats + i).  The peers' values come over NVLink as plain loads, summed in
+// rank order (bit-identical on every rank), after a bounded wait for the epoch their Q pass
+// published.  tables == NULL: plain sum of the Q blocks.  world == 1: peer_bufs[0] is this GPU's own
+// buffer and nothing is waited for.
+__global__ void __launch_bounds__(256)
+k_reduce_q(const ConefMat* __restrict__ mats, int nmats, const int32_t* __restrict__ tables, float* __restrict__ out,
+           const float* const* __restrict__ peer_bufs, const uint32_t* __restrict__ my_flags, int world,
+           uint32_t epoch, float alpha, float scale, int* __restrict__ status, long long spin_limit,
+           const uint32_t* __restrict__ epoch_base) {
+  __shared__ int ok;
+  if (world > 1) {
+    if (threadIdx.x == 0) {
+      if (epoch_base != nullptr) epoch += *epoch_base;
+      ok = wait_flags_bounded(my_flags, world, epoch, spin_limit) ? 1 : 0;
+      if (!ok) atomicExch(status, CONEF_STATUS_FLAG_TIMEOUT);
+    }
+    __syncthreads();
+    if (!ok) return;
+  }
+  const ConefMat M = mats[blockIdx.y];
+  const int r = M.r;
+  const bool sk = tables != nullptr && M.tab_off >= 0;
+  const int32_t* tab = sk ? tables + M.tab_off : nullptr;
+  const long long y_off = sk ? mats[nmats + blockIdx.y].q_off : 0;
+  const bool vec = (r & 3) == 0 && ((M.q_off | y_off) & 3) == 0;
+  for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < M.m; j += gridDim.x * blockDim.x) {
+    float s = 0.f;
+    long long h = 0;
+    if (sk) { const int e = tab[j]; s = unpack_sign(e) * alpha; h = unpack_bucket(e); }
+    const long long qo = M.q_off + (long long)j * r, yo = y_off + h * r;
+    if (vec) {
+      for (int c = 0; c < r; c += 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int p = 0; p < world; ++p) {
+          float4 v;
+          asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                       : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(peer_bufs[p] + qo + c) : "memory");
+          if (sk) {
+            float4 y;
+            asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                         : "=f"(y.x), "=f"(y.y), "=f"(y.z), "=f"(y.w) : "l"(peer_bufs[p] + yo + c) : "memory");
+            v.x = fmaf(s, y.x, v.x); v.y = fmaf(s, y.y, v.y); v.z = fmaf(s, y.z, v.z); v.w = fmaf(s, y.w, v.w);
+          }
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        *reinterpret_cast<float4*>(out + qo + c) = make_float4(acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale);
+      }
+    } else {
+      for (int c = 0; c < r; ++c) {
+        float acc = 0.f;
+        for (int p = 0; p < world; ++p) {
+          float v = ld_relaxed_sys_f32(peer_bufs[p] + qo + c);
+          if (sk) v = fmaf(s, ld_relaxed_sys_f32(peer_bufs[p] + yo + c), v);
+          acc += v;
+        }
+        out[qo + c] = acc * scale;
+      }
+    }
+  }
+}
+
+extern "C" int conef_reduce_q(const ConefMat* mats, int nmats, int max_cols, const int32_t* tables, float* out,
+                              const float* const* peer_bufs, const uint32_t* my_flags, int world, uint32_t epoch,
+                              float alpha, float scale, int* status, long long spin_limit,
+                              const uint32_t* epoch_base, cudaStream_t stream) {
+  if (nmats <= 0) return 0;
+  if (((uintptr_t)out & 15) != 0) { conef_set_error("reduce_q: output must be 16-byte aligned"); return 2; }
+  int bx = (max_cols + 255) / 256;
+  if (bx < 1) bx = 1;
+  if (bx > 32) bx = 32;
+  dim3 grid(bx, nmats);
+  k_reduce_q<<<grid, 256, 0, stream>>>(mats, nmats, tables, out, peer_bufs, my_flags, world, epoch, alpha, scale,
+                                      status, spin_limit, epoch_base);
+  CONEF_CHECK_LAUNCH("k_reduce_q");
+  return 0;
+}
+
 extern "C" int conef_sketch_project(const ConefMat* mats, int nmats, int max_cols, const int32_t* tables,
                                     float* qz, float scale, int unproject, cudaStream_t stream) {
   if (nmats <= 0) return 0;

@@ -97,7 +97,22 @@ class PsgdPlan(C.Structure):
         ("graph_replays", C.c_int),
         ("topk", C.c_int), ("topk_ratio", C.c_float), ("topk_tiles", TileList), ("topk_scratch", C.c_void_p),
         ("ell", C.c_void_p), ("ell_hdr", C.c_void_p), ("dc_tiles", TileList * 4),
+        ("fused", C.c_int), ("has_slots", C.c_int), ("done_word", C.c_void_p),
+        ("zpk", C.c_void_p), ("zpk_n", C.c_longlong),
+        ("one_launch_orth", C.c_int), ("pad3", C.c_int),
     ]
+
+class OrthExtra(C.Structure):
+    """Mirror of ``ConefOrthExtra`` (csrc/conef.h)."""
+    _fields_ = [
+        ("zero0", C.c_void_p), ("zero0_n", C.c_longlong), ("zero1", C.c_void_p), ("zero1_n", C.c_longlong),
+        ("seg_mode", C.c_int), ("nsegs", C.c_int), ("segs", C.c_void_p), ("seg_total", C.c_longlong),
+        ("bucket", C.c_void_p), ("dense_err", C.c_void_p), ("staging", C.c_void_p), ("peer_staging", C.c_void_p),
+        ("seg_scale", C.c_float),
+        ("alpha", C.c_float), ("nm", C.c_int), ("tables", C.c_void_p),
+        ("bar", C.c_void_p), ("max_rank", C.c_int),
+    ]
+
 
 class RandblockPlan(C.Structure):
     """Mirror of ``ConefRandblockPlan`` (csrc/executor.h): field order and types must match."""
@@ -145,6 +160,13 @@ _SIGNATURES = {
     "conef_tc_supported": ([], C.c_int),
     "conef_tc_encode_maps": ([vp, C.c_int, vp, vp, vp, vp], C.c_int),
     "conef_psgd_tc": ([C.c_int, vp, vp, vp, C.c_int, vp, vp, C.c_int, vp, vp], C.c_int),
+    "conef_psgd_tc_signal": ([C.c_int, vp, vp, vp, C.c_int, vp, vp, C.c_int, vp, vp, vp, C.c_int, C.c_int, C.c_uint32,
+                              vp, vp], C.c_int),
+    "conef_orthogonalize_fused": ([vp, vp, C.c_int, C.c_int, vp, C.c_float, vp, vp, C.c_int, C.c_uint32, vp, c_ll, vp,
+                                   C.c_int, vp, vp, C.POINTER(OrthExtra), vp], C.c_int),
+    "conef_reduce_q": ([vp, C.c_int, C.c_int, vp, vp, vp, vp, C.c_int, C.c_uint32, C.c_float, C.c_float, vp, c_ll,
+                        vp, vp], C.c_int),
+    "conef_orth_last_launches": ([], C.c_int),
     "conef_gather_segments": ([vp, C.c_int, vp, vp, vp, c_ll, vp], C.c_int),
     "conef_scatter_segments": ([vp, C.c_int, vp, vp, C.c_int, vp, C.c_float, vp, c_ll, vp], C.c_int),
     "conef_randblock_gather": ([vp, vp, C.c_int, C.c_int, vp, vp, C.c_float, vp, vp, vp, vp, vp, vp,
@@ -180,7 +202,7 @@ _OPTIONAL = {}
 # How many kernels one call of an entry point enqueues (memsets not counted);
 # everything not listed launches exactly one.  Host-only entry points launch none.
 _KERNELS_PER_CALL = {
-    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_lowrank_correct": 2, "conef_topk_keep": 7, "conef_topk_chunk": 0, "conef_dc_groups": 0, "conef_psgd_run": 0, "conef_psgd_plan_size": 0, "conef_randblock_run": 0, "conef_randblock_plan_size": 0, "conef_psgd_step": 0, "conef_psgd_plan_release": 0, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
+    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_orthogonalize_fused": 3, "conef_lowrank_correct": 2, "conef_topk_keep": 7, "conef_topk_chunk": 0, "conef_orth_last_launches": 0, "conef_dc_groups": 0, "conef_psgd_run": 0, "conef_psgd_plan_size": 0, "conef_randblock_run": 0, "conef_randblock_plan_size": 0, "conef_psgd_step": 0, "conef_psgd_plan_release": 0, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
     "conef_ipc_get_handle": 0, "conef_ipc_open_handle": 0, "conef_ipc_close_handle": 0,
     "conef_cpu_hash_table": 0, "conef_cpu_sketch_query": 0, "conef_cpu_sketch_update": 0,
     "conef_cpu_gram_schmidt": 0,

@@ -212,6 +212,39 @@ def gram_schmidt_ref(mat: torch.Tensor, eps: float = 0.0) -> None:
             rest -= torch.sum(col * rest, dim=0) * col
 
 
+ORTH_SHIFT, ORTH_SHIFT_FINAL = 1e-5, 1e-7
+
+
+def shifted_cholesky_qr2_(mat: torch.Tensor, eps: float = 0.0) -> None:
+    """What the native orthogonalisation computes (csrc/orth.cu), restated in the matrix's own
+    precision: two rounds of ``A <- A R^-1`` with ``R`` the Cholesky factor of ``A^T A``, a pivot
+    never taken below ``shift`` times its column's squared norm, exactly-zero columns left zero
+    (the kernel refills those with pseudo-random values in its last round).  In exact arithmetic
+    and without shifts this is the Gram-Schmidt result of :func:`gram_schmidt_ref`."""
+    r = mat.shape[1]
+    for rnd, shift in enumerate((ORTH_SHIFT, ORTH_SHIFT_FINAL)):
+        G = mat.t() @ mat
+        R = torch.zeros_like(G)
+        for j in range(r):
+            if not bool(G[j, j] > 0):
+                continue
+            d = G[j, j] - (R[:j, j] ** 2).sum()
+            d = torch.maximum(d, shift * G[j, j])
+            R[j, j] = d.sqrt()
+            if j + 1 < r:
+                R[j, j + 1:] = (G[j, j + 1:] - R[:j, j] @ R[:j, j + 1:]) / R[j, j]
+        Ri = torch.zeros_like(R)
+        for c in range(r):
+            if not bool(R[c, c] > 0):
+                continue
+            for i in range(c, -1, -1):
+                if not bool(R[i, i] > 0):
+                    continue
+                v = (1.0 if i == c else 0.0) - R[i, i + 1:c + 1] @ Ri[i + 1:c + 1, c]
+                Ri[i, c] = v / (R[i, i] + (eps if rnd == 0 else 0.0))
+        mat.copy_(mat @ Ri)
+
+
 def topk_keep_(err: torch.Tensor, topk_ratio: float) -> None:
     """Keep the ``max(1, int(0.5*ratio*numel))`` largest-magnitude entries."""
     flat = err.view(-1)

@@ -34,7 +34,7 @@ from ..compressors.count_sketch import HalfDenseCS
 from ..ops import native
 from ..ops import reference as ref
 from . import plan as planlib
-from .symm import DEFAULT_SPIN_LIMIT, SymmBuffer, SymmUnavailable, comm_backend_choice
+from .symm import DEFAULT_SPIN_LIMIT, LocalSlots, SymmBuffer, SymmUnavailable, comm_backend_choice
 
 logger = logging.getLogger(__name__)
 
@@ -265,6 +265,7 @@ class PowerSGDEngine(_EngineBase):
                 mats[k]["qpk_off"], mats[k]["ppk_off"] = qpk, ppk
                 qpk += pad32(int(mats[k]["m"])) * self.np_cols
                 ppk += pad32(int(mats[k]["n"])) * self.np_cols
+        self.zpk_off = qpk         # the sketch records' packed operands follow the Q blocks'
         if self.fused_err:
             for k in range(nm):
                 err = mats[nm + k]
@@ -372,8 +373,10 @@ class PowerSGDEngine(_EngineBase):
             self.u_old = torch.zeros(max(self.total_u, 1), device=dev, dtype=torch.float32)
             self.qz2 = torch.zeros_like(self.qz)
             self._build_corrections()
-        self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_p + self.total_u, 4),
-                               max(plan.total_q + self.total_z, 4)], group, dev) if self.world > 1 else None
+        regions = [max(plan.total_unc, 4), max(plan.total_p + self.total_u, 4), max(plan.total_q + self.total_z, 4)]
+        self.symm = _try_symm(regions, group, dev) if self.world > 1 else None
+        # the slot buffers the fused pipeline accumulates into: peer-addressable, or local for one rank
+        self.slots = self.symm if self.symm is not None else (LocalSlots(regions, dev) if self.world == 1 else None)
         self._bound = None
         self.aux_ptr = -1
         self.use_tc = False
@@ -673,16 +676,29 @@ class PowerSGDEngine(_EngineBase):
         symm = self.symm
         if symm is not None:
             P.peer_flags, P.my_flags = symm.peer_flags_dev(), symm.flags_ptr()
+        slots = self.slots
+        if slots is not None:
             for slot in (0, 1):
-                P.peer_stage[slot], P.peer_p[slot], P.peer_q[slot] = (symm.peer_ptrs_dev(slot, r) for r in range(3))
-                P.local_stage[slot], P.local_p[slot], P.local_q[slot] = (ptr(symm.local(slot, r)) for r in range(3))
+                P.peer_stage[slot], P.peer_p[slot], P.peer_q[slot] = (slots.peer_ptrs_dev(slot, r) for r in range(3))
+                P.local_stage[slot], P.local_p[slot], P.local_q[slot] = (ptr(slots.local(slot, r)) for r in range(3))
+        P.has_slots = int(slots is not None)
         P.spin_limit = DEFAULT_SPIN_LIMIT
         # steps that draw no new random Q are captured into a CUDA graph per buffer slot and replayed
         P.use_graph = int(os.environ.get("CONEF_GRAPH", "1") == "1")
         if self.epoch_word is None:
-            self.epoch_word = torch.zeros(4, dtype=torch.int32, device=self.device)
+            self.epoch_word = torch.zeros(8, dtype=torch.int32, device=self.device)   # epoch base, tile counter, barrier words
         P.epoch_word = ptr(self.epoch_word)
         P.epoch_shadow = 0
+        # Fused pipeline (csrc/executor.cu:run_fused): both products must have tensor-core tiles, whose
+        # last CTA publishes the epoch; the low-rank store and the unbiased variant keep the long form.
+        P.done_word = ptr(self.epoch_word) + 4
+        self.fused = bool(slots is not None and self.use_tc and self.nm > 0 and self.n_tc_p > 0
+                          and self.qsets["all"][1] > 0 and not self.lowrank and self.variant != "unbiased"
+                          and os.environ.get("CONEF_FUSED", "1") == "1")
+        P.fused = int(self.fused)
+        P.one_launch_orth = int(os.environ.get("CONEF_ORTH_ONE", "1") == "1")
+        if self.ef_mode == native.EF_SKETCH and self.qpk is not None:
+            P.zpk, P.zpk_n = ptr(self.qpk) + 4 * self.zpk_off, self.qpk_total - self.zpk_off
         self.exec_plan = P
 
     def _release_exec(self) -> None:

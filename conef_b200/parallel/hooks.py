@@ -47,6 +47,24 @@ logger = logging.getLogger(__name__)
 SYNC_EVERY_BUCKET = False
 
 
+# Measurement switch: with BYPASS set every hook returns the bucket as it is (no compression,
+# no communication), so that "step time - step time with BYPASS" is the time the hook leaves
+# exposed on the critical path of a training step.  Gradients are then not synchronised.
+BYPASS = False
+
+
+def _measurable(hook):
+    import functools
+
+    @functools.wraps(hook)
+    def wrapped(state, bucket):
+        if BYPASS:
+            state.maybe_increase_iter(bucket)
+            return _done(bucket.buffer())
+        return hook(state, bucket)
+    return wrapped
+
+
 # --------------------------------------------------------------------------
 # helpers
 # --------------------------------------------------------------------------
@@ -213,6 +231,7 @@ def _native_ok(state, buf) -> bool:
     return native.use_native(buf) and buf.dtype == torch.float32
 
 
+@_measurable
 def powerSGD_hook(state: PowerSGDState, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """Layer-wise PowerSGD with optional (compressed) error feedback."""
     group = _group(state)
@@ -232,6 +251,7 @@ def hpowerSGD_hook(state: hPowerSGDState, bucket: dist.GradBucket) -> torch.futu
     return powerSGD_hook(state, bucket)
 
 
+@_measurable
 def C2CS_hook_v2(state: PowerSGDState, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """PowerSGD + count sketch built over the ``(m, n)`` reinterpretation of each
     ``(n, m)`` matrix's memory (communication/powerSGD_hook.py:918-920)."""
@@ -246,6 +266,7 @@ def C2CS_hook_v2(state: PowerSGDState, bucket: dist.GradBucket) -> torch.futures
     return _powersgd_torch(state, bucket, group, transposed_sketch=True)
 
 
+@_measurable
 def batched_powerSGD_hook(state: PowerSGDState, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """The whole bucket as one zero-padded square matrix; dense error feedback only."""
     group = _group(state)
@@ -312,6 +333,7 @@ def _batched_torch(state, bucket, group):
 # --------------------------------------------------------------------------
 # unbiased random-projection compressor
 # --------------------------------------------------------------------------
+@_measurable
 def UnbiasedMtrx_hook(state: unbiasedMtrxState, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """``M_hat = mean_ranks(M Q) Q^T`` with a fresh shared Gaussian ``Q`` every step;
     no orthogonalisation, no error feedback, nothing kept between steps.
@@ -441,6 +463,7 @@ def _randblock_torch(state, bucket, group, *, unbiased: bool) -> torch.futures.F
     return _done(buf)
 
 
+@_measurable
 def RandomBlock_hook(state: RandomBlockState, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """Send one random contiguous block per tensor; the rest goes to error feedback."""
     group = _group(state)
@@ -454,6 +477,7 @@ def RandomBlock_hook(state: RandomBlockState, bucket: dist.GradBucket) -> torch.
     return _randblock_torch(state, bucket, group, unbiased=False)
 
 
+@_measurable
 def UnbiasedRandomBlock_hook(state: UnbiasedRandomBlockState, bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
     """Random block without error feedback; selected values are divided by the
     selection probability so the estimate is unbiased."""

@@ -86,8 +86,9 @@ class SymmBuffer:
         if int(ok.item()) == 0:
             raise SymmUnavailable("; ".join(errors) or "a peer could not set up symmetric memory")
         self._build_pointer_tables()
-        # flags start at zero everywhere before anyone may signal
-        self.local_bytes[:FLAG_BYTES].zero_()
+        # flags start at zero everywhere before anyone may signal; the regions start at zero because
+        # the fused pipeline accumulates into them and only clears a slot after it has been read
+        self.local_bytes.zero_()
         torch.cuda.current_stream(device).synchronize()
         dist.barrier(group=group)
 
@@ -153,6 +154,38 @@ class SymmBuffer:
             for p in self._ipc_ptrs:
                 lib.conef_ipc_close_handle(p)
             self._ipc_ptrs = []
+
+
+class LocalSlots:
+    """The slot / region layout of :class:`SymmBuffer` in plain device memory for a group of one:
+    the same kernels then run on one GPU with pointer tables of a single entry and no flags."""
+
+    backend = "local"
+
+    def __init__(self, region_floats: Sequence[int], device: torch.device):
+        self.device, self.world, self.rank = device, 1, 0
+        self.region_floats = list(region_floats)
+        self.offsets: List[List[int]] = []
+        cursor = 0
+        for _slot in range(2):
+            row = []
+            for nf in self.region_floats:
+                row.append(cursor)
+                cursor = _round_up(cursor + nf * 4, ALIGN)
+            self.offsets.append(row)
+        self.total_bytes = cursor
+        self.local_bytes = torch.zeros(max(cursor, ALIGN), dtype=torch.uint8, device=device)
+        base = self.local_bytes.data_ptr()
+        rows = [[base + self.offsets[slot][reg]] for slot in range(2) for reg in range(len(self.region_floats))]
+        self.ptr_table = torch.tensor(rows, dtype=torch.int64, device=device)
+
+    def peer_ptrs_dev(self, slot: int, region: int) -> int:
+        return self.ptr_table[slot * len(self.region_floats) + region].data_ptr()
+
+    def local(self, slot: int, region: int) -> torch.Tensor:
+        off = self.offsets[slot][region]
+        nf = self.region_floats[region]
+        return self.local_bytes[off : off + nf * 4].view(torch.float32)
 
 
 def _tensor_from_ptr(ptr: int, nbytes: int, device: torch.device) -> torch.Tensor:

@@ -148,6 +148,29 @@ def main():
                                                       eng.tables.data_ptr(), qz.data_ptr(), 0.1, 1, st))
             t = _time(run_q, args.iters)
             record(f"q_{tag}: Q=G^TP+aH(S^TP)", t, mat_bytes + sk_bytes, "read G and the sketch once")
+        if tc == "1" and want("phase"):
+            # the three phases of a whole hook call, every launch they need included (executor, direct
+            # launches; CUDA events around each phase on the hook's stream)
+            for fused in ("1", "0"):
+                os.environ["CONEF_FUSED"] = fused
+                st2 = cb.PowerSGDState(None, matrix_approximation_rank=rank, start_powerSGD_iter=2,
+                                       use_error_compression=True, sketch_size=args.sketch_size)
+                st2.iter = 2
+                for _ in range(3):
+                    cb.powerSGD_hook(st2, bucket).wait()
+                torch.cuda.synchronize()
+                st2.enable_phase_timing()
+                for _ in range(args.iters):
+                    cb.powerSGD_hook(st2, bucket).wait()
+                torch.cuda.synchronize()
+                e2 = st2._engines[0]
+                label = f"fused, {e2.exec_plan.launched} launches in D" if e2.fused else "long form"
+                algo = {"psgd/P=GQ": mat_bytes + sk_bytes, "psgd/reduce+orth+Q=GtP": mat_bytes + sk_bytes,
+                        "psgd/reduce+decompress": 2 * mat_bytes + 2 * sk_bytes}
+                for name, rec in st2.phase_summary().items():
+                    record(f"phase {name} [{'fused' if e2.fused else 'long'}]", rec["ms_per_call"] * 1e-3,
+                           algo.get(name, mat_bytes), label)
+            os.environ.pop("CONEF_FUSED", None)
         if tc == "1":
             continue
         if want("orth"):

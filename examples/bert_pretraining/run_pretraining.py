@@ -7,11 +7,21 @@ LAMB with linear warm-up, gradient accumulation, optional activation checkpointi
 checkpoints that keep the three most recent files, resume from the newest checkpoint, SIGTERM
 turned into "checkpoint and exit", throughput summary in sequences per second.
 
+Execution modes, as in the reference (``run_pretraining_conef.py:356-404,492-499``):
+* one process per GPU under ``torchrun`` / ``torch.distributed.run``: DistributedDataParallel with
+  the compression hook of ``--grad_reducer`` (default);
+* ``--allreduce_post_accumulation`` (optionally ``--allreduce_post_accumulation_fp16``): no DDP and
+  no hook; gradients accumulate locally and are all-reduced once per optimizer step as one flat
+  buffer (forced off when ``--gradient_accumulation_steps 1``);
+* ``--local_rank -1``: a single process without a process group, ``torch.nn.DataParallel`` over
+  all visible GPUs when there are several.
+
 Differences: bf16 autocast instead of apex amp, the in-tree multi-tensor LAMB instead of apex
 FusedLAMB, synthetic shards instead of HDF5 files (no h5py / corpus on the box), and the reducer's
 state (error buffers, sketches, P/Q memory, RNG) is part of every checkpoint, which the reference omits.
 """
 import argparse
+import contextlib
 import os
 import sys
 import time
@@ -26,6 +36,7 @@ import conef_b200 as cb  # noqa: E402
 from conef_b200 import models  # noqa: E402
 from conef_b200.data import ShardPrefetcher, SyntheticBertShard, shard_files  # noqa: E402
 from conef_b200.optim import FusedLAMB, LinearWarmUpScheduler  # noqa: E402
+from conef_b200.parallel.accumulate import PostAccumulationAllReduce, broadcast_parameters  # noqa: E402
 from conef_b200.utils import (GracefulStop, JsonLogger, latest_checkpoint, load_checkpoint,  # noqa: E402
                               save_checkpoint)
 
@@ -63,9 +74,18 @@ def parse():
     p.add_argument("--min_compression_rate", type=float, default=2)
     p.add_argument("--orthogonalization_epsilon", type=float, default=0)
     p.add_argument("--error_compressor", default=None)
-    p.add_argument("--local_rank", type=int, default=int(os.environ.get("LOCAL_RANK", 0)))
+    p.add_argument("--allreduce_post_accumulation", action="store_true",
+                   help="accumulate locally, all-reduce all gradients once per optimizer step (no DDP, no hook)")
+    p.add_argument("--allreduce_post_accumulation_fp16", action="store_true",
+                   help="do that all-reduce in fp16")
+    p.add_argument("--local_rank", type=int, default=int(os.environ.get("LOCAL_RANK", 0)),
+                   help="-1: single process, torch.nn.DataParallel over the visible GPUs")
     args = p.parse_args()
     args.start_compression_iter = max(2, int(args.max_steps * args.start_compression_percentage))
+    if args.local_rank == -1 or args.gradient_accumulation_steps == 1:
+        args.allreduce_post_accumulation = args.allreduce_post_accumulation_fp16 = False
+    if args.gradient_accumulation_steps < 1 or args.train_batch_size % args.gradient_accumulation_steps:
+        raise ValueError("--train_batch_size must be a positive multiple of --gradient_accumulation_steps")
     return args
 
 
@@ -87,14 +107,16 @@ def build_model(args):
 
 def main():
     args = parse()
-    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    distributed = args.local_rank != -1
+    rank, world = (int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))) if distributed else (0, 1)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29504")
     cuda = torch.cuda.is_available()
-    device = torch.device("cuda", args.local_rank) if cuda else torch.device("cpu")
+    device = torch.device("cuda", max(args.local_rank, 0)) if cuda else torch.device("cpu")
     if cuda:
         torch.cuda.set_device(device)
-    dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world)
+    if distributed:
+        dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world)
     torch.manual_seed(args.seed + rank)
     net, cfg = build_model(args)
     net = net.to(device)
@@ -103,8 +125,19 @@ def main():
     opt = FusedLAMB([{"params": decay, "weight_decay": 0.01}, {"params": no_decay, "weight_decay": 0.0}],
                     lr=args.learning_rate)
     sched = LinearWarmUpScheduler(opt, warmup=args.warmup_proportion, total_steps=args.max_steps)
-    ddp = DDP(net, device_ids=[args.local_rank] if cuda else None, gradient_as_bucket_view=True)
-    state = cb.get_comm_hooks(args, ddp, args.local_rank)
+    state, post = None, None
+    if distributed and not args.allreduce_post_accumulation:
+        ddp = DDP(net, device_ids=[args.local_rank] if cuda else None, gradient_as_bucket_view=True)
+        state = cb.get_comm_hooks(args, ddp, args.local_rank)
+    elif distributed:
+        # no DDP: same start on every rank, one flat all-reduce per optimizer step
+        broadcast_parameters(net)
+        post = PostAccumulationAllReduce(
+            net.parameters(), wire_dtype=torch.float16 if args.allreduce_post_accumulation_fp16 else torch.float32)
+        ddp = net
+    else:
+        ddp = torch.nn.DataParallel(net) if cuda and torch.cuda.device_count() > 1 else net
+    no_sync = ddp.no_sync if isinstance(ddp, DDP) else contextlib.nullcontext
     crit = models.BertPretrainingCriterion(cfg.vocab_size)
     global_step, epoch = 0, 0
     resumed = False
@@ -124,7 +157,7 @@ def main():
     stop, log = GracefulStop(), JsonLogger(os.path.join(args.output_dir, "log.jsonl") if rank == 0 else None)
     micro = args.train_batch_size // args.gradient_accumulation_steps
     steps_this_run = args.steps_this_run if args.steps_this_run > 0 else args.max_steps
-    done, t_start, seqs = 0, time.time(), 0
+    done, t_start, seqs, skipped_steps = 0, time.time(), 0, 0
     amp = torch.autocast("cuda", dtype=torch.bfloat16) if (cuda and args.bf16) else torch.autocast("cpu", enabled=False)
     ddp.train()
     def epoch_shards(epoch):
@@ -147,15 +180,18 @@ def main():
         for it, batch in enumerate(batches(epoch)):
             ids, seg, mask, labels, nsp = (t.to(device, non_blocking=True) for t in batch)
             sync = (it + 1) % args.gradient_accumulation_steps == 0
-            ctx = ddp.no_sync() if not sync else torch.autocast("cpu", enabled=False)
-            with ctx, amp:
+            with (no_sync() if not sync else contextlib.nullcontext()), amp:
                 loss = crit(ddp(ids, seg, mask), (labels, nsp)) / args.gradient_accumulation_steps
-            with (ddp.no_sync() if not sync else torch.autocast("cpu", enabled=False)):
+            with (no_sync() if not sync else contextlib.nullcontext()):
                 loss.backward()
             seqs += ids.size(0)
             if not sync:
                 continue
             sched.step()
+            if post is not None and not post.allreduce():
+                skipped_steps += 1                # a non-finite value came out of the fp16 all-reduce
+                opt.zero_grad(set_to_none=False)
+                continue
             opt.step()
             opt.zero_grad(set_to_none=False)
             global_step += 1
@@ -176,10 +212,15 @@ def main():
     save_checkpoint(args.output_dir, global_step, model=ddp, optimizer=opt, reducer_state=state,
                     extra={"epoch": epoch, "per_rank": True}, rank=rank)
     final = torch.tensor([float(loss) * args.gradient_accumulation_steps], device=device)
-    dist.all_reduce(final)
+    if distributed:
+        dist.all_reduce(final)
+    mode = "ddp+hook" if isinstance(ddp, DDP) else "post-accumulation all-reduce" if post is not None else \
+        "data-parallel (one process)" if isinstance(ddp, torch.nn.DataParallel) else "single device"
     log.log("summary", training_sequences_per_second=seqs * world / dt, final_loss=float(final) / world,
-            ef_buffer_mb=(state.ef_buffer_bytes() / 1e6) if state else 0.0)
-    dist.destroy_process_group()
+            ef_buffer_mb=(state.ef_buffer_bytes() / 1e6) if state else 0.0, mode=mode, skipped_steps=skipped_steps,
+            allreduce_mb_per_step=(post.bytes_on_wire / 1e6) if post is not None else None)
+    if distributed:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

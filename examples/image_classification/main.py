@@ -4,7 +4,10 @@
 Counterpart of the reference's ``examples/ImageClassification/main.py``: same flags
 (``--model``, ``--grad_reducer``, ``--start_compression_iter``, ``--compression_ratio``, ``--beta``,
 ``--sketch_size``, ``--matrix_approximation_rank``, ``--min_compression_rate`` ...), SGD with
-Nesterov momentum, three learning-rate decay milestones, accuracy per epoch, results pickled.
+Nesterov momentum, three learning-rate decay epochs, test accuracy after every epoch on rank 0
+(``main.py:238-257,300-306``), and the results folder the reference writes (``main.py:23-66``):
+``train_losses.pkl``, ``test_accuracies.pkl``, ``time_per_epoch.pkl`` and a ``README.md`` listing the
+run's settings and best accuracy, appended to instead of overwritten with ``--resume``.
 Launch with ``torchrun --nproc-per-node N examples/image_classification/main.py ...`` (or as a
 single process).  Without ``--data_path`` the data is synthetic: there is no dataset on the box.
 """
@@ -47,7 +50,13 @@ def parse():
     p.add_argument("--momentum", type=float, default=0.9)
     p.add_argument("--weight_decay", type=float, default=5e-4)
     p.add_argument("--nesterov", action="store_true", default=True)
-    p.add_argument("--lr_decay", type=float, default=0.1)
+    p.add_argument("--lr_decay_ratio", type=float, default=10, help="the learning rate is divided by this ...")
+    p.add_argument("--lr_decay_at_epoch1", type=int, default=None, help="... at these epochs (default: 53 %, 80 %")
+    p.add_argument("--lr_decay_at_epoch2", type=int, default=None, help="and 100 % of --epochs, the reference's")
+    p.add_argument("--lr_decay_at_epoch3", type=int, default=None, help="80 / 120 / 150 of 150)")
+    p.add_argument("--test_steps", type=int, default=10, help="synthetic data only: test batches per epoch")
+    p.add_argument("--name", default="image_classification", help="results go to <results>/<name>")
+    p.add_argument("-r", "--resume", type=int, default=0, help="1: append to the results README of an earlier run")
     p.add_argument("--grad_reducer", default="conef_powersgd", choices=cb.REDUCERS)
     p.add_argument("--start_compression_iter", type=int, default=10)
     p.add_argument("--compression_ratio", type=float, default=0.1)
@@ -58,9 +67,48 @@ def parse():
     p.add_argument("--orthogonalization_epsilon", type=float, default=0)
     p.add_argument("--error_compressor", default=None)
     p.add_argument("--bf16", action="store_true")
-    p.add_argument("--results", default="results/image_classification")
+    p.add_argument("--results", default="results")
     p.add_argument("--seed", type=int, default=0)
     return p.parse_args()
+
+
+def evaluate(net, loader, device, autocast_dtype=None, channels_last=False) -> float:
+    """Top-1 accuracy in percent over ``loader`` (the reference's ``test``, main.py:238-257)."""
+    was_training = net.training
+    net.eval()
+    correct = total = 0
+    with torch.no_grad():
+        for x, y in loader:
+            x, y = x.to(device, non_blocking=True), y.to(device, non_blocking=True)
+            if channels_last:
+                x = x.contiguous(memory_format=torch.channels_last)
+            with torch.autocast(device.type, dtype=autocast_dtype, enabled=autocast_dtype is not None):
+                out = net(x)
+            correct += int(out.argmax(1).eq(y).sum())
+            total += y.numel()
+    net.train(was_training)
+    return 100.0 * correct / max(1, total)
+
+
+def write_results(args, result, world) -> str:
+    """The reference's results folder (main.py:23-66): three pickles and a README of the settings."""
+    directory = os.path.join(args.results, args.name)
+    make_directory(directory)
+    save_obj(result["train_losses"], os.path.join(directory, "train_losses"))
+    save_obj(result["test_accuracies"], os.path.join(directory, "test_accuracies"))
+    save_obj(result["time"], os.path.join(directory, "time_per_epoch"))
+    save_obj({"args": vars(args), "history": result["history"]}, os.path.join(directory, "results"))
+    summary = dict(model=args.model, dataset=args.dataset, opt="SGD", lr=args.lr, batch_size=args.batch_size,
+                   world_size=world, momentum=args.momentum, nesterov=args.nesterov, weight_decay=args.weight_decay,
+                   grad_reducer=args.grad_reducer, matrix_approximation_rank=args.matrix_approximation_rank,
+                   beta=args.beta, sketch_size=args.sketch_size,
+                   best_acc=max(result["test_accuracies"]) if result["test_accuracies"] else 0)
+    with open(os.path.join(directory, "README.md"), "a" if args.resume else "w") as f:
+        if args.resume:
+            f.write("\n")
+        for key, val in summary.items():
+            f.write(f"{key}: {val}\\\n")
+    return directory
 
 
 def main():
@@ -81,8 +129,11 @@ def main():
         import torchvision.transforms as T
         tf = T.Compose([T.RandomCrop(32, padding=4), T.RandomHorizontalFlip(), T.ToTensor()])
         ds = getattr(torchvision.datasets, args.dataset.upper())(args.data_path, train=True, transform=tf)
+        test_ds = getattr(torchvision.datasets, args.dataset.upper())(args.data_path, train=False, transform=T.ToTensor())
     else:
         ds = SyntheticImages(args.steps_per_epoch * args.batch_size * world, classes)
+        test_ds = SyntheticImages(args.test_steps * args.batch_size, classes, seed=args.seed + 7919)
+    test_loader = DataLoader(test_ds, args.batch_size, shuffle=False, num_workers=2, pin_memory=cuda)
     sampler = DistributedSampler(ds, world, rank, shuffle=True, seed=args.seed)
     loader = DataLoader(ds, args.batch_size, sampler=sampler, num_workers=2, pin_memory=cuda, drop_last=True)
     trainer = cb.DataParallelTrainer(
@@ -91,11 +142,17 @@ def main():
                                   nesterov=args.nesterov),
         F.cross_entropy, reducer=args, device=device, autocast_dtype=torch.bfloat16 if (args.bf16 and cuda) else None,
         channels_last=cuda)
-    milestones = [int(args.epochs * f) for f in (0.5, 0.75, 0.9)]
-    sched = torch.optim.lr_scheduler.MultiStepLR(trainer.optimizer, milestones, args.lr_decay)
+    defaults = [round(args.epochs * f) for f in (80 / 150, 120 / 150, 1.0)]
+    decay_at = {d if v is None else v for v, d in zip(
+        (args.lr_decay_at_epoch1, args.lr_decay_at_epoch2, args.lr_decay_at_epoch3), defaults)}
     stop, log = GracefulStop(), JsonLogger(stdout=True)
     history = []
+    result = dict(train_losses=[], test_accuracies=[], time=[], history=history)
+    ac_dtype = torch.bfloat16 if (args.bf16 and cuda) else None
     for epoch in range(args.epochs):
+        if epoch in decay_at and epoch > 0:
+            for group in trainer.optimizer.param_groups:
+                group["lr"] /= args.lr_decay_ratio
         sampler.set_epoch(epoch)
         t0, seen, correct, loss_sum = time.time(), 0, 0, 0.0
         for x, y in loader:
@@ -104,18 +161,23 @@ def main():
             seen += y.numel()
             if stop.requested:
                 break
-        sched.step()
         dt = time.time() - t0
         rec = dict(epoch=epoch, loss=loss_sum / max(1, len(loader)), img_per_s=seen * world / dt,
+                   lr=trainer.optimizer.param_groups[0]["lr"],
                    ef_buffer_mb=(trainer.state.ef_buffer_bytes() / 1e6) if trainer.state else 0.0)
+        if rank == 0:       # as the reference: rank 0 evaluates its replica on the whole test set
+            rec["test_acc"] = evaluate(trainer.model.module, test_loader, device, ac_dtype, channels_last=cuda)
+            result["train_losses"].append(rec["loss"])
+            result["test_accuracies"].append(rec["test_acc"])
+            result["time"].append(dt)
         history.append(rec)
         log.log(epoch, **rec)
         if stop.requested:
             break
     trainer.check()
     if rank == 0:
-        make_directory(args.results)
-        save_obj({"args": vars(args), "history": history}, os.path.join(args.results, "results"))
+        write_results(args, result, world)
+    dist.barrier()
     dist.destroy_process_group()
 
 

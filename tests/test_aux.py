@@ -337,6 +337,73 @@ def test_bert_driver_phase_two_starts_from_phase_one_weights(tmp_path):
         run(tmp_path / "p3", "--init_checkpoint", str(tmp_path / "nothing_here"))
 
 
+def test_bert_driver_single_process_and_post_accumulation_modes(tmp_path):
+    """--local_rank -1 (no process group; DataParallel when several GPUs are visible) and
+    --allreduce_post_accumulation[_fp16] (no DDP: one flat all-reduce per optimizer step, two gloo ranks)."""
+    import json, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "examples/bert_pretraining/run_pretraining.py")
+    common = ["--bert_model", "tiny", "--train_batch_size", "4", "--max_steps", "3", "--shard_size", "32",
+              "--max_seq_length", "32", "--max_predictions_per_seq", "5"]
+
+    def summary(out):
+        lines = [json.loads(l) for l in open(os.path.join(out, "log.jsonl"))]
+        return [l for l in lines if l.get("step") == "summary"][-1]
+
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    subprocess.run([sys.executable, script, *common, "--output_dir", str(tmp_path / "single"), "--local_rank", "-1",
+                    "--grad_reducer", "allreduce"], check=True, env=env, timeout=600)
+    s1 = summary(str(tmp_path / "single"))
+    assert s1["mode"] == "single device" and np.isfinite(s1["final_loss"])
+
+    port = str(free_port())
+    procs = []
+    for r in range(2):
+        e = dict(env, MASTER_ADDR="127.0.0.1", MASTER_PORT=port, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK="0")
+        procs.append(subprocess.Popen([sys.executable, script, *common, "--output_dir", str(tmp_path / "post"),
+                                       "--gradient_accumulation_steps", "2", "--allreduce_post_accumulation",
+                                       "--allreduce_post_accumulation_fp16", "--local_rank", "0"], env=e))
+    assert [p.wait(timeout=600) for p in procs] == [0, 0]
+    s2 = summary(str(tmp_path / "post"))
+    assert s2["mode"] == "post-accumulation all-reduce" and np.isfinite(s2["final_loss"])
+    assert s2["allreduce_mb_per_step"] > 0 and s2["ef_buffer_mb"] == 0.0
+
+
+def test_post_accumulation_allreduce_averages_over_ranks():
+    from conef_b200.parallel.accumulate import PostAccumulationAllReduce, broadcast_parameters
+    from helpers import run_ranks
+
+    run_ranks(_post_accumulation_worker, world=2, args=(), backend="gloo")
+
+
+def _post_accumulation_worker(rank, world):
+    import torch.distributed as dist
+    from conef_b200.parallel.accumulate import PostAccumulationAllReduce, broadcast_parameters
+
+    torch.manual_seed(100 + rank)
+    net = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Tanh(), torch.nn.Linear(5, 2))
+    broadcast_parameters(net)
+    flat = torch.cat([p.detach().reshape(-1) for p in net.parameters()])
+    both = [torch.zeros_like(flat) for _ in range(world)]
+    dist.all_gather(both, flat)
+    assert torch.equal(both[0], both[1])                     # every rank starts from rank 0's weights
+    for dtype, tol in ((torch.float32, 1e-6), (torch.float16, 2e-3)):
+        net.zero_grad()
+        for micro in range(2):                                # two micro-batches accumulate locally
+            net(torch.randn(3, 6)).pow(2).sum().backward()
+        local = torch.cat([p.grad.reshape(-1) for p in net.parameters()]).clone()
+        gathered = [torch.zeros_like(local) for _ in range(world)]
+        dist.all_gather(gathered, local)
+        red = PostAccumulationAllReduce(net.parameters(), wire_dtype=dtype, accumulation_steps=2,
+                                        predivide_accumulation=True)
+        assert red.allreduce()
+        got = torch.cat([p.grad.reshape(-1) for p in net.parameters()])
+        torch.testing.assert_close(got, sum(gathered) / (world * 2), rtol=tol, atol=tol * 10)
+        assert red.bytes_on_wire == local.numel() * (4 if dtype == torch.float32 else 2)
+
+
 def test_parallel_text_and_translation_driver(tmp_path):
     import subprocess, sys
     src = ["ein mann geht .", "eine frau liest ein buch .", "der hund rennt schnell !", "", "ein kind spielt ."] * 8
@@ -365,3 +432,119 @@ def test_parallel_text_and_translation_driver(tmp_path):
                     "--num_encoder_layers", "1", "--num_decoder_layers", "1", "--start_compression_iter", "2",
                     "--matrix_approximation_rank", "2", "--grad_reducer", "ef_powersgd"],
                    check=True, env=env, timeout=600)
+
+
+def test_image_driver_evaluates_and_writes_the_results_folder(tmp_path):
+    """Test accuracy per epoch on rank 0, learning-rate decay epochs, results pickles and a README that
+    --resume appends to (reference examples/ImageClassification/main.py:23-66,238-257,287-306)."""
+    import subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "examples/image_classification/main.py")
+
+    def run(*extra):
+        env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()), RANK="0", WORLD_SIZE="1",
+                   CUDA_VISIBLE_DEVICES="")
+        subprocess.run([sys.executable, script, "--model", "lenet", "--epochs", "2", "--steps_per_epoch", "3",
+                        "--test_steps", "2", "--batch_size", "8", "--grad_reducer", "ef_powersgd",
+                        "--start_compression_iter", "2", "--results", str(tmp_path), "--name", "run",
+                        "--lr_decay_at_epoch1", "1", *extra], check=True, env=env, timeout=600)
+    run()
+    folder = tmp_path / "run"
+    acc = utils.load_obj(str(folder / "test_accuracies"))
+    assert len(acc) == 2 and all(0.0 <= a <= 100.0 for a in acc)
+    assert len(utils.load_obj(str(folder / "train_losses"))) == 2 and len(utils.load_obj(str(folder / "time_per_epoch"))) == 2
+    hist = utils.load_obj(str(folder / "results"))["history"]
+    assert hist[1]["lr"] == pytest.approx(hist[0]["lr"] / 10)
+    readme = (folder / "README.md").read_text()
+    assert "grad_reducer: ef_powersgd\\" in readme and "best_acc:" in readme
+    run("--resume", "1")
+    assert (folder / "README.md").read_text().count("grad_reducer: ef_powersgd") == 2
+
+
+def test_corpus_formatting_segmentation_and_sharding(tmp_path):
+    """wikiextractor / books formatting -> rule-based sentences -> balanced shards -> .npz instances
+    (reference data/WikicorpusTextFormatting.py, BookscorpusTextFormatting.py, TextSharding.py, bertPrep.py)."""
+    import subprocess, sys
+    from conef_b200.data import corpus_prep as cp
+
+    seg = cp.RuleSegmenter()
+    assert seg.segment_string('Dr. Smith went to Washington. He arrived at 3 p.m. on Monday! "Was it late?" No.') == \
+        ["Dr. Smith went to Washington.", "He arrived at 3 p.m. on Monday!", '"Was it late?"', "No."]
+    assert seg.segment_string("One sentence only") == ["One sentence only"]
+
+    wd = tmp_path / "data"
+    wiki = wd / "download" / "wikicorpus_en" / "AA"
+    wiki.mkdir(parents=True)
+    docs = []
+    for k in range(12):
+        body = " ".join(f"Article {k} sentence {j} is here." for j in range(1 + (k * 7) % 9))
+        docs.append(f'<doc id="{k}" url="u" title="T{k}">\nT{k}\n\n{body}\n</doc>\n')
+    (wiki / "wiki_00").write_text("".join(docs[:6]))
+    (wiki / "wiki_01").write_text("".join(docs[6:]))
+    books = wd / "download" / "bookscorpus"
+    books.mkdir(parents=True)
+    for k in range(5):
+        (books / f"book{k}.txt").write_text("\n".join(f"Book {k} line {j} ends here." for j in range(3 + k)) + "\n\n")
+    out = wd / "fmt"
+    out.mkdir()
+    assert cp.format_wikicorpus(str(wd / "download" / "wikicorpus_en"), str(out / "wiki.txt")) == 12
+    assert cp.format_bookscorpus(str(books), str(out / "books.txt")) == 5
+    lines = (out / "wiki.txt").read_text().splitlines()
+    assert lines[0].startswith("Article 0 sentence 0") and "T0" not in lines[0]       # the title line is dropped
+
+    sh = cp.Sharding([str(out / "wiki.txt"), str(out / "books.txt")], str(tmp_path / "shards" / "corpus"), 3, 2, 0.25)
+    sh.load_articles()
+    sh.segment_articles_into_sentences()
+    sh.distribute_articles_over_shards()
+    files = sh.write_shards_to_disk()
+    assert [os.path.basename(f) for f in files] == ["corpus_training_0.txt", "corpus_training_1.txt",
+                                                     "corpus_training_2.txt", "corpus_test_0.txt", "corpus_test_1.txt"]
+    placed = sorted(a for shard in list(sh.output_training_files.values()) + list(sh.output_test_files.values())
+                    for a in shard)
+    assert placed == list(range(17))                                 # every article exactly once
+    train = [sh.sentences_per_shard(s) for s in sh.output_training_files.values()]
+    test = [sh.sentences_per_shard(s) for s in sh.output_test_files.values()]
+    total = sum(train) + sum(test)
+    assert max(train) - min(train) <= 9 and abs(sum(test) / total - 0.25) < 0.12
+    text = open(files[0]).read()
+    assert text.endswith("\n\n") and "\n\n\n" not in text            # sentence per line, blank line between articles
+    with pytest.raises(ValueError):
+        cp.Sharding([str(out / "books.txt")], str(tmp_path / "x"), 4, 4, 0.1).distribute_articles_over_shards()
+
+    # the command-line pipeline end to end on the books
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "examples/bert_pretraining/prep_corpus.py")
+    vocab = tmp_path / "vocab.txt"
+    words = ["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]", "book", "line", "ends", "here", ".", "0", "1", "2", "3", "4",
+             "5", "6", "7"]
+    vocab.write_text("\n".join(words) + "\n")
+    common = [sys.executable, script, "--dataset", "bookscorpus", "--working_dir", str(wd), "--n_training_shards", "2",
+              "--n_test_shards", "1", "--fraction_test_set", "0.2"]
+    subprocess.run(common + ["--action", "text_formatting"], check=True, timeout=300)
+    subprocess.run(common + ["--action", "sharding"], check=True, timeout=300)
+    subprocess.run(common + ["--action", "create_pretraining_files", "--vocab_file", str(vocab), "--max_seq_length", "32",
+                             "--max_predictions_per_seq", "5"], check=True, timeout=300)
+    import glob
+    npz = glob.glob(str(wd / "npz" / "**" / "*.npz"), recursive=True)
+    assert len(npz) == 3
+    shard = data.pretraining.load_shard(npz[0])
+    assert shard["input_ids"].shape[1] == 32
+    assert subprocess.run(common + ["--action", "download"], capture_output=True).returncode != 0
+
+
+def test_hardware_presets_print_their_settings():
+    """configs/pretrain_config.sh: presets per machine shape (reference scripts/configs/pretrain_config.sh)."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "examples/bert_pretraining/configs/pretrain_config.sh")
+    out = subprocess.run(["bash", script, "b200_8gpu_bf16_conef"], capture_output=True, text=True, check=True).stdout
+    got = dict(line.split("=", 1) for line in out.split())
+    assert got["GPUS"] == "8" and got["REDUCER"] == "conef_powersgd" and got["RANK_R"] == "8"
+    assert int(got["GPUS"]) * int(got["BATCH1"]) * int(got["ACCUM1"]) == 8192      # the LAMB recipe's global batch
+    assert int(got["GPUS"]) * int(got["BATCH2"]) * int(got["ACCUM2"]) == 4096
+    one = dict(l.split("=", 1) for l in subprocess.run(["bash", script, "b200_1gpu_bf16_conef"], capture_output=True,
+                                                       text=True, check=True).stdout.split())
+    assert int(one["GPUS"]) * int(one["BATCH1"]) * int(one["ACCUM1"]) == 8192
+    post = subprocess.run(["bash", script, "b200_8gpu_bf16_post_accumulation"], capture_output=True, text=True,
+                          check=True).stdout
+    assert "POST_ACCUMULATION_FP16=1" in post and "REDUCER=allreduce" in post

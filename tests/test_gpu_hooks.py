@@ -305,6 +305,48 @@ def test_executor_graph_replay_matches_direct_launches(single_rank_group, monkey
             assert (a - c).norm() <= 1e-2 * c.norm()
 
 
+@pytest.mark.parametrize("kw", [
+    dict(matrix_approximation_rank=4, use_error_feedback=False, warm_start=True),
+    dict(matrix_approximation_rank=4, use_error_feedback=True, warm_start=True),
+    dict(matrix_approximation_rank=4, use_error_feedback=True, warm_start=True, use_error_compression=True,
+         sketch_size=0.1),
+    dict(matrix_approximation_rank=8, use_error_feedback=True, warm_start=False, use_error_compression=True,
+         sketch_size=0.3),
+], ids=["noef", "ef", "conef", "conef-r8-cold"])
+def test_fused_pipeline_matches_the_long_form(single_rank_group, monkeypatch, kw):
+    """The ten-launch pipeline (flags published by the tile kernel, packing / projection / segment
+    copies riding along with the Gram-Schmidt kernels, reduce + un-projection in one kernel, slot
+    buffers cleared by the following step) against the long form with its helper launches, and
+    against the PyTorch-ops path; SHAPES mixes TMA-addressable matrices with ones that are not."""
+    monkeypatch.setenv("CONEF_TC", "1")
+
+    def run(fused):
+        monkeypatch.setenv("CONEF_FUSED", fused)
+        monkeypatch.setenv("CONEF_GRAPH", "0")
+        state = _powersgd_states(DEV, **kw)
+        outs = _steps(cb.powerSGD_hook, state, DEV, monkeypatch, "native", steps=6)
+        eng = state._engines[0]
+        return outs, eng, state
+
+    a, eng_a, sa = run("1")
+    b, eng_b, sb = run("0")
+    assert eng_a.fused and not eng_b.fused
+    # ten launches, plus one SIMT kernel per product for the matrices TMA cannot address
+    assert eng_a.exec_plan.launched <= 12 < eng_b.exec_plan.launched
+    for x, y in zip(a, b):
+        assert (x - y).norm() <= 2e-3 * y.norm()
+    if kw.get("warm_start", True):      # a cold start draws Q with Philox on the device, the PyTorch path on the CPU
+        torch_out = _steps(cb.powerSGD_hook, _powersgd_states(DEV, **kw), DEV, monkeypatch, "torch", steps=6)
+        for x, z in zip(a, torch_out):
+            assert (x - z).norm() <= 1e-2 * z.norm()
+    if kw.get("warm_start", True):
+        # single entries of small, nearly rank-deficient blocks move with the order of the split-K
+        # atomics: compare the warm-start memory in norm
+        qa, qb = sa.q_memory_dict[0], sb.q_memory_dict[0]
+        assert (qa - qb).norm() <= 2e-2 * qb.norm()
+    sa.check_status()
+
+
 @pytest.mark.parametrize("executor", ["native", "py"])
 def test_hpowersgd_topk_error_native_vs_cpu(single_rank_group, monkeypatch, executor):
     """hPowerSGD with its top-k error store: dense error records + one grouped radix select per

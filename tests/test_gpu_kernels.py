@@ -160,6 +160,122 @@ def test_orthogonalize_kernel():
         off += n * r
 
 
+def _orth_on_device(blocks, eps=0.0, which=0, one_launch=False):
+    """Runs the native orthogonalisation on a list of (n x r) CPU blocks; returns the results.
+    ``one_launch``: the single-kernel form with two barriers among its CTAs."""
+    mats = np.zeros(len(blocks), dtype=native.MAT_DTYPE)
+    off, tiles = 0, []
+    for k, b in enumerate(blocks):
+        n, r = b.shape
+        mats[k]["n"], mats[k]["m"], mats[k]["r"], mats[k]["p_off"] = n, 1, r, off
+        off += n * r
+        tiles += [(k, c) for c in range((n + 511) // 512)]
+    dev = torch.cat([b.reshape(-1) for b in blocks]).float().to(DEV)
+    md = native.upload_struct_array(mats, torch.device(DEV))
+    td = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    gram = torch.zeros(2 * len(tiles) * 1024, device=DEV)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    if one_launch:
+        bar = torch.zeros(2, dtype=torch.int32, device=DEV)
+        extra = native.OrthExtra()
+        extra.bar, extra.max_rank = bar.data_ptr(), max(b.shape[1] for b in blocks)
+        native.check(native.lib().conef_orthogonalize_fused(md.data_ptr(), td.data_ptr(), len(tiles), which,
+                                                            dev.data_ptr(), eps, 0, 0, 1, 0, status.data_ptr(), 0, 0, 16,
+                                                            gram.data_ptr(), 0, C.byref(extra), _st()))
+        torch.cuda.synchronize()
+        assert native.lib().conef_orth_last_launches() == 1, "the one-launch form was not taken"
+        assert int(status[0]) == 0 and int(bar[0]) == 0 and int(bar[1]) == 2      # two barriers passed
+    else:
+        native.check(native.lib().conef_orthogonalize_packed(md.data_ptr(), td.data_ptr(), len(tiles), len(blocks),
+                                                             which, dev.data_ptr(), eps, 0, 0, 1, 0, status.data_ptr(),
+                                                             0, 0, 16, gram.data_ptr(), _st()))
+    got, out, off = dev.cpu(), [], 0
+    for b in blocks:
+        out.append(got[off : off + b.numel()].view_as(b))
+        off += b.numel()
+    return out
+
+
+@pytest.mark.parametrize("shapes", [[(1000, 4), (37, 3), (5000, 8), (9, 1), (30528, 8)], [(700, 20), (2000, 16)],
+                                    [(1500, 32), (600, 27)]], ids=["r<=8", "r<=32a", "r<=32b"])
+def test_orthogonalize_one_launch_matches_three_kernels(shapes):
+    """The single-launch form (rows kept in shared memory, two barriers among the CTAs) against the
+    three-kernel form and the column-by-column oracle, including a zero column."""
+    torch.manual_seed(7)
+    blocks = [torch.randn(n, r) for n, r in shapes]
+    blocks[0][:, -1] = 0
+    one = _orth_on_device([b.clone() for b in blocks], one_launch=True)
+    three = _orth_on_device([b.clone() for b in blocks], one_launch=False)
+    for k, (b, x, y) in enumerate(zip(blocks, one, three)):
+        torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-5)
+        r = b.shape[1]
+        keep = list(range(r - 1)) if k == 0 else list(range(r))
+        if keep:
+            want = b[:, keep].clone()
+            ref.gram_schmidt_ref(want)
+            torch.testing.assert_close(x[:, keep], want, rtol=2e-3, atol=2e-4)
+            torch.testing.assert_close(x[:, keep].t() @ x[:, keep], torch.eye(len(keep)), rtol=0, atol=1e-4)
+    assert 0.8 < float(one[0][:, -1].norm()) < 1.2            # the zero column was refilled
+
+
+@pytest.mark.parametrize("relres", [1e-3, 1e-4, 1e-5, 1e-6])
+def test_orthogonalize_kernel_keeps_nearly_dependent_columns(relres):
+    """Columns within ``relres`` of the span of earlier ones stay alive, come out orthonormal and
+    agree with the CPU restatement of the same algorithm."""
+    g = torch.Generator().manual_seed(11)
+    blocks = []
+    for n in (2000, 30528):
+        a = torch.randn(n, 8, generator=g, dtype=torch.float64)
+        a[:, 3] = 0.7 * a[:, 0] - 1.3 * a[:, 1] + relres * torch.randn(n, generator=g, dtype=torch.float64)
+        a[:, 6] = a[:, 2] + a[:, 5] + relres * torch.randn(n, generator=g, dtype=torch.float64)
+        blocks.append(a.float())
+    for a, q in zip(blocks + blocks, _orth_on_device(blocks) + _orth_on_device(blocks, one_launch=True)):
+        q = q.double()
+        assert bool((q.norm(dim=0) > 0.99).all()), q.norm(dim=0)
+        torch.testing.assert_close(q.t() @ q, torch.eye(8, dtype=torch.float64), rtol=0, atol=1e-4)
+        want = a.double()
+        ref.gram_schmidt_ref(want)
+        resid = want - q @ (q.t() @ want)
+        assert float(resid.norm(dim=0).max()) < 2e-7 / relres + 1e-4
+
+
+def test_orthogonalize_kernel_refills_a_zero_column():
+    """An all-zero column has no direction to keep: it is replaced by fixed pseudo-random values of
+    about unit norm (identical in every call, hence on every rank), the others are untouched."""
+    torch.manual_seed(2)
+    a = torch.randn(3000, 4)
+    a[:, 2] = 0
+    q1, = _orth_on_device([a.clone()])
+    q2, = _orth_on_device([a.clone()])
+    assert torch.equal(q1, q2)
+    assert 0.9 < float(q1[:, 2].norm()) < 1.1
+    keep = [0, 1, 3]
+    want = a[:, keep].clone()
+    ref.gram_schmidt_ref(want)
+    torch.testing.assert_close(q1[:, keep], want, rtol=1e-3, atol=1e-4)
+    assert float((q1[:, keep].t() @ q1[:, 2]).abs().max()) < 0.1
+
+
+def test_hook_path_sees_a_wait_that_gave_up_without_a_host_sync():
+    """The status word is copied to pinned memory behind a step's kernels; a later hook call raises."""
+    import conef_b200 as cb
+
+    state = cb.PowerSGDState(None, start_powerSGD_iter=2)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream()
+    state.post_status(status, stream)
+    torch.cuda.synchronize()
+    state.poll_status()                               # clean word: nothing happens
+    flags = torch.zeros(8, dtype=torch.int32, device=DEV)
+    native.check(native.lib().conef_wait_flags(flags.data_ptr(), 2, 5, status.data_ptr(), 2000, _st()))
+    state.post_status(status, stream)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="wait gave up"):
+        state.poll_status()
+    assert int(status[0]) == 0                        # cleared for the next step
+    state.poll_status()
+
+
 def test_runtime_compiled_kernel_loader():
     """A CUDA source string compiled at run time for the device's architecture and launched on torch's stream."""
     from conef_b200.ops.jit import JitKernel

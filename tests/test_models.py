@@ -63,3 +63,116 @@ def test_bert_heads_and_checkpointing():
     assert net.cls.predictions.decoder.weight is net.bert.embeddings.word_embeddings.weight
     assert models.BertForQuestionAnswering(cfg)(ids)[0].shape == (2, 12)
     assert models.BertForSequenceClassification(cfg, 3)(ids).shape == (2, 3)
+
+
+def _tiny_bert_config():
+    from conef_b200 import models
+    return models.BertConfig(96, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, intermediate_size=64,
+                             max_position_embeddings=40)
+
+
+def test_bert_task_heads_shapes_and_losses():
+    """Next-sentence, multiple-choice and token-classification heads (reference modeling.py:968-1228)."""
+    import torch
+    from conef_b200 import models
+
+    cfg = _tiny_bert_config()
+    ids = torch.randint(0, 96, (3, 10))
+    seg = torch.randint(0, 2, (3, 10))
+    mask = torch.ones(3, 10, dtype=torch.long)
+    mask[1, 7:] = 0
+    nsp = models.BertForNextSentencePrediction(cfg).eval()
+    assert nsp(ids, seg, mask).shape == (3, 2)
+    assert nsp(ids, seg, mask, next_sentence_label=torch.tensor([0, 1, 1])).dim() == 0
+    mc = models.BertForMultipleChoice(cfg, num_choices=4).eval()
+    ids4 = torch.randint(0, 96, (3, 4, 10))
+    out = mc(ids4, torch.zeros_like(ids4), torch.ones_like(ids4))
+    assert out.shape == (3, 4)
+    mc(ids4, torch.zeros_like(ids4), torch.ones_like(ids4), labels=torch.tensor([0, 3, 2])).backward()
+    tok = models.BertForTokenClassification(cfg, num_labels=5).eval()
+    assert tok(ids, seg, mask).shape == (3, 10, 5)
+    labels = torch.randint(0, 5, (3, 10))
+    full = tok(ids, seg, mask, labels=labels)
+    labels2 = labels.clone()
+    labels2[1, 7:] = (labels2[1, 7:] + 1) % 5           # labels under the padding do not count
+    torch.testing.assert_close(full, tok(ids, seg, mask, labels=labels2))
+    mlm = models.BertForMaskedLM(cfg).eval()
+    lab = torch.full((3, 10), -1)
+    lab[0, 2] = 5
+    assert mlm(ids, seg, mask, masked_lm_labels=lab).dim() == 0
+
+
+def test_bert_from_pretrained_directory_archive_and_prefixes(tmp_path):
+    """save_pretrained -> from_pretrained from a directory and a .tar.gz, LayerNorm gamma/beta names,
+    a pre-training checkpoint loaded into a bare encoder and into a model with a new head."""
+    import tarfile
+    import torch
+    from conef_b200 import models
+
+    torch.manual_seed(0)
+    src = models.BertForPreTraining(_tiny_bert_config())
+    src.save_pretrained(str(tmp_path / "m"))
+    again = models.BertForPreTraining.from_pretrained(str(tmp_path / "m"))
+    for (k, a), (_, b) in zip(src.state_dict().items(), again.state_dict().items()):
+        assert torch.equal(a, b), k
+    with tarfile.open(tmp_path / "m.tar.gz", "w:gz") as tar:
+        for name in ("bert_config.json", "pytorch_model.bin"):
+            tar.add(tmp_path / "m" / name, arcname=name)
+    from_tar = models.BertModel.from_pretrained(str(tmp_path / "m.tar.gz"))       # "bert." prefix stripped
+    assert torch.equal(from_tar.embeddings.word_embeddings.weight, src.bert.embeddings.word_embeddings.weight)
+    old_style = {k.replace("LayerNorm.weight", "LayerNorm.gamma").replace("LayerNorm.bias", "LayerNorm.beta"): v
+                 for k, v in src.state_dict().items()}
+    head = models.BertForSequenceClassification.from_pretrained(str(tmp_path / "m"), state_dict=old_style, num_labels=3)
+    assert head.classifier.weight.shape == (3, 32)
+    assert torch.equal(head.bert.encoder.layer[1].output.LayerNorm.weight, src.bert.encoder.layer[1].output.LayerNorm.weight)
+    import pytest
+    with pytest.raises(EnvironmentError):
+        models.BertModel.from_pretrained(str(tmp_path / "missing"))
+
+
+def test_bert_tensorflow_named_weights_round_trip(tmp_path):
+    """The TensorFlow naming rules (kernel = transposed weight, gamma/beta, layer_N, *_embeddings) both ways."""
+    import numpy as np
+    import torch
+    from conef_b200 import models
+
+    torch.manual_seed(1)
+    src = models.BertForPreTraining(_tiny_bert_config())
+    variables = models.tf_variable_names(src)
+    assert "bert/encoder/layer_1/attention/self/query/kernel" in variables
+    assert "bert/embeddings/word_embeddings" in variables and "bert/embeddings/LayerNorm/gamma" in variables
+    variables["bert/encoder/layer_0/output/dense/kernel/adam_m"] = np.zeros((64, 32), np.float32)   # optimizer slot: skipped
+    variables["global_step"] = np.zeros((), np.int64)
+    dst = models.BertForPreTraining(_tiny_bert_config())
+    models.load_tf_weights_in_bert(dst, variables)
+    for (k, a), (_, b) in zip(src.state_dict().items(), dst.state_dict().items()):
+        assert torch.equal(a, b), k
+    (tmp_path / "tf").mkdir()
+    np.savez(tmp_path / "tf" / "model.ckpt.npz", **{k: v for k, v in variables.items() if "adam" not in k})
+    (tmp_path / "tf" / "bert_config.json").write_text(src.config.to_json_string())
+    via = models.BertForPreTraining.from_pretrained(str(tmp_path / "tf"), from_tf=True)
+    assert torch.equal(via.cls.predictions.transform.dense.weight, src.cls.predictions.transform.dense.weight)
+    bad = dict(variables)
+    bad["bert/pooler/dense/kernel"] = np.zeros((3, 3), np.float32)
+    import pytest
+    with pytest.raises(ValueError):
+        models.load_tf_weights_in_bert(models.BertForPreTraining(_tiny_bert_config()), bad)
+
+
+def test_file_cache_is_local_first(tmp_path):
+    from conef_b200.utils import file_cache as fc
+
+    f = tmp_path / "vocab.txt"
+    f.write_text("[PAD]\n[UNK]\n")
+    assert fc.cached_path(str(f)) == str(f)
+    url = "https://example.invalid/models/bert-tiny/vocab.txt"
+    cache = str(tmp_path / "cache")
+    with __import__("pytest").raises(EnvironmentError):
+        fc.cached_path(url, cache_dir=cache)                   # not cached, and no network
+    stored = fc.add_to_cache(url, str(f), etag='"abc"', cache_dir=cache)
+    assert fc.cached_path(url, cache_dir=cache) == stored
+    import os
+    assert fc.filename_to_url(os.path.basename(stored), cache) == (url, '"abc"')
+    assert fc.url_to_filename(url, '"abc"') == os.path.basename(stored)
+    with __import__("pytest").raises(EnvironmentError):
+        fc.cached_path(str(tmp_path / "nope.txt"))
