@@ -241,8 +241,9 @@ def main():
                             tuple(t.to(device) for t in tgt) if isinstance(tgt, tuple) else tgt.to(device)))
     flush = torch.empty(256 * 1024 * 1024 // 4, device=device) if use_cuda else None
 
-    # untimed: get past the warm-up all-reduce iterations of the hook, then W warm-up steps
-    pre = ns.start_compression_iter + 1 if ns.grad_reducer != "allreduce" else 0
+    # untimed: get past the warm-up all-reduce iterations of the hook and past the executor's
+    # bring-up (two direct runs per buffer slot, then one graph capture per slot), then W warm-up steps
+    pre = ns.start_compression_iter + 7 if ns.grad_reducer != "allreduce" else 0
     for i in range(pre + max(args.warmup, 0)):
         trainer.step(*dev_batches[i % nbuf])
     sync()

@@ -9,6 +9,7 @@
 // The scatter kernels read every peer's staging buffer directly (peer memory),
 // so the all-reduce of the staged values happens inside the kernel that writes
 // them back into the bucket.
+#include <string.h>
 #include "common.cuh"
 
 constexpr int QGROUP = 256;  // elements per quantisation group
@@ -80,12 +81,39 @@ extern "C" int conef_scatter_segments(const ConefSeg* segs, int nsegs, float* bu
 
 // ---------------------------------------------------------------------------
 // random block
+//
+// Two launches per bucket and step:
+//   gather : selected elements (+ remembered error) -> staging, error store updated in the same pass;
+//            spare CTAs copy the uncompressed tensors into their staging; the CTA that finishes last
+//            publishes the step's epoch in every peer's flag array.
+//   reduce+scatter : every CTA waits (bounded) for the peers' epoch, then sums the peers' staged
+//            values over NVLink and writes the averages back into the bucket.  Small payloads are
+//            summed in one shot (every rank reads every peer's whole staging).  Large ones in two
+//            shots: a rank sums only its 1/world slice, stores the result into every peer's
+//            `reduced` buffer, publishes a second epoch, and after the peers' second epoch scatters
+//            from its own `reduced` buffer: the bytes a rank pulls over NVLink drop from
+//            world x payload to payload (plus payload pushed).
 __device__ __forceinline__ bool in_block(const ConefBlk& B, long long idx, long long* stage_pos) {
   const long long end = B.start + B.block;
   if (idx >= B.start && idx < end) { *stage_pos = B.stage_off + (idx - B.start); return true; }
   const long long wrap = end - B.numel;  // > 0 when the block wraps to index 0
   if (idx < wrap) { *stage_pos = B.stage_off + (B.numel - B.start) + idx; return true; }
   return false;
+}
+
+// Uncompressed tensors riding along with the gather kernels: spare CTAs copy them into staging.
+struct SegGather {
+  const ConefSeg* segs;
+  int nsegs, tile_ctas;      // CTAs [tile_ctas, gridDim.x) do the segments
+  long long total;
+  float* staging;
+};
+__device__ __forceinline__ void seg_gather_ctas(const SegGather& S, const float* __restrict__ bucket) {
+  const long long stride = (long long)(gridDim.x - S.tile_ctas) * blockDim.x;
+  for (long long e = (long long)(blockIdx.x - S.tile_ctas) * blockDim.x + threadIdx.x; e < S.total; e += stride) {
+    const int s = find_seg(S.segs, S.nsegs, e, &ConefSeg::dst_off);
+    S.staging[e] = bucket[S.segs[s].src_off + (e - S.segs[s].dst_off)];
+  }
 }
 
 // Flat mapping: tile = (tensor, group of 256 consecutive elements), one warp
@@ -96,104 +124,186 @@ __global__ void __launch_bounds__(256)
 k_randblock_gather_flat(const ConefBlk* __restrict__ blks, const int2* __restrict__ tiles, int ntiles,
                         float* __restrict__ bucket, float* __restrict__ staging, float gather_scale,
                         float* __restrict__ dense_err, int8_t* __restrict__ qcodes,
-                        float* __restrict__ qscales, float alpha, float beta, int ef_mode) {
+                        float* __restrict__ qscales, float alpha, float beta, int ef_mode, const SegGather SG,
+                        const ConefPublish pub) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x * 8 + warp;
-  if (tile >= ntiles) return;
-  const int2 t = tiles[tile];
-  const ConefBlk B = blks[t.x];
-  const long long base = (long long)t.y * QGROUP;
-  float* g = bucket + B.g_off;
-  // gather_scale == 0 selects the unbiased estimator: divide by the selection probability
-  const float gs = gather_scale != 0.f ? gather_scale : (float)B.numel / (float)B.block;
-  float keep[QGROUP / 32];
-  float amax = 0.f;
-  float old_scale = 0.f;
-  // the tensor's codes start at sk_off in the code arena; its groups are aligned to the tensor start
-  const long long qbase = B.sk_off + base;             // code offset
-  const long long sidx = (long long)B.scale_off + t.y;  // scale slot of this group
-  if (ef_mode == CONEF_EF_QUANT8) old_scale = qscales[sidx];
-#pragma unroll
-  for (int k = 0; k < QGROUP / 32; ++k) {
-    const long long idx = base + lane + 32 * k;
-    keep[k] = 0.f;
-    if (idx < B.numel) {
-      float v = g[idx];
-      float carry = 0.f;
-      if (ef_mode == CONEF_EF_DENSE) v += dense_err[B.sk_off + idx];
-      else if (ef_mode == CONEF_EF_QUANT8) {
-        const float e = (float)qcodes[qbase + lane + 32 * k] * old_scale;
-        v += alpha * e;
-        carry = beta * e;
-      }
-      long long sp;
-      if (in_block(B, idx, &sp)) {
-        staging[sp] = v * gs;
-        keep[k] = carry;
-      } else {
-        g[idx] = 0.f;
-        keep[k] = carry + v;
-      }
-      if (ef_mode == CONEF_EF_DENSE) dense_err[B.sk_off + idx] = keep[k];
-      amax = fmaxf(amax, fabsf(keep[k]));
-    }
-  }
-  if (ef_mode == CONEF_EF_QUANT8) {
-    amax = warp_max(amax);
-    const float scale = amax / 127.f;
-    const float inv = scale > 0.f ? 1.f / scale : 0.f;
+  if ((int)blockIdx.x >= SG.tile_ctas) {
+    seg_gather_ctas(SG, bucket);
+  } else if (tile < ntiles) {
+    const int2 t = tiles[tile];
+    const ConefBlk B = blks[t.x];
+    const long long base = (long long)t.y * QGROUP;
+    float* g = bucket + B.g_off;
+    // gather_scale == 0 selects the unbiased estimator: divide by the selection probability
+    const float gs = gather_scale != 0.f ? gather_scale : (float)B.numel / (float)B.block;
+    float keep[QGROUP / 32];
+    float amax = 0.f;
+    float old_scale = 0.f;
+    // the tensor's codes start at sk_off in the code arena; its groups are aligned to the tensor start
+    const long long qbase = B.sk_off + base;             // code offset
+    const long long sidx = (long long)B.scale_off + t.y;  // scale slot of this group
+    if (ef_mode == CONEF_EF_QUANT8) old_scale = qscales[sidx];
 #pragma unroll
     for (int k = 0; k < QGROUP / 32; ++k) {
       const long long idx = base + lane + 32 * k;
+      keep[k] = 0.f;
       if (idx < B.numel) {
-        float q = rintf(keep[k] * inv);
-        q = fminf(fmaxf(q, -127.f), 127.f);
-        qcodes[qbase + lane + 32 * k] = (int8_t)q;
+        float v = g[idx];
+        float carry = 0.f;
+        if (ef_mode == CONEF_EF_DENSE) v += dense_err[B.sk_off + idx];
+        else if (ef_mode == CONEF_EF_QUANT8) {
+          const float e = (float)qcodes[qbase + lane + 32 * k] * old_scale;
+          v += alpha * e;
+          carry = beta * e;
+        }
+        long long sp;
+        if (in_block(B, idx, &sp)) {
+          staging[sp] = v * gs;
+          keep[k] = carry;
+        } else {
+          g[idx] = 0.f;
+          keep[k] = carry + v;
+        }
+        if (ef_mode == CONEF_EF_DENSE) dense_err[B.sk_off + idx] = keep[k];
+        amax = fmaxf(amax, fabsf(keep[k]));
       }
     }
-    if (lane == 0) qscales[sidx] = scale;
+    if (ef_mode == CONEF_EF_QUANT8) {
+      amax = warp_max(amax);
+      const float scale = amax / 127.f;
+      const float inv = scale > 0.f ? 1.f / scale : 0.f;
+#pragma unroll
+      for (int k = 0; k < QGROUP / 32; ++k) {
+        const long long idx = base + lane + 32 * k;
+        if (idx < B.numel) {
+          float q = rintf(keep[k] * inv);
+          q = fminf(fmaxf(q, -127.f), 127.f);
+          qcodes[qbase + lane + 32 * k] = (int8_t)q;
+        }
+      }
+      if (lane == 0) qscales[sidx] = scale;
+    }
   }
+  conef_publish_if_last(pub, gridDim.x);
 }
 
-// Row mapping for the count-sketch error store: tile = (tensor, row block).
+// Row mapping for the count-sketch error store: tile = (tensor, row block).  The sketch update is
+// linear in the remembered term (s_j^2 = 1):
+//   S'[i, w] = S[i, w] (1 - (1 - beta) k_w) + sum over the NOT selected columns j of cell w of (s_j g_ij + alpha S[i, w])
+// so a row none of whose elements are selected (nine rows in ten at a 10 % block) needs no gather of
+// the old sketch value: its remembered term is alpha k_w S[i, w], applied when the accumulator is
+// flushed, and the pass over its elements is one shared-memory atomic each.  A row that is selected
+// whole needs no atomics at all, only the old sketch values for what it sends; they are read from a
+// copy of the row in shared memory.  The (at most four) rows a block boundary cuts take both.
 __global__ void __launch_bounds__(256)
 k_randblock_gather_sketch(const ConefBlk* __restrict__ blks, const int2* __restrict__ tiles, int rows_per_cta,
                           float* __restrict__ bucket, float* __restrict__ staging, float gather_scale,
                           float* __restrict__ sketch, const int32_t* __restrict__ tables,
-                          const int32_t* __restrict__ counts, float alpha, float beta) {
-  extern __shared__ float acc[];  // rows_per_cta * W
-  const int2 t = tiles[blockIdx.x];
-  const ConefBlk B = blks[t.x];
-  const int m = B.m, W = B.W;
-  const int row0 = t.y * rows_per_cta;
-  const int rows = min(rows_per_cta, B.n - row0);
-  for (int i = threadIdx.x; i < rows * W; i += blockDim.x) acc[i] = 0.f;
-  __syncthreads();
-  const int32_t* tab = tables + B.tab_off;
-  const float gs = gather_scale != 0.f ? gather_scale : (float)B.numel / (float)B.block;
-  float* srow0 = sketch + B.sk_off + (size_t)row0 * W;
-  float* g = bucket + B.g_off;
-  for (int j = threadIdx.x; j < m; j += blockDim.x) {
-    const int e = tab[j];
-    const int h = unpack_bucket(e);
-    const float s = unpack_sign(e);
+                          const int32_t* __restrict__ counts, float alpha, float beta, const SegGather SG,
+                          const ConefPublish pub) {
+  extern __shared__ float sm[];  // acc: rows_per_cta * W, then one old sketch row: W
+  if ((int)blockIdx.x >= SG.tile_ctas) {
+    seg_gather_ctas(SG, bucket);
+  } else {
+    const int2 t = tiles[blockIdx.x];
+    const ConefBlk B = blks[t.x];
+    const int m = B.m, W = B.W;
+    const int row0 = t.y * rows_per_cta;
+    const int rows = min(rows_per_cta, B.n - row0);
+    float* acc = sm;
+    float* old = sm + (size_t)rows_per_cta * W;
+    for (int i = threadIdx.x; i < rows * W; i += blockDim.x) acc[i] = 0.f;
+    const int32_t* tab = tables + B.tab_off;
+    const int32_t* cnt = counts + B.cnt_off;
+    const float gs = gather_scale != 0.f ? gather_scale : (float)B.numel / (float)B.block;
+    const float omb = 1.f - beta;
+    float* g = bucket + B.g_off;
+    const long long end = B.start + B.block, wrap = end - B.numel;
     for (int ii = 0; ii < rows; ++ii) {
-      const long long idx = (long long)(row0 + ii) * m + j;
-      const float v = g[idx] + alpha * s * srow0[(size_t)ii * W + h];
-      long long sp;
-      if (in_block(B, idx, &sp)) {
-        staging[sp] = v * gs;
+      const long long r0 = (long long)(row0 + ii) * m, r1 = r0 + m;      // flat range of the row
+      // how much of the row the block [start, end) and its wrapped part [0, wrap) cover
+      const long long c1 = max(0LL, min(r1, end) - max(r0, B.start)) + max(0LL, min(r1, wrap) - r0);
+      float* srow = sketch + B.sk_off + (size_t)(row0 + ii) * W;
+      float* arow = acc + (size_t)ii * W;
+      __syncthreads();                         // acc zeroed / the previous row's copy no longer read
+      if (c1 == 0) {
+        // nothing selected: one atomic per element, the remembered term folds into the flush
+        for (int j = threadIdx.x; j < m; j += blockDim.x) {
+          const int e = __ldg(tab + j);
+          const float v = g[r0 + j];
+          g[r0 + j] = 0.f;
+          atomicAdd(&arow[unpack_bucket(e)], unpack_sign(e) * v);
+        }
+        __syncthreads();
+        for (int w = threadIdx.x; w < W; w += blockDim.x)
+          srow[w] = srow[w] * (1.f + (alpha - omb) * (float)__ldg(cnt + w)) + arow[w];
       } else {
-        g[idx] = 0.f;
-        atomicAdd(&acc[ii * W + h], s * v);
+        for (int w = threadIdx.x; w < W; w += blockDim.x) old[w] = srow[w];
+        __syncthreads();
+        for (int j = threadIdx.x; j < m; j += blockDim.x) {
+          const int e = __ldg(tab + j);
+          const int h = unpack_bucket(e);
+          const float s = unpack_sign(e);
+          const float v = g[r0 + j] + alpha * s * old[h];
+          long long sp;
+          if (in_block(B, r0 + j, &sp)) {
+            staging[sp] = v * gs;
+          } else {
+            g[r0 + j] = 0.f;
+            atomicAdd(&arow[h], s * v);
+          }
+        }
+        __syncthreads();
+        for (int w = threadIdx.x; w < W; w += blockDim.x)
+          srow[w] = old[w] * (1.f - omb * (float)__ldg(cnt + w)) + arow[w];
       }
     }
   }
-  __syncthreads();  // every read of the old sketch row is done
-  const float omb = 1.f - beta;
-  const int32_t* cnt = counts + B.cnt_off;
-  for (int i = threadIdx.x; i < rows * W; i += blockDim.x)
-    srow0[i] = srow0[i] * (1.f - omb * (float)cnt[i % W]) + acc[i];
+  conef_publish_if_last(pub, gridDim.x);
+}
+
+static int seg_cta_count(long long total) {
+  if (total <= 0) return 0;
+  long long n = (total + 1023) / 1024;
+  return (int)(n > 32 ? 32 : n);
+}
+
+// segs / total_unc / staging_unc: the uncompressed tensors (may be empty).  done != NULL with
+// world > 1: the CTA that finishes last stores epoch (+ *epoch_base) into peer_flags[p][rank].
+extern "C" int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles, int ntiles, int rows_per_cta,
+                                         float* bucket, float* staging, float gather_scale, float* sketch,
+                                         const int32_t* tables, const int32_t* counts, float* dense_err,
+                                         int8_t* qcodes, float* qscales, float alpha, float beta, int ef_mode,
+                                         size_t smem_bytes, const ConefSeg* segs, int nsegs, long long total_unc,
+                                         float* staging_unc, uint32_t* done, uint32_t* const* peer_flags, int world,
+                                         int rank, uint32_t epoch, const uint32_t* epoch_base, cudaStream_t stream) {
+  if (ntiles < 0) ntiles = 0;
+  ConefPublish pub;
+  memset(&pub, 0, sizeof(pub));
+  if (done != nullptr && peer_flags != nullptr && world > 1) {
+    pub.done = done; pub.peer_flags = peer_flags; pub.epoch_base = epoch_base;
+    pub.epoch = epoch; pub.world = world; pub.rank = rank;
+  }
+  SegGather SG;
+  SG.segs = segs; SG.nsegs = nsegs; SG.total = (segs != nullptr && nsegs > 0) ? total_unc : 0; SG.staging = staging_unc;
+  const int seg_ctas = seg_cta_count(SG.total);
+  if (ef_mode == CONEF_EF_SKETCH) {
+    smem_bytes += (smem_bytes / (rows_per_cta > 0 ? rows_per_cta : 1));      // one more row: the old sketch values
+    if (smem_bytes > 220 * 1024) { conef_set_error("randblock_gather: sketch rows do not fit in shared memory"); return 2; }
+    SG.tile_ctas = ntiles;
+    if (ntiles + seg_ctas == 0) return 0;
+    CONEF_CUDA(cudaFuncSetAttribute(k_randblock_gather_sketch, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    k_randblock_gather_sketch<<<ntiles + seg_ctas, 256, smem_bytes, stream>>>(
+        blks, tiles, rows_per_cta, bucket, staging, gather_scale, sketch, tables, counts, alpha, beta, SG, pub);
+  } else {
+    SG.tile_ctas = (ntiles + 7) / 8;
+    if (SG.tile_ctas + seg_ctas == 0) return 0;
+    k_randblock_gather_flat<<<SG.tile_ctas + seg_ctas, 256, 0, stream>>>(
+        blks, tiles, ntiles, bucket, staging, gather_scale, dense_err, qcodes, qscales, alpha, beta, ef_mode, SG, pub);
+  }
+  CONEF_CHECK_LAUNCH("k_randblock_gather");
+  return 0;
 }
 
 extern "C" int conef_randblock_gather(const ConefBlk* blks, const int2* tiles, int ntiles, int rows_per_cta,
@@ -202,17 +312,9 @@ extern "C" int conef_randblock_gather(const ConefBlk* blks, const int2* tiles, i
                                       int8_t* qcodes, float* qscales, float alpha, float beta,
                                       int ef_mode, size_t smem_bytes, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
-  if (ef_mode == CONEF_EF_SKETCH) {
-    if (smem_bytes > 220 * 1024) { conef_set_error("randblock_gather: sketch rows do not fit in shared memory"); return 2; }
-    CONEF_CUDA(cudaFuncSetAttribute(k_randblock_gather_sketch, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    k_randblock_gather_sketch<<<ntiles, 256, smem_bytes, stream>>>(blks, tiles, rows_per_cta, bucket, staging,
-                                                                 gather_scale, sketch, tables, counts, alpha, beta);
-  } else {
-    k_randblock_gather_flat<<<(ntiles + 7) / 8, 256, 0, stream>>>(blks, tiles, ntiles, bucket, staging, gather_scale,
-                                                               dense_err, qcodes, qscales, alpha, beta, ef_mode);
-  }
-  CONEF_CHECK_LAUNCH("k_randblock_gather");
-  return 0;
+  return conef_randblock_gather_ex(blks, tiles, ntiles, rows_per_cta, bucket, staging, gather_scale, sketch, tables,
+                                   counts, dense_err, qcodes, qscales, alpha, beta, ef_mode, smem_bytes, nullptr, 0,
+                                   0, nullptr, nullptr, nullptr, 1, 0, 0, nullptr, stream);
 }
 
 __global__ void k_randblock_scatter(const ConefBlk* __restrict__ blks, int nblks, float* __restrict__ bucket,
@@ -244,6 +346,131 @@ extern "C" int conef_randblock_scatter(const ConefBlk* blks, int nblks, float* b
   k_randblock_scatter<<<grid, 256, 0, stream>>>(blks, nblks, bucket, peer_staging, world, local_staging, scale,
                                               total_block);
   CONEF_CHECK_LAUNCH("k_randblock_scatter");
+  return 0;
+}
+
+// Wait + reduce + scatter of a bucket's random blocks AND uncompressed tensors in one launch.
+// Elements [0, total_unc) of the combined index space are the uncompressed tensors' staging,
+// [total_unc, total_unc + total_blk) the blocks'.
+struct RbReduce {
+  const ConefBlk* blks;  int nblks;
+  const ConefSeg* segs;  int nsegs;
+  long long total_unc, total_blk;
+  const float* const* peer_unc;      // [world] staged uncompressed tensors
+  const float* const* peer_blk;      // [world] staged blocks
+  float* const* peer_red;            // [world] `reduced` buffers (two shots only)
+  const float* my_red;
+  const uint32_t* my_flags;
+  uint32_t epoch;                    // epoch of the staged data; two shots publish / wait epoch + 1 as well
+  const uint32_t* epoch_base;
+  int world, rank, two_shot;
+  float scale;
+  int* status;
+  long long spin_limit;
+};
+
+__device__ __forceinline__ void rb_put(const RbReduce& R, float* __restrict__ bucket, long long e, float v) {
+  if (e < R.total_unc) {
+    const int s = find_seg(R.segs, R.nsegs, e, &ConefSeg::dst_off);
+    bucket[R.segs[s].src_off + (e - R.segs[s].dst_off)] = v;
+  } else {
+    const long long eb = e - R.total_unc;
+    const int b = find_seg(R.blks, R.nblks, eb, &ConefBlk::stage_off);
+    const ConefBlk& B = R.blks[b];
+    long long idx = B.start + (eb - B.stage_off);
+    if (idx >= B.numel) idx -= B.numel;
+    bucket[B.g_off + idx] = v;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+k_randblock_reduce_scatter(const RbReduce R, float* __restrict__ bucket, const ConefPublish pub) {
+  __shared__ int ok;
+  const uint32_t epoch = R.epoch + (R.epoch_base != nullptr ? *R.epoch_base : 0u);
+  if (R.world > 1) {
+    if (threadIdx.x == 0) {
+      ok = wait_flags_bounded(R.my_flags, R.world, epoch, R.spin_limit) ? 1 : 0;
+      if (!ok) atomicExch(R.status, CONEF_STATUS_FLAG_TIMEOUT);
+    }
+    __syncthreads();
+    if (!ok) return;
+  }
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long one_shot_total = R.total_unc + (R.two_shot ? 0 : R.total_blk);
+  for (long long e = first; e < one_shot_total; e += stride) {
+    const float* const* peers = e < R.total_unc ? R.peer_unc : R.peer_blk;
+    const long long off = e < R.total_unc ? e : e - R.total_unc;
+    float v = 0.f;
+    for (int p = 0; p < R.world; ++p) v += ld_relaxed_sys_f32(peers[p] + off);
+    rb_put(R, bucket, e, v * R.scale);
+  }
+  if (!R.two_shot) return;
+  // ---- first shot: this rank's slice, 16 bytes at a time, summed in rank order and pushed to every peer ----
+  const long long quads = (R.total_blk + 3) / 4;
+  const long long per = (quads + R.world - 1) / R.world;
+  const long long q0 = per * R.rank, q1 = min(quads, q0 + per);
+  for (long long q = q0 + first; q < q1; q += stride) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < R.world; ++p) {
+      float4 v;
+      asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                   : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(R.peer_blk[p] + 4 * q) : "memory");
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    acc.x *= R.scale; acc.y *= R.scale; acc.z *= R.scale; acc.w *= R.scale;
+    for (int p = 0; p < R.world; ++p)
+      asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+                   ::"l"(R.peer_red[p] + 4 * q), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
+  }
+  // ---- the CTA that finishes last publishes epoch + 1; everybody waits for the peers' ----
+  conef_publish_if_last(pub, gridDim.x);
+  if (threadIdx.x == 0) {
+    ok = wait_flags_bounded(R.my_flags, R.world, epoch + 1, R.spin_limit) ? 1 : 0;
+    if (!ok) atomicExch(R.status, CONEF_STATUS_FLAG_TIMEOUT);
+  }
+  __syncthreads();
+  if (!ok) return;
+  // ---- second shot: scatter from this GPU's own copy of the sums ----
+  for (long long e = first; e < R.total_blk; e += stride) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(R.my_red + e) : "memory");
+    rb_put(R, bucket, R.total_unc + e, v);
+  }
+}
+
+// One launch: wait for `epoch` in my_flags (world > 1), reduce over the peers' staging, scatter into
+// the bucket.  two_shot needs peer_red / my_red (payload rounded up to 4 floats), done and
+// peer_flags; it publishes and waits for epoch + 1.  The grid never exceeds what the device holds
+// at once, because in two shots its CTAs wait for one another through the peers.
+extern "C" int conef_randblock_reduce_scatter(const ConefBlk* blks, int nblks, const ConefSeg* segs, int nsegs,
+                                              long long total_unc, long long total_blk, float* bucket,
+                                              const float* const* peer_unc, const float* const* peer_blk,
+                                              float* const* peer_red, const float* my_red,
+                                              uint32_t* const* peer_flags, const uint32_t* my_flags, int world,
+                                              int rank, uint32_t epoch, const uint32_t* epoch_base, float scale,
+                                              int two_shot, uint32_t* done, int* status, long long spin_limit,
+                                              cudaStream_t stream) {
+  if (nblks <= 0) total_blk = 0;
+  if (nsegs <= 0) total_unc = 0;
+  if (total_unc + total_blk <= 0) return 0;
+  if (world <= 1 || peer_red == nullptr || my_red == nullptr || done == nullptr) two_shot = 0;
+  RbReduce R;
+  R.blks = blks; R.nblks = nblks; R.segs = segs; R.nsegs = nsegs; R.total_unc = total_unc; R.total_blk = total_blk;
+  R.peer_unc = peer_unc; R.peer_blk = peer_blk; R.peer_red = peer_red; R.my_red = my_red; R.my_flags = my_flags;
+  R.epoch = epoch; R.epoch_base = epoch_base; R.world = world; R.rank = rank; R.two_shot = two_shot; R.scale = scale;
+  R.status = status; R.spin_limit = spin_limit;
+  ConefPublish pub;
+  memset(&pub, 0, sizeof(pub));
+  if (two_shot) {
+    pub.done = done; pub.peer_flags = peer_flags; pub.epoch_base = epoch_base; pub.epoch = epoch + 1;
+    pub.world = world; pub.rank = rank;
+  }
+  long long want = (total_unc + total_blk + 255) / 256;
+  const long long cap = two_shot ? 4 * 148 : 2368;
+  const int grid = (int)(want > cap ? cap : want);
+  k_randblock_reduce_scatter<<<grid, 256, 0, stream>>>(R, bucket, pub);
+  CONEF_CHECK_LAUNCH("k_randblock_reduce_scatter");
   return 0;
 }
 

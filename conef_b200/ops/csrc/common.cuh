@@ -85,6 +85,11 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -107,6 +112,31 @@ __device__ __forceinline__ bool wait_flags_bounded(const uint32_t* flags, int wo
     }
   }
   return true;
+}
+
+// "The CTA that finishes last tells the peers": a kernel whose output a peer-memory reduction
+// consumes publishes the epoch itself instead of leaving that to a launch of its own.  `done`
+// counts finished CTAs and is zero between launches.  Call from every CTA, all threads, after the
+// CTA's last global write.  All-zero struct: nothing is published.
+struct ConefPublish {
+  uint32_t* done;
+  uint32_t* const* peer_flags;
+  const uint32_t* epoch_base;     // nullable device word added to `epoch` (replayed launches)
+  uint32_t epoch;
+  int world, rank;
+};
+__device__ __forceinline__ void conef_publish_if_last(const ConefPublish& s, unsigned ncta) {
+  if (s.done == nullptr) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();                                   // this CTA's results, then the counter
+    if (atomicAdd(s.done, 1u) == ncta - 1) {
+      atomicExch(s.done, 0u);
+      __threadfence_system();                          // everything counted above, then the flags
+      const uint32_t epoch = s.epoch + (s.epoch_base != nullptr ? *s.epoch_base : 0u);
+      for (int p = 0; p < s.world; ++p) st_release_sys(s.peer_flags[p] + s.rank, epoch);
+    }
+  }
 }
 
 // Philox-4x32-10 keyed by `seed` at counter `ctr`, turned into four standard normal values by

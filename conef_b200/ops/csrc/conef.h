@@ -149,19 +149,6 @@ int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, i
                           float* sketch, const int32_t* tables, const int32_t* counts,
                           float* dense_err, float alpha, float beta, int ef_mode, int max_rank,
                           size_t smem_bytes, cudaStream_t stream);
-// The same for the count-sketch store, without atomics: tiles are int2 {matrix, block of
-// 4 * conef_dc_groups(m) rows}.  ell: the hash tables regrouped by sketch cell (one blob per (m, W)
-// table: [G x (base, steps)] [32 G cell ids] [interleaved column lists, -1 padded], G = ceil(W / 32);
-// see ops/reference.py:ell_hash_table); ell_hdr[cnt_off] = offset of the table's blob in `ell`.
-// Shared memory: 16 * max_cols bytes with max_cols = max over the launch's matrices of
-// m * conef_dc_groups(m); at most 220 KB.  Launching matrices of similar m together keeps the
-// occupancy of the narrow ones.
-int conef_psgd_decompress_csr(const ConefMat* mats, const int2* tiles, int ntiles, int max_cols,
-                              float* bucket, const float* P, const float* Q, float q_scale,
-                              float* sketch, const int32_t* counts, const int32_t* ell,
-                              const int32_t* ell_hdr, float alpha, float beta, int max_rank,
-                              cudaStream_t stream);
-int conef_dc_groups(int m);
 // Sparse sign matrix H of the sketch applied to the small factors (see csrc/sketch.cu):
 // unproject = 0: Z_i += scale * H_i^T Q_i ; unproject = 1: Q_i += scale * H_i Y_i.
 // Record nmats + i describes the sketch of matrix i; its q_off is where Z_i / Y_i live.
@@ -238,6 +225,27 @@ int conef_randblock_gather(const ConefBlk* blks, const int2* tiles, int ntiles, 
                            float* dense_err, int8_t* qcodes, float* qscales,
                            float alpha, float beta, int ef_mode, size_t smem_bytes,
                            cudaStream_t stream);
+// The same gather with the uncompressed tensors copied into staging_unc by spare CTAs and, with
+// done != NULL and world > 1, the CTA that finishes last publishing `epoch` (+ *epoch_base) in slot
+// `rank` of every peer's flag array.
+int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles, int ntiles, int rows_per_cta,
+                              float* bucket, float* staging, float gather_scale, float* sketch,
+                              const int32_t* tables, const int32_t* counts, float* dense_err, int8_t* qcodes,
+                              float* qscales, float alpha, float beta, int ef_mode, size_t smem_bytes,
+                              const ConefSeg* segs, int nsegs, long long total_unc, float* staging_unc,
+                              uint32_t* done, uint32_t* const* peer_flags, int world, int rank, uint32_t epoch,
+                              const uint32_t* epoch_base, cudaStream_t stream);
+// One launch: bounded wait for `epoch` (world > 1), sum of the peers' staged values in rank order,
+// averages written into the bucket (uncompressed tensors and blocks).  two_shot: every rank sums its
+// 1/world slice of the blocks, stores it into every peer's `reduced` buffer (peer_red), publishes
+// epoch + 1, waits for the peers' and scatters from my_red.
+int conef_randblock_reduce_scatter(const ConefBlk* blks, int nblks, const ConefSeg* segs, int nsegs,
+                                   long long total_unc, long long total_blk, float* bucket,
+                                   const float* const* peer_unc, const float* const* peer_blk,
+                                   float* const* peer_red, const float* my_red, uint32_t* const* peer_flags,
+                                   const uint32_t* my_flags, int world, int rank, uint32_t epoch,
+                                   const uint32_t* epoch_base, float scale, int two_shot, uint32_t* done,
+                                   int* status, long long spin_limit, cudaStream_t stream);
 int conef_randblock_scatter(const ConefBlk* blks, int nblks, float* bucket,
                             const float* const* peer_staging, int world,
                             const float* local_staging, float scale, long long total_block,

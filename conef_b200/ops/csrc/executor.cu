@@ -141,6 +141,11 @@ static int run_fused(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint
     const uint32_t ep1 = ebase + (uint32_t)*ncoll;
     ConefOrthExtra X;
     memset(&X, 0, sizeof(X));
+    // A one-CTA waiter first: when a peer is late, one CTA spins instead of every CTA of the next
+    // kernel sitting on the SMs that this GPU's own backward pass could use; the waits inside the
+    // consumers then pass at once.
+    if (peers && plan->wait_kernel)
+      RUN(conef_wait_flags_ex(plan->my_flags, ws, ep1, plan->status, spin, eb, s));
     X.bar = plan->one_launch_orth ? plan->done_word + 1 : nullptr;
     X.max_rank = plan->max_rank;
     X.zero0 = plan->local_p[slot ^ 1]; X.zero0_n = tp + tu;
@@ -164,6 +169,8 @@ static int run_fused(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint
 
   if (phases & CONEF_PHASE_D) {
     const uint32_t ep2 = ebase + (uint32_t)*ncoll;      // the epoch the Q pass published
+    if (peers && plan->wait_kernel)
+      RUN(conef_wait_flags_ex(plan->my_flags, ws, ep2, plan->status, spin, eb, s));
     RUN(conef_reduce_q(plan->mats, nm, plan->max_cols, sketch ? plan->tables : nullptr, plan->qz,
                        plan->peer_q[slot], plan->my_flags, ws, ep2, plan->alpha, inv_ws, plan->status, spin, eb, s));
     RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_rows,
@@ -283,21 +290,10 @@ static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint3
       OK(copy_floats(plan->u_old, plan->pu + tp, tu, s));
       OK(copy_floats(plan->qz + tq, plan->qz2 + tq, tz, s));
     }
-    bool csr = false;
-    if (plan->ef_mode == CONEF_EF_SKETCH)
-      for (int c = 0; c < 4; ++c) {
-        const ConefTileList& tl = plan->dc_tiles[c];
-        if (tl.n <= 0) continue;
-        csr = true;
-        RUN(conef_psgd_decompress_csr(plan->mats, (const int2*)tl.tiles, tl.n, tl.pad, plan->work, pmem, qmem,
-                                      1.0f, plan->sketch, plan->counts, plan->ell, plan->ell_hdr,
-                                      plan->alpha, plan->beta, plan->max_rank, s));
-      }
-    if (!csr)
-      RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_rows,
-                                plan->work, pmem, qmem, 1.0f, plan->sketch, plan->tables, plan->counts,
-                                dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank,
-                                plan->d_smem, s));
+    RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_rows,
+                              plan->work, pmem, qmem, 1.0f, plan->sketch, plan->tables, plan->counts,
+                              dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank,
+                              plan->d_smem, s));
     if (plan->topk) {
       RUN(conef_topk_keep(plan->mats, nm, (const int2*)plan->topk_tiles.tiles, plan->topk_tiles.n,
                           plan->dense_err, plan->topk_ratio, plan->topk_scratch, s));
@@ -388,6 +384,33 @@ extern "C" int conef_psgd_step(ConefPsgdPlan* plan, cudaStream_t s) {
 extern "C" int conef_randblock_run(ConefRandblockPlan* plan, int phases, cudaStream_t s) {
   plan->launched = 0;
   const int ws = plan->world, slot = plan->slot & 1;
+  if (plan->has_slots && (ws == 1 || plan->has_symm)) {
+    // two launches: the gather publishes epoch + 1, the reduce + scatter waits for it (and, in two
+    // shots, publishes and waits for epoch + 2)
+    const bool peers = ws > 1;
+    const uint32_t ep = plan->epoch + 1;
+    if (phases & 1) {
+      RUNB(conef_randblock_gather_ex(
+          plan->blks, (const int2*)plan->tiles.tiles, plan->nblks ? plan->tiles.n : 0, plan->rows_per_cta, plan->work,
+          plan->local_blk[slot], plan->unbiased ? 0.0f : 1.0f,
+          plan->ef_mode == CONEF_EF_SKETCH ? plan->sketch : nullptr, plan->tables, plan->counts,
+          plan->ef_mode == CONEF_EF_DENSE ? plan->dense_err : nullptr, plan->qcodes, plan->qscales, plan->alpha,
+          plan->beta, plan->ef_mode, plan->smem, plan->segs, plan->nsegs, plan->total_unc, plan->local_unc[slot],
+          plan->done_word, peers ? plan->peer_flags : nullptr, ws, plan->rank, ep, nullptr, s));
+    }
+    if (phases & 2) {
+      const int two = plan->two_shot && peers;
+      if (peers)        // one CTA waits for late peers instead of the whole scatter grid
+        RUNB(conef_wait_flags(plan->my_flags, ws, ep, plan->status, plan->spin_limit, s));
+      RUNB(conef_randblock_reduce_scatter(
+          plan->blks, plan->nblks, plan->segs, plan->nsegs, plan->total_unc, plan->total_block, plan->work,
+          plan->peer_unc[slot], plan->peer_blk[slot], two ? plan->peer_red[slot] : nullptr,
+          two ? plan->local_red[slot] : nullptr, peers ? plan->peer_flags : nullptr, plan->my_flags, ws, plan->rank,
+          ep, nullptr, 1.0f / (float)ws, two, plan->done_word, plan->status, plan->spin_limit, s));
+      plan->epoch += two ? 2 : 1;
+    }
+    return 0;
+  }
   const bool symm = plan->has_symm && ws > 1;
   float* stage_unc = symm ? plan->local_unc[slot] : plan->staging_unc;
   float* stage_blk = symm ? plan->local_blk[slot] : plan->staging_blk;

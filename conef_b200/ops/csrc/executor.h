@@ -91,11 +91,6 @@ typedef struct ConefPsgdPlan {
   float topk_ratio;
   ConefTileList topk_tiles;
   uint32_t* topk_scratch;
-  // ---- count-sketch decompress without atomics (used when dc_tiles.n > 0) --------------------------
-  const int32_t* ell;            // hash tables regrouped by sketch cell
-  const int32_t* ell_hdr;        // per table (indexed like `counts`): offset of its blob in `ell`
-  ConefTileList dc_tiles[4];     // int2 {matrix, row block}; one launch per shared-memory class;
-                                 // `pad` of each list carries the class's max m * groups(m)
   // ---- fused pipeline (ten launches per bucket and step) -------------------------------------------
   int fused;                     // 1: run_fused (see executor.cu); needs tensor-core tiles in both products,
                                  //    no low-rank store, not the unbiased variant, and slot buffers
@@ -103,7 +98,8 @@ typedef struct ConefPsgdPlan {
                                  //    one-entry pointer tables when world == 1); they start zeroed
   uint32_t* done_word;           // device counter of the tile kernel's finished CTAs (zero between launches)
   float* zpk;  long long zpk_n;  // packed small operands of the sketch records inside qpk
-  int one_launch_orth, pad3;     // 1: orthogonalisations as one launch with two CTA barriers (done_word[1..2])
+  int one_launch_orth;           // 1: orthogonalisations as one launch with two CTA barriers (done_word[1..2])
+  int wait_kernel;               // 1 (world > 1): a one-CTA kernel waits for the peers' epoch ahead of each consumer
 } ConefPsgdPlan;
 
 // ---- random-block family ---------------------------------------------------------------------------
@@ -127,8 +123,15 @@ typedef struct ConefRandblockPlan {
   float* work;  int slot, pad0;
   unsigned int epoch;  float alpha, beta;
   int launched;
+  // ---- two-launch form: gather (+ segments, publishes the epoch) and wait + reduce + scatter ----
+  int has_slots;                 // local_* / peer_* set (symmetric memory, or local buffers when world == 1)
+  int two_shot;                  // 1: blocks reduced in two shots through the `reduced` buffers
+  float* const* peer_red[2];     // per slot: device arrays [world] of the peers' `reduced` buffers
+  const float* local_red[2];
+  uint32_t* done_word;           // device counter of finished CTAs (zero between launches)
 } ConefRandblockPlan;
 
+// With has_slots: two launches (see csrc/blocks.cu).  Otherwise:
 // Gather (block -> staging, error update), reduction over peer memory (bounded wait), scatter.
 // phases: 1 = gather, 2 = scatter; without peer memory and world > 1 the caller all-reduces the two
 // staging buffers between the phases.

@@ -272,7 +272,7 @@ __device__ __forceinline__ bool cta_group_barrier(uint32_t* bar, unsigned expect
   __syncthreads();
   if (threadIdx.x == 0) {
     bar_ok = 1;
-    const uint32_t gen = ld_acquire_sys(bar + 1);
+    const uint32_t gen = ld_acquire_gpu(bar + 1);
     __threadfence();                                   // this CTA's partials, then the arrival
     if (atomicAdd(bar, 1u) == expected - 1) {
       atomicExch(bar, 0u);
@@ -280,9 +280,9 @@ __device__ __forceinline__ bool cta_group_barrier(uint32_t* bar, unsigned expect
       atomicAdd(bar + 1, 1u);                          // releases the others
     } else {
       long long n = 0;
-      while (ld_acquire_sys(bar + 1) == gen) {
+      while (ld_acquire_gpu(bar + 1) == gen) {
         if (++n > limit) { bar_ok = 0; break; }
-        __nanosleep(32);
+        if (n > 64) __nanosleep(20);                   // the others are usually a microsecond away
       }
     }
     __threadfence();
@@ -439,10 +439,12 @@ k_orth_one(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
       const float* g = gram + ((size_t)round * ntiles + first) * GRAM_STRIDE + pr;
       float acc = 0.f;
       int c = 0;
-      for (; c + 4 <= count; c += 4) {
-        const float g0 = __ldcg(g + (size_t)c * GRAM_STRIDE), g1 = __ldcg(g + (size_t)(c + 1) * GRAM_STRIDE);
-        const float g2 = __ldcg(g + (size_t)(c + 2) * GRAM_STRIDE), g3 = __ldcg(g + (size_t)(c + 3) * GRAM_STRIDE);
-        acc += g0; acc += g1; acc += g2; acc += g3;
+      for (; c + 8 <= count; c += 8) {          // eight loads in flight; the order of the additions is fixed
+        float gv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) gv[u] = __ldcg(g + (size_t)(c + u) * GRAM_STRIDE);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc += gv[u];
       }
       for (; c < count; ++c) acc += __ldcg(g + (size_t)c * GRAM_STRIDE);
       G[pr / r][pr % r] = acc;

@@ -382,180 +382,6 @@ extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, in
 }
 
 // ---------------------------------------------------------------------------
-// Decompress + count-sketch update without atomics.  Tile = (matrix, block of 4 * G rows).
-//
-// The sketch update is linear in the residual, and the remembered error enters the residual only
-// through the cell it was read from (M[i,j] = G[i,j] + alpha * s_j * S[i,h_j], s_j^2 = 1), so
-//     S'[i,w] = S[i,w] * (1 + (alpha - (1 - beta)) * k_w) + sum_{j : h_j = w} s_j * (G[i,j] - M_hat[i,j])
-// with k_w the number of columns hashing to w.
-// Phase A streams the rows once.  A thread owns a column (the Q row comes in as 16-byte loads at a
-// 4r-byte lane stride: few load wavefronts per byte) and works on items of 4 rows; DC_UNROLL items
-// are loaded before the first is used and the next batch is requested before the current one is
-// processed, which keeps ~128 bytes per thread in flight.  M_hat goes to the bucket, G - M_hat to
-// shared memory as one float4 per (row group, column).
-// Phase B gives every sketch cell to one thread, which walks the cell's columns and sums their
-// signed residuals for up to 16 rows per step.  The column lists come from a regrouped copy of the
-// hash table (built once per (m, W)): cells ordered by decreasing k_w, 32 cells per group, lists
-// interleaved inside a group so that a warp reads consecutive words and runs the same number of
-// steps.  No atomics, no per-element gather of the old sketch, no divergence.
-constexpr int DC_ROWS = 4;              // rows per item: one float4 of residuals per column
-constexpr int DC_MAX_THREADS = 256;
-constexpr int DC_UNROLL = 4;
-
-// Row groups per CTA: narrow matrices take several groups of 4 rows, so that a CTA moves enough
-// bytes per pass and a sketch cell's column list is walked once for up to 16 rows.
-__host__ __device__ __forceinline__ int dc_groups(int m) { return m <= 1024 ? 4 : m <= 2048 ? 2 : 1; }
-
-template <int RP>
-__global__ void __launch_bounds__(DC_MAX_THREADS, 2)
-k_psgd_decompress_csr(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, float* __restrict__ bucket,
-                      const float* __restrict__ P, const float* __restrict__ Q, float q_scale,
-                      float* __restrict__ sketch, const int32_t* __restrict__ counts,
-                      const int32_t* __restrict__ ell, const int32_t* __restrict__ ell_hdr,
-                      float alpha, float beta) {
-  extern __shared__ float4 sm4[];
-  const int2 t = tiles[blockIdx.x];
-  const ConefMat M = mats[t.x];
-  const int m = M.m, r = M.r, W = M.W, Wp = M.Wp;
-  const int G = dc_groups(m);
-  const int row0 = t.y * DC_ROWS * G;
-  const int rows = min(DC_ROWS * G, M.n - row0);      // rows of this CTA
-  const int nthreads = blockDim.x;
-  float4* res = sm4;                                            // G planes of m entries
-  float* ps = reinterpret_cast<float*>(sm4 + (size_t)G * m);    // G * DC_ROWS * RP
-  const float* p = P + M.p_off + (size_t)row0 * r;
-  for (int i = threadIdx.x; i < G * DC_ROWS * RP; i += nthreads) {
-    const int ii = i / RP, c = i - ii * RP;
-    ps[i] = (c < r && ii < rows) ? p[(size_t)ii * r + c] : 0.f;
-  }
-  __syncthreads();
-
-  // ---- phase A ------------------------------------------------------------------------------
-  float* g0 = bucket + M.g_off + (size_t)row0 * m;
-  const bool qvec = (r & 3) == 0 && (reinterpret_cast<uintptr_t>(Q + M.q_off) & 15) == 0;
-  const int total = G * m;                    // items (row group, column), group-major
-  float v[DC_UNROLL][DC_ROWS], vn[DC_UNROLL][DC_ROWS];
-  auto load_batch = [&](int first, float (&dst)[DC_UNROLL][DC_ROWS]) {
-#pragma unroll
-    for (int u = 0; u < DC_UNROLL; ++u) {
-      const int it = first + u * nthreads;
-      const int g = it / m, j = it - g * m;
-#pragma unroll
-      for (int ii = 0; ii < DC_ROWS; ++ii)
-        dst[u][ii] = (it < total && g * DC_ROWS + ii < rows) ? __ldcs(g0 + (size_t)(g * DC_ROWS + ii) * m + j) : 0.f;
-    }
-  };
-  int it0 = threadIdx.x;
-  load_batch(it0, v);
-  for (; it0 < total; it0 += DC_UNROLL * nthreads) {
-    load_batch(it0 + DC_UNROLL * nthreads, vn);
-#pragma unroll
-    for (int u = 0; u < DC_UNROLL; ++u) {
-      const int it = it0 + u * nthreads;
-      if (it < total) {
-        const int g = it / m, j = it - g * m;
-        float qv[RP];
-        load_q_row<RP>(Q + M.q_off + (size_t)j * r, r, q_scale, qvec, qv);
-        const float* pg = ps + g * DC_ROWS * RP;
-        float* gg = g0 + (size_t)g * DC_ROWS * m + j;
-        const int grows = rows - g * DC_ROWS;
-        float d[DC_ROWS];
-#pragma unroll
-        for (int ii = 0; ii < DC_ROWS; ++ii) {
-          float mh = 0.f;
-#pragma unroll
-          for (int c = 0; c < RP; ++c) mh = fmaf(pg[ii * RP + c], qv[c], mh);
-          if (ii < grows) gg[(size_t)ii * m] = mh;
-          d[ii] = v[u][ii] - mh;              // rows past the end: 0 - 0
-        }
-        res[it] = make_float4(d[0], d[1], d[2], d[3]);       // it = g * m + j
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < DC_UNROLL; ++u)
-#pragma unroll
-      for (int ii = 0; ii < DC_ROWS; ++ii) v[u][ii] = vn[u][ii];
-  }
-  __syncthreads();
-
-  // ---- phase B ------------------------------------------------------------------------------
-  const int W32 = (W + 31) & ~31, ngroups = W32 >> 5;
-  const int32_t* blob = ell + __ldg(ell_hdr + M.cnt_off);
-  const int32_t* cell_ids = blob + 2 * ngroups;
-  const int32_t* entries = cell_ids + W32;
-  const int32_t* cnt = counts + M.cnt_off;
-  float* srow = sketch + M.sk_off + (size_t)row0 * Wp;
-  const float keep = alpha - (1.f - beta);
-  for (int i = threadIdx.x; i < W32; i += nthreads) {
-    const int grp = i >> 5, lane = i & 31;
-    const int w = __ldg(cell_ids + i);
-    const int base = __ldg(blob + 2 * grp), steps = __ldg(blob + 2 * grp + 1);
-    float4 acc[4];
-#pragma unroll
-    for (int g = 0; g < 4; ++g) acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-    const int32_t* mine = entries + base + lane;
-    for (int e = 0; e < steps; ++e) {
-      const int32_t ce = __ldg(mine + 32 * e);
-      if (ce != -1) {
-        const int col = ce & 0x7fffffff;
-        const float sg = unpack_sign(ce);
-#pragma unroll
-        for (int g = 0; g < 4; ++g)
-          if (g < G) {
-            const float4 d = res[(size_t)g * m + col];
-            acc[g].x = fmaf(sg, d.x, acc[g].x); acc[g].y = fmaf(sg, d.y, acc[g].y);
-            acc[g].z = fmaf(sg, d.z, acc[g].z); acc[g].w = fmaf(sg, d.w, acc[g].w);
-          }
-      }
-    }
-    if (w >= 0) {
-      const float scale = 1.f + keep * (float)__ldg(cnt + w);
-#pragma unroll
-      for (int g = 0; g < 4; ++g)
-        if (g < G) {
-          const float a4[DC_ROWS] = {acc[g].x, acc[g].y, acc[g].z, acc[g].w};
-#pragma unroll
-          for (int ii = 0; ii < DC_ROWS; ++ii)
-            if (g * DC_ROWS + ii < rows) {
-              float* c = srow + (size_t)(g * DC_ROWS + ii) * Wp + w;
-              *c = *c * scale + a4[ii];
-            }
-        }
-    }
-  }
-}
-
-template <int RP>
-static int launch_d_csr(const ConefMat* mats, const int2* tiles, int ntiles, int max_cols, float* bucket,
-                        const float* P, const float* Q, float q_scale, float* sketch, const int32_t* counts,
-                        const int32_t* ell, const int32_t* ell_hdr, float alpha, float beta,
-                        cudaStream_t stream) {
-  // max_cols here: the largest m * groups(m) over the tiles of this launch
-  const size_t smem = (size_t)max_cols * sizeof(float4) + (size_t)4 * DC_ROWS * RP * sizeof(float);
-  if (smem > 220 * 1024) { conef_set_error("decompress_csr: %zu bytes of shared memory needed", smem); return 2; }
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
-    CONEF_CUDA(cudaFuncSetAttribute(k_psgd_decompress_csr<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
-  }
-  const int threads = 256;
-  k_psgd_decompress_csr<RP><<<ntiles, threads, smem, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, counts,
-                                                              ell, ell_hdr, alpha, beta);
-  CONEF_CHECK_LAUNCH("k_psgd_decompress_csr");
-  return 0;
-}
-
-extern "C" int conef_psgd_decompress_csr(const ConefMat* mats, const int2* tiles, int ntiles, int max_cols,
-                                         float* bucket, const float* P, const float* Q, float q_scale,
-                                         float* sketch, const int32_t* counts, const int32_t* ell,
-                                         const int32_t* ell_hdr, float alpha, float beta, int max_rank,
-                                         cudaStream_t stream) {
-  if (ntiles <= 0) return 0;
-  DISPATCH_RANK(max_rank, launch_d_csr, mats, tiles, ntiles, max_cols, bucket, P, Q, q_scale, sketch, counts,
-                ell, ell_hdr, alpha, beta, stream);
-}
-
-// ---------------------------------------------------------------------------
 // Counter-based standard normal fill (Philox-4x32-10 + Box-Muller, common.cuh): the value
 // of element e depends only on (seed, e).
 __global__ void k_fill_normal(float* __restrict__ buf, long long numel, uint64_t seed) {
@@ -576,4 +402,3 @@ extern "C" int conef_fill_normal(float* buf, long long numel, uint64_t seed, cud
   return 0;
 }
 
-extern "C" int conef_dc_groups(int m) { return dc_groups(m); }

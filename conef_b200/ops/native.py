@@ -96,10 +96,9 @@ class PsgdPlan(C.Structure):
         ("key_alpha", C.c_float), ("key_beta", C.c_float), ("key_eps", C.c_float),
         ("graph_replays", C.c_int),
         ("topk", C.c_int), ("topk_ratio", C.c_float), ("topk_tiles", TileList), ("topk_scratch", C.c_void_p),
-        ("ell", C.c_void_p), ("ell_hdr", C.c_void_p), ("dc_tiles", TileList * 4),
         ("fused", C.c_int), ("has_slots", C.c_int), ("done_word", C.c_void_p),
         ("zpk", C.c_void_p), ("zpk_n", C.c_longlong),
-        ("one_launch_orth", C.c_int), ("pad3", C.c_int),
+        ("one_launch_orth", C.c_int), ("wait_kernel", C.c_int),
     ]
 
 class OrthExtra(C.Structure):
@@ -133,6 +132,8 @@ class RandblockPlan(C.Structure):
         ("work", C.c_void_p), ("slot", C.c_int), ("pad0", C.c_int),
         ("epoch", C.c_uint), ("alpha", C.c_float), ("beta", C.c_float),
         ("launched", C.c_int),
+        ("has_slots", C.c_int), ("two_shot", C.c_int),
+        ("peer_red", C.c_void_p * 2), ("local_red", C.c_void_p * 2), ("done_word", C.c_void_p),
     ]
 
 
@@ -151,9 +152,6 @@ _SIGNATURES = {
     "conef_pack_small": ([vp, C.c_int, C.c_int, vp, vp, C.c_int, vp], C.c_int),
     "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
                                C.c_float, C.c_int, C.c_int, C.c_size_t, vp], C.c_int),
-    "conef_psgd_decompress_csr": ([vp, vp, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
-                                   C.c_float, C.c_int, vp], C.c_int),
-    "conef_dc_groups": ([C.c_int], C.c_int),
     "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),
     "conef_lowrank_correct": ([vp, C.c_int, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_float, vp, vp, vp,
                                C.c_float, vp, vp], C.c_int),
@@ -202,7 +200,7 @@ _OPTIONAL = {}
 # How many kernels one call of an entry point enqueues (memsets not counted);
 # everything not listed launches exactly one.  Host-only entry points launch none.
 _KERNELS_PER_CALL = {
-    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_orthogonalize_fused": 3, "conef_lowrank_correct": 2, "conef_topk_keep": 7, "conef_topk_chunk": 0, "conef_orth_last_launches": 0, "conef_dc_groups": 0, "conef_psgd_run": 0, "conef_psgd_plan_size": 0, "conef_randblock_run": 0, "conef_randblock_plan_size": 0, "conef_psgd_step": 0, "conef_psgd_plan_release": 0, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
+    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_orthogonalize_fused": 3, "conef_lowrank_correct": 2, "conef_topk_keep": 7, "conef_topk_chunk": 0, "conef_orth_last_launches": 0, "conef_psgd_run": 0, "conef_psgd_plan_size": 0, "conef_randblock_run": 0, "conef_randblock_plan_size": 0, "conef_psgd_step": 0, "conef_psgd_plan_release": 0, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
     "conef_ipc_get_handle": 0, "conef_ipc_open_handle": 0, "conef_ipc_close_handle": 0,
     "conef_cpu_hash_table": 0, "conef_cpu_sketch_query": 0, "conef_cpu_sketch_update": 0,
     "conef_cpu_gram_schmidt": 0,

@@ -87,41 +87,6 @@ def packed_hash_table(D: int, W: int, a: int, b: int, sign_offset=SIGN_OFFSETS[0
     return packed.view(np.int32)
 
 
-def ell_hash_table(packed: np.ndarray, W: int) -> np.ndarray:
-    """The packed table regrouped by sketch cell, for one worker per cell and 32 workers per group.
-
-    Cells are ordered by decreasing number of columns and cut into groups of 32; inside a group the
-    column lists are interleaved (entry ``e`` of worker ``l`` at ``base + 32 * e + l``) and padded with
-    ``-1`` to the longest list of the group, so that the 32 workers read consecutive words and run
-    the same number of steps.  Layout of the returned int32 blob, with ``G = ceil(W / 32)``:
-    ``[G x (base, steps)] [32 G cell ids, -1 = no cell] [entries]``; an entry is the column index with
-    the sign bit of the packed table in bit 31.
-    """
-    packed = np.asarray(packed).view(np.uint32)
-    idx = (packed & np.uint32(0x7FFFFFFF)).astype(np.int64)
-    order = np.argsort(idx, kind="stable")
-    counts = np.bincount(idx, minlength=W)
-    starts = np.concatenate([[0], np.cumsum(counts)[:-1]])
-    sorted_cols = (order.astype(np.uint32) | (packed[order] & np.uint32(0x80000000))).view(np.int32)
-    by_count = np.argsort(-counts, kind="stable")
-    G = (W + 31) // 32
-    cell_ids = np.full(32 * G, -1, dtype=np.int32)
-    cell_ids[:W] = by_count
-    groups = np.zeros((G, 2), dtype=np.int32)
-    chunks, base = [], 0
-    for g in range(G):
-        ids = cell_ids[32 * g : 32 * g + 32]
-        steps = int(max((counts[w] for w in ids if w >= 0), default=0))
-        block = np.full((steps, 32), -1, dtype=np.int32)
-        for lane, w in enumerate(ids):
-            if w >= 0:
-                block[: counts[w], lane] = sorted_cols[starts[w] : starts[w] + counts[w]]
-        groups[g] = (base, steps)
-        chunks.append(block.reshape(-1))
-        base += steps * 32
-    return np.ascontiguousarray(np.concatenate([groups.reshape(-1), cell_ids] + chunks).astype(np.int32))
-
-
 def derive_hash_seeds(seed: int, rows: int):
     """Seed-derived ``(a_k, b_k)`` pairs for ``rows`` hash rows.
 

@@ -8,12 +8,13 @@ state's persistent tensors (error buffers, sketches, P/Q memory) so that the
 state keeps the reference's checkpoint layout while the kernels see flat
 arenas.
 
-Per step and bucket the PowerSGD engine enqueues, on a dedicated communication
-stream that waits for the gradients and that the returned future publishes:
+Per step and bucket the PowerSGD engine makes ONE call into the native executor
+(csrc/executor.cu), which enqueues, on a dedicated communication stream that waits for
+the gradients and that the returned future publishes:
 
-    gather(uncompressed) -> P = (G+e)Q -> [signal] -> allreduce(P)+Gram-Schmidt
-    -> scatter(uncompressed, reduced in-kernel) -> Q = M^T P -> allreduce(Q)/ws
-    -> M_hat = P Q^T + error update
+    Gram-Schmidt(Q) [+ gather(uncompressed), pack, project] -> P = (G+e)Q [publishes the epoch]
+    -> allreduce(P)+Gram-Schmidt [+ scatter(uncompressed, reduced in-kernel)] -> Q = M^T P [publishes]
+    -> allreduce(Q)/ws + un-projection -> M_hat = P Q^T + error update
 
 with no host synchronisation and no ``.wait()`` on the host (the reference
 blocks the host once per bucket, communication/powerSGD_hook.py:552-553).
@@ -196,8 +197,7 @@ class PowerSGDEngine(_EngineBase):
         mats = np.zeros(nrec, dtype=native.MAT_DTYPE)
         sk_off = tab_off = cnt_off = z_off = u_off = 0
         err_rank = int(getattr(state, "error_rank", None) or state.matrix_approximation_rank) if self.lowrank else 0
-        table_chunks, count_chunks, ell_chunks, ell_offsets = [], [], [], {}
-        ell_len = 0
+        table_chunks, count_chunks = [], []
         table_index: Dict[tuple, tuple] = {}
         self.widths = []
         seeds = ref.derive_hash_seeds(getattr(state, "hash_seed", 0), 1)[0]
@@ -217,10 +217,6 @@ class PowerSGDEngine(_EngineBase):
                     table_index[key] = (tab_off, cnt_off)
                     table_chunks.append(packed)
                     count_chunks.append(counts)
-                    blob = ref.ell_hash_table(packed.cpu().numpy(), W)     # for the decompress kernel
-                    ell_offsets[cnt_off] = ell_len
-                    ell_chunks.append(torch.from_numpy(blob))
-                    ell_len += len(blob)
                     tab_off += e.m
                     cnt_off += W
                 rec["tab_off"], rec["cnt_off"] = table_index[key]
@@ -290,13 +286,6 @@ class PowerSGDEngine(_EngineBase):
         self.mats_dev = native.upload_struct_array(mats, dev) if nrec else None
         self.tables = torch.cat(table_chunks) if table_chunks else None
         self.counts = torch.cat(count_chunks) if count_chunks else None
-        self.ell = self.ell_hdr = None
-        if ell_chunks:
-            self.ell = torch.cat(ell_chunks).to(dev)
-            hdr = np.zeros(max(cnt_off, 1), dtype=np.int32)
-            for at, off in ell_offsets.items():
-                hdr[at] = off
-            self.ell_hdr = torch.from_numpy(hdr).to(dev)
         # 512-row chunks for the row-parallel Gram-Schmidt and correction kernels
         OC = 512
         chunk = lambda ks, field: [(k, c) for k in ks for c in range(math.ceil(int(mats[k][field]) / OC))]
@@ -324,27 +313,6 @@ class PowerSGDEngine(_EngineBase):
         d_tiles = [(k, rb) for k, e in enumerate(plan.mats) for rb in range(math.ceil(e.n / self.d_rows))]
         self.d_tiles = self._tiles(d_tiles)
         self.n_d_tiles = len(d_tiles)
-        # count-sketch store: the kernel without atomics keeps 16 bytes per column in shared memory
-        # (row blocks of 4 * groups(m) rows; one launch per shared-memory class so that narrow
-        # matrices are not charged the shared memory of the widest one).  Off by default: on B200 it
-        # does not beat the kernel with shared-memory atomics yet (its two phases do not overlap at
-        # the occupancy its shared memory and registers allow); CONEF_DECOMPRESS_CSR=1 selects it.
-        self.dc_classes, self.n_dc_tiles = [], 0
-        if self.ef_mode == native.EF_SKETCH and self.max_cols * 16 + 2048 <= 200 * 1024 \
-                and os.environ.get("CONEF_DECOMPRESS_CSR", "0") == "1":
-            groups = {k: self.lib.conef_dc_groups(e.m) for k, e in enumerate(plan.mats)}
-            classes: Dict[int, list] = {}
-            for k, e in enumerate(plan.mats):
-                need = e.m * groups[k] * 16
-                cls = 0 if need <= 16 << 10 else 1 if need <= 32 << 10 else 2 if need <= 64 << 10 else 3
-                blocks = math.ceil(e.n / (4 * groups[k]))
-                classes.setdefault(cls, []).extend((k, rb) for rb in range(blocks))
-            for cls in sorted(classes):
-                lst = classes[cls]
-                width = max(plan.mats[k].m * groups[k] for k, _ in lst)
-                self.dc_classes.append((self._tiles(lst), len(lst), width))
-                self.n_dc_tiles += len(lst)
-
         segs = np.zeros(len(plan.segs), dtype=native.SEG_DTYPE)
         for k, s in enumerate(plan.segs):
             segs[k] = (s.g_off, s.dst_off, s.numel)
@@ -512,18 +480,8 @@ class PowerSGDEngine(_EngineBase):
         }
         self.cbuf = torch.zeros(max(nm, 1) * 2 * 1024, device=self.device, dtype=torch.float32)
 
-    def _correct(self, name, T, terms, st) -> None:
-        """``terms``: one or two ``(X, L, Rm, coef)``; reductions run over rows of L, updates over rows of T."""
-        over_n = name in ("q", "v")       # these reduce over the n rows and update m rows
-        red = self.chunks_n if over_n else self.chunks_m
-        app = self.chunks_m if over_n else self.chunks_n
-        (x0, l0, r0, c0) = terms[0]
-        (x1, l1, r1, c1) = terms[1] if len(terms) > 1 else (x0, l0, r0, 0.0)
-        native.check(self.lib.conef_lowrank_correct(
-            self.corr[name].data_ptr(), self.nm, red[0].data_ptr(), red[1], app[0].data_ptr(), app[1], T.data_ptr(),
-            x0.data_ptr(), l0.data_ptr(), r0.data_ptr(), float(c0), x1.data_ptr(), l1.data_ptr(), r1.data_ptr(),
-            float(c1), self.cbuf.data_ptr(), st), f"lowrank_correct({name})")
-
+    # The three helpers below launch single stages on their own; the kernel micro-benchmark
+    # (utils/kernel_bench.py) times them.  A training step goes through the native executor.
     def _orth(self, which: int, subset: str, buf: torch.Tensor, eps: float, st, peers=0, flags=0, world=1, epoch=0,
               packed: bool = False) -> None:
         tiles, n = self.orth_tiles[(which, subset)]
@@ -628,8 +586,6 @@ class PowerSGDEngine(_EngineBase):
         """Fill the plan of the native executor (csrc/executor.h): every pointer and size the
         pipeline needs, so that one host call per step enqueues all of it."""
         self._release_exec()
-        if self.external or os.environ.get("CONEF_EXECUTOR", "native") != "native":
-            return
         P, plan = native.PsgdPlan(), self.plan
         ptr = native.ptr
 
@@ -660,9 +616,6 @@ class PowerSGDEngine(_EngineBase):
         P.tc_p, P.simt_p = tl(self.tc_p_tiles, self.n_tc_p), tl(self.p_tiles, self.n_p_tiles)
         P.qset_all, P.qset_grad, P.qset_err = qset("all"), qset("grad"), qset("err")
         P.d_tiles, P.d_rows, P.d_smem = tl(self.d_tiles, self.n_d_tiles), self.d_rows, self.d_smem
-        for i, (tiles, n, width) in enumerate(self.dc_classes):
-            P.dc_tiles[i] = native.TileList(ptr(tiles), n, width)
-        P.ell, P.ell_hdr = ptr(self.ell), ptr(self.ell_hdr)
         P.orth_q, P.orth_p = tl(*self.orth_tiles[(1, "grad")]), tl(*self.orth_tiles[(0, "grad")])
         P.orth_u = tl(*self.orth_tiles[(0, "err")])
         P.chunks_n, P.chunks_m = tl(*self.chunks_n), tl(*self.chunks_m)
@@ -697,6 +650,7 @@ class PowerSGDEngine(_EngineBase):
                           and os.environ.get("CONEF_FUSED", "1") == "1")
         P.fused = int(self.fused)
         P.one_launch_orth = int(os.environ.get("CONEF_ORTH_ONE", "1") == "1")
+        P.wait_kernel = int(os.environ.get("CONEF_WAIT_KERNEL", "1") == "1")
         if self.ef_mode == native.EF_SKETCH and self.qpk is not None:
             P.zpk, P.zpk_n = ptr(self.qpk) + 4 * self.zpk_off, self.qpk_total - self.zpk_off
         self.exec_plan = P
@@ -794,11 +748,6 @@ class PowerSGDEngine(_EngineBase):
         if self.external or self.lowrank:
             from .hooks import _ef_coeffs
             alpha, beta = _ef_coeffs(state)
-        dense_err = self._dense_err(state, bidx)
-        seg_err = None if self.topk else dense_err        # the uncompressed tensors carry no top-k error
-        sketch = self.sketch_arena
-        aux = self.aux_ptr if self.fused_err else 0
-
         # external error compressors: query before, clone, update after
         copy = None
         if self.external:
@@ -809,120 +758,8 @@ class PowerSGDEngine(_EngineBase):
 
         pmem, qmem, fresh = self._pq_memory(state, bidx)
         eps = float(getattr(state, "orthogonalization_epsilon", 0) or 0)
-        if self.exec_plan is not None:
-            self._run_native(state, work, alpha, beta, fresh, eps, st)
-            if self.variant == "batched":
-                buf.copy_(work[: self.buf_numel])
-            if not getattr(state, "warm_start", False) or self.variant == "unbiased":
-                state.p_memory_dict.pop(bidx, None)
-                state.q_memory_dict.pop(bidx, None)
-            self.step += 1
-            return
-        symm = self.symm
-        slot = self.step & 1
-        if nm:
-            if fresh:
-                seed = int(state.rng.randint(1_000_000_000))
-                native.check(lib.conef_fill_normal(qmem.data_ptr(), qmem.numel(), seed, st), "fill_normal")
-            if self.variant != "unbiased":
-                self._orth(1, "grad", self.qz, eps, st)
-            if self.ef_mode == native.EF_SKETCH:
-                # Z = alpha * H^T Q, so that the sketch records contribute alpha * unsketch(S) Q to P
-                self.qz[plan.total_q :].zero_()
-                native.check(lib.conef_sketch_project(self.mats_dev.data_ptr(), nm, self.max_cols,
-                                                      self.tables.data_ptr(), self.qz.data_ptr(), alpha, 0, st),
-                             "sketch_project")
-
-        # 1. uncompressed tensors -> staging ; P = G Q + e Q
-        stage = symm.local(slot, 0) if symm else self.staging
-        p_target = symm.local(slot, 1) if symm else pmem
-        if plan.total_unc:
-            native.check(lib.conef_gather_segments(self.segs_dev.data_ptr(), len(plan.segs), wp,
-                                                   native.ptr(seg_err), stage.data_ptr(), plan.total_unc, st),
-                         "gather_segments")
-        if nm:
-            if self.p_zero:
-                p_target[: plan.total_p + self.total_u].zero_()
-            self._launch_p(wp, aux, self.qz, p_target, st)
-            if self.lowrank:
-                self._correct("p", p_target, [(self.u_old, self.qz, self.qz, alpha)], st)     # P += a U (V^T Q)
-
-        # 2. all-reduce of staging and P ; Gram-Schmidt of P
-        orth_p = self.variant != "unbiased"
-        if symm:
-            self.epoch += 1
-            native.check(lib.conef_signal_peers(symm.peer_flags_dev(), ws, self.rank, self.epoch, st), "signal")
-            if nm and orth_p:
-                self._orth(0, "grad", self.pu, eps, st, symm.peer_ptrs_dev(slot, 1), symm.flags_ptr(), ws, self.epoch,
-                           packed=True)
-            elif nm:
-                native.check(lib.conef_allreduce_oneshot(
-                    pmem.data_ptr(), symm.peer_ptrs_dev(slot, 1), 0, symm.flags_ptr(), ws, self.rank, self.epoch,
-                    plan.total_p, 1.0 / ws, self.status.data_ptr(), DEFAULT_SPIN_LIMIT, st), "allreduce_p")
-            else:
-                native.check(lib.conef_wait_flags(symm.flags_ptr(), ws, self.epoch, self.status.data_ptr(),
-                                                  DEFAULT_SPIN_LIMIT, st), "wait_flags")
-            if plan.total_unc:
-                native.check(lib.conef_scatter_segments(
-                    self.segs_dev.data_ptr(), len(plan.segs), wp, symm.peer_ptrs_dev(slot, 0), ws, 0, 1.0 / ws,
-                    native.ptr(seg_err), plan.total_unc, st), "scatter_segments")
-        else:
-            if ws > 1:
-                if plan.total_unc:
-                    self._nccl_sum(stage[: plan.total_unc], self.group)
-                if nm:
-                    self._nccl_sum(pmem, self.group, average=not orth_p)
-            if plan.total_unc:
-                native.check(lib.conef_scatter_segments(
-                    self.segs_dev.data_ptr(), len(plan.segs), wp, 0, 1, stage.data_ptr(), 1.0 / ws,
-                    native.ptr(seg_err), plan.total_unc, st), "scatter_segments")
-            if nm and orth_p:
-                self._orth(0, "grad", self.pu, eps, st, packed=True)
-
-        if nm:
-            if self.lowrank and symm:
-                # G V arrived behind the P blocks of the symmetric slot; it is local data
-                self.pu[plan.total_p :].copy_(p_target[plan.total_p : plan.total_p + self.total_u])
-            # 3. Q = G^T P + e^T P (skipped by the unbiased compressor: Q stays the random projection)
-            if self.variant != "unbiased":
-                q_target = symm.local(slot, 2) if symm else self.qz
-                if self.lowrank:
-                    if self.q_zero:
-                        q_target[: plan.total_q].zero_()         # the V blocks behind Q stay as they are
-                    self._launch_q(wp, aux, self.pu, q_target, st, packed=True, subset="grad")
-                    self._correct("q", q_target, [(self.qz, self.u_old, self.pu, alpha)], st)   # Q' += a V (U^T P)
-                else:
-                    if self.q_zero:
-                        q_target.zero_()
-                    self._launch_q(wp, aux, pmem, q_target, st, packed=True)
-                if self.ef_mode == native.EF_SKETCH:
-                    # Q += alpha * H Y with Y = S^T P computed by the sketch records
-                    native.check(lib.conef_sketch_project(self.mats_dev.data_ptr(), nm, self.max_cols,
-                                                          self.tables.data_ptr(), q_target.data_ptr(), alpha, 1, st),
-                                 "sketch_unproject")
-                if symm:
-                    self.epoch += 1
-                    native.check(lib.conef_allreduce_oneshot(
-                        qmem.data_ptr(), symm.peer_ptrs_dev(slot, 2), symm.peer_flags_dev(), symm.flags_ptr(), ws,
-                        self.rank, self.epoch, plan.total_q, 1.0 / ws, self.status.data_ptr(),
-                        DEFAULT_SPIN_LIMIT, st), "allreduce_q")
-                elif ws > 1:
-                    self._nccl_sum(qmem, self.group, average=True)
-            if self.lowrank:
-                self._refresh_lowrank(wp, alpha, beta, st)
-            # 4. M_hat = P Q^T ; residual of (G + e) -> error store
-            if self.n_dc_tiles:
-                self.launch_decompress_csr(wp, pmem, qmem, alpha, beta, st)
-            else:
-                native.check(lib.conef_psgd_decompress(
-                    self.mats_dev.data_ptr(), self.d_tiles.data_ptr(), self.n_d_tiles, self.d_rows, wp,
-                    pmem.data_ptr(), qmem.data_ptr(), 1.0, native.ptr(sketch), native.ptr(self.tables),
-                    native.ptr(self.counts), native.ptr(dense_err), alpha, beta, self.ef_mode, self.max_rank,
-                    self.d_smem, st), "decompress")
-            if self.topk:
-                native.check(lib.conef_topk_keep(self.mats_dev.data_ptr(), nm, self.topk_tiles.data_ptr(),
-                                                 self.n_topk_tiles, dense_err.data_ptr(), self.topk_ratio,
-                                                 self.topk_scratch.data_ptr(), st), "topk_keep")
+        # the whole pipeline: one call into the native executor (csrc/executor.cu)
+        self._run_native(state, work, alpha, beta, fresh, eps, st)
 
         if self.external:
             copy.sub_(work)
@@ -935,14 +772,6 @@ class PowerSGDEngine(_EngineBase):
             state.p_memory_dict.pop(bidx, None)
             state.q_memory_dict.pop(bidx, None)
         self.step += 1
-
-    def launch_decompress_csr(self, wp, pmem, qmem, alpha, beta, st) -> None:
-        """M_hat into the bucket and the residual into the count sketch, one launch per class."""
-        for tiles, n, width in self.dc_classes:
-            native.check(self.lib.conef_psgd_decompress_csr(
-                self.mats_dev.data_ptr(), tiles.data_ptr(), n, width, wp, pmem.data_ptr(), qmem.data_ptr(), 1.0,
-                self.sketch_arena.data_ptr(), self.counts.data_ptr(), self.ell.data_ptr(),
-                self.ell_hdr.data_ptr(), alpha, beta, self.max_rank, st), "decompress_csr")
 
     def _launch_p(self, wp, aux, small: torch.Tensor, p_target: torch.Tensor, st) -> None:
         """P (+)= A Q over every record: tcgen05 tiles where TMA can address the matrix, SIMT elsewhere.
@@ -975,20 +804,6 @@ class PowerSGDEngine(_EngineBase):
         if n_q:
             native.check(lib.conef_psgd_q(self.mats_dev.data_ptr(), q_tiles.data_ptr(), n_q, wp, aux,
                                           pmem.data_ptr(), q_target.data_ptr(), self.max_rank, st), "psgd_q")
-
-    def _refresh_lowrank(self, wp, alpha, beta, st) -> None:
-        """One power-iteration step of the error factors on T = G + (a+b) U V^T - P Q^T:
-        U' = orth(T V) with G V already behind the P blocks, then V' = T^T U'."""
-        plan = self.plan
-        # G V += (a+b) U (V^T V) - P (Q^T V)
-        self._correct("u", self.pu, [(self.u_old, self.qz, self.qz, alpha + beta), (self.pu, self.qz, self.qz, -1.0)], st)
-        self._orth(0, "err", self.pu, 1e-12, st, packed=True)
-        self.qz2.zero_()
-        self._launch_q(wp, 0, self.pu, self.qz2, st, packed=True, subset="err")          # G^T U'
-        # G^T U' += (a+b) V (U^T U') - Q (P^T U')
-        self._correct("v", self.qz2, [(self.qz, self.u_old, self.pu, alpha + beta), (self.qz, self.pu, self.pu, -1.0)], st)
-        self.u_old.copy_(self.pu[plan.total_p : plan.total_p + self.total_u])
-        self.qz[plan.total_q :].copy_(self.qz2[plan.total_q :])
 
 
 class _PtrOnly:
@@ -1112,8 +927,14 @@ class RandBlockEngine(_EngineBase):
         self.staging_unc = torch.empty(max(plan.total_unc, 1), device=dev, dtype=torch.float32)
         self.staging_blk = torch.empty(max(plan.total_block, 1), device=dev, dtype=torch.float32)
         self.err_arena = self.codes = self.scales = None
-        self.symm = _try_symm([max(plan.total_unc, 4), max(plan.total_block, 4)], group, dev) \
-            if self.world > 1 else None
+        # regions: staged uncompressed tensors, staged blocks, and the reduced blocks of the two-shot form
+        # (payloads above CONEF_TWO_SHOT_BYTES: each rank sums a 1/world slice and pushes it to the peers)
+        pad4 = lambda x: (max(x, 4) + 3) // 4 * 4
+        self.two_shot = self.world > 1 and 4 * plan.total_block >= int(os.environ.get("CONEF_TWO_SHOT_BYTES", 1 << 20))
+        regions = [pad4(plan.total_unc), pad4(plan.total_block), pad4(plan.total_block) if self.two_shot else 4]
+        self.symm = _try_symm(regions, group, dev) if self.world > 1 else None
+        self.slots = self.symm if self.symm is not None else (LocalSlots(regions, dev) if self.world == 1 else None)
+        self.done_word = torch.zeros(4, dtype=torch.int32, device=dev)
         self.exec_plan, self._exec_key = None, None
 
     def bind_state(self, state, bidx):
@@ -1180,9 +1001,15 @@ class RandBlockEngine(_EngineBase):
         symm = self.symm
         if symm is not None:
             P.peer_flags, P.my_flags = symm.peer_flags_dev(), symm.flags_ptr()
+        slots = self.slots if os.environ.get("CONEF_FUSED", "1") == "1" else symm
+        if slots is not None:
             for slot in (0, 1):
-                P.peer_unc[slot], P.peer_blk[slot] = symm.peer_ptrs_dev(slot, 0), symm.peer_ptrs_dev(slot, 1)
-                P.local_unc[slot], P.local_blk[slot] = ptr(symm.local(slot, 0)), ptr(symm.local(slot, 1))
+                P.peer_unc[slot], P.peer_blk[slot] = slots.peer_ptrs_dev(slot, 0), slots.peer_ptrs_dev(slot, 1)
+                P.local_unc[slot], P.local_blk[slot] = ptr(slots.local(slot, 0)), ptr(slots.local(slot, 1))
+                P.peer_red[slot], P.local_red[slot] = slots.peer_ptrs_dev(slot, 2), ptr(slots.local(slot, 2))
+        P.has_slots = int(slots is not None and os.environ.get("CONEF_FUSED", "1") == "1")
+        P.two_shot = int(self.two_shot)
+        P.done_word = ptr(self.done_word)
         P.spin_limit = DEFAULT_SPIN_LIMIT
         self.exec_plan = P
         self._exec_key = (ptr(self.err_arena), ptr(self.codes))
@@ -1232,49 +1059,13 @@ class RandBlockEngine(_EngineBase):
                 self._pin_evt[k] = torch.cuda.Event()
             self._pin_evt[k].record()
         symm, slot = self.symm, self.step & 1
-        stage_unc = symm.local(slot, 0) if symm else self.staging_unc
-        stage_blk = symm.local(slot, 1) if symm else self.staging_blk
+        fused = self.slots is not None and os.environ.get("CONEF_FUSED", "1") == "1"
+        holder = self.slots if fused else symm
+        stage_unc = holder.local(slot, 0) if holder else self.staging_unc
+        stage_blk = holder.local(slot, 1) if holder else self.staging_blk
         state.compressed_tensor_memory[bidx] = stage_blk[: plan.total_block]
         state.account_wire(plan.total_unc + plan.total_block, buf.numel(), bucket)
-        if os.environ.get("CONEF_EXECUTOR", "native") == "native":
-            self._run_native(state, buf, stage_unc, stage_blk, st)
-            self.step += 1
-            return
-        bp = buf.data_ptr()
-        beta = getattr(state, "beta", 0.0)
-        if plan.total_unc:
-            native.check(lib.conef_gather_segments(self.segs_dev.data_ptr(), len(plan.segs), bp, 0,
-                                                   stage_unc.data_ptr(), plan.total_unc, st), "gather_segments")
-        if nb:
-            # gather scale 0 = unbiased estimator: the kernel divides the selected values by
-            # the per-tensor selection probability block/numel
-            native.check(lib.conef_randblock_gather(
-                self.blks_dev.data_ptr(), self.tiles.data_ptr(), self.n_tiles, self.rows, bp, stage_blk.data_ptr(),
-                0.0 if self.unbiased else 1.0, native.ptr(self.err_arena) if self.ef_mode == native.EF_SKETCH else 0,
-                native.ptr(self.tables), native.ptr(self.counts),
-                native.ptr(self.err_arena) if self.ef_mode == native.EF_DENSE else 0,
-                native.ptr(self.codes), native.ptr(self.scales), 1.0 - beta, beta, self.ef_mode, self.smem, st),
-                "randblock_gather")
-        if symm:
-            self.epoch += 1
-            native.check(lib.conef_signal_peers(symm.peer_flags_dev(), ws, self.rank, self.epoch, st), "signal")
-            native.check(lib.conef_wait_flags(symm.flags_ptr(), ws, self.epoch, self.status.data_ptr(),
-                                              DEFAULT_SPIN_LIMIT, st), "wait_flags")
-            peers_unc, peers_blk, loc_unc, loc_blk = symm.peer_ptrs_dev(slot, 0), symm.peer_ptrs_dev(slot, 1), 0, 0
-        else:
-            if ws > 1:
-                if plan.total_unc:
-                    self._nccl_sum(stage_unc[: plan.total_unc], self.group)
-                if nb:
-                    self._nccl_sum(stage_blk[: plan.total_block], self.group)
-            peers_unc = peers_blk = 0
-            loc_unc, loc_blk = stage_unc.data_ptr(), stage_blk.data_ptr()
-        if plan.total_unc:
-            native.check(lib.conef_scatter_segments(self.segs_dev.data_ptr(), len(plan.segs), bp, peers_unc, ws,
-                                                    loc_unc, 1.0 / ws, 0, plan.total_unc, st), "scatter_segments")
-        if nb:
-            native.check(lib.conef_randblock_scatter(self.blks_dev.data_ptr(), nb, bp, peers_blk, ws, loc_blk,
-                                                     1.0 / ws, plan.total_block, st), "randblock_scatter")
+        self._run_native(state, buf, stage_unc, stage_blk, st)
         self.step += 1
 
 

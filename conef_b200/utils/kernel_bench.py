@@ -186,10 +186,6 @@ def main():
                 eng.counts.data_ptr(), 0, 0.1, 0.9, native.EF_SKETCH, eng.max_rank, eng.d_smem, st)), args.iters)
             record("decompress+sketch update (shared-memory atomics)", t, 2 * mat_bytes + 2 * sk_bytes,
                    "read M, write M_hat, r/w sketch")
-            if eng.n_dc_tiles:          # only with CONEF_DECOMPRESS_CSR=1
-                t = _time(lambda: eng.launch_decompress_csr(buf.data_ptr(), pmem, qmem, 0.1, 0.9, st), args.iters)
-                record("decompress_csr+sketch update (no atomics)", t, 2 * mat_bytes + 2 * sk_bytes,
-                       "read M, write M_hat, r/w sketch")
         if want("segments"):
             t = _time(lambda: native.check(lib.conef_gather_segments(
                 eng.segs_dev.data_ptr(), len(plan.segs), buf.data_ptr(), 0, eng.staging.data_ptr(), plan.total_unc,

@@ -168,6 +168,33 @@ def test_randomblock_native_vs_cpu(single_rank_group, monkeypatch, kw, unbiased)
             torch.testing.assert_close(x, y, **TOL)
 
 
+@pytest.mark.parametrize("kw", [
+    dict(use_error_feedback=True),
+    dict(use_error_feedback=True, use_error_compression=True, sketch_size=0.1),
+    dict(use_error_feedback=True, use_error_compression=True, error_compressor="quant8", beta=0.0),
+], ids=["ef", "conef-sketch", "quant8"])
+def test_randomblock_two_launch_form_matches_four_launch_form(single_rank_group, monkeypatch, kw):
+    """Gather (+ segments, + publish) and wait + reduce + scatter as two launches against the older
+    gather / signal / wait / scatter sequence; the count-sketch gather folds the remembered term for
+    rows that send nothing, so its sums come in another order."""
+    def run(fused):
+        monkeypatch.setenv("CONEF_FUSED", fused)
+        s = cb.RandomBlockState(None, start_compression_iter=2, compression_ratio=0.13, **kw)
+        s.iter = 2
+        outs = _steps(cb.RandomBlock_hook, s, DEV, monkeypatch, "native", steps=5)
+        eng = s._engines[0]
+        return outs, eng.exec_plan.launched, s
+    a, la, sa = run("1")
+    b, lb, sb = run("0")
+    assert la == 2 and lb > la
+    for x, y in zip(a, b):
+        if "sketch_size" in kw:
+            torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-5)
+        else:
+            assert torch.equal(x, y)
+    sa.check_status()
+
+
 def test_randomblock_native_error_layout(single_rank_group, monkeypatch):
     monkeypatch.setenv("CONEF_BACKEND", "native")
     s = cb.RandomBlockState(None, start_compression_iter=2, compression_ratio=0.1)
@@ -277,32 +304,27 @@ def test_hpowersgd_lowrank_error_native_vs_cpu(single_rank_group, monkeypatch, t
 ], ids=["ef", "conef", "lowrank"])
 def test_executor_graph_replay_matches_direct_launches(single_rank_group, monkeypatch, kw, tc):
     """The native executor replays a captured CUDA graph from the fifth step on; its results must
-    match direct launches and the Python launch loop over ten steps."""
+    match direct launches over ten steps."""
     monkeypatch.setenv("CONEF_TC", tc)
 
-    def run(graph, executor="native"):
+    def run(graph):
         monkeypatch.setenv("CONEF_GRAPH", graph)
-        monkeypatch.setenv("CONEF_EXECUTOR", executor)
         state = _powersgd_states(DEV, **kw)
         outs = _steps(cb.powerSGD_hook, state, DEV, monkeypatch, "native", steps=10)
         eng = state._engines[0]
-        replays = eng.exec_plan.graph_replays if eng.exec_plan is not None else -1
-        return outs, replays
+        return outs, eng.exec_plan.graph_replays
 
     replayed, n_replays = run("1")
     direct, n_direct = run("0")
-    looped, n_loop = run("0", executor="py")
-    assert n_replays == 6 and n_direct == 0 and n_loop == -1
-    for a, b, c in zip(replayed, direct, looped):
+    assert n_replays == 6 and n_direct == 0
+    for a, b in zip(replayed, direct):
         if tc == "0":
             torch.testing.assert_close(a, b, **TOL)
-            torch.testing.assert_close(a, c, **TOL)
         else:
             # tf32 tiles with split-K atomics: the summation order differs from run to run, and error
             # feedback plus warm start carry the differences forward, so single elements of small,
             # nearly rank-deficient matrices move; compare in norm
             assert (a - b).norm() <= 1e-2 * b.norm()
-            assert (a - c).norm() <= 1e-2 * c.norm()
 
 
 @pytest.mark.parametrize("kw", [
@@ -347,12 +369,10 @@ def test_fused_pipeline_matches_the_long_form(single_rank_group, monkeypatch, kw
     sa.check_status()
 
 
-@pytest.mark.parametrize("executor", ["native", "py"])
-def test_hpowersgd_topk_error_native_vs_cpu(single_rank_group, monkeypatch, executor):
+def test_hpowersgd_topk_error_native_vs_cpu(single_rank_group, monkeypatch):
     """hPowerSGD with its top-k error store: dense error records + one grouped radix select per
     step on the GPU against torch.topk per matrix on the CPU."""
     monkeypatch.setenv("CONEF_TC", "0")
-    monkeypatch.setenv("CONEF_EXECUTOR", executor)
     shapes = [(96, 200), (96,), (300, 64), (40, 33, 3, 3), (7,)]
 
     def mk(device):
@@ -394,30 +414,6 @@ def test_hpowersgd_topk_error_native_vs_cpu(single_rank_group, monkeypatch, exec
         assert int(((mine != 0) != (comp.err != 0)).sum()) <= 8
         assert rel(mine, comp.err) < 5e-2
     assert sg.ef_buffer_bytes() == sc.ef_buffer_bytes()
-
-
-@pytest.mark.parametrize("kw", [
-    dict(matrix_approximation_rank=2, sketch_size=0.1),
-    dict(matrix_approximation_rank=8, sketch_size=0.3, beta=0.5),
-], ids=["r2", "r8"])
-def test_decompress_without_atomics_matches_atomic_kernel(single_rank_group, monkeypatch, kw):
-    """Two kernels for the count-sketch store: per-cell sums over a CSR of the hash table (default)
-    and shared-memory atomics; same outputs and same sketches over several steps."""
-    monkeypatch.setenv("CONEF_TC", "0")
-    kw = dict(use_error_feedback=True, use_error_compression=True, **kw)
-
-    def run(flag):
-        monkeypatch.setenv("CONEF_DECOMPRESS_CSR", flag)
-        state = _powersgd_states(DEV, **kw)
-        outs = _steps(cb.powerSGD_hook, state, DEV, monkeypatch, "native", steps=4)
-        eng = state._engines[0]
-        assert bool(eng.n_dc_tiles) == (flag == "1")
-        return outs, eng.sketch_arena.cpu().clone()
-    a, sa = run("1")
-    b, sb = run("0")
-    for x, y in zip(a, b):
-        torch.testing.assert_close(x, y, **TOL)
-    torch.testing.assert_close(sa, sb, **TOL)
 
 
 def test_phase_timing_and_wire_bytes_on_gpu(single_rank_group, monkeypatch):

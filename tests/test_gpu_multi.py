@@ -180,6 +180,40 @@ def test_randomblock_more_gpus_ranks_agree(world):
     run_ranks(_randblock_worker, world=world, args=("auto", dict(use_error_feedback=True)), backend="nccl")
 
 
+def _two_shot_worker(rank, world):
+    """The two-shot reduction (slice sum, push to every peer, second epoch) against the one-shot
+    one: same order of additions, hence the same bits, and the closed form on the first step."""
+    outs = {}
+    for limit in ("0", str(1 << 40)):                  # everything in two shots / nothing
+        os.environ["CONEF_TWO_SHOT_BYTES"] = limit
+        os.environ["CONEF_COMM"] = "auto"
+        dev = torch.device("cuda", rank)
+        # dense error feedback: no atomics anywhere, so two runs can be compared bit for bit
+        s = cb.RandomBlockState(None, start_compression_iter=2, compression_ratio=0.2, use_error_feedback=True)
+        s.iter = 2
+        b = FakeBucket(SHAPES, device=dev, seed=300 + rank)
+        res = []
+        for i in range(4):
+            b.refill(500 + 10 * i + rank)
+            res.append(cb.RandomBlock_hook(s, b).wait().clone())
+        torch.cuda.synchronize()
+        s.check_status()
+        eng = s._engines[0]
+        assert eng.symm is not None and bool(eng.exec_plan.two_shot) == (limit == "0")
+        outs[limit] = torch.stack(res)
+        gathered = [torch.zeros_like(outs[limit]) for _ in range(world)]
+        dist.all_gather(gathered, outs[limit])
+        assert _all_equal(gathered)
+    assert torch.equal(outs["0"], outs[str(1 << 40)])
+    os.environ.pop("CONEF_TWO_SHOT_BYTES", None)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_randomblock_two_shot_matches_one_shot(world):
+    _need_gpus(world)
+    run_ranks(_two_shot_worker, world=world, args=(), backend="nccl")
+
+
 def _ddp_worker(rank, world, name):
     import torch.nn.functional as F
 

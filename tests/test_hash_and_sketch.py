@@ -204,36 +204,3 @@ def test_lowrank_recovers_lowrank_error():
     assert lr.nbytes() == (40 + 30) * 2 * 4
 
 
-@pytest.mark.parametrize("D,W", [(5760, 576), (1024, 102), (650, 65), (7, 1), (33, 40)])
-def test_regrouped_hash_table_lists_every_column_once(D, W):
-    """The per-cell regrouping of the packed hash table (used by the atomics-free decompress kernel):
-    every column appears exactly once, under its own cell, with its sign; lists inside a group of 32
-    cells are interleaved and padded with -1; cells are ordered by decreasing list length."""
-    pk = ref.packed_hash_table(D, W, ref.DEFAULT_A, ref.DEFAULT_B)
-    blob = ref.ell_hash_table(pk, W)
-    G = (W + 31) // 32
-    groups = blob[: 2 * G].reshape(G, 2)
-    ids = blob[2 * G : 2 * G + 32 * G]
-    ent = blob[2 * G + 32 * G :]
-    idx = pk.view(np.uint32) & 0x7FFFFFFF
-    counts = np.bincount(idx, minlength=W)
-    seen = np.zeros(D, dtype=np.int64)
-    assert sorted(int(w) for w in ids if w >= 0) == list(range(W))
-    lengths = [int(counts[w]) for w in ids if w >= 0]
-    assert lengths == sorted(lengths, reverse=True)
-    for g in range(G):
-        base, steps = (int(v) for v in groups[g])
-        lanes = ids[32 * g : 32 * g + 32]
-        assert steps == max((int(counts[w]) for w in lanes if w >= 0), default=0)
-        block = ent[base : base + 32 * steps].reshape(steps, 32)
-        for lane, w in enumerate(lanes):
-            col = block[:, lane]
-            real = col[col != -1]
-            if w < 0:
-                assert real.size == 0
-                continue
-            assert real.size == counts[w] and (col[: real.size] != -1).all()
-            c = real.view(np.uint32) & 0x7FFFFFFF
-            assert (idx[c] == w).all() and ((real < 0) == (pk[c] < 0)).all()
-            seen[c] += 1
-    assert (seen == 1).all() and ent.size == sum(32 * int(s) for _, s in groups)
