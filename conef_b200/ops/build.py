@@ -76,11 +76,13 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
             if res.returncode != 0:
                 raise RuntimeError(f"nvcc failed on {src.name}")
             objs.append(str(obj))
-    link = [nvcc, "-shared", "-o", str(OUT), *objs, "-lcudart"]
+    tmp = OUT.with_suffix(".so.tmp")         # link aside, then rename: readers never see a half-written library
+    link = [nvcc, "-shared", "-o", str(tmp), *objs, "-lcudart"]
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
         raise RuntimeError("link failed")
+    os.replace(tmp, OUT)
     (OBJ_DIR / "digest.txt").write_text(_digest())
     return OUT
 

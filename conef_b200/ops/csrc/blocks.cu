@@ -193,16 +193,20 @@ k_randblock_gather_flat(const ConefBlk* __restrict__ blks, const int2* __restric
 //   S'[i, w] = S[i, w] (1 - (1 - beta) k_w) + sum over the NOT selected columns j of cell w of (s_j g_ij + alpha S[i, w])
 // so a row none of whose elements are selected (nine rows in ten at a 10 % block) needs no gather of
 // the old sketch value: its remembered term is alpha k_w S[i, w], applied when the accumulator is
-// flushed, and the pass over its elements is one shared-memory atomic each.  A row that is selected
-// whole needs no atomics at all, only the old sketch values for what it sends; they are read from a
-// copy of the row in shared memory.  The (at most four) rows a block boundary cuts take both.
+// flushed, and the pass over its elements is one shared-memory atomic each.  A row the block covers
+// or cuts needs the old sketch values for what it sends; a tile that has such a row first copies its
+// sketch rows into shared memory.  All rows of the tile are walked together, column by column, so
+// that a thread has one load per row in flight: walking the rows one after another leaves a single
+// load in flight per thread and ran eight times slower.
+constexpr int RB_MAX_ROWS = 8;
+
 __global__ void __launch_bounds__(256)
 k_randblock_gather_sketch(const ConefBlk* __restrict__ blks, const int2* __restrict__ tiles, int rows_per_cta,
                           float* __restrict__ bucket, float* __restrict__ staging, float gather_scale,
                           float* __restrict__ sketch, const int32_t* __restrict__ tables,
                           const int32_t* __restrict__ counts, float alpha, float beta, const SegGather SG,
                           const ConefPublish pub) {
-  extern __shared__ float sm[];  // acc: rows_per_cta * W, then one old sketch row: W
+  extern __shared__ float sm[];  // acc: rows_per_cta * W, then the old sketch rows: rows_per_cta * W
   if ((int)blockIdx.x >= SG.tile_ctas) {
     seg_gather_ctas(SG, bucket);
   } else {
@@ -213,51 +217,60 @@ k_randblock_gather_sketch(const ConefBlk* __restrict__ blks, const int2* __restr
     const int rows = min(rows_per_cta, B.n - row0);
     float* acc = sm;
     float* old = sm + (size_t)rows_per_cta * W;
-    for (int i = threadIdx.x; i < rows * W; i += blockDim.x) acc[i] = 0.f;
     const int32_t* tab = tables + B.tab_off;
     const int32_t* cnt = counts + B.cnt_off;
     const float gs = gather_scale != 0.f ? gather_scale : (float)B.numel / (float)B.block;
     const float omb = 1.f - beta;
-    float* g = bucket + B.g_off;
+    float* g = bucket + B.g_off + (size_t)row0 * m;
+    float* srow0 = sketch + B.sk_off + (size_t)row0 * W;
     const long long end = B.start + B.block, wrap = end - B.numel;
-    for (int ii = 0; ii < rows; ++ii) {
-      const long long r0 = (long long)(row0 + ii) * m, r1 = r0 + m;      // flat range of the row
-      // how much of the row the block [start, end) and its wrapped part [0, wrap) cover
-      const long long c1 = max(0LL, min(r1, end) - max(r0, B.start)) + max(0LL, min(r1, wrap) - r0);
-      float* srow = sketch + B.sk_off + (size_t)(row0 + ii) * W;
-      float* arow = acc + (size_t)ii * W;
-      __syncthreads();                         // acc zeroed / the previous row's copy no longer read
-      if (c1 == 0) {
-        // nothing selected: one atomic per element, the remembered term folds into the flush
-        for (int j = threadIdx.x; j < m; j += blockDim.x) {
-          const int e = __ldg(tab + j);
-          const float v = g[r0 + j];
-          g[r0 + j] = 0.f;
-          atomicAdd(&arow[unpack_bucket(e)], unpack_sign(e) * v);
-        }
-        __syncthreads();
-        for (int w = threadIdx.x; w < W; w += blockDim.x)
-          srow[w] = srow[w] * (1.f + (alpha - omb) * (float)__ldg(cnt + w)) + arow[w];
-      } else {
-        for (int w = threadIdx.x; w < W; w += blockDim.x) old[w] = srow[w];
-        __syncthreads();
-        for (int j = threadIdx.x; j < m; j += blockDim.x) {
-          const int e = __ldg(tab + j);
-          const int h = unpack_bucket(e);
-          const float s = unpack_sign(e);
-          const float v = g[r0 + j] + alpha * s * old[h];
-          long long sp;
-          if (in_block(B, r0 + j, &sp)) {
-            staging[sp] = v * gs;
+    // bit ii of `touched`: the block covers or cuts row ii (the same value in every thread)
+    unsigned touched = 0;
+#pragma unroll
+    for (int ii = 0; ii < RB_MAX_ROWS; ++ii) {
+      if (ii < rows) {
+        const long long r0 = (long long)(row0 + ii) * m, r1 = r0 + m;
+        const long long c1 = max(0LL, min(r1, end) - max(r0, B.start)) + max(0LL, min(r1, wrap) - r0);
+        if (c1 > 0) touched |= 1u << ii;
+      }
+    }
+    for (int i = threadIdx.x; i < rows * W; i += blockDim.x) {
+      acc[i] = 0.f;
+      if (touched) old[i] = srow0[i];
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < m; j += blockDim.x) {
+      const int e = __ldg(tab + j);
+      const int h = unpack_bucket(e);
+      const float s = unpack_sign(e);
+      float v[RB_MAX_ROWS];
+#pragma unroll
+      for (int ii = 0; ii < RB_MAX_ROWS; ++ii) v[ii] = ii < rows ? g[(size_t)ii * m + j] : 0.f;
+#pragma unroll
+      for (int ii = 0; ii < RB_MAX_ROWS; ++ii) {
+        if (ii < rows) {
+          if (!((touched >> ii) & 1u)) {
+            g[(size_t)ii * m + j] = 0.f;
+            atomicAdd(&acc[ii * W + h], s * v[ii]);
           } else {
-            g[r0 + j] = 0.f;
-            atomicAdd(&arow[h], s * v);
+            const float vv = v[ii] + alpha * s * old[ii * W + h];
+            long long sp;
+            if (in_block(B, (long long)(row0 + ii) * m + j, &sp)) {
+              staging[sp] = vv * gs;
+            } else {
+              g[(size_t)ii * m + j] = 0.f;
+              atomicAdd(&acc[ii * W + h], s * vv);
+            }
           }
         }
-        __syncthreads();
-        for (int w = threadIdx.x; w < W; w += blockDim.x)
-          srow[w] = old[w] * (1.f - omb * (float)__ldg(cnt + w)) + arow[w];
       }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < rows * W; i += blockDim.x) {
+      const int ii = i / W, w = i - ii * W;
+      const float k = (float)__ldg(cnt + w);
+      if ((touched >> ii) & 1u) srow0[i] = old[i] * (1.f - omb * k) + acc[i];
+      else srow0[i] = srow0[i] * (1.f + (alpha - omb) * k) + acc[i];
     }
   }
   conef_publish_if_last(pub, gridDim.x);
@@ -289,7 +302,8 @@ extern "C" int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles
   SG.segs = segs; SG.nsegs = nsegs; SG.total = (segs != nullptr && nsegs > 0) ? total_unc : 0; SG.staging = staging_unc;
   const int seg_ctas = seg_cta_count(SG.total);
   if (ef_mode == CONEF_EF_SKETCH) {
-    smem_bytes += (smem_bytes / (rows_per_cta > 0 ? rows_per_cta : 1));      // one more row: the old sketch values
+    if (rows_per_cta > RB_MAX_ROWS) { conef_set_error("randblock_gather: at most %d rows per CTA", RB_MAX_ROWS); return 2; }
+    smem_bytes *= 2;      // the accumulators and a copy of the old sketch rows
     if (smem_bytes > 220 * 1024) { conef_set_error("randblock_gather: sketch rows do not fit in shared memory"); return 2; }
     SG.tile_ctas = ntiles;
     if (ntiles + seg_ctas == 0) return 0;

@@ -114,6 +114,31 @@ __device__ __forceinline__ bool wait_flags_bounded(const uint32_t* flags, int wo
   return true;
 }
 
+// Offset (in floats) of element (k, n) of a small operand inside its packed copy: per K step
+// of 8 rows, NP/8 groups of 8 columns, each two 8x4 core matrices (k%8 < 4, k%8 >= 4) of
+// 32 floats: K-major, no swizzle, exactly what tcgen05.mma reads for a K=8 tf32 step.
+__host__ __device__ __forceinline__ long long conef_packed_offset(long long k, int n, int np) {
+  return (k >> 3) * (np * 8) + (n >> 3) * 64 + ((k & 7) >> 2) * 32 + (n & 7) * 4 + (k & 3);
+}
+
+// Store element (row, c) of a small factor (which = 0: P block, 1: Q block) into the packed copies the
+// tensor-core kernel reads, including the folded ones (see ConefMat::fold).
+__device__ __forceinline__ void conef_pack_store(float* __restrict__ packed, const ConefMat& M, int which,
+                                                 long long row, int c, float v, int np) {
+  if (which == 1) {
+    if (M.fold > 1) {
+      for (int b = 0; b < M.fold; ++b)
+        packed[M.qpk_off + conef_packed_offset((long long)b * M.m + row, b * M.r + c, np)] = v;
+    } else {
+      packed[M.qpk_off + conef_packed_offset(row, c, np)] = v;
+    }
+  } else {
+    packed[M.ppk_off + conef_packed_offset(row, c, np)] = v;
+    if (M.fold > 1)
+      packed[M.ppk_fold_off + conef_packed_offset(row / M.fold, (int)(row % M.fold) * M.r + c, np)] = v;
+  }
+}
+
 // "The CTA that finishes last tells the peers": a kernel whose output a peer-memory reduction
 // consumes publishes the epoch itself instead of leaving that to a launch of its own.  `done`
 // counts finished CTAs and is zero between launches.  Call from every CTA, all threads, after the
@@ -167,9 +192,3 @@ __device__ __forceinline__ void conef_philox_normal4(uint64_t seed, uint64_t ctr
   out[2] = r1 * cosf(two_pi * u3); out[3] = r1 * sinf(two_pi * u3);
 }
 
-// Offset (in floats) of element (k, n) of a small operand inside its packed copy: per K step
-// of 8 rows, NP/8 groups of 8 columns, each two 8x4 core matrices (k%8 < 4, k%8 >= 4) of
-// 32 floats: K-major, no swizzle, exactly what tcgen05.mma reads for a K=8 tf32 step.
-__host__ __device__ __forceinline__ long long conef_packed_offset(long long k, int n, int np) {
-  return (k >> 3) * (np * 8) + (n >> 3) * 64 + ((k & 7) >> 2) * 32 + (n & 7) * 4 + (k & 3);
-}

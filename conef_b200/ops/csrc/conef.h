@@ -32,6 +32,18 @@ typedef struct ConefMat {
   int Wp;             // row pitch of the sketch block in floats (W rounded up so that TMA can address it)
   long long qpk_off;  // packed copy of the (m x r) block for the tensor-core kernel (floats), see conef_pack_small
   long long ppk_off;  // packed copy of the (n x r) block
+  // Folded view for matrices whose row pitch is not a multiple of 16 bytes (m % 4 != 0), which a
+  // tensor map cannot describe: `fold` consecutive rows are read as ONE row of fold * m elements
+  // (pitch then a multiple of 16 bytes), i.e. the same memory as an (n / fold) x (fold * m) matrix.
+  //   P = M Q   : (n/f x f m)(f m x f r) with the block-diagonal operand diag(Q, .., Q) gives the
+  //               (n/f x f r) result whose memory IS the (n x r) block P.
+  //   Q = M^T P : (f m x n/f)(n/f x f r) with P read as (n/f x f r); output row b m + j holds in its
+  //               columns [b r, (b+1) r) one part of Q[j, :]; the f parts are added up.
+  // fold <= 1: no folding.  With fold > 1 the packed block at qpk_off is that block-diagonal operand
+  // (f m rows) and ppk_fold_off the (n/f x f r) packing of P (ppk_off keeps the plain one).
+  long long ppk_fold_off;
+  int fold;
+  int pad_;
 } ConefMat;
 
 // One small-factor correction (see conef_lowrank_correct): offsets in floats into the four
@@ -102,6 +114,7 @@ typedef struct ConefOrthExtra {
 
 const char* conef_last_error(void);
 int conef_version(void);
+int conef_mat_size(void);       // sizeof(ConefMat), so that a binding can verify its mirror of the layout
 
 // ---- count sketch (sketch.cu) ---------------------------------------------
 int conef_build_hash_table(int32_t* table, int32_t* counts, int D, int W,

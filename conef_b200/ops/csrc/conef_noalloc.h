@@ -22,7 +22,8 @@
 //     a message in conef_last_error()); nothing is launched in that case.
 //   * The first call on a device looks up the device address of the scratch
 //     array (cudaGetSymbolAddress, with that device current) and remembers it.
-//     Make that first call outside of any CUDA stream capture.
+//     Make that first call outside of any CUDA stream capture.  Several host threads
+//     may make it at once: each looks the address up and stores the same value.
 //   * The function calls no cudaMalloc / cudaFree and no allocating library
 //     routine.  It enqueues one memset and the same three kernels as
 //     conef_lamb_step() on `stream`.

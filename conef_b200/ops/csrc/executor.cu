@@ -32,10 +32,14 @@ int orth(ConefPsgdPlan* plan, int which, const ConefTileList& tl, float* buf, fl
          cudaStream_t s, const uint32_t* eb = nullptr) {
   if (!tl.n) return 0;
   float* pk = (packed && plan->use_tc) ? (which == 0 ? plan->ppk : plan->qpk) : nullptr;
-  RUN(conef_orthogonalize_packed_ex(plan->mats, (const int2*)tl.tiles, tl.n, plan->nrec, which, buf, eps,
-                                    peers, flags, world, epoch, plan->status,
-                                    world > 1 ? plan->spin_limit : 0, pk, plan->np_cols, plan->gram, eb, s));
-  plan->launched += 2;      // Gram matrix and application, twice over; counted as three kernels
+  ConefOrthExtra X;
+  memset(&X, 0, sizeof(X));
+  X.bar = (plan->one_launch_orth && plan->done_word) ? plan->done_word + 1 : nullptr;    // one launch when it fits
+  X.max_rank = plan->max_rank;
+  RUN(conef_orthogonalize_fused(plan->mats, (const int2*)tl.tiles, tl.n, which, buf, eps,
+                                world > 1 ? peers : nullptr, flags, world, epoch, plan->status,
+                                world > 1 ? plan->spin_limit : 0, pk, plan->np_cols, plan->gram, eb, &X, s));
+  plan->launched += conef_orth_last_launches() - 1;
   return 0;
 }
 
@@ -452,3 +456,4 @@ extern "C" int conef_randblock_plan_size(void) { return (int)sizeof(ConefRandblo
 
 // Size of the plan structure, so that a binding can verify its mirror of the layout.
 extern "C" int conef_psgd_plan_size(void) { return (int)sizeof(ConefPsgdPlan); }
+extern "C" int conef_mat_size(void) { return (int)sizeof(ConefMat); }

@@ -125,22 +125,8 @@ extern "C" int conef_lamb_step_noalloc(const ConefLambTensor* tensors, int ntens
     CONEF_CUDA(cudaGetSymbolAddress((void**)&addr, g_lamb_scratch));
     g_lamb_scratch_addr[dev] = addr;
   }
-  float* norms = g_lamb_scratch_addr[dev];
-  // the accumulators of this call start at zero; the rest of the array keeps old values
-  CONEF_CUDA(cudaMemsetAsync(norms, 0, sizeof(float) * (size_t)(1 + 2 * ntensors), stream));
-  if (max_grad_norm > 0.f) {
-    k_lamb_gnorm<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, norms);
-    CONEF_CHECK_LAUNCH("k_lamb_gnorm");
-  }
-  float bc1 = 1.f, bc2 = 1.f;
-  if (bias_correction) {
-    bc1 = 1.f - powf(beta1, (float)step);
-    bc2 = 1.f - powf(beta2, (float)step);
-  }
-  k_lamb_stage1<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, norms, beta1, beta2, eps, bc1, bc2,
-                                                 grad_scale, max_grad_norm);
-  CONEF_CHECK_LAUNCH("k_lamb_stage1");
-  k_lamb_stage2<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, norms, lr);
-  CONEF_CHECK_LAUNCH("k_lamb_stage2");
-  return 0;
+  // the same memset and kernels as the entry point with a caller-provided buffer: the accumulators
+  // this call uses are cleared first, the rest of the array keeps old values
+  return conef_lamb_step(tensors, ntensors, chunks, nchunks, chunk_elems, g_lamb_scratch_addr[dev], lr, beta1, beta2,
+                         eps, step, bias_correction, grad_scale, max_grad_norm, stream);
 }

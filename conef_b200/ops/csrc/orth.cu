@@ -226,7 +226,7 @@ k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
         for (int k = 0; k < OC_MAXR; ++k)
           if (k <= c) v = fmaf(av[k], Ri[k][c], v);
         rowp[c] = v;
-        if (pk) pk[conef_packed_offset(grow0 + i, c, packed_np)] = v;
+        if (packed) conef_pack_store(packed, M, which, grow0 + i, c, v, packed_np);
         if (project) atomicAdd(zpk + conef_packed_offset(ph, c, packed_np), psc * v);
       }
     }
@@ -241,7 +241,7 @@ k_qr_apply(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
                              (uint64_t)(grow0 + i), z);
         const float v = z[0] * refill_scale;
         a[(size_t)i * r + c] = v;
-        if (pk) pk[conef_packed_offset(grow0 + i, c, packed_np)] = v;
+        if (packed) conef_pack_store(packed, M, which, grow0 + i, c, v, packed_np);
         if (project) {
           const int e = tab[grow0 + i];
           atomicAdd(zpk + conef_packed_offset(unpack_bucket(e), c, packed_np), unpack_sign(e) * proj_alpha * v);
@@ -474,7 +474,7 @@ k_orth_one(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
             xs[i * S + c] = v;
           } else {
             a[(size_t)i * r + c] = v;
-            if (pk) pk[conef_packed_offset(grow0 + i, c, packed_np)] = v;
+            if (packed) conef_pack_store(packed, M, which, grow0 + i, c, v, packed_np);
             if (project) atomicAdd(zpk + conef_packed_offset(ph, c, packed_np), psc * v);
           }
         }
@@ -491,7 +491,7 @@ k_orth_one(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
                            (uint64_t)(grow0 + i), z);
       const float v = z[0] * refill_scale;
       a[(size_t)i * r + c] = v;
-      if (pk) pk[conef_packed_offset(grow0 + i, c, packed_np)] = v;
+      if (packed) conef_pack_store(packed, M, which, grow0 + i, c, v, packed_np);
       if (project) {
         const int e = tab[grow0 + i];
         atomicAdd(zpk + conef_packed_offset(unpack_bucket(e), c, packed_np), unpack_sign(e) * X.alpha * v);

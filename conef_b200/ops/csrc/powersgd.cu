@@ -148,12 +148,11 @@ __global__ void k_pack_small(const ConefMat* __restrict__ mats, int which, const
   const int rows = which == 0 ? M.n : M.m;
   const int r = M.r;
   const float* a = src + (which == 0 ? M.p_off : M.q_off);
-  float* pk = dst + (which == 0 ? M.ppk_off : M.qpk_off);
   const size_t total = (size_t)rows * r;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const long long row = i / r;
     const int c = (int)(i - row * r);
-    pk[conef_packed_offset(row, c, np)] = a[i];
+    conef_pack_store(dst, M, which, row, c, a[i], np);
   }
 }
 
@@ -215,10 +214,12 @@ k_psgd_q(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, cons
 template <int RP>
 static int launch_q(const ConefMat* mats, const int2* tiles, int ntiles, const float* bucket, const float* aux,
                     const float* P, float* Q, size_t smem, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};      // the attribute is per device
+  int dev = 0;
+  CONEF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     CONEF_CUDA(cudaFuncSetAttribute(k_psgd_q<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   k_psgd_q<RP><<<ntiles, Q_THREADS, smem, stream>>>(mats, tiles, bucket, aux, P, Q);
   CONEF_CHECK_LAUNCH("k_psgd_q");
@@ -341,10 +342,12 @@ static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, floa
                        size_t smem, cudaStream_t stream) {
   smem += (size_t)RB * RP * sizeof(float);
   if (smem > 220 * 1024) { conef_set_error("decompress: %zu bytes of shared memory needed", smem); return 2; }
-  static size_t configured = 0;
-  if (smem > 48 * 1024 && smem > configured) {
+  static size_t configured[64] = {};    // largest opt-in so far, per device (the attribute is per device)
+  int dev = 0;
+  CONEF_CUDA(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || smem > configured[dev])) {
     CONEF_CUDA(cudaFuncSetAttribute(k_psgd_decompress<RP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured = smem;
+    if (dev >= 0 && dev < 64) configured[dev] = smem;
   }
   k_psgd_decompress<RP, RB><<<ntiles, D_THREADS, smem, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables,
                                                                 counts, dense_err, alpha, beta, ef_mode);

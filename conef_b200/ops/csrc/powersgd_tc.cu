@@ -160,12 +160,13 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
   const bool atomic_out = (T.mat_flags >> 30) & 1;
   const ConefMat M = mats[mat];
   const int r = M.r;
-  const int mn_total = Q_MODE ? M.m : M.n;
-  const int k_total = Q_MODE ? M.n : M.m;
+  const int fold = M.fold > 1 ? M.fold : 1;          // folded view: (n / fold) x (fold * m), see ConefMat
+  const int mn_total = Q_MODE ? M.m * fold : M.n / fold;
+  const int k_total = Q_MODE ? M.n / fold : M.m * fold;
   const int k_end = min(k_total, T.k0 + T.klen);
   const int iters = (k_end - T.k0 + TC_BK - 1) / TC_BK;
   // small operand, packed: per K step of 8 rows NP * 8 floats (see conef_packed_offset)
-  const float* small = small_packed + (Q_MODE ? M.ppk_off : M.qpk_off);
+  const float* small = small_packed + (Q_MODE ? (fold > 1 ? M.ppk_fold_off : M.ppk_off) : M.qpk_off);
   float* out = out_base + (Q_MODE ? M.q_off : M.p_off);              // (mn_total x r), row-major
   const CUtensorMap* tmap = maps + 2 * mat + Q_MODE;   // [2*mat] K-major view, [2*mat+1] MN-major view
 
@@ -269,13 +270,24 @@ k_tc_skinny(const ConefMat* __restrict__ mats, const CUtensorMap* __restrict__ m
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       const int row = T.mn0 + warp * 32 + lane;
       if (row < mn_total) {
-        float* o = out + (size_t)row * r;
+        if (!Q_MODE || fold == 1) {
+          // P of a folded view: (n / fold) rows of fold * r values, which is the (n x r) block itself
+          const int re = r * fold;
+          float* o = out + (size_t)row * re;
 #pragma unroll
-        for (int c = 0; c < NP; ++c) {
-          if (c < r) {
-            if (atomic_out) atomicAdd(o + c, __uint_as_float(v[c]));
-            else o[c] = __uint_as_float(v[c]);
+          for (int c = 0; c < NP; ++c) {
+            if (c < re) {
+              if (atomic_out) atomicAdd(o + c, __uint_as_float(v[c]));
+              else o[c] = __uint_as_float(v[c]);
+            }
           }
+        } else {
+          // Q of a folded view: output row b * m + j carries its part of Q[j, :] in columns [b r, (b+1) r)
+          const int b = row / M.m, j = row - b * M.m;
+          float* o = out + (size_t)j * r;
+#pragma unroll
+          for (int c = 0; c < NP; ++c)
+            if (c >= b * r && c < (b + 1) * r) atomicAdd(o + (c - b * r), __uint_as_float(v[c]));
         }
       }
     }
@@ -367,9 +379,11 @@ extern "C" int conef_tc_encode_maps(const ConefMat* host_mats, int nmats, const 
     const uintptr_t base = (uintptr_t)((M.src ? aux_dev : bucket_dev) + M.g_off);
     ok[i] = 0;
     memset(&out[2 * i], 0, 2 * sizeof(CUtensorMap));
-    if ((base & 15) != 0 || (M.m % 4) != 0 || M.m < 4 || (M.src && aux_dev == nullptr)) continue;
-    cuuint64_t dims[2] = {(cuuint64_t)M.m, (cuuint64_t)M.n};
-    cuuint64_t strides[1] = {(cuuint64_t)M.m * sizeof(float)};
+    const int fold = M.fold > 1 ? M.fold : 1;
+    const long long vm = (long long)M.m * fold;          // the (n / fold) x (fold * m) view
+    if ((base & 15) != 0 || (vm % 4) != 0 || vm < 4 || (M.n % fold) != 0 || (M.src && aux_dev == nullptr)) continue;
+    cuuint64_t dims[2] = {(cuuint64_t)vm, (cuuint64_t)(M.n / fold)};
+    cuuint64_t strides[1] = {(cuuint64_t)vm * sizeof(float)};
     cuuint32_t box[2] = {32, 32};
     cuuint32_t estr[2] = {1, 1};
     CUresult rc0 = enc(&out[2 * i], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr,

@@ -30,7 +30,8 @@ MAT_DTYPE = np.dtype(
     [("g_off", "<i8"), ("p_off", "<i8"), ("q_off", "<i8"), ("sk_off", "<i8"),
      ("n", "<i4"), ("m", "<i4"), ("r", "<i4"), ("W", "<i4"),
      ("tab_off", "<i4"), ("cnt_off", "<i4"), ("q_rows", "<i4"), ("q_atomic", "<i4"),
-     ("src", "<i4"), ("Wp", "<i4"), ("qpk_off", "<i8"), ("ppk_off", "<i8")], align=True)
+     ("src", "<i4"), ("Wp", "<i4"), ("qpk_off", "<i8"), ("ppk_off", "<i8"),
+     ("ppk_fold_off", "<i8"), ("fold", "<i4"), ("pad_", "<i4")], align=True)
 SEG_DTYPE = np.dtype([("src_off", "<i8"), ("dst_off", "<i8"), ("len", "<i8")], align=True)
 BLK_DTYPE = np.dtype(
     [("g_off", "<i8"), ("numel", "<i8"), ("start", "<i8"), ("block", "<i8"),
@@ -44,7 +45,7 @@ CORR_DTYPE = np.dtype([("t_off", "<i8"), ("x_off", "<i8", (2,)), ("l_off", "<i8"
                        ("rows_t", "<i4"), ("rows_l", "<i4"), ("c1", "<i4"), ("nterms", "<i4"),
                        ("c2", "<i4", (2,))], align=True)
 assert CORR_DTYPE.itemsize == 80
-assert MAT_DTYPE.itemsize == 88 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.itemsize == 72
+assert MAT_DTYPE.itemsize == 104 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.itemsize == 72
 assert LAMB_DTYPE.itemsize == 48
 
 EF_NONE, EF_DENSE, EF_SKETCH, EF_QUANT8 = 0, 1, 2, 3
@@ -182,6 +183,7 @@ _SIGNATURES = {
     "conef_topk_keep": ([vp, C.c_int, vp, C.c_int, vp, C.c_float, vp, vp], C.c_int),
     "conef_topk_chunk": ([], C.c_int),
     "conef_psgd_plan_size": ([], C.c_int),
+    "conef_mat_size": ([], C.c_int),
     "conef_randblock_run": ([C.POINTER(RandblockPlan), C.c_int, vp], C.c_int),
     "conef_randblock_plan_size": ([], C.c_int),
     "conef_psgd_step": ([C.POINTER(PsgdPlan), vp], C.c_int),
@@ -200,7 +202,7 @@ _OPTIONAL = {}
 # How many kernels one call of an entry point enqueues (memsets not counted);
 # everything not listed launches exactly one.  Host-only entry points launch none.
 _KERNELS_PER_CALL = {
-    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_orthogonalize_fused": 3, "conef_lowrank_correct": 2, "conef_topk_keep": 7, "conef_topk_chunk": 0, "conef_orth_last_launches": 0, "conef_psgd_run": 0, "conef_psgd_plan_size": 0, "conef_randblock_run": 0, "conef_randblock_plan_size": 0, "conef_psgd_step": 0, "conef_psgd_plan_release": 0, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
+    "conef_lamb_step": 3, "conef_orthogonalize_packed": 3, "conef_orthogonalize_fused": 3, "conef_lowrank_correct": 2, "conef_topk_keep": 7, "conef_topk_chunk": 0, "conef_orth_last_launches": 0, "conef_psgd_run": 0, "conef_psgd_plan_size": 0, "conef_mat_size": 0, "conef_randblock_run": 0, "conef_randblock_plan_size": 0, "conef_psgd_step": 0, "conef_psgd_plan_release": 0, "conef_version": 0, "conef_tc_supported": 0, "conef_tc_encode_maps": 0, "conef_last_error": 0,
     "conef_ipc_get_handle": 0, "conef_ipc_open_handle": 0, "conef_ipc_close_handle": 0,
     "conef_cpu_hash_table": 0, "conef_cpu_sketch_query": 0, "conef_cpu_sketch_update": 0,
     "conef_cpu_gram_schmidt": 0,
@@ -271,6 +273,9 @@ def lib():
     if handle.conef_randblock_plan_size() != C.sizeof(RandblockPlan):
         raise NativeError(f"RandblockPlan mirrors {C.sizeof(RandblockPlan)} bytes, the library expects "
                           f"{handle.conef_randblock_plan_size()}: rebuild with `python -m conef_b200.ops.build`")
+    if handle.conef_mat_size() != MAT_DTYPE.itemsize:
+        raise NativeError(f"MAT_DTYPE mirrors {MAT_DTYPE.itemsize} bytes, the library expects "
+                          f"{handle.conef_mat_size()}: rebuild with `python -m conef_b200.ops.build`")
     if handle.conef_psgd_plan_size() != C.sizeof(PsgdPlan):
         raise NativeError(f"PsgdPlan mirrors {C.sizeof(PsgdPlan)} bytes, the library expects "
                           f"{handle.conef_psgd_plan_size()}: rebuild with `python -m conef_b200.ops.build`")

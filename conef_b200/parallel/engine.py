@@ -250,12 +250,29 @@ class PowerSGDEngine(_EngineBase):
         # packed copies of the small operands for the tensor-core kernel: rows padded to a
         # multiple of 32, columns to NP; an error record that shares a block shares its copy
         self.np_cols = 16 if self.max_rank <= 16 else 32
+        # A row pitch that is not a multiple of 16 bytes (m % 4 != 0: the LSTM's 650 columns) cannot be
+        # described to TMA.  `fold` consecutive rows read as one row of fold * m elements can: the same
+        # memory as an (n / fold) x (fold * m) matrix (csrc/conef.h:ConefMat).  It needs n % fold == 0
+        # and fold * r accumulator columns.
+        for k in range(nm):
+            n_, m_, r_ = int(mats[k]["n"]), int(mats[k]["m"]), int(mats[k]["r"])
+            fold = 4 // math.gcd(m_, 4)
+            ok_fold = fold > 1 and n_ % fold == 0 and fold * r_ <= self.np_cols and \
+                os.environ.get("CONEF_TC_FOLD", "1") == "1"
+            mats[k]["fold"] = fold if ok_fold else 1
+            mats[k]["ppk_fold_off"] = -1
+            if self.ef_mode == native.EF_DENSE:
+                mats[nm + k]["fold"], mats[nm + k]["ppk_fold_off"] = mats[k]["fold"], -1
         qpk = ppk = 0
         pad32 = lambda x: (x + 31) // 32 * 32
         for k in range(nm):
+            f = int(mats[k]["fold"])
             mats[k]["qpk_off"], mats[k]["ppk_off"] = qpk, ppk
-            qpk += pad32(int(mats[k]["m"])) * self.np_cols
+            qpk += pad32(int(mats[k]["m"]) * f) * self.np_cols
             ppk += pad32(int(mats[k]["n"])) * self.np_cols
+            if f > 1:
+                mats[k]["ppk_fold_off"] = ppk
+                ppk += pad32(int(mats[k]["n"]) // f) * self.np_cols
         if self.lowrank:
             for k in range(nm, nrec):
                 mats[k]["qpk_off"], mats[k]["ppk_off"] = qpk, ppk
@@ -268,6 +285,7 @@ class PowerSGDEngine(_EngineBase):
                 err["ppk_off"] = mats[k]["ppk_off"]
                 if self.ef_mode == native.EF_DENSE:
                     err["qpk_off"] = mats[k]["qpk_off"]
+                    err["ppk_fold_off"] = mats[k]["ppk_fold_off"]
                 else:
                     err["qpk_off"] = qpk
                     qpk += pad32(int(err["m"])) * self.np_cols
@@ -405,8 +423,10 @@ class PowerSGDEngine(_EngineBase):
             # mode 0 (P): output rows = n, K = m.  mode 1 (Q): output rows = m, K = n.
             # Every tile gets about the same K extent, chosen so that the launch has a few
             # waves of CTAs (two CTAs fit on an SM) without making tiles too short.
-            dims = [((int(recs[k]["m"]), int(recs[k]["n"])) if mode else (int(recs[k]["n"]), int(recs[k]["m"])))
-                    for k in good]
+            def view(k):        # (output rows, K) of record k, in its folded view when it has one
+                n_, m_, f = int(recs[k]["n"]), int(recs[k]["m"]), max(1, int(recs[k]["fold"]))
+                return (m_ * f, n_ // f) if mode else (n_ // f, m_ * f)
+            dims = [view(k) for k in good]
             work = sum(math.ceil(mn / 128) * K for mn, K in dims)
             klen_t = work / max(1.0, waves * TARGET_CTAS)
             klen_t = int(min(max_k, max(min_k, math.ceil(klen_t / 32) * 32)))
@@ -416,7 +436,8 @@ class PowerSGDEngine(_EngineBase):
                 klen = math.ceil(math.ceil(K / splits) / 32) * 32
                 splits = math.ceil(K / klen)
                 shared = self.fused_err if mode == 0 else self.ef_mode == native.EF_DENSE
-                flag = (1 << 30) if (splits > 1 or shared) else 0
+                folded_q = mode == 1 and int(recs[k]["fold"]) > 1       # its row blocks add into one Q block
+                flag = (1 << 30) if (splits > 1 or shared or folded_q) else 0
                 for mb in range(math.ceil(mn / 128)):
                     for sp in range(splits):
                         tiles.append((k | flag, mb * 128, sp * klen, klen))
@@ -906,7 +927,7 @@ class RandBlockEngine(_EngineBase):
             maxW = max(widths, default=1)
             if maxW * 4 > SMEM_BUDGET:
                 raise native.NativeError(f"sketch width {maxW} does not fit in shared memory")
-            self.rows = int(max(1, min(8, SMEM_BUDGET // (maxW * 4))))
+            self.rows = int(max(1, min(8, SMEM_BUDGET // (maxW * 8))))     # accumulators + a copy of the old rows
             self.smem = self.rows * maxW * 4
             tiles = [(k, rb) for k, b in enumerate(plan.blocks) for rb in range(math.ceil(b.n / self.rows))]
         else:

@@ -10,6 +10,7 @@ the same compression state.
 from __future__ import annotations
 
 import glob
+import logging
 import os
 import re
 import signal
@@ -56,14 +57,26 @@ def save_checkpoint(directory: str, step: int, *, model, optimizer=None, reducer
     """Rank 0 writes ``ckpt_<step>.pt`` atomically and prunes all but the newest ``keep_last``.
 
     With error feedback every rank has its own error memory: pass ``per_rank=True`` in
-    ``extra`` to write ``ckpt_<step>.rank<r>.pt`` side files with each rank's reducer state.
+    ``extra`` to write ``ckpt_<step>.rank<r>.pt`` side files with each rank's reducer state
+    (atomically, before rank 0 publishes the main file when a process group is up; they are pruned
+    together with their step).  Without ``per_rank`` every rank resumes from rank 0's error memory.
     """
     extra = dict(extra or {})
     per_rank = bool(extra.pop("per_rank", False))
     os.makedirs(directory, exist_ok=True)
     module = getattr(model, "module", model)
     if per_rank and reducer_state is not None and rank != 0:
-        torch.save({"reducer": reducer_state.state_dict()}, os.path.join(directory, f"ckpt_{step}.rank{rank}.pt"))
+        side = os.path.join(directory, f"ckpt_{step}.rank{rank}.pt")
+        torch.save({"reducer": reducer_state.state_dict()}, side + ".tmp")
+        os.replace(side + ".tmp", side)
+    if per_rank:
+        # the main file is the marker of a complete checkpoint: publish it after every side file
+        try:
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                dist.barrier()
+        except Exception:  # noqa: BLE001 - a checkpoint must not fail because of the barrier
+            pass
     if rank != 0:
         return None
     blob = {"model": module.state_dict(), "step": step, "extra": extra,
@@ -79,6 +92,8 @@ def save_checkpoint(directory: str, step: int, *, model, optimizer=None, reducer
     files = [f for f in files if ".rank" not in f]
     for old in files[:-keep_last] if keep_last > 0 else []:
         os.remove(old)
+        for side in glob.glob(old[: -len(".pt")] + ".rank*.pt"):     # the step's per-rank side files
+            os.remove(side)
     return path
 
 
@@ -95,6 +110,9 @@ def load_checkpoint(path: str, *, model, optimizer=None, reducer_state=None, sch
         red = blob.get("reducer")
         if rank != 0 and os.path.exists(side):
             red = torch.load(side, map_location="cpu", weights_only=False)["reducer"]
+        elif rank != 0 and red is not None:
+            logging.getLogger(__name__).warning(
+                "rank %d: %s not found, resuming the reducer from rank 0's error memory", rank, os.path.basename(side))
         if red is not None:
             reducer_state.load_state_dict(red, device=device)
     return {"step": blob.get("step", 0), "extra": blob.get("extra", {})}

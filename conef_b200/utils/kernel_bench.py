@@ -29,6 +29,11 @@ CASES = {
     # (shapes, rank): matrices as in the named model, repeated until the bucket exceeds L2
     "wrn": ([(640, 640, 3, 3)] * 10 + [(640,)] * 10 + [(320, 320, 3, 3)] * 6 + [(100, 640), (100,)], 4),
     "bert": ([(1024, 1024)] * 24 + [(4096, 1024)] * 8 + [(1024, 4096)] * 8 + [(1024,)] * 16 + [(4096,)] * 8, 8),
+    # the LSTM language model: row pitch 650 * 4 bytes, which only the folded view can give to TMA
+    "lstm": ([(33278, 650)] + [(2600, 650)] * 24 + [(2600,)] * 12, 4),
+    # Transformer-base: attention / feed-forward matrices and one embedding; `--only phase` runs it with
+    # the hPowerSGD hook and the low-rank error store of that benchmark configuration
+    "transformer": ([(512, 512)] * 48 + [(2048, 512)] * 12 + [(512, 2048)] * 12 + [(32000, 512)] + [(512,)] * 60, 8),
     "small": ([(256, 1024), (64,), (640, 360)], 4),
 }
 
@@ -153,8 +158,12 @@ def main():
             # launches; CUDA events around each phase on the hook's stream)
             for fused in ("1", "0"):
                 os.environ["CONEF_FUSED"] = fused
-                st2 = cb.PowerSGDState(None, matrix_approximation_rank=rank, start_powerSGD_iter=2,
-                                       use_error_compression=True, sketch_size=args.sketch_size)
+                if args.case == "transformer":
+                    st2 = cb.hPowerSGDState(None, matrix_approximation_rank=rank, start_powerSGD_iter=2,
+                                            use_error_compression=True, error_compressor="lowrank", error_rank=rank)
+                else:
+                    st2 = cb.PowerSGDState(None, matrix_approximation_rank=rank, start_powerSGD_iter=2,
+                                           use_error_compression=True, sketch_size=args.sketch_size)
                 st2.iter = 2
                 for _ in range(3):
                     cb.powerSGD_hook(st2, bucket).wait()

@@ -14,29 +14,49 @@ DEV = "cuda"
 # TMA-addressable matrices (16-byte aligned start, row pitch multiple of 16 bytes) of ragged
 # sizes, plus one that is not addressable and must fall back to the SIMT kernel.
 SHAPES = [(256, 1024), (64,), (130, 64, 3, 3), (640, 40, 3, 3), (1000, 36), (4,), (3, 5001), (33, 2052)]
+# Row pitches that are not a multiple of 16 bytes (the LSTM's 650 columns, a first convolution's 27):
+# addressed through the folded view, `fold` rows read as one; (77, 650) has an odd row count for fold 2
+# and stays on the SIMT kernels.
+SHAPES_FOLD = [(260, 650), (64, 27), (1302, 650), (128, 130), (78, 650), (77, 650), (10,)]
+SHAPE_SETS = {"aligned": SHAPES, "folded": SHAPES_FOLD}
 
 
 def _rel(a, b):
     return float((a - b).norm() / b.norm().clamp_min(1e-12))
 
 
-def _engine(rank, monkeypatch, group):
+def _engine(rank, monkeypatch, group, shapes=SHAPES):
     monkeypatch.setenv("CONEF_TC", "1")
     monkeypatch.setenv("CONEF_BACKEND", "native")
     s = cb.PowerSGDState(None, start_powerSGD_iter=2, matrix_approximation_rank=rank, use_error_feedback=False,
                          warm_start=False)
-    b = FakeBucket(SHAPES, device=DEV, seed=3)
+    b = FakeBucket(shapes, device=DEV, seed=3)
     eng = PowerSGDEngine(s, b.buffer(), b.gradients(), group, "powersgd")
     return eng, b
 
 
+def _addressable(e, np_cols):
+    """TMA needs a 16-byte aligned start and a row pitch that is a multiple of 16 bytes - of the
+    matrix itself, or of its folded view (fold rows read as one; needs n % fold == 0 and
+    fold * r accumulator columns)."""
+    import math
+    fold = 4 // math.gcd(e.m, 4)
+    folded = fold > 1 and e.n % fold == 0 and fold * e.r <= np_cols
+    return e.g_off % 4 == 0 and (e.m % 4 == 0 or folded)
+
+
+@pytest.mark.parametrize("shapes", ["aligned", "folded"])
 @pytest.mark.parametrize("rank", [4, 8, 20])
-def test_tc_p_and_q_tiles_match_matmul(single_rank_group, monkeypatch, rank):
-    eng, b = _engine(rank, monkeypatch, single_rank_group)
+def test_tc_p_and_q_tiles_match_matmul(single_rank_group, monkeypatch, rank, shapes):
+    eng, b = _engine(rank, monkeypatch, single_rank_group, SHAPE_SETS[shapes])
+    assert eng.tc_ok.tolist() == [_addressable(e, eng.np_cols) for e in eng.plan.mats]
+    if shapes == "folded" and rank == 20:
+        assert not any(eng.tc_ok)          # fold * r does not fit the accumulator: everything stays SIMT
+        return
     assert eng.use_tc, "tensor-core path should be available on sm_100"
-    # TMA needs a 16-byte aligned start and a row pitch that is a multiple of 16 bytes
-    assert eng.tc_ok.tolist() == [e.g_off % 4 == 0 and e.m % 4 == 0 for e in eng.plan.mats]
     assert any(eng.tc_ok)
+    if shapes == "folded" and rank == 4:
+        assert [int(r["fold"]) for r in eng.mats_host] == [2, 4, 2, 2, 2, 1]
     plan = eng.plan
     buf = b.buffer()
     st = native.stream_ptr(buf.device)
@@ -76,7 +96,10 @@ def test_tc_p_and_q_tiles_match_matmul(single_rank_group, monkeypatch, rank):
     dict(matrix_approximation_rank=4, use_error_feedback=True),
     dict(matrix_approximation_rank=4, use_error_feedback=True, use_error_compression=True, sketch_size=0.1),
 ], ids=["ef", "conef"])
-def test_hook_with_tensorcore_path_matches_cpu(single_rank_group, monkeypatch, kw):
+@pytest.mark.parametrize("shapes", ["aligned", "folded"])
+def test_hook_with_tensorcore_path_matches_cpu(single_rank_group, monkeypatch, kw, shapes):
+    SHAPES = SHAPE_SETS[shapes]
+
     def mk(device):
         s = cb.PowerSGDState(None, start_powerSGD_iter=2, **kw)
         s.iter = 2
