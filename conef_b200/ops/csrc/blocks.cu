@@ -200,7 +200,7 @@ k_randblock_gather_flat(const ConefBlk* __restrict__ blks, const int2* __restric
 // load in flight per thread and ran eight times slower.
 constexpr int RB_MAX_ROWS = 8;
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)      // 64 registers: four CTAs of 37 KB per SM
 k_randblock_gather_sketch(const ConefBlk* __restrict__ blks, const int2* __restrict__ tiles, int rows_per_cta,
                           float* __restrict__ bucket, float* __restrict__ staging, float gather_scale,
                           float* __restrict__ sketch, const int32_t* __restrict__ tables,
@@ -308,6 +308,8 @@ extern "C" int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles
     SG.tile_ctas = ntiles;
     if (ntiles + seg_ctas == 0) return 0;
     CONEF_CUDA(cudaFuncSetAttribute(k_randblock_gather_sketch, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    CONEF_CUDA(cudaFuncSetAttribute(k_randblock_gather_sketch, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                    (int)cudaSharedmemCarveoutMaxShared));
     k_randblock_gather_sketch<<<ntiles + seg_ctas, 256, smem_bytes, stream>>>(
         blks, tiles, rows_per_cta, bucket, staging, gather_scale, sketch, tables, counts, alpha, beta, SG, pub);
   } else {

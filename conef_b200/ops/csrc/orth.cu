@@ -604,27 +604,80 @@ extern "C" int conef_orthogonalize_packed(const ConefMat* mats, const int2* tile
 
 // ---------------------------------------------------------------------------
 // Corrections of the low-rank error store.
+//
+// k_corr_reduce: C = L^T Rm over the chunk's rows.  The rows come into shared memory in sub-chunks
+// with coalesced loads first: summing straight from global memory leaves one load in flight per
+// thread (the loop over rows is a chain of dependent-latency iterations) and took 70-130 us per
+// launch on a Transformer-sized bucket.
+constexpr int CR_SUB = 128;                       // rows per sub-chunk
 __global__ void __launch_bounds__(OC_THREADS)
 k_corr_reduce(const ConefCorr* __restrict__ table, const int2* __restrict__ tiles, const float* __restrict__ L0b,
               const float* __restrict__ R0b, const float* __restrict__ L1b, const float* __restrict__ R1b,
               float* __restrict__ cbuf) {
-  __shared__ float Csm[GRAM_STRIDE];
-  __shared__ float scratch[OC_THREADS];
+  __shared__ float Ls[CR_SUB * OC_MAXR];
+  __shared__ float Rs[CR_SUB * OC_MAXR];
+  __shared__ float part[OC_THREADS / 32][256];
   const int2 t = tiles[blockIdx.x];
   const ConefCorr K = table[t.x];
   const int row0 = t.y * OC_ROWS;
   const int rows = min(OC_ROWS, K.rows_l - row0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int term = 0; term < K.nterms; ++term) {
     const int c2 = K.c2[term], c1 = K.c1;
+    const int pairs = c1 * c2;
     const float* L = (term ? L1b : L0b) + K.l_off[term] + (size_t)row0 * c2;
     const float* Rm = (term ? R1b : R0b) + K.r_off[term] + (size_t)row0 * c1;
-    __syncthreads();
-    pair_reduce(L, Rm, rows, c2, c1, Csm, scratch);
     float* c = cbuf + ((size_t)t.x * 2 + term) * GRAM_STRIDE;
-    for (int i = threadIdx.x; i < c1 * c2; i += OC_THREADS) atomicAdd(c + i, Csm[i]);
+    // every warp owns a slice of each sub-chunk's rows; lanes own pairs (a, b) = (pr / c1, pr % c1)
+    float acc[8];                                  // pairs handled by this lane: pr = lane + 32 u (pairs <= 256)
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[u] = 0.f;
+    for (int s0 = 0; s0 < rows; s0 += CR_SUB) {
+      const int sub = min(CR_SUB, rows - s0);
+      __syncthreads();
+      for (int i = threadIdx.x; i < sub * c2; i += OC_THREADS) Ls[i] = L[(size_t)s0 * c2 + i];
+      for (int i = threadIdx.x; i < sub * c1; i += OC_THREADS) Rs[i] = Rm[(size_t)s0 * c1 + i];
+      __syncthreads();
+      if (pairs <= 256) {
+        const int per = (sub + (OC_THREADS / 32) - 1) / (OC_THREADS / 32);
+        const int i0 = warp * per, i1 = min(sub, i0 + per);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int pr = lane + 32 * u;
+          if (pr < pairs) {
+            const int a = pr / c1, b = pr - a * c1;
+            float v = acc[u];
+            for (int i = i0; i < i1; ++i) v = fmaf(Ls[i * c2 + a], Rs[i * c1 + b], v);
+            acc[u] = v;
+          }
+        }
+      } else {                                     // ranks above 16: every thread its pairs over all rows
+        for (int pr = threadIdx.x; pr < pairs; pr += OC_THREADS) {
+          const int a = pr / c1, b = pr - a * c1;
+          float v = 0.f;
+          for (int i = 0; i < sub; ++i) v = fmaf(Ls[i * c2 + a], Rs[i * c1 + b], v);
+          atomicAdd(c + pr, v);
+        }
+      }
+    }
+    if (pairs <= 256) {
+      __syncthreads();
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (lane + 32 * u < pairs) part[warp][lane + 32 * u] = acc[u];
+      __syncthreads();
+      if ((int)threadIdx.x < pairs) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < OC_THREADS / 32; ++w) v += part[w][threadIdx.x];
+        atomicAdd(c + threadIdx.x, v);
+      }
+    }
   }
 }
 
+// k_corr_apply: T += sum_t coef_t X_t C_t.  A thread owns whole rows (its X row in registers, the small
+// C matrices in shared memory), so every row is one pass of wide loads and stores.
 __global__ void __launch_bounds__(OC_THREADS)
 k_corr_apply(const ConefCorr* __restrict__ table, const int2* __restrict__ tiles, float* __restrict__ Tb,
              const float* __restrict__ X0b, const float* __restrict__ X1b, const float* __restrict__ cbuf,
@@ -641,17 +694,25 @@ k_corr_apply(const ConefCorr* __restrict__ table, const int2* __restrict__ tiles
   const int row0 = t.y * OC_ROWS;
   const int rows = min(OC_ROWS, K.rows_t - row0);
   float* T = Tb + K.t_off + (size_t)row0 * c1;
-  for (int e = threadIdx.x; e < rows * c1; e += OC_THREADS) {
-    const int i = e / c1, b = e - i * c1;
-    float add = 0.f;
+  for (int i = threadIdx.x; i < rows; i += OC_THREADS) {
+    float out[OC_MAXR];
+#pragma unroll
+    for (int b = 0; b < OC_MAXR; ++b) out[b] = 0.f;
     for (int term = 0; term < K.nterms; ++term) {
       const int c2 = K.c2[term];
+      const float coef = term ? coef1 : coef0;
       const float* X = (term ? X1b : X0b) + K.x_off[term] + (size_t)(row0 + i) * c2;
-      float acc = 0.f;
-      for (int a = 0; a < c2; ++a) acc = fmaf(X[a], Csm[term][a * c1 + b], acc);
-      add += (term ? coef1 : coef0) * acc;
+      for (int a = 0; a < c2; ++a) {
+        const float xa = coef * X[a];
+#pragma unroll
+        for (int b = 0; b < OC_MAXR; ++b)
+          if (b < c1) out[b] = fmaf(xa, Csm[term][a * c1 + b], out[b]);
+      }
     }
-    T[e] += add;
+    float* trow = T + (size_t)i * c1;
+#pragma unroll
+    for (int b = 0; b < OC_MAXR; ++b)
+      if (b < c1) trow[b] += out[b];
   }
 }
 

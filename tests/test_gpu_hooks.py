@@ -353,8 +353,9 @@ def test_fused_pipeline_matches_the_long_form(single_rank_group, monkeypatch, kw
     a, eng_a, sa = run("1")
     b, eng_b, sb = run("0")
     assert eng_a.fused and not eng_b.fused
-    # ten launches, plus one SIMT kernel per product for the matrices TMA cannot address
-    assert eng_a.exec_plan.launched <= 12 < eng_b.exec_plan.launched
+    # six to ten launches, plus one SIMT kernel per product for the matrices TMA cannot address; the long form
+    # adds its helper launches (clears, packing, projection, segment copies) to that
+    assert eng_a.exec_plan.launched <= 12 and eng_a.exec_plan.launched < eng_b.exec_plan.launched
     for x, y in zip(a, b):
         assert (x - y).norm() <= 2e-3 * y.norm()
     if kw.get("warm_start", True):      # a cold start draws Q with Philox on the device, the PyTorch path on the CPU
