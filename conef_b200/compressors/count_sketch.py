@@ -39,7 +39,7 @@ def default_device() -> torch.device:
 def tables_for(device, D: int, W: int, a: int, b: int, sign_offset=ref.SIGN_OFFSETS[0]):
     """(idx int64, sign fp32, packed int32, counts int32) on ``device``, cached."""
     device = torch.device(device)
-    key = (device.type, device.index, D, W, a, b, tuple(sign_offset))
+    key = (device.type, device.index, D, W, a, b, tuple(sign_offset), ref.hash_layout())
     hit = _TABLE_CACHE.get(key)
     if hit is not None:
         return hit
@@ -49,6 +49,17 @@ def tables_for(device, D: int, W: int, a: int, b: int, sign_offset=ref.SIGN_OFFS
     out = (idx.to(device), sign.to(device), packed.to(device), counts.to(device))
     _TABLE_CACHE[key] = out
     return out
+
+
+def block_csr_for(device, D: int, W: int, a: int, b: int, sign_offset=ref.SIGN_OFFSETS[0]):
+    """The hash of ``(D, W)`` regrouped by cell block (``ops.reference.block_csr``) as an int32 tensor on
+    ``device``, cached; ``None`` when this (D, W) uses the per-element hash."""
+    device = torch.device(device)
+    key = ("csr", device.type, device.index, D, W, a, b, tuple(sign_offset), ref.hash_layout())
+    if key not in _TABLE_CACHE:
+        csr = ref.block_csr(D, W, a, b, sign_offset)
+        _TABLE_CACHE[key] = None if csr is None else torch.from_numpy(csr.copy()).to(device)
+    return _TABLE_CACHE[key]
 
 
 class DenseCS:

@@ -48,6 +48,30 @@ __host__ __device__ __forceinline__ int conef_hash(int value, int range, int a, 
   return (int)(h % (uint32_t)range);
 }
 
+// Cell of column j.  layout 0: the reference's per-element hash.  layout 1 (sketch rows of at least
+// CONEF_BLOCK_MIN_WIDTH cells): columns are hashed in aligned groups of 32 and the groups in windows of
+// nb = W / 32 consecutive groups.  Inside a window a pseudo-random permutation (the rank of
+// hash(g, 2^30) among the window's nb group numbers, ties by group number) gives every group a cell
+// block of its own, u_g; column 32 g + k goes to cell 32 u_g + (k xor x_g), x_g = hash(g, 32).  The 32
+// columns a warp handles together then fall into 32 different shared-memory banks, every cell block
+// receives exactly one group per window, and a warp that walks the groups of one cell block keeps
+// the block's 32 sums in registers.  O(nb) per call: meant for building tables.
+#define CONEF_BLOCK_MIN_WIDTH 64
+__host__ __device__ __forceinline__ int conef_cell(int j, int W, int a, int b, int layout) {
+  if (layout == 1 && W >= CONEF_BLOCK_MIN_WIDTH) {
+    const int nb = W >> 5, g = j >> 5;
+    const int g0 = (g / nb) * nb;
+    const int key = conef_hash(g, 1 << 30, a, b);
+    int u = 0;
+    for (int k = 0; k < nb; ++k) {
+      const int other = conef_hash(g0 + k, 1 << 30, a, b);
+      u += (other < key || (other == key && g0 + k < g)) ? 1 : 0;
+    }
+    return 32 * u + ((j & 31) ^ conef_hash(g, 32, a + 11, b + 13));
+  }
+  return conef_hash(j, W, a, b);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

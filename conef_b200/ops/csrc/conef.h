@@ -43,7 +43,9 @@ typedef struct ConefMat {
   // (f m rows) and ppk_fold_off the (n/f x f r) packing of P (ppk_off keeps the plain one).
   long long ppk_fold_off;
   int fold;
-  int pad_;
+  // Block layout of the hash (columns hashed in aligned groups of 32, see k_psgd_decompress_blk): offset,
+  // inside the hash-table arena, of the matrix's groups regrouped by cell block; -1: per-element hash.
+  int cb_off;
 } ConefMat;
 
 // One small-factor correction (see conef_lowrank_correct): offsets in floats into the four
@@ -117,8 +119,9 @@ int conef_version(void);
 int conef_mat_size(void);       // sizeof(ConefMat), so that a binding can verify its mirror of the layout
 
 // ---- count sketch (sketch.cu) ---------------------------------------------
+// layout 0: per-element hash of the reference; 1: block layout (see conef_cell in common.cuh)
 int conef_build_hash_table(int32_t* table, int32_t* counts, int D, int W,
-                           int a, int b, int sa, int sb, cudaStream_t stream);
+                           int a, int b, int sa, int sb, int layout, cudaStream_t stream);
 int conef_sketch_query(float* mat, const void* cs, int cs_is_half, const int32_t* table,
                        int N, int D, int W, float alpha, cudaStream_t stream);
 int conef_sketch_update(const float* vec, void* cs, int cs_is_half, const int32_t* table,
@@ -157,7 +160,9 @@ int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles, const floa
 // (alpha * unsketch(S) or the dense buffer); the residual M - M_hat goes to the error
 // store selected by ef_mode (dense buffer, or count sketch with decay beta).
 // smem_bytes = rows_per_cta * max W * 4 in sketch mode, else 0.
-int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta,
+// In sketch mode the first nblk_tiles tiles belong to matrices whose hash has the block layout
+// (cb_off >= 0): they run on the atomics-free kernel that walks the columns cell block by cell block.
+int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int nblk_tiles, int rows_per_cta,
                           float* bucket, const float* P, const float* Q, float q_scale,
                           float* sketch, const int32_t* tables, const int32_t* counts,
                           float* dense_err, float alpha, float beta, int ef_mode, int max_rank,
@@ -327,7 +332,7 @@ int conef_lamb_step(const ConefLambTensor* tensors, int ntensors, const int2* ch
                     cudaStream_t stream);
 
 // ---- host implementations (cpu_ops.cu) --------------------------------------
-void conef_cpu_hash_table(int32_t* table, int32_t* counts, int D, int W, int a, int b, int sa, int sb);
+void conef_cpu_hash_table(int32_t* table, int32_t* counts, int D, int W, int a, int b, int sa, int sb, int layout);
 void conef_cpu_sketch_query(float* mat, const float* cs, const int32_t* table, int N, int D, int W, float alpha);
 void conef_cpu_sketch_update(const float* vec, float* cs, const int32_t* table, const int32_t* counts,
                              int N, int D, int W, float beta);

@@ -8,10 +8,11 @@
 #include <vector>
 #include "common.cuh"
 
-extern "C" void conef_cpu_hash_table(int32_t* table, int32_t* counts, int D, int W, int a, int b, int sa, int sb) {
+extern "C" void conef_cpu_hash_table(int32_t* table, int32_t* counts, int D, int W, int a, int b, int sa, int sb,
+                                     int layout) {
   if (counts) memset(counts, 0, sizeof(int32_t) * (size_t)W);
   for (int j = 0; j < D; ++j) {
-    const int h = conef_hash(j, W, a, b);
+    const int h = conef_cell(j, W, a, b, layout);
     const int sign_bit = conef_hash(j, W, a + sa, b + sb) & 1;
     table[j] = (int32_t)((uint32_t)h | ((uint32_t)sign_bit << 31));
     if (counts) counts[h] += 1;

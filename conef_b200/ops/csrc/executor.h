@@ -46,7 +46,7 @@ typedef struct ConefPsgdPlan {
   const void* tc_maps;
   ConefTileList tc_p, simt_p;
   ConefQSet qset_all, qset_grad, qset_err;
-  ConefTileList d_tiles;  int d_rows, pad1;  size_t d_smem;
+  ConefTileList d_tiles;  int d_rows, d_nblk;  size_t d_smem;      // d_nblk: leading tiles on the block layout
   ConefTileList orth_q, orth_p, orth_u, chunks_n, chunks_m;
   float* gram;
   float* cbuf;

@@ -17,6 +17,7 @@
 //   :531  torch.matmul(M^T, P) -> k_psgd_q
 //   :550  torch.matmul(P, Q^T), :558/:563 residual, CountSketch.py:27-67 update
 //                              -> k_psgd_decompress (one pass, residual kept in registers)
+#include <stdlib.h>
 #include "common.cuh"
 
 constexpr int P_WARPS = 8;       // warps per CTA in k_psgd_p
@@ -335,8 +336,167 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
   }
 }
 
+// Count-sketch decompress over the block layout of the hash (conef_cell, layout 1: columns hashed in
+// aligned groups of 32, one group per cell block and window of nb = W / 32 groups).  The table arena
+// holds, per matrix, S x nb two-word records, window-major: {g | x_g << 27 (0x7ffffff: none), sign bits
+// of the group's 32 columns} = the group cell block c receives from window s.
+// Work unit of a warp: (block of RB rows, cell block c).  The warp walks the S groups of its cell block;
+// lane l handles column 32 g + (l xor x_g), whose cell is 32 c + l for every one of them, so the 32 sums
+// of the cell block stay in the lanes' registers: no atomics, no shared-memory accumulator, all warps
+// do the same amount of work, and every access of a warp is one full 128-byte line (G row segment,
+// M_hat row segment, sketch cells).  A CTA's eight warps take neighbouring cell blocks of the same
+// rows and therefore read inside the same window of the row at about the same time.  The records of
+// the cell block are fetched up front (one per lane) and handed round by shuffles, so the addresses
+// of later groups never wait for a load.  G travels through a per-warp ring in shared memory filled by
+// cp.async (D_STAGES - 1 groups, i.e. 3 KB per warp, in flight at no cost in registers; the kernel is
+// bound by the latency of its loads, not by any pipe); the Q row of the next group is in flight in
+// registers.  Tile = (matrix, chunk of eight consecutive units of that matrix).
+constexpr int D_WARPS = D_THREADS / 32;
+constexpr int D_STAGES = 4;      // groups of G in flight per warp (a ring of RB x 128 bytes per stage)
+
+// 4-byte cp.async into shared memory at `dst + OFF` (a shared-space address plus an immediate).
+template <int OFF>
+__device__ __forceinline__ void cp_async_f32(uint32_t dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0+%2], [%1], 4;" ::"r"(dst), "l"(gmem_src), "n"(OFF) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+template <int OFF>
+__device__ __forceinline__ float lds_f32(uint32_t src) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(src), "n"(OFF) : "memory");
+  return v;
+}
+
+// The walk of one unit.  FULL: the row block has all RB rows (no per-row predicates).  The kernel issues
+// few bytes per instruction (4 per lane), so the instruction count per row is what bounds it once the
+// loads are deep enough in flight: row addresses are one multiply-add on a 32-bit byte stride, shared
+// memory is addressed with immediates off one register per stage.
+template <int RP, int RB, bool FULL>
+__device__ __forceinline__ void dblk_walk(const int2* __restrict__ recs, int nb, int S, int m, int r, int rows,
+                                          float* __restrict__ g0, const float* __restrict__ q0, float q_scale,
+                                          bool qvec, const float* __restrict__ ps, uint32_t ring, int lane,
+                                          float (&acc)[RB]) {
+  const unsigned pitch = (unsigned)m * 4u;      // bytes between rows
+  auto row_ptr = [&](float* base, int ii) {
+    return reinterpret_cast<float*>(reinterpret_cast<char*>(base) + (unsigned long long)pitch * (unsigned)ii);
+  };
+  for (int s0 = 0; s0 < S; s0 += 32) {
+    int2 mine = make_int2(0x7ffffff, 0);
+    if (s0 + lane < S) mine = __ldg(recs + (size_t)(s0 + lane) * nb);
+    const int cnt = min(32, S - s0);
+    // column of this lane in the i-th group of the chunk (m: none); every lane calls it together
+    auto column = [&](int i) {
+      const int rx = __shfl_sync(0xffffffffu, mine.x, i & 31);
+      const int g = rx & 0x7ffffff;
+      return (i < cnt && g != 0x7ffffff) ? (g << 5) + (lane ^ (int)((uint32_t)rx >> 27)) : m;
+    };
+    auto issue = [&](int i) {
+      const int cl = column(i);
+      if (cl < m) {
+        float* src = g0 + cl;
+        const uint32_t dst = ring + (uint32_t)(i & (D_STAGES - 1)) * (RB * 128);
+#pragma unroll
+        for (int ii = 0; ii < RB; ++ii)
+          if (FULL || ii < rows) cp_async_f32<0>(dst + ii * 128, row_ptr(src, ii));
+      }
+      cp_async_commit();
+    };
+#pragma unroll
+    for (int k = 0; k < D_STAGES - 1; ++k) issue(k);
+    float qv[RP];
+    load_q_row<RP>(q0 + (size_t)min(column(0), m - 1) * r, r, q_scale, qvec, qv);
+    for (int i = 0; i < cnt; ++i) {
+      issue(i + D_STAGES - 1);
+      float qn[RP];
+      load_q_row<RP>(q0 + (size_t)min(column(i + 1), m - 1) * r, r, q_scale, qvec, qn);
+      const int col = column(i);
+      const uint32_t sbits = (uint32_t)__shfl_sync(0xffffffffu, mine.y, i & 31);
+      cp_async_wait<D_STAGES - 1>();      // the copies of group i have landed
+      if (col < m) {
+        const float sgn = ((sbits >> (col & 31)) & 1u) ? 1.f : -1.f;
+        float* dstp = g0 + col;
+        const uint32_t src = ring + (uint32_t)(i & (D_STAGES - 1)) * (RB * 128);
+#pragma unroll
+        for (int ii = 0; ii < RB; ++ii) {
+          if (FULL || ii < rows) {
+            float mh = 0.f;
+#pragma unroll
+            for (int cc = 0; cc < RP; cc += 4) {
+              const float4 pv = *reinterpret_cast<const float4*>(ps + ii * RP + cc);
+              mh = fmaf(pv.x, qv[cc], mh);
+              mh = fmaf(pv.y, qv[cc + 1], mh);
+              mh = fmaf(pv.z, qv[cc + 2], mh);
+              mh = fmaf(pv.w, qv[cc + 3], mh);
+            }
+            const float v = lds_f32<0>(src + ii * 128);
+            *row_ptr(dstp, ii) = mh;
+            acc[ii] = fmaf(sgn, v - mh, acc[ii]);
+          }
+        }
+      }
+#pragma unroll
+      for (int cc = 0; cc < RP; ++cc) qv[cc] = qn[cc];
+    }
+    cp_async_wait<0>();
+  }
+}
+
+template <int RP, int RB, int MINB>
+__global__ void __launch_bounds__(D_THREADS, RP <= 8 ? MINB : 1)
+k_psgd_decompress_blk(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles,
+                      float* __restrict__ bucket, const float* __restrict__ P, const float* __restrict__ Q,
+                      float q_scale, float* __restrict__ sketch, const int32_t* __restrict__ tables,
+                      const int32_t* __restrict__ counts, float alpha, float beta) {
+  static_assert((D_STAGES & (D_STAGES - 1)) == 0, "the ring is indexed with a mask");
+  __shared__ __align__(16) float ps_all[D_WARPS][RB * RP];
+  __shared__ float ring_all[D_WARPS][D_STAGES][RB][32];
+  const int2 t = tiles[blockIdx.x];
+  const ConefMat M = mats[t.x];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int m = M.m, r = M.r, Wp = M.Wp, nb = M.W >> 5;
+  const int unit = t.y * D_WARPS + warp;
+  if (unit >= ((M.n + RB - 1) / RB) * nb) return;      // nothing below synchronises the CTA
+  const int rb = unit / nb, c = unit - rb * nb;
+  const int row0 = rb * RB;
+  const int rows = min(RB, M.n - row0);
+  float* ps = ps_all[warp];
+  {
+    const float* p = P + M.p_off + (size_t)row0 * r;
+    for (int i = lane; i < RB * RP; i += 32) {
+      const int ii = i / RP, cc = i - ii * RP;
+      ps[i] = (cc < r && ii < rows) ? p[(size_t)ii * r + cc] : 0.f;
+    }
+  }
+  __syncwarp();
+  const int S = (((m + 31) >> 5) + nb - 1) / nb;
+  const int2* recs = reinterpret_cast<const int2*>(tables + M.cb_off) + c;
+  float* g0 = bucket + M.g_off + (size_t)row0 * m;
+  const float* q0 = Q + M.q_off;
+  const bool qvec = (r & 3) == 0 && (reinterpret_cast<uintptr_t>(q0) & 15) == 0;
+  const int cell = (c << 5) + lane;
+  float* sc0 = sketch + M.sk_off + (size_t)row0 * Wp + cell;
+  const float f = 1.f + (alpha - (1.f - beta)) * (float)__ldg(counts + M.cnt_off + cell);
+  float so[RB], acc[RB];
+#pragma unroll
+  for (int ii = 0; ii < RB; ++ii) {
+    so[ii] = ii < rows ? sc0[(size_t)ii * Wp] : 0.f;      // in flight during the walk
+    acc[ii] = 0.f;
+  }
+  // a lane reads back only what it copied itself: the ring needs no barriers
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(&ring_all[warp][0][0][lane]);
+  if (rows == RB)
+    dblk_walk<RP, RB, true>(recs, nb, S, m, r, rows, g0, q0, q_scale, qvec, ps, ring, lane, acc);
+  else
+    dblk_walk<RP, RB, false>(recs, nb, S, m, r, rows, g0, q0, q_scale, qvec, ps, ring, lane, acc);
+#pragma unroll
+  for (int ii = 0; ii < RB; ++ii)
+    if (ii < rows) sc0[(size_t)ii * Wp] = fmaf(so[ii], f, acc[ii]);
+}
+
 template <int RP, int RB>
-static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket, const float* P,
+static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, float* bucket, const float* P,
                        const float* Q, float q_scale, float* sketch, const int32_t* tables,
                        const int32_t* counts, float* dense_err, float alpha, float beta, int ef_mode,
                        size_t smem, cudaStream_t stream) {
@@ -349,19 +509,34 @@ static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, floa
     CONEF_CUDA(cudaFuncSetAttribute(k_psgd_decompress<RP, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev >= 0 && dev < 64) configured[dev] = smem;
   }
-  k_psgd_decompress<RP, RB><<<ntiles, D_THREADS, smem, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables,
-                                                                counts, dense_err, alpha, beta, ef_mode);
-  CONEF_CHECK_LAUNCH("k_psgd_decompress");
+  if (nblk > 0) {
+    static int minb = -1;
+    if (minb < 0) { const char* e = getenv("CONEF_DBLK_MINB"); minb = e ? atoi(e) : 3; }
+    constexpr int RQ = RP < 4 ? 4 : RP;
+    if (minb == 2)
+      k_psgd_decompress_blk<RQ, RB, 2><<<nblk, D_THREADS, 0, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables, counts, alpha, beta);
+    else if (minb == 3)
+      k_psgd_decompress_blk<RQ, RB, 3><<<nblk, D_THREADS, 0, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables, counts, alpha, beta);
+    else
+      k_psgd_decompress_blk<RQ, RB, 4><<<nblk, D_THREADS, 0, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables, counts, alpha, beta);
+    CONEF_CHECK_LAUNCH("k_psgd_decompress_blk");
+  }
+  if (ntiles > nblk) {
+    k_psgd_decompress<RP, RB><<<ntiles - nblk, D_THREADS, smem, stream>>>(mats, tiles + nblk, bucket, P, Q, q_scale,
+                                                                       sketch, tables, counts, dense_err, alpha,
+                                                                       beta, ef_mode);
+    CONEF_CHECK_LAUNCH("k_psgd_decompress");
+  }
   return 0;
 }
 
 template <int RP>
-static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta, float* bucket,
+static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, int rows_per_cta, float* bucket,
                     const float* P, const float* Q, float q_scale, float* sketch, const int32_t* tables,
                     const int32_t* counts, float* dense_err, float alpha, float beta, int ef_mode, size_t smem,
                     cudaStream_t stream) {
 #define CONEF_D_CASE(RB)                                                                              \
-  case RB: return launch_d_rb<RP, RB>(mats, tiles, ntiles, bucket, P, Q, q_scale, sketch, tables, counts, \
+  case RB: return launch_d_rb<RP, RB>(mats, tiles, ntiles, nblk, bucket, P, Q, q_scale, sketch, tables, counts, \
                                       dense_err, alpha, beta, ef_mode, smem, stream)
   switch (rows_per_cta) {
     CONEF_D_CASE(8);
@@ -374,13 +549,15 @@ static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int row
   return 2;
 }
 
-extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int rows_per_cta,
+extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int nblk_tiles, int rows_per_cta,
                                      float* bucket, const float* P, const float* Q, float q_scale,
                                      float* sketch, const int32_t* tables, const int32_t* counts,
                                      float* dense_err, float alpha, float beta, int ef_mode, int max_rank,
                                      size_t smem_bytes, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
-  DISPATCH_RANK(max_rank, launch_d, mats, tiles, ntiles, rows_per_cta, bucket, P, Q, q_scale, sketch, tables,
+  if (ef_mode != CONEF_EF_SKETCH || nblk_tiles < 0) nblk_tiles = 0;
+  if (nblk_tiles > ntiles) nblk_tiles = ntiles;
+  DISPATCH_RANK(max_rank, launch_d, mats, tiles, ntiles, nblk_tiles, rows_per_cta, bucket, P, Q, q_scale, sketch, tables,
                 counts, dense_err, alpha, beta, ef_mode, smem_bytes, stream);
 }
 

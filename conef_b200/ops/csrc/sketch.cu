@@ -24,20 +24,20 @@ extern "C" int conef_version(void) { return 100; }
 
 // ---------------------------------------------------------------------------
 __global__ void k_hash_table(int32_t* __restrict__ table, int32_t* __restrict__ counts, int D, int W,
-                             int a, int b, int sa, int sb) {
+                             int a, int b, int sa, int sb, int layout) {
   int j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j >= D) return;
-  int h = conef_hash(j, W, a, b);
+  int h = conef_cell(j, W, a, b, layout);
   int sign_bit = conef_hash(j, W, a + sa, b + sb) & 1;
   table[j] = (int32_t)((uint32_t)h | ((uint32_t)sign_bit << 31));
   if (counts) atomicAdd(&counts[h], 1);
 }
 
 extern "C" int conef_build_hash_table(int32_t* table, int32_t* counts, int D, int W, int a, int b,
-                                      int sa, int sb, cudaStream_t stream) {
+                                      int sa, int sb, int layout, cudaStream_t stream) {
   if (D <= 0 || W <= 0) { conef_set_error("hash table: bad D=%d W=%d", D, W); return 1; }
   if (counts) CONEF_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t) * (size_t)W, stream));
-  k_hash_table<<<(D + 255) / 256, 256, 0, stream>>>(table, counts, D, W, a, b, sa, sb);
+  k_hash_table<<<(D + 255) / 256, 256, 0, stream>>>(table, counts, D, W, a, b, sa, sb, layout);
   CONEF_CHECK_LAUNCH("k_hash_table");
   return 0;
 }

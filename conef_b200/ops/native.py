@@ -31,7 +31,7 @@ MAT_DTYPE = np.dtype(
      ("n", "<i4"), ("m", "<i4"), ("r", "<i4"), ("W", "<i4"),
      ("tab_off", "<i4"), ("cnt_off", "<i4"), ("q_rows", "<i4"), ("q_atomic", "<i4"),
      ("src", "<i4"), ("Wp", "<i4"), ("qpk_off", "<i8"), ("ppk_off", "<i8"),
-     ("ppk_fold_off", "<i8"), ("fold", "<i4"), ("pad_", "<i4")], align=True)
+     ("ppk_fold_off", "<i8"), ("fold", "<i4"), ("cb_off", "<i4")], align=True)
 SEG_DTYPE = np.dtype([("src_off", "<i8"), ("dst_off", "<i8"), ("len", "<i8")], align=True)
 BLK_DTYPE = np.dtype(
     [("g_off", "<i8"), ("numel", "<i8"), ("start", "<i8"), ("block", "<i8"),
@@ -77,7 +77,7 @@ class PsgdPlan(C.Structure):
         ("staging", C.c_void_p), ("tc_maps", C.c_void_p),
         ("tc_p", TileList), ("simt_p", TileList),
         ("qset_all", QSet), ("qset_grad", QSet), ("qset_err", QSet),
-        ("d_tiles", TileList), ("d_rows", C.c_int), ("pad1", C.c_int), ("d_smem", C.c_size_t),
+        ("d_tiles", TileList), ("d_rows", C.c_int), ("d_nblk", C.c_int), ("d_smem", C.c_size_t),
         ("orth_q", TileList), ("orth_p", TileList), ("orth_u", TileList),
         ("chunks_n", TileList), ("chunks_m", TileList),
         ("gram", C.c_void_p), ("cbuf", C.c_void_p),
@@ -140,7 +140,7 @@ class RandblockPlan(C.Structure):
 
 _SIGNATURES = {
     "conef_version": ([], C.c_int),
-    "conef_build_hash_table": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp], C.c_int),
+    "conef_build_hash_table": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp], C.c_int),
     "conef_sketch_query": ([vp, vp, C.c_int, vp, C.c_int, C.c_int, C.c_int, C.c_float, vp], C.c_int),
     "conef_sketch_update": ([vp, vp, C.c_int, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, vp], C.c_int),
     "conef_sketch3_query": ([vp] * 7 + [C.c_int, C.c_int, C.c_int, C.c_float, vp], C.c_int),
@@ -151,7 +151,7 @@ _SIGNATURES = {
     "conef_orthogonalize_packed": ([vp, vp, C.c_int, C.c_int, C.c_int, vp, C.c_float, vp, vp, C.c_int, C.c_uint32,
                                     vp, c_ll, vp, C.c_int, vp, vp], C.c_int),
     "conef_pack_small": ([vp, C.c_int, C.c_int, vp, vp, C.c_int, vp], C.c_int),
-    "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
+    "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
                                C.c_float, C.c_int, C.c_int, C.c_size_t, vp], C.c_int),
     "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),
     "conef_lowrank_correct": ([vp, C.c_int, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_float, vp, vp, vp,
@@ -191,7 +191,7 @@ _SIGNATURES = {
     "conef_epoch_word": ([vp, C.c_uint32, C.c_int, vp], C.c_int),
     "conef_lamb_step": ([vp, C.c_int, vp, C.c_int, C.c_int, vp, C.c_float, C.c_float, C.c_float, C.c_float,
                          C.c_int, C.c_int, C.c_float, C.c_float, vp], C.c_int),
-    "conef_cpu_hash_table": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int], None),
+    "conef_cpu_hash_table": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int], None),
     "conef_cpu_sketch_query": ([vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float], None),
     "conef_cpu_sketch_update": ([vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float], None),
     "conef_cpu_gram_schmidt": ([vp, C.c_int, C.c_int, C.c_float], None),

@@ -16,8 +16,9 @@ Behavioural spec (paths are relative to the reference project):
 from __future__ import annotations
 
 import functools
+import os
 import math
-from typing import Tuple
+from typing import Optional, Tuple
 
 import numpy as np
 import torch
@@ -60,31 +61,117 @@ def hash32(value, rng: int, a: int, b: int) -> np.ndarray:
     return (h % np.int64(rng)).astype(np.int64)
 
 
+def hash_layout() -> str:
+    """``block`` (default) or ``universal`` (``CONEF_HASH=universal``): see :func:`_hash_table_cached`."""
+    return "universal" if os.environ.get("CONEF_HASH", "block").lower().startswith("u") else "block"
+
+
+BLOCK_MIN_WIDTH = 64      # sketch rows narrower than this keep the per-element hash
+
+
+def _hash_table_np(D: int, W: int, a: int, b: int, sa: int, sb: int, layout: Optional[str] = None):
+    return _hash_table_cached(D, W, a, b, sa, sb, layout or hash_layout())
+
+
+def _block_hash_np(D: int, W: int, a: int, b: int):
+    """Block layout: (cell block u_g, lane mask x_g) of every aligned group of 32 columns, and
+    ``order[s, c]`` = position inside window s of the group that goes to cell block c."""
+    nb, ng = W // 32, (D + 31) // 32
+    S = (ng + nb - 1) // nb
+    key = hash32(np.arange(S * nb, dtype=np.int64), 1 << 30, a, b).reshape(S, nb)
+    order = np.argsort(key, axis=1, kind="stable")
+    rank = np.empty_like(order)
+    rank[np.arange(S)[:, None], order] = np.arange(nb)[None, :]
+    u = rank.reshape(-1)[:ng]
+    x = hash32(np.arange(ng, dtype=np.int64), 32, a + 11, b + 13)
+    return u, x, order
+
+
 @functools.lru_cache(maxsize=512)
-def _hash_table_np(D: int, W: int, a: int, b: int, sa: int, sb: int):
+def _hash_table_cached(D: int, W: int, a: int, b: int, sa: int, sb: int, layout: str):
+    """Bucket and sign of every column.
+
+    ``universal``: h_j = hash(j, W), the reference's per-element hash (CountSketch.py:7-18,60-62), bit
+    for bit.
+
+    ``block``: columns are hashed in aligned groups of 32, and the groups in windows of
+    nb = W // 32 consecutive groups.  Inside window s a pseudo-random permutation (the ranks of
+    hash(g, 2**30) among the window's nb group numbers, the ones past the end of the row included)
+    sends every group to a cell block of its own, u_g; column 32 g + k goes to cell
+    32 u_g + (k xor x_g) with x_g = hash(g, 32).  Two columns of different windows share a cell with
+    probability 1 / (32 nb), columns of one window never do, and the signs stay per column: the
+    sketch is unbiased, with at most the per-element variance of the universal hash; up to 31 cells
+    at the end of a sketch row stay unused.  What it buys on the GPU: the 32 columns a warp handles
+    together land in 32 different shared-memory banks (a uniformly random cell costs about 3.5
+    serialised passes per warp-wide atomic); every cell block receives exactly one group per window,
+    so a warp that walks the groups of ONE cell block (:func:`block_csr`) keeps that block's 32 sums
+    in registers, with no atomics and no imbalance between warps; and the warps of a CTA, which
+    take neighbouring cell blocks, read inside the same window of 128 nb bytes per row at the same
+    time.  Rows narrower than ``BLOCK_MIN_WIDTH`` cells use ``universal``.
+    """
     cols = np.arange(D, dtype=np.int64)
-    idx = hash32(cols, W, a, b)
+    if layout == "block" and W >= BLOCK_MIN_WIDTH:
+        u, x, _ = _block_hash_np(D, W, a, b)
+        idx = 32 * u[cols >> 5] + ((cols & 31) ^ x[cols >> 5])
+    else:
+        idx = hash32(cols, W, a, b)
     sign_bit = hash32(cols, W, a + sa, b + sb) & 1
     sign = np.where(sign_bit == 1, 1.0, -1.0).astype(np.float32)
     return idx, sign
 
 
 def hash_table(D: int, W: int, a: int = DEFAULT_A, b: int = DEFAULT_B,
-               sign_offset: Tuple[int, int] = SIGN_OFFSETS[0], device="cpu"):
+               sign_offset: Tuple[int, int] = SIGN_OFFSETS[0], device="cpu", layout: Optional[str] = None):
     """Column table ``(bucket index h_j, sign s_j)`` for ``j in [0, D)``.
 
     The hash depends only on the column, so one table serves every row of a
     matrix: sketch = M @ H, unsketch = S @ H^T with H in {0, +1, -1}^{D x W}.
     """
-    idx, sign = _hash_table_np(int(D), int(W), int(a), int(b), int(sign_offset[0]), int(sign_offset[1]))
+    idx, sign = _hash_table_np(int(D), int(W), int(a), int(b), int(sign_offset[0]), int(sign_offset[1]), layout)
     return (torch.from_numpy(idx).to(device), torch.from_numpy(sign).to(device))
 
 
-def packed_hash_table(D: int, W: int, a: int, b: int, sign_offset=SIGN_OFFSETS[0]) -> np.ndarray:
+def packed_hash_table(D: int, W: int, a: int, b: int, sign_offset=SIGN_OFFSETS[0],
+                      layout: Optional[str] = None) -> np.ndarray:
     """``h_j | (sign_bit_j << 31)`` as int32 — the layout the CUDA kernels read."""
-    idx, sign = _hash_table_np(int(D), int(W), int(a), int(b), int(sign_offset[0]), int(sign_offset[1]))
+    idx, sign = _hash_table_np(int(D), int(W), int(a), int(b), int(sign_offset[0]), int(sign_offset[1]), layout)
     packed = idx.astype(np.uint32) | ((sign > 0).astype(np.uint32) << np.uint32(31))
     return packed.view(np.int32)
+
+
+NO_GROUP = 0x7FFFFFF
+
+
+@functools.lru_cache(maxsize=512)
+def _block_csr_cached(D: int, W: int, a: int, b: int, sa: int, sb: int):
+    u, x, order = _block_hash_np(D, W, a, b)
+    _, sign = _hash_table_cached(D, W, a, b, sa, sb, "block")
+    nb, ng = W // 32, (D + 31) // 32
+    S = order.shape[0]
+    bits = np.zeros(ng * 32, dtype=np.uint32)
+    bits[:D] = (sign > 0).astype(np.uint32)
+    words = (bits.reshape(ng, 32) << np.arange(32, dtype=np.uint32)).sum(axis=1, dtype=np.uint64).astype(np.uint32)
+    g = (np.arange(S, dtype=np.int64)[:, None] * nb + order)          # (S, nb): group of cell block c in window s
+    real = g < ng
+    gc = np.where(real, g, 0)
+    rec = np.empty((S, nb, 2), dtype=np.uint32)
+    rec[..., 0] = np.where(real, gc.astype(np.uint32) | (x[gc].astype(np.uint32) << np.uint32(27)), np.uint32(NO_GROUP))
+    rec[..., 1] = np.where(real, words[gc], np.uint32(0))
+    return rec.reshape(-1).view(np.int32)
+
+
+def block_csr(D: int, W: int, a: int, b: int, sign_offset=SIGN_OFFSETS[0]) -> Optional[np.ndarray]:
+    """The block layout regrouped by cell block, as one int32 array, or ``None`` when the layout of
+    this (D, W) is not ``block``.
+
+    ``S = ceil(ceil(D / 32) / nb)`` windows times ``nb = W // 32`` cell blocks two-word records,
+    window-major: record ``s * nb + c`` names the group that cell block c receives from window s as
+    ``g | x_g << 27`` (``NO_GROUP``: none, past the end of the row; so D < 2**32) and the 32 sign bits
+    of the group's columns (bit k: column 32 g + k has sign +1).
+    """
+    if hash_layout() != "block" or W < BLOCK_MIN_WIDTH:
+        return None
+    return _block_csr_cached(int(D), int(W), int(a), int(b), int(sign_offset[0]), int(sign_offset[1]))
 
 
 def derive_hash_seeds(seed: int, rows: int):

@@ -31,6 +31,7 @@ import torch
 import torch.distributed as dist
 
 from ..compressors import DenseCS, Quant8Error, tables_for
+from ..compressors.count_sketch import block_csr_for
 from ..compressors.count_sketch import HalfDenseCS
 from ..ops import native
 from ..ops import reference as ref
@@ -195,6 +196,7 @@ class PowerSGDEngine(_EngineBase):
         self.nm = nm
         nrec = nm * (2 if (self.fused_err or self.lowrank) else 1)
         mats = np.zeros(nrec, dtype=native.MAT_DTYPE)
+        mats["cb_off"] = -1
         sk_off = tab_off = cnt_off = z_off = u_off = 0
         err_rank = int(getattr(state, "error_rank", None) or state.matrix_approximation_rank) if self.lowrank else 0
         table_chunks, count_chunks = [], []
@@ -214,12 +216,22 @@ class PowerSGDEngine(_EngineBase):
                 key = (e.m, W)
                 if key not in table_index:
                     _, _, packed, counts = tables_for(dev, e.m, W, seeds[0], seeds[1])
-                    table_index[key] = (tab_off, cnt_off)
                     table_chunks.append(packed)
                     count_chunks.append(counts)
-                    tab_off += e.m
+                    cb_off = -1
+                    # block layout of the hash: the groups regrouped by cell block follow the column
+                    # table in the same arena, on an 8-byte boundary (two-word records)
+                    csr = block_csr_for(dev, e.m, W, seeds[0], seeds[1]) if self.ef_mode == native.EF_SKETCH else None
+                    if csr is not None:
+                        pad = (tab_off + e.m) & 1
+                        if pad:
+                            table_chunks.append(torch.zeros(1, dtype=torch.int32, device=dev))
+                        cb_off = tab_off + e.m + pad
+                        table_chunks.append(csr)
+                    table_index[key] = (tab_off, cnt_off, cb_off)
+                    tab_off = sum(int(c.numel()) for c in table_chunks)
                     cnt_off += W
-                rec["tab_off"], rec["cnt_off"] = table_index[key]
+                rec["tab_off"], rec["cnt_off"], rec["cb_off"] = table_index[key]
                 # record nm + k: the (n x W) sketch as a matrix; Z / Y (W x r) live behind the Q blocks
                 err = mats[nm + k]
                 # (its pad columns stay zero and meet zero rows of Z / produce unused rows of Y)
@@ -328,7 +340,14 @@ class PowerSGDEngine(_EngineBase):
         if os.environ.get("CONEF_D_ROWS"):
             self.d_rows = int(os.environ["CONEF_D_ROWS"])
         self.d_smem = self.d_rows * maxW * 4
-        d_tiles = [(k, rb) for k, e in enumerate(plan.mats) for rb in range(math.ceil(e.n / self.d_rows))]
+        # matrices on the block layout of the hash first: they run on the atomics-free kernel, whose tile
+        # is a chunk of eight (row block, cell block) units, one per warp; the others by row block
+        on_blocks = [int(mats[k]["cb_off"]) >= 0 for k in range(nm)]
+        d_tiles = [(k, ch) for k, e in enumerate(plan.mats) if on_blocks[k]
+                   for ch in range(math.ceil(math.ceil(e.n / self.d_rows) * (self.widths[k] // 32) / 8))]
+        self.d_nblk = len(d_tiles)
+        d_tiles += [(k, rb) for k, e in enumerate(plan.mats) if not on_blocks[k]
+                    for rb in range(math.ceil(e.n / self.d_rows))]
         self.d_tiles = self._tiles(d_tiles)
         self.n_d_tiles = len(d_tiles)
         segs = np.zeros(len(plan.segs), dtype=native.SEG_DTYPE)
@@ -637,6 +656,7 @@ class PowerSGDEngine(_EngineBase):
         P.tc_p, P.simt_p = tl(self.tc_p_tiles, self.n_tc_p), tl(self.p_tiles, self.n_p_tiles)
         P.qset_all, P.qset_grad, P.qset_err = qset("all"), qset("grad"), qset("err")
         P.d_tiles, P.d_rows, P.d_smem = tl(self.d_tiles, self.n_d_tiles), self.d_rows, self.d_smem
+        P.d_nblk = self.d_nblk
         P.orth_q, P.orth_p = tl(*self.orth_tiles[(1, "grad")]), tl(*self.orth_tiles[(0, "grad")])
         P.orth_u = tl(*self.orth_tiles[(0, "err")])
         P.chunks_n, P.chunks_m = tl(*self.chunks_n), tl(*self.chunks_m)

@@ -22,15 +22,16 @@ def test_native_library_is_loaded():
     assert native.lib().conef_version() >= 100
 
 
+@pytest.mark.parametrize("layout", ["universal", "block"])
 @pytest.mark.parametrize("D,W", [(5760, 576), (650, 65), (33, 1), (1024, 409)])
-def test_hash_table_kernel(D, W):
+def test_hash_table_kernel(D, W, layout):
     tab = torch.zeros(D, dtype=torch.int32, device=DEV)
     cnt = torch.zeros(W, dtype=torch.int32, device=DEV)
     native.check(native.lib().conef_build_hash_table(tab.data_ptr(), cnt.data_ptr(), D, W, ref.DEFAULT_A,
-                                                     ref.DEFAULT_B, 2, 3, _st()))
-    want = ref.packed_hash_table(D, W, ref.DEFAULT_A, ref.DEFAULT_B)
+                                                     ref.DEFAULT_B, 2, 3, int(layout == "block"), _st()))
+    want = ref.packed_hash_table(D, W, ref.DEFAULT_A, ref.DEFAULT_B, layout=layout)
     assert np.array_equal(tab.cpu().numpy(), want)
-    idx, _ = ref.hash_table(D, W)
+    idx, _ = ref.hash_table(D, W, layout=layout)
     assert np.array_equal(cnt.cpu().numpy(), np.bincount(idx.numpy(), minlength=W))
 
 

@@ -41,13 +41,15 @@ def test_sign_split_reference_config():
 
 
 @pytest.mark.skipif(not native.available(), reason="native library not built")
-def test_cpp_hash_table_matches_python():
+@pytest.mark.parametrize("layout", ["universal", "block"])
+def test_cpp_hash_table_matches_python(layout):
     D, W = 1000, 77
     tab = np.zeros(D, dtype=np.int32)
     cnt = np.zeros(W, dtype=np.int32)
-    native.lib().conef_cpu_hash_table(tab.ctypes.data, cnt.ctypes.data, D, W, ref.DEFAULT_A, ref.DEFAULT_B, 2, 3)
-    assert np.array_equal(tab, ref.packed_hash_table(D, W, ref.DEFAULT_A, ref.DEFAULT_B))
-    idx, _ = ref.hash_table(D, W)
+    native.lib().conef_cpu_hash_table(tab.ctypes.data, cnt.ctypes.data, D, W, ref.DEFAULT_A, ref.DEFAULT_B, 2, 3,
+                                      int(layout == "block"))
+    assert np.array_equal(tab, ref.packed_hash_table(D, W, ref.DEFAULT_A, ref.DEFAULT_B, layout=layout))
+    idx, _ = ref.hash_table(D, W, layout=layout)
     assert np.array_equal(cnt, np.bincount(idx.numpy(), minlength=W))
 
 
