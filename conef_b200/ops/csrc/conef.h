@@ -162,7 +162,11 @@ int conef_psgd_q(const ConefMat* mats, const int2* tiles, int ntiles, const floa
 // smem_bytes = rows_per_cta * max W * 4 in sketch mode, else 0.
 // In sketch mode the first nblk_tiles tiles belong to matrices whose hash has the block layout
 // (cb_off >= 0): they run on the atomics-free kernel that walks the columns cell block by cell block.
-int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int nblk_tiles, int rows_per_cta,
+// Such a tile is (matrix, chunk of 8 units); a unit is (rbu consecutive row blocks, cell block), rbu in
+// 1..4, and 1 regardless for matrices with more than 32 windows; a matrix has
+// ceil(ceil(n / rows_per_cta) / rbu) * (W / 32) units.
+int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int nblk_tiles, int rbu,
+                          int rows_per_cta,
                           float* bucket, const float* P, const float* Q, float q_scale,
                           float* sketch, const int32_t* tables, const int32_t* counts,
                           float* dense_err, float alpha, float beta, int ef_mode, int max_rank,

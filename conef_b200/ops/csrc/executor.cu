@@ -177,7 +177,7 @@ static int run_fused(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint
       RUN(conef_wait_flags_ex(plan->my_flags, ws, ep2, plan->status, spin, eb, s));
     RUN(conef_reduce_q(plan->mats, nm, plan->max_cols, sketch ? plan->tables : nullptr, plan->qz,
                        plan->peer_q[slot], plan->my_flags, ws, ep2, plan->alpha, inv_ws, plan->status, spin, eb, s));
-    RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_nblk, plan->d_rows,
+    RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_nblk, plan->d_rbu, plan->d_rows,
                               plan->work, plan->pu, plan->qz, 1.0f, plan->sketch, plan->tables, plan->counts,
                               dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank, plan->d_smem, s));
     if (plan->ef_mode == CONEF_EF_SKETCH && plan->d_nblk > 0 && plan->d_nblk < plan->d_tiles.n) ++plan->launched;
@@ -295,7 +295,7 @@ static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint3
       OK(copy_floats(plan->u_old, plan->pu + tp, tu, s));
       OK(copy_floats(plan->qz + tq, plan->qz2 + tq, tz, s));
     }
-    RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_nblk, plan->d_rows,
+    RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_nblk, plan->d_rbu, plan->d_rows,
                               plan->work, pmem, qmem, 1.0f, plan->sketch, plan->tables, plan->counts,
                               dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank,
                               plan->d_smem, s));

@@ -56,7 +56,7 @@ typedef struct ConefPsgdPlan {
   const ConefCorr* corr_v;
   int* status;
   // ---- peer memory (world > 1 with symmetric buffers) -------------------------------------
-  int world, rank, has_symm, pad2;
+  int world, rank, has_symm, d_rbu;      // d_rbu: row blocks per unit of the block-layout decompress
   uint32_t* const* peer_flags;   // device array [world] of the peers' flag arrays
   const uint32_t* my_flags;
   const float* const* peer_stage[2];   // per slot: device arrays [world] of region pointers

@@ -17,7 +17,6 @@
 //   :531  torch.matmul(M^T, P) -> k_psgd_q
 //   :550  torch.matmul(P, Q^T), :558/:563 residual, CountSketch.py:27-67 update
 //                              -> k_psgd_decompress (one pass, residual kept in registers)
-#include <stdlib.h>
 #include "common.cuh"
 
 constexpr int P_WARPS = 8;       // warps per CTA in k_psgd_p
@@ -340,24 +339,32 @@ k_psgd_decompress(const ConefMat* __restrict__ mats, const int2* __restrict__ ti
 // aligned groups of 32, one group per cell block and window of nb = W / 32 groups).  The table arena
 // holds, per matrix, S x nb two-word records, window-major: {g | x_g << 27 (0x7ffffff: none), sign bits
 // of the group's 32 columns} = the group cell block c receives from window s.
-// Work unit of a warp: (block of RB rows, cell block c).  The warp walks the S groups of its cell block;
-// lane l handles column 32 g + (l xor x_g), whose cell is 32 c + l for every one of them, so the 32 sums
-// of the cell block stay in the lanes' registers: no atomics, no shared-memory accumulator, all warps
-// do the same amount of work, and every access of a warp is one full 128-byte line (G row segment,
-// M_hat row segment, sketch cells).  A CTA's eight warps take neighbouring cell blocks of the same
-// rows and therefore read inside the same window of the row at about the same time.  The records of
-// the cell block are fetched up front (one per lane) and handed round by shuffles, so the addresses
-// of later groups never wait for a load.  G travels through a per-warp ring in shared memory filled by
-// cp.async (D_STAGES - 1 groups, i.e. 3 KB per warp, in flight at no cost in registers; the kernel is
-// bound by the latency of its loads, not by any pipe); the Q row of the next group is in flight in
-// registers.  Tile = (matrix, chunk of eight consecutive units of that matrix).
+// Work unit of a warp: (rbu consecutive blocks of RB rows, cell block c).  The warp walks the S groups of
+// its cell block once per row block; lane l handles column 32 g + (l xor x_g), whose cell is 32 c + l for
+// every one of them, so the 32 sums of the cell block stay in the lanes' registers: no atomics, no
+// shared-memory accumulator, all warps do the same amount of work, and every access of a warp is one
+// full 128-byte line (G row segment, M_hat row segment, sketch cells).  A CTA's eight warps take
+// neighbouring cell blocks of the same rows and therefore read inside the same window of the row at
+// about the same time.  The records of the cell block are fetched up front (one per lane) and handed
+// round by shuffles, so addresses never wait for a load.  G and the Q rows travel through a per-warp
+// ring in shared memory filled by cp.async: D_STAGES - 1 groups (3 KB of G per warp) are in flight at
+// no cost in registers, across the boundaries between row blocks; a lane reads back only what it
+// copied itself, so the ring needs no barriers.  The kernel moves 4 bytes per lane and instruction,
+// which makes the instruction count per row its second limit after load latency: row addresses are one
+// multiply-add on a 32-bit byte stride, shared memory is addressed with immediates off one register
+// per stage, and row blocks with all RB rows skip the per-row predicates.
+// Tile = (matrix, chunk of eight consecutive units of that matrix).
 constexpr int D_WARPS = D_THREADS / 32;
-constexpr int D_STAGES = 4;      // groups of G in flight per warp (a ring of RB x 128 bytes per stage)
+constexpr int D_STAGES = 4;       // ring depth (a power of two)
+constexpr int D_RBU_MAX = 4;      // most row blocks per unit
 
-// 4-byte cp.async into shared memory at `dst + OFF` (a shared-space address plus an immediate).
 template <int OFF>
 __device__ __forceinline__ void cp_async_f32(uint32_t dst, const void* gmem_src) {
   asm volatile("cp.async.ca.shared.global [%0+%2], [%1], 4;" ::"r"(dst), "l"(gmem_src), "n"(OFF) : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0+%2], [%1], 16;" ::"r"(dst), "l"(gmem_src), "n"(OFF) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -368,109 +375,179 @@ __device__ __forceinline__ float lds_f32(uint32_t src) {
   asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(src), "n"(OFF) : "memory");
   return v;
 }
+template <int OFF>
+__device__ __forceinline__ float4 lds_f32x4(uint32_t src) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(src), "n"(OFF) : "memory");
+  return v;
+}
 
-// The walk of one unit.  FULL: the row block has all RB rows (no per-row predicates).  The kernel issues
-// few bytes per instruction (4 per lane), so the instruction count per row is what bounds it once the
-// loads are deep enough in flight: row addresses are one multiply-add on a 32-bit byte stride, shared
-// memory is addressed with immediates off one register per stage.
+template <int RP, int RB>
+struct DblkLayout {
+  static constexpr int STAGE_BYTES = RB * 128 + 32 * RP * 4;      // G [RB][32] | Q rows [32][RP]
+  static constexpr int PS_BYTES = D_RBU_MAX * RB * RP * 4;        // P rows of the unit
+  static constexpr int WARP_BYTES = PS_BYTES + D_STAGES * STAGE_BYTES;
+  static constexpr int CTA_BYTES = D_WARPS * WARP_BYTES;
+};
+
+// One chunk (at most 32 groups) of the walk over `nrbh` row blocks.  FULL: every row block has RB rows.
 template <int RP, int RB, bool FULL>
-__device__ __forceinline__ void dblk_walk(const int2* __restrict__ recs, int nb, int S, int m, int r, int rows,
-                                          float* __restrict__ g0, const float* __restrict__ q0, float q_scale,
-                                          bool qvec, const float* __restrict__ ps, uint32_t ring, int lane,
-                                          float (&acc)[RB]) {
+__device__ __forceinline__ void dblk_walk(int2 mine, int cnt, bool last_chunk, bool first_chunk, int nrbh, int m,
+                                          int r, int rows_total, float* __restrict__ g0,
+                                          const float* __restrict__ q0, float q_scale, bool qvec, uint32_t ps,
+                                          uint32_t ring_g, uint32_t ring_q, int lane, float* __restrict__ sc0,
+                                          int Wp, float f, float (&acc)[RB], float (&so)[RB]) {
+  using L = DblkLayout<RP, RB>;
   const unsigned pitch = (unsigned)m * 4u;      // bytes between rows
   auto row_ptr = [&](float* base, int ii) {
     return reinterpret_cast<float*>(reinterpret_cast<char*>(base) + (unsigned long long)pitch * (unsigned)ii);
   };
-  for (int s0 = 0; s0 < S; s0 += 32) {
-    int2 mine = make_int2(0x7ffffff, 0);
-    if (s0 + lane < S) mine = __ldg(recs + (size_t)(s0 + lane) * nb);
-    const int cnt = min(32, S - s0);
-    // column of this lane in the i-th group of the chunk (m: none); every lane calls it together
-    auto column = [&](int i) {
-      const int rx = __shfl_sync(0xffffffffu, mine.x, i & 31);
-      const int g = rx & 0x7ffffff;
-      return (i < cnt && g != 0x7ffffff) ? (g << 5) + (lane ^ (int)((uint32_t)rx >> 27)) : m;
-    };
-    auto issue = [&](int i) {
-      const int cl = column(i);
+  // column of this lane in the i-th group of the chunk (m: none); every lane calls it together
+  auto column = [&](int i) {
+    const int rx = __shfl_sync(0xffffffffu, mine.x, i & 31);
+    const int g = rx & 0x7ffffff;
+    return (i < cnt && g != 0x7ffffff) ? (g << 5) + (lane ^ (int)((uint32_t)rx >> 27)) : m;
+  };
+  const int total = nrbh * cnt;
+  // issue side: item k_i = (row block rb_i, group i_i)
+  int k_i = 0, rb_i = 0, i_i = 0;
+  float* g_i = g0;
+  auto issue = [&]() {
+    if (k_i < total) {
+      const int cl = column(i_i);
       if (cl < m) {
-        float* src = g0 + cl;
-        const uint32_t dst = ring + (uint32_t)(i & (D_STAGES - 1)) * (RB * 128);
+        float* src = g_i + cl;
+        const uint32_t stage = (uint32_t)(k_i & (D_STAGES - 1)) * L::STAGE_BYTES;
+        const uint32_t dst = ring_g + stage;
+        const int rows = FULL ? RB : min(RB, rows_total - rb_i * RB);
 #pragma unroll
         for (int ii = 0; ii < RB; ++ii)
           if (FULL || ii < rows) cp_async_f32<0>(dst + ii * 128, row_ptr(src, ii));
-      }
-      cp_async_commit();
-    };
+        const float* qs = q0 + (size_t)cl * r;
+        const uint32_t qd = ring_q + stage;
+        if (qvec) {
 #pragma unroll
-    for (int k = 0; k < D_STAGES - 1; ++k) issue(k);
-    float qv[RP];
-    load_q_row<RP>(q0 + (size_t)min(column(0), m - 1) * r, r, q_scale, qvec, qv);
-    for (int i = 0; i < cnt; ++i) {
-      issue(i + D_STAGES - 1);
-      float qn[RP];
-      load_q_row<RP>(q0 + (size_t)min(column(i + 1), m - 1) * r, r, q_scale, qvec, qn);
-      const int col = column(i);
-      const uint32_t sbits = (uint32_t)__shfl_sync(0xffffffffu, mine.y, i & 31);
-      cp_async_wait<D_STAGES - 1>();      // the copies of group i have landed
-      if (col < m) {
-        const float sgn = ((sbits >> (col & 31)) & 1u) ? 1.f : -1.f;
-        float* dstp = g0 + col;
-        const uint32_t src = ring + (uint32_t)(i & (D_STAGES - 1)) * (RB * 128);
+          for (int cc = 0; cc < RP; cc += 4)
+            if (cc < r) cp_async_16<0>(qd + cc * 4, qs + cc);
+        } else {
 #pragma unroll
-        for (int ii = 0; ii < RB; ++ii) {
-          if (FULL || ii < rows) {
-            float mh = 0.f;
-#pragma unroll
-            for (int cc = 0; cc < RP; cc += 4) {
-              const float4 pv = *reinterpret_cast<const float4*>(ps + ii * RP + cc);
-              mh = fmaf(pv.x, qv[cc], mh);
-              mh = fmaf(pv.y, qv[cc + 1], mh);
-              mh = fmaf(pv.z, qv[cc + 2], mh);
-              mh = fmaf(pv.w, qv[cc + 3], mh);
-            }
-            const float v = lds_f32<0>(src + ii * 128);
-            *row_ptr(dstp, ii) = mh;
-            acc[ii] = fmaf(sgn, v - mh, acc[ii]);
-          }
+          for (int cc = 0; cc < RP; ++cc)
+            if (cc < r) cp_async_f32<0>(qd + cc * 4, qs + cc);
         }
       }
-#pragma unroll
-      for (int cc = 0; cc < RP; ++cc) qv[cc] = qn[cc];
+      ++k_i;
+      if (++i_i == cnt) { i_i = 0; ++rb_i; g_i = row_ptr(g_i, RB); }
     }
-    cp_async_wait<0>();
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int k = 0; k < D_STAGES - 1; ++k) issue();
+  int rb_p = 0, i_p = 0;
+  float* g_p = g0;
+  float* sc_p = sc0;
+  uint32_t ps_p = ps;
+  for (int k = 0; k < total; ++k) {
+    issue();
+    const int col = column(i_p);
+    const uint32_t sbits = (uint32_t)__shfl_sync(0xffffffffu, mine.y, i_p & 31);
+    const int rows = FULL ? RB : min(RB, rows_total - rb_p * RB);
+    if (i_p == 0) {
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii) {
+        if (first_chunk) acc[ii] = 0.f;
+        if (last_chunk) so[ii] = (FULL || ii < rows) ? sc_p[(size_t)ii * Wp] : 0.f;      // in flight during the walk
+      }
+    }
+    cp_async_wait<D_STAGES - 1>();      // the copies of item k have landed
+    if (col < m) {
+      const float sgn = ((sbits >> (col & 31)) & 1u) ? 1.f : -1.f;
+      float* dstp = g_p + col;
+      const uint32_t stage = (uint32_t)(k & (D_STAGES - 1)) * L::STAGE_BYTES;
+      const uint32_t src = ring_g + stage;
+      float qv[RP];
+#pragma unroll
+      for (int cc = 0; cc < RP; cc += 4) {
+        const float4 q4 = lds_f32x4<0>(ring_q + stage + cc * 4);
+        qv[cc] = q4.x * q_scale;
+        qv[cc + 1] = q4.y * q_scale;
+        qv[cc + 2] = q4.z * q_scale;
+        qv[cc + 3] = q4.w * q_scale;
+      }
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii) {
+        if (FULL || ii < rows) {
+          float mh = 0.f;
+#pragma unroll
+          for (int cc = 0; cc < RP; cc += 4) {
+            const float4 pv = lds_f32x4<0>(ps_p + (ii * RP + cc) * 4);
+            mh = fmaf(pv.x, qv[cc], mh);
+            mh = fmaf(pv.y, qv[cc + 1], mh);
+            mh = fmaf(pv.z, qv[cc + 2], mh);
+            mh = fmaf(pv.w, qv[cc + 3], mh);
+          }
+          const float v = lds_f32<0>(src + ii * 128);
+          *row_ptr(dstp, ii) = mh;
+          acc[ii] = fmaf(sgn, v - mh, acc[ii]);
+        }
+      }
+    }
+    if (++i_p == cnt) {
+      if (last_chunk) {
+#pragma unroll
+        for (int ii = 0; ii < RB; ++ii)
+          if (FULL || ii < rows) sc_p[(size_t)ii * Wp] = fmaf(so[ii], f, acc[ii]);
+      }
+      i_p = 0;
+      ++rb_p;
+      g_p = row_ptr(g_p, RB);
+      sc_p += (size_t)RB * Wp;
+      ps_p += RB * RP * 4;
+    }
   }
+  cp_async_wait<0>();
 }
 
-template <int RP, int RB, int MINB>
-__global__ void __launch_bounds__(D_THREADS, RP <= 8 ? MINB : 1)
+template <int RP, int RB>
+__global__ void __launch_bounds__(D_THREADS, RP <= 8 ? 3 : 1)
 k_psgd_decompress_blk(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles,
                       float* __restrict__ bucket, const float* __restrict__ P, const float* __restrict__ Q,
                       float q_scale, float* __restrict__ sketch, const int32_t* __restrict__ tables,
-                      const int32_t* __restrict__ counts, float alpha, float beta) {
+                      const int32_t* __restrict__ counts, float alpha, float beta, int rbu) {
   static_assert((D_STAGES & (D_STAGES - 1)) == 0, "the ring is indexed with a mask");
-  __shared__ __align__(16) float ps_all[D_WARPS][RB * RP];
-  __shared__ float ring_all[D_WARPS][D_STAGES][RB][32];
+  using L = DblkLayout<RP, RB>;
+  extern __shared__ __align__(16) unsigned char dblk_smem[];
   const int2 t = tiles[blockIdx.x];
   const ConefMat M = mats[t.x];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int m = M.m, r = M.r, Wp = M.Wp, nb = M.W >> 5;
+  const int S = (((m + 31) >> 5) + nb - 1) / nb;
+  const int nrb = (M.n + RB - 1) / RB;
+  const int R = S <= 32 ? min(max(rbu, 1), D_RBU_MAX) : 1;      // the host counts units the same way
   const int unit = t.y * D_WARPS + warp;
-  if (unit >= ((M.n + RB - 1) / RB) * nb) return;      // nothing below synchronises the CTA
-  const int rb = unit / nb, c = unit - rb * nb;
-  const int row0 = rb * RB;
-  const int rows = min(RB, M.n - row0);
-  float* ps = ps_all[warp];
+  if (unit >= ((nrb + R - 1) / R) * nb) return;      // nothing below synchronises the CTA
+  const int ru = unit / nb, c = unit - ru * nb;
+  const int nrbh = min(R, nrb - ru * R);
+  const int row0 = ru * R * RB;
+  const int rows_total = min(nrbh * RB, M.n - row0);
+  unsigned char* mine_smem = dblk_smem + (size_t)warp * L::WARP_BYTES;
+  float* psf = reinterpret_cast<float*>(mine_smem);
   {
     const float* p = P + M.p_off + (size_t)row0 * r;
-    for (int i = lane; i < RB * RP; i += 32) {
+    for (int i = lane; i < nrbh * RB * RP; i += 32) {
       const int ii = i / RP, cc = i - ii * RP;
-      ps[i] = (cc < r && ii < rows) ? p[(size_t)ii * r + cc] : 0.f;
+      psf[i] = (cc < r && ii < rows_total) ? p[(size_t)ii * r + cc] : 0.f;
     }
+    // the pad columns of the Q rows in the ring are never copied: they meet zeros of P, but must be finite
+    float* ringf = reinterpret_cast<float*>(mine_smem + L::PS_BYTES);
+    for (int st = 0; st < D_STAGES; ++st)
+      for (int cc = 0; cc < RP; ++cc) ringf[st * (L::STAGE_BYTES / 4) + RB * 32 + lane * RP + cc] = 0.f;
   }
   __syncwarp();
-  const int S = (((m + 31) >> 5) + nb - 1) / nb;
+  const uint32_t ps = (uint32_t)__cvta_generic_to_shared(mine_smem);
+  // per-lane views of a ring stage: G element (ii, lane) at ring_g + ii * 128, this lane's Q row at ring_q
+  const uint32_t ring_g = ps + L::PS_BYTES + lane * 4;
+  const uint32_t ring_q = ps + L::PS_BYTES + RB * 128 + lane * (RP * 4);
   const int2* recs = reinterpret_cast<const int2*>(tables + M.cb_off) + c;
   float* g0 = bucket + M.g_off + (size_t)row0 * m;
   const float* q0 = Q + M.q_off;
@@ -478,25 +555,22 @@ k_psgd_decompress_blk(const ConefMat* __restrict__ mats, const int2* __restrict_
   const int cell = (c << 5) + lane;
   float* sc0 = sketch + M.sk_off + (size_t)row0 * Wp + cell;
   const float f = 1.f + (alpha - (1.f - beta)) * (float)__ldg(counts + M.cnt_off + cell);
-  float so[RB], acc[RB];
-#pragma unroll
-  for (int ii = 0; ii < RB; ++ii) {
-    so[ii] = ii < rows ? sc0[(size_t)ii * Wp] : 0.f;      // in flight during the walk
-    acc[ii] = 0.f;
+  float acc[RB], so[RB];
+  for (int s0 = 0; s0 < S; s0 += 32) {
+    int2 mine = make_int2(0x7ffffff, 0);
+    if (s0 + lane < S) mine = __ldg(recs + (size_t)(s0 + lane) * nb);
+    const int cnt = min(32, S - s0);
+    if (rows_total == nrbh * RB)
+      dblk_walk<RP, RB, true>(mine, cnt, s0 + cnt == S, s0 == 0, nrbh, m, r, rows_total, g0, q0, q_scale, qvec, ps,
+                              ring_g, ring_q, lane, sc0, Wp, f, acc, so);
+    else
+      dblk_walk<RP, RB, false>(mine, cnt, s0 + cnt == S, s0 == 0, nrbh, m, r, rows_total, g0, q0, q_scale, qvec, ps,
+                               ring_g, ring_q, lane, sc0, Wp, f, acc, so);
   }
-  // a lane reads back only what it copied itself: the ring needs no barriers
-  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(&ring_all[warp][0][0][lane]);
-  if (rows == RB)
-    dblk_walk<RP, RB, true>(recs, nb, S, m, r, rows, g0, q0, q_scale, qvec, ps, ring, lane, acc);
-  else
-    dblk_walk<RP, RB, false>(recs, nb, S, m, r, rows, g0, q0, q_scale, qvec, ps, ring, lane, acc);
-#pragma unroll
-  for (int ii = 0; ii < RB; ++ii)
-    if (ii < rows) sc0[(size_t)ii * Wp] = fmaf(so[ii], f, acc[ii]);
 }
 
 template <int RP, int RB>
-static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, float* bucket, const float* P,
+static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, int rbu, float* bucket, const float* P,
                        const float* Q, float q_scale, float* sketch, const int32_t* tables,
                        const int32_t* counts, float* dense_err, float alpha, float beta, int ef_mode,
                        size_t smem, cudaStream_t stream) {
@@ -510,15 +584,15 @@ static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int 
     if (dev >= 0 && dev < 64) configured[dev] = smem;
   }
   if (nblk > 0) {
-    static int minb = -1;
-    if (minb < 0) { const char* e = getenv("CONEF_DBLK_MINB"); minb = e ? atoi(e) : 3; }
     constexpr int RQ = RP < 4 ? 4 : RP;
-    if (minb == 2)
-      k_psgd_decompress_blk<RQ, RB, 2><<<nblk, D_THREADS, 0, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables, counts, alpha, beta);
-    else if (minb == 3)
-      k_psgd_decompress_blk<RQ, RB, 3><<<nblk, D_THREADS, 0, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables, counts, alpha, beta);
-    else
-      k_psgd_decompress_blk<RQ, RB, 4><<<nblk, D_THREADS, 0, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch, tables, counts, alpha, beta);
+    constexpr int blk_smem = DblkLayout<RQ, RB>::CTA_BYTES;
+    static bool opted[64] = {};
+    if (blk_smem > 48 * 1024 && (dev < 0 || dev >= 64 || !opted[dev])) {
+      CONEF_CUDA(cudaFuncSetAttribute(k_psgd_decompress_blk<RQ, RB>, cudaFuncAttributeMaxDynamicSharedMemorySize, blk_smem));
+      if (dev >= 0 && dev < 64) opted[dev] = true;
+    }
+    k_psgd_decompress_blk<RQ, RB><<<nblk, D_THREADS, blk_smem, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch,
+                                                                        tables, counts, alpha, beta, rbu);
     CONEF_CHECK_LAUNCH("k_psgd_decompress_blk");
   }
   if (ntiles > nblk) {
@@ -531,12 +605,12 @@ static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int 
 }
 
 template <int RP>
-static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, int rows_per_cta, float* bucket,
+static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, int rbu, int rows_per_cta, float* bucket,
                     const float* P, const float* Q, float q_scale, float* sketch, const int32_t* tables,
                     const int32_t* counts, float* dense_err, float alpha, float beta, int ef_mode, size_t smem,
                     cudaStream_t stream) {
 #define CONEF_D_CASE(RB)                                                                              \
-  case RB: return launch_d_rb<RP, RB>(mats, tiles, ntiles, nblk, bucket, P, Q, q_scale, sketch, tables, counts, \
+  case RB: return launch_d_rb<RP, RB>(mats, tiles, ntiles, nblk, rbu, bucket, P, Q, q_scale, sketch, tables, counts, \
                                       dense_err, alpha, beta, ef_mode, smem, stream)
   switch (rows_per_cta) {
     CONEF_D_CASE(8);
@@ -549,7 +623,8 @@ static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int nbl
   return 2;
 }
 
-extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int nblk_tiles, int rows_per_cta,
+extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, int nblk_tiles, int rbu,
+                                     int rows_per_cta,
                                      float* bucket, const float* P, const float* Q, float q_scale,
                                      float* sketch, const int32_t* tables, const int32_t* counts,
                                      float* dense_err, float alpha, float beta, int ef_mode, int max_rank,
@@ -557,7 +632,7 @@ extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, in
   if (ntiles <= 0) return 0;
   if (ef_mode != CONEF_EF_SKETCH || nblk_tiles < 0) nblk_tiles = 0;
   if (nblk_tiles > ntiles) nblk_tiles = ntiles;
-  DISPATCH_RANK(max_rank, launch_d, mats, tiles, ntiles, nblk_tiles, rows_per_cta, bucket, P, Q, q_scale, sketch, tables,
+  DISPATCH_RANK(max_rank, launch_d, mats, tiles, ntiles, nblk_tiles, rbu, rows_per_cta, bucket, P, Q, q_scale, sketch, tables,
                 counts, dense_err, alpha, beta, ef_mode, smem_bytes, stream);
 }
 

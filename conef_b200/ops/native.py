@@ -83,7 +83,7 @@ class PsgdPlan(C.Structure):
         ("gram", C.c_void_p), ("cbuf", C.c_void_p),
         ("corr_p", C.c_void_p), ("corr_q", C.c_void_p), ("corr_u", C.c_void_p), ("corr_v", C.c_void_p),
         ("status", C.c_void_p),
-        ("world", C.c_int), ("rank", C.c_int), ("has_symm", C.c_int), ("pad2", C.c_int),
+        ("world", C.c_int), ("rank", C.c_int), ("has_symm", C.c_int), ("d_rbu", C.c_int),
         ("peer_flags", C.c_void_p), ("my_flags", C.c_void_p),
         ("peer_stage", C.c_void_p * 2), ("peer_p", C.c_void_p * 2), ("peer_q", C.c_void_p * 2),
         ("local_stage", C.c_void_p * 2), ("local_p", C.c_void_p * 2), ("local_q", C.c_void_p * 2),
@@ -151,7 +151,7 @@ _SIGNATURES = {
     "conef_orthogonalize_packed": ([vp, vp, C.c_int, C.c_int, C.c_int, vp, C.c_float, vp, vp, C.c_int, C.c_uint32,
                                     vp, c_ll, vp, C.c_int, vp, vp], C.c_int),
     "conef_pack_small": ([vp, C.c_int, C.c_int, vp, vp, C.c_int, vp], C.c_int),
-    "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
+    "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
                                C.c_float, C.c_int, C.c_int, C.c_size_t, vp], C.c_int),
     "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),
     "conef_lowrank_correct": ([vp, C.c_int, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_float, vp, vp, vp,

@@ -343,8 +343,15 @@ class PowerSGDEngine(_EngineBase):
         # matrices on the block layout of the hash first: they run on the atomics-free kernel, whose tile
         # is a chunk of eight (row block, cell block) units, one per warp; the others by row block
         on_blocks = [int(mats[k]["cb_off"]) >= 0 for k in range(nm)]
+        self.d_rbu = int(os.environ.get("CONEF_D_RBU", "2"))
+
+        def units(e, W):      # (row blocks of a unit, cell block); matrices with more than 32 windows: one row block
+            nb = W // 32
+            windows = math.ceil(math.ceil(e.m / 32) / nb)
+            per_unit = self.d_rbu if windows <= 32 else 1
+            return math.ceil(math.ceil(e.n / self.d_rows) / per_unit) * nb
         d_tiles = [(k, ch) for k, e in enumerate(plan.mats) if on_blocks[k]
-                   for ch in range(math.ceil(math.ceil(e.n / self.d_rows) * (self.widths[k] // 32) / 8))]
+                   for ch in range(math.ceil(units(e, self.widths[k]) / 8))]
         self.d_nblk = len(d_tiles)
         d_tiles += [(k, rb) for k, e in enumerate(plan.mats) if not on_blocks[k]
                     for rb in range(math.ceil(e.n / self.d_rows))]
@@ -656,7 +663,7 @@ class PowerSGDEngine(_EngineBase):
         P.tc_p, P.simt_p = tl(self.tc_p_tiles, self.n_tc_p), tl(self.p_tiles, self.n_p_tiles)
         P.qset_all, P.qset_grad, P.qset_err = qset("all"), qset("grad"), qset("err")
         P.d_tiles, P.d_rows, P.d_smem = tl(self.d_tiles, self.n_d_tiles), self.d_rows, self.d_smem
-        P.d_nblk = self.d_nblk
+        P.d_nblk, P.d_rbu = self.d_nblk, self.d_rbu
         P.orth_q, P.orth_p = tl(*self.orth_tiles[(1, "grad")]), tl(*self.orth_tiles[(0, "grad")])
         P.orth_u = tl(*self.orth_tiles[(0, "err")])
         P.chunks_n, P.chunks_m = tl(*self.chunks_n), tl(*self.chunks_m)
