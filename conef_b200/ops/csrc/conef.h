@@ -170,7 +170,9 @@ int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, int ntiles, i
                           float* bucket, const float* P, const float* Q, float q_scale,
                           float* sketch, const int32_t* tables, const int32_t* counts,
                           float* dense_err, float alpha, float beta, int ef_mode, int max_rank,
-                          size_t smem_bytes, cudaStream_t stream);
+                          size_t smem_bytes, int* status, cudaStream_t stream);
+// status: device word that receives CONEF_STATUS_MBAR_TIMEOUT when a bounded wait of the bulk-copy
+// ring runs out (NULL: the ring is filled with cp.async, which needs no waits on barriers).
 // Sparse sign matrix H of the sketch applied to the small factors (see csrc/sketch.cu):
 // unproject = 0: Z_i += scale * H_i^T Q_i ; unproject = 1: Q_i += scale * H_i Y_i.
 // Record nmats + i describes the sketch of matrix i; its q_off is where Z_i / Y_i live.

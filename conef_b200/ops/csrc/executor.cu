@@ -179,7 +179,8 @@ static int run_fused(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint
                        plan->peer_q[slot], plan->my_flags, ws, ep2, plan->alpha, inv_ws, plan->status, spin, eb, s));
     RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_nblk, plan->d_rbu, plan->d_rows,
                               plan->work, plan->pu, plan->qz, 1.0f, plan->sketch, plan->tables, plan->counts,
-                              dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank, plan->d_smem, s));
+                              dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank, plan->d_smem,
+                              plan->status, s));
     if (plan->ef_mode == CONEF_EF_SKETCH && plan->d_nblk > 0 && plan->d_nblk < plan->d_tiles.n) ++plan->launched;
     if (plan->topk) {
       RUN(conef_topk_keep(plan->mats, nm, (const int2*)plan->topk_tiles.tiles, plan->topk_tiles.n,
@@ -298,7 +299,7 @@ static int run_impl(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint3
     RUN(conef_psgd_decompress(plan->mats, (const int2*)plan->d_tiles.tiles, plan->d_tiles.n, plan->d_nblk, plan->d_rbu, plan->d_rows,
                               plan->work, pmem, qmem, 1.0f, plan->sketch, plan->tables, plan->counts,
                               dense_err, plan->alpha, plan->beta, plan->ef_mode, plan->max_rank,
-                              plan->d_smem, s));
+                              plan->d_smem, plan->status, s));
     if (plan->ef_mode == CONEF_EF_SKETCH && plan->d_nblk > 0 && plan->d_nblk < plan->d_tiles.n) ++plan->launched;
     if (plan->topk) {
       RUN(conef_topk_keep(plan->mats, nm, (const int2*)plan->topk_tiles.tiles, plan->topk_tiles.n,

@@ -17,6 +17,7 @@
 //   :531  torch.matmul(M^T, P) -> k_psgd_q
 //   :550  torch.matmul(P, Q^T), :558/:563 residual, CountSketch.py:27-67 update
 //                              -> k_psgd_decompress (one pass, residual kept in registers)
+#include <stdlib.h>
 #include "common.cuh"
 
 constexpr int P_WARPS = 8;       // warps per CTA in k_psgd_p
@@ -383,12 +384,45 @@ __device__ __forceinline__ float4 lds_f32x4(uint32_t src) {
   return v;
 }
 
+// mbarrier + bulk-copy (TMA without a tensor map) helpers of the ring's second filling mode
+// Every probe may sleep in hardware for up to the hinted time, so the limit below is seconds, and a
+// warp that waits does not spend issue slots on a spin loop.
+constexpr int D_MBAR_PROBES = 1 << 18;
+constexpr uint32_t D_MBAR_SUSPEND_NS = 2000;
+__device__ __forceinline__ void dmbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void dmbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool dmbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(D_MBAR_SUSPEND_NS) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool dmbar_wait(uint32_t bar, uint32_t parity) {      // bounded
+  for (int it = 0; it < D_MBAR_PROBES; ++it)
+    if (dmbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// untiled bulk copy global -> shared: both addresses 16-byte aligned, size a multiple of 16 bytes
+__device__ __forceinline__ void dbulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
 template <int RP, int RB>
 struct DblkLayout {
+  static constexpr int MBAR_BYTES = 64;                           // D_STAGES mbarriers (bulk-copy mode)
   static constexpr int STAGE_BYTES = RB * 128 + 32 * RP * 4;      // G [RB][32] | Q rows [32][RP]
   static constexpr int PS_BYTES = D_RBU_MAX * RB * RP * 4;        // P rows of the unit
-  static constexpr int WARP_BYTES = PS_BYTES + D_STAGES * STAGE_BYTES;
+  static constexpr int WARP_BYTES = MBAR_BYTES + PS_BYTES + D_STAGES * STAGE_BYTES;
   static constexpr int CTA_BYTES = D_WARPS * WARP_BYTES;
+  static_assert(D_STAGES * 8 <= MBAR_BYTES && PS_BYTES % 16 == 0 && STAGE_BYTES % 16 == 0, "ring layout");
 };
 
 // One chunk (at most 32 groups) of the walk over `nrbh` row blocks.  FULL: every row block has RB rows.
@@ -508,12 +542,133 @@ __device__ __forceinline__ void dblk_walk(int2 mine, int cnt, bool last_chunk, b
   cp_async_wait<0>();
 }
 
+// The same walk with the ring filled by bulk copies (the TMA engine instead of the load/store unit, which
+// otherwise carries every byte of G twice: global -> shared, shared -> register): per item the warp posts
+// RB row segments of 128 bytes and the 32 Q rows of the group on the stage's mbarrier; every lane then
+// reads column (lane xor x_g) of the stage.  Needs 16-byte aligned row segments (matrix start and row
+// pitch), no ragged last group (m a multiple of 32), r == RP and one chunk (at most 32 windows).  Waits
+// are bounded: a wait that runs out reports CONEF_STATUS_MBAR_TIMEOUT, the copies still in flight are
+// waited for (bounded again), and the unit is given up.  Returns false in that case.
+template <int RP, int RB, bool FULL>
+__device__ __forceinline__ bool dblk_walk_bulk(int2 mine, int cnt, int nrbh, int m, int rows_total,
+                                               float* __restrict__ g0, const float* __restrict__ q0, float q_scale,
+                                               uint32_t ps, uint32_t ring0, uint32_t bar0, int lane,
+                                               float* __restrict__ sc0, int Wp, float f, int* __restrict__ status) {
+  using L = DblkLayout<RP, RB>;
+  const unsigned pitch = (unsigned)m * 4u;
+  auto row_ptr = [&](float* base, int ii) {
+    return reinterpret_cast<float*>(reinterpret_cast<char*>(base) + (unsigned long long)pitch * (unsigned)ii);
+  };
+  const int total = nrbh * cnt;
+  int k_i = 0, rb_i = 0, i_i = 0;
+  float* g_i = g0;
+  uint32_t pending = 0;      // stages with copies in flight
+  auto issue = [&]() {
+    if (k_i < total) {
+      const int rx = __shfl_sync(0xffffffffu, mine.x, i_i);
+      const int g = rx & 0x7ffffff;
+      const int st = k_i & (D_STAGES - 1);
+      if (g != 0x7ffffff) {
+        const int rows = FULL ? RB : min(RB, rows_total - rb_i * RB);
+        const uint32_t bar = bar0 + st * 8;
+        const uint32_t dst = ring0 + (uint32_t)st * L::STAGE_BYTES;
+        __syncwarp();      // every lane is done reading the stage that is refilled
+        if (lane == 0) dmbar_expect_tx(bar, (uint32_t)rows * 128u + 32u * RP * 4u);
+        __syncwarp();      // the transaction count is posted before any copy can complete
+        // lanes 0 .. rows - 1 post one row segment each, lane RB the Q rows: two instructions for the warp
+        if (lane < rows) dbulk_load(dst + lane * 128, row_ptr(g_i + (g << 5), lane), 128u, bar);
+        else if (lane == RB) dbulk_load(dst + RB * 128, q0 + (size_t)(g << 5) * RP, 32u * RP * 4u, bar);
+        pending |= 1u << st;
+      }
+      ++k_i;
+      if (++i_i == cnt) { i_i = 0; ++rb_i; g_i = row_ptr(g_i, RB); }
+    }
+  };
+#pragma unroll
+  for (int k = 0; k < D_STAGES - 1; ++k) issue();
+  float so[RB], acc[RB];
+  int rb_p = 0, i_p = 0;
+  float* g_p = g0;
+  float* sc_p = sc0;
+  uint32_t ps_p = ps;
+  uint32_t parity = 0;       // bit st: phase parity the next wait on stage st expects
+  for (int k = 0; k < total; ++k) {
+    issue();
+    const int rx = __shfl_sync(0xffffffffu, mine.x, i_p);
+    const uint32_t sbits = (uint32_t)__shfl_sync(0xffffffffu, mine.y, i_p);
+    const int g = rx & 0x7ffffff;
+    const int rows = FULL ? RB : min(RB, rows_total - rb_p * RB);
+    if (i_p == 0) {
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii) {
+        acc[ii] = 0.f;
+        so[ii] = (FULL || ii < rows) ? sc_p[(size_t)ii * Wp] : 0.f;      // in flight during the walk
+      }
+    }
+    if (g != 0x7ffffff) {
+      const int st = k & (D_STAGES - 1);
+      if (!dmbar_wait(bar0 + st * 8, (parity >> st) & 1u)) {
+        if (lane == 0) atomicExch(status, CONEF_STATUS_MBAR_TIMEOUT);
+        for (int s2 = 0; s2 < D_STAGES; ++s2)
+          if ((pending >> s2) & 1u) dmbar_wait(bar0 + s2 * 8, (parity >> s2) & 1u);
+        return false;
+      }
+      parity ^= 1u << st;
+      pending &= ~(1u << st);
+      const int lx = lane ^ (int)((uint32_t)rx >> 27);      // this lane's column inside the group
+      const float sgn = ((sbits >> lx) & 1u) ? 1.f : -1.f;
+      float* dstp = g_p + (g << 5) + lx;
+      const uint32_t stage = ring0 + (uint32_t)st * L::STAGE_BYTES;
+      const uint32_t src = stage + lx * 4;
+      const uint32_t qsrc = stage + RB * 128 + lx * (RP * 4);
+      float qv[RP];
+#pragma unroll
+      for (int cc = 0; cc < RP; cc += 4) {
+        const float4 q4 = lds_f32x4<0>(qsrc + cc * 4);
+        qv[cc] = q4.x * q_scale;
+        qv[cc + 1] = q4.y * q_scale;
+        qv[cc + 2] = q4.z * q_scale;
+        qv[cc + 3] = q4.w * q_scale;
+      }
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii) {
+        if (FULL || ii < rows) {
+          float mh = 0.f;
+#pragma unroll
+          for (int cc = 0; cc < RP; cc += 4) {
+            const float4 pv = lds_f32x4<0>(ps_p + (ii * RP + cc) * 4);
+            mh = fmaf(pv.x, qv[cc], mh);
+            mh = fmaf(pv.y, qv[cc + 1], mh);
+            mh = fmaf(pv.z, qv[cc + 2], mh);
+            mh = fmaf(pv.w, qv[cc + 3], mh);
+          }
+          const float v = lds_f32<0>(src + ii * 128);
+          *row_ptr(dstp, ii) = mh;
+          acc[ii] = fmaf(sgn, v - mh, acc[ii]);
+        }
+      }
+    }
+    if (++i_p == cnt) {
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii)
+        if (FULL || ii < rows) sc_p[(size_t)ii * Wp] = fmaf(so[ii], f, acc[ii]);
+      i_p = 0;
+      ++rb_p;
+      g_p = row_ptr(g_p, RB);
+      sc_p += (size_t)RB * Wp;
+      ps_p += RB * RP * 4;
+    }
+  }
+  return true;
+}
+
 template <int RP, int RB>
 __global__ void __launch_bounds__(D_THREADS, RP <= 8 ? 3 : 1)
 k_psgd_decompress_blk(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles,
                       float* __restrict__ bucket, const float* __restrict__ P, const float* __restrict__ Q,
                       float q_scale, float* __restrict__ sketch, const int32_t* __restrict__ tables,
-                      const int32_t* __restrict__ counts, float alpha, float beta, int rbu) {
+                      const int32_t* __restrict__ counts, float alpha, float beta, int rbu, int bulk,
+                      int* __restrict__ status) {
   static_assert((D_STAGES & (D_STAGES - 1)) == 0, "the ring is indexed with a mask");
   using L = DblkLayout<RP, RB>;
   extern __shared__ __align__(16) unsigned char dblk_smem[];
@@ -531,7 +686,7 @@ k_psgd_decompress_blk(const ConefMat* __restrict__ mats, const int2* __restrict_
   const int row0 = ru * R * RB;
   const int rows_total = min(nrbh * RB, M.n - row0);
   unsigned char* mine_smem = dblk_smem + (size_t)warp * L::WARP_BYTES;
-  float* psf = reinterpret_cast<float*>(mine_smem);
+  float* psf = reinterpret_cast<float*>(mine_smem + L::MBAR_BYTES);
   {
     const float* p = P + M.p_off + (size_t)row0 * r;
     for (int i = lane; i < nrbh * RB * RP; i += 32) {
@@ -539,15 +694,17 @@ k_psgd_decompress_blk(const ConefMat* __restrict__ mats, const int2* __restrict_
       psf[i] = (cc < r && ii < rows_total) ? p[(size_t)ii * r + cc] : 0.f;
     }
     // the pad columns of the Q rows in the ring are never copied: they meet zeros of P, but must be finite
-    float* ringf = reinterpret_cast<float*>(mine_smem + L::PS_BYTES);
+    float* ringf = reinterpret_cast<float*>(mine_smem + L::MBAR_BYTES + L::PS_BYTES);
     for (int st = 0; st < D_STAGES; ++st)
       for (int cc = 0; cc < RP; ++cc) ringf[st * (L::STAGE_BYTES / 4) + RB * 32 + lane * RP + cc] = 0.f;
   }
   __syncwarp();
-  const uint32_t ps = (uint32_t)__cvta_generic_to_shared(mine_smem);
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(mine_smem);
+  const uint32_t ps = bar0 + L::MBAR_BYTES;
+  const uint32_t ring0 = ps + L::PS_BYTES;
   // per-lane views of a ring stage: G element (ii, lane) at ring_g + ii * 128, this lane's Q row at ring_q
-  const uint32_t ring_g = ps + L::PS_BYTES + lane * 4;
-  const uint32_t ring_q = ps + L::PS_BYTES + RB * 128 + lane * (RP * 4);
+  const uint32_t ring_g = ring0 + lane * 4;
+  const uint32_t ring_q = ring0 + RB * 128 + lane * (RP * 4);
   const int2* recs = reinterpret_cast<const int2*>(tables + M.cb_off) + c;
   float* g0 = bucket + M.g_off + (size_t)row0 * m;
   const float* q0 = Q + M.q_off;
@@ -555,12 +712,32 @@ k_psgd_decompress_blk(const ConefMat* __restrict__ mats, const int2* __restrict_
   const int cell = (c << 5) + lane;
   float* sc0 = sketch + M.sk_off + (size_t)row0 * Wp + cell;
   const float f = 1.f + (alpha - (1.f - beta)) * (float)__ldg(counts + M.cnt_off + cell);
+  const bool full = rows_total == nrbh * RB;
+  // bulk copies: 16-byte aligned row segments and Q rows, whole groups only, one chunk
+  if (bulk && S <= 32 && r == RP && (m & 31) == 0 && (reinterpret_cast<uintptr_t>(bucket + M.g_off) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(q0) & 15) == 0) {
+    if (lane == 0) {
+      for (int st = 0; st < D_STAGES; ++st) dmbar_init(bar0 + st * 8, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the ring was written with plain stores above
+    __syncwarp();
+    int2 mine = make_int2(0x7ffffff, 0);
+    if (lane < S) mine = __ldg(recs + (size_t)lane * nb);
+    if (full)
+      dblk_walk_bulk<RP, RB, true>(mine, S, nrbh, m, rows_total, g0, q0, q_scale, ps, ring0, bar0, lane, sc0, Wp, f,
+                                   status);
+    else
+      dblk_walk_bulk<RP, RB, false>(mine, S, nrbh, m, rows_total, g0, q0, q_scale, ps, ring0, bar0, lane, sc0, Wp, f,
+                                    status);
+    return;
+  }
   float acc[RB], so[RB];
   for (int s0 = 0; s0 < S; s0 += 32) {
     int2 mine = make_int2(0x7ffffff, 0);
     if (s0 + lane < S) mine = __ldg(recs + (size_t)(s0 + lane) * nb);
     const int cnt = min(32, S - s0);
-    if (rows_total == nrbh * RB)
+    if (full)
       dblk_walk<RP, RB, true>(mine, cnt, s0 + cnt == S, s0 == 0, nrbh, m, r, rows_total, g0, q0, q_scale, qvec, ps,
                               ring_g, ring_q, lane, sc0, Wp, f, acc, so);
     else
@@ -570,7 +747,8 @@ k_psgd_decompress_blk(const ConefMat* __restrict__ mats, const int2* __restrict_
 }
 
 template <int RP, int RB>
-static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, int rbu, float* bucket, const float* P,
+static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, int rbu, int bulk, int* status,
+                       float* bucket, const float* P,
                        const float* Q, float q_scale, float* sketch, const int32_t* tables,
                        const int32_t* counts, float* dense_err, float alpha, float beta, int ef_mode,
                        size_t smem, cudaStream_t stream) {
@@ -592,7 +770,7 @@ static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int 
       if (dev >= 0 && dev < 64) opted[dev] = true;
     }
     k_psgd_decompress_blk<RQ, RB><<<nblk, D_THREADS, blk_smem, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch,
-                                                                        tables, counts, alpha, beta, rbu);
+                                                                        tables, counts, alpha, beta, rbu, bulk, status);
     CONEF_CHECK_LAUNCH("k_psgd_decompress_blk");
   }
   if (ntiles > nblk) {
@@ -605,12 +783,13 @@ static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int 
 }
 
 template <int RP>
-static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, int rbu, int rows_per_cta, float* bucket,
+static int launch_d(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, int rbu, int bulk, int* status,
+                    int rows_per_cta, float* bucket,
                     const float* P, const float* Q, float q_scale, float* sketch, const int32_t* tables,
                     const int32_t* counts, float* dense_err, float alpha, float beta, int ef_mode, size_t smem,
                     cudaStream_t stream) {
 #define CONEF_D_CASE(RB)                                                                              \
-  case RB: return launch_d_rb<RP, RB>(mats, tiles, ntiles, nblk, rbu, bucket, P, Q, q_scale, sketch, tables, counts, \
+  case RB: return launch_d_rb<RP, RB>(mats, tiles, ntiles, nblk, rbu, bulk, status, bucket, P, Q, q_scale, sketch, tables, counts, \
                                       dense_err, alpha, beta, ef_mode, smem, stream)
   switch (rows_per_cta) {
     CONEF_D_CASE(8);
@@ -628,11 +807,13 @@ extern "C" int conef_psgd_decompress(const ConefMat* mats, const int2* tiles, in
                                      float* bucket, const float* P, const float* Q, float q_scale,
                                      float* sketch, const int32_t* tables, const int32_t* counts,
                                      float* dense_err, float alpha, float beta, int ef_mode, int max_rank,
-                                     size_t smem_bytes, cudaStream_t stream) {
+                                     size_t smem_bytes, int* status, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
+  const char* bulk_env = getenv("CONEF_D_BULK");      // "0": fill the ring with cp.async everywhere
+  const int bulk = (status != nullptr && !(bulk_env && bulk_env[0] == '0')) ? 1 : 0;
   if (ef_mode != CONEF_EF_SKETCH || nblk_tiles < 0) nblk_tiles = 0;
   if (nblk_tiles > ntiles) nblk_tiles = ntiles;
-  DISPATCH_RANK(max_rank, launch_d, mats, tiles, ntiles, nblk_tiles, rbu, rows_per_cta, bucket, P, Q, q_scale, sketch, tables,
+  DISPATCH_RANK(max_rank, launch_d, mats, tiles, ntiles, nblk_tiles, rbu, bulk, status, rows_per_cta, bucket, P, Q, q_scale, sketch, tables,
                 counts, dense_err, alpha, beta, ef_mode, smem_bytes, stream);
 }
 

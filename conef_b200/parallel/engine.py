@@ -343,7 +343,7 @@ class PowerSGDEngine(_EngineBase):
         # matrices on the block layout of the hash first: they run on the atomics-free kernel, whose tile
         # is a chunk of eight (row block, cell block) units, one per warp; the others by row block
         on_blocks = [int(mats[k]["cb_off"]) >= 0 for k in range(nm)]
-        self.d_rbu = int(os.environ.get("CONEF_D_RBU", "2"))
+        self.d_rbu = int(os.environ.get("CONEF_D_RBU", "1"))
 
         def units(e, W):      # (row blocks of a unit, cell block); matrices with more than 32 windows: one row block
             nb = W // 32

@@ -192,8 +192,9 @@ def main():
             t = _time(lambda: native.check(lib.conef_psgd_decompress(
                 eng.mats_dev.data_ptr(), eng.d_tiles.data_ptr(), eng.n_d_tiles, eng.d_nblk, eng.d_rbu, eng.d_rows, buf.data_ptr(),
                 pmem.data_ptr(), qmem.data_ptr(), 1.0, eng.sketch_arena.data_ptr(), eng.tables.data_ptr(),
-                eng.counts.data_ptr(), 0, 0.1, 0.9, native.EF_SKETCH, eng.max_rank, eng.d_smem, st)), args.iters)
-            record("decompress+sketch update (shared-memory atomics)", t, 2 * mat_bytes + 2 * sk_bytes,
+                eng.counts.data_ptr(), 0, 0.1, 0.9, native.EF_SKETCH, eng.max_rank, eng.d_smem,
+                eng.status.data_ptr(), st)), args.iters)
+            record("decompress+sketch update", t, 2 * mat_bytes + 2 * sk_bytes,
                    "read M, write M_hat, r/w sketch")
         if want("segments"):
             t = _time(lambda: native.check(lib.conef_gather_segments(

@@ -370,6 +370,52 @@ def test_fused_pipeline_matches_the_long_form(single_rank_group, monkeypatch, kw
     sa.check_status()
 
 
+# matrices that reach every filling mode of the count-sketch decompress kernel's ring: 16-byte aligned starts
+# with whole groups of 32 columns (bulk copies; (44, 2048) ends in a ragged row block), a start that is not
+# aligned ((20, 640) after five elements), a ragged last group (650 columns) and a narrow sketch row that
+# keeps the per-element hash ((130, 576) at 10 %: 57 cells)
+SHAPES_BLOCKS = [(48, 1024), (16,), (100, 640), (44, 2048), (5,), (20, 640), (3,), (33, 650), (130, 576)]
+
+
+@pytest.mark.parametrize("rank", [4, 3, 8])
+@pytest.mark.parametrize("mode", ["bulk", "cp.async", "universal"])
+def test_count_sketch_decompress_modes_match_the_torch_path(single_rank_group, monkeypatch, mode, rank):
+    """The atomics-free decompress kernel (block layout of the hash; ring filled by bulk copies or by
+    cp.async) and the column-order kernel (per-element hash) against the PyTorch-ops path, which uses the
+    same tables through ``DenseCS``; SIMT products, so that the comparison is tight."""
+    monkeypatch.setenv("CONEF_TC", "0")
+    monkeypatch.setenv("CONEF_GRAPH", "0")
+    monkeypatch.setenv("CONEF_D_BULK", "0" if mode == "cp.async" else "1")
+    monkeypatch.setenv("CONEF_HASH", "universal" if mode == "universal" else "block")
+    kw = dict(matrix_approximation_rank=rank, use_error_feedback=True, warm_start=True, use_error_compression=True,
+              sketch_size=0.1)
+
+    def run(backend):
+        monkeypatch.setenv("CONEF_BACKEND", backend)
+        state = cb.PowerSGDState(None, start_powerSGD_iter=2, **kw)
+        state.iter = 2
+        b = FakeBucket(SHAPES_BLOCKS, device=DEV, seed=1)
+        plan = planlib.build_powersgd_plan(b.buffer(), b.gradients(), rank, 2)
+        g = torch.Generator().manual_seed(0)
+        state.p_memory_dict[0] = torch.zeros(plan.total_p).to(DEV)
+        state.q_memory_dict[0] = torch.randn(plan.total_q, generator=g).to(DEV)
+        outs = []
+        for i in range(5):
+            b.refill(10 + i)
+            outs.append(cb.powerSGD_hook(state, b).wait().detach().cpu().clone())
+            torch.cuda.synchronize()
+        return outs, state
+
+    native_out, st = run("native")
+    eng = st._engines[0]
+    nblk = eng.d_nblk
+    assert (nblk > 0) == (mode != "universal") and nblk < eng.n_d_tiles      # (130, 576) stays on the column kernel
+    torch_out, _ = run("torch")
+    for a, b in zip(native_out, torch_out):
+        torch.testing.assert_close(a, b, **TOL)
+    st.check_status()
+
+
 def test_hpowersgd_topk_error_native_vs_cpu(single_rank_group, monkeypatch):
     """hPowerSGD with its top-k error store: dense error records + one grouped radix select per
     step on the GPU against torch.topk per matrix on the CPU."""

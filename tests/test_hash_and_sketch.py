@@ -34,6 +34,69 @@ def test_hash_matches_int32_emulation(D, W, a, b):
     assert got.min() >= 0 and got.max() < W
 
 
+@pytest.mark.parametrize("D,W", [(5760, 576), (650, 65), (1024, 102), (70, 64), (33278, 3327)])
+def test_block_layout_of_the_hash(D, W):
+    """Block layout: columns hashed in aligned groups of 32, one group per cell block and window.  The
+    regrouped records must describe the same map as the column table, columns of one window never
+    share a cell, and every cell block receives the same number of groups (give or take the last
+    window)."""
+    idx, sign = ref.hash_table(D, W, layout="block")
+    idx, sign = idx.numpy(), sign.numpy()
+    nb, ng = W // 32, (D + 31) // 32
+    S = (ng + nb - 1) // nb
+    assert idx.min() >= 0 and idx.max() < 32 * nb
+    # inside an aligned group the 32 columns take 32 different lanes of ONE cell block
+    for g in (0, ng // 2, ng - 1):
+        cols = np.arange(32 * g, min(32 * g + 32, D))
+        assert len(set(idx[cols] // 32)) == 1 and len(set(idx[cols] % 32)) == len(cols)
+    # inside a window no two columns share a cell
+    for s in (0, S - 1):
+        cols = np.arange(32 * nb * s, min(32 * nb * (s + 1), D))
+        assert len(set(idx[cols])) == len(cols)
+    counts = np.bincount(idx, minlength=W)
+    assert counts[:32 * nb].max() - counts[:32 * nb].min() <= 1 and counts[32 * nb:].sum() == 0
+    rec = ref.block_csr(D, W, ref.DEFAULT_A, ref.DEFAULT_B).view(np.uint32).reshape(S, nb, 2)
+    seen = np.zeros(D, dtype=bool)
+    for s in range(S):
+        for c in range(nb):
+            word, bits = int(rec[s, c, 0]), int(rec[s, c, 1])
+            g, x = word & ref.NO_GROUP, word >> 27
+            if g == ref.NO_GROUP:
+                continue
+            assert s * nb <= g < (s + 1) * nb
+            lanes = np.arange(32)
+            cols = 32 * g + (lanes ^ x)
+            ok = cols < D
+            assert np.array_equal(idx[cols[ok]], 32 * c + lanes[ok])
+            assert np.array_equal(sign[cols[ok]] > 0, ((bits >> (lanes[ok] ^ x)) & 1).astype(bool))
+            seen[cols[ok]] = True
+    assert seen.all()
+
+
+def test_block_layout_is_an_unbiased_sketch(monkeypatch):
+    """Query after update returns the vector plus zero-mean noise whose energy matches the count-sketch
+    bound (each cell holds about D / W columns)."""
+    monkeypatch.setenv("CONEF_HASH", "block")
+    N, D = 64, 2048
+    torch.manual_seed(0)
+    v = torch.randn(N, D)
+    cs = DenseCS(N, D, 0.125, device="cpu")
+    assert cs.range == 256
+    cs.update(v.clone(), 1.0)
+    est = torch.zeros(N, D)
+    cs.query(est, 1.0)
+    err = est - v
+    assert abs(float(err.mean())) < 0.05
+    # per-element noise variance = (colliders per cell) * var(v) = (D / W - 1) = 7
+    assert 5.5 < float(err.var()) < 8.5
+    monkeypatch.setenv("CONEF_HASH", "universal")
+    cs2 = DenseCS(N, D, 0.125, device="cpu")
+    cs2.update(v.clone(), 1.0)
+    est2 = torch.zeros(N, D)
+    cs2.query(est2, 1.0)
+    assert float((est2 - v).var()) > 0.9 * float(err.var())      # the block layout is not noisier
+
+
 def test_sign_split_reference_config():
     idx, sign = ref.hash_table(5760, 576)
     assert idx.min() == 0 and idx.max() == 575
