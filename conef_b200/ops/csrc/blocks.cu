@@ -282,10 +282,131 @@ static int seg_cta_count(long long total) {
   return (int)(n > 32 ? 32 : n);
 }
 
+// The same pass over the block layout of the hash (conef_cell, layout 1; the table arena holds the
+// matrix's S x nb records {g | x_g << 27, sign bits}, window-major, at cb_off).  A warp's unit is
+// (block of RB_MAX_ROWS rows, cell block c): it walks the S column groups of its cell block, lane l
+// handles column 32 g + (l xor x_g), whose cell is 32 c + l for every group.  The cell block's sums and
+// its old sketch values therefore sit in the lanes' registers: no atomics and no copy of sketch rows in
+// shared memory; the gradient travels through a per-warp cp.async ring (three groups in flight).
+// Tile = (tensor, chunk of eight consecutive units).
+constexpr int RBK_STAGES = 4;
+__global__ void __launch_bounds__(256, 3)
+k_randblock_gather_sketch_blk(const ConefBlk* __restrict__ blks, const int2* __restrict__ tiles,
+                              float* __restrict__ bucket, float* __restrict__ staging, float gather_scale,
+                              float* __restrict__ sketch, const int32_t* __restrict__ tables,
+                              const int32_t* __restrict__ counts, float alpha, float beta, const SegGather SG,
+                              const ConefPublish pub) {
+  constexpr int RB = RB_MAX_ROWS;
+  __shared__ float ring_all[8][RBK_STAGES][RB][32];
+  if ((int)blockIdx.x >= SG.tile_ctas) {
+    seg_gather_ctas(SG, bucket);
+  } else {
+    const int2 t = tiles[blockIdx.x];
+    const ConefBlk B = blks[t.x];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int m = B.m, W = B.W, nb = W >> 5;
+    const int unit = t.y * 8 + warp;
+    if (unit < ((B.n + RB - 1) / RB) * nb) {
+      const int rbk = unit / nb, c = unit - rbk * nb;
+      const int row0 = rbk * RB;
+      const int rows = min(RB, B.n - row0);
+      const int S = (((m + 31) >> 5) + nb - 1) / nb;
+      const int2* recs = reinterpret_cast<const int2*>(tables + B.cb_off) + c;
+      const float gs = gather_scale != 0.f ? gather_scale : (float)B.numel / (float)B.block;
+      const float omb = 1.f - beta;
+      float* g0 = bucket + B.g_off + (size_t)row0 * m;
+      const int cell = (c << 5) + lane;
+      float* sc0 = sketch + B.sk_off + (size_t)row0 * W + cell;
+      const float kcnt = (float)__ldg(counts + B.cnt_off + cell);
+      const long long end = B.start + B.block, wrap = end - B.numel;
+      // bit ii of `touched`: the block covers or cuts row ii (the same value in every thread)
+      unsigned touched = 0;
+      float so[RB], acc[RB];
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii) {
+        acc[ii] = 0.f;
+        so[ii] = 0.f;
+        if (ii < rows) {
+          const long long r0 = (long long)(row0 + ii) * m, r1 = r0 + m;
+          const long long c1 = max(0LL, min(r1, end) - max(r0, B.start)) + max(0LL, min(r1, wrap) - r0);
+          if (c1 > 0) touched |= 1u << ii;
+          so[ii] = sc0[(size_t)ii * W];
+        }
+      }
+      const uint32_t ring = (uint32_t)__cvta_generic_to_shared(&ring_all[warp][0][0][lane]);
+      const unsigned pitch = (unsigned)m * 4u;
+      auto row_ptr = [&](float* base, int ii) {
+        return reinterpret_cast<float*>(reinterpret_cast<char*>(base) + (unsigned long long)pitch * (unsigned)ii);
+      };
+      for (int s0 = 0; s0 < S; s0 += 32) {
+        int2 mine = make_int2(0x7ffffff, 0);
+        if (s0 + lane < S) mine = __ldg(recs + (size_t)(s0 + lane) * nb);
+        const int cnt = min(32, S - s0);
+        auto column = [&](int i) {      // this lane's column in group i of the chunk (m: none)
+          const int rx = __shfl_sync(0xffffffffu, mine.x, i & 31);
+          const int g = rx & 0x7ffffff;
+          return (i < cnt && g != 0x7ffffff) ? (g << 5) + (lane ^ (int)((uint32_t)rx >> 27)) : m;
+        };
+        auto issue = [&](int i) {
+          const int cl = column(i);
+          if (cl < m) {
+            const uint32_t dst = ring + (uint32_t)(i & (RBK_STAGES - 1)) * (RB * 128);
+#pragma unroll
+            for (int ii = 0; ii < RB; ++ii)
+              if (ii < rows) cp_async_f32<0>(dst + ii * 128, row_ptr(g0 + cl, ii));
+          }
+          cp_async_commit();
+        };
+#pragma unroll
+        for (int k = 0; k < RBK_STAGES - 1; ++k) issue(k);
+        for (int i = 0; i < cnt; ++i) {
+          issue(i + RBK_STAGES - 1);
+          const int col = column(i);
+          const uint32_t sbits = (uint32_t)__shfl_sync(0xffffffffu, mine.y, i & 31);
+          cp_async_wait<RBK_STAGES - 1>();      // the copies of group i have landed
+          if (col < m) {
+            const float sgn = ((sbits >> (col & 31)) & 1u) ? 1.f : -1.f;
+            const uint32_t src = ring + (uint32_t)(i & (RBK_STAGES - 1)) * (RB * 128);
+            float* gp = g0 + col;
+#pragma unroll
+            for (int ii = 0; ii < RB; ++ii) {
+              if (ii < rows) {
+                const float v = lds_f32<0>(src + ii * 128);
+                if (!((touched >> ii) & 1u)) {
+                  *row_ptr(gp, ii) = 0.f;
+                  acc[ii] = fmaf(sgn, v, acc[ii]);
+                } else {
+                  const float vv = v + alpha * sgn * so[ii];
+                  long long sp;
+                  if (in_block(B, (long long)(row0 + ii) * m + col, &sp)) {
+                    staging[sp] = vv * gs;
+                  } else {
+                    *row_ptr(gp, ii) = 0.f;
+                    acc[ii] = fmaf(sgn, vv, acc[ii]);
+                  }
+                }
+              }
+            }
+          }
+        }
+        cp_async_wait<0>();
+      }
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii) {
+        if (ii < rows) {
+          const float fct = ((touched >> ii) & 1u) ? 1.f - omb * kcnt : 1.f + (alpha - omb) * kcnt;
+          sc0[(size_t)ii * W] = fmaf(so[ii], fct, acc[ii]);
+        }
+      }
+    }
+  }
+  conef_publish_if_last(pub, gridDim.x);
+}
+
 // segs / total_unc / staging_unc: the uncompressed tensors (may be empty).  done != NULL with
 // world > 1: the CTA that finishes last stores epoch (+ *epoch_base) into peer_flags[p][rank].
-extern "C" int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles, int ntiles, int rows_per_cta,
-                                         float* bucket, float* staging, float gather_scale, float* sketch,
+extern "C" int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles, int ntiles, int nblk_tiles,
+                                         int rows_per_cta, float* bucket, float* staging, float gather_scale, float* sketch,
                                          const int32_t* tables, const int32_t* counts, float* dense_err,
                                          int8_t* qcodes, float* qscales, float alpha, float beta, int ef_mode,
                                          size_t smem_bytes, const ConefSeg* segs, int nsegs, long long total_unc,
@@ -305,13 +426,30 @@ extern "C" int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles
     if (rows_per_cta > RB_MAX_ROWS) { conef_set_error("randblock_gather: at most %d rows per CTA", RB_MAX_ROWS); return 2; }
     smem_bytes *= 2;      // the accumulators and a copy of the old sketch rows
     if (smem_bytes > 220 * 1024) { conef_set_error("randblock_gather: sketch rows do not fit in shared memory"); return 2; }
-    SG.tile_ctas = ntiles;
+    // the first nblk_tiles tiles belong to tensors on the block layout of the hash (cb_off >= 0; a tile is a
+    // chunk of eight (row block, cell block) units); the kernel launched last carries the uncompressed
+    // tensors and the publishing tail
+    const int nblk = nblk_tiles < 0 ? 0 : (nblk_tiles > ntiles ? ntiles : nblk_tiles);
+    const int nleg = ntiles - nblk;
     if (ntiles + seg_ctas == 0) return 0;
-    CONEF_CUDA(cudaFuncSetAttribute(k_randblock_gather_sketch, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    CONEF_CUDA(cudaFuncSetAttribute(k_randblock_gather_sketch, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                    (int)cudaSharedmemCarveoutMaxShared));
-    k_randblock_gather_sketch<<<ntiles + seg_ctas, 256, smem_bytes, stream>>>(
-        blks, tiles, rows_per_cta, bucket, staging, gather_scale, sketch, tables, counts, alpha, beta, SG, pub);
+    if (nleg > 0 || nblk == 0) {
+      SegGather SL = SG;
+      ConefPublish pl = pub;
+      if (nblk > 0) { SL.total = 0; memset(&pl, 0, sizeof(pl)); }
+      SL.tile_ctas = nleg;
+      const int extra = nblk > 0 ? 0 : seg_ctas;
+      CONEF_CUDA(cudaFuncSetAttribute(k_randblock_gather_sketch, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+      CONEF_CUDA(cudaFuncSetAttribute(k_randblock_gather_sketch, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                      (int)cudaSharedmemCarveoutMaxShared));
+      k_randblock_gather_sketch<<<nleg + extra, 256, smem_bytes, stream>>>(
+          blks, tiles + nblk, rows_per_cta, bucket, staging, gather_scale, sketch, tables, counts, alpha, beta, SL, pl);
+      CONEF_CHECK_LAUNCH("k_randblock_gather_sketch");
+    }
+    if (nblk > 0) {
+      SG.tile_ctas = nblk;
+      k_randblock_gather_sketch_blk<<<nblk + seg_ctas, 256, 0, stream>>>(
+          blks, tiles, bucket, staging, gather_scale, sketch, tables, counts, alpha, beta, SG, pub);
+    }
   } else {
     SG.tile_ctas = (ntiles + 7) / 8;
     if (SG.tile_ctas + seg_ctas == 0) return 0;
@@ -322,13 +460,14 @@ extern "C" int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles
   return 0;
 }
 
-extern "C" int conef_randblock_gather(const ConefBlk* blks, const int2* tiles, int ntiles, int rows_per_cta,
+extern "C" int conef_randblock_gather(const ConefBlk* blks, const int2* tiles, int ntiles, int nblk_tiles,
+                                      int rows_per_cta,
                                       float* bucket, float* staging, float gather_scale, float* sketch,
                                       const int32_t* tables, const int32_t* counts, float* dense_err,
                                       int8_t* qcodes, float* qscales, float alpha, float beta,
                                       int ef_mode, size_t smem_bytes, cudaStream_t stream) {
   if (ntiles <= 0) return 0;
-  return conef_randblock_gather_ex(blks, tiles, ntiles, rows_per_cta, bucket, staging, gather_scale, sketch, tables,
+  return conef_randblock_gather_ex(blks, tiles, ntiles, nblk_tiles, rows_per_cta, bucket, staging, gather_scale, sketch, tables,
                                    counts, dense_err, qcodes, qscales, alpha, beta, ef_mode, smem_bytes, nullptr, 0,
                                    0, nullptr, nullptr, nullptr, 1, 0, 0, nullptr, stream);
 }

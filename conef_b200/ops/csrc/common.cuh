@@ -188,6 +188,32 @@ __device__ __forceinline__ void conef_publish_if_last(const ConefPublish& s, uns
   }
 }
 
+// cp.async into / loads from shared memory at a shared-space address plus an immediate offset
+template <int OFF>
+__device__ __forceinline__ void cp_async_f32(uint32_t dst, const void* gmem_src) {
+  asm volatile("cp.async.ca.shared.global [%0+%2], [%1], 4;" ::"r"(dst), "l"(gmem_src), "n"(OFF) : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0+%2], [%1], 16;" ::"r"(dst), "l"(gmem_src), "n"(OFF) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+template <int OFF>
+__device__ __forceinline__ float lds_f32(uint32_t src) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(src), "n"(OFF) : "memory");
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ float4 lds_f32x4(uint32_t src) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(src), "n"(OFF) : "memory");
+  return v;
+}
+
 // Philox-4x32-10 keyed by `seed` at counter `ctr`, turned into four standard normal values by
 // Box-Muller: a pure function of (seed, ctr), so every rank draws the same numbers.
 __device__ __forceinline__ void conef_philox_round(uint32_t& c0, uint32_t& c1, uint32_t& c2, uint32_t& c3,

@@ -78,6 +78,8 @@ typedef struct ConefBlk {
   int n, m, W;
   int tab_off, cnt_off;
   int scale_off;      // first scale slot of this tensor in the 8-bit store's scale array
+  int cb_off;         // block layout of the hash: offset of the regrouped records in the table arena (-1: none)
+  int pad_;
 } ConefBlk;
 
 enum { CONEF_EF_NONE = 0, CONEF_EF_DENSE = 1, CONEF_EF_SKETCH = 2, CONEF_EF_QUANT8 = 3 };
@@ -243,7 +245,10 @@ int conef_gather_segments(const ConefSeg* segs, int nsegs, const float* bucket,
 int conef_scatter_segments(const ConefSeg* segs, int nsegs, float* bucket,
                            const float* const* peer_staging, int world, const float* local_staging,
                            float scale, float* dense_err, long long total, cudaStream_t stream);
-int conef_randblock_gather(const ConefBlk* blks, const int2* tiles, int ntiles, int rows_per_cta,
+// Count-sketch mode: the first nblk_tiles tiles belong to tensors on the block layout of the hash
+// (cb_off >= 0) and are chunks of eight (block of 8 rows, cell block) units; the others are
+// (tensor, block of rows_per_cta rows).
+int conef_randblock_gather(const ConefBlk* blks, const int2* tiles, int ntiles, int nblk_tiles, int rows_per_cta,
                            float* bucket, float* staging, float gather_scale,
                            float* sketch, const int32_t* tables, const int32_t* counts,
                            float* dense_err, int8_t* qcodes, float* qscales,
@@ -252,7 +257,7 @@ int conef_randblock_gather(const ConefBlk* blks, const int2* tiles, int ntiles, 
 // The same gather with the uncompressed tensors copied into staging_unc by spare CTAs and, with
 // done != NULL and world > 1, the CTA that finishes last publishing `epoch` (+ *epoch_base) in slot
 // `rank` of every peer's flag array.
-int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles, int ntiles, int rows_per_cta,
+int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles, int ntiles, int nblk_tiles, int rows_per_cta,
                               float* bucket, float* staging, float gather_scale, float* sketch,
                               const int32_t* tables, const int32_t* counts, float* dense_err, int8_t* qcodes,
                               float* qscales, float alpha, float beta, int ef_mode, size_t smem_bytes,

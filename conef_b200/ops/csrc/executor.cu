@@ -398,7 +398,8 @@ extern "C" int conef_randblock_run(ConefRandblockPlan* plan, int phases, cudaStr
     const uint32_t ep = plan->epoch + 1;
     if (phases & 1) {
       RUNB(conef_randblock_gather_ex(
-          plan->blks, (const int2*)plan->tiles.tiles, plan->nblks ? plan->tiles.n : 0, plan->rows_per_cta, plan->work,
+          plan->blks, (const int2*)plan->tiles.tiles, plan->nblks ? plan->tiles.n : 0, plan->nblk_tiles,
+          plan->rows_per_cta, plan->work,
           plan->local_blk[slot], plan->unbiased ? 0.0f : 1.0f,
           plan->ef_mode == CONEF_EF_SKETCH ? plan->sketch : nullptr, plan->tables, plan->counts,
           plan->ef_mode == CONEF_EF_DENSE ? plan->dense_err : nullptr, plan->qcodes, plan->qscales, plan->alpha,
@@ -427,8 +428,8 @@ extern "C" int conef_randblock_run(ConefRandblockPlan* plan, int phases, cudaStr
       RUNB(conef_gather_segments(plan->segs, plan->nsegs, plan->work, nullptr, stage_unc, plan->total_unc, s));
     if (plan->nblks)
       // gather scale 0 = unbiased estimator: the kernel divides by the selection probability
-      RUNB(conef_randblock_gather(plan->blks, (const int2*)plan->tiles.tiles, plan->tiles.n, plan->rows_per_cta,
-                                  plan->work, stage_blk, plan->unbiased ? 0.0f : 1.0f,
+      RUNB(conef_randblock_gather(plan->blks, (const int2*)plan->tiles.tiles, plan->tiles.n, plan->nblk_tiles,
+                                  plan->rows_per_cta, plan->work, stage_blk, plan->unbiased ? 0.0f : 1.0f,
                                   plan->ef_mode == CONEF_EF_SKETCH ? plan->sketch : nullptr, plan->tables,
                                   plan->counts, plan->ef_mode == CONEF_EF_DENSE ? plan->dense_err : nullptr,
                                   plan->qcodes, plan->qscales, plan->alpha, plan->beta, plan->ef_mode, plan->smem, s));

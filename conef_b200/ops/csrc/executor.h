@@ -120,7 +120,7 @@ typedef struct ConefRandblockPlan {
   float* local_unc[2];  float* local_blk[2];
   long long spin_limit;
   // per step
-  float* work;  int slot, pad0;
+  float* work;  int slot, nblk_tiles;      // nblk_tiles: leading tiles of tensors on the block layout of the hash
   unsigned int epoch;  float alpha, beta;
   int launched;
   // ---- two-launch form: gather (+ segments, publishes the epoch) and wait + reduce + scatter ----

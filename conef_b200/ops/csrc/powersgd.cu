@@ -359,31 +359,6 @@ constexpr int D_WARPS = D_THREADS / 32;
 constexpr int D_STAGES = 4;       // ring depth (a power of two)
 constexpr int D_RBU_MAX = 4;      // most row blocks per unit
 
-template <int OFF>
-__device__ __forceinline__ void cp_async_f32(uint32_t dst, const void* gmem_src) {
-  asm volatile("cp.async.ca.shared.global [%0+%2], [%1], 4;" ::"r"(dst), "l"(gmem_src), "n"(OFF) : "memory");
-}
-template <int OFF>
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* gmem_src) {
-  asm volatile("cp.async.cg.shared.global [%0+%2], [%1], 16;" ::"r"(dst), "l"(gmem_src), "n"(OFF) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-template <int OFF>
-__device__ __forceinline__ float lds_f32(uint32_t src) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(src), "n"(OFF) : "memory");
-  return v;
-}
-template <int OFF>
-__device__ __forceinline__ float4 lds_f32x4(uint32_t src) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];"
-               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(src), "n"(OFF) : "memory");
-  return v;
-}
-
 // mbarrier + bulk-copy (TMA without a tensor map) helpers of the ring's second filling mode
 // Every probe may sleep in hardware for up to the hinted time, so the limit below is seconds, and a
 // warp that waits does not spend issue slots on a spin loop.

@@ -37,7 +37,7 @@ BLK_DTYPE = np.dtype(
     [("g_off", "<i8"), ("numel", "<i8"), ("start", "<i8"), ("block", "<i8"),
      ("stage_off", "<i8"), ("sk_off", "<i8"),
      ("n", "<i4"), ("m", "<i4"), ("W", "<i4"), ("tab_off", "<i4"), ("cnt_off", "<i4"),
-     ("scale_off", "<i4")], align=True)
+     ("scale_off", "<i4"), ("cb_off", "<i4"), ("pad_", "<i4")], align=True)
 LAMB_DTYPE = np.dtype(
     [("p", "<u8"), ("g", "<u8"), ("m", "<u8"), ("v", "<u8"), ("numel", "<i8"),
      ("weight_decay", "<f4"), ("pad", "<i4")], align=True)
@@ -45,7 +45,7 @@ CORR_DTYPE = np.dtype([("t_off", "<i8"), ("x_off", "<i8", (2,)), ("l_off", "<i8"
                        ("rows_t", "<i4"), ("rows_l", "<i4"), ("c1", "<i4"), ("nterms", "<i4"),
                        ("c2", "<i4", (2,))], align=True)
 assert CORR_DTYPE.itemsize == 80
-assert MAT_DTYPE.itemsize == 104 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.itemsize == 72
+assert MAT_DTYPE.itemsize == 104 and SEG_DTYPE.itemsize == 24 and BLK_DTYPE.itemsize == 80
 assert LAMB_DTYPE.itemsize == 48
 
 EF_NONE, EF_DENSE, EF_SKETCH, EF_QUANT8 = 0, 1, 2, 3
@@ -130,7 +130,7 @@ class RandblockPlan(C.Structure):
         ("peer_unc", C.c_void_p * 2), ("peer_blk", C.c_void_p * 2),
         ("local_unc", C.c_void_p * 2), ("local_blk", C.c_void_p * 2),
         ("spin_limit", C.c_longlong),
-        ("work", C.c_void_p), ("slot", C.c_int), ("pad0", C.c_int),
+        ("work", C.c_void_p), ("slot", C.c_int), ("nblk_tiles", C.c_int),
         ("epoch", C.c_uint), ("alpha", C.c_float), ("beta", C.c_float),
         ("launched", C.c_int),
         ("has_slots", C.c_int), ("two_shot", C.c_int),
@@ -168,7 +168,7 @@ _SIGNATURES = {
     "conef_orth_last_launches": ([], C.c_int),
     "conef_gather_segments": ([vp, C.c_int, vp, vp, vp, c_ll, vp], C.c_int),
     "conef_scatter_segments": ([vp, C.c_int, vp, vp, C.c_int, vp, C.c_float, vp, c_ll, vp], C.c_int),
-    "conef_randblock_gather": ([vp, vp, C.c_int, C.c_int, vp, vp, C.c_float, vp, vp, vp, vp, vp, vp,
+    "conef_randblock_gather": ([vp, vp, C.c_int, C.c_int, C.c_int, vp, vp, C.c_float, vp, vp, vp, vp, vp, vp,
                                 C.c_float, C.c_float, C.c_int, C.c_size_t, vp], C.c_int),
     "conef_randblock_scatter": ([vp, C.c_int, vp, vp, C.c_int, vp, C.c_float, c_ll, vp], C.c_int),
     "conef_quant8_query": ([vp, vp, vp, c_ll, C.c_float, vp], C.c_int),

@@ -918,6 +918,7 @@ class RandBlockEngine(_EngineBase):
             raise native.NativeError(f"random block + {kind}: not fused")  # caller falls back
 
         blks = np.zeros(len(plan.blocks), dtype=native.BLK_DTYPE)
+        self.nblk_tiles = 0
         seeds = ref.derive_hash_seeds(getattr(state, "hash_seed", 0), 1)[0]
         arena = tab_off = cnt_off = scale_off = 0
         table_index, table_chunks, count_chunks = {}, [], []
@@ -926,7 +927,7 @@ class RandBlockEngine(_EngineBase):
             rec = blks[k]
             rec["g_off"], rec["numel"], rec["block"], rec["stage_off"] = b.g_off, b.numel, b.block, b.stage_off
             rec["n"], rec["m"] = b.n, b.m
-            rec["tab_off"], rec["cnt_off"] = -1, -1
+            rec["tab_off"], rec["cnt_off"], rec["cb_off"] = -1, -1, -1
             rec["sk_off"] = arena
             if self.ef_mode == native.EF_SKETCH:
                 W = ref.sketch_width(b.m, state.sketch_size)
@@ -935,12 +936,20 @@ class RandBlockEngine(_EngineBase):
                 key = (b.m, W)
                 if key not in table_index:
                     _, _, packed, counts = tables_for(dev, b.m, W, seeds[0], seeds[1])
-                    table_index[key] = (tab_off, cnt_off)
                     table_chunks.append(packed)
                     count_chunks.append(counts)
-                    tab_off += b.m
+                    cb_off = -1
+                    csr = block_csr_for(dev, b.m, W, seeds[0], seeds[1])      # block layout: regrouped records
+                    if csr is not None:
+                        pad = (tab_off + b.m) & 1
+                        if pad:
+                            table_chunks.append(torch.zeros(1, dtype=torch.int32, device=dev))
+                        cb_off = tab_off + b.m + pad
+                        table_chunks.append(csr)
+                    table_index[key] = (tab_off, cnt_off, cb_off)
+                    tab_off = sum(int(c.numel()) for c in table_chunks)
                     cnt_off += W
-                rec["tab_off"], rec["cnt_off"] = table_index[key]
+                rec["tab_off"], rec["cnt_off"], rec["cb_off"] = table_index[key]
                 arena += b.n * W
             else:
                 arena += b.numel
@@ -956,7 +965,14 @@ class RandBlockEngine(_EngineBase):
                 raise native.NativeError(f"sketch width {maxW} does not fit in shared memory")
             self.rows = int(max(1, min(8, SMEM_BUDGET // (maxW * 8))))     # accumulators + a copy of the old rows
             self.smem = self.rows * maxW * 4
-            tiles = [(k, rb) for k, b in enumerate(plan.blocks) for rb in range(math.ceil(b.n / self.rows))]
+            # tensors on the block layout of the hash first: their tile is a chunk of eight (block of 8 rows,
+            # cell block) units of the atomics-free kernel; the others go by blocks of `rows` rows
+            on_blocks = [int(blks[k]["cb_off"]) >= 0 for k in range(len(plan.blocks))]
+            tiles = [(k, ch) for k, b in enumerate(plan.blocks) if on_blocks[k]
+                     for ch in range(math.ceil(math.ceil(b.n / 8) * (int(blks[k]["W"]) // 32) / 8))]
+            self.nblk_tiles = len(tiles)
+            tiles += [(k, rb) for k, b in enumerate(plan.blocks) if not on_blocks[k]
+                      for rb in range(math.ceil(b.n / self.rows))]
         else:
             self.rows, self.smem = 0, 0
             tiles = [(k, g) for k, b in enumerate(plan.blocks) for g in range((b.numel + QGROUP - 1) // QGROUP)]
@@ -1037,6 +1053,7 @@ class RandBlockEngine(_EngineBase):
         P, plan, ptr = native.RandblockPlan(), self.plan, native.ptr
         P.blks, P.nblks, P.rows_per_cta = ptr(self.blks_dev), len(plan.blocks), self.rows
         P.tiles = native.TileList(ptr(self.tiles) if self.n_tiles else None, self.n_tiles, 0)
+        P.nblk_tiles = self.nblk_tiles
         P.segs, P.nsegs, P.ef_mode = ptr(self.segs_dev), len(plan.segs), self.ef_mode
         P.total_unc, P.total_block = plan.total_unc, plan.total_block
         P.staging_unc, P.staging_blk = ptr(self.staging_unc), ptr(self.staging_blk)

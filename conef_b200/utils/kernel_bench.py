@@ -229,7 +229,7 @@ def main():
         sk = native.ptr(eng.err_arena) if eng.ef_mode == native.EF_SKETCH else 0
         de = native.ptr(eng.err_arena) if eng.ef_mode == native.EF_DENSE else 0
         t = _time(lambda: native.check(lib.conef_randblock_gather(
-            eng.blks_dev.data_ptr(), eng.tiles.data_ptr(), eng.n_tiles, eng.rows, buf.data_ptr(),
+            eng.blks_dev.data_ptr(), eng.tiles.data_ptr(), eng.n_tiles, eng.nblk_tiles, eng.rows, buf.data_ptr(),
             eng.staging_blk.data_ptr(), 1.0, sk, native.ptr(eng.tables), native.ptr(eng.counts), de,
             native.ptr(eng.codes), native.ptr(eng.scales), 1.0 - beta, beta, eng.ef_mode, eng.smem, st)), args.iters,
             prep=refill)

@@ -416,6 +416,36 @@ def test_count_sketch_decompress_modes_match_the_torch_path(single_rank_group, m
     st.check_status()
 
 
+@pytest.mark.parametrize("layout", ["block", "universal"])
+def test_randomblock_count_sketch_on_the_block_layout(single_rank_group, monkeypatch, layout):
+    """Random block + count sketch on tensors wide enough for the block layout of the hash (the
+    atomics-free gather that walks cell blocks) against the PyTorch-ops path on the CPU; with the
+    per-element hash the same tensors run on the column-order kernel."""
+    monkeypatch.setenv("CONEF_HASH", layout)
+    kw = dict(use_error_feedback=True, use_error_compression=True, sketch_size=0.1)
+
+    def run(device, backend):
+        monkeypatch.setenv("CONEF_BACKEND", backend)
+        s = cb.RandomBlockState(None, start_compression_iter=2, compression_ratio=0.13, **kw)
+        s.iter = 2
+        b = FakeBucket(SHAPES_BLOCKS, device=device, seed=1)
+        outs = []
+        for i in range(5):
+            b.refill(10 + i)
+            outs.append(cb.RandomBlock_hook(s, b).wait().detach().cpu().clone())
+            if device != "cpu":
+                torch.cuda.synchronize()
+        return outs, s
+
+    a, sa = run(DEV, "native")
+    eng = sa._engines[0]
+    assert (eng.nblk_tiles > 0) == (layout == "block") and eng.nblk_tiles < eng.n_tiles
+    c, _ = run("cpu", "torch")
+    for x, y in zip(a, c):
+        torch.testing.assert_close(x, y, **TOL)
+    sa.check_status()
+
+
 def test_hpowersgd_topk_error_native_vs_cpu(single_rank_group, monkeypatch):
     """hPowerSGD with its top-k error store: dense error records + one grouped radix select per
     step on the GPU against torch.topk per matrix on the CPU."""
