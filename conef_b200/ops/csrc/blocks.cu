@@ -116,14 +116,40 @@ __device__ __forceinline__ void seg_gather_ctas(const SegGather& S, const float*
   }
 }
 
-// Flat mapping: tile = (tensor, group of 256 consecutive elements), one warp
+// Flat mapping: tile = (tensor, run of `groups_per_tile` groups of 256 consecutive elements), one warp
 // per tile.  Modes NONE / DENSE / QUANT8.
 //   v = g + error ; selected -> staging (times gather_scale), kept error 0
 //                 ; not selected -> gradient zeroed, kept error v
-__global__ void __launch_bounds__(256)
+// A warp walks its groups with the loads of the next group in flight while it works on the current
+// one: with a single group per warp the two dependent loads in front of the data (tile, tensor
+// record) left the memory pipe idle for most of a warp's life.
+struct FlatLoad {
+  float v[QGROUP / 32];      // gradient
+  float e[QGROUP / 32];      // dense error, or the 8-bit code as a float
+  float old_scale;
+};
+__device__ __forceinline__ void flat_load(const ConefBlk& B, long long group, int lane, const float* __restrict__ g,
+                                          const float* __restrict__ dense_err, const int8_t* __restrict__ qcodes,
+                                          const float* __restrict__ qscales, int ef_mode, FlatLoad& L) {
+  const long long base = group * QGROUP;
+  L.old_scale = ef_mode == CONEF_EF_QUANT8 ? qscales[(long long)B.scale_off + group] : 0.f;
+#pragma unroll
+  for (int k = 0; k < QGROUP / 32; ++k) {
+    const long long idx = base + lane + 32 * k;
+    L.v[k] = 0.f;
+    L.e[k] = 0.f;
+    if (idx < B.numel) {
+      L.v[k] = g[idx];
+      if (ef_mode == CONEF_EF_DENSE) L.e[k] = dense_err[B.sk_off + idx];
+      else if (ef_mode == CONEF_EF_QUANT8) L.e[k] = (float)qcodes[B.sk_off + idx];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256, 3)
 k_randblock_gather_flat(const ConefBlk* __restrict__ blks, const int2* __restrict__ tiles, int ntiles,
-                        float* __restrict__ bucket, float* __restrict__ staging, float gather_scale,
-                        float* __restrict__ dense_err, int8_t* __restrict__ qcodes,
+                        int groups_per_tile, float* __restrict__ bucket, float* __restrict__ staging,
+                        float gather_scale, float* __restrict__ dense_err, int8_t* __restrict__ qcodes,
                         float* __restrict__ qscales, float alpha, float beta, int ef_mode, const SegGather SG,
                         const ConefPublish pub) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,56 +159,63 @@ k_randblock_gather_flat(const ConefBlk* __restrict__ blks, const int2* __restric
   } else if (tile < ntiles) {
     const int2 t = tiles[tile];
     const ConefBlk B = blks[t.x];
-    const long long base = (long long)t.y * QGROUP;
     float* g = bucket + B.g_off;
     // gather_scale == 0 selects the unbiased estimator: divide by the selection probability
     const float gs = gather_scale != 0.f ? gather_scale : (float)B.numel / (float)B.block;
-    float keep[QGROUP / 32];
-    float amax = 0.f;
-    float old_scale = 0.f;
     // the tensor's codes start at sk_off in the code arena; its groups are aligned to the tensor start
-    const long long qbase = B.sk_off + base;             // code offset
-    const long long sidx = (long long)B.scale_off + t.y;  // scale slot of this group
-    if (ef_mode == CONEF_EF_QUANT8) old_scale = qscales[sidx];
-#pragma unroll
-    for (int k = 0; k < QGROUP / 32; ++k) {
-      const long long idx = base + lane + 32 * k;
-      keep[k] = 0.f;
-      if (idx < B.numel) {
-        float v = g[idx];
-        float carry = 0.f;
-        if (ef_mode == CONEF_EF_DENSE) v += dense_err[B.sk_off + idx];
-        else if (ef_mode == CONEF_EF_QUANT8) {
-          const float e = (float)qcodes[qbase + lane + 32 * k] * old_scale;
-          v += alpha * e;
-          carry = beta * e;
-        }
-        long long sp;
-        if (in_block(B, idx, &sp)) {
-          staging[sp] = v * gs;
-          keep[k] = carry;
-        } else {
-          g[idx] = 0.f;
-          keep[k] = carry + v;
-        }
-        if (ef_mode == CONEF_EF_DENSE) dense_err[B.sk_off + idx] = keep[k];
-        amax = fmaxf(amax, fabsf(keep[k]));
-      }
-    }
-    if (ef_mode == CONEF_EF_QUANT8) {
-      amax = warp_max(amax);
-      const float scale = amax / 127.f;
-      const float inv = scale > 0.f ? 1.f / scale : 0.f;
+    const long long ngroups = (B.numel + QGROUP - 1) / QGROUP;
+    const long long first = (long long)t.y * groups_per_tile;
+    const int count = (int)min((long long)groups_per_tile, ngroups - first);
+    FlatLoad cur, nxt;
+    if (count > 0) flat_load(B, first, lane, g, dense_err, qcodes, qscales, ef_mode, cur);
+#pragma unroll 1
+    for (int q = 0; q < count; ++q) {
+      const long long group = first + q;
+      if (q + 1 < count) flat_load(B, group + 1, lane, g, dense_err, qcodes, qscales, ef_mode, nxt);
+      const long long base = group * QGROUP;
+      float keep[QGROUP / 32];
+      float amax = 0.f;
 #pragma unroll
       for (int k = 0; k < QGROUP / 32; ++k) {
         const long long idx = base + lane + 32 * k;
+        keep[k] = 0.f;
         if (idx < B.numel) {
-          float q = rintf(keep[k] * inv);
-          q = fminf(fmaxf(q, -127.f), 127.f);
-          qcodes[qbase + lane + 32 * k] = (int8_t)q;
+          float v = cur.v[k];
+          float carry = 0.f;
+          if (ef_mode == CONEF_EF_DENSE) v += cur.e[k];
+          else if (ef_mode == CONEF_EF_QUANT8) {
+            const float e = cur.e[k] * cur.old_scale;
+            v += alpha * e;
+            carry = beta * e;
+          }
+          long long sp;
+          if (in_block(B, idx, &sp)) {
+            staging[sp] = v * gs;
+            keep[k] = carry;
+          } else {
+            g[idx] = 0.f;
+            keep[k] = carry + v;
+          }
+          if (ef_mode == CONEF_EF_DENSE) dense_err[B.sk_off + idx] = keep[k];
+          amax = fmaxf(amax, fabsf(keep[k]));
         }
       }
-      if (lane == 0) qscales[sidx] = scale;
+      if (ef_mode == CONEF_EF_QUANT8) {
+        amax = warp_max(amax);
+        const float scale = amax / 127.f;
+        const float inv = scale > 0.f ? 1.f / scale : 0.f;
+#pragma unroll
+        for (int k = 0; k < QGROUP / 32; ++k) {
+          const long long idx = base + lane + 32 * k;
+          if (idx < B.numel) {
+            float qv = rintf(keep[k] * inv);
+            qv = fminf(fmaxf(qv, -127.f), 127.f);
+            qcodes[B.sk_off + idx] = (int8_t)qv;
+          }
+        }
+        if (lane == 0) qscales[(long long)B.scale_off + group] = scale;
+      }
+      cur = nxt;
     }
   }
   conef_publish_if_last(pub, gridDim.x);
@@ -453,8 +486,10 @@ extern "C" int conef_randblock_gather_ex(const ConefBlk* blks, const int2* tiles
   } else {
     SG.tile_ctas = (ntiles + 7) / 8;
     if (SG.tile_ctas + seg_ctas == 0) return 0;
+    // rows_per_cta: groups of 256 elements per warp tile in these modes (0 or 1: one)
     k_randblock_gather_flat<<<SG.tile_ctas + seg_ctas, 256, 0, stream>>>(
-        blks, tiles, ntiles, bucket, staging, gather_scale, dense_err, qcodes, qscales, alpha, beta, ef_mode, SG, pub);
+        blks, tiles, ntiles, rows_per_cta > 1 ? rows_per_cta : 1, bucket, staging, gather_scale, dense_err, qcodes,
+        qscales, alpha, beta, ef_mode, SG, pub);
   }
   CONEF_CHECK_LAUNCH("k_randblock_gather");
   return 0;

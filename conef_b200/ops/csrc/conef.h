@@ -114,6 +114,15 @@ typedef struct ConefOrthExtra {
   // all of them at once; otherwise, and when either is zero, as three launches.
   uint32_t* bar;
   int max_rank;
+  // With `cl_list` (cl_nmat device entries {record, unused}: the records whose blocks the tile list covers)
+  // and `cl_max_rows` (an upper bound of their row counts) every block is orthogonalised by one
+  // thread-block cluster of eight CTAs that keep the block's rows in shared memory, exchange Gram
+  // partials through distributed shared memory and meet at the cluster barrier; taken when a CTA's
+  // share of the largest block fits in shared memory, before the one-launch form above.
+  int cl_nmat;
+  const int2* cl_list;
+  int cl_max_rows;
+  int pad_;
 } ConefOrthExtra;
 
 const char* conef_last_error(void);

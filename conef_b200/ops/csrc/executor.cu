@@ -27,6 +27,16 @@ inline int copy_floats(float* dst, const float* src, long long n, cudaStream_t s
   return (int)cudaMemcpyAsync(dst, src, (size_t)n * sizeof(float), cudaMemcpyDeviceToDevice, s);
 }
 
+// A tile list's `pad` entries behind its `n` tiles name the records it covers: the cluster form of the
+// Gram-Schmidt kernel goes by record, not by chunk of rows.
+inline void set_cluster_list(const ConefPsgdPlan* plan, const ConefTileList& tl, ConefOrthExtra& X) {
+  if (plan->one_launch_orth && plan->orth_max_rows > 0 && tl.pad > 0) {
+    X.cl_list = (const int2*)tl.tiles + tl.n;
+    X.cl_nmat = tl.pad;
+    X.cl_max_rows = plan->orth_max_rows;
+  }
+}
+
 int orth(ConefPsgdPlan* plan, int which, const ConefTileList& tl, float* buf, float eps,
          const float* const* peers, const uint32_t* flags, int world, uint32_t epoch, bool packed,
          cudaStream_t s, const uint32_t* eb = nullptr) {
@@ -36,6 +46,7 @@ int orth(ConefPsgdPlan* plan, int which, const ConefTileList& tl, float* buf, fl
   memset(&X, 0, sizeof(X));
   X.bar = (plan->one_launch_orth && plan->done_word) ? plan->done_word + 1 : nullptr;    // one launch when it fits
   X.max_rank = plan->max_rank;
+  set_cluster_list(plan, tl, X);
   RUN(conef_orthogonalize_fused(plan->mats, (const int2*)tl.tiles, tl.n, which, buf, eps,
                                 world > 1 ? peers : nullptr, flags, world, epoch, plan->status,
                                 world > 1 ? plan->spin_limit : 0, pk, plan->np_cols, plan->gram, eb, &X, s));
@@ -123,6 +134,7 @@ static int run_fused(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint
     memset(&X, 0, sizeof(X));
     X.bar = plan->one_launch_orth ? plan->done_word + 1 : nullptr;
     X.max_rank = plan->max_rank;
+    set_cluster_list(plan, plan->orth_q, X);
     if (sketch) { X.zero0 = plan->zpk; X.zero0_n = plan->zpk_n; X.tables = plan->tables; X.nm = nm; X.alpha = plan->alpha; }
     if (plan->total_unc) {
       X.seg_mode = 1; X.nsegs = plan->nsegs; X.segs = plan->segs; X.seg_total = plan->total_unc;
@@ -152,6 +164,7 @@ static int run_fused(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint
       RUN(conef_wait_flags_ex(plan->my_flags, ws, ep1, plan->status, spin, eb, s));
     X.bar = plan->one_launch_orth ? plan->done_word + 1 : nullptr;
     X.max_rank = plan->max_rank;
+    set_cluster_list(plan, plan->orth_p, X);
     X.zero0 = plan->local_p[slot ^ 1]; X.zero0_n = tp + tu;
     X.zero1 = plan->local_q[slot ^ 1]; X.zero1_n = tq + tz;
     if (plan->total_unc) {

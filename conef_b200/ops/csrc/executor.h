@@ -41,7 +41,8 @@ typedef struct ConefPsgdPlan {
   float* qz2;
   float* qpk;
   float* ppk;
-  const ConefSeg* segs;  int nsegs, pad0;  long long total_unc;
+  const ConefSeg* segs;  int nsegs, orth_max_rows;  long long total_unc;      // orth_max_rows: most rows of any P or Q block
+                                                                             // (0: no cluster form of the Gram-Schmidt kernel)
   float* staging;
   const void* tc_maps;
   ConefTileList tc_p, simt_p;

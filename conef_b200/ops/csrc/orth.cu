@@ -500,6 +500,253 @@ k_orth_one(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
   }
 }
 
+// ---------------------------------------------------------------------------
+// The same orthogonalisation with one thread-block cluster per block of rows to orthogonalise: the
+// OCL CTAs of a cluster split the block's rows evenly, keep their rows in shared memory for the whole
+// kernel, exchange their Gram partials through distributed shared memory and meet at the cluster's
+// hardware barrier.  Against k_orth_one (one barrier over ALL CTAs of the launch through two words in
+// global memory, partials through L2) a round costs a cluster barrier and eight remote shared-memory
+// reads per Gram entry.  Every CTA sums the partials in rank order, so all CTAs (and all GPUs) hold the
+// same bits.  `list[c].x` is the record of cluster c.
+constexpr int OCL = 8;      // CTAs per cluster (the portable maximum)
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(const float* local_smem, uint32_t rank) {
+  const uint32_t la = (uint32_t)__cvta_generic_to_shared(local_smem);
+  uint32_t ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(la), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+
+template <int RP>
+__global__ void __launch_bounds__(OC_THREADS)
+k_orth_cluster(const ConefMat* __restrict__ mats, const int2* __restrict__ list, int nmat, int which,
+               float* __restrict__ buf, const float* const* __restrict__ peer_bufs,
+               const uint32_t* __restrict__ flags, int world, uint32_t epoch, int* __restrict__ status,
+               long long spin_limit, const uint32_t* __restrict__ epoch_base, float eps, float* __restrict__ packed,
+               int packed_np, const ConefOrthExtra X) {
+  extern __shared__ float xs[];                    // this CTA's rows, row stride RP + 1
+  constexpr int S = RP + 1;
+  constexpr int PAIRS_MAX = RP * RP;
+  __shared__ float G[RP][RP + 1], R[RP][RP + 1], Ri[RP][RP + 1];
+  __shared__ float part[OC_THREADS / 32][PAIRS_MAX < 32 ? 32 : PAIRS_MAX > 256 ? 256 : PAIRS_MAX];
+  __shared__ float gpart[2][PAIRS_MAX];            // this CTA's Gram partial of each round, read by the cluster
+  __shared__ int ok;
+  bool peers_ok = true;
+  if (world > 1) {
+    if (threadIdx.x == 0) {
+      if (epoch_base != nullptr) epoch += *epoch_base;
+      ok = wait_flags_bounded(flags, world, epoch, spin_limit) ? 1 : 0;
+      if (!ok) atomicExch(status, CONEF_STATUS_FLAG_TIMEOUT);
+    }
+    __syncthreads();
+    peers_ok = ok != 0;     // on a timeout the CTA still takes part in the barriers, on zeros
+  }
+  if (peers_ok) {
+    const long long stride = (long long)gridDim.x * OC_THREADS;
+    const long long first = (long long)blockIdx.x * OC_THREADS + threadIdx.x;
+    for (long long i = first; i < X.zero0_n; i += stride) X.zero0[i] = 0.f;
+    for (long long i = first; i < X.zero1_n; i += stride) X.zero1[i] = 0.f;
+  }
+  const int tile_ctas = nmat * OCL;
+  if ((int)blockIdx.x >= tile_ctas) {              // spare clusters: the uncompressed tensors; no barriers
+    if (!peers_ok) return;
+    const long long stride = (long long)(gridDim.x - tile_ctas) * OC_THREADS;
+    for (long long e = (long long)(blockIdx.x - tile_ctas) * OC_THREADS + threadIdx.x; e < X.seg_total; e += stride) {
+      const int s = orth_find_seg(X.segs, X.nsegs, e);
+      const long long src = X.segs[s].src_off + (e - X.segs[s].dst_off);
+      if (X.seg_mode == 1) {
+        float v = X.bucket[src];
+        if (X.dense_err) { v += X.dense_err[src]; X.dense_err[src] = v; }
+        X.staging[e] = v;
+      } else {
+        float v = 0.f;
+        for (int p = 0; p < world; ++p) v += ld_relaxed_sys_f32(X.peer_staging[p] + e);
+        v *= X.seg_scale;
+        X.bucket[src] = v;
+        if (X.dense_err) X.dense_err[src] -= v;
+      }
+    }
+    return;
+  }
+  const int rec = list[blockIdx.x / OCL].x;
+  const uint32_t rank = cluster_rank();
+  const ConefMat M = mats[rec];
+  const int rows_total = which == 0 ? M.n : M.m, r = M.r;
+  const int rows_per = (rows_total + OCL - 1) / OCL;
+  const long long grow0 = (long long)rank * rows_per;
+  const int rows = max(0, min(rows_per, rows_total - (int)grow0));
+  const size_t off = (which == 0 ? M.p_off : M.q_off) + (size_t)grow0 * r;
+  float* a = buf + off;
+  // ---- load this CTA's rows (summing the peers' copies) ----
+  for (int i = threadIdx.x; i < rows * r; i += OC_THREADS) {
+    float v = 0.f;
+    if (peer_bufs != nullptr) {
+      if (peers_ok) for (int p = 0; p < world; ++p) v += ld_relaxed_sys_f32(peer_bufs[p] + off + i);
+    } else {
+      v = a[i];
+    }
+    const int row = i / r;
+    xs[row * S + (i - row * r)] = v;
+  }
+  const int pairs = r * r;
+  float* pk = packed ? packed + (which == 0 ? M.ppk_off : M.qpk_off) : nullptr;
+  const bool project = X.tables != nullptr && which == 1 && pk != nullptr && M.tab_off >= 0;
+  const int32_t* tab = project ? X.tables + M.tab_off : nullptr;
+  float* zpk = project ? packed + mats[X.nm + rec].qpk_off : nullptr;
+  const float refill_scale = rsqrtf((float)rows_total);
+
+#pragma unroll 1
+  for (int round = 0; round < 2; ++round) {
+    __syncthreads();
+    // ---- Gram partial of this CTA's rows, fixed summation order: warps over row slices, then warps in order ----
+    if (pairs <= 256) {
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+      const int per = (rows + (OC_THREADS / 32) - 1) / (OC_THREADS / 32);
+      const int i0 = warp * per, i1 = min(rows, i0 + per);
+      for (int pr = lane; pr < pairs; pr += 32) {
+        const int ca = pr / r, cb = pr - ca * r;
+        float acc = 0.f;
+        for (int i = i0; i < i1; ++i) acc = fmaf(xs[i * S + ca], xs[i * S + cb], acc);
+        part[warp][pr] = acc;
+      }
+      __syncthreads();
+      if ((int)threadIdx.x < pairs) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < OC_THREADS / 32; ++w) acc += part[w][threadIdx.x];
+        gpart[round][threadIdx.x] = acc;
+      }
+    } else {
+      for (int pr = threadIdx.x; pr < pairs; pr += OC_THREADS) {
+        const int ca = pr / r, cb = pr - ca * r;
+        float acc = 0.f;
+        for (int i = 0; i < rows; ++i) acc = fmaf(xs[i * S + ca], xs[i * S + cb], acc);
+        gpart[round][pr] = acc;
+      }
+    }
+    cluster_sync_all();      // every CTA's partial of this round is in its shared memory
+    // ---- the block's Gram matrix: the cluster's partials in rank order; factor; inverse ----
+    for (int i = threadIdx.x; i < RP * (RP + 1); i += OC_THREADS) { (&R[0][0])[i] = 0.f; (&Ri[0][0])[i] = 0.f; }
+    for (int pr = threadIdx.x; pr < pairs; pr += OC_THREADS) {
+      float gv[OCL];
+#pragma unroll
+      for (int c = 0; c < OCL; ++c) gv[c] = ld_dsmem_f32(&gpart[round][pr], (uint32_t)c);
+      float acc = 0.f;
+#pragma unroll
+      for (int c = 0; c < OCL; ++c) acc += gv[c];
+      G[pr / r][pr % r] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) chol_inverse<RP>(G, R, Ri, r, round == 0 ? ORTH_SHIFT : ORTH_SHIFT_FINAL, round == 0 ? eps : 0.f);
+    __syncthreads();
+    // ---- apply: every thread its rows ----
+    for (int i = threadIdx.x; i < rows; i += OC_THREADS) {
+      float av[RP];
+#pragma unroll
+      for (int k = 0; k < RP; ++k) av[k] = xs[i * S + k];
+      float psc = 0.f;
+      long long ph = 0;
+      if (round == 1 && project) {
+        const int e = tab[grow0 + i];
+        psc = unpack_sign(e) * X.alpha;
+        ph = unpack_bucket(e);
+      }
+#pragma unroll
+      for (int c = 0; c < RP; ++c) {
+        if (c < r) {
+          float v = 0.f;
+#pragma unroll
+          for (int k = 0; k <= c; ++k) v = fmaf(av[k], Ri[k][c], v);
+          if (round == 0) {
+            xs[i * S + c] = v;
+          } else {
+            a[(size_t)i * r + c] = v;
+            if (packed) conef_pack_store(packed, M, which, grow0 + i, c, v, packed_np);
+            if (project) atomicAdd(zpk + conef_packed_offset(ph, c, packed_np), psc * v);
+          }
+        }
+      }
+    }
+  }
+  // ---- columns that were exactly zero: fixed pseudo-random values instead (rare; not unrolled) ----
+#pragma unroll 1
+  for (int c = 0; c < r; ++c) {
+    if (R[c][c] > 0.f) continue;
+    for (int i = threadIdx.x; i < rows; i += OC_THREADS) {
+      float z[4];
+      conef_philox_normal4(ORTH_REFILL_SEED + (unsigned long long)rec * 64ull + (unsigned long long)which * 32ull + c,
+                           (uint64_t)(grow0 + i), z);
+      const float v = z[0] * refill_scale;
+      a[(size_t)i * r + c] = v;
+      if (packed) conef_pack_store(packed, M, which, grow0 + i, c, v, packed_np);
+      if (project) {
+        const int e = tab[grow0 + i];
+        atomicAdd(zpk + conef_packed_offset(unpack_bucket(e), c, packed_np), unpack_sign(e) * X.alpha * v);
+      }
+    }
+  }
+  cluster_sync_all();      // no CTA leaves while a neighbour may still read its partials
+}
+
+// *launched: false when the rows of the largest block do not fit in shared memory or the device cannot
+// hold one cluster; the caller then takes another form.
+template <int RP>
+static int launch_orth_cluster(const ConefMat* mats, const int2* list, int nmat, int max_rows, int seg_ctas, int which,
+                               float* buf, float eps, const float* const* peer_bufs, const uint32_t* flags, int world,
+                               uint32_t epoch, int* status, long long spin_limit, float* packed, int packed_np,
+                               const uint32_t* epoch_base, const ConefOrthExtra& X, cudaStream_t stream,
+                               bool* launched) {
+  *launched = false;
+  const size_t smem = (size_t)((max_rows + OCL - 1) / OCL) * (RP + 1) * sizeof(float);
+  if (smem > 180 * 1024) return 0;
+  static size_t configured[64] = {};      // largest opt-in so far, per device
+  static int cluster_ok[64] = {};         // 1: clusters of OCL CTAs can be scheduled, -1: they cannot
+  int dev = 0;
+  CONEF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return 0;
+  if (smem > configured[dev]) {      // static + dynamic shared memory may pass 48 KB well before the dynamic part does
+    CONEF_CUDA(cudaFuncSetAttribute(k_orth_cluster<RP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured[dev] = smem;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  const int spare = (seg_ctas + OCL - 1) / OCL * OCL;
+  cfg.gridDim = dim3((unsigned)(nmat * OCL + spare), 1, 1);
+  cfg.blockDim = dim3(OC_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = OCL;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  static size_t probed[64] = {};          // shared memory the answer below was obtained with
+  if (cluster_ok[dev] == 0 || smem > probed[dev]) {
+    probed[dev] = smem;
+    int nclusters = 0;
+    const cudaError_t e = cudaOccupancyMaxActiveClusters(&nclusters, k_orth_cluster<RP>, &cfg);
+    cluster_ok[dev] = (e == cudaSuccess && nclusters > 0) ? 1 : -1;
+    if (e != cudaSuccess) (void)cudaGetLastError();
+  }
+  if (cluster_ok[dev] < 0) return 0;
+  CONEF_CUDA(cudaLaunchKernelEx(&cfg, k_orth_cluster<RP>, mats, list, nmat, which, buf, peer_bufs, flags, world, epoch,
+                                status, spin_limit, epoch_base, eps, packed, packed_np, X));
+  *launched = true;
+  return 0;
+}
+
 template <int RP>
 static int launch_orth_one(const ConefMat* mats, const int2* tiles, int ntiles, int seg_ctas, int which, float* buf,
                            float eps, const float* const* peer_bufs, const uint32_t* flags, int world, uint32_t epoch,
@@ -549,6 +796,23 @@ extern "C" int conef_orthogonalize_fused(const ConefMat* mats, const int2* tiles
   }
   if (ntiles <= 0 && seg_ctas == 0 && X.zero0_n <= 0 && X.zero1_n <= 0) return 0;
   if (ntiles < 0) ntiles = 0;
+  if (ntiles > 0 && X.cl_list != nullptr && X.cl_nmat > 0 && X.cl_max_rows > 0 && X.max_rank > 0 &&
+      X.max_rank <= OC_MAXR) {
+    // one cluster per block when a CTA's share of the largest block fits in shared memory
+    bool launched = false;
+    int rc;
+#define CONEF_ORTH_CL(RP)                                                                                        \
+    rc = launch_orth_cluster<RP>(mats, X.cl_list, X.cl_nmat, X.cl_max_rows, seg_ctas, which, buf, eps, peer_bufs, \
+                                 flags, world, epoch, status, spin_limit, packed, packed_np, epoch_base, X, stream, \
+                                 &launched)
+    if (X.max_rank <= 4) CONEF_ORTH_CL(4);
+    else if (X.max_rank <= 8) CONEF_ORTH_CL(8);
+    else if (X.max_rank <= 16) CONEF_ORTH_CL(16);
+    else CONEF_ORTH_CL(32);
+#undef CONEF_ORTH_CL
+    if (rc != 0) return rc;
+    if (launched) { g_orth_launches = 1; return 0; }
+  }
   if (ntiles > 0 && X.bar != nullptr && X.max_rank > 0 && X.max_rank <= OC_MAXR) {
     // one launch when all tile CTAs can be resident together
     bool launched = false;

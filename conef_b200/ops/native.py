@@ -73,7 +73,7 @@ class PsgdPlan(C.Structure):
         ("qz", C.c_void_p), ("total_q", C.c_longlong), ("total_z", C.c_longlong),
         ("pu", C.c_void_p), ("total_p", C.c_longlong), ("total_u", C.c_longlong),
         ("u_old", C.c_void_p), ("qz2", C.c_void_p), ("qpk", C.c_void_p), ("ppk", C.c_void_p),
-        ("segs", C.c_void_p), ("nsegs", C.c_int), ("pad0", C.c_int), ("total_unc", C.c_longlong),
+        ("segs", C.c_void_p), ("nsegs", C.c_int), ("orth_max_rows", C.c_int), ("total_unc", C.c_longlong),
         ("staging", C.c_void_p), ("tc_maps", C.c_void_p),
         ("tc_p", TileList), ("simt_p", TileList),
         ("qset_all", QSet), ("qset_grad", QSet), ("qset_err", QSet),
@@ -111,6 +111,7 @@ class OrthExtra(C.Structure):
         ("seg_scale", C.c_float),
         ("alpha", C.c_float), ("nm", C.c_int), ("tables", C.c_void_p),
         ("bar", C.c_void_p), ("max_rank", C.c_int),
+        ("cl_nmat", C.c_int), ("cl_list", C.c_void_p), ("cl_max_rows", C.c_int), ("pad_", C.c_int),
     ]
 
 

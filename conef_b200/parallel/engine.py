@@ -320,10 +320,19 @@ class PowerSGDEngine(_EngineBase):
         OC = 512
         chunk = lambda ks, field: [(k, c) for k in ks for c in range(math.ceil(int(mats[k][field]) / OC))]
         tl = lambda lst: (self._tiles(lst), len(lst))
-        self.orth_tiles = {(0, "grad"): tl(chunk(range(nm), "n")), (1, "grad"): tl(chunk(range(nm), "m")),
-                           (0, "err"): tl(chunk(range(nm, nrec), "n") if self.lowrank else [])}
+
+        def orth_list(ks, field):
+            """(tiles, number of tiles, number of records): the tiles by chunk of rows, followed by one entry
+            per record for the form that gives every block a thread-block cluster."""
+            ks, lst = list(ks), chunk(ks, field)
+            return self._tiles(lst + [(k, int(mats[k][field])) for k in ks]), len(lst), len(ks)
+        self.orth_tiles = {(0, "grad"): orth_list(range(nm), "n"), (1, "grad"): orth_list(range(nm), "m"),
+                           (0, "err"): orth_list(range(nm, nrec) if self.lowrank else [], "n")}
+        self.orth_max_rows = 0
+        if nrec and os.environ.get("CONEF_ORTH_CLUSTER", "1") == "1":
+            self.orth_max_rows = int(max(int(mats["n"].max()), int(mats["m"][:nm].max())))
         self.chunks_n, self.chunks_m = tl(chunk(range(nm), "n")), tl(chunk(range(nm), "m"))
-        max_tiles = max((n for _, n in self.orth_tiles.values()), default=1)
+        max_tiles = max((n for _, n, _ in self.orth_tiles.values()), default=1)
         self.gram = torch.zeros(max(max_tiles, 1) * 2 * 1024, device=dev, dtype=torch.float32)
 
         # decompress: rows per CTA in {8, 4, 2, 1}: the most that fit in shared memory (one
@@ -531,7 +540,7 @@ class PowerSGDEngine(_EngineBase):
     # (utils/kernel_bench.py) times them.  A training step goes through the native executor.
     def _orth(self, which: int, subset: str, buf: torch.Tensor, eps: float, st, peers=0, flags=0, world=1, epoch=0,
               packed: bool = False) -> None:
-        tiles, n = self.orth_tiles[(which, subset)]
+        tiles, n, _ = self.orth_tiles[(which, subset)]
         if not n:
             return
         native.check(self.lib.conef_orthogonalize_packed(
@@ -664,8 +673,10 @@ class PowerSGDEngine(_EngineBase):
         P.qset_all, P.qset_grad, P.qset_err = qset("all"), qset("grad"), qset("err")
         P.d_tiles, P.d_rows, P.d_smem = tl(self.d_tiles, self.n_d_tiles), self.d_rows, self.d_smem
         P.d_nblk, P.d_rbu = self.d_nblk, self.d_rbu
-        P.orth_q, P.orth_p = tl(*self.orth_tiles[(1, "grad")]), tl(*self.orth_tiles[(0, "grad")])
-        P.orth_u = tl(*self.orth_tiles[(0, "err")])
+        otl = lambda t, n, nmat: native.TileList(ptr(t) if n else None, n, nmat if n else 0)
+        P.orth_q, P.orth_p = otl(*self.orth_tiles[(1, "grad")]), otl(*self.orth_tiles[(0, "grad")])
+        P.orth_u = otl(*self.orth_tiles[(0, "err")])
+        P.orth_max_rows = self.orth_max_rows
         P.chunks_n, P.chunks_m = tl(*self.chunks_n), tl(*self.chunks_m)
         P.gram = ptr(self.gram)
         if self.lowrank:
@@ -974,8 +985,10 @@ class RandBlockEngine(_EngineBase):
             tiles += [(k, rb) for k, b in enumerate(plan.blocks) if not on_blocks[k]
                       for rb in range(math.ceil(b.n / self.rows))]
         else:
-            self.rows, self.smem = 0, 0
-            tiles = [(k, g) for k, b in enumerate(plan.blocks) for g in range((b.numel + QGROUP - 1) // QGROUP)]
+            # flat modes: `rows` is the number of 256-element groups a warp walks (loads of the next group in flight)
+            self.rows, self.smem = int(os.environ.get("CONEF_RB_GROUPS", "8")), 0
+            tiles = [(k, g) for k, b in enumerate(plan.blocks)
+                     for g in range(math.ceil(((b.numel + QGROUP - 1) // QGROUP) / self.rows))]
         self.n_tiles = len(tiles)
         self.tiles = torch.from_numpy(np.asarray(tiles, dtype=np.int32).reshape(-1, 2)).to(dev) if tiles else None
         segs = np.zeros(len(plan.segs), dtype=native.SEG_DTYPE)

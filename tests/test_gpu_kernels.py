@@ -161,9 +161,10 @@ def test_orthogonalize_kernel():
         off += n * r
 
 
-def _orth_on_device(blocks, eps=0.0, which=0, one_launch=False):
+def _orth_on_device(blocks, eps=0.0, which=0, one_launch=False, cluster=False):
     """Runs the native orthogonalisation on a list of (n x r) CPU blocks; returns the results.
-    ``one_launch``: the single-kernel form with two barriers among its CTAs."""
+    ``one_launch``: the single-kernel form with two barriers among its CTAs; ``cluster``: one
+    thread-block cluster per block (Gram partials through distributed shared memory)."""
     mats = np.zeros(len(blocks), dtype=native.MAT_DTYPE)
     off, tiles = 0, []
     for k, b in enumerate(blocks):
@@ -173,10 +174,21 @@ def _orth_on_device(blocks, eps=0.0, which=0, one_launch=False):
         tiles += [(k, c) for c in range((n + 511) // 512)]
     dev = torch.cat([b.reshape(-1) for b in blocks]).float().to(DEV)
     md = native.upload_struct_array(mats, torch.device(DEV))
-    td = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    td = torch.tensor(tiles + [(k, b.shape[0]) for k, b in enumerate(blocks)], dtype=torch.int32, device=DEV)
     gram = torch.zeros(2 * len(tiles) * 1024, device=DEV)
     status = torch.zeros(4, dtype=torch.int32, device=DEV)
-    if one_launch:
+    if cluster:
+        extra = native.OrthExtra()
+        extra.max_rank = max(b.shape[1] for b in blocks)
+        extra.cl_list, extra.cl_nmat = td.data_ptr() + 8 * len(tiles), len(blocks)
+        extra.cl_max_rows = max(b.shape[0] for b in blocks)
+        native.check(native.lib().conef_orthogonalize_fused(md.data_ptr(), td.data_ptr(), len(tiles), which,
+                                                            dev.data_ptr(), eps, 0, 0, 1, 0, status.data_ptr(), 0, 0, 16,
+                                                            gram.data_ptr(), 0, C.byref(extra), _st()))
+        torch.cuda.synchronize()
+        assert native.lib().conef_orth_last_launches() == 1, "the cluster form was not taken"
+        assert int(status[0]) == 0
+    elif one_launch:
         bar = torch.zeros(2, dtype=torch.int32, device=DEV)
         extra = native.OrthExtra()
         extra.bar, extra.max_rank = bar.data_ptr(), max(b.shape[1] for b in blocks)
@@ -199,13 +211,16 @@ def _orth_on_device(blocks, eps=0.0, which=0, one_launch=False):
 
 @pytest.mark.parametrize("shapes", [[(1000, 4), (37, 3), (5000, 8), (9, 1), (30528, 8)], [(700, 20), (2000, 16)],
                                     [(1500, 32), (600, 27)]], ids=["r<=8", "r<=32a", "r<=32b"])
-def test_orthogonalize_one_launch_matches_three_kernels(shapes):
-    """The single-launch form (rows kept in shared memory, two barriers among the CTAs) against the
-    three-kernel form and the column-by-column oracle, including a zero column."""
+@pytest.mark.parametrize("form", ["one_launch", "cluster"])
+def test_orthogonalize_one_launch_matches_three_kernels(shapes, form):
+    """The single-launch forms (rows kept in shared memory; two barriers among all CTAs, or one
+    thread-block cluster per block with Gram partials read through distributed shared memory) against
+    the three-kernel form and the column-by-column oracle, including a zero column and blocks with
+    fewer rows than a cluster has CTAs."""
     torch.manual_seed(7)
     blocks = [torch.randn(n, r) for n, r in shapes]
     blocks[0][:, -1] = 0
-    one = _orth_on_device([b.clone() for b in blocks], one_launch=True)
+    one = _orth_on_device([b.clone() for b in blocks], one_launch=form == "one_launch", cluster=form == "cluster")
     three = _orth_on_device([b.clone() for b in blocks], one_launch=False)
     for k, (b, x, y) in enumerate(zip(blocks, one, three)):
         torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-5)
@@ -230,7 +245,8 @@ def test_orthogonalize_kernel_keeps_nearly_dependent_columns(relres):
         a[:, 3] = 0.7 * a[:, 0] - 1.3 * a[:, 1] + relres * torch.randn(n, generator=g, dtype=torch.float64)
         a[:, 6] = a[:, 2] + a[:, 5] + relres * torch.randn(n, generator=g, dtype=torch.float64)
         blocks.append(a.float())
-    for a, q in zip(blocks + blocks, _orth_on_device(blocks) + _orth_on_device(blocks, one_launch=True)):
+    for a, q in zip(blocks * 3, _orth_on_device(blocks) + _orth_on_device(blocks, one_launch=True)
+                    + _orth_on_device(blocks, cluster=True)):
         q = q.double()
         assert bool((q.norm(dim=0) > 0.99).all()), q.norm(dim=0)
         torch.testing.assert_close(q.t() @ q, torch.eye(8, dtype=torch.float64), rtol=0, atol=1e-4)
