@@ -29,11 +29,11 @@ inline int copy_floats(float* dst, const float* src, long long n, cudaStream_t s
 
 // A tile list's `pad` entries behind its `n` tiles name the records it covers: the cluster form of the
 // Gram-Schmidt kernel goes by record, not by chunk of rows.
-inline void set_cluster_list(const ConefPsgdPlan* plan, const ConefTileList& tl, ConefOrthExtra& X) {
-  if (plan->one_launch_orth && plan->orth_max_rows > 0 && tl.pad > 0) {
+inline void set_cluster_list(const ConefPsgdPlan* plan, const ConefTileList& tl, int max_rows, ConefOrthExtra& X) {
+  if (plan->one_launch_orth && plan->orth_max_rows > 0 && tl.pad > 0 && max_rows > 0) {
     X.cl_list = (const int2*)tl.tiles + tl.n;
     X.cl_nmat = tl.pad;
-    X.cl_max_rows = plan->orth_max_rows;
+    X.cl_max_rows = max_rows;
   }
 }
 
@@ -46,7 +46,8 @@ int orth(ConefPsgdPlan* plan, int which, const ConefTileList& tl, float* buf, fl
   memset(&X, 0, sizeof(X));
   X.bar = (plan->one_launch_orth && plan->done_word) ? plan->done_word + 1 : nullptr;    // one launch when it fits
   X.max_rank = plan->max_rank;
-  set_cluster_list(plan, tl, X);
+  set_cluster_list(plan, tl, &tl == &plan->orth_q ? plan->orth_rows_q : &tl == &plan->orth_p ? plan->orth_rows_p
+                                                                                             : plan->orth_rows_u, X);
   RUN(conef_orthogonalize_fused(plan->mats, (const int2*)tl.tiles, tl.n, which, buf, eps,
                                 world > 1 ? peers : nullptr, flags, world, epoch, plan->status,
                                 world > 1 ? plan->spin_limit : 0, pk, plan->np_cols, plan->gram, eb, &X, s));
@@ -134,7 +135,7 @@ static int run_fused(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint
     memset(&X, 0, sizeof(X));
     X.bar = plan->one_launch_orth ? plan->done_word + 1 : nullptr;
     X.max_rank = plan->max_rank;
-    set_cluster_list(plan, plan->orth_q, X);
+    set_cluster_list(plan, plan->orth_q, plan->orth_rows_q, X);
     if (sketch) { X.zero0 = plan->zpk; X.zero0_n = plan->zpk_n; X.tables = plan->tables; X.nm = nm; X.alpha = plan->alpha; }
     if (plan->total_unc) {
       X.seg_mode = 1; X.nsegs = plan->nsegs; X.segs = plan->segs; X.seg_total = plan->total_unc;
@@ -164,7 +165,7 @@ static int run_fused(ConefPsgdPlan* plan, int phases, cudaStream_t s, const uint
       RUN(conef_wait_flags_ex(plan->my_flags, ws, ep1, plan->status, spin, eb, s));
     X.bar = plan->one_launch_orth ? plan->done_word + 1 : nullptr;
     X.max_rank = plan->max_rank;
-    set_cluster_list(plan, plan->orth_p, X);
+    set_cluster_list(plan, plan->orth_p, plan->orth_rows_p, X);
     X.zero0 = plan->local_p[slot ^ 1]; X.zero0_n = tp + tu;
     X.zero1 = plan->local_q[slot ^ 1]; X.zero1_n = tq + tz;
     if (plan->total_unc) {

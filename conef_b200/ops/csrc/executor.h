@@ -101,6 +101,7 @@ typedef struct ConefPsgdPlan {
   float* zpk;  long long zpk_n;  // packed small operands of the sketch records inside qpk
   int one_launch_orth;           // 1: orthogonalisations as one launch with two CTA barriers (done_word[1..2])
   int wait_kernel;               // 1 (world > 1): a one-CTA kernel waits for the peers' epoch ahead of each consumer
+  int orth_rows_q, orth_rows_p, orth_rows_u, pad3;   // most rows of a block in each Gram-Schmidt tile list
 } ConefPsgdPlan;
 
 // ---- random-block family ---------------------------------------------------------------------------

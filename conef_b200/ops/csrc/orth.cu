@@ -394,11 +394,22 @@ k_orth_one(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
   const int nel = rows * r;
   const bool vec4 = peer_bufs == nullptr && (r & 3) == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0;
   if (vec4) {      // 16-byte loads of this GPU's own rows: an element group never straddles a row
-    for (int q = threadIdx.x; q < (nel >> 2); q += OC_THREADS) {
-      const float4 v4 = __ldcg(reinterpret_cast<const float4*>(a) + q);
-      const int i = q << 2, row = i / r;
-      float* x = xs + row * S + (i - row * r);
-      x[0] = v4.x; x[1] = v4.y; x[2] = v4.z; x[3] = v4.w;
+    for (int q0 = 0; q0 < (nel >> 2); q0 += 4 * OC_THREADS) {
+      float4 v4[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int q = q0 + u * OC_THREADS + threadIdx.x;
+        if (q < (nel >> 2)) v4[u] = __ldcg(reinterpret_cast<const float4*>(a) + q);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int q = q0 + u * OC_THREADS + threadIdx.x;
+        if (q < (nel >> 2)) {
+          const int i = q << 2, row = i / r;
+          float* x = xs + row * S + (i - row * r);
+          x[0] = v4[u].x; x[1] = v4[u].y; x[2] = v4[u].z; x[3] = v4[u].w;
+        }
+      }
     }
   }
   for (int base = vec4 ? nel : 0; base < nel; base += 4 * OC_THREADS) {
@@ -543,6 +554,7 @@ k_orth_one(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, in
 // reads per Gram entry.  Every CTA sums the partials in rank order, so all CTAs (and all GPUs) hold the
 // same bits.  `list[c].x` is the record of cluster c.
 constexpr int OCL = 8;      // CTAs per cluster (the portable maximum)
+constexpr int OCL_MAX_ROWS = 1024;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -626,11 +638,22 @@ k_orth_cluster(const ConefMat* __restrict__ mats, const int2* __restrict__ list,
   const int nel = rows * r;
   const bool vec4 = peer_bufs == nullptr && (r & 3) == 0 && (reinterpret_cast<uintptr_t>(a) & 15) == 0;
   if (vec4) {      // 16-byte loads of this GPU's own rows: an element group never straddles a row
-    for (int q = threadIdx.x; q < (nel >> 2); q += OC_THREADS) {
-      const float4 v4 = __ldcg(reinterpret_cast<const float4*>(a) + q);
-      const int i = q << 2, row = i / r;
-      float* x = xs + row * S + (i - row * r);
-      x[0] = v4.x; x[1] = v4.y; x[2] = v4.z; x[3] = v4.w;
+    for (int q0 = 0; q0 < (nel >> 2); q0 += 4 * OC_THREADS) {
+      float4 v4[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int q = q0 + u * OC_THREADS + threadIdx.x;
+        if (q < (nel >> 2)) v4[u] = __ldcg(reinterpret_cast<const float4*>(a) + q);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int q = q0 + u * OC_THREADS + threadIdx.x;
+        if (q < (nel >> 2)) {
+          const int i = q << 2, row = i / r;
+          float* x = xs + row * S + (i - row * r);
+          x[0] = v4[u].x; x[1] = v4[u].y; x[2] = v4[u].z; x[3] = v4[u].w;
+        }
+      }
     }
   }
   for (int base = vec4 ? nel : 0; base < nel; base += 4 * OC_THREADS) {
@@ -765,6 +788,9 @@ static int launch_orth_cluster(const ConefMat* mats, const int2* list, int nmat,
                                const uint32_t* epoch_base, const ConefOrthExtra& X, cudaStream_t stream,
                                bool* launched) {
   *launched = false;
+  // a cluster has eight CTAs for a block however tall it is: beyond OCL_MAX_ROWS rows per CTA the form that
+  // splits every block into 512-row chunks over as many CTAs as it takes is faster
+  if ((max_rows + OCL - 1) / OCL > OCL_MAX_ROWS) return 0;
   const size_t smem = (size_t)((max_rows + OCL - 1) / OCL) * (RP + 1) * sizeof(float);
   if (smem > 180 * 1024) return 0;
   static size_t configured[64] = {};      // largest opt-in so far, per device

@@ -100,6 +100,7 @@ class PsgdPlan(C.Structure):
         ("fused", C.c_int), ("has_slots", C.c_int), ("done_word", C.c_void_p),
         ("zpk", C.c_void_p), ("zpk_n", C.c_longlong),
         ("one_launch_orth", C.c_int), ("wait_kernel", C.c_int),
+        ("orth_rows_q", C.c_int), ("orth_rows_p", C.c_int), ("orth_rows_u", C.c_int), ("pad3", C.c_int),
     ]
 
 class OrthExtra(C.Structure):

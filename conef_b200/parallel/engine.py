@@ -677,6 +677,10 @@ class PowerSGDEngine(_EngineBase):
         P.orth_q, P.orth_p = otl(*self.orth_tiles[(1, "grad")]), otl(*self.orth_tiles[(0, "grad")])
         P.orth_u = otl(*self.orth_tiles[(0, "err")])
         P.orth_max_rows = self.orth_max_rows
+        mats, nm = self.mats_host, self.nm
+        P.orth_rows_q = int(mats["m"][:nm].max()) if nm else 0
+        P.orth_rows_p = int(mats["n"][:nm].max()) if nm else 0
+        P.orth_rows_u = int(mats["n"][nm:].max()) if self.lowrank and len(mats) > nm else 0
         P.chunks_n, P.chunks_m = tl(*self.chunks_n), tl(*self.chunks_m)
         P.gram = ptr(self.gram)
         if self.lowrank:

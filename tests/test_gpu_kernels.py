@@ -186,7 +186,9 @@ def _orth_on_device(blocks, eps=0.0, which=0, one_launch=False, cluster=False):
                                                             dev.data_ptr(), eps, 0, 0, 1, 0, status.data_ptr(), 0, 0, 16,
                                                             gram.data_ptr(), 0, C.byref(extra), _st()))
         torch.cuda.synchronize()
-        assert native.lib().conef_orth_last_launches() == 1, "the cluster form was not taken"
+        # blocks taller than 8 x 1024 rows go to the chunked forms (here, without barrier words: three launches)
+        want_launches = 1 if extra.cl_max_rows <= 8 * 1024 else 3
+        assert native.lib().conef_orth_last_launches() == want_launches, "unexpected form"
         assert int(status[0]) == 0
     elif one_launch:
         bar = torch.zeros(2, dtype=torch.int32, device=DEV)
