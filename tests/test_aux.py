@@ -548,3 +548,27 @@ def test_hardware_presets_print_their_settings():
     post = subprocess.run(["bash", script, "b200_8gpu_bf16_post_accumulation"], capture_output=True, text=True,
                           check=True).stdout
     assert "POST_ACCUMULATION_FP16=1" in post and "REDUCER=allreduce" in post
+
+
+def test_cluster_and_container_launch_files_parse():
+    """The SLURM batch file and the container scripts (reference: run.sub, Dockerfile, scripts/docker/*) cannot
+    run here (no scheduler, no container runtime): their shell syntax is checked and the batch file is
+    expanded with a fake `srun` to see the command a node would run."""
+    import subprocess
+    import tempfile
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ex = os.path.join(root, "examples/bert_pretraining")
+    for f in ("run.sub", "docker/build.sh", "docker/launch.sh"):
+        subprocess.run(["bash", "-n", os.path.join(ex, f)], check=True)
+    assert "conef_b200.ops.build" in open(os.path.join(ex, "Dockerfile")).read()
+    with tempfile.TemporaryDirectory() as d:
+        for name, body in (("srun", 'echo "SRUN $@"'), ("scontrol", "echo node-a; echo node-b")):
+            path = os.path.join(d, name)
+            with open(path, "w") as fh:
+                fh.write("#!/bin/bash\n" + body + "\n")
+            os.chmod(path, 0o755)
+        env = dict(os.environ, PATH=d + os.pathsep + os.environ["PATH"], SLURM_JOB_NODELIST="node-[a-b]",
+                   SLURM_JOB_NUM_NODES="2", SLURM_SUBMIT_DIR=root, PHASE="2", REDUCER="ef_powersgd", OUT=os.path.join(d, "out"))
+        out = subprocess.run(["bash", os.path.join(ex, "run.sub")], capture_output=True, text=True, check=True, env=env).stdout
+    assert "--nnodes 2" in out and "--master_addr node-a" in out and "--max_seq_length 512" in out
+    assert "--grad_reducer ef_powersgd" in out and "--init_checkpoint results/bert/phase1" in out
