@@ -123,16 +123,47 @@ __device__ __forceinline__ void seg_gather_ctas(const SegGather& S, const float*
 // A warp walks its groups with the loads of the next group in flight while it works on the current
 // one: with a single group per warp the two dependent loads in front of the data (tile, tensor
 // record) left the memory pipe idle for most of a warp's life.
+// Element k of lane `lane` in a group: PACK = false: base + lane + 32 k (4-byte accesses, any alignment);
+// PACK = true: base + 128 (k / 4) + 4 lane + k % 4, i.e. two chunks of 128 elements, four consecutive elements
+// per lane and chunk, moved as one 16-byte word (gradient, dense error) or one 4-byte word (codes) per chunk: a
+// warp's access is contiguous either way.  The packed form needs the tensor's gradient (and dense error)
+// 16-byte aligned, its codes 4-byte aligned, and a whole group (no ragged end).
 struct FlatLoad {
   float v[QGROUP / 32];      // gradient
   float e[QGROUP / 32];      // dense error, or the 8-bit code as a float
   float old_scale;
 };
+template <bool PACK>
+__device__ __forceinline__ long long flat_index(long long base, int lane, int k) {
+  return PACK ? base + 128 * (k >> 2) + 4 * lane + (k & 3) : base + lane + 32 * k;
+}
+template <bool PACK>
 __device__ __forceinline__ void flat_load(const ConefBlk& B, long long group, int lane, const float* __restrict__ g,
                                           const float* __restrict__ dense_err, const int8_t* __restrict__ qcodes,
                                           const float* __restrict__ qscales, int ef_mode, FlatLoad& L) {
+  static_assert(QGROUP == 256, "the packed form moves eight elements per lane");
   const long long base = group * QGROUP;
   L.old_scale = ef_mode == CONEF_EF_QUANT8 ? qscales[(long long)B.scale_off + group] : 0.f;
+  if (PACK) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+      const long long i0 = base + 128 * c + 4 * lane;
+      const float4 a = *reinterpret_cast<const float4*>(g + i0);
+      L.v[4 * c] = a.x; L.v[4 * c + 1] = a.y; L.v[4 * c + 2] = a.z; L.v[4 * c + 3] = a.w;
+      if (ef_mode == CONEF_EF_DENSE) {
+        const float4 d = *reinterpret_cast<const float4*>(dense_err + B.sk_off + i0);
+        L.e[4 * c] = d.x; L.e[4 * c + 1] = d.y; L.e[4 * c + 2] = d.z; L.e[4 * c + 3] = d.w;
+      } else if (ef_mode == CONEF_EF_QUANT8) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(qcodes + B.sk_off + i0);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) L.e[4 * c + j] = (float)(int8_t)((w >> (8 * j)) & 0xffu);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) L.e[4 * c + j] = 0.f;
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int k = 0; k < QGROUP / 32; ++k) {
     const long long idx = base + lane + 32 * k;
@@ -143,6 +174,84 @@ __device__ __forceinline__ void flat_load(const ConefBlk& B, long long group, in
       if (ef_mode == CONEF_EF_DENSE) L.e[k] = dense_err[B.sk_off + idx];
       else if (ef_mode == CONEF_EF_QUANT8) L.e[k] = (float)qcodes[B.sk_off + idx];
     }
+  }
+}
+
+// One tile (tensor, run of groups) of the flat gather; see k_randblock_gather_flat.
+template <bool PACK>
+__device__ __forceinline__ void flat_tile(const ConefBlk& B, long long first, int count, int lane, float* __restrict__ g,
+                                          float* __restrict__ staging, float gs, float* __restrict__ dense_err,
+                                          int8_t* __restrict__ qcodes, float* __restrict__ qscales, float alpha,
+                                          float beta, int ef_mode) {
+  FlatLoad cur, nxt;
+  if (count > 0) flat_load<PACK>(B, first, lane, g, dense_err, qcodes, qscales, ef_mode, cur);
+#pragma unroll 1
+  for (int q = 0; q < count; ++q) {
+    const long long group = first + q;
+    if (q + 1 < count) flat_load<PACK>(B, group + 1, lane, g, dense_err, qcodes, qscales, ef_mode, nxt);
+    const long long base = group * QGROUP;
+    float keep[QGROUP / 32], gout[QGROUP / 32];
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < QGROUP / 32; ++k) {
+      const long long idx = flat_index<PACK>(base, lane, k);
+      keep[k] = 0.f;
+      gout[k] = cur.v[k];
+      if (PACK || idx < B.numel) {
+        float v = cur.v[k];
+        float carry = 0.f;
+        if (ef_mode == CONEF_EF_DENSE) v += cur.e[k];
+        else if (ef_mode == CONEF_EF_QUANT8) {
+          const float e = cur.e[k] * cur.old_scale;
+          v += alpha * e;
+          carry = beta * e;
+        }
+        long long sp;
+        if (in_block(B, idx, &sp)) {
+          staging[sp] = v * gs;
+          keep[k] = carry;
+        } else {
+          gout[k] = 0.f;
+          if (!PACK) g[idx] = 0.f;
+          keep[k] = carry + v;
+        }
+        if (!PACK && ef_mode == CONEF_EF_DENSE) dense_err[B.sk_off + idx] = keep[k];
+        amax = fmaxf(amax, fabsf(keep[k]));
+      }
+    }
+    if (PACK) {      // selected elements keep their gradient value: the scatter overwrites them later
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const long long i0 = base + 128 * c + 4 * lane;
+        *reinterpret_cast<float4*>(g + i0) = make_float4(gout[4 * c], gout[4 * c + 1], gout[4 * c + 2], gout[4 * c + 3]);
+        if (ef_mode == CONEF_EF_DENSE)
+          *reinterpret_cast<float4*>(dense_err + B.sk_off + i0) =
+              make_float4(keep[4 * c], keep[4 * c + 1], keep[4 * c + 2], keep[4 * c + 3]);
+      }
+    }
+    if (ef_mode == CONEF_EF_QUANT8) {
+      amax = warp_max(amax);
+      const float scale = amax / 127.f;
+      const float inv = scale > 0.f ? 1.f / scale : 0.f;
+      uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+      for (int k = 0; k < QGROUP / 32; ++k) {
+        const long long idx = flat_index<PACK>(base, lane, k);
+        if (PACK || idx < B.numel) {
+          float qv = rintf(keep[k] * inv);
+          qv = fminf(fmaxf(qv, -127.f), 127.f);
+          if (PACK) packed[k >> 2] |= ((uint32_t)(int)qv & 0xffu) << (8 * (k & 3));
+          else qcodes[B.sk_off + idx] = (int8_t)qv;
+        }
+      }
+      if (PACK) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          *reinterpret_cast<uint32_t*>(qcodes + B.sk_off + base + 128 * c + 4 * lane) = packed[c];
+      }
+      if (lane == 0) qscales[(long long)B.scale_off + group] = scale;
+    }
+    cur = nxt;
   }
 }
 
@@ -165,57 +274,18 @@ k_randblock_gather_flat(const ConefBlk* __restrict__ blks, const int2* __restric
     // the tensor's codes start at sk_off in the code arena; its groups are aligned to the tensor start
     const long long ngroups = (B.numel + QGROUP - 1) / QGROUP;
     const long long first = (long long)t.y * groups_per_tile;
-    const int count = (int)min((long long)groups_per_tile, ngroups - first);
-    FlatLoad cur, nxt;
-    if (count > 0) flat_load(B, first, lane, g, dense_err, qcodes, qscales, ef_mode, cur);
-#pragma unroll 1
-    for (int q = 0; q < count; ++q) {
-      const long long group = first + q;
-      if (q + 1 < count) flat_load(B, group + 1, lane, g, dense_err, qcodes, qscales, ef_mode, nxt);
-      const long long base = group * QGROUP;
-      float keep[QGROUP / 32];
-      float amax = 0.f;
-#pragma unroll
-      for (int k = 0; k < QGROUP / 32; ++k) {
-        const long long idx = base + lane + 32 * k;
-        keep[k] = 0.f;
-        if (idx < B.numel) {
-          float v = cur.v[k];
-          float carry = 0.f;
-          if (ef_mode == CONEF_EF_DENSE) v += cur.e[k];
-          else if (ef_mode == CONEF_EF_QUANT8) {
-            const float e = cur.e[k] * cur.old_scale;
-            v += alpha * e;
-            carry = beta * e;
-          }
-          long long sp;
-          if (in_block(B, idx, &sp)) {
-            staging[sp] = v * gs;
-            keep[k] = carry;
-          } else {
-            g[idx] = 0.f;
-            keep[k] = carry + v;
-          }
-          if (ef_mode == CONEF_EF_DENSE) dense_err[B.sk_off + idx] = keep[k];
-          amax = fmaxf(amax, fabsf(keep[k]));
-        }
-      }
-      if (ef_mode == CONEF_EF_QUANT8) {
-        amax = warp_max(amax);
-        const float scale = amax / 127.f;
-        const float inv = scale > 0.f ? 1.f / scale : 0.f;
-#pragma unroll
-        for (int k = 0; k < QGROUP / 32; ++k) {
-          const long long idx = base + lane + 32 * k;
-          if (idx < B.numel) {
-            float qv = rintf(keep[k] * inv);
-            qv = fminf(fmaxf(qv, -127.f), 127.f);
-            qcodes[B.sk_off + idx] = (int8_t)qv;
-          }
-        }
-        if (lane == 0) qscales[(long long)B.scale_off + group] = scale;
-      }
-      cur = nxt;
+    int count = (int)min((long long)groups_per_tile, ngroups - first);
+    // packed accesses for the whole groups of a tensor whose arrays are aligned for them
+    bool pack = (reinterpret_cast<uintptr_t>(g) & 15) == 0;
+    if (ef_mode == CONEF_EF_DENSE) pack = pack && (reinterpret_cast<uintptr_t>(dense_err + B.sk_off) & 15) == 0;
+    if (ef_mode == CONEF_EF_QUANT8) pack = pack && (reinterpret_cast<uintptr_t>(qcodes + B.sk_off) & 3) == 0;
+    if (pack) {
+      const int whole = (int)max(0LL, min((long long)count, B.numel / QGROUP - first));
+      flat_tile<true>(B, first, whole, lane, g, staging, gs, dense_err, qcodes, qscales, alpha, beta, ef_mode);
+      flat_tile<false>(B, first + whole, count - whole, lane, g, staging, gs, dense_err, qcodes, qscales, alpha, beta,
+                       ef_mode);
+    } else {
+      flat_tile<false>(B, first, count, lane, g, staging, gs, dense_err, qcodes, qscales, alpha, beta, ef_mode);
     }
   }
   conef_publish_if_last(pub, gridDim.x);

@@ -721,6 +721,147 @@ k_psgd_decompress_blk(const ConefMat* __restrict__ mats, const int2* __restrict_
   }
 }
 
+// Decompress for dense error feedback and for no error feedback: M_hat = P Q^T into the bucket and, with dense
+// feedback, E' = G + E - M_hat into the error buffer.  Same machinery as k_psgd_decompress_blk without the hash:
+// tile = (matrix, block of RB rows); warp w of the CTA walks the column groups w, w + 8, w + 16, ... (the eight
+// warps together read 1 KB of every row at a time), lane l owns column 32 g + l.  G, E and the Q rows travel
+// through the per-warp cp.async ring (D_STAGES - 1 groups in flight); without error feedback only the Q rows do,
+// and the kernel is a pure store stream.  The column-order kernel it replaces for these modes issued the loads
+// of one group ahead through registers and reached 0.55 (dense) and 0.31 (none) of copy bandwidth.
+template <int RP, int RB, int MODE>      // MODE: CONEF_EF_DENSE or CONEF_EF_NONE
+__global__ void __launch_bounds__(D_THREADS, RP <= 8 ? 3 : 1)
+k_psgd_decompress_str(const ConefMat* __restrict__ mats, const int2* __restrict__ tiles, float* __restrict__ bucket,
+                      const float* __restrict__ P, const float* __restrict__ Q, float q_scale,
+                      float* __restrict__ dense_err) {
+  constexpr int NSRC = MODE == CONEF_EF_DENSE ? 2 : 0;                 // row arrays that go through the ring
+  constexpr int STAGE_BYTES = NSRC * RB * 128 + 32 * RP * 4;          // [G [RB][32] | E [RB][32]] | Q rows [32][RP]
+  constexpr int PS_BYTES = RB * RP * 4;
+  constexpr int WARP_BYTES = D_STAGES * STAGE_BYTES;
+  extern __shared__ __align__(16) unsigned char dstr_smem[];
+  const int2 t = tiles[blockIdx.x];
+  const ConefMat M = mats[t.x];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int m = M.m, r = M.r;
+  const int row0 = t.y * RB;
+  const int rows = min(RB, M.n - row0);
+  float* psf = reinterpret_cast<float*>(dstr_smem);      // P rows of the tile, shared by the warps
+  {
+    const float* p = P + M.p_off + (size_t)row0 * r;
+    for (int i = threadIdx.x; i < RB * RP; i += D_THREADS) {
+      const int ii = i / RP, cc = i - ii * RP;
+      psf[i] = (cc < r && ii < rows) ? p[(size_t)ii * r + cc] : 0.f;
+    }
+    // the pad columns of the Q rows in the ring are never copied: they meet zeros of P, but must be finite
+    float* ringf = reinterpret_cast<float*>(dstr_smem + PS_BYTES + (size_t)warp * WARP_BYTES);
+    for (int st = 0; st < D_STAGES; ++st)
+      for (int cc = 0; cc < RP; ++cc) ringf[st * (STAGE_BYTES / 4) + NSRC * RB * 32 + lane * RP + cc] = 0.f;
+  }
+  __syncthreads();
+  const uint32_t ps = (uint32_t)__cvta_generic_to_shared(dstr_smem);
+  const uint32_t ring0 = ps + PS_BYTES + warp * WARP_BYTES;
+  const uint32_t ring_g = ring0 + lane * 4;                              // G element (ii, lane) at + ii * 128
+  const uint32_t ring_q = ring0 + NSRC * RB * 128 + lane * (RP * 4);     // this lane's Q row
+  float* g0 = bucket + M.g_off + (size_t)row0 * m;
+  float* e0 = MODE == CONEF_EF_DENSE ? dense_err + M.g_off + (size_t)row0 * m : nullptr;
+  const float* q0 = Q + M.q_off;
+  const bool qvec = (r & 3) == 0 && (reinterpret_cast<uintptr_t>(q0) & 15) == 0;
+  const unsigned pitch = (unsigned)m * 4u;
+  auto row_ptr = [&](float* base, int ii) {
+    return reinterpret_cast<float*>(reinterpret_cast<char*>(base) + (unsigned long long)pitch * (unsigned)ii);
+  };
+  const int ng = (m + 31) >> 5;
+  const int total = (ng - warp + D_WARPS - 1) / D_WARPS;      // groups of this warp: warp, warp + 8, ...
+  const bool full = rows == RB;
+  int k_i = 0;
+  auto issue = [&]() {
+    if (k_i < total) {
+      const int cl = ((warp + k_i * D_WARPS) << 5) + lane;
+      if (cl < m) {
+        const uint32_t stage = (uint32_t)(k_i & (D_STAGES - 1)) * STAGE_BYTES;
+        if (MODE == CONEF_EF_DENSE) {
+#pragma unroll
+          for (int ii = 0; ii < RB; ++ii) {
+            if (full || ii < rows) {
+              cp_async_f32<0>(ring_g + stage + ii * 128, row_ptr(g0 + cl, ii));
+              cp_async_f32<0>(ring_g + stage + (RB + ii) * 128, row_ptr(e0 + cl, ii));
+            }
+          }
+        }
+        const float* qs = q0 + (size_t)cl * r;
+        if (qvec) {
+#pragma unroll
+          for (int cc = 0; cc < RP; cc += 4)
+            if (cc < r) cp_async_16<0>(ring_q + stage + cc * 4, qs + cc);
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < RP; ++cc)
+            if (cc < r) cp_async_f32<0>(ring_q + stage + cc * 4, qs + cc);
+        }
+      }
+      ++k_i;
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int k = 0; k < D_STAGES - 1; ++k) issue();
+  for (int k = 0; k < total; ++k) {
+    issue();
+    const int col = ((warp + k * D_WARPS) << 5) + lane;
+    cp_async_wait<D_STAGES - 1>();      // the copies of group k have landed
+    if (col < m) {
+      const uint32_t stage = (uint32_t)(k & (D_STAGES - 1)) * STAGE_BYTES;
+      float qv[RP];
+#pragma unroll
+      for (int cc = 0; cc < RP; cc += 4) {
+        const float4 q4 = lds_f32x4<0>(ring_q + stage + cc * 4);
+        qv[cc] = q4.x * q_scale;
+        qv[cc + 1] = q4.y * q_scale;
+        qv[cc + 2] = q4.z * q_scale;
+        qv[cc + 3] = q4.w * q_scale;
+      }
+      float* gp = g0 + col;
+      float* ep = MODE == CONEF_EF_DENSE ? e0 + col : nullptr;
+#pragma unroll
+      for (int ii = 0; ii < RB; ++ii) {
+        if (full || ii < rows) {
+          float mh = 0.f;
+#pragma unroll
+          for (int cc = 0; cc < RP; cc += 4) {
+            const float4 pv = lds_f32x4<0>(ps + (ii * RP + cc) * 4);
+            mh = fmaf(pv.x, qv[cc], mh);
+            mh = fmaf(pv.y, qv[cc + 1], mh);
+            mh = fmaf(pv.z, qv[cc + 2], mh);
+            mh = fmaf(pv.w, qv[cc + 3], mh);
+          }
+          *row_ptr(gp, ii) = mh;
+          if (MODE == CONEF_EF_DENSE) {
+            const float v = lds_f32<0>(ring_g + stage + ii * 128) + lds_f32<0>(ring_g + stage + (RB + ii) * 128);
+            __stcs(row_ptr(ep, ii), v - mh);
+          }
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+}
+
+template <int RP, int RB, int MODE>
+static int launch_d_str(const ConefMat* mats, const int2* tiles, int ntiles, float* bucket, const float* P,
+                        const float* Q, float q_scale, float* dense_err, cudaStream_t stream) {
+  constexpr int NSRC = MODE == CONEF_EF_DENSE ? 2 : 0;
+  constexpr int smem = RB * RP * 4 + D_WARPS * D_STAGES * (NSRC * RB * 128 + 32 * RP * 4);
+  static bool opted[64] = {};
+  int dev = 0;
+  CONEF_CUDA(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !opted[dev])) {
+    CONEF_CUDA(cudaFuncSetAttribute(k_psgd_decompress_str<RP, RB, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (dev >= 0 && dev < 64) opted[dev] = true;
+  }
+  k_psgd_decompress_str<RP, RB, MODE><<<ntiles, D_THREADS, smem, stream>>>(mats, tiles, bucket, P, Q, q_scale, dense_err);
+  CONEF_CHECK_LAUNCH("k_psgd_decompress_str");
+  return 0;
+}
+
 template <int RP, int RB>
 static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int nblk, int rbu, int bulk, int* status,
                        float* bucket, const float* P,
@@ -747,6 +888,15 @@ static int launch_d_rb(const ConefMat* mats, const int2* tiles, int ntiles, int 
     k_psgd_decompress_blk<RQ, RB><<<nblk, D_THREADS, blk_smem, stream>>>(mats, tiles, bucket, P, Q, q_scale, sketch,
                                                                         tables, counts, alpha, beta, rbu, bulk, status);
     CONEF_CHECK_LAUNCH("k_psgd_decompress_blk");
+  }
+  if (ef_mode == CONEF_EF_DENSE || ef_mode == CONEF_EF_NONE) {
+    const char* legacy = getenv("CONEF_D_STREAM");      // "0": the column-order kernel for these modes too
+    if (!(legacy && legacy[0] == '0')) {
+      constexpr int RQ = RP < 4 ? 4 : RP;
+      if (ef_mode == CONEF_EF_DENSE)
+        return launch_d_str<RQ, RB, CONEF_EF_DENSE>(mats, tiles, ntiles, bucket, P, Q, q_scale, dense_err, stream);
+      return launch_d_str<RQ, RB, CONEF_EF_NONE>(mats, tiles, ntiles, bucket, P, Q, q_scale, dense_err, stream);
+    }
   }
   if (ntiles > nblk) {
     k_psgd_decompress<RP, RB><<<ntiles - nblk, D_THREADS, smem, stream>>>(mats, tiles + nblk, bucket, P, Q, q_scale,

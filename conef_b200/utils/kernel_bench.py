@@ -196,6 +196,20 @@ def main():
                 eng.status.data_ptr(), st)), args.iters)
             record("decompress+sketch update", t, 2 * mat_bytes + 2 * sk_bytes,
                    "read M, write M_hat, r/w sketch")
+        if want("decompress"):      # (this part of the loop runs once, in the second iteration)
+            # dense error feedback and no error feedback: the column-order kernel (no sketch, no atomics)
+            state_d = cb.PowerSGDState(None, matrix_approximation_rank=rank, start_powerSGD_iter=2, use_error_feedback=True)
+            eng_d = PowerSGDEngine(state_d, buf, bucket.gradients(), group, "powersgd")
+            err = torch.zeros_like(buf)
+            for mode, nb, what in ((native.EF_DENSE, 4 * mat_bytes, "read M and the error, write M_hat and the error"),
+                                   (native.EF_NONE, mat_bytes, "write M_hat")):
+                t = _time(lambda: native.check(lib.conef_psgd_decompress(
+                    eng_d.mats_dev.data_ptr(), eng_d.d_tiles.data_ptr(), eng_d.n_d_tiles, 0, 1, eng_d.d_rows,
+                    buf.data_ptr(), pmem.data_ptr(), qmem.data_ptr(), 1.0, 0, 0, 0, err.data_ptr(), 1.0, 1.0, mode,
+                    eng_d.max_rank, 0, eng_d.status.data_ptr(), st)), args.iters)
+                record("decompress, dense error feedback" if mode == native.EF_DENSE else "decompress, no error feedback",
+                       t, nb, what)
+            del err, eng_d, state_d
         if want("segments"):
             t = _time(lambda: native.check(lib.conef_gather_segments(
                 eng.segs_dev.data_ptr(), len(plan.segs), buf.data_ptr(), 0, eng.staging.data_ptr(), plan.total_unc,
