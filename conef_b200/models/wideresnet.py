@@ -12,18 +12,20 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .layers import Conv2d
+
 
 class WideBlock(nn.Module):
     def __init__(self, cin, cout, dropout, stride):
         super().__init__()
         self.bn1 = nn.BatchNorm2d(cin, momentum=0.9)
-        self.conv1 = nn.Conv2d(cin, cout, 3, padding=1, bias=True)
+        self.conv1 = Conv2d(cin, cout, 3, padding=1, bias=True)
         self.drop = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
         self.bn2 = nn.BatchNorm2d(cout, momentum=0.9)
-        self.conv2 = nn.Conv2d(cout, cout, 3, stride=stride, padding=1, bias=True)
+        self.conv2 = Conv2d(cout, cout, 3, stride=stride, padding=1, bias=True)
         self.shortcut = None
         if stride != 1 or cin != cout:
-            self.shortcut = nn.Conv2d(cin, cout, 1, stride=stride, bias=True)
+            self.shortcut = Conv2d(cin, cout, 1, stride=stride, bias=True)
 
     def forward(self, x):
         y = self.drop(self.conv1(F.relu(self.bn1(x))))
@@ -37,7 +39,7 @@ class WideResNet(nn.Module):
         assert (depth - 4) % 6 == 0, "depth must be 6n + 4"
         n = (depth - 4) // 6
         widths = [16, 16 * widen_factor, 32 * widen_factor, 64 * widen_factor]
-        self.conv1 = nn.Conv2d(3, widths[0], 3, padding=1, bias=True)
+        self.conv1 = Conv2d(3, widths[0], 3, padding=1, bias=True)
         blocks, cin = [], widths[0]
         for stage, w in enumerate(widths[1:]):
             for b in range(n):

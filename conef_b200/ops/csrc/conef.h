@@ -351,6 +351,14 @@ int conef_lamb_step(const ConefLambTensor* tensors, int ntensors, const int2* ch
                     int step, int bias_correction, float grad_scale, float max_grad_norm,
                     cudaStream_t stream);
 
+// ---- column sums (colsum.cu) -------------------------------------------------
+// out[c] = sum over rows of x[row, c] for a row-major (rows x cols) matrix: the bias gradient of a convolution
+// whose output gradient lies in channels-last memory.  dtype: 0 fp32, 1 bf16, 2 fp16.  partial: scratch of
+// nparts * cols floats (one partial row per CTA, added up in CTA order by a second kernel).  Returns 2 for
+// inputs it does not take (cols % 8 != 0, cols > 2048, x not 16-byte aligned).
+int conef_colsum(const void* x, int dtype, long long rows, int cols, float* partial, int nparts, float* out,
+                 cudaStream_t stream);
+
 // ---- host implementations (cpu_ops.cu) --------------------------------------
 void conef_cpu_hash_table(int32_t* table, int32_t* counts, int D, int W, int a, int b, int sa, int sb, int layout);
 void conef_cpu_sketch_query(float* mat, const float* cs, const int32_t* table, int N, int D, int W, float alpha);
