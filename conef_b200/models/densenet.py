@@ -6,15 +6,17 @@ import math
 
 import torch
 import torch.nn as nn
+
+from .layers import BatchNorm2d
 import torch.nn.functional as F
 
 
 class _DenseLayer(nn.Module):
     def __init__(self, cin, growth):
         super().__init__()
-        self.bn1 = nn.BatchNorm2d(cin)
+        self.bn1 = BatchNorm2d(cin)
         self.conv1 = nn.Conv2d(cin, 4 * growth, 1, bias=False)
-        self.bn2 = nn.BatchNorm2d(4 * growth)
+        self.bn2 = BatchNorm2d(4 * growth)
         self.conv2 = nn.Conv2d(4 * growth, growth, 3, padding=1, bias=False)
 
     def forward(self, x):
@@ -26,7 +28,7 @@ class _DenseLayer(nn.Module):
 class _Transition(nn.Module):
     def __init__(self, cin, cout):
         super().__init__()
-        self.bn = nn.BatchNorm2d(cin)
+        self.bn = BatchNorm2d(cin)
         self.conv = nn.Conv2d(cin, cout, 1, bias=False)
 
     def forward(self, x):
@@ -48,7 +50,7 @@ class DenseNet(nn.Module):
                 stages.append(_Transition(planes, out))
                 planes = out
         self.features = nn.Sequential(*stages)
-        self.bn = nn.BatchNorm2d(planes)
+        self.bn = BatchNorm2d(planes)
         self.linear = nn.Linear(planes, num_classes)
 
     def forward(self, x):

@@ -50,3 +50,56 @@ class Conv2d(nn.Conv2d):
                 and x.is_contiguous(memory_format=torch.channels_last) and native.available()):
             return _ConvBiasFn.apply(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
         return super().forward(x)
+
+
+class _BatchNormFn(torch.autograd.Function):
+    """Training-mode batch norm over a channels-last activation: the two per-channel reductions (statistics
+    in the forward pass, the sums of dy and dy (x - mean) in the backward pass) run on the library's
+    column kernels; the two elementwise passes stay with PyTorch (``batch_norm_elemt`` /
+    ``batch_norm_backward_elemt``, the pair SyncBatchNorm is built from)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, mean, invstd, eps, count):
+        y = torch.batch_norm_elemt(x, weight, bias, mean, invstd, eps)
+        ctx.save_for_backward(x, weight, mean, invstd, count)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        from ..ops.colsum import channel_dot
+        x, weight, mean, invstd, count = ctx.saved_tensors
+        if gy.dtype != x.dtype:
+            gy = gy.to(x.dtype)
+        if not gy.is_contiguous(memory_format=torch.channels_last):
+            gy = gy.contiguous(memory_format=torch.channels_last)
+        sums = channel_dot(gy, x, mean, invstd)
+        if sums is None:
+            sum_dy, sum_dy_xmu, gw, gb = torch.batch_norm_backward_reduce(gy, x, mean, invstd, weight, True, True, True)
+        else:
+            sum_dy, sum_dy_xmu, gw, gb = sums
+        gx = torch.batch_norm_backward_elemt(gy, x, mean, invstd, weight, sum_dy, sum_dy_xmu, count) \
+            if ctx.needs_input_grad[0] else None
+        return gx, gw.to(weight.dtype), gb.to(weight.dtype), None, None, None, None
+
+
+class BatchNorm2d(nn.BatchNorm2d):
+    """``nn.BatchNorm2d`` (same parameters, buffers and ``state_dict``) whose training-mode reductions run on
+    ``conef_b200.ops.colsum`` when the input lies in channels-last memory on a GPU.  PyTorch's channels-last
+    statistics kernels reach about 0.8 TB/s on WRN-28-10's bf16 activations (55-59 us per 42 MB pass)."""
+
+    def forward(self, x):
+        if (self.training and self.track_running_stats and self.affine and self.momentum is not None
+                and x.is_cuda and x.dim() == 4 and torch.is_grad_enabled() and native.available()
+                and x.is_contiguous(memory_format=torch.channels_last)):
+            from ..ops.colsum import channel_stats
+            stats = channel_stats(x, self.eps, self.running_mean, self.running_var, self.momentum)
+            if stats is not None:
+                if self.num_batches_tracked is not None:
+                    self.num_batches_tracked.add_(1)
+                n = x.numel() // x.shape[1]
+                key = (n, x.device)
+                if getattr(self, "_count_key", None) != key:
+                    self._count = torch.full((1,), n, dtype=torch.int32, device=x.device)
+                    self._count_key = key
+                return _BatchNormFn.apply(x, self.weight, self.bias, stats[0], stats[1], self.eps, self._count)
+        return super().forward(x)

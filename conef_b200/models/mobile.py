@@ -5,6 +5,8 @@ Counterparts of the reference's ``examples/ImageClassification/models/mobilenetv
 """
 import torch
 import torch.nn as nn
+
+from .layers import BatchNorm2d
 import torch.nn.functional as F
 
 
@@ -14,14 +16,14 @@ class _InvertedResidual(nn.Module):
         mid = cin * expansion
         self.stride = stride
         self.conv1 = nn.Conv2d(cin, mid, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(mid)
+        self.bn1 = BatchNorm2d(mid)
         self.conv2 = nn.Conv2d(mid, mid, 3, stride, 1, groups=mid, bias=False)
-        self.bn2 = nn.BatchNorm2d(mid)
+        self.bn2 = BatchNorm2d(mid)
         self.conv3 = nn.Conv2d(mid, cout, 1, bias=False)
-        self.bn3 = nn.BatchNorm2d(cout)
+        self.bn3 = BatchNorm2d(cout)
         self.shortcut = None
         if stride == 1 and cin != cout:
-            self.shortcut = nn.Sequential(nn.Conv2d(cin, cout, 1, bias=False), nn.BatchNorm2d(cout))
+            self.shortcut = nn.Sequential(nn.Conv2d(cin, cout, 1, bias=False), BatchNorm2d(cout))
         self.identity = stride == 1 and cin == cout
 
     def forward(self, x):
@@ -40,7 +42,7 @@ class MobileNetV2(nn.Module):
     def __init__(self, num_classes=10):
         super().__init__()
         self.conv1 = nn.Conv2d(3, 32, 3, 1, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(32)
+        self.bn1 = BatchNorm2d(32)
         layers, cin = [], 32
         for t, c, n, s in self.cfg:
             for i in range(n):
@@ -48,7 +50,7 @@ class MobileNetV2(nn.Module):
                 cin = c
         self.layers = nn.Sequential(*layers)
         self.conv2 = nn.Conv2d(320, 1280, 1, bias=False)
-        self.bn2 = nn.BatchNorm2d(1280)
+        self.bn2 = BatchNorm2d(1280)
         self.linear = nn.Linear(1280, num_classes)
 
     def forward(self, x):
@@ -73,15 +75,15 @@ class _ShuffleUnit(nn.Module):
 
         def branch(c_in):
             return nn.Sequential(
-                nn.Conv2d(c_in, mid, 1, bias=False), nn.BatchNorm2d(mid), nn.ReLU(inplace=True),
-                nn.Conv2d(mid, mid, 3, stride, 1, groups=mid, bias=False), nn.BatchNorm2d(mid),
-                nn.Conv2d(mid, mid, 1, bias=False), nn.BatchNorm2d(mid), nn.ReLU(inplace=True))
+                nn.Conv2d(c_in, mid, 1, bias=False), BatchNorm2d(mid), nn.ReLU(inplace=True),
+                nn.Conv2d(mid, mid, 3, stride, 1, groups=mid, bias=False), BatchNorm2d(mid),
+                nn.Conv2d(mid, mid, 1, bias=False), BatchNorm2d(mid), nn.ReLU(inplace=True))
         self.right = branch(inp)
         self.left = None
         if stride == 2:
             self.left = nn.Sequential(
-                nn.Conv2d(cin, cin, 3, 2, 1, groups=cin, bias=False), nn.BatchNorm2d(cin),
-                nn.Conv2d(cin, mid, 1, bias=False), nn.BatchNorm2d(mid), nn.ReLU(inplace=True))
+                nn.Conv2d(cin, cin, 3, 2, 1, groups=cin, bias=False), BatchNorm2d(cin),
+                nn.Conv2d(cin, mid, 1, bias=False), BatchNorm2d(mid), nn.ReLU(inplace=True))
 
     def forward(self, x):
         if self.stride == 1:
@@ -99,7 +101,7 @@ class ShuffleNetV2(nn.Module):
         super().__init__()
         c1, c2, c3, c4 = self.configs[net_size]
         self.conv1 = nn.Conv2d(3, 24, 3, 1, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(24)
+        self.bn1 = BatchNorm2d(24)
         layers, cin = [], 24
         for cout, n in ((c1, 3), (c2, 7), (c3, 3)):
             layers.append(_ShuffleUnit(cin, cout, 2))
@@ -107,7 +109,7 @@ class ShuffleNetV2(nn.Module):
             cin = cout
         self.layers = nn.Sequential(*layers)
         self.conv2 = nn.Conv2d(cin, c4, 1, bias=False)
-        self.bn2 = nn.BatchNorm2d(c4)
+        self.bn2 = BatchNorm2d(c4)
         self.linear = nn.Linear(c4, num_classes)
 
     def forward(self, x):

@@ -4,13 +4,15 @@ Same family as the reference's ``examples/ImageClassification/models/resnet.py:9
 """
 import torch
 import torch.nn as nn
+
+from .layers import BatchNorm2d
 import torch.nn.functional as F
 
 
 def _shortcut(cin, cout, stride):
     if stride == 1 and cin == cout:
         return nn.Identity()
-    return nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), nn.BatchNorm2d(cout))
+    return nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), BatchNorm2d(cout))
 
 
 class BasicBlock(nn.Module):
@@ -19,9 +21,9 @@ class BasicBlock(nn.Module):
     def __init__(self, cin, planes, stride=1):
         super().__init__()
         self.conv1 = nn.Conv2d(cin, planes, 3, stride, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(planes)
+        self.bn1 = BatchNorm2d(planes)
         self.conv2 = nn.Conv2d(planes, planes, 3, 1, 1, bias=False)
-        self.bn2 = nn.BatchNorm2d(planes)
+        self.bn2 = BatchNorm2d(planes)
         self.shortcut = _shortcut(cin, planes, stride)
 
     def forward(self, x):
@@ -36,11 +38,11 @@ class Bottleneck(nn.Module):
         super().__init__()
         cout = planes * self.expansion
         self.conv1 = nn.Conv2d(cin, planes, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(planes)
+        self.bn1 = BatchNorm2d(planes)
         self.conv2 = nn.Conv2d(planes, planes, 3, stride, 1, bias=False)
-        self.bn2 = nn.BatchNorm2d(planes)
+        self.bn2 = BatchNorm2d(planes)
         self.conv3 = nn.Conv2d(planes, cout, 1, bias=False)
-        self.bn3 = nn.BatchNorm2d(cout)
+        self.bn3 = BatchNorm2d(cout)
         self.shortcut = _shortcut(cin, cout, stride)
 
     def forward(self, x):
@@ -53,7 +55,7 @@ class ResNet(nn.Module):
     def __init__(self, block, num_blocks, num_classes=10):
         super().__init__()
         self.conv1 = nn.Conv2d(3, 64, 3, 1, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(64)
+        self.bn1 = BatchNorm2d(64)
         layers, cin = [], 64
         for stage, (planes, n) in enumerate(zip((64, 128, 256, 512), num_blocks)):
             for b in range(n):

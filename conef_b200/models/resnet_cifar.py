@@ -7,6 +7,8 @@ configuration of the benchmarks.
 """
 import torch
 import torch.nn as nn
+
+from .layers import BatchNorm2d
 import torch.nn.functional as F
 
 
@@ -14,12 +16,12 @@ class _Block(nn.Module):
     def __init__(self, cin, cout, stride):
         super().__init__()
         self.conv1 = nn.Conv2d(cin, cout, 3, stride, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(cout)
+        self.bn1 = BatchNorm2d(cout)
         self.conv2 = nn.Conv2d(cout, cout, 3, 1, 1, bias=False)
-        self.bn2 = nn.BatchNorm2d(cout)
+        self.bn2 = BatchNorm2d(cout)
         self.proj = None
         if stride != 1 or cin != cout:
-            self.proj = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), nn.BatchNorm2d(cout))
+            self.proj = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), BatchNorm2d(cout))
 
     def forward(self, x):
         y = F.relu(self.bn1(self.conv1(x)))
@@ -30,7 +32,7 @@ class _Block(nn.Module):
 class CifarResNet(nn.Module):
     def __init__(self, blocks_per_stage=3, num_classes=10, widths=(16, 32, 64)):
         super().__init__()
-        self.stem = nn.Sequential(nn.Conv2d(3, widths[0], 3, 1, 1, bias=False), nn.BatchNorm2d(widths[0]), nn.ReLU())
+        self.stem = nn.Sequential(nn.Conv2d(3, widths[0], 3, 1, 1, bias=False), BatchNorm2d(widths[0]), nn.ReLU())
         layers, cin = [], widths[0]
         for i, w in enumerate(widths):
             for b in range(blocks_per_stage):

@@ -4,6 +4,8 @@ Counterpart of the reference's ``examples/ImageClassification/models/resnext.py:
 """
 import torch
 import torch.nn as nn
+
+from .layers import BatchNorm2d
 import torch.nn.functional as F
 
 
@@ -15,14 +17,14 @@ class _Block(nn.Module):
         g = cardinality * width
         cout = self.expansion * g
         self.conv1 = nn.Conv2d(cin, g, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(g)
+        self.bn1 = BatchNorm2d(g)
         self.conv2 = nn.Conv2d(g, g, 3, stride, 1, groups=cardinality, bias=False)
-        self.bn2 = nn.BatchNorm2d(g)
+        self.bn2 = BatchNorm2d(g)
         self.conv3 = nn.Conv2d(g, cout, 1, bias=False)
-        self.bn3 = nn.BatchNorm2d(cout)
+        self.bn3 = BatchNorm2d(cout)
         self.shortcut = nn.Identity()
         if stride != 1 or cin != cout:
-            self.shortcut = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), nn.BatchNorm2d(cout))
+            self.shortcut = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), BatchNorm2d(cout))
 
     def forward(self, x):
         y = F.relu(self.bn1(self.conv1(x)))
@@ -34,7 +36,7 @@ class ResNeXt(nn.Module):
     def __init__(self, num_blocks, cardinality, bottleneck_width, num_classes=10):
         super().__init__()
         self.conv1 = nn.Conv2d(3, 64, 1, bias=False)
-        self.bn1 = nn.BatchNorm2d(64)
+        self.bn1 = BatchNorm2d(64)
         layers, cin, width = [], 64, bottleneck_width
         for stage, n in enumerate(num_blocks):
             for b in range(n):

@@ -5,6 +5,8 @@ Counterparts of the reference's ``examples/ImageClassification/models/vgg.py:14-
 """
 import torch
 import torch.nn as nn
+
+from .layers import BatchNorm2d
 import torch.nn.functional as F
 
 VGG_LAYOUTS = {
@@ -23,7 +25,7 @@ class VGG(nn.Module):
             if item == "M":
                 layers.append(nn.MaxPool2d(2, 2))
             else:
-                layers += [nn.Conv2d(cin, item, 3, padding=1), nn.BatchNorm2d(item), nn.ReLU(inplace=True)]
+                layers += [nn.Conv2d(cin, item, 3, padding=1), BatchNorm2d(item), nn.ReLU(inplace=True)]
                 cin = item
         self.features = nn.Sequential(*layers)
         self.classifier = nn.Linear(512, num_classes)

@@ -12,16 +12,16 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .layers import Conv2d
+from .layers import BatchNorm2d, Conv2d
 
 
 class WideBlock(nn.Module):
     def __init__(self, cin, cout, dropout, stride):
         super().__init__()
-        self.bn1 = nn.BatchNorm2d(cin, momentum=0.9)
+        self.bn1 = BatchNorm2d(cin, momentum=0.9)
         self.conv1 = Conv2d(cin, cout, 3, padding=1, bias=True)
         self.drop = nn.Dropout(dropout) if dropout > 0 else nn.Identity()
-        self.bn2 = nn.BatchNorm2d(cout, momentum=0.9)
+        self.bn2 = BatchNorm2d(cout, momentum=0.9)
         self.conv2 = Conv2d(cout, cout, 3, stride=stride, padding=1, bias=True)
         self.shortcut = None
         if stride != 1 or cin != cout:
@@ -46,7 +46,7 @@ class WideResNet(nn.Module):
                 blocks.append(WideBlock(cin, w, dropout, stride=(1 if stage == 0 else 2) if b == 0 else 1))
                 cin = w
         self.blocks = nn.Sequential(*blocks)
-        self.bn = nn.BatchNorm2d(cin, momentum=0.9)
+        self.bn = BatchNorm2d(cin, momentum=0.9)
         self.linear = nn.Linear(cin, num_classes)
 
     def forward(self, x):

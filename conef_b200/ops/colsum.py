@@ -12,7 +12,7 @@ import torch
 from . import native
 
 _DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
-_MAX_PARTS = 592      # four CTAs per SM
+_MAX_PARTS = 296      # two CTAs per SM: the second stage walks the partial rows
 
 
 def _rows_cols(t: torch.Tensor):
@@ -41,3 +41,57 @@ def channel_sum(t: torch.Tensor) -> torch.Tensor:
             return out
     dims = [d for d in range(t.dim()) if d != 1] if t.dim() != 2 else [0]
     return t.float().sum(dim=dims)
+
+
+def _native_shape(t: torch.Tensor):
+    """(rows, cols) when the native kernels take ``t``; else None."""
+    if not (t.is_cuda and t.dtype in _DTYPES and native.available()):
+        return None
+    rc = _rows_cols(t)
+    if rc is None:
+        return None
+    rows, cols = rc
+    if cols % 8 != 0 or cols > 2048 or t.data_ptr() % 16 != 0 or rows <= 0:
+        return None
+    return rows, cols
+
+
+def channel_stats(x: torch.Tensor, eps: float, running_mean=None, running_var=None, momentum: float = 0.1):
+    """Batch-norm statistics of a channels-last activation: ``(mean, invstd)`` in fp32 with
+    ``invstd = 1 / sqrt(biased variance + eps)``, and the momentum update of the running statistics in
+    place (unbiased variance), as ``torch.batch_norm`` does in training mode.  Returns None when the
+    native kernel does not take the input (the caller then uses the library)."""
+    rc = _native_shape(x)
+    if rc is None:
+        return None
+    for r in (running_mean, running_var):
+        if r is not None and not (r.is_cuda and r.dtype == torch.float32 and r.is_contiguous()):
+            return None
+    rows, cols = rc
+    nparts = int(max(1, min(_MAX_PARTS, rows // 32)))
+    partial = torch.empty(nparts * 2 * cols, dtype=torch.float32, device=x.device)
+    mean = torch.empty(cols, dtype=torch.float32, device=x.device)
+    invstd = torch.empty(cols, dtype=torch.float32, device=x.device)
+    native.check(native.lib().conef_colstats(
+        x.data_ptr(), _DTYPES[x.dtype], rows, cols, float(eps), float(momentum), partial.data_ptr(), nparts,
+        mean.data_ptr(), invstd.data_ptr(), native.ptr(running_mean), native.ptr(running_var),
+        native.stream_ptr(x.device)), "colstats")
+    return mean, invstd
+
+
+def channel_dot(dy: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, invstd: torch.Tensor):
+    """``(sum_dy, sum_dy_xmu, grad_weight, grad_bias)`` of the batch-norm backward pass, all fp32; None
+    when the native kernel does not take the inputs."""
+    rc = _native_shape(x)
+    if rc is None or dy.dtype != x.dtype or dy.shape != x.shape or _native_shape(dy) != rc:
+        return None
+    rows, cols = rc
+    nparts = int(max(1, min(_MAX_PARTS, rows // 32)))
+    dev = x.device
+    partial = torch.empty(nparts * 2 * cols, dtype=torch.float32, device=dev)
+    out = torch.empty(4, cols, dtype=torch.float32, device=dev)
+    native.check(native.lib().conef_coldot(
+        dy.data_ptr(), x.data_ptr(), _DTYPES[x.dtype], rows, cols, mean.data_ptr(), invstd.data_ptr(),
+        partial.data_ptr(), nparts, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(),
+        native.stream_ptr(dev)), "coldot")
+    return out[0], out[1], out[2], out[3]

@@ -73,20 +73,40 @@ k_colsum_partial(const T* __restrict__ x, long long rows, int cols, long long ro
   }
 }
 
-__global__ void k_colsum_final(const float* __restrict__ partial, int nparts, int cols, float* __restrict__ out) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+// Second stage: a CTA of CF_THREADS threads adds up the partial rows of CF_COLS columns.  Thread (slice, col)
+// sums every CF_SLICES-th partial row with eight loads in flight, the slices are then added in slice order:
+// the order of the additions is fixed, and no thread walks more than nparts / CF_SLICES values.
+constexpr int CF_COLS = 32, CF_SLICES = 8, CF_THREADS = CF_COLS * CF_SLICES;
+__device__ __forceinline__ float cf_combine(const float* __restrict__ partial, int nparts, size_t part_stride, int c,
+                                            int cols, float* sm /* CF_THREADS floats */) {
+  const int col_l = threadIdx.x % CF_COLS, slice = threadIdx.x / CF_COLS;
   float s = 0.f;
-  int p = 0;
-  for (; p + 8 <= nparts; p += 8) {      // eight loads in flight, fixed order of the additions
-    float v[8];
+  if (c < cols) {
+    int p = slice;
+    for (; p + 7 * CF_SLICES < nparts; p += 8 * CF_SLICES) {
+      float v[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) v[u] = partial[(size_t)(p + u) * cols + c];
+      for (int u = 0; u < 8; ++u) v[u] = partial[(size_t)(p + u * CF_SLICES) * part_stride + c];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) s += v[u];
+      for (int u = 0; u < 8; ++u) s += v[u];
+    }
+    for (; p < nparts; p += CF_SLICES) s += partial[(size_t)p * part_stride + c];
   }
-  for (; p < nparts; ++p) s += partial[(size_t)p * cols + c];
-  out[c] = s;
+  __syncthreads();      // the scratch may still be in use by a previous call
+  sm[slice * CF_COLS + col_l] = s;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int u = 0; u < CF_SLICES; ++u) total += sm[u * CF_COLS + col_l];
+  return total;      // the same value in every slice of a column
+}
+
+__global__ void __launch_bounds__(CF_THREADS)
+k_colsum_final(const float* __restrict__ partial, int nparts, int cols, float* __restrict__ out) {
+  __shared__ float sm[CF_THREADS];
+  const int c = blockIdx.x * CF_COLS + threadIdx.x % CF_COLS;
+  const float s = cf_combine(partial, nparts, (size_t)cols, c, cols, sm);
+  if (c < cols && threadIdx.x < CF_COLS) out[c] = s;
 }
 
 template <typename T>
@@ -104,7 +124,7 @@ static int launch_colsum(const void* x, long long rows, int cols, float* partial
   }
   k_colsum_partial<T><<<nparts, CS_THREADS, smem, stream>>>((const T*)x, rows, cols, rows_per_cta, partial);
   CONEF_CHECK_LAUNCH("k_colsum_partial");
-  k_colsum_final<<<(cols + 127) / 128, 128, 0, stream>>>(partial, nparts, cols, out);
+  k_colsum_final<<<(cols + CF_COLS - 1) / CF_COLS, CF_THREADS, 0, stream>>>(partial, nparts, cols, out);
   CONEF_CHECK_LAUNCH("k_colsum_final");
   return 0;
 }
@@ -123,4 +143,204 @@ extern "C" int conef_colsum(const void* x, int dtype, long long rows, int cols, 
   if (dtype == 2) return launch_colsum<__half>(x, rows, cols, partial, nparts, out, stream);
   conef_set_error("colsum: dtype %d", dtype);
   return 1;
+}
+
+// ---------------------------------------------------------------------------
+// Batch-norm statistics over a channels-last activation: per column the sums of (x - pivot) and (x - pivot)^2
+// with pivot = x[0, c] (shifted sums: the variance does not cancel when |mean| >> std), then mean, 1 / std and
+// the running statistics in a small second kernel.  Same slab / row-group layout as k_colsum_partial.
+template <typename T> struct Load8;
+template <> struct Load8<__nv_bfloat16> {
+  static __device__ __forceinline__ void get(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+};
+template <> struct Load8<__half> {
+  static __device__ __forceinline__ void get(const __half* p, float (&v)[8]) {
+    const uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __half22float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+  }
+};
+template <> struct Load8<float> {
+  static __device__ __forceinline__ void get(const float* p, float (&v)[8]) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(p)), b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
+
+// MODE 0: s1 = sum (x - pivot), s2 = sum (x - pivot)^2, pivot = x[0, c] (`y` unused).
+// MODE 1: s1 = sum y, s2 = sum y (x - center[c]): the two sums of the batch-norm backward pass (y = dL/dout).
+// partial[blockIdx.x][0 | 1][0..cols).
+template <typename T, int MODE>
+__global__ void __launch_bounds__(CS_THREADS)
+k_colpair_partial(const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ center, long long rows,
+                  int cols, long long rows_per_cta, float* __restrict__ partial) {
+  extern __shared__ float cs_sm[];      // (row groups) x 2 x cols
+  const int chunks = cols >> 3;
+  const int groups = CS_THREADS / chunks;
+  const int cc = threadIdx.x % chunks, rr = threadIdx.x / chunks;
+  const long long r0 = (long long)blockIdx.x * rows_per_cta;
+  const long long r1 = min(rows, r0 + rows_per_cta);
+  float s1[8], s2[8], ctr[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { s1[i] = 0.f; s2[i] = 0.f; }
+  if (rr < groups) {
+    if (MODE == 0) {
+      Load8<T>::get(x + 8 * cc, ctr);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ctr[i] = center[8 * cc + i];
+    }
+    const size_t step = (size_t)groups * cols;
+    size_t off = (size_t)(r0 + rr) * cols + 8 * cc;
+    long long row = r0 + rr;
+    for (; row + groups < r1; row += 2LL * groups, off += 2 * step) {      // two rows (times two arrays) in flight
+      float a[8], b[8], ya[8], yb[8];
+      Load8<T>::get(x + off, a);
+      Load8<T>::get(x + off + step, b);
+      if (MODE == 1) { Load8<T>::get(y + off, ya); Load8<T>::get(y + off + step, yb); }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float da = a[i] - ctr[i], db = b[i] - ctr[i];
+        if (MODE == 0) { s1[i] += da + db; s2[i] = fmaf(da, da, fmaf(db, db, s2[i])); }
+        else { s1[i] += ya[i] + yb[i]; s2[i] = fmaf(ya[i], da, fmaf(yb[i], db, s2[i])); }
+      }
+    }
+    for (; row < r1; row += groups, off += step) {
+      float a[8], ya[8];
+      Load8<T>::get(x + off, a);
+      if (MODE == 1) Load8<T>::get(y + off, ya);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float da = a[i] - ctr[i];
+        if (MODE == 0) { s1[i] += da; s2[i] = fmaf(da, da, s2[i]); }
+        else { s1[i] += ya[i]; s2[i] = fmaf(ya[i], da, s2[i]); }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      cs_sm[(rr * 2 + 0) * cols + 8 * cc + i] = s1[i];
+      cs_sm[(rr * 2 + 1) * cols + 8 * cc + i] = s2[i];
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < 2 * cols; c += CS_THREADS) {
+    const int which = c / cols, col = c - which * cols;
+    float s = 0.f;
+    for (int g = 0; g < groups; ++g) s += cs_sm[(g * 2 + which) * cols + col];      // fixed order
+    partial[((size_t)blockIdx.x * 2 + which) * cols + col] = s;
+  }
+}
+
+// mean, 1 / sqrt(var + eps) (biased variance) and, when given, the running statistics
+// (running = (1 - momentum) running + momentum new; the running variance takes the unbiased estimate).
+template <typename T>
+__global__ void __launch_bounds__(CF_THREADS) k_colstats_final(const float* __restrict__ partial, int nparts, const T* __restrict__ x, long long rows,
+                                 int cols, float eps, float momentum, float* __restrict__ mean,
+                                 float* __restrict__ invstd, float* __restrict__ running_mean,
+                                 float* __restrict__ running_var) {
+  __shared__ float sm[CF_THREADS];
+  const int c = blockIdx.x * CF_COLS + threadIdx.x % CF_COLS;
+  const float s1 = cf_combine(partial, nparts, (size_t)2 * cols, c, cols, sm);
+  const float s2 = cf_combine(partial + cols, nparts, (size_t)2 * cols, c, cols, sm);
+  if (c >= cols || threadIdx.x >= CF_COLS) return;
+  const float n = (float)rows;
+  const float pivot = (float)x[c];
+  const float m1 = s1 / n;
+  const float var = fmaxf(s2 / n - m1 * m1, 0.f);
+  const float mu = pivot + m1;
+  mean[c] = mu;
+  invstd[c] = rsqrtf(var + eps);
+  if (running_mean != nullptr) running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mu;
+  if (running_var != nullptr)
+    running_var[c] = (1.f - momentum) * running_var[c] + momentum * var * (rows > 1 ? n / (n - 1.f) : 1.f);
+}
+
+// sum_dy, sum_dy_xmu and, when given, grad_weight = sum_dy_xmu * invstd and grad_bias = sum_dy
+__global__ void __launch_bounds__(CF_THREADS) k_coldot_final(const float* __restrict__ partial, int nparts, int cols,
+                               const float* __restrict__ invstd, float* __restrict__ sum_dy,
+                               float* __restrict__ sum_dy_xmu, float* __restrict__ grad_weight,
+                               float* __restrict__ grad_bias) {
+  __shared__ float sm[CF_THREADS];
+  const int c = blockIdx.x * CF_COLS + threadIdx.x % CF_COLS;
+  const float s1 = cf_combine(partial, nparts, (size_t)2 * cols, c, cols, sm);
+  const float s2 = cf_combine(partial + cols, nparts, (size_t)2 * cols, c, cols, sm);
+  if (c >= cols || threadIdx.x >= CF_COLS) return;
+  sum_dy[c] = s1;
+  sum_dy_xmu[c] = s2;
+  if (grad_weight != nullptr) grad_weight[c] = s2 * invstd[c];
+  if (grad_bias != nullptr) grad_bias[c] = s1;
+}
+
+static bool colpair_ok(const void* x, const void* y, long long rows, int cols, int nparts) {
+  if (rows <= 0 || cols <= 0 || nparts <= 0) return false;
+  if ((cols & 7) != 0 || cols > CS_MAX_COLS) return false;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(y) & 15) != 0) return false;
+  return true;
+}
+
+template <typename T, int MODE>
+static int launch_colpair(const void* x, const void* y, const float* center, long long rows, int cols, float* partial,
+                          int nparts, cudaStream_t stream) {
+  const long long rows_per_cta = (rows + nparts - 1) / nparts;
+  const int groups = CS_THREADS / (cols >> 3);
+  const size_t smem = (size_t)groups * 2 * cols * sizeof(float);
+  static size_t configured[64] = {};
+  int dev = 0;
+  CONEF_CUDA(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || smem > configured[dev])) {
+    CONEF_CUDA(cudaFuncSetAttribute(k_colpair_partial<T, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev >= 0 && dev < 64) configured[dev] = smem;
+  }
+  k_colpair_partial<T, MODE><<<nparts, CS_THREADS, smem, stream>>>((const T*)x, (const T*)y, center, rows, cols,
+                                                                  rows_per_cta, partial);
+  CONEF_CHECK_LAUNCH("k_colpair_partial");
+  return 0;
+}
+
+template <typename T>
+static int colstats_t(const void* x, long long rows, int cols, float eps, float momentum, float* partial, int nparts,
+                      float* mean, float* invstd, float* running_mean, float* running_var, cudaStream_t stream) {
+  const int rc = launch_colpair<T, 0>(x, x, nullptr, rows, cols, partial, nparts, stream);
+  if (rc != 0) return rc;
+  k_colstats_final<T><<<(cols + CF_COLS - 1) / CF_COLS, CF_THREADS, 0, stream>>>(partial, nparts, (const T*)x, rows, cols, eps, momentum,
+                                                             mean, invstd, running_mean, running_var);
+  CONEF_CHECK_LAUNCH("k_colstats_final");
+  return 0;
+}
+
+// Batch statistics of a row-major (rows x cols) activation (channels-last: rows = N H W).  partial: scratch of
+// nparts * 2 * cols floats.  running_mean / running_var may be NULL.  Returns 2 for inputs it does not take.
+extern "C" int conef_colstats(const void* x, int dtype, long long rows, int cols, float eps, float momentum,
+                              float* partial, int nparts, float* mean, float* invstd, float* running_mean,
+                              float* running_var, cudaStream_t stream) {
+  if (!colpair_ok(x, x, rows, cols, nparts)) { conef_set_error("colstats: shape or alignment not supported"); return 2; }
+  if (dtype == 0) return colstats_t<float>(x, rows, cols, eps, momentum, partial, nparts, mean, invstd, running_mean, running_var, stream);
+  if (dtype == 1) return colstats_t<__nv_bfloat16>(x, rows, cols, eps, momentum, partial, nparts, mean, invstd, running_mean, running_var, stream);
+  if (dtype == 2) return colstats_t<__half>(x, rows, cols, eps, momentum, partial, nparts, mean, invstd, running_mean, running_var, stream);
+  conef_set_error("colstats: dtype %d", dtype);
+  return 1;
+}
+
+// The two sums of the batch-norm backward pass: sum_dy[c] = sum dy, sum_dy_xmu[c] = sum dy (x - mean[c]);
+// grad_weight (= sum_dy_xmu * invstd) and grad_bias (= sum_dy) when given.  dy and x have the same dtype.
+extern "C" int conef_coldot(const void* dy, const void* x, int dtype, long long rows, int cols, const float* mean,
+                            const float* invstd, float* partial, int nparts, float* sum_dy, float* sum_dy_xmu,
+                            float* grad_weight, float* grad_bias, cudaStream_t stream) {
+  if (!colpair_ok(x, dy, rows, cols, nparts)) { conef_set_error("coldot: shape or alignment not supported"); return 2; }
+  int rc;
+  if (dtype == 0) rc = launch_colpair<float, 1>(x, dy, mean, rows, cols, partial, nparts, stream);
+  else if (dtype == 1) rc = launch_colpair<__nv_bfloat16, 1>(x, dy, mean, rows, cols, partial, nparts, stream);
+  else if (dtype == 2) rc = launch_colpair<__half, 1>(x, dy, mean, rows, cols, partial, nparts, stream);
+  else { conef_set_error("coldot: dtype %d", dtype); return 1; }
+  if (rc != 0) return rc;
+  k_coldot_final<<<(cols + CF_COLS - 1) / CF_COLS, CF_THREADS, 0, stream>>>(partial, nparts, cols, invstd, sum_dy, sum_dy_xmu, grad_weight,
+                                                        grad_bias);
+  CONEF_CHECK_LAUNCH("k_coldot_final");
+  return 0;
 }

@@ -358,6 +358,16 @@ int conef_lamb_step(const ConefLambTensor* tensors, int ntensors, const int2* ch
 // inputs it does not take (cols % 8 != 0, cols > 2048, x not 16-byte aligned).
 int conef_colsum(const void* x, int dtype, long long rows, int cols, float* partial, int nparts, float* out,
                  cudaStream_t stream);
+// Batch-norm statistics of the same kind of matrix: mean and 1 / sqrt(biased variance + eps) per column from
+// shifted sums, plus the momentum update of the running statistics (NULL: none).  partial: nparts * 2 * cols floats.
+int conef_colstats(const void* x, int dtype, long long rows, int cols, float eps, float momentum, float* partial,
+                   int nparts, float* mean, float* invstd, float* running_mean, float* running_var,
+                   cudaStream_t stream);
+// The two sums of the batch-norm backward pass: sum_dy = sum dy, sum_dy_xmu = sum dy (x - mean); grad_weight
+// (= sum_dy_xmu * invstd) and grad_bias (= sum_dy) when given.  dy and x share dtype and layout.
+int conef_coldot(const void* dy, const void* x, int dtype, long long rows, int cols, const float* mean,
+                 const float* invstd, float* partial, int nparts, float* sum_dy, float* sum_dy_xmu,
+                 float* grad_weight, float* grad_bias, cudaStream_t stream);
 
 // ---- host implementations (cpu_ops.cu) --------------------------------------
 void conef_cpu_hash_table(int32_t* table, int32_t* counts, int D, int W, int a, int b, int sa, int sb, int layout);

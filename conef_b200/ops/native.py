@@ -157,6 +157,8 @@ _SIGNATURES = {
                                C.c_float, C.c_int, C.c_int, C.c_size_t, vp, vp], C.c_int),
     "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),
     "conef_colsum": ([vp, C.c_int, c_ll, C.c_int, vp, C.c_int, vp, vp], C.c_int),
+    "conef_colstats": ([vp, C.c_int, c_ll, C.c_int, C.c_float, C.c_float, vp, C.c_int, vp, vp, vp, vp, vp], C.c_int),
+    "conef_coldot": ([vp, vp, C.c_int, c_ll, C.c_int, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp], C.c_int),
     "conef_lowrank_correct": ([vp, C.c_int, vp, C.c_int, vp, C.c_int, vp, vp, vp, vp, C.c_float, vp, vp, vp,
                                C.c_float, vp, vp], C.c_int),
     "conef_tc_supported": ([], C.c_int),

@@ -400,3 +400,38 @@ def test_conv_layer_bias_gradient_matches_torch():
             torch.testing.assert_close(a, b, rtol=2e-2, atol=2e-2)
         # the bias gradient is an fp32 sum of the bf16 output gradient: tighter than bf16 accumulation
         assert outs[1][3].dtype == torch.float32
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_batch_norm_layer_matches_torch(dtype):
+    """``models.layers.BatchNorm2d`` (statistics and backward sums on the column kernels) against
+    ``nn.BatchNorm2d`` in training mode: outputs, gradients and running statistics, with a mean far from
+    zero (the shifted sums must not lose the variance) and a channel count of every slab layout."""
+    from conef_b200.models.layers import BatchNorm2d
+    torch.manual_seed(3)
+    for n, c, h, w in ((16, 160, 8, 8), (4, 16, 7, 5), (9, 640, 3, 3)):
+        ref_bn = torch.nn.BatchNorm2d(c, momentum=0.9).to(DEV)
+        own = BatchNorm2d(c, momentum=0.9).to(DEV)
+        with torch.no_grad():
+            ref_bn.weight.uniform_(0.5, 1.5)
+            ref_bn.bias.uniform_(-1, 1)
+        own.load_state_dict(ref_bn.state_dict())
+        x = (torch.randn(n, c, h, w, device=DEV) * 0.5 + 30.0).to(dtype).contiguous(memory_format=torch.channels_last)
+        g = torch.randn(n, c, h, w, device=DEV).to(dtype).contiguous(memory_format=torch.channels_last)
+        res = []
+        for bn in (ref_bn, own):
+            xi = x.clone().requires_grad_(True)
+            before = native.reset_launch_count()
+            y = bn(xi)
+            y.backward(g)
+            launches = native.reset_launch_count()
+            res.append((y.detach().float(), xi.grad.float(), bn.weight.grad.float(), bn.bias.grad.float(),
+                        bn.running_mean.clone(), bn.running_var.clone()))
+        assert launches >= 2, "the native kernels did not run"
+        tol = dict(rtol=3e-2, atol=3e-2) if dtype == torch.bfloat16 else dict(rtol=2e-3, atol=2e-3)
+        for a, b in zip(*res):
+            torch.testing.assert_close(a, b, **tol)
+        assert int(own.num_batches_tracked) == 1
+    # evaluation mode and NCHW inputs take the library path
+    own.eval()
+    torch.testing.assert_close(own(x), ref_bn.eval()(x), rtol=1e-4, atol=1e-3)
