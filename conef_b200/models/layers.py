@@ -53,41 +53,59 @@ class Conv2d(nn.Conv2d):
 
 
 class _BatchNormFn(torch.autograd.Function):
-    """Training-mode batch norm over a channels-last activation: the two per-channel reductions (statistics
-    in the forward pass, the sums of dy and dy (x - mean) in the backward pass) run on the library's
-    column kernels; the two elementwise passes stay with PyTorch (``batch_norm_elemt`` /
-    ``batch_norm_backward_elemt``, the pair SyncBatchNorm is built from)."""
+    """Training-mode batch norm over a channels-last activation, optionally fused with the ReLU behind it.
+    All four passes run on the library's column kernels (``csrc/colsum.cu``): statistics (before this
+    function), the normalisation (+ ReLU) in one pass, the backward sums of dy and dy (x - mean) with dy
+    masked by the ReLU, and the input gradient in one pass.  Anything the kernels do not take goes through
+    ``batch_norm_elemt`` / ``batch_norm_backward_reduce`` / ``batch_norm_backward_elemt`` (the ops
+    SyncBatchNorm is built from) and a separate ReLU."""
 
     @staticmethod
-    def forward(ctx, x, weight, bias, mean, invstd, eps, count):
-        y = torch.batch_norm_elemt(x, weight, bias, mean, invstd, eps)
-        ctx.save_for_backward(x, weight, mean, invstd, count)
+    def forward(ctx, x, weight, bias, mean, invstd, eps, count, relu):
+        from ..ops.colsum import bn_apply
+        y = bn_apply(x, mean, invstd, weight, bias, relu)
+        if y is None:
+            y = torch.batch_norm_elemt(x, weight, bias, mean, invstd, eps)
+            if relu:
+                y = torch.relu(y)
+        ctx.save_for_backward(x, weight, bias, mean, invstd, count)
+        ctx.relu = relu
         return y
 
     @staticmethod
     def backward(ctx, gy):
-        from ..ops.colsum import channel_dot
-        x, weight, mean, invstd, count = ctx.saved_tensors
+        from ..ops.colsum import bn_backward_apply, channel_dot, channel_dot_relu
+        x, weight, bias, mean, invstd, count = ctx.saved_tensors
+        relu = ctx.relu
         if gy.dtype != x.dtype:
             gy = gy.to(x.dtype)
         if not gy.is_contiguous(memory_format=torch.channels_last):
             gy = gy.contiguous(memory_format=torch.channels_last)
-        sums = channel_dot(gy, x, mean, invstd)
+        sums = channel_dot_relu(gy, x, mean, invstd, weight, bias) if relu else channel_dot(gy, x, mean, invstd)
+        native_mask = sums is not None
         if sums is None:
-            sum_dy, sum_dy_xmu, gw, gb = torch.batch_norm_backward_reduce(gy, x, mean, invstd, weight, True, True, True)
-        else:
-            sum_dy, sum_dy_xmu, gw, gb = sums
-        gx = torch.batch_norm_backward_elemt(gy, x, mean, invstd, weight, sum_dy, sum_dy_xmu, count) \
-            if ctx.needs_input_grad[0] else None
-        return gx, gw.to(weight.dtype), gb.to(weight.dtype), None, None, None, None
+            if relu:      # mask by the recomputed activation, then the unfused ops
+                gy = gy * (torch.batch_norm_elemt(x, weight, bias, mean, invstd, 0.0) > 0)
+            sums = torch.batch_norm_backward_reduce(gy, x, mean, invstd, weight, True, True, True)
+        sum_dy, sum_dy_xmu, gw, gb = sums
+        gx = None
+        if ctx.needs_input_grad[0]:
+            gx = bn_backward_apply(gy, x, mean, invstd, weight, bias, sum_dy, sum_dy_xmu, relu and native_mask)
+            if gx is None:
+                if relu and native_mask:
+                    gy = gy * (torch.batch_norm_elemt(x, weight, bias, mean, invstd, 0.0) > 0)
+                gx = torch.batch_norm_backward_elemt(gy, x, mean, invstd, weight, sum_dy, sum_dy_xmu, count)
+        return gx, gw.to(weight.dtype), gb.to(weight.dtype), None, None, None, None, None
 
 
 class BatchNorm2d(nn.BatchNorm2d):
-    """``nn.BatchNorm2d`` (same parameters, buffers and ``state_dict``) whose training-mode reductions run on
-    ``conef_b200.ops.colsum`` when the input lies in channels-last memory on a GPU.  PyTorch's channels-last
-    statistics kernels reach about 0.8 TB/s on WRN-28-10's bf16 activations (55-59 us per 42 MB pass)."""
+    """``nn.BatchNorm2d`` (same parameters, buffers and ``state_dict``) whose training-mode passes run on
+    ``conef_b200.ops.colsum`` when the input lies in channels-last memory on a GPU; ``forward(x, relu=True)``
+    applies the ReLU that follows in the same passes.  PyTorch's channels-last statistics kernels reach
+    about 0.8 TB/s on WRN-28-10's bf16 activations (55-59 us per 42 MB pass), and batch norm + ReLU cost
+    two passes over the activation in each direction."""
 
-    def forward(self, x):
+    def forward(self, x, relu: bool = False):
         if (self.training and self.track_running_stats and self.affine and self.momentum is not None
                 and x.is_cuda and x.dim() == 4 and torch.is_grad_enabled() and native.available()
                 and x.is_contiguous(memory_format=torch.channels_last)):
@@ -101,5 +119,6 @@ class BatchNorm2d(nn.BatchNorm2d):
                 if getattr(self, "_count_key", None) != key:
                     self._count = torch.full((1,), n, dtype=torch.int32, device=x.device)
                     self._count_key = key
-                return _BatchNormFn.apply(x, self.weight, self.bias, stats[0], stats[1], self.eps, self._count)
-        return super().forward(x)
+                return _BatchNormFn.apply(x, self.weight, self.bias, stats[0], stats[1], self.eps, self._count, relu)
+        y = super().forward(x)
+        return F.relu(y) if relu else y

@@ -28,8 +28,8 @@ class WideBlock(nn.Module):
             self.shortcut = Conv2d(cin, cout, 1, stride=stride, bias=True)
 
     def forward(self, x):
-        y = self.drop(self.conv1(F.relu(self.bn1(x))))
-        y = self.conv2(F.relu(self.bn2(y)))
+        y = self.drop(self.conv1(self.bn1(x, relu=True)))
+        y = self.conv2(self.bn2(y, relu=True))
         return y + (x if self.shortcut is None else self.shortcut(x))
 
 
@@ -51,7 +51,7 @@ class WideResNet(nn.Module):
 
     def forward(self, x):
         x = self.blocks(self.conv1(x))
-        x = F.relu(self.bn(x))
+        x = self.bn(x, relu=True)
         x = F.adaptive_avg_pool2d(x, 1)
         return self.linear(torch.flatten(x, 1))
 

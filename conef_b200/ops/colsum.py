@@ -95,3 +95,57 @@ def channel_dot(dy: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, invstd: t
         partial.data_ptr(), nparts, out[0].data_ptr(), out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(),
         native.stream_ptr(dev)), "coldot")
     return out[0], out[1], out[2], out[3]
+
+
+def _elem_parts(rows: int) -> int:
+    return int(max(1, min(4 * _MAX_PARTS, rows // 16)))
+
+
+def bn_apply(x, mean, invstd, weight, bias, relu: bool):
+    """``relu?((x - mean) * invstd * weight + bias)`` in one pass over a channels-last activation; None
+    when the native kernel does not take the input."""
+    rc = _native_shape(x)
+    if rc is None:
+        return None
+    rows, cols = rc
+    y = torch.empty_like(x)      # keeps the channels-last strides
+    if y.data_ptr() % 16 != 0:
+        return None
+    native.check(native.lib().conef_bn_apply(
+        x.data_ptr(), y.data_ptr(), _DTYPES[x.dtype], rows, cols, mean.data_ptr(), invstd.data_ptr(),
+        native.ptr(weight), native.ptr(bias), int(bool(relu)), _elem_parts(rows), native.stream_ptr(x.device)),
+        "bn_apply")
+    return y
+
+
+def channel_dot_relu(dy, x, mean, invstd, weight, bias):
+    """:func:`channel_dot` with ``dy`` masked where the ReLU behind the batch norm is inactive."""
+    rc = _native_shape(x)
+    if rc is None or dy.dtype != x.dtype or dy.shape != x.shape or _native_shape(dy) != rc:
+        return None
+    rows, cols = rc
+    nparts = int(max(1, min(_MAX_PARTS, rows // 32)))
+    dev = x.device
+    partial = torch.empty(nparts * 2 * cols, dtype=torch.float32, device=dev)
+    out = torch.empty(4, cols, dtype=torch.float32, device=dev)
+    native.check(native.lib().conef_coldot_relu(
+        dy.data_ptr(), x.data_ptr(), _DTYPES[x.dtype], rows, cols, mean.data_ptr(), invstd.data_ptr(),
+        native.ptr(weight), native.ptr(bias), partial.data_ptr(), nparts, out[0].data_ptr(), out[1].data_ptr(),
+        out[2].data_ptr(), out[3].data_ptr(), native.stream_ptr(dev)), "coldot_relu")
+    return out[0], out[1], out[2], out[3]
+
+
+def bn_backward_apply(gy, x, mean, invstd, weight, bias, sum_dy, sum_dy_xmu, relu: bool):
+    """Input gradient of batch norm (+ ReLU) in one pass; None when the native kernel does not take the inputs."""
+    rc = _native_shape(x)
+    if rc is None or gy.dtype != x.dtype or _native_shape(gy) != rc:
+        return None
+    rows, cols = rc
+    gx = torch.empty_like(x)
+    if gx.data_ptr() % 16 != 0:
+        return None
+    native.check(native.lib().conef_bn_backward_apply(
+        gy.data_ptr(), x.data_ptr(), gx.data_ptr(), _DTYPES[x.dtype], rows, cols, mean.data_ptr(), invstd.data_ptr(),
+        native.ptr(weight), native.ptr(bias), sum_dy.data_ptr(), sum_dy_xmu.data_ptr(), int(bool(relu)),
+        _elem_parts(rows), native.stream_ptr(x.device)), "bn_backward_apply")
+    return gx

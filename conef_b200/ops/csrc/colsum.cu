@@ -173,28 +173,42 @@ template <> struct Load8<float> {
   }
 };
 
+// per-channel scale = invstd * weight and shift = bias - mean * scale for the eight columns of a thread
+__device__ __forceinline__ void bn_coeffs(const float* mean, const float* invstd, const float* weight, const float* bias,
+                                          int c0, float (&scale)[8], float (&shift)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    scale[i] = invstd[c0 + i] * (weight ? weight[c0 + i] : 1.f);
+    shift[i] = (bias ? bias[c0 + i] : 0.f) - mean[c0 + i] * scale[i];
+  }
+}
+
 // MODE 0: s1 = sum (x - pivot), s2 = sum (x - pivot)^2, pivot = x[0, c] (`y` unused).
 // MODE 1: s1 = sum y, s2 = sum y (x - center[c]): the two sums of the batch-norm backward pass (y = dL/dout).
+// MODE 2: as MODE 1 with y masked by the ReLU that follows the batch norm: y counts where
+//         (x - mean) invstd weight + bias > 0 (center = mean; invstd, weight, bias given).
 // partial[blockIdx.x][0 | 1][0..cols).
 template <typename T, int MODE>
 __global__ void __launch_bounds__(CS_THREADS)
 k_colpair_partial(const T* __restrict__ x, const T* __restrict__ y, const float* __restrict__ center, long long rows,
-                  int cols, long long rows_per_cta, float* __restrict__ partial) {
+                  int cols, long long rows_per_cta, float* __restrict__ partial, const float* __restrict__ invstd,
+                  const float* __restrict__ weight, const float* __restrict__ bias) {
   extern __shared__ float cs_sm[];      // (row groups) x 2 x cols
   const int chunks = cols >> 3;
   const int groups = CS_THREADS / chunks;
   const int cc = threadIdx.x % chunks, rr = threadIdx.x / chunks;
   const long long r0 = (long long)blockIdx.x * rows_per_cta;
   const long long r1 = min(rows, r0 + rows_per_cta);
-  float s1[8], s2[8], ctr[8];
+  float s1[8], s2[8], ctr[8], scale[8], shift[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) { s1[i] = 0.f; s2[i] = 0.f; }
+  for (int i = 0; i < 8; ++i) { s1[i] = 0.f; s2[i] = 0.f; scale[i] = 0.f; shift[i] = 0.f; }
   if (rr < groups) {
     if (MODE == 0) {
       Load8<T>::get(x + 8 * cc, ctr);
     } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) ctr[i] = center[8 * cc + i];
+      if (MODE == 2) bn_coeffs(center, invstd, weight, bias, 8 * cc, scale, shift);
     }
     const size_t step = (size_t)groups * cols;
     size_t off = (size_t)(r0 + rr) * cols + 8 * cc;
@@ -203,9 +217,13 @@ k_colpair_partial(const T* __restrict__ x, const T* __restrict__ y, const float*
       float a[8], b[8], ya[8], yb[8];
       Load8<T>::get(x + off, a);
       Load8<T>::get(x + off + step, b);
-      if (MODE == 1) { Load8<T>::get(y + off, ya); Load8<T>::get(y + off + step, yb); }
+      if (MODE >= 1) { Load8<T>::get(y + off, ya); Load8<T>::get(y + off + step, yb); }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
+        if (MODE == 2) {
+          if (!(fmaf(a[i], scale[i], shift[i]) > 0.f)) ya[i] = 0.f;
+          if (!(fmaf(b[i], scale[i], shift[i]) > 0.f)) yb[i] = 0.f;
+        }
         const float da = a[i] - ctr[i], db = b[i] - ctr[i];
         if (MODE == 0) { s1[i] += da + db; s2[i] = fmaf(da, da, fmaf(db, db, s2[i])); }
         else { s1[i] += ya[i] + yb[i]; s2[i] = fmaf(ya[i], da, fmaf(yb[i], db, s2[i])); }
@@ -214,9 +232,10 @@ k_colpair_partial(const T* __restrict__ x, const T* __restrict__ y, const float*
     for (; row < r1; row += groups, off += step) {
       float a[8], ya[8];
       Load8<T>::get(x + off, a);
-      if (MODE == 1) Load8<T>::get(y + off, ya);
+      if (MODE >= 1) Load8<T>::get(y + off, ya);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
+        if (MODE == 2 && !(fmaf(a[i], scale[i], shift[i]) > 0.f)) ya[i] = 0.f;
         const float da = a[i] - ctr[i];
         if (MODE == 0) { s1[i] += da; s2[i] = fmaf(da, da, s2[i]); }
         else { s1[i] += ya[i]; s2[i] = fmaf(ya[i], da, s2[i]); }
@@ -286,7 +305,8 @@ static bool colpair_ok(const void* x, const void* y, long long rows, int cols, i
 
 template <typename T, int MODE>
 static int launch_colpair(const void* x, const void* y, const float* center, long long rows, int cols, float* partial,
-                          int nparts, cudaStream_t stream) {
+                          int nparts, cudaStream_t stream, const float* invstd = nullptr, const float* weight = nullptr,
+                          const float* bias = nullptr) {
   const long long rows_per_cta = (rows + nparts - 1) / nparts;
   const int groups = CS_THREADS / (cols >> 3);
   const size_t smem = (size_t)groups * 2 * cols * sizeof(float);
@@ -298,7 +318,7 @@ static int launch_colpair(const void* x, const void* y, const float* center, lon
     if (dev >= 0 && dev < 64) configured[dev] = smem;
   }
   k_colpair_partial<T, MODE><<<nparts, CS_THREADS, smem, stream>>>((const T*)x, (const T*)y, center, rows, cols,
-                                                                  rows_per_cta, partial);
+                                                                  rows_per_cta, partial, invstd, weight, bias);
   CONEF_CHECK_LAUNCH("k_colpair_partial");
   return 0;
 }
@@ -342,5 +362,165 @@ extern "C" int conef_coldot(const void* dy, const void* x, int dtype, long long 
   k_coldot_final<<<(cols + CF_COLS - 1) / CF_COLS, CF_THREADS, 0, stream>>>(partial, nparts, cols, invstd, sum_dy, sum_dy_xmu, grad_weight,
                                                         grad_bias);
   CONEF_CHECK_LAUNCH("k_coldot_final");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Elementwise passes of batch norm fused with the ReLU that follows it (pre-activation blocks:
+// relu(bn(x))).  PyTorch runs batch_norm_elemt and relu as two passes over the activation in each
+// direction; fused, the activation is read once and written once.
+template <typename T> struct Store8;
+template <> struct Store8<__nv_bfloat16> {
+  static __device__ __forceinline__ void put(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct Store8<__half> {
+  static __device__ __forceinline__ void put(__half* p, const float (&v)[8]) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  }
+};
+template <> struct Store8<float> {
+  static __device__ __forceinline__ void put(float* p, const float (&v)[8]) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+
+// y = x * scale + shift, then max(0, .) with RELU.  Thread (rr, cc): columns 8 cc .. 8 cc + 7, rows rr, rr + groups, ...
+template <typename T, bool RELU>
+__global__ void __launch_bounds__(CS_THREADS)
+k_bn_apply(const T* __restrict__ x, T* __restrict__ y, long long rows, int cols, long long rows_per_cta,
+           const float* __restrict__ mean, const float* __restrict__ invstd, const float* __restrict__ weight,
+           const float* __restrict__ bias) {
+  const int chunks = cols >> 3, groups = CS_THREADS / chunks;
+  const int cc = threadIdx.x % chunks, rr = threadIdx.x / chunks;
+  if (rr >= groups) return;
+  float scale[8], shift[8];
+  bn_coeffs(mean, invstd, weight, bias, 8 * cc, scale, shift);
+  const long long r0 = (long long)blockIdx.x * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
+  const size_t step = (size_t)groups * cols;
+  size_t off = (size_t)(r0 + rr) * cols + 8 * cc;
+  long long row = r0 + rr;
+  for (; row + groups < r1; row += 2LL * groups, off += 2 * step) {
+    float a[8], b[8];
+    Load8<T>::get(x + off, a);
+    Load8<T>::get(x + off + step, b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      a[i] = fmaf(a[i], scale[i], shift[i]);
+      b[i] = fmaf(b[i], scale[i], shift[i]);
+      if (RELU) { a[i] = fmaxf(a[i], 0.f); b[i] = fmaxf(b[i], 0.f); }
+    }
+    Store8<T>::put(y + off, a);
+    Store8<T>::put(y + off + step, b);
+  }
+  for (; row < r1; row += groups, off += step) {
+    float a[8];
+    Load8<T>::get(x + off, a);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { a[i] = fmaf(a[i], scale[i], shift[i]); if (RELU) a[i] = fmaxf(a[i], 0.f); }
+    Store8<T>::put(y + off, a);
+  }
+}
+
+// gx = (gy - sum_dy / n - (x - mean) invstd^2 sum_dy_xmu / n) invstd weight, with gy masked by the ReLU
+// ((x - mean) invstd weight + bias > 0) when RELU.
+template <typename T, bool RELU>
+__global__ void __launch_bounds__(CS_THREADS)
+k_bn_backward_apply(const T* __restrict__ gy, const T* __restrict__ x, T* __restrict__ gx, long long rows, int cols,
+                    long long rows_per_cta, const float* __restrict__ mean, const float* __restrict__ invstd,
+                    const float* __restrict__ weight, const float* __restrict__ bias,
+                    const float* __restrict__ sum_dy, const float* __restrict__ sum_dy_xmu) {
+  const int chunks = cols >> 3, groups = CS_THREADS / chunks;
+  const int cc = threadIdx.x % chunks, rr = threadIdx.x / chunks;
+  if (rr >= groups) return;
+  float scale[8], shift[8], mu[8], k0[8], k1[8], k2[8];
+  bn_coeffs(mean, invstd, weight, bias, 8 * cc, scale, shift);
+  const float inv_n = 1.f / (float)rows;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = 8 * cc + i;
+    const float is = invstd[c], w = weight ? weight[c] : 1.f;
+    mu[i] = mean[c];
+    k0[i] = is * w;                                  // gx = (gy - k1 - (x - mu) k2) k0
+    k1[i] = sum_dy[c] * inv_n;
+    k2[i] = is * is * sum_dy_xmu[c] * inv_n;
+  }
+  const long long r0 = (long long)blockIdx.x * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
+  const size_t step = (size_t)groups * cols;
+  size_t off = (size_t)(r0 + rr) * cols + 8 * cc;
+  for (long long row = r0 + rr; row < r1; row += groups, off += step) {
+    float g[8], a[8];
+    Load8<T>::get(gy + off, g);
+    Load8<T>::get(x + off, a);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (RELU && !(fmaf(a[i], scale[i], shift[i]) > 0.f)) g[i] = 0.f;
+      g[i] = (g[i] - k1[i] - (a[i] - mu[i]) * k2[i]) * k0[i];
+    }
+    Store8<T>::put(gx + off, g);
+  }
+}
+
+#define CONEF_BY_DTYPE(dtype, ...)                                             \
+  do {                                                                         \
+    if ((dtype) == 0) { using T = float; __VA_ARGS__; }                        \
+    else if ((dtype) == 1) { using T = __nv_bfloat16; __VA_ARGS__; }           \
+    else if ((dtype) == 2) { using T = __half; __VA_ARGS__; }                  \
+    else { conef_set_error("unknown dtype %d", (int)(dtype)); return 1; }      \
+  } while (0)
+
+// y = relu?((x - mean) invstd weight + bias) over a row-major (rows x cols) activation; weight / bias may be NULL.
+extern "C" int conef_bn_apply(const void* x, void* y, int dtype, long long rows, int cols, const float* mean,
+                              const float* invstd, const float* weight, const float* bias, int relu, int nparts,
+                              cudaStream_t stream) {
+  if (!colpair_ok(x, y, rows, cols, nparts)) { conef_set_error("bn_apply: shape or alignment not supported"); return 2; }
+  const long long rpc = (rows + nparts - 1) / nparts;
+  CONEF_BY_DTYPE(dtype, {
+    if (relu) k_bn_apply<T, true><<<nparts, CS_THREADS, 0, stream>>>((const T*)x, (T*)y, rows, cols, rpc, mean, invstd, weight, bias);
+    else k_bn_apply<T, false><<<nparts, CS_THREADS, 0, stream>>>((const T*)x, (T*)y, rows, cols, rpc, mean, invstd, weight, bias);
+  });
+  CONEF_CHECK_LAUNCH("k_bn_apply");
+  return 0;
+}
+
+// The backward sums with dy masked by the ReLU behind the batch norm (see k_colpair_partial, MODE 2).
+extern "C" int conef_coldot_relu(const void* dy, const void* x, int dtype, long long rows, int cols, const float* mean,
+                                 const float* invstd, const float* weight, const float* bias, float* partial,
+                                 int nparts, float* sum_dy, float* sum_dy_xmu, float* grad_weight, float* grad_bias,
+                                 cudaStream_t stream) {
+  if (!colpair_ok(x, dy, rows, cols, nparts)) { conef_set_error("coldot_relu: shape or alignment not supported"); return 2; }
+  int rc = 0;
+  CONEF_BY_DTYPE(dtype, { rc = launch_colpair<T, 2>(x, dy, mean, rows, cols, partial, nparts, stream, invstd, weight, bias); });
+  if (rc != 0) return rc;
+  k_coldot_final<<<(cols + CF_COLS - 1) / CF_COLS, CF_THREADS, 0, stream>>>(partial, nparts, cols, invstd, sum_dy,
+                                                                          sum_dy_xmu, grad_weight, grad_bias);
+  CONEF_CHECK_LAUNCH("k_coldot_final");
+  return 0;
+}
+
+extern "C" int conef_bn_backward_apply(const void* gy, const void* x, void* gx, int dtype, long long rows, int cols,
+                                       const float* mean, const float* invstd, const float* weight, const float* bias,
+                                       const float* sum_dy, const float* sum_dy_xmu, int relu, int nparts,
+                                       cudaStream_t stream) {
+  if (!colpair_ok(x, gy, rows, cols, nparts) || (reinterpret_cast<uintptr_t>(gx) & 15) != 0) {
+    conef_set_error("bn_backward_apply: shape or alignment not supported");
+    return 2;
+  }
+  const long long rpc = (rows + nparts - 1) / nparts;
+  CONEF_BY_DTYPE(dtype, {
+    if (relu) k_bn_backward_apply<T, true><<<nparts, CS_THREADS, 0, stream>>>((const T*)gy, (const T*)x, (T*)gx, rows, cols, rpc, mean, invstd, weight, bias, sum_dy, sum_dy_xmu);
+    else k_bn_backward_apply<T, false><<<nparts, CS_THREADS, 0, stream>>>((const T*)gy, (const T*)x, (T*)gx, rows, cols, rpc, mean, invstd, weight, bias, sum_dy, sum_dy_xmu);
+  });
+  CONEF_CHECK_LAUNCH("k_bn_backward_apply");
   return 0;
 }

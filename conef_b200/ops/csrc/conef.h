@@ -368,6 +368,19 @@ int conef_colstats(const void* x, int dtype, long long rows, int cols, float eps
 int conef_coldot(const void* dy, const void* x, int dtype, long long rows, int cols, const float* mean,
                  const float* invstd, float* partial, int nparts, float* sum_dy, float* sum_dy_xmu,
                  float* grad_weight, float* grad_bias, cudaStream_t stream);
+// Elementwise passes of batch norm, optionally fused with the ReLU behind it (relu != 0):
+//   conef_bn_apply          y = relu?((x - mean) invstd weight + bias)
+//   conef_coldot_relu       conef_coldot with dy masked where that ReLU is inactive
+//   conef_bn_backward_apply gx = (gy - sum_dy / n - (x - mean) invstd^2 sum_dy_xmu / n) invstd weight (gy masked likewise)
+// nparts CTAs split the rows; weight / bias may be NULL (1 and 0).
+int conef_bn_apply(const void* x, void* y, int dtype, long long rows, int cols, const float* mean, const float* invstd,
+                   const float* weight, const float* bias, int relu, int nparts, cudaStream_t stream);
+int conef_coldot_relu(const void* dy, const void* x, int dtype, long long rows, int cols, const float* mean,
+                      const float* invstd, const float* weight, const float* bias, float* partial, int nparts,
+                      float* sum_dy, float* sum_dy_xmu, float* grad_weight, float* grad_bias, cudaStream_t stream);
+int conef_bn_backward_apply(const void* gy, const void* x, void* gx, int dtype, long long rows, int cols,
+                            const float* mean, const float* invstd, const float* weight, const float* bias,
+                            const float* sum_dy, const float* sum_dy_xmu, int relu, int nparts, cudaStream_t stream);
 
 // ---- host implementations (cpu_ops.cu) --------------------------------------
 void conef_cpu_hash_table(int32_t* table, int32_t* counts, int D, int W, int a, int b, int sa, int sb, int layout);

@@ -402,11 +402,13 @@ def test_conv_layer_bias_gradient_matches_torch():
         assert outs[1][3].dtype == torch.float32
 
 
+@pytest.mark.parametrize("relu", [False, True])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_batch_norm_layer_matches_torch(dtype):
-    """``models.layers.BatchNorm2d`` (statistics and backward sums on the column kernels) against
-    ``nn.BatchNorm2d`` in training mode: outputs, gradients and running statistics, with a mean far from
-    zero (the shifted sums must not lose the variance) and a channel count of every slab layout."""
+def test_batch_norm_layer_matches_torch(dtype, relu):
+    """``models.layers.BatchNorm2d`` (statistics, normalisation (+ ReLU), backward sums and input gradient
+    on the column kernels) against ``nn.BatchNorm2d`` (+ ``F.relu``) in training mode: outputs, gradients
+    and running statistics, with a mean far from zero (the shifted sums must not lose the variance) and a
+    channel count of every slab layout."""
     from conef_b200.models.layers import BatchNorm2d
     torch.manual_seed(3)
     for n, c, h, w in ((16, 160, 8, 8), (4, 16, 7, 5), (9, 640, 3, 3)):
@@ -421,17 +423,22 @@ def test_batch_norm_layer_matches_torch(dtype):
         res = []
         for bn in (ref_bn, own):
             xi = x.clone().requires_grad_(True)
-            before = native.reset_launch_count()
-            y = bn(xi)
+            native.reset_launch_count()
+            y = bn(xi, relu=relu) if bn is own else (torch.relu(bn(xi)) if relu else bn(xi))
             y.backward(g)
             launches = native.reset_launch_count()
             res.append((y.detach().float(), xi.grad.float(), bn.weight.grad.float(), bn.bias.grad.float(),
                         bn.running_mean.clone(), bn.running_var.clone()))
-        assert launches >= 2, "the native kernels did not run"
+        assert launches >= 4, "the native kernels did not run"
         tol = dict(rtol=3e-2, atol=3e-2) if dtype == torch.bfloat16 else dict(rtol=2e-3, atol=2e-3)
-        for a, b in zip(*res):
-            torch.testing.assert_close(a, b, **tol)
+        for k, (a, b) in enumerate(zip(*res)):
+            if relu and k in (1, 2, 3):
+                # an activation within rounding of zero may fall on the other side of the ReLU
+                assert (a - b).norm() <= (3e-2 if dtype == torch.bfloat16 else 1e-2) * b.norm() + 1e-3
+            else:
+                torch.testing.assert_close(a, b, **tol)
         assert int(own.num_batches_tracked) == 1
-    # evaluation mode and NCHW inputs take the library path
+    # evaluation mode takes the library path
     own.eval()
-    torch.testing.assert_close(own(x), ref_bn.eval()(x), rtol=1e-4, atol=1e-3)
+    want = ref_bn.eval()(x)
+    torch.testing.assert_close(own(x, relu=relu), torch.relu(want) if relu else want, rtol=1e-4, atol=1e-3)
