@@ -20,7 +20,10 @@ from ..ops.colsum import channel_sum
 class _ConvBiasFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, stride, padding, dilation, groups):
-        y = F.conv2d(x, weight, bias, stride, padding, dilation, groups)      # autocast applies as usual
+        from ..ops.colsum import bias_add_
+        y = F.conv2d(x, weight, None, stride, padding, dilation, groups)      # autocast applies as usual
+        if not bias_add_(y, bias):      # the library adds it with a broadcasting kernel that is not vectorised
+            y = y + bias.to(y.dtype).view(1, -1, 1, 1)
         ctx.save_for_backward(x, weight)
         ctx.conf = (stride, padding, dilation, groups)
         ctx.bias_dtype = bias.dtype

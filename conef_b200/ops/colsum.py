@@ -149,3 +149,15 @@ def bn_backward_apply(gy, x, mean, invstd, weight, bias, sum_dy, sum_dy_xmu, rel
         native.ptr(weight), native.ptr(bias), sum_dy.data_ptr(), sum_dy_xmu.data_ptr(), int(bool(relu)),
         _elem_parts(rows), native.stream_ptr(x.device)), "bn_backward_apply")
     return gx
+
+
+def bias_add_(y: torch.Tensor, bias: torch.Tensor) -> bool:
+    """``y[:, c] += bias[c]`` in place on a channels-last activation; False when the native kernel does
+    not take the input (nothing is changed then)."""
+    rc = _native_shape(y)
+    if rc is None or not (bias.is_cuda and bias.dtype == torch.float32 and bias.is_contiguous()):
+        return False
+    rows, cols = rc
+    native.check(native.lib().conef_bias_add(y.data_ptr(), _DTYPES[y.dtype], rows, cols, bias.data_ptr(),
+                                             _elem_parts(rows), native.stream_ptr(y.device)), "bias_add")
+    return True

@@ -373,6 +373,8 @@ int conef_coldot(const void* dy, const void* x, int dtype, long long rows, int c
 //   conef_coldot_relu       conef_coldot with dy masked where that ReLU is inactive
 //   conef_bn_backward_apply gx = (gy - sum_dy / n - (x - mean) invstd^2 sum_dy_xmu / n) invstd weight (gy masked likewise)
 // nparts CTAs split the rows; weight / bias may be NULL (1 and 0).
+// y[row, c] += bias[c] in place (the bias of a convolution with a channels-last output)
+int conef_bias_add(void* y, int dtype, long long rows, int cols, const float* bias, int nparts, cudaStream_t stream);
 int conef_bn_apply(const void* x, void* y, int dtype, long long rows, int cols, const float* mean, const float* invstd,
                    const float* weight, const float* bias, int relu, int nparts, cudaStream_t stream);
 int conef_coldot_relu(const void* dy, const void* x, int dtype, long long rows, int cols, const float* mean,
