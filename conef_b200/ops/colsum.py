@@ -12,7 +12,7 @@ import torch
 from . import native
 
 _DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
-_MAX_PARTS = 296      # two CTAs per SM: the second stage walks the partial rows
+_MAX_PARTS = 592      # four CTAs per SM (the second stage adds the partial rows with 64 of them in flight)
 
 
 def _rows_cols(t: torch.Tensor):

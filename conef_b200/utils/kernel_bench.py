@@ -270,6 +270,39 @@ def main():
         record("hpowerSGD_hook top-k (whole bucket, ws=1)", t, (3 * 2 + 2 + 4.8) * mat_bytes,
                "G and E read by P, Q, decompress; M_hat and E written; top-k")
 
+    # ---------------- model-side column kernels (bias gradient, batch norm) ----------------
+    if want("colsum"):
+        from conef_b200.ops import colsum
+        # a channels-last bf16 activation larger than L2: WRN-28-10's first stage at four times its batch
+        x = torch.randn(512, 160, 32, 32, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        dy = torch.randn_like(x)
+        nb = x.numel() * 2
+        w = torch.rand(160, device=dev) + 0.5
+        b = torch.randn(160, device=dev)
+        mean, invstd = colsum.channel_stats(x, 1e-5)
+        sums = colsum.channel_dot_relu(dy, x, mean, invstd, w, b)
+        cnt = torch.full((1,), x.numel() // 160, dtype=torch.int32, device=dev)
+        record("channel_sum (bias gradient)", _time(lambda: colsum.channel_sum(dy), args.iters), nb, "read dy")
+        record("  torch: dy.sum((0, 2, 3))", _time(lambda: dy.sum(dim=(0, 2, 3)), args.iters), nb, "library")
+        record("channel_stats (batch-norm statistics)", _time(lambda: colsum.channel_stats(x, 1e-5), args.iters), nb, "read x")
+        record("  torch: batch_norm_stats", _time(lambda: torch.batch_norm_stats(x, 1e-5), args.iters), nb, "library")
+        record("bn_apply + ReLU", _time(lambda: colsum.bn_apply(x, mean, invstd, w, b, True), args.iters), 2 * nb,
+               "read x, write y")
+        record("  torch: batch_norm_elemt, relu", _time(lambda: torch.relu(torch.batch_norm_elemt(x, w, b, mean, invstd, 1e-5)),
+                                                       args.iters), 4 * nb, "library: two passes")
+        record("channel_dot_relu (backward sums)", _time(lambda: colsum.channel_dot_relu(dy, x, mean, invstd, w, b), args.iters),
+               2 * nb, "read dy and x")
+        record("  torch: batch_norm_backward_reduce", _time(lambda: torch.batch_norm_backward_reduce(dy, x, mean, invstd, w, True, True, True),
+                                                           args.iters), 2 * nb, "library (no ReLU mask)")
+        record("bn_backward_apply + ReLU", _time(lambda: colsum.bn_backward_apply(dy, x, mean, invstd, w, b, sums[0], sums[1], True),
+                                                 args.iters), 3 * nb, "read dy and x, write dx")
+        record("  torch: batch_norm_backward_elemt", _time(lambda: torch.batch_norm_backward_elemt(dy, x, mean, invstd, w, sums[0], sums[1], cnt),
+                                                          args.iters), 3 * nb, "library (no ReLU mask)")
+        y = x.clone()
+        record("bias_add_", _time(lambda: colsum.bias_add_(y, b), args.iters), 2 * nb, "read and write y")
+        record("  torch: y += bias", _time(lambda: y.add_(b.to(y.dtype).view(1, -1, 1, 1)), args.iters), 2 * nb, "library")
+        del x, dy, y
+
     # ---------------- LAMB ----------------
     if want("lamb"):
         from conef_b200.optim import FusedLAMB
