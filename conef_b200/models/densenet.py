@@ -20,8 +20,8 @@ class _DenseLayer(nn.Module):
         self.conv2 = nn.Conv2d(4 * growth, growth, 3, padding=1, bias=False)
 
     def forward(self, x):
-        y = self.conv1(F.relu(self.bn1(x)))
-        y = self.conv2(F.relu(self.bn2(y)))
+        y = self.conv1(self.bn1(x, relu=True))
+        y = self.conv2(self.bn2(y, relu=True))
         return torch.cat([y, x], 1)
 
 
@@ -32,7 +32,7 @@ class _Transition(nn.Module):
         self.conv = nn.Conv2d(cin, cout, 1, bias=False)
 
     def forward(self, x):
-        return F.avg_pool2d(self.conv(F.relu(self.bn(x))), 2)
+        return F.avg_pool2d(self.conv(self.bn(x, relu=True)), 2)
 
 
 class DenseNet(nn.Module):
@@ -55,7 +55,7 @@ class DenseNet(nn.Module):
 
     def forward(self, x):
         x = self.features(self.conv1(x))
-        x = F.avg_pool2d(F.relu(self.bn(x)), 4)
+        x = F.avg_pool2d(self.bn(x, relu=True), 4)
         return self.linear(torch.flatten(x, 1))
 
 

@@ -27,7 +27,7 @@ class BasicBlock(nn.Module):
         self.shortcut = _shortcut(cin, planes, stride)
 
     def forward(self, x):
-        y = F.relu(self.bn1(self.conv1(x)))
+        y = self.bn1(self.conv1(x), relu=True)
         return F.relu(self.bn2(self.conv2(y)) + self.shortcut(x))
 
 
@@ -46,8 +46,8 @@ class Bottleneck(nn.Module):
         self.shortcut = _shortcut(cin, cout, stride)
 
     def forward(self, x):
-        y = F.relu(self.bn1(self.conv1(x)))
-        y = F.relu(self.bn2(self.conv2(y)))
+        y = self.bn1(self.conv1(x), relu=True)
+        y = self.bn2(self.conv2(y), relu=True)
         return F.relu(self.bn3(self.conv3(y)) + self.shortcut(x))
 
 
@@ -65,7 +65,7 @@ class ResNet(nn.Module):
         self.linear = nn.Linear(cin, num_classes)
 
     def forward(self, x):
-        x = self.layers(F.relu(self.bn1(self.conv1(x))))
+        x = self.layers(self.bn1(self.conv1(x), relu=True))
         return self.linear(torch.flatten(F.adaptive_avg_pool2d(x, 1), 1))
 
 

@@ -24,7 +24,7 @@ class _Block(nn.Module):
             self.proj = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), BatchNorm2d(cout))
 
     def forward(self, x):
-        y = F.relu(self.bn1(self.conv1(x)))
+        y = self.bn1(self.conv1(x), relu=True)
         y = self.bn2(self.conv2(y))
         return F.relu(y + (x if self.proj is None else self.proj(x)))
 

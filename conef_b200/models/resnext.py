@@ -27,8 +27,8 @@ class _Block(nn.Module):
             self.shortcut = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, bias=False), BatchNorm2d(cout))
 
     def forward(self, x):
-        y = F.relu(self.bn1(self.conv1(x)))
-        y = F.relu(self.bn2(self.conv2(y)))
+        y = self.bn1(self.conv1(x), relu=True)
+        y = self.bn2(self.conv2(y), relu=True)
         return F.relu(self.bn3(self.conv3(y)) + self.shortcut(x))
 
 
@@ -47,7 +47,7 @@ class ResNeXt(nn.Module):
         self.linear = nn.Linear(cin, num_classes)
 
     def forward(self, x):
-        x = self.layers(F.relu(self.bn1(self.conv1(x))))
+        x = self.layers(self.bn1(self.conv1(x), relu=True))
         return self.linear(torch.flatten(F.adaptive_avg_pool2d(x, 1), 1))
 
 
