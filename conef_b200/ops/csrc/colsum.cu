@@ -458,23 +458,7 @@ k_bn_backward_apply(const T* __restrict__ gy, const T* __restrict__ x, T* __rest
   const long long r0 = (long long)blockIdx.x * rows_per_cta, r1 = min(rows, r0 + rows_per_cta);
   const size_t step = (size_t)groups * cols;
   size_t off = (size_t)(r0 + rr) * cols + 8 * cc;
-  long long row = r0 + rr;
-  for (; row + groups < r1; row += 2LL * groups, off += 2 * step) {      // two rows (four loads) in flight
-    float g[8], a[8], g2[8], a2[8];
-    Load8<T>::get(gy + off, g);
-    Load8<T>::get(x + off, a);
-    Load8<T>::get(gy + off + step, g2);
-    Load8<T>::get(x + off + step, a2);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (RELU && !(fmaf(a[i], scale[i], shift[i]) > 0.f)) g[i] = 0.f;
-      if (RELU && !(fmaf(a2[i], scale[i], shift[i]) > 0.f)) g2[i] = 0.f;
-      g[i] = (g[i] - k1[i] - (a[i] - mu[i]) * k2[i]) * k0[i];
-      g2[i] = (g2[i] - k1[i] - (a2[i] - mu[i]) * k2[i]) * k0[i];
-    }
-    Store8<T>::put(gx + off, g);
-    Store8<T>::put(gx + off + step, g2);
-  }
+  long long row = r0 + rr;      // one row (two loads) per pass: two rows in flight cost occupancy and measured slower
   for (; row < r1; row += groups, off += step) {
     float g[8], a[8];
     Load8<T>::get(gy + off, g);
