@@ -161,3 +161,39 @@ def bias_add_(y: torch.Tensor, bias: torch.Tensor) -> bool:
     native.check(native.lib().conef_bias_add(y.data_ptr(), _DTYPES[y.dtype], rows, cols, bias.data_ptr(),
                                              _elem_parts(rows), native.stream_ptr(y.device)), "bias_add")
     return True
+
+
+def layer_norm_wgrad(dy: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, rstd: torch.Tensor):
+    """``(dgamma, dbeta)`` (fp32) of a layer norm over the last dimension; ``mean`` / ``rstd`` are the per-row
+    statistics its forward pass saved.  None when the native kernel does not take the inputs."""
+    if not (x.is_cuda and x.dtype in _DTYPES and dy.dtype == x.dtype and native.available()
+            and x.is_contiguous() and dy.is_contiguous() and dy.shape == x.shape):
+        return None
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    if (cols % 8 != 0 or cols > 2048 or rows <= 0 or x.data_ptr() % 16 != 0 or dy.data_ptr() % 16 != 0
+            or mean.numel() != rows or rstd.numel() != rows or mean.dtype != torch.float32 or rstd.dtype != torch.float32
+            or not mean.is_contiguous() or not rstd.is_contiguous()):
+        return None
+    nparts = int(max(1, min(_MAX_PARTS, rows // 32)))
+    partial = torch.empty(nparts * 2 * cols, dtype=torch.float32, device=x.device)
+    out = torch.empty(2, cols, dtype=torch.float32, device=x.device)
+    native.check(native.lib().conef_ln_wgrad(
+        dy.data_ptr(), x.data_ptr(), _DTYPES[x.dtype], rows, cols, mean.data_ptr(), rstd.data_ptr(),
+        partial.data_ptr(), nparts, out[0].data_ptr(), out[1].data_ptr(), native.stream_ptr(x.device)), "ln_wgrad")
+    return out[0], out[1]
+
+
+def cast_like_autocast(t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """``t.to(dtype)``; the fp32 -> bf16 case of a dense CUDA tensor runs on the library's vectorised copy
+    (PyTorch's kernel for this pair of types reaches 0.5 TB/s)."""
+    if t.dtype == dtype:
+        return t
+    if (t.dtype == torch.float32 and dtype == torch.bfloat16 and t.is_cuda and native.available()
+            and (t.is_contiguous() or t.is_contiguous(memory_format=torch.channels_last)) and t.data_ptr() % 16 == 0):
+        out = torch.empty_like(t, dtype=dtype)      # same strides
+        if out.data_ptr() % 16 == 0:
+            native.check(native.lib().conef_cast_f32_bf16(t.data_ptr(), out.data_ptr(), t.numel(),
+                                                          native.stream_ptr(t.device)), "cast")
+            return out
+    return t.to(dtype)

@@ -373,6 +373,12 @@ int conef_coldot(const void* dy, const void* x, int dtype, long long rows, int c
 //   conef_coldot_relu       conef_coldot with dy masked where that ReLU is inactive
 //   conef_bn_backward_apply gx = (gy - sum_dy / n - (x - mean) invstd^2 sum_dy_xmu / n) invstd weight (gy masked likewise)
 // nparts CTAs split the rows; weight / bias may be NULL (1 and 0).
+// Weight and bias gradients of a layer norm along the rows of a (rows x cols) activation:
+// dgamma[c] = sum_rows dy (x - mean[row]) rstd[row], dbeta[c] = sum_rows dy.  partial: nparts * 2 * cols floats.
+int conef_ln_wgrad(const void* dy, const void* x, int dtype, long long rows, int cols, const float* mean,
+                   const float* rstd, float* partial, int nparts, float* dgamma, float* dbeta, cudaStream_t stream);
+// dst (bf16) = src (fp32), n elements; both 16-byte aligned
+int conef_cast_f32_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
 // y[row, c] += bias[c] in place (the bias of a convolution with a channels-last output)
 int conef_bias_add(void* y, int dtype, long long rows, int cols, const float* bias, int nparts, cudaStream_t stream);
 int conef_bn_apply(const void* x, void* y, int dtype, long long rows, int cols, const float* mean, const float* invstd,

@@ -159,6 +159,8 @@ _SIGNATURES = {
     "conef_colsum": ([vp, C.c_int, c_ll, C.c_int, vp, C.c_int, vp, vp], C.c_int),
     "conef_colstats": ([vp, C.c_int, c_ll, C.c_int, C.c_float, C.c_float, vp, C.c_int, vp, vp, vp, vp, vp], C.c_int),
     "conef_coldot": ([vp, vp, C.c_int, c_ll, C.c_int, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp], C.c_int),
+    "conef_ln_wgrad": ([vp, vp, C.c_int, c_ll, C.c_int, vp, vp, vp, C.c_int, vp, vp, vp], C.c_int),
+    "conef_cast_f32_bf16": ([vp, vp, c_ll, vp], C.c_int),
     "conef_bias_add": ([vp, C.c_int, c_ll, C.c_int, vp, C.c_int, vp], C.c_int),
     "conef_bn_apply": ([vp, vp, C.c_int, c_ll, C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, vp], C.c_int),
     "conef_coldot_relu": ([vp, vp, C.c_int, c_ll, C.c_int, vp, vp, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp], C.c_int),

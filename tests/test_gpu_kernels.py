@@ -442,3 +442,34 @@ def test_batch_norm_layer_matches_torch(dtype, relu):
     own.eval()
     want = ref_bn.eval()(x)
     torch.testing.assert_close(own(x, relu=relu), torch.relu(want) if relu else want, rtol=1e-4, atol=1e-3)
+
+
+def test_linear_and_layer_norm_layers_match_torch():
+    """``models.layers.Linear`` (bias gradient on the column-sum kernel) and ``models.layers.LayerNorm`` (weight
+    and bias gradients on the column kernel) against ``torch.nn`` under bf16 autocast and in fp32."""
+    from conef_b200.models.layers import LayerNorm, Linear
+    torch.manual_seed(5)
+    for autocast in (True, False):
+        ref_lin, own_lin = torch.nn.Linear(256, 512).to(DEV), Linear(256, 512).to(DEV)
+        ref_ln, own_ln = torch.nn.LayerNorm(512, eps=1e-12).to(DEV), LayerNorm(512, eps=1e-12).to(DEV)
+        with torch.no_grad():
+            ref_ln.weight.uniform_(0.5, 1.5)
+            ref_ln.bias.uniform_(-1, 1)
+        own_lin.load_state_dict(ref_lin.state_dict())
+        own_ln.load_state_dict(ref_ln.state_dict())
+        x = torch.randn(6, 37, 256, device=DEV)
+        g = torch.randn(6, 37, 512, device=DEV)
+        res = []
+        for lin, ln in ((ref_lin, ref_ln), (own_lin, own_ln)):
+            xi = x.clone().requires_grad_(True)
+            native.reset_launch_count()
+            with torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+                y = ln(lin(xi) * 3.0 + 20.0)
+            y.backward(g.to(y.dtype))
+            launches = native.reset_launch_count()
+            res.append((y.detach().float(), xi.grad, lin.weight.grad, lin.bias.grad, ln.weight.grad, ln.bias.grad))
+        assert launches >= 2, "the native kernels did not run"
+        tol = dict(rtol=3e-2, atol=3e-2) if autocast else dict(rtol=2e-4, atol=2e-4)
+        for a, b in zip(*res):
+            assert a.dtype == b.dtype and a.shape == b.shape
+            assert (a.float() - b.float()).norm() <= tol["rtol"] * b.float().norm() + tol["atol"]
