@@ -142,6 +142,7 @@ def build_workload(args, device, world):
     import torch.nn.functional as F
 
     from conef_b200 import models
+    from conef_b200.optim import FusedSGD
 
     ns = argparse.Namespace(grad_reducer="conef_powersgd", start_compression_iter=2, compression_ratio=0.1,
                             beta=0.9, sketch_size=0.1, matrix_approximation_rank=4, min_compression_rate=2,
@@ -150,7 +151,7 @@ def build_workload(args, device, world):
     if args.config == "wrn":
         batch = args.batch or 128
         model = models.WideResNet(16, 2, 0.3, 100) if args.small else models.WideResNet28_10(100)
-        opt = lambda p: torch.optim.SGD(p, lr=0.05, momentum=0.9, nesterov=True, weight_decay=5e-4)
+        opt = lambda p: FusedSGD(p, lr=0.05, momentum=0.9, nesterov=True, weight_decay=5e-4)
         loss_fn = F.cross_entropy
 
         def make_batch():
@@ -164,7 +165,7 @@ def build_workload(args, device, world):
         ns.error_compressor = "count_sketch3"
         ns.hash_seed = 7
         model = models.ResNet20(10)
-        opt = lambda p: torch.optim.SGD(p, lr=0.1, momentum=0.9)
+        opt = lambda p: FusedSGD(p, lr=0.1, momentum=0.9)
 
         def make_batch():
             return (torch.randn(batch, 3, 32, 32, generator=gen),), torch.randint(0, 10, (batch,), generator=gen)

@@ -351,6 +351,11 @@ int conef_lamb_step(const ConefLambTensor* tensors, int ntensors, const int2* ch
                     int step, int bias_correction, float grad_scale, float max_grad_norm,
                     cudaStream_t stream);
 
+// Multi-tensor SGD with momentum (torch.optim.SGD semantics; weight decay per tensor from the table, `v` unused;
+// first != 0: the momentum buffers are initialised with the gradient).
+int conef_sgd_step(const ConefLambTensor* tensors, int ntensors, const int2* chunks, int nchunks, int chunk_elems,
+                   float lr, float momentum, float dampening, int nesterov, int first, cudaStream_t stream);
+
 // ---- column sums (colsum.cu) -------------------------------------------------
 // out[c] = sum over rows of x[row, c] for a row-major (rows x cols) matrix: the bias gradient of a convolution
 // whose output gradient lies in channels-last memory.  dtype: 0 fp32, 1 bf16, 2 fp16.  partial: scratch of

@@ -130,3 +130,64 @@ extern "C" int conef_lamb_step_noalloc(const ConefLambTensor* tensors, int ntens
   return conef_lamb_step(tensors, ntensors, chunks, nchunks, chunk_elems, g_lamb_scratch_addr[dev], lr, beta1, beta2,
                          eps, step, bias_correction, grad_scale, max_grad_norm, stream);
 }
+
+// ---------------------------------------------------------------------------
+// Multi-tensor SGD with momentum: one launch over all tensors (the same tensor / chunk tables as LAMB; `v` is
+// unused).  torch.optim.SGD semantics: g += weight_decay p; buf = first ? g : momentum buf + (1 - dampening) g;
+// update = nesterov ? g + momentum buf : buf; p -= lr update.  PyTorch's foreach path is about fifteen launches
+// and three passes over parameters, gradients and buffers; this is one pass (read p, g, buf; write p, buf).
+__global__ void __launch_bounds__(L_THREADS)
+k_sgd_step(const ConefLambTensor* __restrict__ tensors, const int2* __restrict__ chunks, int chunk_elems, float lr,
+           float momentum, float dampening, int nesterov, int first) {
+  const int2 c = chunks[blockIdx.x];
+  const ConefLambTensor T = tensors[c.x];
+  const long long lo = (long long)c.y * chunk_elems;
+  const long long hi = min(lo + (long long)chunk_elems, T.numel);
+  const float wd = T.weight_decay;
+  const bool vec = ((reinterpret_cast<uintptr_t>(T.p) | reinterpret_cast<uintptr_t>(T.g) |
+                     reinterpret_cast<uintptr_t>(T.m)) & 15) == 0 && (lo & 3) == 0;
+  long long i = lo;
+  if (vec) {
+    const long long hi4 = lo + ((hi - lo) & ~3LL);
+    for (i = lo + 4LL * threadIdx.x; i < hi4; i += 4LL * L_THREADS) {
+      float4 p = *reinterpret_cast<const float4*>(T.p + i);
+      const float4 g4 = *reinterpret_cast<const float4*>(T.g + i);
+      float4 b = momentum != 0.f && !first ? *reinterpret_cast<const float4*>(T.m + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      float* pp = reinterpret_cast<float*>(&p);
+      const float* gp = reinterpret_cast<const float*>(&g4);
+      float* bp = reinterpret_cast<float*>(&b);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float g = fmaf(wd, pp[k], gp[k]);
+        float u = g;
+        if (momentum != 0.f) {
+          bp[k] = first ? g : fmaf(momentum, bp[k], (1.f - dampening) * g);
+          u = nesterov ? fmaf(momentum, bp[k], g) : bp[k];
+        }
+        pp[k] = fmaf(-lr, u, pp[k]);
+      }
+      *reinterpret_cast<float4*>(T.p + i) = p;
+      if (momentum != 0.f) *reinterpret_cast<float4*>(T.m + i) = b;
+    }
+    i = hi4;
+  }
+  for (i += threadIdx.x; i < hi; i += L_THREADS) {
+    const float g = fmaf(wd, T.p[i], T.g[i]);
+    float u = g;
+    if (momentum != 0.f) {
+      const float b = first ? g : fmaf(momentum, T.m[i], (1.f - dampening) * g);
+      T.m[i] = b;
+      u = nesterov ? fmaf(momentum, b, g) : b;
+    }
+    T.p[i] = fmaf(-lr, u, T.p[i]);
+  }
+}
+
+extern "C" int conef_sgd_step(const ConefLambTensor* tensors, int ntensors, const int2* chunks, int nchunks,
+                              int chunk_elems, float lr, float momentum, float dampening, int nesterov, int first,
+                              cudaStream_t stream) {
+  if (ntensors <= 0 || nchunks <= 0) return 0;
+  k_sgd_step<<<nchunks, L_THREADS, 0, stream>>>(tensors, chunks, chunk_elems, lr, momentum, dampening, nesterov, first);
+  CONEF_CHECK_LAUNCH("k_sgd_step");
+  return 0;
+}

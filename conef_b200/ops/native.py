@@ -156,6 +156,7 @@ _SIGNATURES = {
     "conef_psgd_decompress": ([vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float,
                                C.c_float, C.c_int, C.c_int, C.c_size_t, vp, vp], C.c_int),
     "conef_fill_normal": ([vp, c_ll, C.c_uint64, vp], C.c_int),
+    "conef_sgd_step": ([vp, C.c_int, vp, C.c_int, C.c_int, C.c_float, C.c_float, C.c_float, C.c_int, C.c_int, vp], C.c_int),
     "conef_colsum": ([vp, C.c_int, c_ll, C.c_int, vp, C.c_int, vp, vp], C.c_int),
     "conef_colstats": ([vp, C.c_int, c_ll, C.c_int, C.c_float, C.c_float, vp, C.c_int, vp, vp, vp, vp, vp], C.c_int),
     "conef_coldot": ([vp, vp, C.c_int, c_ll, C.c_int, vp, vp, vp, C.c_int, vp, vp, vp, vp, vp], C.c_int),

@@ -26,6 +26,7 @@ sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), ".."
 import conef_b200 as cb  # noqa: E402
 from conef_b200 import models  # noqa: E402
 from conef_b200.data import SyntheticImages  # noqa: E402
+from conef_b200.optim import FusedSGD  # noqa: E402
 from conef_b200.utils import GracefulStop, JsonLogger, make_directory, save_obj  # noqa: E402
 
 MODELS = {
@@ -138,8 +139,8 @@ def main():
     loader = DataLoader(ds, args.batch_size, sampler=sampler, num_workers=2, pin_memory=cuda, drop_last=True)
     trainer = cb.DataParallelTrainer(
         MODELS[args.model](classes),
-        lambda p: torch.optim.SGD(p, lr=args.lr, momentum=args.momentum, weight_decay=args.weight_decay,
-                                  nesterov=args.nesterov),
+        lambda p: FusedSGD(p, lr=args.lr, momentum=args.momentum, weight_decay=args.weight_decay,
+                           nesterov=args.nesterov),
         F.cross_entropy, reducer=args, device=device, autocast_dtype=torch.bfloat16 if (args.bf16 and cuda) else None,
         channels_last=cuda)
     defaults = [round(args.epochs * f) for f in (80 / 150, 120 / 150, 1.0)]

@@ -342,3 +342,22 @@ def test_shifted_cholesky_qr_matches_gram_schmidt_on_conditioned_input():
     ref.shifted_cholesky_qr2_(a)
     ref.gram_schmidt_ref(b)
     torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-5)
+
+
+@pytest.mark.parametrize("kw", [dict(momentum=0.9, nesterov=True, weight_decay=5e-4), dict(momentum=0.9, dampening=0.1),
+                                dict(weight_decay=1e-2), dict()])
+def test_fused_sgd_matches_torch_sgd_on_cpu(kw):
+    """FusedSGD's PyTorch-ops path (CPU tensors) against torch.optim.SGD over several steps."""
+    from conef_b200.optim import FusedSGD
+    torch.manual_seed(0)
+    ref_p = [torch.nn.Parameter(torch.randn(13, 7)), torch.nn.Parameter(torch.randn(5))]
+    own_p = [torch.nn.Parameter(p.detach().clone()) for p in ref_p]
+    ref_opt, own_opt = torch.optim.SGD(ref_p, lr=0.1, **kw), FusedSGD(own_p, lr=0.1, **kw)
+    for step in range(4):
+        for a, b in zip(ref_p, own_p):
+            g = torch.randn_like(a)
+            a.grad, b.grad = g.clone(), g.clone()
+        ref_opt.step()
+        own_opt.step()
+    for a, b in zip(ref_p, own_p):
+        torch.testing.assert_close(a, b)
