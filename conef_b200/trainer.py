@@ -25,16 +25,86 @@ from torch.nn.parallel import DistributedDataParallel
 from .parallel.registry import build_state_and_hook
 
 
+def _graph_submodules(model, modules, sample_inputs, device, autocast_dtype, channels_last) -> int:
+    """Capture forward and backward of ``modules`` as CUDA graphs (``torch.cuda.make_graphed_callables``; must
+    happen before the model is wrapped in DistributedDataParallel).  The input shapes come from one dry run
+    of the model on ``sample_inputs``; a module called with another shape, without gradients or in
+    evaluation mode runs its own code.  Returns the number of modules captured."""
+    if not modules:
+        return 0
+    sample = []
+    for t in sample_inputs:
+        t = t.to(device)
+        if channels_last and t.dim() == 4:
+            t = t.contiguous(memory_format=torch.channels_last)
+        sample.append(t)
+    shapes, handles = {}, []
+    def note_shape(mod, args):      # (a pre-hook's return value would replace the inputs: return nothing)
+        shapes.setdefault(id(mod), (tuple(args[0].shape), args[0].dtype, len(args)))
+
+    for m in modules:
+        handles.append(m.register_forward_pre_hook(note_shape))
+    ctx = (lambda: torch.autocast("cuda", dtype=autocast_dtype, cache_enabled=False)) if autocast_dtype is not None \
+        else contextlib.nullcontext
+    was_training = model.training
+    buffers = {name: b.detach().clone() for name, b in model.named_buffers()}      # batch-norm statistics, counters
+    model.train()
+    with torch.no_grad(), ctx():
+        model(*sample)
+    for h in handles:
+        h.remove()
+    if any(id(m) not in shapes or shapes[id(m)][2] != 1 for m in modules):
+        with torch.no_grad():
+            for name, b in model.named_buffers():
+                b.copy_(buffers[name])
+        model.train(was_training)
+        return 0
+    args = []
+    for m in modules:
+        shape, dtype, _ = shapes[id(m)]
+        x = torch.randn(shape, device=device, dtype=dtype)
+        if channels_last and x.dim() == 4:
+            x = x.contiguous(memory_format=torch.channels_last)
+        args.append((x.requires_grad_(True),))
+    eager = [m.forward for m in modules]
+    with ctx():
+        torch.cuda.make_graphed_callables(tuple(modules), tuple(args), num_warmup_iters=3)
+    # the warm-up ran on a side stream, so the parameters' AccumulateGrad nodes belong to that stream: autograd
+    # orders them against the training stream with an event and says so at every backward pass
+    mute = getattr(torch.autograd.graph, "set_warn_on_accumulate_grad_stream_mismatch", None)
+    if mute is not None:
+        mute(False)
+    for m, own, (shape, dtype, _) in zip(modules, eager, (shapes[id(m)] for m in modules)):
+        graphed = m.forward
+
+        def guarded(x, _g=graphed, _own=own, _shape=shape, _dtype=dtype):
+            if torch.is_grad_enabled() and x.requires_grad and tuple(x.shape) == _shape and x.dtype == _dtype:
+                return _g(x)
+            return _own(x)
+        m.forward = guarded
+    with torch.no_grad():      # in place: the graphs hold the buffers' addresses
+        for name, b in model.named_buffers():
+            b.copy_(buffers[name])
+    model.train(was_training)
+    return len(modules)
+
+
 class DataParallelTrainer:
     def __init__(self, model: torch.nn.Module, optimizer_factory: Callable, loss_fn: Callable, *,
                  reducer: Union[None, Any, Tuple[Any, Callable]] = None, device: Optional[torch.device] = None,
                  autocast_dtype: Optional[torch.dtype] = None, bucket_cap_mb: float = 25.0,
                  channels_last: bool = False, grad_clip: Optional[float] = None,
-                 forward_fn: Optional[Callable] = None):
+                 forward_fn: Optional[Callable] = None,
+                 graph_modules: Optional[Callable[[torch.nn.Module], Sequence[torch.nn.Module]]] = None,
+                 graph_sample_inputs: Optional[Sequence[torch.Tensor]] = None):
         """``reducer`` is ``None`` (plain all-reduce), an argparse-like namespace with
         ``grad_reducer`` etc. (see :func:`conef_b200.get_comm_hooks`), or a ``(state, hook)`` pair.
         ``optimizer_factory(params)`` builds the optimizer on the wrapped model's parameters.
-        ``forward_fn(model, *inputs)`` customises the forward call (default ``model(*inputs)``)."""
+        ``forward_fn(model, *inputs)`` customises the forward call (default ``model(*inputs)``).
+        ``graph_modules(model)`` names submodules (each taking and returning one tensor) whose forward and
+        backward passes are captured as CUDA graphs from ``graph_sample_inputs`` (one batch of model inputs
+        of the training shape): a step of a deep CNN is otherwise bound by the host's launch rate, not by
+        the GPU.  Other input shapes, evaluation mode and CPU runs go through the modules' own code."""
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() \
                 else torch.device("cpu")
@@ -43,6 +113,10 @@ class DataParallelTrainer:
         if channels_last:
             model = model.to(memory_format=torch.channels_last)
         self.channels_last = channels_last
+        self.graphed_modules = 0
+        if graph_modules is not None and graph_sample_inputs is not None and device.type == "cuda":
+            self.graphed_modules = _graph_submodules(model, list(graph_modules(model)), graph_sample_inputs, device,
+                                                     autocast_dtype, channels_last)
         ddp_kwargs = dict(bucket_cap_mb=bucket_cap_mb, gradient_as_bucket_view=True)
         if device.type == "cuda":
             ddp_kwargs.update(device_ids=[device.index], output_device=device.index)

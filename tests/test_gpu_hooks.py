@@ -546,3 +546,33 @@ def _rb_state(**kw):
     s = cb.RandomBlockState(None, compression_ratio=0.1, start_compression_iter=2, **kw)
     s.iter = 2
     return s
+
+
+def test_trainer_with_cuda_graph_blocks_matches_eager(single_rank_group, monkeypatch):
+    """``DataParallelTrainer(graph_modules=...)``: forward and backward of the model's blocks replayed as CUDA
+    graphs (custom layers and their kernels inside the capture) against the same training run in eager mode;
+    batch-norm statistics must not be disturbed by the capture, other batch sizes take the modules' own code."""
+    from conef_b200 import DataParallelTrainer, models
+    monkeypatch.setenv("CONEF_BACKEND", "native")
+
+    def run(graph):
+        torch.manual_seed(0)
+        model = models.WideResNet(10, 2, 0.0, 10)
+        x = torch.randn(16, 3, 32, 32)
+        y = torch.randint(0, 10, (16,))
+        kw = dict(graph_modules=lambda m: list(m.blocks), graph_sample_inputs=(x,)) if graph else {}
+        tr = DataParallelTrainer(model, lambda p: torch.optim.SGD(p, lr=0.05, momentum=0.9), torch.nn.functional.cross_entropy,
+                                 reducer=None, device=torch.device(DEV, 0), autocast_dtype=torch.bfloat16,
+                                 channels_last=True, **kw)
+        stats0 = model.blocks[0].bn1.running_mean.clone()
+        losses = [float(tr.step(x, y)) for _ in range(6)]
+        small = float(tr.step(x[:8], y[:8]))      # another batch size: not the captured shape
+        return losses, small, tr.graphed_modules, stats0
+
+    eager, eager_small, n0, s0 = run(False)
+    graphed, graphed_small, n1, s1 = run(True)
+    assert n0 == 0 and n1 == 3
+    assert torch.equal(s0, s1) and float(s1.abs().max()) == 0.0      # capture left the running statistics alone
+    assert graphed[-1] < graphed[0]
+    for a, b in zip(eager + [eager_small], graphed + [graphed_small]):
+        assert abs(a - b) <= 0.05 * max(1.0, abs(a)), (eager, graphed)
