@@ -52,8 +52,8 @@ def parse():
     p.add_argument("--weight_decay", type=float, default=5e-4)
     p.add_argument("--nesterov", action="store_true", default=True)
     p.add_argument("--lr_decay_ratio", type=float, default=10, help="the learning rate is divided by this ...")
-    p.add_argument("--lr_decay_at_epoch1", type=int, default=None, help="... at these epochs (default: 53 %, 80 %")
-    p.add_argument("--lr_decay_at_epoch2", type=int, default=None, help="and 100 % of --epochs, the reference's")
+    p.add_argument("--lr_decay_at_epoch1", type=int, default=None, help="... at these epochs (default: 53 %%, 80 %%")
+    p.add_argument("--lr_decay_at_epoch2", type=int, default=None, help="and 100 %% of --epochs, the reference's")
     p.add_argument("--lr_decay_at_epoch3", type=int, default=None, help="80 / 120 / 150 of 150)")
     p.add_argument("--test_steps", type=int, default=10, help="synthetic data only: test batches per epoch")
     p.add_argument("--name", default="image_classification", help="results go to <results>/<name>")
@@ -68,6 +68,8 @@ def parse():
     p.add_argument("--orthogonalization_epsilon", type=float, default=0)
     p.add_argument("--error_compressor", default=None)
     p.add_argument("--bf16", action="store_true")
+    p.add_argument("--cuda_graphs", action="store_true",
+                   help="replay the forward and backward passes of the model's blocks as CUDA graphs (fixed batch size)")
     p.add_argument("--results", default="results")
     p.add_argument("--seed", type=int, default=0)
     return p.parse_args()
@@ -137,12 +139,17 @@ def main():
     test_loader = DataLoader(test_ds, args.batch_size, shuffle=False, num_workers=2, pin_memory=cuda)
     sampler = DistributedSampler(ds, world, rank, shuffle=True, seed=args.seed)
     loader = DataLoader(ds, args.batch_size, sampler=sampler, num_workers=2, pin_memory=cuda, drop_last=True)
+    net = MODELS[args.model](classes)
+    graph_kw = {}
+    if args.cuda_graphs and cuda and isinstance(getattr(net, "blocks", None), torch.nn.Sequential):
+        graph_kw = dict(graph_modules=lambda m: list(m.blocks),
+                        graph_sample_inputs=(torch.randn(args.batch_size, 3, 32, 32),))
     trainer = cb.DataParallelTrainer(
-        MODELS[args.model](classes),
+        net,
         lambda p: FusedSGD(p, lr=args.lr, momentum=args.momentum, weight_decay=args.weight_decay,
                            nesterov=args.nesterov),
         F.cross_entropy, reducer=args, device=device, autocast_dtype=torch.bfloat16 if (args.bf16 and cuda) else None,
-        channels_last=cuda)
+        channels_last=cuda, **graph_kw)
     defaults = [round(args.epochs * f) for f in (80 / 150, 120 / 150, 1.0)]
     decay_at = {d if v is None else v for v, d in zip(
         (args.lr_decay_at_epoch1, args.lr_decay_at_epoch2, args.lr_decay_at_epoch3), defaults)}
