@@ -4,8 +4,12 @@
 first gradient, dampening, Nesterov), for the image-classification and language-modelling drivers of the
 reference (examples/ImageClassification/main.py:188-190, examples/LanguageModeling/main.py).  On CUDA fp32
 parameters the step is a single pass over parameters, gradients and momentum buffers
-(``csrc/lamb.cu:k_sgd_step``); PyTorch's foreach path is about fifteen launches and three passes.  Anything
-else (CPU, other dtypes, ``maximize``) runs as PyTorch ops.
+(``csrc/lamb.cu:k_sgd_step``); PyTorch's foreach path is about fifteen launches and three passes.  The
+kernel walks the storage, so a parameter qualifies when it is dense in any dimension order (contiguous or
+channels-last) and its gradient and momentum buffer have the same strides; the others of a group (CPU,
+other dtypes, strided views) run as PyTorch ops beside it.  ``zero_grad(set_to_none=False)`` clears all
+gradients with one multi-tensor call, which keeps the gradient addresses (and the kernel's tensor table)
+stable from step to step.
 """
 from __future__ import annotations
 
@@ -16,6 +20,23 @@ from torch.optim import Optimizer
 from ..ops import native
 
 CHUNK = 65536
+
+
+def _dense(t):
+    """Non-overlapping and dense: the elements fill the storage range in some dimension order."""
+    if t.is_contiguous():
+        return True
+    if t.dim() == 4:
+        return t.is_contiguous(memory_format=torch.channels_last)
+    if t.dim() == 5:
+        return t.is_contiguous(memory_format=torch.channels_last_3d)
+    return False
+
+
+def _fusable(p):
+    g = p.grad
+    return (p.is_cuda and p.dtype == torch.float32 and g.dtype == torch.float32 and g.layout == torch.strided
+            and _dense(p) and g.stride() == p.stride())
 
 
 class FusedSGD(Optimizer):
@@ -42,14 +63,31 @@ class FusedSGD(Optimizer):
             params = [p for p in group["params"] if p.grad is not None]
             if not params:
                 continue
-            fused = all(p.is_cuda and p.dtype == torch.float32 and p.grad.dtype == torch.float32
-                        and p.is_contiguous() and p.grad.is_contiguous() for p in params) \
-                and native.use_native(params[0])
+            fused = [p for p in params if _fusable(p)]
+            if fused and not native.use_native(fused[0]):
+                fused = []
+            if len(fused) != len(params):
+                chosen = set(map(id, fused))
+                self._step_torch(group, [p for p in params if id(p) not in chosen])
             if fused:
-                self._step_fused(gi, group, params)
-            else:
-                self._step_torch(group, params)
+                self._step_fused(gi, group, fused)
         return loss
+
+    @torch.no_grad()
+    def zero_grad(self, set_to_none: bool = True):
+        if set_to_none:
+            return super().zero_grad(set_to_none=True)
+        by_kind = {}
+        for group in self.param_groups:
+            for p in group["params"]:
+                if p.grad is not None:
+                    if p.grad.grad_fn is not None:
+                        p.grad.detach_()
+                    else:
+                        p.grad.requires_grad_(False)
+                    by_kind.setdefault((p.grad.device, p.grad.dtype), []).append(p.grad)
+        for grads in by_kind.values():
+            torch._foreach_zero_(grads)
 
     def _step_torch(self, group, params):
         lr, mu, damp, wd, nest = (group[k] for k in ("lr", "momentum", "dampening", "weight_decay", "nesterov"))
@@ -77,7 +115,7 @@ class FusedSGD(Optimizer):
             if first:
                 for p in params:
                     self.state[p]["momentum_buffer"] = torch.empty_like(p, memory_format=torch.preserve_format)
-            if not all(self.state[p]["momentum_buffer"].is_contiguous() for p in params):
+            if not all(self.state[p]["momentum_buffer"].stride() == p.stride() for p in params):
                 return self._step_torch(group, params)
         key = tuple((p.data_ptr(), p.grad.data_ptr(), self.state[p]['momentum_buffer'].data_ptr() if mu != 0 else 0)
                     for p in params) + (wd,)

@@ -496,3 +496,35 @@ def test_fused_sgd_kernel_matches_torch_sgd(kw):
         assert native.reset_launch_count() == 1
     for a, b in zip(ref_p, own_p):
         torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_fused_sgd_takes_channels_last_and_mixed_groups():
+    """Channels-last convolution weights go through the kernel (it walks the storage); a strided view in the
+    same group runs as PyTorch ops beside it; zero_grad keeps the gradient tensors and clears them."""
+    from conef_b200.optim import FusedSGD
+    torch.manual_seed(1)
+    kw = dict(lr=0.05, momentum=0.9, weight_decay=5e-4)
+    w = torch.randn(64, 32, 3, 3, device=DEV).contiguous(memory_format=torch.channels_last)
+    wide = torch.randn(40, 12, device=DEV)
+    ref_p = [torch.nn.Parameter(w.clone(memory_format=torch.preserve_format)), torch.nn.Parameter(torch.randn(33, device=DEV)),
+             torch.nn.Parameter(wide.clone())]
+    own_p = [torch.nn.Parameter(p.detach().clone(memory_format=torch.preserve_format)) for p in ref_p]
+    assert not own_p[0].is_contiguous() and own_p[0].stride() == ref_p[0].stride()
+    ref_opt, own_opt = torch.optim.SGD(ref_p, **kw), FusedSGD(own_p, **kw)
+    for step in range(3):
+        for i, (a, b) in enumerate(zip(ref_p, own_p)):
+            g = torch.randn_like(a)                      # keeps the parameter's strides
+            a.grad = g.clone(memory_format=torch.preserve_format)
+            b.grad = g.clone(memory_format=torch.preserve_format) if i < 2 else g.t().contiguous().t()   # transposed strides
+        native.reset_launch_count()
+        ref_opt.step()
+        own_opt.step()
+        assert native.reset_launch_count() == 1          # the two dense parameters; the third took the PyTorch path
+    for a, b in zip(ref_p, own_p):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    ptrs = [p.grad.data_ptr() for p in own_p]
+    own_opt.zero_grad(set_to_none=False)
+    assert [p.grad.data_ptr() for p in own_p] == ptrs and all(float(p.grad.abs().max()) == 0 for p in own_p)
+    own_opt.zero_grad()
+    assert all(p.grad is None for p in own_p)

@@ -361,3 +361,18 @@ def test_fused_sgd_matches_torch_sgd_on_cpu(kw):
         own_opt.step()
     for a, b in zip(ref_p, own_p):
         torch.testing.assert_close(a, b)
+
+
+def test_fused_sgd_zero_grad_keeps_or_drops_the_gradient_tensors():
+    """``zero_grad(set_to_none=False)`` clears in place (same tensors, any dtype mix); the default drops them."""
+    from conef_b200.optim import FusedSGD
+    ps = [torch.nn.Parameter(torch.randn(5, 3)), torch.nn.Parameter(torch.randn(7).double()),
+          torch.nn.Parameter(torch.randn(2, 2))]
+    opt = FusedSGD(ps, lr=0.1, momentum=0.9)
+    for p in ps[:2]:
+        p.grad = torch.randn_like(p)
+    kept = [p.grad for p in ps[:2]]
+    opt.zero_grad(set_to_none=False)
+    assert all(p.grad is g and float(g.abs().sum()) == 0 for p, g in zip(ps[:2], kept)) and ps[2].grad is None
+    opt.zero_grad()
+    assert all(p.grad is None for p in ps)
