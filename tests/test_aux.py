@@ -572,3 +572,86 @@ def test_cluster_and_container_launch_files_parse():
         out = subprocess.run(["bash", os.path.join(ex, "run.sub")], capture_output=True, text=True, check=True, env=env).stdout
     assert "--nnodes 2" in out and "--master_addr node-a" in out and "--max_seq_length 512" in out
     assert "--grad_reducer ef_powersgd" in out and "--init_checkpoint results/bert/phase1" in out
+
+
+def test_model_repository_export_and_in_process_client(tmp_path):
+    """Export a tiny QA model as a served-model repository, check ``config.pbtxt`` and the exported-against-eager
+    errors, then answer questions and a SQuAD file through the in-process back end of the client."""
+    import importlib.util, json, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def load(name, rel):
+        spec = importlib.util.spec_from_file_location(name, os.path.join(root, rel))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        return mod
+
+    exp = load("deploy_export", "examples/bert_pretraining/deploy/export.py")
+    cli = load("deploy_client", "examples/bert_pretraining/deploy/client.py")
+    vf, _ = _toy_corpus(tmp_path)
+    tok = data.BertTokenizer(str(vf))
+    repo = tmp_path / "repo"
+    rep = exp.main(["--repository", str(repo), "--model_name", "qa", "--bert_model", "tiny", "--tiny_vocab",
+                    str(max(len(tok.vocab), 8)), "--max_seq_length", "32", "--batch_size", "3", "--no_cuda",
+                    "--dynamic_batching_delay_us", "50", "--preferred_batch_sizes", "2", "--tolerance", "1e-5"])
+    assert rep["check"]["max_linf"] <= 1e-5 and rep["check"]["tensors_compared"] == 6
+    assert rep["input_dims"] == [[-1]] * 3 and rep["output_dims"] == [[-1]] * 2      # the sequence axis is dynamic
+    text = (repo / "qa" / "config.pbtxt").read_text()
+    assert 'platform: "pytorch_libtorch"' in text and "max_batch_size: 3" in text and "KIND_CPU" in text
+    assert text.count("TYPE_INT64") == 3 and text.count("TYPE_FP32") == 2 and "preferred_batch_size: [2]" in text
+    assert (repo / "qa" / "1" / "model.pt").exists()
+    cfg = cli.read_config(str(repo / "qa" / "config.pbtxt"))
+    assert cfg == {"max_batch_size": 3, "inputs": ["input__0", "input__1", "input__2"],
+                   "outputs": ["output__0", "output__1"]}
+
+    backend = cli.LocalBackend(str(repo), "qa", device="cpu")
+    pairs = [("the cat", "the dog sat on the mat fast")] * 5 + [("the dog", "the cat sat")] * 2
+    spans = cli.answer_batch(backend, tok, pairs, max_seq_length=24, max_query_length=4, n_best_size=3)
+    assert len(spans) == 7 and spans[0] == spans[4] and all(isinstance(s[0]["text"], str) for s in spans)
+    # seven requests went through in chunks of max_batch_size = 3 and equal the one-by-one answers
+    single = cli.answer_batch(backend, tok, pairs[5:6], max_seq_length=24, max_query_length=4, n_best_size=3)
+    assert single[0] == spans[5]
+
+    squad = {"data": [{"paragraphs": [{"context": "the dog sat on the mat",
+                                       "qas": [{"id": "q1", "question": "the cat"}, {"id": "q2", "question": "the mat"}]}]}]}
+    sf = tmp_path / "dev.json"
+    sf.write_text(json.dumps(squad))
+    out = tmp_path / "pred.json"
+    preds = cli.main(["--local_repository", str(repo), "--model_name", "qa", "--vocab_file", str(vf), "--device", "cpu",
+                      "--squad_file", str(sf), "--output_file", str(out), "--max_seq_length", "24", "--batch_size", "2"])
+    assert set(preds) == {"q1", "q2"} and json.loads(out.read_text()) == preds
+    perf = cli.main(["--local_repository", str(repo), "--model_name", "qa", "--device", "cpu", "--perf",
+                     "--batch_size", "4", "--max_seq_length", "16", "--perf_iters", "2", "--perf_vocab", "8"])
+    assert perf["seq_per_s"] > 0 and perf["batch_size"] == 4
+    with pytest.raises(RuntimeError, match="tritonclient"):
+        cli.TritonBackend("127.0.0.1:8000", "qa")
+    gold = {"data": [{"paragraphs": [{"context": "c", "qas": [
+        {"id": "a", "answers": [{"text": "The Mat."}, {"text": "a rug"}]},
+        {"id": "b", "answers": [{"text": "on the red mat"}]}, {"id": "c", "answers": [{"text": "dog"}]}]}]}]}
+    gf = tmp_path / "gold.json"
+    gf.write_text(json.dumps(gold))
+    sc = cli.squad_scores({"a": "mat", "b": "the mat", "c": "cat"}, str(gf))
+    # a: exact after normalisation; b: one of three gold words, precision 1 and recall 1/3, F1 = 0.5; c: nothing shared
+    assert sc["questions"] == 3 and abs(sc["exact_match"] - 100 / 3) < 1e-9 and abs(sc["f1"] - 50.0) < 1e-9
+    assert exp.dynamic_dims([(torch.zeros(2, 5, 7),), (torch.zeros(3, 5, 9),)]) == [[5, -1]]
+
+
+def test_serving_scripts_parse_and_dry_run():
+    """The server launch needs a container runtime: its command line is printed instead (DRY_RUN=1); the wait
+    script gives up after its limit when nothing listens; the export script chains exporter and client."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    d = os.path.join(root, "examples/bert_pretraining/deploy")
+    for f in ("launch_server.sh", "wait_for_server.sh", "export_model.sh"):
+        subprocess.run(["bash", "-n", os.path.join(d, f)], check=True)
+    env = dict(os.environ, DRY_RUN="1", REPOSITORY="/models/repo", GPUS="0,1")
+    out = subprocess.run(["bash", os.path.join(d, "launch_server.sh")], capture_output=True, text=True, check=True, env=env).stdout
+    assert "--gpus device=0,1" in out and "-v /models/repo:/models:ro" in out and "tritonserver --model-repository=/models" in out
+    out = subprocess.run(["bash", os.path.join(d, "export_model.sh"), "ck.pt", "4", "fp16", "ts-trace", "128"],
+                         capture_output=True, text=True, check=True,
+                         env=dict(env, VOCAB_FILE="v.txt", SQUAD_FILE="dev.json", BERT_MODEL="base")).stdout.splitlines()
+    assert len(out) == 3 and "export.py" in out[0] and "--fp16" in out[0] and "--init_checkpoint ck.pt" in out[0]
+    assert "--squad_file dev.json --evaluate" in out[1] and "--perf" in out[2]
+    r = subprocess.run(["bash", os.path.join(d, "wait_for_server.sh"), "127.0.0.1:%d" % free_port(), "1"],
+                       capture_output=True, text=True)
+    assert r.returncode == 1 and "did not become ready" in r.stderr
