@@ -576,3 +576,50 @@ def test_trainer_with_cuda_graph_blocks_matches_eager(single_rank_group, monkeyp
     assert graphed[-1] < graphed[0]
     for a, b in zip(eager + [eager_small], graphed + [graphed_small]):
         assert abs(a - b) <= 0.05 * max(1.0, abs(a)), (eager, graphed)
+
+
+@pytest.mark.gpu
+def test_three_hundred_steps_native_tensorcore_path_converges_like_the_torch_path(single_rank_group, monkeypatch):
+    """300 optimisation steps of a small MLP on a fixed, learnable data set with PowerSGD + count-sketch error
+    feedback: the native pipeline (tf32 tensor-core tiles, fused kernels) must train as well as the PyTorch-ops
+    path of the same hook and nearly as well as the uncompressed all-reduce.  The two compressed runs start from
+    different random Q, so the comparison is on the loss level reached (mean of the last 50 steps), not on values."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    from conef_b200 import DataParallelTrainer
+
+    g = torch.Generator().manual_seed(11)
+    x_all = torch.randn(512, 768, generator=g)
+    y_all = (x_all @ torch.randn(768, 10, generator=g)).argmax(1)
+    x_all, y_all = x_all.to(DEV), y_all.to(DEV)
+
+    def run(backend, reducer):
+        monkeypatch.setenv("CONEF_BACKEND", backend)
+        monkeypatch.setenv("CONEF_TC", "1")
+        torch.manual_seed(3)
+        ns = argparse.Namespace(grad_reducer=reducer, start_compression_iter=5, compression_ratio=0.1, beta=0.9,
+                                sketch_size=0.1, matrix_approximation_rank=4, min_compression_rate=2,
+                                orthogonalization_epsilon=0, error_compressor=None)
+        net = nn.Sequential(nn.Linear(768, 512), nn.ReLU(), nn.Linear(512, 512), nn.ReLU(), nn.Linear(512, 10))
+        tr = DataParallelTrainer(net, lambda p: torch.optim.SGD(p, lr=0.02, momentum=0.9), F.cross_entropy,
+                                 reducer=ns, device=torch.device(DEV, 0), bucket_cap_mb=0.5)
+        losses = []
+        for step in range(300):
+            lo = (step * 64) % 512
+            losses.append(tr.step(x_all[lo:lo + 64], y_all[lo:lo + 64]))
+        torch.cuda.synchronize()
+        tr.check()
+        losses = [float(v) for v in losses]
+        return losses[0], sum(losses[-50:]) / 50
+
+    native.reset_launch_count()
+    first_n, last_n = run("native", "conef_powersgd")
+    assert native.reset_launch_count() > 300          # the native pipeline ran every compressed step
+    first_t, last_t = run("torch", "conef_powersgd")
+    first_a, last_a = run("native", "allreduce")
+    print(f"loss start {first_n:.3f}; last 50 steps: native {last_n:.4f}, torch path {last_t:.4f}, all-reduce {last_a:.4f}")
+    assert first_n == pytest.approx(first_t, rel=1e-4) and first_n == pytest.approx(first_a, rel=1e-4)
+    assert last_n < 0.5 * first_n and last_t < 0.5 * first_n
+    assert last_n <= 1.5 * last_t + 0.1 and last_t <= 1.5 * last_n + 0.1
+    assert last_n <= 3.0 * last_a + 0.3
