@@ -655,3 +655,72 @@ def test_serving_scripts_parse_and_dry_run():
     r = subprocess.run(["bash", os.path.join(d, "wait_for_server.sh"), "127.0.0.1:%d" % free_port(), "1"],
                        capture_output=True, text=True)
     assert r.returncode == 1 and "did not become ready" in r.stderr
+
+
+def test_glue_fine_tuning_driver_trains_evaluates_and_reloads(tmp_path):
+    """The sentence-pair fine-tuning driver on a toy task (label 1 when the first sentence has a cat): the loss
+    falls, the dev metrics are written, and an evaluation-only run from the saved weights repeats them; a
+    pre-training checkpoint contributes its encoder and leaves the classifier fresh."""
+    import importlib.util, json, random
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("run_glue", os.path.join(root, "examples/bert_pretraining/run_glue.py"))
+    rg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rg)
+    vf, _ = _toy_corpus(tmp_path)
+    rng = random.Random(1)
+    words = ["dog", "sat", "ran", "on", "mat", "fast", "slow", "blue", "red", "house", "tree"]
+
+    def rows(n):
+        out = ["Quality\t#1 ID\t#2 ID\t#1 String\t#2 String"]
+        for i in range(n):
+            a = [rng.choice(words) for _ in range(rng.randint(2, 5))]
+            lab = i % 2
+            if lab:
+                a[rng.randrange(len(a))] = "cat"
+            b = [rng.choice(words) for _ in range(rng.randint(2, 5))]
+            out.append(f"{lab}\t{i}\t{i}\t{' '.join(a)}\t{' '.join(b)}")
+        return "\n".join(out) + "\n"
+    d = tmp_path / "mrpc"
+    d.mkdir()
+    (d / "train.tsv").write_text(rows(96))
+    (d / "dev.tsv").write_text(rows(32))
+    out = tmp_path / "out"
+    common = ["--task_name", "mrpc", "--data_dir", str(d), "--vocab_file", str(vf), "--bert_model", "tiny", "--no_cuda",
+              "--max_seq_length", "16", "--output_dir", str(out)]
+    res = rg.main(common + ["--do_train", "--do_eval", "--train_batch_size", "16", "--gradient_accumulation_steps", "2",
+                            "--learning_rate", "5e-4", "--num_train_epochs", "10"])
+    assert res["train_steps"] == 60 and res["train_loss_last"] < 0.5 * res["train_loss_first"]
+    assert res["eval_examples"] == 32 and res["eval_accuracy"] >= 0.9 and 0.0 <= res["eval_f1"] <= 1.0
+    assert json.loads((out / "eval_results.json").read_text())["eval_accuracy"] == res["eval_accuracy"]
+    again = rg.main(common + ["--do_eval", "--init_checkpoint", str(out / "pytorch_model.pt")])
+    assert again["eval_accuracy"] == res["eval_accuracy"] and again["tensors_not_in_checkpoint"] == 0
+    assert abs(again["eval_loss"] - res["eval_loss"]) < 1e-6
+    # a pre-training checkpoint: encoder tensors are taken, the two classifier tensors stay fresh
+    from conef_b200 import models
+    sd = torch.load(out / "pytorch_model.pt")["model"]
+    pre = {k: v for k, v in sd.items() if not k.startswith("classifier.")}
+    torch.save({"model": pre}, tmp_path / "pre.pt")
+    third = rg.main(common + ["--do_eval", "--init_checkpoint", str(tmp_path / "pre.pt")])
+    assert third["tensors_not_in_checkpoint"] == 2
+    m = rg.classification_metrics("cola", [1, 1, 0, 0], [1, 0, 0, 0])
+    assert abs(m["mcc"] - (1 * 2 - 1 * 0) / (2 * 1 * 3 * 2) ** 0.5) < 1e-12 and m["accuracy"] == 0.75
+    assert rg.classification_metrics("mrpc", [1, 1, 0], [1, 0, 1])["f1"] == 0.5
+    assert "f1" not in rg.classification_metrics("sst-2", [1], [1])
+
+
+def test_glue_launcher_and_presets_dry_run(tmp_path):
+    """Task x machine presets split the global batch into per-GPU batch and accumulation; the launcher turns them
+    into the driver's command line (printed under DRY_RUN=1) and runs evaluation alone on one GPU."""
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ex = os.path.join(root, "examples/bert_pretraining")
+    for f in ("run_glue.sh", "configs/glue_config.sh"):
+        subprocess.run(["bash", "-n", os.path.join(ex, f)], check=True)
+    script = (f"source {ex}/configs/glue_config.sh && glue_sst2 && b200_1gpu_fp32 && glue_show && "
+              f"glue_mrpc && b200_8gpu_bf16 && glue_show && DRY_RUN=1 OUT={tmp_path}/o bash {ex}/run_glue.sh && "
+              f"MODE=eval DRY_RUN=1 OUT={tmp_path}/o CHECKPOINT=ck.pt bash {ex}/run_glue.sh")
+    out = subprocess.run(["bash", "-c", script], capture_output=True, text=True, check=True).stdout.splitlines()
+    assert "TASK=sst-2 GPUS=1 BATCH=256 ACCUM=4" in out[0] and "PRECISION=fp32" in out[0]
+    assert "TASK=mrpc GPUS=8 BATCH=16 ACCUM=1" in out[1]
+    assert "--nproc-per-node 8" in out[2] and "--task_name mrpc" in out[2] and "--do_train --do_eval --bf16" in out[2]
+    assert "torch.distributed.run" not in out[3] and "--do_train" not in out[3] and "--init_checkpoint ck.pt" in out[3]
