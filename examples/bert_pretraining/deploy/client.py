@@ -32,6 +32,7 @@ sys.path.insert(0, os.path.join(HERE, "..", "..", ".."))
 sys.path.insert(0, os.path.join(HERE, ".."))
 
 from inference import best_spans, build_features  # noqa: E402
+from conef_b200.data.squad import squad_scores  # noqa: E402,F401
 from conef_b200.data.tokenization import BertTokenizer  # noqa: E402
 
 
@@ -130,37 +131,6 @@ def read_squad(path):
             for qa in para["qas"]:
                 rows.append((qa["id"], qa["question"], para["context"]))
     return rows
-
-
-def _normalise_answer(text):
-    text = "".join(ch for ch in text.lower() if ch.isalnum() or ch.isspace())
-    return [w for w in text.split() if w not in ("a", "an", "the")]
-
-
-def squad_scores(predictions, path):
-    """Exact match and F1 (percent) of ``{id: text}`` against the gold answers of a SQuAD file, with the
-    benchmark's answer normalisation (case, punctuation and articles ignored; best score over the golds)."""
-    em = f1 = n = 0
-    for article in json.load(open(path))["data"]:
-        for para in article["paragraphs"]:
-            for qa in para["qas"]:
-                golds = [a["text"] for a in qa.get("answers", [])] or [""]
-                pred = _normalise_answer(predictions.get(qa["id"], ""))
-                best_em = best_f1 = 0.0
-                for g in golds:
-                    gold = _normalise_answer(g)
-                    best_em = max(best_em, float(pred == gold))
-                    common = sum(min(pred.count(w), gold.count(w)) for w in set(pred))
-                    if not pred or not gold:
-                        score = float(pred == gold)
-                    elif common == 0:
-                        score = 0.0
-                    else:
-                        prec, rec = common / len(pred), common / len(gold)
-                        score = 2 * prec * rec / (prec + rec)
-                    best_f1 = max(best_f1, score)
-                em, f1, n = em + best_em, f1 + best_f1, n + 1
-    return {"exact_match": 100.0 * em / max(n, 1), "f1": 100.0 * f1 / max(n, 1), "questions": n}
 
 
 def throughput(backend, batch_size, seq_length, iters=20, warmup=3, vocab=1000, seed=0):

@@ -724,3 +724,123 @@ def test_glue_launcher_and_presets_dry_run(tmp_path):
     assert "TASK=mrpc GPUS=8 BATCH=16 ACCUM=1" in out[1]
     assert "--nproc-per-node 8" in out[2] and "--task_name mrpc" in out[2] and "--do_train --do_eval --bf16" in out[2]
     assert "torch.distributed.run" not in out[3] and "--do_train" not in out[3] and "--init_checkpoint ck.pt" in out[3]
+
+
+def _toy_squad(path, n, rng, with_impossible=False):
+    filler = ["dog", "sat", "ran", "on", "mat", "fast", "slow", "house", "tree", "the"]
+    paragraphs = []
+    for i in range(n):
+        words = [rng.choice(filler) for _ in range(rng.randint(6, 14))]
+        impossible = with_impossible and i % 4 == 3
+        qa = {"id": f"q{i}", "question": "the cat"}
+        if not impossible:
+            pos = rng.randrange(len(words))
+            words[pos] = rng.choice(["blue", "red"])
+        context = " ".join(words)
+        if impossible:
+            qa.update({"answers": [], "is_impossible": True})
+        else:
+            start = len(" ".join(words[:pos])) + (1 if pos else 0)
+            qa["answers"] = [{"text": words[pos], "answer_start": start}]
+            assert context[start:start + len(words[pos])] == words[pos]
+        paragraphs.append({"context": context, "qas": [qa]})
+    path.write_text(__import__("json").dumps({"data": [{"title": "toy", "paragraphs": paragraphs}]}))
+
+
+def test_squad_features_windows_and_answers(tmp_path):
+    from conef_b200.data import squad
+    vf, _ = _toy_corpus(tmp_path)
+    tok = data.BertTokenizer(str(vf))
+    words, c2w = squad.split_context("the  cat sat\ton the mat")
+    assert words == ["the", "cat", "sat", "on", "the", "mat"] and c2w[:5] == [0, 0, 0, 0, 0] and c2w[5] == 1
+    ctx = "the dog sat on the blue mat fast the cats ran on the red house slow"
+    doc = {"data": [{"paragraphs": [{"context": ctx, "qas": [
+        {"id": "a", "question": "the cat", "answers": [{"text": "blue mat", "answer_start": ctx.index("blue mat")}]},
+        {"id": "b", "question": "the dog", "answers": [{"text": "cat", "answer_start": ctx.index("cats")}]},
+        {"id": "c", "question": "the tree", "answers": [], "is_impossible": True},
+        {"id": "bad", "question": "x", "answers": [{"text": "zebra", "answer_start": 3}]}]}]}]}
+    f = tmp_path / "s.json"
+    f.write_text(__import__("json").dumps(doc))
+    train = squad.read_squad_examples(str(f), True, with_negative=True)
+    assert [e.qas_id for e in train] == ["a", "b", "c"]              # the mis-annotated answer is dropped
+    assert (train[0].start_word, train[0].end_word) == (5, 6) and train[2].is_impossible
+    assert len(squad.read_squad_examples(str(f), False)) == 4
+    # 17 pieces ("cats" is two), 2 question pieces: max_seq_length 14 leaves room for 9, stride 4 -> windows at 0, 4, 8
+    feats = squad.convert_examples_to_features(train, tok, max_seq_length=14, doc_stride=4, max_query_length=4, is_training=True)
+    fa = [x for x in feats if x.example_index == 0]
+    assert [x.window for x in fa] == [0, 1, 2] and all(len(x.input_ids) == 14 for x in fa)
+    assert fa[0].tokens[:4] == ["[CLS]", "the", "cat", "[SEP]"] and fa[0].tokens[4:13] == ctx.split()[:9]
+    assert (fa[0].start_position, fa[0].end_position) == (4 + 5, 4 + 6)           # "blue mat" inside window 0
+    assert (fa[1].start_position, fa[1].end_position) == (4 + 1, 4 + 2)           # window 1 starts at piece 4
+    assert (fa[2].start_position, fa[2].end_position) == (0, 0)                   # not in window 2: [CLS]
+    # every context piece has exactly one best window, and it is the one where it sits deepest
+    owners = {}
+    for x in fa:
+        for t, (w, best) in enumerate(zip(x.token_to_word, x.max_context)):
+            if best:
+                piece = (x.window * 4) + t - 4
+                assert piece not in owners
+                owners[piece] = x.window
+    assert sorted(owners) == list(range(17)) and owners[0] == 0 and owners[16] == 2 and owners[8] == 1
+    fb = [x for x in feats if x.example_index == 1]
+    s, e = fb[1].start_position, fb[1].end_position
+    assert fb[1].tokens[s:e + 1] == ["cat"]                                       # the answer is one piece of "cats"
+    assert all((x.start_position, x.end_position) == (0, 0) for x in feats if x.example_index == 2)
+    # answers: logits that point at "red house" in the last window; the same span seen from a worse window is ignored
+    ex = squad.read_squad_examples(str(f), False, with_negative=True)[:1]
+    pf = squad.convert_examples_to_features(ex, tok, 14, 4, 4)
+    sl = [[0.0] * 14 for _ in pf]
+    el = [[0.0] * 14 for _ in pf]
+    t_red = pf[2].tokens.index("red")
+    sl[2][t_red], el[2][t_red + 1] = 5.0, 5.0
+    ans, ranked = squad.best_answers(ex, pf, sl, el, n_best_size=5, max_answer_length=4)
+    assert ans == {"a": "red house"} and ranked["a"][0]["score"] == 10.0
+    sl[0][0] = el[0][0] = sl[1][0] = el[1][0] = sl[2][0] = el[2][0] = 9.0          # strong [CLS] in every window
+    assert squad.best_answers(ex, pf, sl, el, 5, 4, with_negative=True)[0] == {"a": ""}
+    assert squad.best_answers(ex, pf, sl, el, 5, 4, with_negative=True, null_score_diff_threshold=20.0)[0] == {"a": "red house"}
+    sc = squad.squad_scores({"a": "Blue mat.", "b": "cats", "c": "", "bad": "zebra"}, str(f))
+    assert sc["questions"] == 4 and sc["exact_match"] == 75.0
+
+
+def test_squad_fine_tuning_driver_learns_a_toy_task(tmp_path):
+    """The answer is the one colour word of the context: after fine-tuning, exact match on held-out contexts is
+    high; predictions, n-best lists and the checkpoint are written; the checkpoint feeds the export tool."""
+    import importlib.util, json, random
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("run_squad", os.path.join(root, "examples/bert_pretraining/run_squad.py"))
+    rs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rs)
+    vf, _ = _toy_corpus(tmp_path)
+    rng = random.Random(3)
+    _toy_squad(tmp_path / "train.json", 96, rng)
+    _toy_squad(tmp_path / "dev.json", 24, rng)
+    out = tmp_path / "out"
+    res = rs.main(["--do_train", "--do_predict", "--do_eval", "--train_file", str(tmp_path / "train.json"),
+                   "--predict_file", str(tmp_path / "dev.json"), "--vocab_file", str(vf), "--bert_model", "tiny", "--no_cuda",
+                   "--max_seq_length", "24", "--doc_stride", "8", "--max_query_length", "4", "--train_batch_size", "16",
+                   "--learning_rate", "1e-3", "--num_train_epochs", "15", "--output_dir", str(out), "--n_best_size", "5"])
+    assert res["train_windows"] == 96 and res["train_steps"] == 90 and res["train_loss_last"] < 0.3 * res["train_loss_first"]
+    assert res["questions"] == 24 and res["exact_match"] >= 85.0 and res["f1"] >= res["exact_match"]
+    preds = json.loads((out / "predictions.json").read_text())
+    assert len(preds) == 24 and sum(p in ("blue", "red") for p in preds.values()) >= 20
+    assert len(json.loads((out / "nbest_predictions.json").read_text())["q0"]) >= 1
+    again = rs.main(["--do_predict", "--do_eval", "--predict_file", str(tmp_path / "dev.json"), "--vocab_file", str(vf),
+                     "--bert_model", "tiny", "--no_cuda", "--max_seq_length", "24", "--doc_stride", "8", "--max_query_length", "4",
+                     "--init_checkpoint", str(out / "pytorch_model.pt"), "--output_dir", str(tmp_path / "out2"), "--n_best_size", "5"])
+    assert again["exact_match"] == res["exact_match"] and again["tensors_not_in_checkpoint"] == 0
+
+
+def test_squad_launcher_and_presets_dry_run(tmp_path):
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ex = os.path.join(root, "examples/bert_pretraining")
+    for f in ("run_squad.sh", "configs/squad_config.sh"):
+        subprocess.run(["bash", "-n", os.path.join(ex, f)], check=True)
+    script = (f"source {ex}/configs/squad_config.sh && squad_b200_8gpu_bf16_conef && "
+              f"DRY_RUN=1 OUT={tmp_path}/o SQUAD_DIR=sq bash {ex}/run_squad.sh && "
+              f"MODE=eval VERSION=2.0 DRY_RUN=1 OUT={tmp_path}/o SQUAD_DIR=sq CHECKPOINT=ck.pt bash {ex}/run_squad.sh")
+    out = subprocess.run(["bash", "-c", script], capture_output=True, text=True, check=True).stdout.splitlines()
+    assert "--nproc-per-node 8" in out[0] and "--train_file sq/train-v1.1.json" in out[0] and "--grad_reducer conef_powersgd" in out[0]
+    assert "--do_predict --do_eval --predict_file sq/dev-v1.1.json" in out[0] and out[0].endswith("--bf16")
+    assert "torch.distributed.run" not in out[1] and "--do_train" not in out[1] and "--version_2_with_negative" in out[1]
+    assert "--predict_file sq/dev-v2.0.json" in out[1] and "--init_checkpoint ck.pt" in out[1]
