@@ -844,3 +844,51 @@ def test_squad_launcher_and_presets_dry_run(tmp_path):
     assert "--do_predict --do_eval --predict_file sq/dev-v1.1.json" in out[0] and out[0].endswith("--bf16")
     assert "torch.distributed.run" not in out[1] and "--do_train" not in out[1] and "--version_2_with_negative" in out[1]
     assert "--predict_file sq/dev-v2.0.json" in out[1] and "--init_checkpoint ck.pt" in out[1]
+
+
+def test_swag_multiple_choice_driver(tmp_path):
+    """Four endings, the right one holds a cat: the shared encoder with a one-logit head learns to pick it."""
+    import csv, importlib.util, random, subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ex = os.path.join(root, "examples/bert_pretraining")
+    spec = importlib.util.spec_from_file_location("run_swag", os.path.join(ex, "run_swag.py"))
+    sw = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sw)
+    vf, _ = _toy_corpus(tmp_path)
+    rng = random.Random(5)
+    filler = ["dog", "sat", "ran", "on", "mat", "fast", "slow", "house", "tree", "blue", "red"]
+    d = tmp_path / "swag"
+    d.mkdir()
+
+    def write(name, n):
+        with open(d / name, "w", newline="") as f:
+            w = csv.writer(f)
+            w.writerow(["", "video-id", "fold-ind", "startphrase", "sent1", "sent2", "gold-source",
+                        "ending0", "ending1", "ending2", "ending3", "label"])
+            for i in range(n):
+                sent = lambda k: " ".join(rng.choice(filler) for _ in range(k))
+                label = rng.randrange(4)
+                ends = [sent(3) for _ in range(4)]
+                ends[label] = "cat " + sent(2)
+                w.writerow([i, "v", i, "", sent(4), "the", "gold", *ends, label])
+    write("train.csv", 64)
+    write("val.csv", 24)
+    rows = sw.read_swag(str(d / "val.csv"))
+    assert len(rows) == 24 and len(rows[0][2]) == 4 and rows[0][1] == "the" and "cat" in rows[0][2][rows[0][3]]
+    tok = data.BertTokenizer(str(vf))
+    ids, seg, mask, lab = sw.choice_features(rows[:2], tok, 16)
+    assert len(ids) == 2 and len(ids[0]) == 4 and len(ids[0][0]) == 16 and lab == [rows[0][3], rows[1][3]]
+    assert ids[0][0][:6] == ids[0][1][:6] and ids[0][rows[0][3]].count(tok.vocab["cat"]) == 1     # shared context
+    out = tmp_path / "out"
+    common = ["--data_dir", str(d), "--vocab_file", str(vf), "--bert_model", "tiny", "--no_cuda", "--max_seq_length", "16",
+              "--output_dir", str(out)]
+    res = sw.main(common + ["--do_train", "--do_eval", "--train_batch_size", "8", "--learning_rate", "1e-3",
+                            "--num_train_epochs", "8"])
+    assert res["num_choices"] == 4 and res["train_steps"] == 64 and res["train_loss_last"] < 0.5 * res["train_loss_first"]
+    assert res["eval_examples"] == 24 and res["eval_accuracy"] >= 0.85
+    again = sw.main(common + ["--do_eval", "--init_checkpoint", str(out / "pytorch_model.pt")])
+    assert again["eval_accuracy"] == res["eval_accuracy"] and again["tensors_not_in_checkpoint"] == 0
+    subprocess.run(["bash", "-n", os.path.join(ex, "run_swag.sh")], check=True)
+    line = subprocess.run(["bash", os.path.join(ex, "run_swag.sh")], capture_output=True, text=True, check=True,
+                          env=dict(os.environ, DRY_RUN="1", OUT=str(tmp_path / "o"), MODE="eval", CHECKPOINT="ck.pt")).stdout
+    assert "run_swag.py" in line and "--do_eval" in line and "--do_train" not in line and "torch.distributed.run" not in line
