@@ -14,11 +14,13 @@ Differences from the reference, on purpose:
     reloaded object could not be queried);
   * ``DenseCSHash3`` uses the same sign hash for its third row in query and
     update (the reference uses two different ones);
-  * CPU tensors are supported (PyTorch ops); CUDA tensors run the sm_100a
-    kernels of ``csrc/sketch.cu``.
+  * CPU tensors are supported (the library's host loops of ``csrc/cpu_ops.cu``, or
+    PyTorch ops without the library); CUDA tensors run the sm_100a kernels of
+    ``csrc/sketch.cu``.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional, Tuple
 
 import numpy as np
@@ -60,6 +62,13 @@ def block_csr_for(device, D: int, W: int, a: int, b: int, sign_offset=ref.SIGN_O
         csr = ref.block_csr(D, W, a, b, sign_offset)
         _TABLE_CACHE[key] = None if csr is None else torch.from_numpy(csr.copy()).to(device)
     return _TABLE_CACHE[key]
+
+
+def _host_native(mat: torch.Tensor, cs: torch.Tensor) -> bool:
+    """CPU tensors take the library's host loops (``csrc/cpu_ops.cu``: one pass per row, no index tensors)
+    when it is built; ``CONEF_BACKEND=torch`` or a missing library leaves the PyTorch ops."""
+    return (not mat.is_cuda and mat.dtype == torch.float32 and cs.dtype == torch.float32 and cs.is_contiguous()
+            and os.environ.get("CONEF_BACKEND", "native") != "torch" and native.available())
 
 
 class DenseCS:
@@ -107,6 +116,9 @@ class DenseCS:
             native.check(native.lib().conef_sketch_query(
                 mat.data_ptr(), self.cs.data_ptr(), int(self.cs.dtype == torch.float16), packed.data_ptr(),
                 self.N, self.D, self.range, float(alpha), native.stream_ptr(mat.device)), "sketch_query")
+        elif _host_native(mat, self.cs):
+            native.lib().conef_cpu_sketch_query(mat.data_ptr(), self.cs.data_ptr(), packed.data_ptr(),
+                                                self.N, self.D, self.range, float(alpha))
         else:
             ref.sketch_query_ref(mat, self.cs.float(), idx, sign, alpha)
 
@@ -118,6 +130,9 @@ class DenseCS:
                 mat.data_ptr(), self.cs.data_ptr(), int(self.cs.dtype == torch.float16), packed.data_ptr(),
                 counts.data_ptr(), self.N, self.D, self.range, float(beta),
                 native.stream_ptr(mat.device)), "sketch_update")
+        elif _host_native(mat, self.cs):
+            native.lib().conef_cpu_sketch_update(mat.data_ptr(), self.cs.data_ptr(), packed.data_ptr(),
+                                                 counts.data_ptr(), self.N, self.D, self.range, float(beta))
         elif self.cs.dtype == torch.float32 and self.cs.is_contiguous():
             ref.sketch_update_ref(mat.float(), self.cs, idx, sign, beta)
         else:

@@ -269,3 +269,27 @@ def test_lowrank_recovers_lowrank_error():
     assert lr.nbytes() == (40 + 30) * 2 * 4
 
 
+
+
+def test_dense_cs_on_cpu_host_loops_equal_the_pytorch_ops(monkeypatch):
+    """CPU tensors go through the library's host loops when it is built; ``CONEF_BACKEND=torch`` keeps the
+    PyTorch ops.  Both must give the same sketch and the same query."""
+    from conef_b200.compressors import DenseCS
+    from conef_b200.ops import native
+    if not native.available():
+        pytest.skip("native library not built")
+    torch.manual_seed(0)
+    v1, v2, g = torch.randn(5, 301), torch.randn(5, 301), torch.randn(5, 301)
+
+    def run(backend):
+        monkeypatch.setenv("CONEF_BACKEND", backend)
+        cs = DenseCS(5, 301, 0.1, device="cpu", seed=3)
+        cs.update(v1.clone(), 0.9)
+        cs.update(v2.clone(), 0.9)
+        out = g.clone()
+        cs.query(out, 0.5)
+        return cs.cs.clone(), out
+    (c_host, q_host), (c_torch, q_torch) = run("native"), run("torch")
+    torch.testing.assert_close(c_host, c_torch, rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(q_host, q_torch, rtol=1e-5, atol=1e-5)
+    assert not torch.equal(q_host, g)
