@@ -892,3 +892,37 @@ def test_swag_multiple_choice_driver(tmp_path):
     line = subprocess.run(["bash", os.path.join(ex, "run_swag.sh")], capture_output=True, text=True, check=True,
                           env=dict(os.environ, DRY_RUN="1", OUT=str(tmp_path / "o"), MODE="eval", CHECKPOINT="ck.pt")).stdout
     assert "run_swag.py" in line and "--do_eval" in line and "--do_train" not in line and "torch.distributed.run" not in line
+
+
+def test_fine_tuning_on_two_gloo_ranks_with_a_compression_hook(tmp_path):
+    """The shared fine-tuning loop under DDP on two CPU ranks with PowerSGD + count-sketch error feedback:
+    both ranks run the same number of steps, rank 0 writes the results, the task is learnt."""
+    import json, random, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    vf, _ = _toy_corpus(tmp_path)
+    rng = random.Random(1)
+    words = ["dog", "sat", "ran", "on", "mat", "fast", "slow", "blue", "red", "house", "tree"]
+
+    def rows(n):
+        out = ["Quality\t#1 ID\t#2 ID\t#1 String\t#2 String"]
+        for i in range(n):
+            a = [rng.choice(words) for _ in range(rng.randint(2, 5))]
+            if i % 2:
+                a[rng.randrange(len(a))] = "cat"
+            out.append(f"{i % 2}\t{i}\t{i}\t{' '.join(a)}\t{' '.join(rng.choice(words) for _ in range(3))}")
+        return "\n".join(out) + "\n"
+    d = tmp_path / "mrpc"
+    d.mkdir()
+    (d / "train.tsv").write_text(rows(96))
+    (d / "dev.tsv").write_text(rows(32))
+    out = tmp_path / "out"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(free_port()), os.path.join(root, "examples/bert_pretraining/run_glue.py"),
+           "--task_name", "mrpc", "--data_dir", str(d), "--vocab_file", str(vf), "--bert_model", "tiny", "--no_cuda",
+           "--max_seq_length", "16", "--output_dir", str(out), "--do_train", "--do_eval", "--train_batch_size", "8",
+           "--learning_rate", "5e-4", "--num_train_epochs", "10", "--grad_reducer", "conef_powersgd",
+           "--matrix_approximation_rank", "2"]
+    subprocess.run(cmd, check=True, capture_output=True, text=True, timeout=600, env=dict(os.environ, CUDA_VISIBLE_DEVICES=""))
+    res = json.loads((out / "eval_results.json").read_text())
+    assert res["world_size"] == 2 and res["grad_reducer"] == "conef_powersgd" and res["train_steps"] == 60
+    assert res["train_loss_last"] < 0.3 * res["train_loss_first"] and res["eval_accuracy"] >= 0.9
