@@ -159,7 +159,7 @@ def build_workload(args, device, world):
             return (torch.randn(batch, 3, 32, 32, generator=gen),), torch.randint(0, 100, (batch,), generator=gen)
         desc = dict(model="WideResNet-28-10 (100 classes)" if not args.small else "WRN-16-2 (smoke)",
                     unit="img/s", dtype="bf16", seq_len=None, reducer="PowerSGD rank 4 + ConEF count sketch 10%, beta 0.9")
-        tkw = dict(channels_last=True)
+        tkw = dict(channels_last=True, cudnn_autotune=os.environ.get("CONEF_CUDNN_AUTOTUNE", "1") == "1")
         if not args.no_graph:      # forward and backward of the twelve blocks as CUDA graphs: the step is host-bound otherwise
             tkw.update(graph_modules=lambda m: list(m.blocks), graph_sample_inputs=make_batch()[0])
         return model, opt, loss_fn, make_batch, batch, ns, torch.bfloat16, desc, tkw
@@ -375,7 +375,8 @@ def main():
                        "l2": "256 MB buffer written between timed steps (outside the per-step event pair)",
                        "timing": "CUDA events per step on the launching stream, mean over steps, max over ranks",
                        "comm": os.environ.get("CONEF_COMM", "auto"), "bucket_cap_mb": tkw.get("bucket_cap_mb", 25.0), "tc": os.environ.get("CONEF_TC", "1"),
-                       "cuda_graph_blocks": int(getattr(trainer, "graphed_modules", 0))},
+                       "cuda_graph_blocks": int(getattr(trainer, "graphed_modules", 0)),
+                       "cudnn_autotune": bool(tkw.get("cudnn_autotune", False))},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
             "wall_s_timed_region": wall,
             "ef_buffer_mb": (state.ef_buffer_bytes() / 1e6) if state is not None else 0.0,

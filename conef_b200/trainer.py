@@ -96,7 +96,8 @@ class DataParallelTrainer:
                  channels_last: bool = False, grad_clip: Optional[float] = None,
                  forward_fn: Optional[Callable] = None,
                  graph_modules: Optional[Callable[[torch.nn.Module], Sequence[torch.nn.Module]]] = None,
-                 graph_sample_inputs: Optional[Sequence[torch.Tensor]] = None):
+                 graph_sample_inputs: Optional[Sequence[torch.Tensor]] = None,
+                 cudnn_autotune: bool = False):
         """``reducer`` is ``None`` (plain all-reduce), an argparse-like namespace with
         ``grad_reducer`` etc. (see :func:`conef_b200.get_comm_hooks`), or a ``(state, hook)`` pair.
         ``optimizer_factory(params)`` builds the optimizer on the wrapped model's parameters.
@@ -104,7 +105,11 @@ class DataParallelTrainer:
         ``graph_modules(model)`` names submodules (each taking and returning one tensor) whose forward and
         backward passes are captured as CUDA graphs from ``graph_sample_inputs`` (one batch of model inputs
         of the training shape): a step of a deep CNN is otherwise bound by the host's launch rate, not by
-        the GPU.  Other input shapes, evaluation mode and CPU runs go through the modules' own code."""
+        the GPU.  Other input shapes, evaluation mode and CPU runs go through the modules' own code.
+        ``cudnn_autotune`` lets cuDNN time its convolution engines on the first call of every shape and keep
+        the fastest (``torch.backends.cudnn.benchmark``, a process-wide switch; for fixed-shape CNN training)."""
+        if cudnn_autotune and torch.cuda.is_available():
+            torch.backends.cudnn.benchmark = True
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() \
                 else torch.device("cpu")

@@ -70,6 +70,8 @@ def parse():
     p.add_argument("--bf16", action="store_true")
     p.add_argument("--cuda_graphs", action="store_true",
                    help="replay the forward and backward passes of the model's blocks as CUDA graphs (fixed batch size)")
+    p.add_argument("--no_cudnn_autotune", action="store_true",
+                   help="keep cuDNN's heuristic choice of convolution engines instead of timing them on first use")
     p.add_argument("--results", default="results")
     p.add_argument("--seed", type=int, default=0)
     return p.parse_args()
@@ -149,7 +151,7 @@ def main():
         lambda p: FusedSGD(p, lr=args.lr, momentum=args.momentum, weight_decay=args.weight_decay,
                            nesterov=args.nesterov),
         F.cross_entropy, reducer=args, device=device, autocast_dtype=torch.bfloat16 if (args.bf16 and cuda) else None,
-        channels_last=cuda, **graph_kw)
+        channels_last=cuda, cudnn_autotune=not args.no_cudnn_autotune, **graph_kw)
     defaults = [round(args.epochs * f) for f in (80 / 150, 120 / 150, 1.0)]
     decay_at = {d if v is None else v for v, d in zip(
         (args.lr_decay_at_epoch1, args.lr_decay_at_epoch2, args.lr_decay_at_epoch3), defaults)}
