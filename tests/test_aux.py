@@ -142,6 +142,14 @@ def test_trainer_checkpoint_resume_over_gloo(single_rank_group, tmp_path):
     tr2.load_state_dict(sd)
     assert tr2.state.iter == 4 and tr2.state.ef_buffer_bytes() == tr.state.ef_buffer_bytes()
     assert torch.isfinite(tr2.step(x, y))
+    # the GPU-only options are inert on a CPU run: no graphs are captured, cuDNN's switch is left alone
+    before = torch.backends.cudnn.benchmark
+    tr3 = DataParallelTrainer(models.LeNet(), lambda p: torch.optim.SGD(p, lr=0.05), F.cross_entropy, reducer=None,
+                              device=torch.device("cpu"), cudnn_autotune=True,
+                              graph_modules=lambda m: [m], graph_sample_inputs=(x,))
+    assert tr3.graphed_modules == 0 and (torch.cuda.is_available() or torch.backends.cudnn.benchmark == before)
+    assert torch.isfinite(tr3.step(x, y))
+    torch.backends.cudnn.benchmark = before
 
 
 def _toy_corpus(tmp_path):
