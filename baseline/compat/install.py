@@ -15,7 +15,8 @@ def ensure_reference_copy(source=None):
     git).  When it is missing and the reference checkout is present, copy it."""
     if os.path.isdir(os.path.join(REF, "communication")):
         return REF
-    source = source or os.environ.get("CONEF_REFERENCE_SRC", "/root/reference")
+    # default: a checkout named `reference` beside this repository
+    source = source or os.environ.get("CONEF_REFERENCE_SRC") or os.path.join(os.path.dirname(os.path.dirname(BASELINE)), "reference")
     if not os.path.isdir(os.path.join(source, "communication")):
         raise FileNotFoundError("no copy of the reference under baseline/_ref and no checkout to copy from")
     os.makedirs(REF, exist_ok=True)

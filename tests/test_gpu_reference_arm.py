@@ -18,7 +18,8 @@ pytestmark = pytest.mark.gpu
 
 
 def _have_reference():
-    return os.path.isdir(REF_SRC) or os.path.isdir("/root/reference/communication")
+    beside = os.path.join(os.environ.get("CONEF_REFERENCE_SRC") or os.path.join(os.path.dirname(REPO), "reference"), "communication")
+    return os.path.isdir(REF_SRC) or os.path.isdir(beside)
 
 
 @pytest.mark.skipif(not _have_reference(), reason="no copy of the reference tree on this machine")
