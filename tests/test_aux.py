@@ -934,3 +934,35 @@ def test_fine_tuning_on_two_gloo_ranks_with_a_compression_hook(tmp_path):
     res = json.loads((out / "eval_results.json").read_text())
     assert res["world_size"] == 2 and res["grad_reducer"] == "conef_powersgd" and res["train_steps"] == 60
     assert res["train_loss_last"] < 0.3 * res["train_loss_first"] and res["eval_accuracy"] >= 0.9
+
+
+def test_cluster_presets_keep_the_recipes_global_batch_and_drive_the_batch_file(tmp_path):
+    import importlib.util, subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ex = os.path.join(root, "examples/bert_pretraining")
+    spec = importlib.util.spec_from_file_location("cluster_preset", os.path.join(ex, "cluster_preset.py"))
+    cp = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(cp)
+    presets = cp.load()
+    assert len(presets) >= 10 and not any(k.startswith(".") for k in presets)
+    for name, v in presets.items():
+        assert cp.global_batch(v) == (8192 if v["PHASE"] == "1" else 4096), name
+        assert name.startswith(f"bert--B200_{v['NNODES']}x{v['GPUS']}x{v['BATCH']}x{v['ACCUM']}")
+    assert presets["bert--B200_4x8x64x4_allreduce"]["REDUCER"] == "allreduce"
+    assert cp.main(["nope"]) == 2
+    for name, body in (("srun", 'echo "SRUN $@"'), ("scontrol", "echo node-a; echo node-b")):
+        path = tmp_path / name
+        path.write_text("#!/bin/bash\n" + body + "\n")
+        path.chmod(0o755)
+    script = (f'eval "$({sys_executable()} {ex}/cluster_preset.py bert--B200_4x8x16x8_phase2)" && '
+              f'OUT={tmp_path}/out bash {ex}/run.sub')
+    env = dict(os.environ, PATH=str(tmp_path) + os.pathsep + os.environ["PATH"], SLURM_JOB_NODELIST="node-[a-d]",
+               SLURM_JOB_NUM_NODES="4", SLURM_SUBMIT_DIR=root)
+    out = subprocess.run(["bash", "-c", script], capture_output=True, text=True, check=True, env=env).stdout
+    assert "--max_seq_length 512" in out and "--train_batch_size 128 --gradient_accumulation_steps 8" in out
+    assert "--learning_rate 4e-3" in out and "--max_steps 1563" in out and "--grad_reducer conef_powersgd" in out
+
+
+def sys_executable():
+    import sys
+    return sys.executable
