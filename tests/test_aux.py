@@ -966,3 +966,31 @@ def test_cluster_presets_keep_the_recipes_global_batch_and_drive_the_batch_file(
 def sys_executable():
     import sys
     return sys.executable
+
+
+def test_dataset_creation_script_runs_both_phases_from_raw_books(tmp_path):
+    """create_datasets.sh chains formatting, sharding and instance creation for sequence lengths 128 and 512."""
+    import glob, subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "examples/bert_pretraining/create_datasets.sh")
+    subprocess.run(["bash", "-n", script], check=True)
+    dry = subprocess.run(["bash", script, "wiki_books"], capture_output=True, text=True, check=True,
+                         env=dict(os.environ, DRY_RUN="1")).stdout.splitlines()
+    assert len(dry) == 5 and "--dataset bookscorpus" in dry[0] and "--dataset wikicorpus_en" in dry[1]
+    assert "--action sharding --dataset books_wiki_en_corpus" in dry[2]
+    assert "--max_seq_length 128 --max_predictions_per_seq 20" in dry[3] and "--max_seq_length 512" in dry[4]
+    assert subprocess.run(["bash", script, "nope"], capture_output=True).returncode == 2
+    wd = tmp_path / "data"
+    books = wd / "download" / "bookscorpus"
+    books.mkdir(parents=True)
+    for k in range(6):
+        (books / f"book{k}.txt").write_text("\n".join(f"Book {k} line {j} ends here." for j in range(4 + k)) + "\n\n")
+    vocab = tmp_path / "vocab.txt"
+    vocab.write_text("\n".join(["[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]", "book", "line", "ends", "here", "."]
+                               + [str(i) for i in range(10)]) + "\n")
+    env = dict(os.environ, WORKING_DIR=str(wd), VOCAB=str(vocab), SHARDS_TRAIN="2", SHARDS_TEST="1", TEST_FRACTION="0.2",
+               CUDA_VISIBLE_DEVICES="")
+    subprocess.run(["bash", script, "books_only"], check=True, timeout=600, env=env, capture_output=True)
+    npz = glob.glob(str(wd / "npz" / "**" / "*.npz"), recursive=True)
+    lengths = sorted({data.pretraining.load_shard(f)["input_ids"].shape[1] for f in npz})
+    assert len(npz) == 6 and lengths == [128, 512]
