@@ -115,8 +115,10 @@ class FusedSGD(Optimizer):
             if first:
                 for p in params:
                     self.state[p]["momentum_buffer"] = torch.empty_like(p, memory_format=torch.preserve_format)
-            if not all(self.state[p]["momentum_buffer"].stride() == p.stride() for p in params):
-                return self._step_torch(group, params)
+            for p in params:       # a buffer restored from a checkpoint of another memory format: re-lay it once
+                buf = self.state[p]["momentum_buffer"]
+                if buf.stride() != p.stride() or buf.dtype != p.dtype or buf.device != p.device:
+                    self.state[p]["momentum_buffer"] = torch.empty_like(p, memory_format=torch.preserve_format).copy_(buf)
         key = tuple((p.data_ptr(), p.grad.data_ptr(), self.state[p]['momentum_buffer'].data_ptr() if mu != 0 else 0)
                     for p in params) + (wd,)
         tab = self._tables.get(gi)

@@ -523,6 +523,20 @@ def test_fused_sgd_takes_channels_last_and_mixed_groups():
         assert native.reset_launch_count() == 1          # the two dense parameters; the third took the PyTorch path
     for a, b in zip(ref_p, own_p):
         torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    # a momentum buffer that comes back from a checkpoint in another memory format is re-laid, not a reason to fall back
+    own_opt.state[own_p[0]]["momentum_buffer"] = own_opt.state[own_p[0]]["momentum_buffer"].contiguous()
+    assert own_opt.state[own_p[0]]["momentum_buffer"].stride() != own_p[0].stride()
+    for i, (a, b) in enumerate(zip(ref_p, own_p)):
+        g = torch.randn_like(a)
+        a.grad = g.clone(memory_format=torch.preserve_format)
+        b.grad = g.clone(memory_format=torch.preserve_format) if i < 2 else g.t().contiguous().t()
+    native.reset_launch_count()
+    ref_opt.step()
+    own_opt.step()
+    assert native.reset_launch_count() == 1
+    assert own_opt.state[own_p[0]]["momentum_buffer"].stride() == own_p[0].stride()
+    for a, b in zip(ref_p, own_p):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
     ptrs = [p.grad.data_ptr() for p in own_p]
     own_opt.zero_grad(set_to_none=False)
     assert [p.grad.data_ptr() for p in own_p] == ptrs and all(float(p.grad.abs().max()) == 0 for p in own_p)
