@@ -631,6 +631,14 @@ def test_model_repository_export_and_in_process_client(tmp_path):
     perf = cli.main(["--local_repository", str(repo), "--model_name", "qa", "--device", "cpu", "--perf",
                      "--batch_size", "4", "--max_seq_length", "16", "--perf_iters", "2", "--perf_vocab", "8"])
     assert perf["seq_per_s"] > 0 and perf["batch_size"] == 4
+    import subprocess
+    csv_path = tmp_path / "perf.csv"
+    subprocess.run(["bash", os.path.join(root, "examples/bert_pretraining/deploy/run_perf.sh"), "1", "3"], check=True,
+                   capture_output=True, timeout=300,
+                   env=dict(os.environ, REPOSITORY=str(repo), MODEL_NAME="qa", SEQ_LENGTH="16", ITERS="2", PERF_VOCAB="8",
+                            DEVICE="cpu", OUT=str(csv_path), CUDA_VISIBLE_DEVICES=""))
+    table = csv_path.read_text().splitlines()
+    assert table[0] == "batch_size,seq_length,seq_per_s,ms_per_request" and [r.split(",")[0] for r in table[1:]] == ["1", "3"]
     with pytest.raises(RuntimeError, match="tritonclient"):
         cli.TritonBackend("127.0.0.1:8000", "qa")
     gold = {"data": [{"paragraphs": [{"context": "c", "qas": [
