@@ -1002,3 +1002,31 @@ def test_dataset_creation_script_runs_both_phases_from_raw_books(tmp_path):
     npz = glob.glob(str(wd / "npz" / "**" / "*.npz"), recursive=True)
     lengths = sorted({data.pretraining.load_shard(f)["input_ids"].shape[1] for f in npz})
     assert len(npz) == 6 and lengths == [128, 512]
+
+
+def test_squad_driver_with_unanswerable_questions(tmp_path):
+    """Version-2 style data: a quarter of the contexts hold no colour word and must get the empty answer."""
+    import importlib.util, json, random
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("run_squad_v2", os.path.join(root, "examples/bert_pretraining/run_squad.py"))
+    rs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rs)
+    vf, _ = _toy_corpus(tmp_path)
+    rng = random.Random(7)
+    _toy_squad(tmp_path / "train.json", 128, rng, with_impossible=True)
+    _toy_squad(tmp_path / "dev.json", 32, rng, with_impossible=True)
+    out = tmp_path / "out"
+    res = rs.main(["--do_train", "--do_predict", "--do_eval", "--version_2_with_negative",
+                   "--train_file", str(tmp_path / "train.json"), "--predict_file", str(tmp_path / "dev.json"),
+                   "--vocab_file", str(vf), "--bert_model", "tiny", "--no_cuda", "--max_seq_length", "24", "--doc_stride", "8",
+                   "--max_query_length", "4", "--train_batch_size", "16", "--learning_rate", "1e-3", "--num_train_epochs", "15",
+                   "--output_dir", str(out), "--n_best_size", "5"])
+    preds = json.loads((out / "predictions.json").read_text())
+    gold = json.loads((tmp_path / "dev.json").read_text())["data"][0]["paragraphs"]
+    empty_gold = {p["qas"][0]["id"] for p in gold if p["qas"][0].get("is_impossible")}
+    assert len(empty_gold) == 8
+    hits = sum(preds[q] == "" for q in empty_gold)
+    false_empty = sum(preds[q] == "" for q in preds if q not in empty_gold)
+    assert res["exact_match"] >= 80.0 and hits >= 6 and false_empty <= 4
+    nbest = json.loads((out / "nbest_predictions.json").read_text())
+    assert all(any(c["text"] == "" for c in nbest[q]) for q in preds)         # the empty answer always competes
