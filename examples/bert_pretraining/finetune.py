@@ -84,7 +84,7 @@ def init_runtime(args, training: bool, port: str) -> Runtime:
         torch.cuda.set_device(device)
     use_ddp = training and (world > 1 or args.grad_reducer != "allreduce")
     own_group = False
-    if use_ddp and not dist.is_initialized():
+    if (use_ddp or world > 1) and not dist.is_initialized():      # several ranks also share evaluation work
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", port)
         dist.init_process_group("nccl" if cuda else "gloo", rank=rank, world_size=world)
@@ -148,8 +148,8 @@ def train(net, args, rt: Runtime, n_items: int, loss_of: Callable) -> dict:
         total = min(total, args.max_steps)
     total = max(total, 1)
     args.start_compression_iter = max(2, int(total * args.start_compression_percentage))
-    decay = [p for n, p in net.named_parameters() if p.dim() > 1]
-    no_decay = [p for n, p in net.named_parameters() if p.dim() <= 1]
+    decay = [p for n, p in net.named_parameters() if p.requires_grad and p.dim() > 1]
+    no_decay = [p for n, p in net.named_parameters() if p.requires_grad and p.dim() <= 1]
     opt = BertAdam([{"params": decay, "weight_decay": 0.01}, {"params": no_decay, "weight_decay": 0.0}],
                    lr=args.learning_rate, warmup=args.warmup_proportion, t_total=total)
     model, state = net, None

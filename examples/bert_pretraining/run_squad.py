@@ -22,6 +22,7 @@ import sys
 import time
 
 import torch
+import torch.distributed as dist
 import torch.nn.functional as F
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -74,6 +75,8 @@ def main(argv=None):
     tok = BertTokenizer(args.vocab_file, do_lower_case=args.do_lower_case)
     net = models.BertForQuestionAnswering(ft.bert_config(args, len(tok.vocab)))
     fresh = ft.load_matching_weights(net, args.init_checkpoint) if args.init_checkpoint else []
+    for p in net.bert.pooler.parameters():      # the span head reads the token outputs only: the pooler gets no
+        p.requires_grad_(False)                 # gradient, which DistributedDataParallel would report as an error
     net = net.to(rt.device)
     if rt.rank == 0:
         os.makedirs(args.output_dir, exist_ok=True)
@@ -95,27 +98,38 @@ def main(argv=None):
         if rt.rank == 0:
             torch.save({"model": net.state_dict()}, os.path.join(args.output_dir, "pytorch_model.pt"))
 
-    if args.do_predict and rt.rank == 0:
+    sharded = args.do_predict and dist.is_initialized() and rt.world > 1      # every rank scores its share of the windows
+    if args.do_predict and (rt.rank == 0 or sharded):
         examples = squad.read_squad_examples(args.predict_file, False, args.version_2_with_negative)
         feats = squad.convert_examples_to_features(examples, tok, args.max_seq_length, args.doc_stride,
                                                    args.max_query_length, is_training=False)
-        ids, seg, mask = inputs(feats)
+        mine = list(range(rt.rank, len(feats), rt.world)) if sharded else list(range(len(feats)))
+        ids, seg, mask = inputs([feats[i] for i in mine])
         net.eval()
         starts, ends, t0 = [], [], time.time()
         with torch.no_grad():
-            for lo in range(0, len(feats), args.predict_batch_size):
+            for lo in range(0, len(mine), args.predict_batch_size):
                 sl = slice(lo, lo + args.predict_batch_size)
                 with rt.amp():
                     s, e = net(ids[sl], seg[sl], mask[sl])
                 starts += s.float().tolist()
                 ends += e.float().tolist()
+        if sharded:
+            parts = [None] * rt.world if rt.rank == 0 else None
+            dist.gather_object((mine, starts, ends), parts, dst=0)
+            if rt.rank == 0:
+                starts, ends = [None] * len(feats), [None] * len(feats)
+                for idx, ss, ee in parts:
+                    for i, a, b in zip(idx, ss, ee):
+                        starts[i], ends[i] = a, b
+    if args.do_predict and rt.rank == 0:
         answers, ranked = squad.best_answers(examples, feats, starts, ends, args.n_best_size, args.max_answer_length,
                                              args.version_2_with_negative, args.null_score_diff_threshold)
         with open(os.path.join(args.output_dir, "predictions.json"), "w") as f:
             json.dump(answers, f, indent=1)
         with open(os.path.join(args.output_dir, "nbest_predictions.json"), "w") as f:
             json.dump(ranked, f, indent=1)
-        results.update({"predict_questions": len(examples), "predict_windows": len(feats),
+        results.update({"predict_questions": len(examples), "predict_windows": len(feats), "predict_ranks": rt.world if sharded else 1,
                         "predict_seq_per_s": len(feats) / max(time.time() - t0, 1e-9)})
         if args.do_eval:
             results.update(squad.squad_scores(answers, args.predict_file))

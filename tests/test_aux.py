@@ -1030,3 +1030,30 @@ def test_squad_driver_with_unanswerable_questions(tmp_path):
     assert res["exact_match"] >= 80.0 and hits >= 6 and false_empty <= 4
     nbest = json.loads((out / "nbest_predictions.json").read_text())
     assert all(any(c["text"] == "" for c in nbest[q]) for q in preds)         # the empty answer always competes
+
+
+def test_squad_prediction_is_shared_by_the_ranks(tmp_path):
+    """Two gloo ranks train, then each scores half of the windows and rank 0 assembles the answers: the file equals
+    what one process predicts from the saved weights."""
+    import json, random, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "examples/bert_pretraining/run_squad.py")
+    vf, _ = _toy_corpus(tmp_path)
+    rng = random.Random(9)
+    _toy_squad(tmp_path / "train.json", 64, rng)
+    _toy_squad(tmp_path / "dev.json", 21, rng)
+    common = ["--predict_file", str(tmp_path / "dev.json"), "--vocab_file", str(vf), "--bert_model", "tiny", "--no_cuda",
+              "--max_seq_length", "16", "--doc_stride", "4", "--max_query_length", "4", "--n_best_size", "5", "--predict_batch_size", "4"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                    "127.0.0.1", "--master-port", str(free_port()), script, "--do_train", "--do_predict", "--do_eval",
+                    "--train_file", str(tmp_path / "train.json"), "--train_batch_size", "8", "--learning_rate", "1e-3",
+                    "--num_train_epochs", "4", "--output_dir", str(tmp_path / "two")] + common,
+                   check=True, capture_output=True, text=True, timeout=600, env=env)
+    two = json.loads((tmp_path / "two" / "results.json").read_text())
+    assert two["world_size"] == 2 and two["predict_ranks"] == 2 and two["predict_windows"] > two["predict_questions"] == 21
+    subprocess.run([sys.executable, script, "--do_predict", "--do_eval", "--init_checkpoint", str(tmp_path / "two" / "pytorch_model.pt"),
+                    "--output_dir", str(tmp_path / "one")] + common, check=True, capture_output=True, text=True, timeout=600, env=env)
+    one = json.loads((tmp_path / "one" / "results.json").read_text())
+    assert one["predict_ranks"] == 1 and one["exact_match"] == two["exact_match"]
+    assert json.loads((tmp_path / "one" / "predictions.json").read_text()) == json.loads((tmp_path / "two" / "predictions.json").read_text())
