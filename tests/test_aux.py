@@ -1057,3 +1057,35 @@ def test_squad_prediction_is_shared_by_the_ranks(tmp_path):
     one = json.loads((tmp_path / "one" / "results.json").read_text())
     assert one["predict_ranks"] == 1 and one["exact_match"] == two["exact_match"]
     assert json.loads((tmp_path / "one" / "predictions.json").read_text()) == json.loads((tmp_path / "two" / "predictions.json").read_text())
+
+
+def test_example_drivers_on_two_gloo_ranks(tmp_path):
+    """Image, language-modelling and translation drivers under torchrun with two CPU ranks and a compression hook
+    each: they finish, and rank 0 reports a finite loss."""
+    import json, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = ["ein mann geht .", "eine frau liest ein buch .", "der hund rennt schnell !", "ein kind spielt ."] * 8
+    tgt = ["a man walks .", "a woman reads a book .", "the dog runs fast !", "a child plays ."] * 8
+    (tmp_path / "train.de").write_text("\n".join(src) + "\n")
+    (tmp_path / "train.en").write_text("\n".join(tgt) + "\n")
+    runs = {
+        "image_classification": ["--model", "lenet", "--epochs", "2", "--steps_per_epoch", "3", "--test_steps", "2",
+                                 "--batch_size", "8", "--grad_reducer", "conef_powersgd", "--start_compression_iter", "2",
+                                 "--results", str(tmp_path), "--name", "run"],
+        "language_modeling": ["--model", "LSTM", "--tied", "--emsize", "32", "--nhid", "32", "--nlayers", "1", "--epochs", "1",
+                              "--batch_size", "8", "--bptt", "8", "--vocab", "50", "--tokens", "2000",
+                              "--grad_reducer", "conef_randomblock", "--start_compression_iter", "2"],
+        "machine_translation": ["--train_src", str(tmp_path / "train.de"), "--train_tgt", str(tmp_path / "train.en"),
+                                "--batch_size", "8", "--emb_size", "32", "--nhead", "2", "--ffn_hid_dim", "64",
+                                "--num_encoder_layers", "1", "--num_decoder_layers", "1", "--start_compression_iter", "2",
+                                "--matrix_approximation_rank", "2", "--grad_reducer", "hefsgd_powersgd"],
+    }
+    for name, args in runs.items():
+        out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                              "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+                              os.path.join(root, "examples", name, "main.py"), *args],
+                             check=True, capture_output=True, text=True, timeout=600,
+                             env=dict(os.environ, CUDA_VISIBLE_DEVICES="")).stdout
+        last = json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
+        loss = last.get("loss", last.get("train_loss"))
+        assert loss is not None and loss == loss and abs(loss) < 1e6, (name, last)
