@@ -1089,3 +1089,19 @@ def test_example_drivers_on_two_gloo_ranks(tmp_path):
         last = json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
         loss = last.get("loss", last.get("train_loss"))
         assert loss is not None and loss == loss and abs(loss) < 1e6, (name, last)
+
+
+def test_bert_pretraining_driver_on_two_gloo_ranks(tmp_path):
+    """Synthetic shards, PowerSGD + count-sketch error feedback, accumulation over two micro-batches, two ranks."""
+    import json, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
+                          os.path.join(root, "examples/bert_pretraining/run_pretraining.py"), "--bert_model", "tiny",
+                          "--max_steps", "6", "--train_batch_size", "4", "--max_seq_length", "32", "--max_predictions_per_seq", "5",
+                          "--output_dir", str(tmp_path / "out"), "--shard_size", "64", "--grad_reducer", "conef_powersgd",
+                          "--matrix_approximation_rank", "2", "--gradient_accumulation_steps", "2"],
+                         check=True, capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, CUDA_VISIBLE_DEVICES="")).stdout
+    summary = json.loads([l for l in out.splitlines() if '"summary"' in l][-1])
+    assert summary["mode"] == "ddp+hook" and summary["final_loss"] == summary["final_loss"] and summary["ef_buffer_mb"] > 0
